@@ -1,0 +1,154 @@
+/* sapient_cuda.h — C ABI of the B200 (sm_100a) CUDA backend for sapient's quantized
+ * decoder-LLM path. Plain pointers and sizes only; no exception crosses the boundary
+ * (the reference's release profile aborts on panic: Cargo.toml:147-152).
+ *
+ * Every entry point returns an int32 status (SP_OK == 0). On failure
+ * sp_cuda_last_error() returns a message for the calling thread.
+ *
+ * The reference items each entry replaces are cited as file:line within the
+ * reference repository (SkidGod4444/sapient v0.6.0).
+ *
+ * Threading: an engine is not re-entrant (the reference wraps its engine in a
+ * Mutex: crates/sapient-generate/src/pipeline.rs:144); calls may arrive on different
+ * OS threads. Several engines may coexist in one process.
+ */
+#ifndef SAPIENT_CUDA_H
+#define SAPIENT_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* status codes (crates/sapient-core/src/error.rs:10-96 collapses onto these) */
+enum {
+    SP_OK = 0,
+    SP_ERR_SHAPE = 1,    /* ShapeMismatch / k not a multiple of the block size */
+    SP_ERR_DTYPE = 2,    /* unsupported dtype */
+    SP_ERR_OOM = 3,      /* device allocation failed */
+    SP_ERR_CUDA = 4,     /* a CUDA call failed */
+    SP_ERR_KV_FULL = 5,  /* context window or page pool exhausted (wgpu_engine.rs:372-374) */
+    SP_ERR_COMM = 6,     /* tensor-parallel exchange timed out */
+    SP_ERR_ARG = 7,      /* null / empty / out-of-range argument */
+    SP_ERR_VOCAB = 8,    /* token id out of vocab range (forward/common.rs:184-186) */
+    SP_ERR_STATE = 9,    /* engine not finalised / missing weight */
+    SP_ERR_IO = 10       /* GGUF file unreadable or malformed */
+};
+
+/* ggml tensor type codes (crates/sapient-io/src/gguf.rs:88-129) */
+enum { SP_F32 = 0, SP_F16 = 1, SP_Q8_0 = 8, SP_Q4_K = 12, SP_Q6_K = 14, SP_BF16 = 30 };
+
+const char* sp_cuda_last_error(void);
+/* number of visible CUDA devices, or 0 */
+int32_t sp_cuda_device_count(void);
+
+/* ── op level: replaces WgpuContext::{upload_q8_0,upload_q4_k,upload_q6_k,matmul_nt*}
+ *    (crates/sapient-backends/wgpu/src/quant.rs:94-480) and kernels::matmul::matmul_nt
+ *    (crates/sapient-backends/cpu/src/kernels/matmul.rs:114-145) ───────────────── */
+typedef struct SpWeight SpWeight;
+
+/* Copies a [n, k] matrix of raw ggml blocks (Tensor::as_quant_blocks layout,
+ * crates/sapient-core/src/tensor.rs:261-268) to the device. nbytes must equal the
+ * dtype's byte_count(n*k) (crates/sapient-core/src/dtype.rs:136-145); K-quants need
+ * k % 256 == 0 and Q8_0 k % 32 == 0 (kernels/matmul.rs:576,863,1112). */
+int32_t sp_cuda_upload_weight(int32_t device, int32_t dtype, int64_t n, int64_t k, const void* host_blocks,
+                              size_t nbytes, SpWeight** out);
+void sp_cuda_free_weight(SpWeight* w);
+/* Tensor::to_f32_vec (crates/sapient-core/src/tensor.rs:341-498): bit-exact f32 values, n*k floats to host. */
+int32_t sp_cuda_dequant(const SpWeight* w, float* out_host);
+/* Y[m,n] = X[m,k] · Wᵀ, host buffers (copies inside). */
+int32_t sp_cuda_matmul_nt(const SpWeight* w, const float* x_host, int64_t m, float* y_host);
+/* Same with device buffers on `stream` (a cudaStream_t, or NULL for the default stream); no synchronisation. */
+int32_t sp_cuda_matmul_nt_dev(const SpWeight* w, const float* x_dev, int64_t m, float* y_dev, void* stream);
+/* Device address and byte size of the resident blocks (for benchmarks that rotate buffers). */
+int32_t sp_cuda_weight_info(const SpWeight* w, int32_t* dtype, int64_t* n, int64_t* k, size_t* nbytes);
+
+/* LlmBackend per-op contract (crates/sapient-models/src/forward/backend.rs:57-115), host buffers. */
+int32_t sp_cuda_rms_norm(int32_t device, const float* x, const float* w, int64_t rows, int64_t dim, float eps, float* y);
+int32_t sp_cuda_layer_norm(int32_t device, const float* x, const float* w, const float* b, int64_t rows, int64_t dim,
+                           float eps, float* y);
+/* x: [n_heads, seq, head_dim] like the reference's [1,H,seq,hd]; positions[seq]. */
+int32_t sp_cuda_rope(int32_t device, const float* x, int64_t n_heads, int64_t seq, int64_t head_dim,
+                     const int64_t* positions, float base, int64_t rotary_dim, float* y);
+/* causal GQA attention: q [H, sq, hd], k/v [Hkv, sk, hd] (f32, stored as fp16 pages on the device), out [H, sq, hd] */
+int32_t sp_cuda_attention(int32_t device, const float* q, const float* k, const float* v, int64_t n_heads,
+                          int64_t n_kv_heads, int64_t sq, int64_t sk, int64_t head_dim, float* out);
+int32_t sp_cuda_silu(int32_t device, const float* x, int64_t n, float* y);
+int32_t sp_cuda_gelu(int32_t device, const float* x, int64_t n, float* y);
+int32_t sp_cuda_add(int32_t device, const float* a, const float* b, int64_t n, float* y);
+int32_t sp_cuda_mul(int32_t device, const float* a, const float* b, int64_t n, float* y);
+/* embed_tokens (forward/common.rs:164-217): rows of a [vocab, hidden] table, dequantised per row. */
+int32_t sp_cuda_embed(const SpWeight* table, const uint32_t* ids, int64_t n, float* out_host);
+/* sampler::argmax (crates/sapient-generate/src/sampler.rs:161-168): last maximum wins. */
+int32_t sp_cuda_argmax(int32_t device, const float* logits, int64_t rows, int64_t n, uint32_t* out);
+
+/* ── engine level: replaces ForwardEngine (crates/sapient-models/src/forward/mod.rs:49-65,381-506)
+ *    in the shape of the resident WgpuForwardEngine (forward/wgpu_engine.rs:93-110,173-341,362-676) ── */
+typedef struct SpEngine SpEngine;
+
+typedef struct SpModelDesc {
+    int32_t arch;        /* 0: llama/qwen2 family (LlamaForward); 1: phi2 (PhiForward parallel block) */
+    int32_t n_layers, hidden, n_heads, n_kv_heads, head_dim, ffn, vocab;
+    int32_t max_ctx;     /* KV window per sequence (kv_cache_ctx, forward/common.rs:25-37) */
+    int32_t rotary_dim;  /* head_dim for full RoPE */
+    float norm_eps, rope_theta;
+    int32_t max_batch;   /* sequence slots (1 = the reference's single-sequence engine) */
+    int32_t max_tokens;  /* tokens per internal forward chunk (prefill is chunked; results do not depend on it) */
+    int32_t device;      /* CUDA device ordinal */
+    int32_t tp_rank, tp_size; /* tensor-parallel placement (1 = single GPU) */
+    int64_t kv_pages;    /* pages of 16 tokens in the pool; 0 = max_batch * ceil(max_ctx/16) */
+} SpModelDesc;
+
+/* ModelInfo::from_gguf_metadata (crates/sapient-hub/src/model_info.rs:234-352) + ForwardEngine::from_weights */
+int32_t sp_cuda_engine_create(const SpModelDesc* desc, SpEngine** out);
+/* One entry of the HF-named weight map that from_weights consumes (forward/wgpu_engine.rs:173-186). dims are
+ * [out, in] for matrices, [n] for vectors; bytes are raw ggml blocks / f32 / f16; the library copies. */
+int32_t sp_cuda_engine_set_tensor(SpEngine* e, const char* hf_name, int32_t dtype, const int64_t* dims, int32_t ndim,
+                                  const void* host_bytes, size_t nbytes);
+/* Resolves weights (tied lm_head fallback: crates/sapient-models/src/weights.rs:88-109), allocates KV pages and
+ * activations. */
+int32_t sp_cuda_engine_finalize(SpEngine* e);
+/* ForwardEngine::from_gguf (forward/mod.rs:223-316): parse a GGUF file (crates/sapient-io/src/gguf.rs:517-778), map
+ * names (crates/sapient-models/src/gguf_weights.rs:61-96,360-455), un-permute llama q/k rows (:114-154), split Phi
+ * qkv (:273-330), create + finalize. max_ctx/max_batch 0 = file's context_length (capped at 8192) / 1. */
+int32_t sp_cuda_engine_from_gguf(const char* path, int32_t device, int32_t max_ctx, int32_t max_batch, SpEngine** out);
+int32_t sp_cuda_engine_desc(const SpEngine* e, SpModelDesc* out);
+void sp_cuda_engine_destroy(SpEngine* e);
+/* Launch on this cudaStream_t instead of the engine's own stream (NULL restores it). */
+int32_t sp_cuda_engine_set_stream(SpEngine* e, void* stream);
+
+/* ForwardEngine::forward_logits (forward/mod.rs:416-426): appends ids to slot 0 (use_cache == 0 resets first, like
+ * wgpu_engine.rs:639-641) and writes last-position logits[vocab] to host. */
+int32_t sp_cuda_forward_logits(SpEngine* e, const uint32_t* ids, size_t n, int32_t use_cache, float* logits_out);
+/* forward_all_logits (reset, all positions) and forward_all_logits_cached (append): out[n * vocab]. */
+int32_t sp_cuda_forward_all_logits(SpEngine* e, const uint32_t* ids, size_t n, float* out);
+int32_t sp_cuda_forward_all_logits_cached(SpEngine* e, const uint32_t* ids, size_t n, float* out);
+/* Same for an explicit sequence slot (batched extension; the reference engine has exactly one sequence). */
+int32_t sp_cuda_forward_slot(SpEngine* e, int32_t slot, const uint32_t* ids, size_t n, int32_t all_positions,
+                             float* logits_out);
+/* One decode step for b sequences: ids[i] is appended to slot slots[i]. Either output may be NULL:
+ * logits_out[b * vocab] (host) and/or argmax_out[b] (host; last-maximum tie rule). */
+int32_t sp_cuda_decode_batch(SpEngine* e, const uint32_t* ids, const int32_t* slots, int32_t b, float* logits_out,
+                             uint32_t* argmax_out);
+/* reset_cache / truncate_cache (forward/mod.rs:381-414): kept = min(n, current). slot < 0 = all slots. */
+int32_t sp_cuda_reset_cache(SpEngine* e, int32_t slot);
+int32_t sp_cuda_truncate_cache(SpEngine* e, int32_t slot, size_t n, size_t* kept);
+int32_t sp_cuda_seq_len(const SpEngine* e, int32_t slot, size_t* len);
+/* backend_label (forward/mod.rs:482-494) -> "cuda"; is_hybrid is always false. */
+int32_t sp_cuda_backend_label(const SpEngine* e, char* buf, size_t cap);
+/* Keep the hidden state after every layer of each forward chunk (for per-layer parity checks); off by default. */
+int32_t sp_cuda_engine_set_trace(SpEngine* e, int32_t on);
+/* Hidden state after `layer` of the most recent forward chunk, [n_tokens, hidden] to host; returns rows in *n_tokens. */
+int32_t sp_cuda_debug_layer_out(SpEngine* e, int32_t layer, float* out, size_t cap_floats, int32_t* n_tokens);
+/* Number of kernels this library has launched since process start (all engines and ops). */
+uint64_t sp_cuda_launch_count(void);
+/* Device bytes held by the weights and by the KV page pool (the reference logs the same at engine-ready time,
+ * forward/wgpu_engine.rs:314-327). */
+int32_t sp_cuda_engine_resident_bytes(const SpEngine* e, uint64_t* weights, uint64_t* kv);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SAPIENT_CUDA_H */

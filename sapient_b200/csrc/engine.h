@@ -1,0 +1,107 @@
+// Host-side resident engine: device weights in raw ggml block layout, a paged fp16 KV
+// cache with per-slot page tables, and the per-layer launch sequence for Llama/Qwen
+// and Phi-2 shaped decoders. Mirrors the contract of the reference's resident GPU
+// engine (crates/sapient-models/src/forward/wgpu_engine.rs:93-110,173-341,362-676)
+// behind ForwardEngine (crates/sapient-models/src/forward/mod.rs:381-506).
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <map>
+#include <string>
+#include <vector>
+
+#include "../../include/sapient_cuda.h"
+#include "kernels.h"
+
+namespace sp {
+
+void set_error(const std::string& msg);
+const char* get_error();
+
+#define SP_CUDA_TRY(expr)                                                                          \
+    do {                                                                                           \
+        cudaError_t _e = (expr);                                                                   \
+        if (_e != cudaSuccess) {                                                                   \
+            ::sp::set_error(std::string(#expr) + ": " + cudaGetErrorString(_e));                   \
+            return _e == cudaErrorMemoryAllocation ? SP_ERR_OOM : SP_ERR_CUDA;                     \
+        }                                                                                          \
+    } while (0)
+
+struct DevTensor {
+    int dtype = 0;
+    std::vector<int64_t> dims;
+    uint8_t* d = nullptr;
+    size_t nbytes = 0;
+    int64_t numel() const { int64_t n = 1; for (auto v : dims) n *= v; return n; }
+};
+
+struct LayerW {
+    const float *n1w = nullptr, *n1b = nullptr, *n2w = nullptr;  // norm weights / bias as f32
+    const DevTensor *q = nullptr, *k = nullptr, *v = nullptr, *o = nullptr;
+    const DevTensor *gate = nullptr, *up = nullptr, *down = nullptr;  // Phi-2: up = fc1, down = fc2
+    const float *qb = nullptr, *kb = nullptr, *vb = nullptr, *ob = nullptr, *upb = nullptr, *downb = nullptr;
+};
+
+class Engine {
+  public:
+    explicit Engine(const SpModelDesc& d);
+    ~Engine();
+    int set_tensor(const char* name, int dtype, const int64_t* dims, int ndim, const void* bytes, size_t nbytes);
+    int finalize();
+    // Appends n tokens (ids[i] to slot slots[i]; consecutive entries of one slot take consecutive
+    // positions). want_all: logits for every token, else only for the last token. Either output may be null.
+    int forward(const uint32_t* ids, const int32_t* slots, int64_t n, bool want_all, float* logits_out,
+                uint32_t* argmax_out);
+    int reset(int slot);
+    int truncate(int slot, size_t n, size_t* kept);
+    int debug_layer_out(int layer, float* out, size_t cap, int32_t* n_tokens);
+
+    SpModelDesc d;
+    cudaStream_t own_stream = nullptr, stream = nullptr;
+    bool finalized = false;
+    bool trace_on = false;
+    std::vector<int> seq_len;
+    uint64_t weight_bytes = 0, kv_bytes = 0;
+
+  private:
+    int run_chunk(const uint32_t* ids, const int32_t* slots, int T, int rows_from, float* logits_out, uint32_t* argmax_out);
+    int alloc_pages(int slot, int new_len);
+    const DevTensor* find(const std::string& name) const;
+    const float* find_f32(const std::string& name, int64_t n);
+    int layer_llama(const LayerW& w, int l, int T);
+    int layer_phi(const LayerW& w, int l, int T);
+    int gemv(const float* x, int ldx, int m, int k, const DevTensor* w0, const float* b0, float* y0, int ldy0,
+             const DevTensor* w1 = nullptr, const float* b1 = nullptr, float* y1 = nullptr, const DevTensor* w2 = nullptr,
+             const float* b2 = nullptr, float* y2 = nullptr, const float* res = nullptr);
+
+    std::map<std::string, DevTensor> tensors_;
+    std::vector<void*> owned_;  // extra device allocations (converted biases, ...)
+    std::vector<LayerW> layers_;
+    const DevTensor *embed_ = nullptr, *lm_head_ = nullptr;
+    const float *final_w_ = nullptr, *final_b_ = nullptr;
+    const float* lm_bias_ = nullptr;
+
+    // paged KV cache
+    KvGeom kv_{};
+    int32_t* d_page_table_ = nullptr;
+    std::vector<int32_t> h_page_table_;
+    std::vector<int> free_pages_, slot_pages_;
+    bool pages_dirty_ = true;
+
+    // activations (sized for max_tokens)
+    float *x_ = nullptr, *h_ = nullptr, *qkv_ = nullptr, *attn_ = nullptr, *gu_ = nullptr, *mid_ = nullptr, *sel_ = nullptr,
+          *logits_ = nullptr, *trace_ = nullptr;
+    uint32_t *d_ids_ = nullptr, *d_argmax_ = nullptr;
+    int32_t *d_tok_slot_ = nullptr, *d_tok_pos_ = nullptr;
+    float2* cos_sin_ = nullptr;
+    int trace_tokens_ = 0;
+    int logit_rows_ = 32;  // rows of the lm_head GEMV per pass
+    // pinned staging
+    uint32_t* p_ids_ = nullptr;
+    int32_t *p_slot_ = nullptr, *p_pos_ = nullptr;
+    float* p_logits_ = nullptr;
+    uint32_t* p_argmax_ = nullptr;
+};
+
+}  // namespace sp

@@ -1,0 +1,214 @@
+// Forward pass of the resident engine: token table + paged-KV bookkeeping on the host,
+// then the per-layer kernel sequence. Layer wiring follows
+//   Llama/Qwen: crates/sapient-models/src/forward/llama.rs:400-539
+//   Phi-2     : crates/sapient-models/src/forward/phi.rs:373-503
+#include <algorithm>
+#include <cstring>
+
+#include "engine.h"
+#include "sp_common.cuh"
+
+namespace sp {
+
+#define SP_TRY(expr)                  \
+    do {                              \
+        int _s = (expr);              \
+        if (_s != SP_OK) return _s;   \
+    } while (0)
+
+int Engine::alloc_pages(int slot, int new_len) {
+    const int need = (new_len + KV_PAGE - 1) / KV_PAGE;
+    while (slot_pages_[slot] < need) {
+        if (free_pages_.empty()) { set_error("KV page pool exhausted"); return SP_ERR_KV_FULL; }
+        const int pg = free_pages_.back();
+        free_pages_.pop_back();
+        h_page_table_[(size_t)slot * kv_.max_pages + slot_pages_[slot]] = pg;
+        slot_pages_[slot]++;
+        pages_dirty_ = true;
+    }
+    return SP_OK;
+}
+
+int Engine::reset(int slot) {
+    size_t kept;
+    if (slot < 0) {
+        for (int s = 0; s < d.max_batch; ++s) SP_TRY(truncate(s, 0, &kept));
+        return SP_OK;
+    }
+    return truncate(slot, 0, &kept);
+}
+
+// truncate_cache (crates/sapient-models/src/forward/llama.rs:307-313): kept = min(n, current). Rollback is
+// O(1): the page-table tail is returned to the pool, the kept pages stay where they are.
+int Engine::truncate(int slot, size_t n, size_t* kept) {
+    if (slot < 0 || slot >= d.max_batch) { set_error("slot out of range"); return SP_ERR_ARG; }
+    const int k = (int)std::min<size_t>(n, (size_t)seq_len[slot]);
+    seq_len[slot] = k;
+    const int keep_pages = (k + KV_PAGE - 1) / KV_PAGE;
+    while (slot_pages_.size() && slot_pages_[slot] > keep_pages) {
+        slot_pages_[slot]--;
+        free_pages_.push_back(h_page_table_[(size_t)slot * kv_.max_pages + slot_pages_[slot]]);
+    }
+    if (kept) *kept = (size_t)k;
+    return SP_OK;
+}
+
+int Engine::gemv(const float* x, int ldx, int m, int k, const DevTensor* w0, const float* b0, float* y0, int ldy0,
+                 const DevTensor* w1, const float* b1, float* y1, const DevTensor* w2, const float* b2, float* y2,
+                 const float* res) {
+    GemvArgs a{};
+    a.x = x; a.ldx = ldx; a.m = m; a.k = k; a.res = res; a.ldres = ldy0;
+    const DevTensor* ws[3] = {w0, w1, w2};
+    const float* bs[3] = {b0, b1, b2};
+    float* ys[3] = {y0, y1, y2};
+    a.nseg = 0;
+    for (int i = 0; i < 3; ++i) {
+        if (!ws[i]) break;
+        a.seg[i].w = ws[i]->d; a.seg[i].bias = bs[i]; a.seg[i].y = ys[i]; a.seg[i].dtype = ws[i]->dtype;
+        a.seg[i].n = (int)ws[i]->dims[0]; a.seg[i].ldy = ldy0;
+        a.nseg++;
+    }
+    SP_CUDA_TRY(launch_gemv(a, stream));
+    return SP_OK;
+}
+
+int Engine::layer_llama(const LayerW& w, int l, int T) {
+    const int H = d.n_heads, Hkv = d.n_kv_heads, hd = d.head_dim, hid = d.hidden, ffn = d.ffn;
+    const int qkv_ld = (H + 2 * Hkv) * hd;
+    SP_CUDA_TRY(launch_rms_norm(x_, w.n1w, T, hid, d.norm_eps, h_, stream));
+    SP_TRY(gemv(h_, hid, T, hid, w.q, w.qb, qkv_, qkv_ld, w.k, w.kb, qkv_ + (size_t)H * hd, w.v, w.vb,
+                qkv_ + (size_t)(H + Hkv) * hd));
+    SP_CUDA_TRY(launch_rope_kv_append(qkv_, T, H, Hkv, hd, d.rotary_dim, cos_sin_, d_tok_slot_, d_tok_pos_, kv_, l, stream));
+    SP_CUDA_TRY(launch_attention(qkv_, qkv_ld, attn_, H * hd, T, H, d_tok_slot_, d_tok_pos_, kv_, l,
+                                 1.0f / sqrtf((float)hd), stream));
+    SP_TRY(gemv(attn_, H * hd, T, H * hd, w.o, w.ob, x_, hid, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, x_));
+    SP_CUDA_TRY(launch_rms_norm(x_, w.n2w, T, hid, d.norm_eps, h_, stream));
+    SP_TRY(gemv(h_, hid, T, hid, w.gate, nullptr, gu_, 2 * ffn, w.up, nullptr, gu_ + ffn));
+    SP_CUDA_TRY(launch_swiglu(gu_, 2 * ffn, ffn, T, mid_, stream));
+    SP_TRY(gemv(mid_, ffn, T, ffn, w.down, nullptr, x_, hid, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, x_));
+    return SP_OK;
+}
+
+int Engine::layer_phi(const LayerW& w, int l, int T) {
+    const int H = d.n_heads, Hkv = d.n_kv_heads, hd = d.head_dim, hid = d.hidden, ffn = d.ffn;
+    const int qkv_ld = (H + 2 * Hkv) * hd;
+    SP_CUDA_TRY(launch_layer_norm(x_, w.n1w, w.n1b, T, hid, d.norm_eps, h_, stream));
+    SP_TRY(gemv(h_, hid, T, hid, w.q, w.qb, qkv_, qkv_ld, w.k, w.kb, qkv_ + (size_t)H * hd, w.v, w.vb,
+                qkv_ + (size_t)(H + Hkv) * hd));
+    SP_CUDA_TRY(launch_rope_kv_append(qkv_, T, H, Hkv, hd, d.rotary_dim, cos_sin_, d_tok_slot_, d_tok_pos_, kv_, l, stream));
+    SP_CUDA_TRY(launch_attention(qkv_, qkv_ld, attn_, H * hd, T, H, d_tok_slot_, d_tok_pos_, kv_, l,
+                                 1.0f / sqrtf((float)hd), stream));
+    // parallel block: x + (attn_out + mlp(h)); both branches read the same normalised input h
+    SP_TRY(gemv(h_, hid, T, hid, w.up, w.upb, mid_, ffn));
+    SP_CUDA_TRY(launch_gelu(mid_, (int64_t)T * ffn, stream));
+    SP_TRY(gemv(attn_, H * hd, T, H * hd, w.o, w.ob, x_, hid, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, x_));
+    SP_TRY(gemv(mid_, ffn, T, ffn, w.down, w.downb, x_, hid, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, x_));
+    return SP_OK;
+}
+
+// One chunk of T <= max_tokens tokens whose (slot, pos) are already staged in p_slot_/p_pos_.
+// Logits are produced for chunk rows [rows_from, T).
+int Engine::run_chunk(const uint32_t* ids, const int32_t* slots, int T, int rows_from, float* logits_out,
+                      uint32_t* argmax_out) {
+    (void)slots;
+    std::memcpy(p_ids_, ids, (size_t)T * 4);
+    SP_CUDA_TRY(cudaMemcpyAsync(d_ids_, p_ids_, (size_t)T * 4, cudaMemcpyHostToDevice, stream));
+    SP_CUDA_TRY(cudaMemcpyAsync(d_tok_slot_, p_slot_, (size_t)T * 4, cudaMemcpyHostToDevice, stream));
+    SP_CUDA_TRY(cudaMemcpyAsync(d_tok_pos_, p_pos_, (size_t)T * 4, cudaMemcpyHostToDevice, stream));
+    if (pages_dirty_) {
+        SP_CUDA_TRY(cudaMemcpyAsync(d_page_table_, h_page_table_.data(), h_page_table_.size() * 4, cudaMemcpyHostToDevice, stream));
+        pages_dirty_ = false;
+    }
+    const int hid = d.hidden;
+    SP_CUDA_TRY(launch_embed(embed_->dtype, embed_->d, hid, d_ids_, T, x_, stream));
+    if (trace_on && !trace_) SP_CUDA_TRY(cudaMalloc((void**)&trace_, (size_t)d.n_layers * d.max_tokens * hid * 4));
+    for (int l = 0; l < d.n_layers; ++l) {
+        SP_TRY(d.arch == 1 ? layer_phi(layers_[l], l, T) : layer_llama(layers_[l], l, T));
+        if (trace_on)
+            SP_CUDA_TRY(cudaMemcpyAsync(trace_ + (size_t)l * d.max_tokens * hid, x_, (size_t)T * hid * 4, cudaMemcpyDeviceToDevice, stream));
+    }
+    trace_tokens_ = T;
+    const int rows = T - rows_from;
+    if (rows > 0 && (logits_out || argmax_out)) {
+        const float* src = x_ + (size_t)rows_from * hid;
+        if (d.arch == 1) SP_CUDA_TRY(launch_layer_norm(src, final_w_, final_b_, rows, hid, d.norm_eps, sel_, stream));
+        else SP_CUDA_TRY(launch_rms_norm(src, final_w_, rows, hid, d.norm_eps, sel_, stream));
+        const int V = d.vocab;
+        for (int r0 = 0; r0 < rows; r0 += logit_rows_) {
+            const int rc = std::min(logit_rows_, rows - r0);
+            GemvArgs a{};
+            a.x = sel_ + (size_t)r0 * hid; a.ldx = hid; a.m = rc; a.k = hid; a.nseg = 1;
+            a.seg[0].w = lm_head_->d; a.seg[0].bias = lm_bias_; a.seg[0].y = logits_; a.seg[0].dtype = lm_head_->dtype;
+            a.seg[0].n = V; a.seg[0].ldy = V;
+            SP_CUDA_TRY(launch_gemv(a, stream));
+            if (argmax_out) {
+                SP_CUDA_TRY(launch_argmax(logits_, rc, V, V, d_argmax_, stream));
+                SP_CUDA_TRY(cudaMemcpyAsync(p_argmax_, d_argmax_, (size_t)rc * 4, cudaMemcpyDeviceToHost, stream));
+            }
+            if (logits_out) SP_CUDA_TRY(cudaMemcpyAsync(p_logits_, logits_, (size_t)rc * V * 4, cudaMemcpyDeviceToHost, stream));
+            SP_CUDA_TRY(cudaStreamSynchronize(stream));
+            if (logits_out) std::memcpy(logits_out + (size_t)r0 * V, p_logits_, (size_t)rc * V * 4);
+            if (argmax_out) std::memcpy(argmax_out + r0, p_argmax_, (size_t)rc * 4);
+        }
+    }
+    SP_CUDA_TRY(cudaStreamSynchronize(stream));
+    return SP_OK;
+}
+
+int Engine::forward(const uint32_t* ids, const int32_t* slots, int64_t n, bool want_all, float* logits_out,
+                    uint32_t* argmax_out) {
+    if (!finalized) { set_error("engine not finalised"); return SP_ERR_STATE; }
+    if (!ids || !slots || n <= 0) { set_error("empty input"); return SP_ERR_ARG; }
+    SP_CUDA_TRY(cudaSetDevice(d.device));
+    // validate everything before touching any state
+    std::vector<int> add(d.max_batch, 0);
+    for (int64_t i = 0; i < n; ++i) {
+        if (slots[i] < 0 || slots[i] >= d.max_batch) { set_error("slot out of range"); return SP_ERR_ARG; }
+        if ((int64_t)ids[i] >= (int64_t)d.vocab) { set_error("token id " + std::to_string(ids[i]) + " out of vocab range"); return SP_ERR_VOCAB; }
+        add[slots[i]]++;
+    }
+    for (int s = 0; s < d.max_batch; ++s)
+        if (seq_len[s] + add[s] > d.max_ctx) { set_error("KV cache full"); return SP_ERR_KV_FULL; }
+    {
+        int need = 0;
+        for (int s = 0; s < d.max_batch; ++s)
+            need += std::max(0, (seq_len[s] + add[s] + KV_PAGE - 1) / KV_PAGE - slot_pages_[s]);
+        if (need > (int)free_pages_.size()) { set_error("KV page pool exhausted"); return SP_ERR_KV_FULL; }
+    }
+    const int C = d.max_tokens;
+    for (int64_t c0 = 0; c0 < n; c0 += C) {
+        const int T = (int)std::min<int64_t>(C, n - c0);
+        for (int i = 0; i < T; ++i) {
+            const int s = slots[c0 + i];
+            p_slot_[i] = s;
+            p_pos_[i] = seq_len[s]++;
+            SP_TRY(alloc_pages(s, seq_len[s]));
+        }
+        const bool last_chunk = c0 + T >= n;
+        int rows_from;
+        float* lo = nullptr;
+        uint32_t* ao = nullptr;
+        if (want_all) {
+            rows_from = 0;
+            lo = logits_out ? logits_out + (size_t)c0 * d.vocab : nullptr;
+            ao = argmax_out ? argmax_out + c0 : nullptr;
+        } else {
+            rows_from = last_chunk ? T - 1 : T;
+            if (last_chunk) { lo = logits_out; ao = argmax_out; }
+        }
+        SP_TRY(run_chunk(ids + c0, slots + c0, T, rows_from, lo, ao));
+    }
+    return SP_OK;
+}
+
+int Engine::debug_layer_out(int layer, float* out, size_t cap, int32_t* n_tokens) {
+    if (!trace_ || layer < 0 || layer >= d.n_layers) { set_error("no trace (enable tracing before the forward)"); return SP_ERR_STATE; }
+    const size_t n = (size_t)trace_tokens_ * d.hidden;
+    if (cap < n) { set_error("trace buffer too small"); return SP_ERR_ARG; }
+    SP_CUDA_TRY(cudaSetDevice(d.device));
+    SP_CUDA_TRY(cudaMemcpy(out, trace_ + (size_t)layer * d.max_tokens * d.hidden, n * 4, cudaMemcpyDeviceToHost));
+    if (n_tokens) *n_tokens = trace_tokens_;
+    return SP_OK;
+}
+
+}  // namespace sp

@@ -1,0 +1,71 @@
+// Launch wrappers of the sm_100a kernels (definitions in kernels.cu). All pointers are
+// device pointers; every launcher enqueues on `st` and returns cudaGetLastError().
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace sp {
+
+// One weight matrix of a grouped dequant-GEMV: rows [N, K] of raw ggml blocks.
+struct GemvSeg {
+    const uint8_t* w;   // raw blocks, row-major
+    const float* bias;  // [n] or null
+    float* y;           // output base; element (m, r) at y[m * ldy + r]
+    int dtype;
+    int n;
+    int ldy;
+    int pad_;
+};
+
+struct GemvArgs {
+    GemvSeg seg[3];
+    int nseg;
+    int k;
+    int m;
+    int ldx;
+    const float* x;     // [m, k], row stride ldx
+    const float* res;   // optional residual added to segment 0's output (same indexing as y), may alias y
+    int ldres;
+    int pad_;
+};
+
+// Paged KV cache geometry: half pool[layer][page][2 (K,V)][n_kv][KV_PAGE][head_dim].
+struct KvGeom {
+    __half* pool;
+    const int32_t* page_table;  // [n_slots, max_pages]
+    int n_pages, n_kv, head_dim, max_pages;
+};
+
+// Kernels launched by this library since process start.
+uint64_t launch_count();
+
+cudaError_t launch_dequant(int dtype, const uint8_t* w, int64_t n, int64_t k, float* out, cudaStream_t st);
+cudaError_t launch_gemv(const GemvArgs& a, cudaStream_t st);
+cudaError_t launch_embed(int dtype, const uint8_t* table, int64_t hidden, const uint32_t* ids, int n_tok, float* out,
+                         cudaStream_t st);
+cudaError_t launch_rms_norm(const float* x, const float* w, int rows, int dim, float eps, float* y, cudaStream_t st);
+cudaError_t launch_layer_norm(const float* x, const float* w, const float* b, int rows, int dim, float eps, float* y,
+                              cudaStream_t st);
+// In-place NEOX rotation of the q heads of qkv[T, (H+2Hkv)*hd]; rotated k and raw v are
+// written as fp16 into the paged cache at (slot, pos) of each token.
+cudaError_t launch_rope_kv_append(float* qkv, int n_tok, int n_heads, int n_kv, int head_dim, int rotary_dim,
+                                  const float2* cos_sin, const int32_t* tok_slot, const int32_t* tok_pos, KvGeom kv,
+                                  int layer, cudaStream_t st);
+// Rotation only (no cache): x[T, n_heads*hd] in place. Used by the standalone RoPE op.
+cudaError_t launch_rope(float* x, int n_tok, int n_heads, int head_dim, int rotary_dim, const float2* cos_sin,
+                        const int32_t* tok_pos, int ld, cudaStream_t st);
+// Causal GQA attention of each token against keys 0..pos of its slot, online softmax.
+cudaError_t launch_attention(const float* q, int ldq, float* out, int ldo, int n_tok, int n_heads, const int32_t* tok_slot,
+                             const int32_t* tok_pos, KvGeom kv, int layer, float scale, cudaStream_t st);
+cudaError_t launch_swiglu(const float* gate_up, int ld, int ffn, int rows, float* out, cudaStream_t st);
+cudaError_t launch_gelu(float* x, int64_t n, cudaStream_t st);
+cudaError_t launch_silu(float* x, int64_t n, cudaStream_t st);
+cudaError_t launch_add(const float* a, const float* b, float* y, int64_t n, cudaStream_t st);
+cudaError_t launch_mul(const float* a, const float* b, float* y, int64_t n, cudaStream_t st);
+// Row-wise argmax with the reference's tie rule (the LAST maximum wins).
+cudaError_t launch_argmax(const float* logits, int rows, int n, int ld, uint32_t* out, cudaStream_t st);
+cudaError_t launch_gather_rows(const float* src, int ld, const int32_t* rows, int n_rows, int dim, float* dst,
+                               cudaStream_t st);
+
+}  // namespace sp

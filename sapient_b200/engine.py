@@ -1,0 +1,169 @@
+"""`ForwardEngine` for the CUDA backend: the interface the reference's generation
+pipeline drives (crates/sapient-models/src/forward/mod.rs:381-506), implemented by
+the resident engine inside libsapient_cuda.so.
+
+    eng = ForwardEngine.from_weights(cfg, weights)      # HF-named weight map
+    eng = ForwardEngine.from_gguf("model.gguf")         # GGUF file
+    logits = eng.forward_logits(ids, use_cache=True)    # last-position logits, f32 [vocab]
+
+Batched extensions (no counterpart in the single-sequence reference engine):
+`forward_slot`, `decode_batch`. Greedy speculative decoding lives in
+sapient_b200/speculative.py.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import _lib
+from ._lib import SapientCudaError, SpModelDesc, check, lib
+
+
+def _p(a: np.ndarray):
+    return a.ctypes.data_as(C.c_void_p)
+
+
+def _ids(ids) -> np.ndarray:
+    return np.ascontiguousarray(ids, dtype=np.uint32).reshape(-1)
+
+
+class ForwardEngine:
+    def __init__(self, handle, desc: SpModelDesc):
+        self._h = handle
+        self.desc = desc
+        self.vocab = desc.vocab
+
+    # ── construction ────────────────────────────────────────────────────────
+    @classmethod
+    def from_weights(cls, cfg: dict, weights: dict, device: int = 0, max_batch: int = 1, max_tokens: int = 256,
+                     kv_pages: int = 0) -> "ForwardEngine":
+        """cfg: arch ('llama'|'qwen2'|'phi2'), n_layers, hidden, n_heads, n_kv_heads, head_dim, ffn, vocab,
+        max_ctx, rotary_dim (optional), norm_eps, rope_theta. weights: name -> (ggml dtype, dims, uint8 bytes)
+        with HF names and [out, in] dims, as the reference's GGUF name map yields."""
+        d = SpModelDesc()
+        d.arch = 1 if cfg["arch"] in ("phi2", "phi") else 0
+        d.n_layers, d.hidden, d.n_heads, d.n_kv_heads = cfg["n_layers"], cfg["hidden"], cfg["n_heads"], cfg["n_kv_heads"]
+        d.head_dim, d.ffn, d.vocab, d.max_ctx = cfg["head_dim"], cfg["ffn"], cfg["vocab"], cfg["max_ctx"]
+        d.rotary_dim = cfg.get("rotary_dim") or cfg["head_dim"]
+        d.norm_eps, d.rope_theta = cfg["norm_eps"], cfg["rope_theta"]
+        d.max_batch, d.max_tokens, d.device, d.tp_rank, d.tp_size, d.kv_pages = max_batch, max_tokens, device, 0, 1, kv_pages
+        h = C.c_void_p()
+        check(lib().sp_cuda_engine_create(C.byref(d), C.byref(h)))
+        try:
+            for name, (dtype, dims, raw) in weights.items():
+                if hasattr(raw, "detach"):
+                    raw = raw.detach().cpu().numpy()
+                raw = np.ascontiguousarray(raw, dtype=np.uint8).reshape(-1)
+                dd = (C.c_int64 * len(dims))(*dims)
+                check(lib().sp_cuda_engine_set_tensor(h, name.encode(), dtype, dd, len(dims), _p(raw), raw.size))
+            check(lib().sp_cuda_engine_finalize(h))
+        except Exception:
+            lib().sp_cuda_engine_destroy(h)
+            raise
+        return cls(h, d)
+
+    @classmethod
+    def from_gguf(cls, path: str, device: int = 0, max_ctx: int = 0, max_batch: int = 1) -> "ForwardEngine":
+        h = C.c_void_p()
+        check(lib().sp_cuda_engine_from_gguf(str(path).encode(), device, max_ctx, max_batch, C.byref(h)))
+        d = SpModelDesc()
+        check(lib().sp_cuda_engine_desc(h, C.byref(d)))
+        return cls(h, d)
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            lib().sp_cuda_engine_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # ── the reference's ForwardEngine surface ───────────────────────────────
+    def forward_logits(self, input_ids, use_cache: bool = True) -> np.ndarray:
+        ids = _ids(input_ids)
+        if ids.size == 0:
+            raise SapientCudaError(_lib.SP_ERR_ARG, "empty input")
+        out = np.empty(self.vocab, np.float32)
+        check(lib().sp_cuda_forward_logits(self._h, _p(ids), ids.size, int(use_cache), _p(out)))
+        return out
+
+    def forward_all_logits(self, input_ids) -> np.ndarray:
+        ids = _ids(input_ids)
+        if ids.size == 0:
+            raise SapientCudaError(_lib.SP_ERR_ARG, "empty input")
+        out = np.empty((ids.size, self.vocab), np.float32)
+        check(lib().sp_cuda_forward_all_logits(self._h, _p(ids), ids.size, _p(out)))
+        return out
+
+    def forward_all_logits_cached(self, input_ids) -> np.ndarray:
+        ids = _ids(input_ids)
+        if ids.size == 0:
+            raise SapientCudaError(_lib.SP_ERR_ARG, "empty input")
+        out = np.empty((ids.size, self.vocab), np.float32)
+        check(lib().sp_cuda_forward_all_logits_cached(self._h, _p(ids), ids.size, _p(out)))
+        return out
+
+    def reset_cache(self, slot: int = -1) -> None:
+        check(lib().sp_cuda_reset_cache(self._h, slot))
+
+    def truncate_cache(self, n: int, slot: int = 0) -> int:
+        kept = C.c_size_t()
+        check(lib().sp_cuda_truncate_cache(self._h, slot, n, C.byref(kept)))
+        return int(kept.value)
+
+    def backend_label(self) -> str:
+        buf = C.create_string_buffer(64)
+        check(lib().sp_cuda_backend_label(self._h, buf, 64))
+        return buf.value.decode()
+
+    def is_hybrid(self) -> bool:
+        return False
+
+    def embed(self, input_ids):
+        raise SapientCudaError(_lib.SP_ERR_ARG, "embed() is not supported by the CUDA engine")
+
+    # ── batched extensions ──────────────────────────────────────────────────
+    def seq_len(self, slot: int = 0) -> int:
+        n = C.c_size_t()
+        check(lib().sp_cuda_seq_len(self._h, slot, C.byref(n)))
+        return int(n.value)
+
+    def forward_slot(self, slot: int, input_ids, all_positions: bool = False) -> np.ndarray:
+        ids = _ids(input_ids)
+        if ids.size == 0:
+            raise SapientCudaError(_lib.SP_ERR_ARG, "empty input")
+        out = np.empty((ids.size, self.vocab) if all_positions else (self.vocab,), np.float32)
+        check(lib().sp_cuda_forward_slot(self._h, slot, _p(ids), ids.size, int(all_positions), _p(out)))
+        return out
+
+    def decode_batch(self, input_ids, slots, want_logits: bool = True, want_argmax: bool = False):
+        """One token per sequence slot. Returns (logits [b, vocab] or None, argmax [b] or None)."""
+        ids = _ids(input_ids)
+        sl = np.ascontiguousarray(slots, dtype=np.int32).reshape(-1)
+        assert ids.size == sl.size
+        logits = np.empty((ids.size, self.vocab), np.float32) if want_logits else None
+        am = np.empty(ids.size, np.uint32) if want_argmax else None
+        check(lib().sp_cuda_decode_batch(self._h, _p(ids), _p(sl), ids.size, _p(logits) if want_logits else None,
+                                         _p(am) if want_argmax else None))
+        return logits, am
+
+    def set_stream(self, stream: int) -> None:
+        check(lib().sp_cuda_engine_set_stream(self._h, C.c_void_p(stream)))
+
+    def set_trace(self, on: bool) -> None:
+        check(lib().sp_cuda_engine_set_trace(self._h, int(on)))
+
+    def layer_out(self, layer: int) -> np.ndarray:
+        buf = np.empty(self.desc.max_tokens * self.desc.hidden, np.float32)
+        n = C.c_int32()
+        check(lib().sp_cuda_debug_layer_out(self._h, layer, _p(buf), buf.size, C.byref(n)))
+        return buf[: n.value * self.desc.hidden].reshape(n.value, self.desc.hidden).copy()
+
+    def resident_bytes(self) -> tuple[int, int]:
+        w, kv = C.c_uint64(), C.c_uint64()
+        check(lib().sp_cuda_engine_resident_bytes(self._h, C.byref(w), C.byref(kv)))
+        return int(w.value), int(kv.value)

@@ -3,7 +3,7 @@ blocks, model weight sets in the layouts the reference's GGUF loader produces,
 and a GGUF writer.
 
 The quantisers are simple min/max quantisers of this project (not ggml's search):
-both the CUDA path and the CPU oracle decode the same bytes, so quantisation
+both the CUDA path and any CPU checker decode the same bytes, so quantisation
 quality does not enter any comparison. Everything is written with torch ops so
 the same code builds tiny CPU test models and multi-GB models on a GPU.
 

@@ -1,0 +1,89 @@
+"""CPU-side checks of the C-ABI library: it loads, exports every declared symbol, and
+fails loudly (never falls back) when there is no CUDA device."""
+import ctypes as C
+import os
+import re
+
+import numpy as np
+import pytest
+
+from sapient_b200 import _lib
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "sapient_cuda.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(sp_cuda_\w+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    L = _lib.lib()
+    names = declared_symbols()
+    assert len(names) >= 35
+    for n in names:
+        assert hasattr(L, n), f"{n} declared in include/sapient_cuda.h but not exported"
+    assert set(names) == set(_lib.SIGNATURES), set(names) ^ set(_lib.SIGNATURES)
+
+
+def test_desc_struct_layout_matches_header():
+    # 17 int32/float fields then an int64: 4*17 = 68 -> padded to 72, + 8
+    assert C.sizeof(_lib.SpModelDesc) == 80
+
+
+def test_host_side_validation_needs_no_gpu():
+    L = _lib.lib()
+    h = C.c_void_p()
+    buf = np.zeros(144, np.uint8)
+    # k % 256 != 0 for a K-quant is rejected before any CUDA call (kernels/matmul.rs:863-865)
+    st = L.sp_cuda_upload_weight(0, 12, 1, 128, buf.ctypes.data_as(C.c_void_p), 72, C.byref(h))
+    assert st == _lib.SP_ERR_SHAPE and b"256" in L.sp_cuda_last_error()
+    st = L.sp_cuda_upload_weight(0, 8, 1, 48, buf.ctypes.data_as(C.c_void_p), 51, C.byref(h))
+    assert st == _lib.SP_ERR_SHAPE
+    st = L.sp_cuda_upload_weight(0, 99, 1, 256, buf.ctypes.data_as(C.c_void_p), 144, C.byref(h))
+    assert st == _lib.SP_ERR_DTYPE
+    st = L.sp_cuda_upload_weight(0, 12, 1, 256, buf.ctypes.data_as(C.c_void_p), 100, C.byref(h))
+    assert st == _lib.SP_ERR_SHAPE
+    assert L.sp_cuda_forward_logits(None, None, 0, 1, None) == _lib.SP_ERR_ARG
+
+
+def test_gguf_errors_before_any_device_work(tmp_path):
+    L = _lib.lib()
+    h = C.c_void_p()
+    assert L.sp_cuda_engine_from_gguf(str(tmp_path / "nope.gguf").encode(), 0, 0, 1, C.byref(h)) == _lib.SP_ERR_IO
+    bad = tmp_path / "bad.gguf"
+    bad.write_bytes(b"NOPE" + b"\0" * 64)
+    assert L.sp_cuda_engine_from_gguf(str(bad).encode(), 0, 0, 1, C.byref(h)) == _lib.SP_ERR_IO
+    assert b"magic" in L.sp_cuda_last_error()
+    import gguf
+
+    p = tmp_path / "arch.gguf"
+    w = gguf.GGUFWriter(str(p), "gpt2")
+    w.add_uint32("gpt2.block_count", 1)
+    w.add_tensor("token_embd.weight", np.zeros((2, 32), np.float32))
+    w.write_header_to_file(); w.write_kv_data_to_file(); w.write_tensors_to_file(); w.close()
+    assert L.sp_cuda_engine_from_gguf(str(p).encode(), 0, 0, 1, C.byref(h)) == _lib.SP_ERR_DTYPE
+    assert b"gpt2" in L.sp_cuda_last_error()
+
+
+def test_no_device_is_an_error_not_a_fallback():
+    L = _lib.lib()
+    if L.sp_cuda_device_count() > 0:
+        pytest.skip("a CUDA device is present")
+    d = _lib.SpModelDesc()
+    h = C.c_void_p()
+    assert L.sp_cuda_engine_create(C.byref(d), C.byref(h)) == _lib.SP_ERR_CUDA
+    from sapient_b200 import ops
+
+    with pytest.raises(_lib.SapientCudaError):
+        ops.rms_norm(np.ones((1, 4), np.float32), None, 1e-5)
+
+
+def test_product_never_imports_the_oracle():
+    pkg = os.path.join(ROOT, "sapient_b200")
+    for dirpath, _, files in os.walk(pkg):
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh", ".h", ".cpp")):
+                src = open(os.path.join(dirpath, f)).read()
+                assert "oracle" not in src.lower(), f"{f} mentions the oracle"
