@@ -1,0 +1,305 @@
+"""Benchmark of the quantized decode path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload (config.workload): batch-1 greedy decode of a Llama-3-8B-shaped decoder with
+random-init N(0, 0.02) weights quantised to the Q4_K_M-like GGUF block layout
+(Q4_K; Q6_K for output/token_embd and for attn_v/ffn_down on even layers), after a
+128-token random prompt. One step = one decode step (one token per sequence).
+
+  value      tokens/s with the loop resident on the device (token ids never leave HBM)
+  e2e        tokens/s through ForwardEngine.forward_logits with host buffers: per step the
+             token id goes host->device and the full f32 logits come back
+  roofline   the dequant-GEMV kernel: algorithmic weight bytes per step / its device time
+  cpu_baseline  the CPU restatement of the reference's x86 path on this host's cores
+
+--impl reference times that CPU restatement alone (the reference is Rust and cannot be
+built here), same metric/config, all host threads.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+MODEL = "llama8b"
+PROMPT = 128
+CPU_PROMPT = 4
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return json.load(open(p)), "measured"
+        except Exception:
+            pass
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.idx, self.rows, self.proc, self.thr = gpu_index, [], None, None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                                          "-i", str(self.idx)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+            return
+        def pump():
+            for line in self.proc.stdout:
+                self.rows.append((time.perf_counter(), line.strip()))
+        self.thr = threading.Thread(target=pump, daemon=True)
+        self.thr.start()
+
+    def stop(self):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=3)
+            except Exception:
+                self.proc.kill()
+
+    def summary(self, t0: float, t1: float) -> dict:
+        sm, mx, reasons, power = [], [], set(), []
+        for t, line in self.rows:
+            if t < t0 or t > t1 + 0.05:
+                continue
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 8:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2])); power.append(float(f[3]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[4:8]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)), "reasons": sorted(reasons),
+                "samples": len(sm), "power_w_max": float(max(power))}
+
+
+def build_weights(device: str, seed: int = 3000):
+    import torch
+
+    from sapient_b200 import synth
+
+    cfg, W = synth.build_model(synth.CONFIGS[MODEL], seed=seed, device=device, max_ctx=4096)
+    Wn = synth.weights_to_numpy(W)
+    del W
+    if device != "cpu":
+        torch.cuda.empty_cache()
+    return cfg, Wn
+
+
+def step_weight_bytes(cfg, W) -> int:
+    """Algorithmic weight bytes one decode step streams: every 2-D matrix once (lm_head included; the
+    embedding gather touches one row)."""
+    total = 0
+    for name, (dt, dims, raw) in W.items():
+        if len(dims) == 2 and "embed_tokens" not in name:
+            total += raw.size
+    if cfg.get("tied"):
+        total += W["model.embed_tokens.weight"][2].size
+    return total
+
+
+def cpu_decode_rate(cfg, W, steps: int, budget_s: float):
+    """tokens/s of the CPU restatement: `steps` decode steps after a short prompt, stopping early at budget_s."""
+    from oracle import oracle
+
+    eng = oracle.OracleEngine(cfg, W, kv_mode=0)
+    ids = np.random.default_rng(1).integers(0, cfg["vocab"], CPU_PROMPT).astype(np.uint32)
+    logits = eng.forward_logits(ids, True)
+    tok = oracle.argmax(logits)
+    done, t0 = 0, time.perf_counter()
+    while done < steps:
+        logits = eng.forward_logits([tok], True)
+        tok = oracle.argmax(logits)
+        done += 1
+        if time.perf_counter() - t0 > budget_s:
+            break
+    dt = time.perf_counter() - t0
+    return done / dt, done, oracle.num_threads()
+
+
+def config_dict(cfg, n_gpus: int, mode: str) -> dict:
+    return {"workload": f"{MODEL} (Llama-3-8B-shaped, L32 h4096 32q/8kv hd128 ffn14336 V128256) Q4_K_M-like GGUF blocks, "
+                        f"batch-1 greedy decode after a {PROMPT}-token random prompt, fp16 paged KV (16-token pages)",
+            "batch": 1, "prompt_len": PROMPT, "kv": "fp16 paged/16", "parallelism": mode if n_gpus > 1 else "single",
+            "l2": "each step streams 4.6 GB of weights (>> 126 MB L2), no flush needed"}
+
+
+def run_reference(args, rank: int, world: int) -> None:
+    if rank != 0:
+        return
+    import torch
+
+    dev = "cuda" if torch.cuda.is_available() else "cpu"
+    cfg, W = build_weights(dev)
+    # bounded sample: at most ~150 s of CPU work in total
+    n_warm = min(args.warmup, 1)
+    _, _, threads = cpu_decode_rate(cfg, W, max(n_warm, 1), 30.0)
+    rate, done, threads = cpu_decode_rate(cfg, W, args.steps, 120.0)
+    sample = f"{done} decode steps after a {CPU_PROMPT}-token prompt (of {args.steps} requested), full model, {threads} threads"
+    line = {"impl": "reference", "metric": "decode_tokens_per_s", "value": rate, "unit": "tok/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 / rate, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": config_dict(cfg, args.gpus, "replicas"),
+            "cpu_baseline": {"value": rate, "unit": "tok/s", "cores": threads, "kind": "port", "sample": sample},
+            "e2e": {"value": rate, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "note": "CPU restatement (C++) of sapient's x86_64 path; the Rust reference cannot be built without cargo"}
+    print(json.dumps(line), flush=True)
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+    args.warmup = max(args.warmup, 3)
+
+    import torch
+    import torch.distributed as dist
+
+    from sapient_b200 import ops
+    from sapient_b200.engine import ForwardEngine
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: this backend has no CPU fallback")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    cfg, W = build_weights(f"cuda:{local}")
+    wbytes = step_weight_bytes(cfg, W)
+    eng = ForwardEngine.from_weights(cfg, W, device=local, max_batch=1, max_tokens=256)
+    stream = torch.cuda.current_stream()
+    eng.set_stream(stream.cuda_stream)
+    K, Wm = args.steps, args.warmup
+    rng = np.random.default_rng(0)
+    prompt = rng.integers(0, cfg["vocab"], PROMPT).astype(np.uint32)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ── value: device-resident greedy loop ──
+    logits = eng.forward_logits(prompt, use_cache=False)
+    first = np.array([int(np.flatnonzero(logits == logits.max())[-1])], np.uint32)
+    toks = eng.decode_greedy(first, [0], Wm)  # warm-up (captures the step graph)
+    sampler = ClockSampler(local)
+    sampler.start()
+    time.sleep(0.3)
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches0 = ops.launch_count()
+    barrier()
+    t_wall0 = time.perf_counter()
+    ev0.record(stream)
+    eng.decode_greedy(toks[-1], [0], K, fetch=False)
+    ev1.record(stream)
+    barrier()
+    t_wall1 = time.perf_counter()
+    launches = ops.launch_count() - launches0
+    dev_ms = ev0.elapsed_time(ev1)
+    kv_ctx_mid = PROMPT + Wm + K // 2
+
+    # ── e2e: public API with host buffers, every step ──
+    eng.truncate_cache(PROMPT)
+    tok = int(first[0])
+    for _ in range(Wm):
+        lg = eng.forward_logits([tok], True)
+        tok = int(np.flatnonzero(lg == lg.max())[-1])
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(K):
+        lg = eng.forward_logits(np.array([tok], np.uint32), True)
+        tok = int(lg.argmax())
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    time.sleep(0.2)
+    sampler.stop()
+    clocks = sampler.summary(t_wall0, t_wall1)
+
+    # ── per-family device time (events around every launch, graphs off) ──
+    eng.truncate_cache(PROMPT)
+    eng.set_profile(True)
+    P = min(K, 16)
+    tok = int(first[0])
+    for i in range(P + 2):
+        if i == 2:
+            eng.profile_read(reset=True)
+        _, am = eng.decode_batch([tok], [0], want_logits=False, want_argmax=True)
+        tok = int(am[0])
+    prof = eng.profile_read(reset=True)
+    eng.set_profile(False)
+    gemv_ms, gemv_n = prof["gemv"]
+    fam_ms = {k: v[0] / P for k, v in prof.items()}
+
+    t = torch.tensor([dev_ms, e2e_s * 1000.0], device=f"cuda:{local}", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    dev_ms, e2e_ms = float(t[0]), float(t[1])
+
+    if rank == 0:
+        peaks, peak_src = measured_peaks()
+        value = world * K / (dev_ms / 1000.0)
+        kv_bytes = 2 * cfg["n_layers"] * cfg["n_kv_heads"] * cfg["head_dim"] * 2 * kv_ctx_mid
+        achieved = (wbytes / 1e9) / ((gemv_ms / P) / 1000.0) if gemv_ms > 0 else None
+        line = {
+            "metric": "decode_tokens_per_s", "value": value, "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": Wm,
+            "ms_per_step": dev_ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic", "config": config_dict(cfg, world, "replicas"),
+            "e2e": {"value": world * K / (e2e_ms / 1000.0), "unit": "tok/s", "h2d_bytes_per_step": 12,
+                    "d2h_bytes_per_step": cfg["vocab"] * 4, "api": "ForwardEngine.forward_logits (full f32 logits to host)"},
+            "gpu_launches": int(launches),
+            "clocks": clocks,
+            "roofline": {"bound": "hbm", "kernel": "gemv_kernel (dequant-fused GEMV, M=1)", "achieved": achieved,
+                         "peak": peaks["hbm_gbs"], "peak_source": peak_src, "unit": "GB/s",
+                         "frac": (achieved / peaks["hbm_gbs"]) if achieved else None, "traffic": None,
+                         "algorithmic_bytes_per_step": wbytes, "launches_per_step": gemv_n / P,
+                         "avg_launch_us": 1000.0 * gemv_ms / max(gemv_n, 1)},
+            "step_roofline": {"bytes_per_step": wbytes + kv_bytes, "ideal_ms_at_8TBs": (wbytes + kv_bytes) / 8e12 * 1e3,
+                              "frac_of_8TBs": ((wbytes + kv_bytes) / 8e12 * 1e3) / (dev_ms / K),
+                              "frac_of_measured_peak": ((wbytes + kv_bytes) / (peaks["hbm_gbs"] * 1e9) * 1e3) / (dev_ms / K)},
+            "family_ms_per_step": fam_ms,
+        }
+        if not args.no_cpu_baseline:
+            rate, done, threads = cpu_decode_rate(cfg, W, 8, 25.0)
+            line["cpu_baseline"] = {"value": rate, "unit": "tok/s", "cores": threads, "kind": "port",
+                                    "sample": f"{done} decode steps after a {CPU_PROMPT}-token prompt, full model"}
+        print(json.dumps(line), flush=True)
+    eng.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

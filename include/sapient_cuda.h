@@ -132,6 +132,20 @@ int32_t sp_cuda_forward_slot(SpEngine* e, int32_t slot, const uint32_t* ids, siz
  * logits_out[b * vocab] (host) and/or argmax_out[b] (host; last-maximum tie rule). */
 int32_t sp_cuda_decode_batch(SpEngine* e, const uint32_t* ids, const int32_t* slots, int32_t b, float* logits_out,
                              uint32_t* argmax_out);
+/* Greedy decode kept on the device: `steps` steps for b slots; step 0 consumes first_ids, each later step consumes the
+ * argmax (last-maximum rule) of the previous one, with no host work in between. tokens_out[steps * b] (host, step-major)
+ * may be NULL, in which case the call returns without synchronising (use sp_cuda_engine_synchronize). This is the loop
+ * Pipeline::generate_* runs with SamplingStrategy::Greedy (crates/sapient-generate/src/pipeline.rs:540-659). */
+int32_t sp_cuda_decode_greedy(SpEngine* e, const uint32_t* first_ids, const int32_t* slots, int32_t b, int32_t steps,
+                              uint32_t* tokens_out);
+int32_t sp_cuda_engine_synchronize(SpEngine* e);
+/* Replay decode steps as CUDA graphs (default on). */
+int32_t sp_cuda_engine_set_graphs(SpEngine* e, int32_t on);
+/* Per-kernel-family device timing (CUDA events around every launch; disables graphs while on). Families, in order:
+ * gemv, attention, norm, rope_kv, elementwise, embed, argmax. Returns the family count; ms/launches accumulate
+ * until reset (reset != 0 clears after reading). */
+int32_t sp_cuda_engine_set_profile(SpEngine* e, int32_t on);
+int32_t sp_cuda_engine_profile_read(SpEngine* e, double* ms, uint64_t* launches, int32_t cap, int32_t reset);
 /* reset_cache / truncate_cache (forward/mod.rs:381-414): kept = min(n, current). slot < 0 = all slots. */
 int32_t sp_cuda_reset_cache(SpEngine* e, int32_t slot);
 int32_t sp_cuda_truncate_cache(SpEngine* e, int32_t slot, size_t n, size_t* kept);

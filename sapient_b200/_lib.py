@@ -66,6 +66,11 @@ SIGNATURES = {
     "sp_cuda_forward_all_logits_cached": (_i32, [_vp, _vp, _sz, _vp]),
     "sp_cuda_forward_slot": (_i32, [_vp, _i32, _vp, _sz, _i32, _vp]),
     "sp_cuda_decode_batch": (_i32, [_vp, _vp, _vp, _i32, _vp, _vp]),
+    "sp_cuda_decode_greedy": (_i32, [_vp, _vp, _vp, _i32, _i32, _vp]),
+    "sp_cuda_engine_synchronize": (_i32, [_vp]),
+    "sp_cuda_engine_set_graphs": (_i32, [_vp, _i32]),
+    "sp_cuda_engine_set_profile": (_i32, [_vp, _i32]),
+    "sp_cuda_engine_profile_read": (_i32, [_vp, _vp, _vp, _i32, _i32]),
     "sp_cuda_reset_cache": (_i32, [_vp, _i32]),
     "sp_cuda_truncate_cache": (_i32, [_vp, _i32, _sz, C.POINTER(_sz)]),
     "sp_cuda_seq_len": (_i32, [_vp, _i32, C.POINTER(_sz)]),

@@ -466,6 +466,42 @@ int32_t sp_cuda_decode_batch(SpEngine* e, const uint32_t* ids, const int32_t* sl
     API_END
 }
 
+int32_t sp_cuda_decode_greedy(SpEngine* e, const uint32_t* first_ids, const int32_t* slots, int32_t b, int32_t steps,
+                              uint32_t* tokens_out) {
+    API_BEGIN
+    if (!e) { set_error("null engine"); return SP_ERR_ARG; }
+    return e->e->decode_greedy(first_ids, slots, b, steps, tokens_out);
+    API_END
+}
+
+int32_t sp_cuda_engine_synchronize(SpEngine* e) {
+    API_BEGIN
+    if (!e) { set_error("null engine"); return SP_ERR_ARG; }
+    SP_CUDA_TRY(cudaSetDevice(e->e->d.device));
+    SP_CUDA_TRY(cudaStreamSynchronize(e->e->stream));
+    return SP_OK;
+    API_END
+}
+
+int32_t sp_cuda_engine_set_graphs(SpEngine* e, int32_t on) {
+    if (!e) { set_error("null engine"); return SP_ERR_ARG; }
+    e->e->use_graphs = on != 0;
+    return SP_OK;
+}
+
+int32_t sp_cuda_engine_set_profile(SpEngine* e, int32_t on) {
+    if (!e) { set_error("null engine"); return SP_ERR_ARG; }
+    e->e->profile_on = on != 0;
+    return SP_OK;
+}
+
+int32_t sp_cuda_engine_profile_read(SpEngine* e, double* ms, uint64_t* launches, int32_t cap, int32_t reset) {
+    if (!e) { set_error("null engine"); return SP_ERR_ARG; }
+    const int n = e->e->profile_read(ms, launches, cap);
+    if (reset) e->e->profile_reset();
+    return n;
+}
+
 int32_t sp_cuda_reset_cache(SpEngine* e, int32_t slot) {
     API_BEGIN
     if (!e) { set_error("null engine"); return SP_ERR_ARG; }

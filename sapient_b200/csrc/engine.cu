@@ -45,6 +45,10 @@ Engine::Engine(const SpModelDesc& desc) : d(desc) {
 Engine::~Engine() {
     cudaSetDevice(d.device);
     if (stream) cudaStreamSynchronize(stream);
+    for (auto& g : step_graphs_) cudaGraphExecDestroy(g.second);
+    for (auto& r : prof_recs_) { cudaEventDestroy(r.a); cudaEventDestroy(r.b); }
+    for (cudaEvent_t ev : prof_pool_) cudaEventDestroy(ev);
+    if (d_tokens_) cudaFree(d_tokens_);
     for (auto& kv : tensors_) cudaFree(kv.second.d);
     for (void* p : owned_) cudaFree(p);
     void* bufs[] = {kv_.pool, d_page_table_, x_, h_, qkv_, attn_, gu_, mid_, sel_, logits_, trace_, d_ids_, d_argmax_,

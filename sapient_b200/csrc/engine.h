@@ -56,16 +56,31 @@ class Engine {
     int reset(int slot);
     int truncate(int slot, size_t n, size_t* kept);
     int debug_layer_out(int layer, float* out, size_t cap, int32_t* n_tokens);
+    // `steps` greedy decode steps for b slots with no host work in between: step 0 consumes first_ids, every
+    // later step consumes the device-side argmax of the previous one. tokens_out[steps * b] (host) may be null.
+    int decode_greedy(const uint32_t* first_ids, const int32_t* slots, int b, int steps, uint32_t* tokens_out);
+    // Per-kernel-family device time of profiled forwards (ms, accumulated) and launch counts.
+    enum Family { F_GEMV = 0, F_ATTN, F_NORM, F_ROPE, F_ELEM, F_EMBED, F_ARGMAX, F_COUNT };
+    int profile_read(double* ms, uint64_t* launches, int cap);
+    void profile_reset();
 
     SpModelDesc d;
     cudaStream_t own_stream = nullptr, stream = nullptr;
     bool finalized = false;
     bool trace_on = false;
+    bool use_graphs = true;
+    bool profile_on = false;
     std::vector<int> seq_len;
     uint64_t weight_bytes = 0, kv_bytes = 0;
 
   private:
     int run_chunk(const uint32_t* ids, const int32_t* slots, int T, int rows_from, float* logits_out, uint32_t* argmax_out);
+    int enqueue_layers(int T);                       // embed + all layers for the staged token table
+    int enqueue_head(int rows_from, int r0, int rc); // final norm is done by the caller; lm_head + argmax of rc rows
+    int enqueue_decode_step(int T);                  // embed, layers, final norm, lm_head, argmax for T <= logit_rows_ rows
+    int launch_decode_step(int T);                   // the same through a cached CUDA graph when allowed
+    void prof_begin(int fam);
+    void prof_end(int fam);
     int alloc_pages(int slot, int new_len);
     const DevTensor* find(const std::string& name) const;
     const float* find_f32(const std::string& name, int64_t n);
@@ -102,6 +117,19 @@ class Engine {
     int32_t *p_slot_ = nullptr, *p_pos_ = nullptr;
     float* p_logits_ = nullptr;
     uint32_t* p_argmax_ = nullptr;
+    // device-resident greedy loop
+    uint32_t* d_tokens_ = nullptr;
+    size_t d_tokens_cap_ = 0;
+    // CUDA graphs of one decode step, keyed by token count
+    std::map<int, cudaGraphExec_t> step_graphs_;
+    std::map<int, int64_t> step_graph_kernels_;
+    // profiling: event pairs per launch, resolved after a synchronise
+    struct ProfRec { int fam; cudaEvent_t a, b; };
+    std::vector<ProfRec> prof_recs_;
+    std::vector<cudaEvent_t> prof_pool_;
+    double prof_ms_[F_COUNT] = {0};
+    uint64_t prof_n_[F_COUNT] = {0};
+    int prof_flush();
 };
 
 }  // namespace sp

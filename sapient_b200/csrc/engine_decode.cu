@@ -1,0 +1,162 @@
+// Decode-step CUDA graphs, the device-resident greedy loop and per-family profiling.
+//
+// A decode step launches ~9 kernels per layer; at batch 1 each lasts a few
+// microseconds, so the step is captured once per token count into a CUDA graph and
+// replayed (the reference's CPU engine pays a thread-pool dispatch per matmul instead,
+// crates/sapient-backends/cpu/src/kernels/matmul.rs:486-534). All kernel arguments are
+// fixed device buffers; positions, slots, token ids and the page table are read from
+// device memory, so one graph serves every step.
+#include <algorithm>
+#include <cstring>
+
+#include "engine.h"
+#include "sp_common.cuh"
+
+namespace sp {
+
+#define SP_TRY(expr)                  \
+    do {                              \
+        int _s = (expr);              \
+        if (_s != SP_OK) return _s;   \
+    } while (0)
+
+// After a greedy step: the argmax becomes the next input token, positions advance, the token is logged.
+__global__ void advance_greedy_kernel(const uint32_t* __restrict__ argmax, uint32_t* __restrict__ ids,
+                                      int32_t* __restrict__ pos, uint32_t* __restrict__ log, int b) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < b) {
+        const uint32_t t = argmax[i];
+        ids[i] = t;
+        pos[i] += 1;
+        log[i] = t;
+    }
+}
+
+void Engine::prof_begin(int fam) {
+    if (!profile_on) return;
+    ProfRec r{fam, nullptr, nullptr};
+    for (cudaEvent_t* e : {&r.a, &r.b}) {
+        if (!prof_pool_.empty()) { *e = prof_pool_.back(); prof_pool_.pop_back(); }
+        else cudaEventCreate(e);
+    }
+    cudaEventRecord(r.a, stream);
+    prof_recs_.push_back(r);
+}
+
+void Engine::prof_end(int fam) {
+    (void)fam;
+    if (!profile_on || prof_recs_.empty()) return;
+    cudaEventRecord(prof_recs_.back().b, stream);
+}
+
+// Resolve the recorded event pairs (the stream has been synchronised by the caller).
+int Engine::prof_flush() {
+    if (prof_recs_.empty()) return SP_OK;
+    for (ProfRec& r : prof_recs_) {
+        float ms = 0.f;
+        if (cudaEventElapsedTime(&ms, r.a, r.b) == cudaSuccess) {
+            prof_ms_[r.fam] += ms;
+            prof_n_[r.fam] += 1;
+        } else {
+            cudaGetLastError();
+        }
+        prof_pool_.push_back(r.a);
+        prof_pool_.push_back(r.b);
+    }
+    prof_recs_.clear();
+    return SP_OK;
+}
+
+int Engine::profile_read(double* ms, uint64_t* launches, int cap) {
+    for (int i = 0; i < std::min<int>(cap, F_COUNT); ++i) {
+        if (ms) ms[i] = prof_ms_[i];
+        if (launches) launches[i] = prof_n_[i];
+    }
+    return F_COUNT;
+}
+
+void Engine::profile_reset() {
+    for (int i = 0; i < F_COUNT; ++i) { prof_ms_[i] = 0; prof_n_[i] = 0; }
+}
+
+int Engine::launch_decode_step(int T) {
+    if (!use_graphs || profile_on || trace_on) return enqueue_decode_step(T);
+    auto it = step_graphs_.find(T);
+    if (it == step_graphs_.end()) {
+        cudaGraph_t graph = nullptr;
+        const uint64_t before = launch_count();
+        SP_CUDA_TRY(cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal));
+        const int st = enqueue_decode_step(T);
+        const cudaError_t ce = cudaStreamEndCapture(stream, &graph);
+        const int64_t captured = (int64_t)(launch_count() - before);
+        adjust_launch_count(-captured);  // captured, not executed
+        step_graph_kernels_[T] = captured;
+        if (st != SP_OK) { if (graph) cudaGraphDestroy(graph); return st; }
+        if (ce != cudaSuccess) { set_error(std::string("graph capture: ") + cudaGetErrorString(ce)); return SP_ERR_CUDA; }
+        cudaGraphExec_t exec = nullptr;
+        const cudaError_t ie = cudaGraphInstantiate(&exec, graph, 0);
+        cudaGraphDestroy(graph);
+        if (ie != cudaSuccess) { set_error(std::string("graph instantiate: ") + cudaGetErrorString(ie)); return SP_ERR_CUDA; }
+        it = step_graphs_.emplace(T, exec).first;
+    }
+    SP_CUDA_TRY(cudaGraphLaunch(it->second, stream));
+    adjust_launch_count(step_graph_kernels_[T]);
+    return SP_OK;
+}
+
+int Engine::decode_greedy(const uint32_t* first_ids, const int32_t* slots, int b, int steps, uint32_t* tokens_out) {
+    if (!finalized) { set_error("engine not finalised"); return SP_ERR_STATE; }
+    if (!first_ids || !slots || b <= 0 || steps <= 0) { set_error("empty input"); return SP_ERR_ARG; }
+    if (b > logit_rows_ || b > d.max_tokens) { set_error("decode_greedy: batch larger than the decode step capacity"); return SP_ERR_ARG; }
+    SP_CUDA_TRY(cudaSetDevice(d.device));
+    for (int i = 0; i < b; ++i) {
+        if (slots[i] < 0 || slots[i] >= d.max_batch) { set_error("slot out of range"); return SP_ERR_ARG; }
+        for (int j = 0; j < i; ++j) if (slots[i] == slots[j]) { set_error("decode_greedy: a slot appears twice"); return SP_ERR_ARG; }
+        if ((int64_t)first_ids[i] >= (int64_t)d.vocab) { set_error("token id out of vocab range"); return SP_ERR_VOCAB; }
+        if (seq_len[slots[i]] + steps > d.max_ctx) { set_error("KV cache full"); return SP_ERR_KV_FULL; }
+    }
+    {
+        int need = 0;
+        for (int i = 0; i < b; ++i) need += std::max(0, (seq_len[slots[i]] + steps + KV_PAGE - 1) / KV_PAGE - slot_pages_[slots[i]]);
+        if (need > (int)free_pages_.size()) { set_error("KV page pool exhausted"); return SP_ERR_KV_FULL; }
+    }
+    // pages for every step up front, so nothing on the host has to happen between steps
+    for (int i = 0; i < b; ++i) {
+        SP_TRY(alloc_pages(slots[i], seq_len[slots[i]] + steps));
+        p_slot_[i] = slots[i];
+        p_pos_[i] = seq_len[slots[i]];
+        p_ids_[i] = first_ids[i];
+    }
+    const size_t need_tok = (size_t)b * steps;
+    if (need_tok > d_tokens_cap_) {
+        if (d_tokens_) cudaFree(d_tokens_);
+        d_tokens_ = nullptr;
+        d_tokens_cap_ = 0;
+        SP_CUDA_TRY(cudaMalloc((void**)&d_tokens_, need_tok * 4));
+        d_tokens_cap_ = need_tok;
+    }
+    SP_CUDA_TRY(cudaMemcpyAsync(d_ids_, p_ids_, (size_t)b * 4, cudaMemcpyHostToDevice, stream));
+    SP_CUDA_TRY(cudaMemcpyAsync(d_tok_slot_, p_slot_, (size_t)b * 4, cudaMemcpyHostToDevice, stream));
+    SP_CUDA_TRY(cudaMemcpyAsync(d_tok_pos_, p_pos_, (size_t)b * 4, cudaMemcpyHostToDevice, stream));
+    if (pages_dirty_) {
+        SP_CUDA_TRY(cudaMemcpyAsync(d_page_table_, h_page_table_.data(), h_page_table_.size() * 4, cudaMemcpyHostToDevice, stream));
+        pages_dirty_ = false;
+    }
+    for (int s = 0; s < steps; ++s) {
+        SP_TRY(launch_decode_step(b));
+        advance_greedy_kernel<<<(b + 127) / 128, 128, 0, stream>>>(d_argmax_, d_ids_, d_tok_pos_, d_tokens_ + (size_t)s * b, b);
+        SP_CUDA_TRY(cudaGetLastError());
+        adjust_launch_count(1);
+    }
+    for (int i = 0; i < b; ++i) seq_len[slots[i]] += steps;
+    if (tokens_out) {
+        std::vector<uint32_t> tmp(need_tok);
+        SP_CUDA_TRY(cudaMemcpyAsync(tmp.data(), d_tokens_, need_tok * 4, cudaMemcpyDeviceToHost, stream));
+        SP_CUDA_TRY(cudaStreamSynchronize(stream));
+        std::memcpy(tokens_out, tmp.data(), need_tok * 4);
+        return prof_flush();
+    }
+    return SP_OK;  // asynchronous: the caller synchronises the stream
+}
+
+}  // namespace sp

@@ -16,6 +16,14 @@ namespace sp {
         if (_s != SP_OK) return _s;   \
     } while (0)
 
+// Launch `expr` (a cudaError_t) bracketed by profiling events of kernel family `fam`.
+#define SP_LAUNCH(fam, expr)          \
+    do {                              \
+        prof_begin(fam);              \
+        SP_CUDA_TRY(expr);            \
+        prof_end(fam);                \
+    } while (0)
+
 int Engine::alloc_pages(int slot, int new_len) {
     const int need = (new_len + KV_PAGE - 1) / KV_PAGE;
     while (slot_pages_[slot] < need) {
@@ -45,7 +53,7 @@ int Engine::truncate(int slot, size_t n, size_t* kept) {
     const int k = (int)std::min<size_t>(n, (size_t)seq_len[slot]);
     seq_len[slot] = k;
     const int keep_pages = (k + KV_PAGE - 1) / KV_PAGE;
-    while (slot_pages_.size() && slot_pages_[slot] > keep_pages) {
+    while (slot_pages_[slot] > keep_pages) {
         slot_pages_[slot]--;
         free_pages_.push_back(h_page_table_[(size_t)slot * kv_.max_pages + slot_pages_[slot]]);
     }
@@ -68,23 +76,23 @@ int Engine::gemv(const float* x, int ldx, int m, int k, const DevTensor* w0, con
         a.seg[i].n = (int)ws[i]->dims[0]; a.seg[i].ldy = ldy0;
         a.nseg++;
     }
-    SP_CUDA_TRY(launch_gemv(a, stream));
+    SP_LAUNCH(F_GEMV, launch_gemv(a, stream));
     return SP_OK;
 }
 
 int Engine::layer_llama(const LayerW& w, int l, int T) {
     const int H = d.n_heads, Hkv = d.n_kv_heads, hd = d.head_dim, hid = d.hidden, ffn = d.ffn;
     const int qkv_ld = (H + 2 * Hkv) * hd;
-    SP_CUDA_TRY(launch_rms_norm(x_, w.n1w, T, hid, d.norm_eps, h_, stream));
+    SP_LAUNCH(F_NORM, launch_rms_norm(x_, w.n1w, T, hid, d.norm_eps, h_, stream));
     SP_TRY(gemv(h_, hid, T, hid, w.q, w.qb, qkv_, qkv_ld, w.k, w.kb, qkv_ + (size_t)H * hd, w.v, w.vb,
                 qkv_ + (size_t)(H + Hkv) * hd));
-    SP_CUDA_TRY(launch_rope_kv_append(qkv_, T, H, Hkv, hd, d.rotary_dim, cos_sin_, d_tok_slot_, d_tok_pos_, kv_, l, stream));
-    SP_CUDA_TRY(launch_attention(qkv_, qkv_ld, attn_, H * hd, T, H, d_tok_slot_, d_tok_pos_, kv_, l,
-                                 1.0f / sqrtf((float)hd), stream));
+    SP_LAUNCH(F_ROPE, launch_rope_kv_append(qkv_, T, H, Hkv, hd, d.rotary_dim, cos_sin_, d_tok_slot_, d_tok_pos_, kv_, l, stream));
+    SP_LAUNCH(F_ATTN, launch_attention(qkv_, qkv_ld, attn_, H * hd, T, H, d_tok_slot_, d_tok_pos_, kv_, l,
+                                       1.0f / sqrtf((float)hd), stream));
     SP_TRY(gemv(attn_, H * hd, T, H * hd, w.o, w.ob, x_, hid, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, x_));
-    SP_CUDA_TRY(launch_rms_norm(x_, w.n2w, T, hid, d.norm_eps, h_, stream));
+    SP_LAUNCH(F_NORM, launch_rms_norm(x_, w.n2w, T, hid, d.norm_eps, h_, stream));
     SP_TRY(gemv(h_, hid, T, hid, w.gate, nullptr, gu_, 2 * ffn, w.up, nullptr, gu_ + ffn));
-    SP_CUDA_TRY(launch_swiglu(gu_, 2 * ffn, ffn, T, mid_, stream));
+    SP_LAUNCH(F_ELEM, launch_swiglu(gu_, 2 * ffn, ffn, T, mid_, stream));
     SP_TRY(gemv(mid_, ffn, T, ffn, w.down, nullptr, x_, hid, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, x_));
     return SP_OK;
 }
@@ -92,18 +100,51 @@ int Engine::layer_llama(const LayerW& w, int l, int T) {
 int Engine::layer_phi(const LayerW& w, int l, int T) {
     const int H = d.n_heads, Hkv = d.n_kv_heads, hd = d.head_dim, hid = d.hidden, ffn = d.ffn;
     const int qkv_ld = (H + 2 * Hkv) * hd;
-    SP_CUDA_TRY(launch_layer_norm(x_, w.n1w, w.n1b, T, hid, d.norm_eps, h_, stream));
+    SP_LAUNCH(F_NORM, launch_layer_norm(x_, w.n1w, w.n1b, T, hid, d.norm_eps, h_, stream));
     SP_TRY(gemv(h_, hid, T, hid, w.q, w.qb, qkv_, qkv_ld, w.k, w.kb, qkv_ + (size_t)H * hd, w.v, w.vb,
                 qkv_ + (size_t)(H + Hkv) * hd));
-    SP_CUDA_TRY(launch_rope_kv_append(qkv_, T, H, Hkv, hd, d.rotary_dim, cos_sin_, d_tok_slot_, d_tok_pos_, kv_, l, stream));
-    SP_CUDA_TRY(launch_attention(qkv_, qkv_ld, attn_, H * hd, T, H, d_tok_slot_, d_tok_pos_, kv_, l,
-                                 1.0f / sqrtf((float)hd), stream));
+    SP_LAUNCH(F_ROPE, launch_rope_kv_append(qkv_, T, H, Hkv, hd, d.rotary_dim, cos_sin_, d_tok_slot_, d_tok_pos_, kv_, l, stream));
+    SP_LAUNCH(F_ATTN, launch_attention(qkv_, qkv_ld, attn_, H * hd, T, H, d_tok_slot_, d_tok_pos_, kv_, l,
+                                       1.0f / sqrtf((float)hd), stream));
     // parallel block: x + (attn_out + mlp(h)); both branches read the same normalised input h
     SP_TRY(gemv(h_, hid, T, hid, w.up, w.upb, mid_, ffn));
-    SP_CUDA_TRY(launch_gelu(mid_, (int64_t)T * ffn, stream));
+    SP_LAUNCH(F_ELEM, launch_gelu(mid_, (int64_t)T * ffn, stream));
     SP_TRY(gemv(attn_, H * hd, T, H * hd, w.o, w.ob, x_, hid, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, x_));
     SP_TRY(gemv(mid_, ffn, T, ffn, w.down, w.downb, x_, hid, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, x_));
     return SP_OK;
+}
+
+int Engine::enqueue_layers(int T) {
+    const int hid = d.hidden;
+    SP_LAUNCH(F_EMBED, launch_embed(embed_->dtype, embed_->d, hid, d_ids_, T, x_, stream));
+    for (int l = 0; l < d.n_layers; ++l) {
+        SP_TRY(d.arch == 1 ? layer_phi(layers_[l], l, T) : layer_llama(layers_[l], l, T));
+        if (trace_on)
+            SP_CUDA_TRY(cudaMemcpyAsync(trace_ + (size_t)l * d.max_tokens * hid, x_, (size_t)T * hid * 4, cudaMemcpyDeviceToDevice, stream));
+    }
+    trace_tokens_ = T;
+    return SP_OK;
+}
+
+// lm_head over rows [r0, r0+rc) of the normalised selection sel_, plus their argmax.
+int Engine::enqueue_head(int rows_from, int r0, int rc) {
+    (void)rows_from;
+    const int V = d.vocab, hid = d.hidden;
+    GemvArgs a{};
+    a.x = sel_ + (size_t)r0 * hid; a.ldx = hid; a.m = rc; a.k = hid; a.nseg = 1;
+    a.seg[0].w = lm_head_->d; a.seg[0].bias = lm_bias_; a.seg[0].y = logits_; a.seg[0].dtype = lm_head_->dtype;
+    a.seg[0].n = V; a.seg[0].ldy = V;
+    SP_LAUNCH(F_GEMV, launch_gemv(a, stream));
+    SP_LAUNCH(F_ARGMAX, launch_argmax(logits_, rc, V, V, d_argmax_, stream));
+    return SP_OK;
+}
+
+int Engine::enqueue_decode_step(int T) {
+    const int hid = d.hidden;
+    SP_TRY(enqueue_layers(T));
+    if (d.arch == 1) SP_LAUNCH(F_NORM, launch_layer_norm(x_, final_w_, final_b_, T, hid, d.norm_eps, sel_, stream));
+    else SP_LAUNCH(F_NORM, launch_rms_norm(x_, final_w_, T, hid, d.norm_eps, sel_, stream));
+    return enqueue_head(0, 0, T);
 }
 
 // One chunk of T <= max_tokens tokens whose (slot, pos) are already staged in p_slot_/p_pos_.
@@ -119,32 +160,29 @@ int Engine::run_chunk(const uint32_t* ids, const int32_t* slots, int T, int rows
         SP_CUDA_TRY(cudaMemcpyAsync(d_page_table_, h_page_table_.data(), h_page_table_.size() * 4, cudaMemcpyHostToDevice, stream));
         pages_dirty_ = false;
     }
-    const int hid = d.hidden;
-    SP_CUDA_TRY(launch_embed(embed_->dtype, embed_->d, hid, d_ids_, T, x_, stream));
+    const int hid = d.hidden, V = d.vocab;
     if (trace_on && !trace_) SP_CUDA_TRY(cudaMalloc((void**)&trace_, (size_t)d.n_layers * d.max_tokens * hid * 4));
-    for (int l = 0; l < d.n_layers; ++l) {
-        SP_TRY(d.arch == 1 ? layer_phi(layers_[l], l, T) : layer_llama(layers_[l], l, T));
-        if (trace_on)
-            SP_CUDA_TRY(cudaMemcpyAsync(trace_ + (size_t)l * d.max_tokens * hid, x_, (size_t)T * hid * 4, cudaMemcpyDeviceToDevice, stream));
-    }
-    trace_tokens_ = T;
     const int rows = T - rows_from;
-    if (rows > 0 && (logits_out || argmax_out)) {
+    const bool want = rows > 0 && (logits_out || argmax_out);
+    if (want && rows_from == 0 && T <= logit_rows_) {
+        // decode-shaped call: the whole step is one (graph) launch
+        SP_TRY(launch_decode_step(T));
+        if (argmax_out) SP_CUDA_TRY(cudaMemcpyAsync(p_argmax_, d_argmax_, (size_t)T * 4, cudaMemcpyDeviceToHost, stream));
+        if (logits_out) SP_CUDA_TRY(cudaMemcpyAsync(p_logits_, logits_, (size_t)T * V * 4, cudaMemcpyDeviceToHost, stream));
+        SP_CUDA_TRY(cudaStreamSynchronize(stream));
+        if (logits_out) std::memcpy(logits_out, p_logits_, (size_t)T * V * 4);
+        if (argmax_out) std::memcpy(argmax_out, p_argmax_, (size_t)T * 4);
+        return prof_flush();
+    }
+    SP_TRY(enqueue_layers(T));
+    if (want) {
         const float* src = x_ + (size_t)rows_from * hid;
-        if (d.arch == 1) SP_CUDA_TRY(launch_layer_norm(src, final_w_, final_b_, rows, hid, d.norm_eps, sel_, stream));
-        else SP_CUDA_TRY(launch_rms_norm(src, final_w_, rows, hid, d.norm_eps, sel_, stream));
-        const int V = d.vocab;
+        if (d.arch == 1) SP_LAUNCH(F_NORM, launch_layer_norm(src, final_w_, final_b_, rows, hid, d.norm_eps, sel_, stream));
+        else SP_LAUNCH(F_NORM, launch_rms_norm(src, final_w_, rows, hid, d.norm_eps, sel_, stream));
         for (int r0 = 0; r0 < rows; r0 += logit_rows_) {
             const int rc = std::min(logit_rows_, rows - r0);
-            GemvArgs a{};
-            a.x = sel_ + (size_t)r0 * hid; a.ldx = hid; a.m = rc; a.k = hid; a.nseg = 1;
-            a.seg[0].w = lm_head_->d; a.seg[0].bias = lm_bias_; a.seg[0].y = logits_; a.seg[0].dtype = lm_head_->dtype;
-            a.seg[0].n = V; a.seg[0].ldy = V;
-            SP_CUDA_TRY(launch_gemv(a, stream));
-            if (argmax_out) {
-                SP_CUDA_TRY(launch_argmax(logits_, rc, V, V, d_argmax_, stream));
-                SP_CUDA_TRY(cudaMemcpyAsync(p_argmax_, d_argmax_, (size_t)rc * 4, cudaMemcpyDeviceToHost, stream));
-            }
+            SP_TRY(enqueue_head(rows_from, r0, rc));
+            if (argmax_out) SP_CUDA_TRY(cudaMemcpyAsync(p_argmax_, d_argmax_, (size_t)rc * 4, cudaMemcpyDeviceToHost, stream));
             if (logits_out) SP_CUDA_TRY(cudaMemcpyAsync(p_logits_, logits_, (size_t)rc * V * 4, cudaMemcpyDeviceToHost, stream));
             SP_CUDA_TRY(cudaStreamSynchronize(stream));
             if (logits_out) std::memcpy(logits_out + (size_t)r0 * V, p_logits_, (size_t)rc * V * 4);
@@ -152,7 +190,7 @@ int Engine::run_chunk(const uint32_t* ids, const int32_t* slots, int T, int rows
         }
     }
     SP_CUDA_TRY(cudaStreamSynchronize(stream));
-    return SP_OK;
+    return prof_flush();
 }
 
 int Engine::forward(const uint32_t* ids, const int32_t* slots, int64_t n, bool want_all, float* logits_out,

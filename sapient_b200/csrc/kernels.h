@@ -39,6 +39,8 @@ struct KvGeom {
 
 // Kernels launched by this library since process start.
 uint64_t launch_count();
+// Graph replays launch kernels without passing through the launchers; they report their node count here.
+void adjust_launch_count(int64_t delta);
 
 cudaError_t launch_dequant(int dtype, const uint8_t* w, int64_t n, int64_t k, float* out, cudaStream_t st);
 cudaError_t launch_gemv(const GemvArgs& a, cudaStream_t st);

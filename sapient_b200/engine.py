@@ -151,6 +151,34 @@ class ForwardEngine:
                                          _p(am) if want_argmax else None))
         return logits, am
 
+    def decode_greedy(self, first_ids, slots, steps: int, fetch: bool = True):
+        """`steps` greedy decode steps kept on the device. Returns tokens [steps, b] (uint32), or None when
+        fetch is False (then call synchronize() before touching the engine again)."""
+        ids = _ids(first_ids)
+        sl = np.ascontiguousarray(slots, dtype=np.int32).reshape(-1)
+        assert ids.size == sl.size
+        out = np.empty((steps, ids.size), np.uint32) if fetch else None
+        check(lib().sp_cuda_decode_greedy(self._h, _p(ids), _p(sl), ids.size, steps, _p(out) if fetch else None))
+        return out
+
+    def synchronize(self) -> None:
+        check(lib().sp_cuda_engine_synchronize(self._h))
+
+    def set_graphs(self, on: bool) -> None:
+        check(lib().sp_cuda_engine_set_graphs(self._h, int(on)))
+
+    PROFILE_FAMILIES = ("gemv", "attention", "norm", "rope_kv", "elementwise", "embed", "argmax")
+
+    def set_profile(self, on: bool) -> None:
+        check(lib().sp_cuda_engine_set_profile(self._h, int(on)))
+
+    def profile_read(self, reset: bool = True) -> dict:
+        """{family: (device ms, launches)} accumulated over profiled forwards."""
+        ms = np.zeros(8, np.float64)
+        n = np.zeros(8, np.uint64)
+        k = lib().sp_cuda_engine_profile_read(self._h, _p(ms), _p(n), 8, int(reset))
+        return {self.PROFILE_FAMILIES[i]: (float(ms[i]), int(n[i])) for i in range(k)}
+
     def set_stream(self, stream: int) -> None:
         check(lib().sp_cuda_engine_set_stream(self._h, C.c_void_p(stream)))
 

@@ -1,0 +1,95 @@
+"""The device-resident greedy loop, CUDA-graph replay and the profiling mode must not
+change any result."""
+import numpy as np
+import pytest
+
+from helpers import oracle_engine, tiny_model
+from sapient_b200 import ops
+from sapient_b200.engine import ForwardEngine
+
+pytestmark = pytest.mark.gpu
+
+
+def last_argmax(v):
+    return int(np.flatnonzero(v == v.max())[-1])
+
+
+@pytest.mark.parametrize("name", ["tiny_llama", "tiny_qwen", "tiny_phi2"])
+def test_greedy_loop_equals_stepwise_host_loop(oracle, name):
+    cfg, W = tiny_model(name)
+    eng = ForwardEngine.from_weights(cfg, W)
+    ids = np.random.default_rng(1).integers(0, cfg["vocab"], 9).astype(np.uint32)
+    first = last_argmax(eng.forward_logits(ids, False))
+    toks = eng.decode_greedy([first], [0], 20)
+    assert toks.shape == (20, 1) and eng.seq_len() == 29
+    eng.truncate_cache(9)
+    eng.set_graphs(False)
+    want, tok = [], first
+    for _ in range(20):
+        lg = eng.forward_logits([tok], True)
+        tok = last_argmax(lg)
+        want.append(tok)
+    assert toks[:, 0].tolist() == want
+    # token stream of the reference CPU path under teacher forcing: >= 99 % agreement
+    ref = oracle_engine(oracle, cfg, W, kv_mode=0)
+    rl = ref.forward_logits(ids, True)
+    agree, tok = 0, first
+    for t in want:
+        rl = ref.forward_logits([tok], True)
+        agree += int(oracle.argmax(rl) == t)
+        tok = t
+    assert agree >= 19
+    eng.close()
+
+
+def test_graph_replay_and_profiling_are_bitwise_neutral():
+    cfg, W = tiny_model("tiny_llama")
+    eng = ForwardEngine.from_weights(cfg, W, max_batch=3, max_tokens=8)
+    rng = np.random.default_rng(2)
+    for s in range(3):
+        eng.forward_slot(s, rng.integers(0, cfg["vocab"], 4 + s).astype(np.uint32))
+    ids = rng.integers(0, cfg["vocab"], 3).astype(np.uint32)
+    outs = []
+    for mode in ("graph", "graph", "direct", "profile"):
+        eng.set_graphs(mode == "graph")
+        eng.set_profile(mode == "profile")
+        lens = [eng.seq_len(s) for s in range(3)]
+        before = ops.launch_count()
+        logits, am = eng.decode_batch(ids, [0, 1, 2], want_logits=True, want_argmax=True)
+        launched = ops.launch_count() - before
+        assert launched == 2 * 9 + 4, launched  # 9 kernels per layer + embed, final norm, lm_head, argmax
+        outs.append((logits.copy(), am.copy()))
+        for s in range(3):
+            assert eng.truncate_cache(lens[s], s) == lens[s]
+    for lg, am in outs[1:]:
+        assert np.array_equal(lg, outs[0][0]) and np.array_equal(am, outs[0][1])
+    prof = eng.profile_read()
+    assert prof["gemv"][1] == 2 * 4 + 1 and prof["attention"][1] == 2 and prof["gemv"][0] > 0
+    eng.close()
+
+
+def test_greedy_loop_batched_and_capacity_errors():
+    from sapient_b200 import _lib
+
+    cfg, W = tiny_model("tiny_qwen", max_ctx=32)
+    eng = ForwardEngine.from_weights(cfg, W, max_batch=2, max_tokens=8)
+    rng = np.random.default_rng(3)
+    firsts = []
+    for s in range(2):
+        firsts.append(last_argmax(eng.forward_slot(s, rng.integers(0, cfg["vocab"], 5).astype(np.uint32))))
+    toks = eng.decode_greedy(firsts, [0, 1], 6)
+    solo = ForwardEngine.from_weights(cfg, W)
+    rng = np.random.default_rng(3)
+    for s in range(2):
+        solo.reset_cache()
+        tok = last_argmax(solo.forward_logits(rng.integers(0, cfg["vocab"], 5).astype(np.uint32), True))
+        assert tok == firsts[s]
+        for i in range(6):
+            tok = last_argmax(solo.forward_logits([tok], True))
+            assert tok == toks[i, s]
+    with pytest.raises(_lib.SapientCudaError) as e:
+        eng.decode_greedy(firsts, [0, 1], 40)
+    assert e.value.status == _lib.SP_ERR_KV_FULL and eng.seq_len(0) == 11
+    with pytest.raises(_lib.SapientCudaError):
+        eng.decode_greedy(firsts, [0, 0], 1)
+    eng.close(); solo.close()
