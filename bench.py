@@ -176,6 +176,7 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--quick", action="store_true", help="prefill + warm-up + timed device loop only (for profiler runs)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -200,7 +201,9 @@ def main() -> None:
     cfg, W = build_weights(f"cuda:{local}")
     wbytes = step_weight_bytes(cfg, W)
     eng = ForwardEngine.from_weights(cfg, W, device=local, max_batch=1, max_tokens=256)
-    stream = torch.cuda.current_stream()
+    # a real (non-default) stream: CUDA events below are recorded on the stream the kernels run on
+    stream = torch.cuda.Stream(device=local)
+    torch.cuda.set_stream(stream)
     eng.set_stream(stream.cuda_stream)
     K, Wm = args.steps, args.warmup
     rng = np.random.default_rng(0)
@@ -231,6 +234,14 @@ def main() -> None:
     dev_ms = ev0.elapsed_time(ev1)
     kv_ctx_mid = PROMPT + Wm + K // 2
 
+    if args.quick:  # launch-list / profiler runs: prefill + warm-up + timed steps only
+        sampler.stop()
+        if rank == 0:
+            print(json.dumps({"quick": True, "ms_per_step": dev_ms / K, "value": world * K / (dev_ms / 1000.0),
+                              "gpu_launches": int(launches)}), flush=True)
+        eng.close()
+        return
+
     # ── e2e: public API with host buffers, every step ──
     eng.truncate_cache(PROMPT)
     tok = int(first[0])
@@ -248,20 +259,13 @@ def main() -> None:
     sampler.stop()
     clocks = sampler.summary(t_wall0, t_wall1)
 
-    # ── per-family device time (events around every launch, graphs off) ──
+    # ── per-family device time: each family's launches of one step replayed alone as a CUDA graph ──
+    P = 20
+    fam_ms = {f: eng.time_families(f, 1, P) for f in eng.PROFILE_FAMILIES}
+    fam_ms["all"] = eng.time_families("all", 1, P)
+    gemv_ms = fam_ms["gemv"] * P
+    gemv_n = (4 * cfg["n_layers"] + 1) * P
     eng.truncate_cache(PROMPT)
-    eng.set_profile(True)
-    P = min(K, 16)
-    tok = int(first[0])
-    for i in range(P + 2):
-        if i == 2:
-            eng.profile_read(reset=True)
-        _, am = eng.decode_batch([tok], [0], want_logits=False, want_argmax=True)
-        tok = int(am[0])
-    prof = eng.profile_read(reset=True)
-    eng.set_profile(False)
-    gemv_ms, gemv_n = prof["gemv"]
-    fam_ms = {k: v[0] / P for k, v in prof.items()}
 
     t = torch.tensor([dev_ms, e2e_s * 1000.0], device=f"cuda:{local}", dtype=torch.float64)
     if world > 1:

@@ -145,6 +145,10 @@ int32_t sp_cuda_engine_set_graphs(SpEngine* e, int32_t on);
  * gemv, attention, norm, rope_kv, elementwise, embed, argmax. Returns the family count; ms/launches accumulate
  * until reset (reset != 0 clears after reading). */
 int32_t sp_cuda_engine_set_profile(SpEngine* e, int32_t on);
+/* Device time (ms) of one decode step of n_tokens rows restricted to the kernel families whose bits are set in
+ * family_mask (bit i = family i of the list above; 0x7F = the whole step), measured by replaying that subset as a
+ * CUDA graph `reps` times between two events. Activations and the newest KV entries are undefined afterwards. */
+int32_t sp_cuda_engine_time_families(SpEngine* e, uint32_t family_mask, int32_t n_tokens, int32_t reps, float* ms_per_step);
 int32_t sp_cuda_engine_profile_read(SpEngine* e, double* ms, uint64_t* launches, int32_t cap, int32_t reset);
 /* reset_cache / truncate_cache (forward/mod.rs:381-414): kept = min(n, current). slot < 0 = all slots. */
 int32_t sp_cuda_reset_cache(SpEngine* e, int32_t slot);

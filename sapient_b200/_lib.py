@@ -71,6 +71,7 @@ SIGNATURES = {
     "sp_cuda_engine_set_graphs": (_i32, [_vp, _i32]),
     "sp_cuda_engine_set_profile": (_i32, [_vp, _i32]),
     "sp_cuda_engine_profile_read": (_i32, [_vp, _vp, _vp, _i32, _i32]),
+    "sp_cuda_engine_time_families": (_i32, [_vp, C.c_uint32, _i32, _i32, C.POINTER(C.c_float)]),
     "sp_cuda_reset_cache": (_i32, [_vp, _i32]),
     "sp_cuda_truncate_cache": (_i32, [_vp, _i32, _sz, C.POINTER(_sz)]),
     "sp_cuda_seq_len": (_i32, [_vp, _i32, C.POINTER(_sz)]),

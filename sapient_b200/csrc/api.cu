@@ -495,6 +495,13 @@ int32_t sp_cuda_engine_set_profile(SpEngine* e, int32_t on) {
     return SP_OK;
 }
 
+int32_t sp_cuda_engine_time_families(SpEngine* e, uint32_t family_mask, int32_t n_tokens, int32_t reps, float* ms_per_step) {
+    API_BEGIN
+    if (!e) { set_error("null engine"); return SP_ERR_ARG; }
+    return e->e->time_families(family_mask, n_tokens, reps, ms_per_step);
+    API_END
+}
+
 int32_t sp_cuda_engine_profile_read(SpEngine* e, double* ms, uint64_t* launches, int32_t cap, int32_t reset) {
     if (!e) { set_error("null engine"); return SP_ERR_ARG; }
     const int n = e->e->profile_read(ms, launches, cap);

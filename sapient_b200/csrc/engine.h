@@ -61,6 +61,11 @@ class Engine {
     int decode_greedy(const uint32_t* first_ids, const int32_t* slots, int b, int steps, uint32_t* tokens_out);
     // Per-kernel-family device time of profiled forwards (ms, accumulated) and launch counts.
     enum Family { F_GEMV = 0, F_ATTN, F_NORM, F_ROPE, F_ELEM, F_EMBED, F_ARGMAX, F_COUNT };
+    // Device time of one decode step of T tokens restricted to the kernel families in fam_mask (bit i = family i):
+    // the step is captured with the other launches left out and replayed `reps` times between two events.
+    // Activations and the KV entries of the last staged positions are undefined afterwards.
+    int time_families(unsigned fam_mask, int T, int reps, float* ms_per_step);
+    unsigned fam_mask = 0xFFFFFFFFu;
     int profile_read(double* ms, uint64_t* launches, int cap);
     void profile_reset();
 

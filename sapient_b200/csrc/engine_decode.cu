@@ -104,6 +104,53 @@ int Engine::launch_decode_step(int T) {
     return SP_OK;
 }
 
+int Engine::time_families(unsigned mask, int T, int reps, float* ms_per_step) {
+    if (!finalized) { set_error("engine not finalised"); return SP_ERR_STATE; }
+    if (T <= 0 || T > logit_rows_ || reps <= 0 || !ms_per_step) { set_error("time_families: bad argument"); return SP_ERR_ARG; }
+    SP_CUDA_TRY(cudaSetDevice(d.device));
+    SP_CUDA_TRY(cudaStreamSynchronize(stream));
+    const bool prof = profile_on, tr = trace_on;
+    profile_on = false;
+    trace_on = false;
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    const uint64_t before = launch_count();
+    fam_mask = mask;
+    cudaError_t ce = cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal);
+    int st = SP_OK;
+    if (ce == cudaSuccess) {
+        st = enqueue_decode_step(T);
+        ce = cudaStreamEndCapture(stream, &graph);
+    }
+    fam_mask = 0xFFFFFFFFu;
+    profile_on = prof;
+    trace_on = tr;
+    const int64_t nodes = (int64_t)(launch_count() - before);
+    adjust_launch_count(-nodes);
+    if (st != SP_OK) { if (graph) cudaGraphDestroy(graph); return st; }
+    if (ce != cudaSuccess || !graph) { set_error(std::string("time_families capture: ") + cudaGetErrorString(ce)); return SP_ERR_CUDA; }
+    ce = cudaGraphInstantiate(&exec, graph, 0);
+    cudaGraphDestroy(graph);
+    if (ce != cudaSuccess) { set_error(std::string("time_families instantiate: ") + cudaGetErrorString(ce)); return SP_ERR_CUDA; }
+    cudaEvent_t a, b;
+    cudaEventCreate(&a);
+    cudaEventCreate(&b);
+    for (int i = 0; i < 3; ++i) cudaGraphLaunch(exec, stream);
+    cudaEventRecord(a, stream);
+    for (int i = 0; i < reps; ++i) cudaGraphLaunch(exec, stream);
+    cudaEventRecord(b, stream);
+    ce = cudaStreamSynchronize(stream);
+    float ms = 0.f;
+    if (ce == cudaSuccess) ce = cudaEventElapsedTime(&ms, a, b);
+    adjust_launch_count(nodes * (reps + 3));
+    cudaEventDestroy(a);
+    cudaEventDestroy(b);
+    cudaGraphExecDestroy(exec);
+    if (ce != cudaSuccess) { set_error(std::string("time_families: ") + cudaGetErrorString(ce)); return SP_ERR_CUDA; }
+    *ms_per_step = ms / reps;
+    return SP_OK;
+}
+
 int Engine::decode_greedy(const uint32_t* first_ids, const int32_t* slots, int b, int steps, uint32_t* tokens_out) {
     if (!finalized) { set_error("engine not finalised"); return SP_ERR_STATE; }
     if (!first_ids || !slots || b <= 0 || steps <= 0) { set_error("empty input"); return SP_ERR_ARG; }

