@@ -1,5 +1,7 @@
 // extern "C" surface of libsapient_cuda.so (declarations: include/sapient_cuda.h).
 // No exception leaves this file; every entry sets the CUDA device it works on.
+#include <algorithm>
+#include <atomic>
 #include <cmath>
 #include <cstring>
 #include <new>
@@ -17,6 +19,8 @@ struct SpWeight {
     int64_t n, k;
     uint8_t* d;
     size_t nbytes;
+    uint8_t* tiled = nullptr;  // tile-repacked copy for the tensor-core GEMV (quantised types)
+    ActWorkspace ws;           // activation digits for up to 16 rows
 };
 struct SpEngine {
     Engine* e;
@@ -25,6 +29,8 @@ struct SpEngine {
 int sp_engine_from_gguf_impl(const char* path, int device, int max_ctx, int max_batch, Engine** out);  // gguf.cu
 
 namespace {
+
+std::atomic<int> g_gemv_path{0};  // 0: tensor-core GEMV on tiled weights; 1: CUDA-core GEMV on raw blocks
 
 #define API_BEGIN try {
 #define API_END                                                     \
@@ -117,6 +123,12 @@ int32_t sp_cuda_device_count(void) {
 
 uint64_t sp_cuda_launch_count(void) { return launch_count(); }
 
+int32_t sp_cuda_set_gemv_path(int32_t path) {
+    if (path != 0 && path != 1) { set_error("gemv path must be 0 or 1"); return SP_ERR_ARG; }
+    g_gemv_path.store(path);
+    return SP_OK;
+}
+
 int32_t sp_cuda_upload_weight(int32_t device, int32_t dtype, int64_t n, int64_t k, const void* host_blocks, size_t nbytes,
                               SpWeight** out) {
     API_BEGIN
@@ -127,9 +139,17 @@ int32_t sp_cuda_upload_weight(int32_t device, int32_t dtype, int64_t n, int64_t 
     SpWeight* w = new SpWeight{device, dtype, n, k, nullptr, nbytes};
     cudaError_t ce = cudaMalloc((void**)&w->d, nbytes + 16);
     if (ce == cudaSuccess) ce = cudaMemcpy(w->d, host_blocks, nbytes, cudaMemcpyHostToDevice);
+    if (ce == cudaSuccess && imma_supported(dtype, k) && n > 0) {
+        ce = cudaMalloc((void**)&w->tiled, imma_tiled_bytes(dtype, n, k) + 16);
+        if (ce == cudaSuccess) ce = launch_repack(dtype, w->d, n, k, w->tiled, 0);
+        if (ce == cudaSuccess) ce = cudaStreamSynchronize(0);
+        if (ce == cudaSuccess) ce = w->ws.alloc((int)k);
+    }
     if (ce != cudaSuccess) {
         set_error(std::string("upload_weight: ") + cudaGetErrorString(ce));
         if (w->d) cudaFree(w->d);
+        if (w->tiled) cudaFree(w->tiled);
+        w->ws.release();
         delete w;
         return ce == cudaErrorMemoryAllocation ? SP_ERR_OOM : SP_ERR_CUDA;
     }
@@ -142,6 +162,8 @@ void sp_cuda_free_weight(SpWeight* w) {
     if (!w) return;
     cudaSetDevice(w->device);
     cudaFree(w->d);
+    if (w->tiled) cudaFree(w->tiled);
+    w->ws.release();
     delete w;
 }
 
@@ -171,6 +193,16 @@ int32_t sp_cuda_matmul_nt_dev(const SpWeight* w, const float* x_dev, int64_t m, 
     if (!w || !x_dev || !y_dev || m < 0) { set_error("null argument"); return SP_ERR_ARG; }
     if (((uintptr_t)x_dev & 15) != 0) { set_error("x must be 16-byte aligned"); return SP_ERR_ARG; }
     SP_CUDA_TRY(cudaSetDevice(w->device));
+    if (w->tiled && g_gemv_path.load() == 0) {
+        for (int64_t m0 = 0; m0 < m; m0 += 16) {
+            ImmaArgs ia{};
+            ia.k = (int)w->k; ia.m = (int)std::min<int64_t>(16, m - m0); ia.nseg = 1;
+            ia.seg[0].wt = w->tiled; ia.seg[0].y = y_dev + m0 * w->n; ia.seg[0].dtype = w->dtype; ia.seg[0].n = (int)w->n;
+            ia.seg[0].ldy = (int)w->n; ia.seg[0].bpt = imma_q8_bpt(w->k);
+            SP_CUDA_TRY(launch_quant_gemv(x_dev + m0 * w->k, (int)w->k, ia, w->ws, true, (cudaStream_t)stream));
+        }
+        return SP_OK;
+    }
     GemvArgs a{};
     a.x = x_dev; a.ldx = (int)w->k; a.m = (int)m; a.k = (int)w->k; a.nseg = 1;
     a.seg[0].w = w->d; a.seg[0].y = y_dev; a.seg[0].dtype = w->dtype; a.seg[0].n = (int)w->n; a.seg[0].ldy = (int)w->n;

@@ -49,7 +49,8 @@ Engine::~Engine() {
     for (auto& r : prof_recs_) { cudaEventDestroy(r.a); cudaEventDestroy(r.b); }
     for (cudaEvent_t ev : prof_pool_) cudaEventDestroy(ev);
     if (d_tokens_) cudaFree(d_tokens_);
-    for (auto& kv : tensors_) cudaFree(kv.second.d);
+    for (auto& kv : tensors_) { if (kv.second.d) cudaFree(kv.second.d); if (kv.second.tiled) cudaFree(kv.second.tiled); }
+    ws_.release();
     for (void* p : owned_) cudaFree(p);
     void* bufs[] = {kv_.pool, d_page_table_, x_, h_, qkv_, attn_, gu_, mid_, sel_, logits_, trace_, d_ids_, d_argmax_,
                     d_tok_slot_, d_tok_pos_, cos_sin_};
@@ -127,6 +128,33 @@ const float* Engine::find_f32(const std::string& name, int64_t n) {
     return out;
 }
 
+// Tile-repack every quantised matrix for the tensor-core GEMV. The raw blocks are kept only for the
+// embedding table (rows are gathered from it); a tied output head therefore holds both layouts.
+int Engine::repack_weights() {
+    int kmax = 256;
+    for (auto& kv : tensors_) {
+        DevTensor& t = kv.second;
+        if (t.dims.size() != 2 || t.tiled) continue;
+        const int64_t n = t.dims[0], k = t.dims[1];
+        kmax = std::max<int>(kmax, (int)k);
+        if (!imma_supported(t.dtype, k)) continue;
+        const bool is_embed = &t == embed_;
+        if (is_embed && lm_head_ != embed_) continue;  // gather only
+        t.tiled_bytes = imma_tiled_bytes(t.dtype, n, k);
+        SP_CUDA_TRY(cudaMalloc((void**)&t.tiled, t.tiled_bytes + 16));
+        SP_CUDA_TRY(launch_repack(t.dtype, t.d, n, k, t.tiled, 0));
+        SP_CUDA_TRY(cudaStreamSynchronize(0));
+        weight_bytes += t.tiled_bytes;
+        if (!is_embed) {
+            cudaFree(t.d);
+            t.d = nullptr;
+            weight_bytes -= t.nbytes;
+        }
+    }
+    SP_CUDA_TRY(ws_.alloc(kmax));
+    return SP_OK;
+}
+
 int Engine::finalize() {
     if (finalized) return SP_OK;
     SP_CUDA_TRY(cudaSetDevice(d.device));
@@ -186,6 +214,10 @@ int Engine::finalize() {
             if (!(w.up = need(p + "mlp.up_proj.weight", d.ffn, hid))) return SP_ERR_STATE;
             if (!(w.down = need(p + "mlp.down_proj.weight", hid, d.ffn))) return SP_ERR_STATE;
         }
+    }
+    {
+        const int st = repack_weights();
+        if (st != SP_OK) return st;
     }
     // KV pages
     const int pages_per_seq = (d.max_ctx + KV_PAGE - 1) / KV_PAGE;

@@ -31,8 +31,10 @@ const char* get_error();
 struct DevTensor {
     int dtype = 0;
     std::vector<int64_t> dims;
-    uint8_t* d = nullptr;
+    uint8_t* d = nullptr;      // raw ggml blocks (freed after repacking unless rows are gathered from it)
     size_t nbytes = 0;
+    uint8_t* tiled = nullptr;  // tile-repacked copy for the tensor-core GEMV
+    size_t tiled_bytes = 0;
     int64_t numel() const { int64_t n = 1; for (auto v : dims) n *= v; return n; }
 };
 
@@ -101,6 +103,9 @@ class Engine {
     const DevTensor *embed_ = nullptr, *lm_head_ = nullptr;
     const float *final_w_ = nullptr, *final_b_ = nullptr;
     const float* lm_bias_ = nullptr;
+
+    ActWorkspace ws_;          // activation digits of the current GEMV input
+    int repack_weights();
 
     // paged KV cache
     KvGeom kv_{};

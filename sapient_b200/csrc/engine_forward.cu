@@ -66,11 +66,45 @@ int Engine::truncate(int slot, size_t n, size_t* kept) {
 int Engine::gemv(const float* x, int ldx, int m, int k, const DevTensor* w0, const float* b0, float* y0, int ldy0,
                  const DevTensor* w1, const float* b1, float* y1, const DevTensor* w2, const float* b2, float* y2,
                  const float* res) {
-    GemvArgs a{};
-    a.x = x; a.ldx = ldx; a.m = m; a.k = k; a.res = res; a.ldres = ldy0;
     const DevTensor* ws[3] = {w0, w1, w2};
     const float* bs[3] = {b0, b1, b2};
     float* ys[3] = {y0, y1, y2};
+    bool tiled = true;
+    for (int i = 0; i < 3 && ws[i]; ++i) tiled = tiled && ws[i]->tiled != nullptr;
+    if (tiled) {
+        // tensor-core path: digits of up to 16 activation rows at a time, all segments share them
+        for (int m0 = 0; m0 < m; m0 += 16) {
+            ImmaArgs ia{};
+            ia.k = k; ia.m = std::min(16, m - m0);
+            ia.res = res ? res + (size_t)m0 * ldy0 : nullptr;
+            ia.ldres = ldy0;
+            ia.nseg = 0;
+            for (int i = 0; i < 3 && ws[i]; ++i) {
+                ImmaSeg& sgm = ia.seg[i];
+                sgm.wt = ws[i]->tiled; sgm.bias = bs[i]; sgm.y = ys[i] + (size_t)m0 * ldy0; sgm.dtype = ws[i]->dtype;
+                sgm.n = (int)ws[i]->dims[0]; sgm.ldy = ldy0; sgm.bpt = imma_q8_bpt(k);
+                ia.nseg++;
+            }
+            ia.digits = ia.m <= 2 ? 3 : 2;
+            const int cols = ia.m * ia.digits;
+            ia.ncp = cols <= 8 ? 8 : cols <= 16 ? 16 : 32;
+            ia.eb = (k % 256 == 0) ? 256 : 32;
+            ia.xq = ws_.xq; ia.colscale = ws_.colscale; ia.xsum = ws_.xsum; ia.cinit16 = ws_.cinit16;
+            SP_LAUNCH(F_ELEM, launch_act_quant(x + (size_t)m0 * ldx, ldx, ia.m, k, ia.digits, ia.eb, ia.ncp, ws_.xq, ws_.colscale,
+                                               ws_.xsum, ws_.cinit16, stream));
+            SP_LAUNCH(F_GEMV, launch_gemv_imma(ia, stream));
+        }
+        return SP_OK;
+    }
+    if (w1 && (w0->tiled || w1->tiled || (w2 && w2->tiled))) {
+        // mixed layouts: one launch per matrix
+        SP_TRY(gemv(x, ldx, m, k, w0, b0, y0, ldy0, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, res));
+        SP_TRY(gemv(x, ldx, m, k, w1, b1, y1, ldy0));
+        if (w2) SP_TRY(gemv(x, ldx, m, k, w2, b2, y2, ldy0));
+        return SP_OK;
+    }
+    GemvArgs a{};
+    a.x = x; a.ldx = ldx; a.m = m; a.k = k; a.res = res; a.ldres = ldy0;
     a.nseg = 0;
     for (int i = 0; i < 3; ++i) {
         if (!ws[i]) break;
@@ -132,11 +166,10 @@ int Engine::enqueue_layers(int T) {
 int Engine::enqueue_head(int rows_from, int r0, int rc) {
     (void)rows_from;
     const int V = d.vocab, hid = d.hidden;
-    GemvArgs a{};
-    a.x = sel_ + (size_t)r0 * hid; a.ldx = hid; a.m = rc; a.k = hid; a.nseg = 1;
-    a.seg[0].w = lm_head_->d; a.seg[0].bias = lm_bias_; a.seg[0].y = logits_; a.seg[0].dtype = lm_head_->dtype;
-    a.seg[0].n = V; a.seg[0].ldy = V;
-    SP_LAUNCH(F_GEMV, launch_gemv(a, stream));
+    // lm_head rows beyond the vocabulary (if the table is larger) are not computed: n = V
+    DevTensor head = *lm_head_;
+    head.dims[0] = V;
+    SP_TRY(gemv(sel_ + (size_t)r0 * hid, hid, rc, hid, &head, lm_bias_, logits_, V));
     SP_LAUNCH(F_ARGMAX, launch_argmax(logits_, rc, V, V, d_argmax_, stream));
     return SP_OK;
 }

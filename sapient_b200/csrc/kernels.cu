@@ -22,6 +22,10 @@ namespace sp {
 static std::atomic<uint64_t> g_launches{0};
 uint64_t launch_count() { return g_launches.load(); }
 void adjust_launch_count(int64_t delta) { g_launches.fetch_add((uint64_t)delta, std::memory_order_relaxed); }
+cudaError_t count_launch_and_check() {
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return cudaGetLastError();
+}
 static inline cudaError_t finish_launch() {
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return cudaGetLastError();

@@ -5,6 +5,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "gemv_imma.cuh"
+
 namespace sp {
 
 // One weight matrix of a grouped dequant-GEMV: rows [N, K] of raw ggml blocks.
@@ -41,6 +43,30 @@ struct KvGeom {
 uint64_t launch_count();
 // Graph replays launch kernels without passing through the launchers; they report their node count here.
 void adjust_launch_count(int64_t delta);
+
+// Tensor-core GEMV on tile-repacked weights (gemv_imma.cu).
+bool imma_supported(int dtype, int64_t k);
+size_t imma_tiled_bytes(int dtype, int64_t n, int64_t k);
+int imma_q8_bpt(int64_t k);
+cudaError_t launch_repack(int dtype, const uint8_t* raw, int64_t n, int64_t k, uint8_t* tiled, cudaStream_t st);
+cudaError_t launch_act_quant(const float* x, int ldx, int m, int k, int digits, int eb, int ncp, int8_t* xq, float* colscale,
+                             int32_t* xsum, int32_t* cinit16, cudaStream_t st);
+cudaError_t launch_gemv_imma(const ImmaArgs& a, cudaStream_t st);
+
+// Workspace of the activation digits for up to 16 activation rows of k_max columns.
+struct ActWorkspace {
+    int8_t* xq = nullptr;
+    float* colscale = nullptr;
+    int32_t* xsum = nullptr;
+    int32_t* cinit16 = nullptr;
+    int k_max = 0;
+    static constexpr int NCP_MAX = 32;
+    cudaError_t alloc(int k_max_);
+    void release();
+};
+// Digits for x[m, k] (m <= 16) followed by the tensor-core GEMV over up to three weight segments sharing x.
+// Fills a.digits/ncp/eb/xq/...; a.seg/nseg/k/m/res must be set by the caller.
+cudaError_t launch_quant_gemv(const float* x, int ldx, ImmaArgs& a, const ActWorkspace& ws, bool requantize, cudaStream_t st);
 
 cudaError_t launch_dequant(int dtype, const uint8_t* w, int64_t n, int64_t k, float* out, cudaStream_t st);
 cudaError_t launch_gemv(const GemvArgs& a, cudaStream_t st);

@@ -162,5 +162,10 @@ def argmax(logits, device: int = 0) -> np.ndarray:
     return out
 
 
+def set_gemv_path(path: int) -> None:
+    """0: tensor-core GEMV on tile-repacked weights (default); 1: CUDA-core GEMV on raw blocks."""
+    check(lib().sp_cuda_set_gemv_path(path))
+
+
 def launch_count() -> int:
     return int(lib().sp_cuda_launch_count())

@@ -14,6 +14,10 @@ from sapient_b200.engine import ForwardEngine
 
 pytestmark = pytest.mark.gpu
 LOGIT_BAR = 2e-2
+# Prefill-shaped and decode-shaped calls must agree. They are not bit-identical: batches of more than two rows
+# carry two int8 digits per activation (2^-15 of the block maximum) instead of three (2^-23), which moves logits
+# by ~1e-4. The reference's own chunked-vs-per-token gate is 5e-3 (wgpu_coherence.rs:556-600).
+INVARIANCE_BAR = 1e-3
 MODELS = ["tiny_llama", "tiny_qwen", "tiny_phi2"]
 
 
@@ -69,15 +73,15 @@ def test_cached_decode_equals_full_forward_and_chunking_is_invisible(oracle, nam
     small = ForwardEngine.from_weights(cfg, W, max_tokens=4)  # 21 tokens -> 6 internal chunks
     full = big.forward_logits(ids, False)
     chunked = small.forward_logits(ids, False)
-    assert np.max(np.abs(full - chunked)) < 1e-4
+    assert np.max(np.abs(full - chunked)) < INVARIANCE_BAR
     big.reset_cache()
     for t in ids[:-1]:
         big.forward_logits([t], True)
     step = big.forward_logits([ids[-1]], True)
-    assert np.max(np.abs(full - step)) < 1e-4  # forward_test.rs:165-188
+    assert np.max(np.abs(full - step)) < INVARIANCE_BAR  # forward_test.rs:165-188
     all_rows = small.forward_all_logits(ids)
     assert all_rows.shape == (21, cfg["vocab"])
-    assert np.max(np.abs(all_rows[-1] - full)) < 1e-4
+    assert np.max(np.abs(all_rows[-1] - full)) < INVARIANCE_BAR
     ref = oracle_engine(oracle, cfg, W, kv_mode=1)
     assert np.max(np.abs(all_rows - ref.forward_all_logits_cached(ids))) < 2e-3
     big.close(); small.close()
@@ -108,7 +112,7 @@ def test_truncate_cache_rollback_and_verify_matches_sequential(oracle):
     assert eng.truncate_cache(100) == 12
     assert eng.truncate_cache(10) == 10
     seq = np.stack([eng.forward_logits([t], True) for t in drafts])
-    assert np.max(np.abs(ver - seq)) < 1e-4  # verify logits == sequential decode logits with the same cache
+    assert np.max(np.abs(ver - seq)) < INVARIANCE_BAR  # verify logits == sequential decode logits with the same cache
     eng.reset_cache()
     assert eng.seq_len() == 0
     eng.close()
@@ -125,7 +129,7 @@ def test_batched_decode_equals_independent_sequences(oracle):
         got = eng.forward_slot(i, p)
         solo.reset_cache()
         want = solo.forward_logits(p, True)
-        assert np.max(np.abs(got - want)) < 1e-4
+        assert np.max(np.abs(got - want)) < INVARIANCE_BAR
         want_last.append(want)
     toks = np.array([int(oracle.argmax(w)) for w in want_last], np.uint32)
     for step in range(4):
@@ -135,7 +139,7 @@ def test_batched_decode_equals_independent_sequences(oracle):
             prompts[i] = np.append(prompts[i], toks[i])
             solo.reset_cache()
             w = solo.forward_logits(prompts[i], True)
-            assert np.max(np.abs(logits[i] - w)) < 1e-4
+            assert np.max(np.abs(logits[i] - w)) < INVARIANCE_BAR
             assert am[i] == oracle.argmax(logits[i])
             nxt.append(int(oracle.argmax(w)))
         toks = np.array(nxt, np.uint32)

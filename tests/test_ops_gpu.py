@@ -51,9 +51,16 @@ MATMUL_CASES = [(1, 1536, 512), (3, 256, 48), (17, 256, 48), (1, 256, 1), (2, 51
                 (8, 2048, 64), (9, 512, 16), (32, 1024, 40)]
 
 
+@pytest.fixture(params=[0, 1], ids=["tensor-core", "cuda-core"])
+def gemv_path(request):
+    ops.set_gemv_path(request.param)
+    yield request.param
+    ops.set_gemv_path(0)
+
+
 @pytest.mark.parametrize("dtype", [Q4_K, Q6_K, Q8_0])
 @pytest.mark.parametrize("m,k,n", MATMUL_CASES)
-def test_matmul_nt_random_bits(oracle, dtype, m, k, n):
+def test_matmul_nt_random_bits(oracle, gemv_path, dtype, m, k, n):
     be, _ = synth.BLOCK[dtype]
     rng = np.random.default_rng(m * 1000 + k + n)
     raw = synth.random_bit_blocks(dtype, n * k // be, seed=k + n + dtype)
@@ -61,8 +68,31 @@ def test_matmul_nt_random_bits(oracle, dtype, m, k, n):
     got = ops.matmul_nt(x, raw, dtype, n)
     want = oracle.matmul_nt(x, raw, dtype, n)
     assert got.shape == (m, n)
-    assert rel_l2(got, want) < REL_L2_BAR, rel_l2(got, want)
-    assert rel_l2(got, want) < 2e-5  # what f32 accumulation in a different order should give
+    err = rel_l2(got, want)
+    assert err < REL_L2_BAR, err
+    # cuda-core: f32 accumulation in a different order. tensor-core: exact integer products, activations held
+    # to 2^-23 (m <= 2, three digits) or 2^-15 (two digits) of each 256-column block's maximum.
+    assert err < (2e-5 if gemv_path == 1 or m <= 2 else 3e-4), err
+
+
+@pytest.mark.parametrize("dtype", [Q4_K, Q6_K, Q8_0])
+def test_matmul_nt_activation_outliers_and_zeros(oracle, dtype):
+    """Digit conversion edge cases: a huge outlier in one block, all-zero blocks, denormal-scale rows."""
+    be, _ = synth.BLOCK[dtype]
+    k, n = 1024, 24
+    rng = np.random.default_rng(77)
+    raw = synth.random_bit_blocks(dtype, n * k // be, seed=dtype)
+    x = rng.standard_normal((4, k)).astype(np.float32)
+    x[0, 5] = 3.0e4
+    x[1, 256:512] = 0.0
+    x[2] *= 1e-30
+    x[3, :] = 0.0
+    for rows in (x[:1], x[1:3], x):
+        got = ops.matmul_nt(rows, raw, dtype, n)
+        want = oracle.matmul_nt(rows, raw, dtype, n)
+        assert np.all(np.isfinite(got))
+        assert rel_l2(got, want) < REL_L2_BAR
+    assert np.all(ops.matmul_nt(x[3:], raw, dtype, n) == 0.0)
 
 
 def test_matmul_nt_q8_0_small_k_like_hidden_896(oracle):
@@ -71,7 +101,7 @@ def test_matmul_nt_q8_0_small_k_like_hidden_896(oracle):
     raw = synth.random_bit_blocks(Q8_0, n * k // 32, seed=5)
     for m in (1, 2, 7):
         x = rng.standard_normal((m, k)).astype(np.float32)
-        assert rel_l2(ops.matmul_nt(x, raw, Q8_0, n), oracle.matmul_nt(x, raw, Q8_0, n)) < 2e-5
+        assert rel_l2(ops.matmul_nt(x, raw, Q8_0, n), oracle.matmul_nt(x, raw, Q8_0, n)) < (2e-5 if m <= 2 else 3e-4)
 
 
 def test_matmul_errors_mirror_reference():
