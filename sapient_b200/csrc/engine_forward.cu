@@ -85,13 +85,8 @@ int Engine::gemv(const float* x, int ldx, int m, int k, const DevTensor* w0, con
                 sgm.n = (int)ws[i]->dims[0]; sgm.ldy = ldy0; sgm.bpt = imma_q8_bpt(k);
                 ia.nseg++;
             }
-            ia.digits = ia.m <= 2 ? 3 : 2;
-            const int cols = ia.m * ia.digits;
-            ia.ncp = cols <= 8 ? 8 : cols <= 16 ? 16 : 32;
-            ia.eb = (k % 256 == 0) ? 256 : 32;
-            ia.xq = ws_.xq; ia.colscale = ws_.colscale; ia.xsum = ws_.xsum; ia.cinit16 = ws_.cinit16;
-            SP_LAUNCH(F_ELEM, launch_act_quant(x + (size_t)m0 * ldx, ldx, ia.m, k, ia.digits, ia.eb, ia.ncp, ws_.xq, ws_.colscale,
-                                               ws_.xsum, ws_.cinit16, stream));
+            imma_plan(ia, ws_);
+            SP_LAUNCH(F_ELEM, launch_act_quant(x + (size_t)m0 * ldx, ldx, ia, stream));
             SP_LAUNCH(F_GEMV, launch_gemv_imma(ia, stream));
         }
         return SP_OK;

@@ -142,23 +142,22 @@ cudaError_t launch_repack(int dtype, const uint8_t* raw, int64_t n, int64_t k, u
 
 // ─────────────────────────── activation digits ───────────────────────────────
 // One warp per (256 columns, activation row); lane handles 8 consecutive columns.
-__global__ void __launch_bounds__(32) act_quant_kernel(const float* __restrict__ x, int ldx, int k, int digits, int eb, int ncp,
-                                                       int8_t* __restrict__ xq, float* __restrict__ colscale,
-                                                       int32_t* __restrict__ xsum, int32_t* __restrict__ cinit16) {
-    const int lane = threadIdx.x, m = blockIdx.y;
-    const int k0 = blockIdx.x * 256 + lane * 8;
+__global__ void __launch_bounds__(32) act_quant_kernel(const float* __restrict__ x, int ldx, int k, int kp, int digits, int eb,
+                                                       int ncp, int8_t* __restrict__ xq, float* __restrict__ colscale,
+                                                       int8_t* __restrict__ xs32d, int8_t* __restrict__ xs16d) {
+    const int lane = threadIdx.x, m = blockIdx.y, tile = blockIdx.x;
+    const int k0 = tile * 256 + lane * 8;
     const bool live = k0 < k;
     float v[8];
     float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = 0.f;
     if (live) {
         const float4 a = *reinterpret_cast<const float4*>(x + (int64_t)m * ldx + k0);
         const float4 b = *reinterpret_cast<const float4*>(x + (int64_t)m * ldx + k0 + 4);
         v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
 #pragma unroll
         for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
-    } else {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) v[i] = 0.f;
     }
     // exponent block: the 4 lanes of a 32-column block, or the whole warp
     amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
@@ -169,53 +168,53 @@ __global__ void __launch_bounds__(32) act_quant_kernel(const float* __restrict__
         amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 16));
     }
     const int P = 8 * digits - 2;
-    int e = 0;
     float up = 0.f, down = 0.f;  // x * up -> fixed point; digit 0 scale = down
     if (amax > 0.f && amax < INFINITY) {
-        e = ilogbf(amax) + 1;              // amax < 2^e
+        int e = ilogbf(amax) + 1;          // amax < 2^e
         e = max(e, -100);                  // keep 2^(P-e) finite
         up = scalbnf(1.0f, P - e);         // exact powers of two
         down = scalbnf(1.0f, e - P);
     }
-    int dg[3][8];
+    // balanced base-256 digits, least significant first
+    uint32_t w0[3] = {0u, 0u, 0u}, w1[3] = {0u, 0u, 0u};
     int sum[3] = {0, 0, 0};
+    const int lim = 1 << P;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-        int X = __float2int_rn(v[i] * up);
-        const int lim = 1 << P;
-        X = max(-lim, min(lim, X));
-#pragma unroll
-        for (int d = 0; d < 3; ++d) {
-            int q;
-            if (d == digits - 1) { q = X; }
-            else { q = ((X + 128) & 255) - 128; X = (X - q) >> 8; }
-            if (d >= digits) q = 0;
-            dg[d][i] = q;
-            sum[d] += q;
-        }
+        int X = max(-lim, min(lim, __float2int_rn(v[i] * up)));
+        const int q0 = ((X + 128) & 255) - 128;
+        X = (X - q0) >> 8;
+        int q1, q2;
+        if (digits == 3) { q1 = ((X + 128) & 255) - 128; q2 = (X - q1) >> 8; }
+        else { q1 = X; q2 = 0; }
+        sum[0] += q0; sum[1] += q1; sum[2] += q2;
+        const int sh = 8 * (i & 3);
+        if (i < 4) { w0[0] |= (uint32_t)(q0 & 255) << sh; w0[1] |= (uint32_t)(q1 & 255) << sh; w0[2] |= (uint32_t)(q2 & 255) << sh; }
+        else { w1[0] |= (uint32_t)(q0 & 255) << sh; w1[1] |= (uint32_t)(q1 & 255) << sh; w1[2] |= (uint32_t)(q2 & 255) << sh; }
     }
-    const int blk32 = k0 >> 5, a4 = lane & 3;
-    // fragment order inside a 32-block: byte p = 8 t' + 4 h + i  <->  column 16 h + 4 t' + i
-    const int h = a4 >> 1, t0 = 2 * (a4 & 1);
-    for (int d = 0; d < digits && live; ++d) {
-        const int col = m * digits + d;
-        int8_t* dst = xq + (int64_t)col * k + (int64_t)blk32 * 32;
-        const uint32_t w0 = (uint32_t)(dg[d][0] & 255) | ((uint32_t)(dg[d][1] & 255) << 8) | ((uint32_t)(dg[d][2] & 255) << 16) |
-                            ((uint32_t)(dg[d][3] & 255) << 24);
-        const uint32_t w1 = (uint32_t)(dg[d][4] & 255) | ((uint32_t)(dg[d][5] & 255) << 8) | ((uint32_t)(dg[d][6] & 255) << 16) |
-                            ((uint32_t)(dg[d][7] & 255) << 24);
-        *reinterpret_cast<uint32_t*>(dst + 8 * t0 + 4 * h) = w0;
-        *reinterpret_cast<uint32_t*>(dst + 8 * (t0 + 1) + 4 * h) = w1;
-    }
-    // per-16 and per-32 digit sums
+    const int a4 = lane & 3, blk = lane >> 2;       // 32-block of the tile
+    const int h = a4 >> 1, t0 = 2 * (a4 & 1);       // columns 16h + 4t + i of the block go to byte 8t' ... see gemv_imma.cuh
 #pragma unroll
     for (int d = 0; d < 3; ++d) {
         const int s16 = sum[d] + __shfl_xor_sync(0xFFFFFFFFu, sum[d], 1);
         const int s32 = s16 + __shfl_xor_sync(0xFFFFFFFFu, s16, 2);
         if (d < digits && live) {
             const int col = m * digits + d;
-            if ((lane & 1) == 0) cinit16[(int64_t)(k0 >> 4) * ncp + col] = -32 * s16;
-            if (a4 == 0) xsum[(int64_t)blk32 * ncp + col] = s32;
+            int8_t* dst = xq + (int64_t)col * kp + (int64_t)tile * 256 + blk * 8 + 4 * h;
+            *reinterpret_cast<uint32_t*>(dst + t0 * 64) = w0[d];
+            *reinterpret_cast<uint32_t*>(dst + (t0 + 1) * 64) = w1[d];
+            int8_t* r32 = xs32d + ((int64_t)tile * ncp + col) * 32;
+            int8_t* r16 = xs16d + ((int64_t)tile * ncp + col) * 32;
+            if ((lane & 1) == 0) {
+                const int a = ((s16 + 32) & 63) - 32;
+                r16[lane >> 1] = (int8_t)a;
+                r16[16 + (lane >> 1)] = (int8_t)((s16 - a) >> 6);
+            }
+            if (a4 == 0) {
+                const int a = ((s32 + 32) & 63) - 32;
+                r32[blk] = (int8_t)a;
+                r32[16 + blk] = (int8_t)((s32 - a) >> 6);
+            }
         }
     }
     const bool writer = (eb == 256) ? (lane == 0) : (a4 == 0);
@@ -228,23 +227,62 @@ __global__ void __launch_bounds__(32) act_quant_kernel(const float* __restrict__
     }
 }
 
-cudaError_t launch_act_quant(const float* x, int ldx, int m, int k, int digits, int eb, int ncp, int8_t* xq, float* colscale,
-                             int32_t* xsum, int32_t* cinit16, cudaStream_t st) {
-    if (m <= 0) return cudaSuccess;
-    act_quant_kernel<<<dim3((k + 255) / 256, m), 32, 0, st>>>(x, ldx, k, digits, eb, ncp, xq, colscale, xsum, cinit16);
+void imma_plan(ImmaArgs& a, const ActWorkspace& ws) {
+    // 3 digits while they fit one 8-column n-tile (m <= 2), else 2 digits
+    a.digits = a.m <= 2 ? 3 : 2;
+    const int cols = a.m * a.digits;
+    a.ncp = cols <= 8 ? 8 : cols <= 16 ? 16 : 32;
+    a.eb = (a.k % 256 == 0) ? 256 : 32;
+    a.kp = (a.k + 255) / 256 * 256;
+    a.xq = ws.xq; a.colscale = ws.colscale; a.xs32d = ws.xs32d; a.xs16d = ws.xs16d;
+}
+
+cudaError_t launch_act_quant(const float* x, int ldx, const ImmaArgs& a, cudaStream_t st) {
+    if (a.m <= 0) return cudaSuccess;
+    act_quant_kernel<<<dim3(a.kp / 256, a.m), 32, 0, st>>>(x, ldx, a.k, a.kp, a.digits, a.eb, a.ncp, const_cast<int8_t*>(a.xq),
+                                                            const_cast<float*>(a.colscale), const_cast<int8_t*>(a.xs32d),
+                                                            const_cast<int8_t*>(a.xs16d));
     return count_launch_and_check();
 }
 
-// ─────────────────────────────── the GEMV ────────────────────────────────────
-__device__ __forceinline__ void imma_k32(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
-                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+cudaError_t ActWorkspace::alloc(int k_max_) {
+    release();
+    k_max = (k_max_ + 255) / 256 * 256;
+    const size_t tiles = (size_t)k_max / 256;
+    cudaError_t e;
+    if ((e = cudaMalloc((void**)&xq, (size_t)NCP_MAX * k_max)) != cudaSuccess) return e;
+    if ((e = cudaMalloc((void**)&colscale, (size_t)(k_max / 32) * NCP_MAX * 4)) != cudaSuccess) return e;
+    if ((e = cudaMalloc((void**)&xs32d, tiles * NCP_MAX * 32)) != cudaSuccess) return e;
+    if ((e = cudaMalloc((void**)&xs16d, tiles * NCP_MAX * 32)) != cudaSuccess) return e;
+    // unused digit columns are read (and meet zero digits): keep them finite; bytes 8..15 / 24..31 of the
+    // xs32d records are never written and must stay zero
+    cudaMemset(xq, 0, (size_t)NCP_MAX * k_max);
+    cudaMemset(colscale, 0, (size_t)(k_max / 32) * NCP_MAX * 4);
+    cudaMemset(xs32d, 0, tiles * NCP_MAX * 32);
+    cudaMemset(xs16d, 0, tiles * NCP_MAX * 32);
+    return cudaDeviceSynchronize();
 }
-__device__ __forceinline__ void imma_k16(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};\n"
-                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
-                 : "r"(a0), "r"(a1), "r"(b0));
+
+void ActWorkspace::release() {
+    if (xq) cudaFree(xq);
+    if (colscale) cudaFree(colscale);
+    if (xs32d) cudaFree(xs32d);
+    if (xs16d) cudaFree(xs16d);
+    xq = nullptr; colscale = nullptr; xs32d = nullptr; xs16d = nullptr; k_max = 0;
+}
+
+// ─────────────────────────────── the GEMV ────────────────────────────────────
+// d = a * b + c on the integer tensor path; c may be literal zeros.
+__device__ __forceinline__ void imma_k32(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1,
+                                         int c0, int c1, int c2, int c3) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};\n"
+                 : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(c0), "r"(c1), "r"(c2), "r"(c3));
+}
+__device__ __forceinline__ void imma_k16(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0, int c0, int c1, int c2, int c3) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%8,%9,%10};\n"
+                 : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+                 : "r"(a0), "r"(a1), "r"(b0), "r"(c0), "r"(c1), "r"(c2), "r"(c3));
 }
 
 __device__ __forceinline__ uint4 ldg_u4(const void* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
@@ -253,91 +291,126 @@ __device__ __forceinline__ int byte_s(uint32_t w, int i) { return (int)(int8_t)(
 
 constexpr int IMMA_WARPS = 8;
 
-// B fragments (digit words) of the eight 32-blocks of one 256-column tile for n-tile nt.
+// B fragments of one 256-column tile: for n-tile nt, words [2 * blk] and [2 * blk + 1] are the k 4t.. and k 16+4t..
+// digit words of 32-block blk for digit column nt * 8 + g. Columns past the live ones read zeros.
 template <int NT>
-__device__ __forceinline__ void load_b256(const ImmaArgs& a, int kt, int g, int t, uint2 (&b)[NT][8]) {
+struct BFrag {
+    uint32_t w[NT][16];
+};
+template <int NT>
+__device__ __forceinline__ void load_b256(const ImmaArgs& a, int kt, int g, int t, BFrag<NT>& b) {
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
         const int col = nt * 8 + g;
-        const bool on = col < a.m * a.digits;
-        const int8_t* base = a.xq + (int64_t)col * a.k + (int64_t)kt * 256 + 8 * t;
+        if (col < a.m * a.digits) {
+            const int8_t* base = a.xq + (int64_t)col * a.kp + (int64_t)kt * 256 + t * 64;
 #pragma unroll
-        for (int s = 0; s < 8; ++s) b[nt][s] = on ? __ldg(reinterpret_cast<const uint2*>(base + 32 * s)) : make_uint2(0u, 0u);
+            for (int i = 0; i < 4; ++i) {
+                const uint4 v = ldg_u4(base + 16 * i);
+                b.w[nt][4 * i] = v.x; b.w[nt][4 * i + 1] = v.y; b.w[nt][4 * i + 2] = v.z; b.w[nt][4 * i + 3] = v.w;
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) b.w[nt][i] = 0u;
+        }
     }
 }
 
-template <int NT>
-__device__ __forceinline__ void tile_q4_k(const ImmaArgs& a, const uint8_t* tile, int kt, int lane, float (&acc)[NT][4]) {
-    const int g = lane >> 2, t = lane & 3;
+// ── Q4_K ──
+struct Q4Regs {
     uint4 q[4];
+    uint4 h0, h1;
+};
+__device__ __forceinline__ void load_q4_k(const uint8_t* tile, int lane, Q4Regs& r) {
+    const int g = lane >> 2;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) q[j] = ldg_u4(tile + j * 512 + lane * 16);
-    const uint4 h0 = ldg_u4(tile + 2048 + g * 16), h1 = ldg_u4(tile + 2048 + (g + 8) * 16);
-    uint2 b[NT][8];
+    for (int j = 0; j < 4; ++j) r.q[j] = ldg_u4(tile + j * 512 + lane * 16);
+    r.h0 = ldg_u4(tile + 2048 + g * 16);
+    r.h1 = ldg_u4(tile + 2048 + (g + 8) * 16);
+}
+
+template <int NT>
+__device__ __forceinline__ void compute_q4_k(const ImmaArgs& a, const Q4Regs& r, int kt, int lane, float (&acc)[NT][4]) {
+    const int g = lane >> 2, t = lane & 3;
+    BFrag<NT> b;
     load_b256<NT>(a, kt, g, t, b);
-    // 6-bit scales / mins of the two rows -> one byte each
+    // 6-bit scales / mins of rows g and g+8 unpacked to one byte each (sub-blocks 0..3 | 4..7)
     uint32_t sc[2][2], mn[2][2];
     {
-        const uint4 hh[2] = {h0, h1};
+        const uint4 hh[2] = {r.h0, r.h1};
 #pragma unroll
-        for (int r = 0; r < 2; ++r) {
-            const uint32_t u0 = hh[r].y, u1 = hh[r].z, u2 = hh[r].w;
-            sc[r][0] = u0 & 0x3f3f3f3fu;
-            sc[r][1] = (u2 & 0x0f0f0f0fu) | (((u0 >> 6) & 0x03030303u) << 4);
-            mn[r][0] = u1 & 0x3f3f3f3fu;
-            mn[r][1] = ((u2 >> 4) & 0x0f0f0f0fu) | (((u1 >> 6) & 0x03030303u) << 4);
+        for (int i = 0; i < 2; ++i) {
+            const uint32_t u0 = hh[i].y, u1 = hh[i].z, u2 = hh[i].w;
+            sc[i][0] = u0 & 0x3f3f3f3fu;
+            sc[i][1] = (u2 & 0x0f0f0f0fu) | (((u0 >> 6) & 0x03030303u) << 4);
+            mn[i][0] = u1 & 0x3f3f3f3fu;
+            mn[i][1] = ((u2 >> 4) & 0x0f0f0f0fu) | (((u1 >> 6) & 0x03030303u) << 4);
         }
     }
-    int D[NT][4], Dm[NT][4];
+    int D[NT][4];
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) { D[nt][e] = 0; Dm[nt][e] = 0; }
+        for (int e = 0; e < 4; ++e) D[nt][e] = 0;
 #pragma unroll
     for (int s = 0; s < 8; ++s) {
         const int j = s >> 1, sh = (s & 1) * 4;
-        const uint32_t a0 = (q[j].x >> sh) & 0x0F0F0F0Fu, a2 = (q[j].y >> sh) & 0x0F0F0F0Fu;
-        const uint32_t a1 = (q[j].z >> sh) & 0x0F0F0F0Fu, a3 = (q[j].w >> sh) & 0x0F0F0F0Fu;
+        const uint32_t a0 = (r.q[j].x >> sh) & 0x0F0F0F0Fu, a2 = (r.q[j].y >> sh) & 0x0F0F0F0Fu;
+        const uint32_t a1 = (r.q[j].z >> sh) & 0x0F0F0F0Fu, a3 = (r.q[j].w >> sh) & 0x0F0F0F0Fu;
         const int sc0 = byte_u(sc[0][s >> 2], s & 3), sc1 = byte_u(sc[1][s >> 2], s & 3);
-        const int m0 = byte_u(mn[0][s >> 2], s & 3), m1 = byte_u(mn[1][s >> 2], s & 3);
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
-            int c[4] = {0, 0, 0, 0};
-            imma_k32(c, a0, a1, a2, a3, b[nt][s].x, b[nt][s].y);
+            int c[4];
+            imma_k32(c, a0, a1, a2, a3, b.w[nt][2 * s], b.w[nt][2 * s + 1], 0, 0, 0, 0);
             D[nt][0] += sc0 * c[0]; D[nt][1] += sc0 * c[1];
             D[nt][2] += sc1 * c[2]; D[nt][3] += sc1 * c[3];
-            const int2 xs = __ldg(reinterpret_cast<const int2*>(a.xsum + (int64_t)(kt * 8 + s) * a.ncp + nt * 8 + 2 * t));
-            Dm[nt][0] += m0 * xs.x; Dm[nt][1] += m0 * xs.y;
-            Dm[nt][2] += m1 * xs.x; Dm[nt][3] += m1 * xs.y;
         }
     }
-    const float d0 = half_bits_to_float((uint16_t)(h0.x & 0xFFFFu)), dm0 = half_bits_to_float((uint16_t)(h0.x >> 16));
-    const float d1 = half_bits_to_float((uint16_t)(h1.x & 0xFFFFu)), dm1 = half_bits_to_float((uint16_t)(h1.x >> 16));
+    // minimum term: sum_s m_s * S_s as two k16 mma over the sub-block index (S = a + 64 b)
+    const uint32_t am0 = t == 0 ? mn[0][0] : (t == 1 ? mn[0][1] : 0u);
+    const uint32_t am1 = t == 0 ? mn[1][0] : (t == 1 ? mn[1][1] : 0u);
+    const float d0 = half_bits_to_float((uint16_t)(r.h0.x & 0xFFFFu)), dm0 = half_bits_to_float((uint16_t)(r.h0.x >> 16));
+    const float d1 = half_bits_to_float((uint16_t)(r.h1.x & 0xFFFFu)), dm1 = half_bits_to_float((uint16_t)(r.h1.x >> 16));
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
-        const float2 cs = __ldg(reinterpret_cast<const float2*>(a.colscale + (int64_t)(kt * 256 / a.eb) * a.ncp + nt * 8 + 2 * t));
-        acc[nt][0] = fmaf(cs.x, d0 * (float)D[nt][0] - dm0 * (float)Dm[nt][0], acc[nt][0]);
-        acc[nt][1] = fmaf(cs.y, d0 * (float)D[nt][1] - dm0 * (float)Dm[nt][1], acc[nt][1]);
-        acc[nt][2] = fmaf(cs.x, d1 * (float)D[nt][2] - dm1 * (float)Dm[nt][2], acc[nt][2]);
-        acc[nt][3] = fmaf(cs.y, d1 * (float)D[nt][3] - dm1 * (float)Dm[nt][3], acc[nt][3]);
+        const int8_t* rec = a.xs32d + ((int64_t)kt * a.ncp + nt * 8 + g) * 32 + 4 * t;
+        const uint32_t ba = __ldg(reinterpret_cast<const uint32_t*>(rec)), bb = __ldg(reinterpret_cast<const uint32_t*>(rec + 16));
+        int ca[4], cb[4];
+        imma_k16(ca, am0, am1, ba, 0, 0, 0, 0);
+        imma_k16(cb, am0, am1, bb, 0, 0, 0, 0);
+        const float2 cs = __ldg(reinterpret_cast<const float2*>(a.colscale + (int64_t)kt * a.ncp + nt * 8 + 2 * t));
+        acc[nt][0] = fmaf(cs.x, d0 * (float)D[nt][0] - dm0 * (float)(ca[0] + 64 * cb[0]), acc[nt][0]);
+        acc[nt][1] = fmaf(cs.y, d0 * (float)D[nt][1] - dm0 * (float)(ca[1] + 64 * cb[1]), acc[nt][1]);
+        acc[nt][2] = fmaf(cs.x, d1 * (float)D[nt][2] - dm1 * (float)(ca[2] + 64 * cb[2]), acc[nt][2]);
+        acc[nt][3] = fmaf(cs.y, d1 * (float)D[nt][3] - dm1 * (float)(ca[3] + 64 * cb[3]), acc[nt][3]);
     }
 }
 
-template <int NT>
-__device__ __forceinline__ void tile_q6_k(const ImmaArgs& a, const uint8_t* tile, int kt, int lane, float (&acc)[NT][4]) {
-    const int g = lane >> 2, t = lane & 3;
+// ── Q6_K ──
+struct Q6Regs {
     uint32_t w[24];
+    uint4 s0, s1;
+    uint32_t dd;  // d of row g | d of row g+8 << 16
+};
+__device__ __forceinline__ void load_q6_k(const uint8_t* tile, int lane, Q6Regs& r) {
+    const int g = lane >> 2;
 #pragma unroll
     for (int i = 0; i < 6; ++i) {
         const uint4 v = ldg_u4(tile + i * 512 + lane * 16);
-        w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
+        r.w[4 * i] = v.x; r.w[4 * i + 1] = v.y; r.w[4 * i + 2] = v.z; r.w[4 * i + 3] = v.w;
     }
-    const uint4 s0 = ldg_u4(tile + 3072 + g * 16), s1 = ldg_u4(tile + 3072 + (g + 8) * 16);
-    const float d0 = half_bits_to_float(__ldg(reinterpret_cast<const uint16_t*>(tile + 3328 + 2 * g)));
-    const float d1 = half_bits_to_float(__ldg(reinterpret_cast<const uint16_t*>(tile + 3328 + 2 * (g + 8))));
-    uint2 b[NT][8];
+    r.s0 = ldg_u4(tile + 3072 + g * 16);
+    r.s1 = ldg_u4(tile + 3072 + (g + 8) * 16);
+    r.dd = (uint32_t)__ldg(reinterpret_cast<const uint16_t*>(tile + 3328 + 2 * g)) |
+           ((uint32_t)__ldg(reinterpret_cast<const uint16_t*>(tile + 3328 + 2 * (g + 8))) << 16);
+}
+
+template <int NT>
+__device__ __forceinline__ void compute_q6_k(const ImmaArgs& a, const Q6Regs& r, int kt, int lane, float (&acc)[NT][4]) {
+    const int g = lane >> 2, t = lane & 3;
+    BFrag<NT> b;
     load_b256<NT>(a, kt, g, t, b);
-    const uint32_t sw0[4] = {s0.x, s0.y, s0.z, s0.w}, sw1[4] = {s1.x, s1.y, s1.z, s1.w};
+    const uint32_t sw0[4] = {r.s0.x, r.s0.y, r.s0.z, r.s0.w}, sw1[4] = {r.s1.x, r.s1.y, r.s1.z, r.s1.w};
     int D[NT][4];
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt)
@@ -346,40 +419,48 @@ __device__ __forceinline__ void tile_q6_k(const ImmaArgs& a, const uint8_t* tile
 #pragma unroll
     for (int c = 0; c < 4; ++c) {       // c = (half, p)
         const int half = c >> 1, p = c & 1;
-        const uint32_t qlA0 = w[6 * c], qlB0 = w[6 * c + 1], qh0 = w[6 * c + 2];
-        const uint32_t qlA1 = w[6 * c + 3], qlB1 = w[6 * c + 4], qh1 = w[6 * c + 5];
+        const uint32_t qlA0 = r.w[6 * c], qlB0 = r.w[6 * c + 1], qh0 = r.w[6 * c + 2];
+        const uint32_t qlA1 = r.w[6 * c + 3], qlB1 = r.w[6 * c + 4], qh1 = r.w[6 * c + 5];
 #pragma unroll
         for (int Q = 0; Q < 4; ++Q) {   // quarter: 32-column slice of the 128-half
             const uint32_t l0 = (Q & 1) ? qlB0 : qlA0, l1 = (Q & 1) ? qlB1 : qlA1;
             const uint32_t n0 = (Q >= 2) ? (l0 >> 4) : l0, n1 = (Q >= 2) ? (l1 >> 4) : l1;
             const uint32_t hb0 = Q == 0 ? (qh0 << 4) : Q == 1 ? (qh0 << 2) : Q == 2 ? qh0 : (qh0 >> 2);
             const uint32_t hb1 = Q == 0 ? (qh1 << 4) : Q == 1 ? (qh1 << 2) : Q == 2 ? qh1 : (qh1 >> 2);
-            const uint32_t a0 = (n0 & 0x0F0F0F0Fu) | (hb0 & 0x30303030u);  // unsigned 0..63; the -32 rides in the C init
+            const uint32_t a0 = (n0 & 0x0F0F0F0Fu) | (hb0 & 0x30303030u);  // unsigned 0..63; the -32 is applied below
             const uint32_t a1 = (n1 & 0x0F0F0F0Fu) | (hb1 & 0x30303030u);
             const int gi = 8 * half + 2 * Q + p;   // 16-column scale group
             const int blk = 4 * half + Q;          // 32-block of the tile
             const int sc0 = byte_s(sw0[gi >> 2], gi & 3), sc1 = byte_s(sw1[gi >> 2], gi & 3);
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
-                const int2 ci = __ldg(reinterpret_cast<const int2*>(a.cinit16 + (int64_t)(kt * 16 + gi) * a.ncp + nt * 8 + 2 * t));
-                int cc[4] = {ci.x, ci.y, ci.x, ci.y};
-                imma_k16(cc, a0, a1, p ? b[nt][blk].y : b[nt][blk].x);
+                int cc[4];
+                imma_k16(cc, a0, a1, b.w[nt][2 * blk + p], 0, 0, 0, 0);
                 D[nt][0] += sc0 * cc[0]; D[nt][1] += sc0 * cc[1];
                 D[nt][2] += sc1 * cc[2]; D[nt][3] += sc1 * cc[3];
             }
         }
     }
+    // zero point: sum_g sc_g * (-32 S_g) with the int8 scales themselves as the A fragment (S = a + 64 b)
+    const float d0 = half_bits_to_float((uint16_t)(r.dd & 0xFFFFu)), d1 = half_bits_to_float((uint16_t)(r.dd >> 16));
+    const uint32_t az0 = t == 0 ? r.s0.x : t == 1 ? r.s0.y : t == 2 ? r.s0.z : r.s0.w;  // scales 4t..4t+3 of row g
+    const uint32_t az1 = t == 0 ? r.s1.x : t == 1 ? r.s1.y : t == 2 ? r.s1.z : r.s1.w;  // ... of row g+8
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
-        const float2 cs = __ldg(reinterpret_cast<const float2*>(a.colscale + (int64_t)(kt * 256 / a.eb) * a.ncp + nt * 8 + 2 * t));
-        acc[nt][0] = fmaf(cs.x * d0, (float)D[nt][0], acc[nt][0]);
-        acc[nt][1] = fmaf(cs.y * d0, (float)D[nt][1], acc[nt][1]);
-        acc[nt][2] = fmaf(cs.x * d1, (float)D[nt][2], acc[nt][2]);
-        acc[nt][3] = fmaf(cs.y * d1, (float)D[nt][3], acc[nt][3]);
+        const int8_t* rec = a.xs16d + ((int64_t)kt * a.ncp + nt * 8 + g) * 32 + 4 * t;
+        const uint32_t ba = __ldg(reinterpret_cast<const uint32_t*>(rec)), bb = __ldg(reinterpret_cast<const uint32_t*>(rec + 16));
+        int ca[4], cb[4];
+        imma_k16(ca, az0, az1, ba, 0, 0, 0, 0);
+        imma_k16(cb, az0, az1, bb, 0, 0, 0, 0);
+        const float2 cs = __ldg(reinterpret_cast<const float2*>(a.colscale + (int64_t)kt * a.ncp + nt * 8 + 2 * t));
+        acc[nt][0] = fmaf(cs.x * d0, (float)(D[nt][0] - 32 * (ca[0] + 64 * cb[0])), acc[nt][0]);
+        acc[nt][1] = fmaf(cs.y * d0, (float)(D[nt][1] - 32 * (ca[1] + 64 * cb[1])), acc[nt][1]);
+        acc[nt][2] = fmaf(cs.x * d1, (float)(D[nt][2] - 32 * (ca[2] + 64 * cb[2])), acc[nt][2]);
+        acc[nt][3] = fmaf(cs.y * d1, (float)(D[nt][3] - 32 * (ca[3] + 64 * cb[3])), acc[nt][3]);
     }
 }
 
-// Q8_0: one tile = bpt 32-blocks; kt counts tiles.
+// ── Q8_0: one tile = bpt 32-blocks; kt counts tiles ──
 template <int NT>
 __device__ __forceinline__ void tile_q8_0(const ImmaArgs& a, const uint8_t* tile, int kt, int bpt, int lane, float (&acc)[NT][4]) {
     const int g = lane >> 2, t = lane & 3;
@@ -392,9 +473,10 @@ __device__ __forceinline__ void tile_q8_0(const ImmaArgs& a, const uint8_t* tile
         for (int nt = 0; nt < NT; ++nt) {
             const int col = nt * 8 + g;
             uint2 b = make_uint2(0u, 0u);
-            if (col < a.m * a.digits) b = __ldg(reinterpret_cast<const uint2*>(a.xq + (int64_t)col * a.k + (int64_t)blk32 * 32 + 8 * t));
-            int c[4] = {0, 0, 0, 0};
-            imma_k32(c, q.x, q.z, q.y, q.w, b.x, b.y);
+            if (col < a.m * a.digits)
+                b = __ldg(reinterpret_cast<const uint2*>(a.xq + (int64_t)col * a.kp + (int64_t)(blk32 >> 3) * 256 + t * 64 + (blk32 & 7) * 8));
+            int c[4];
+            imma_k32(c, q.x, q.z, q.y, q.w, b.x, b.y, 0, 0, 0, 0);
             const float2 cs = __ldg(reinterpret_cast<const float2*>(a.colscale + (int64_t)(blk32 * 32 / a.eb) * a.ncp + nt * 8 + 2 * t));
             acc[nt][0] = fmaf(cs.x * d0, (float)c[0], acc[nt][0]);
             acc[nt][1] = fmaf(cs.y * d0, (float)c[1], acc[nt][1]);
@@ -404,8 +486,10 @@ __device__ __forceinline__ void tile_q8_0(const ImmaArgs& a, const uint8_t* tile
     }
 }
 
+// One CTA per tile row (16 weight rows); its warps split the k-tiles and prefetch the next tile's
+// weight registers before computing the current one.
 template <int NT>
-__global__ void __launch_bounds__(IMMA_WARPS * 32) gemv_imma_kernel(const ImmaArgs a) {
+__global__ void __launch_bounds__(IMMA_WARPS * 32, (NT <= 2 ? 2 : 1)) gemv_imma_kernel(const ImmaArgs a) {
     __shared__ float red[IMMA_WARPS][NT][4][32];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     int rt = blockIdx.x, s = 0;
@@ -419,11 +503,33 @@ __global__ void __launch_bounds__(IMMA_WARPS * 32) gemv_imma_kernel(const ImmaAr
     if (sg.dtype == T_Q4_K) {
         const int kts = a.k >> 8;
         const uint8_t* base = sg.wt + (int64_t)rt * kts * Q4_K_TILE_BYTES;
-        for (int kt = warp; kt < kts; kt += IMMA_WARPS) tile_q4_k<NT>(a, base + (int64_t)kt * Q4_K_TILE_BYTES, kt, lane, acc);
+        Q4Regs ra, rb;
+        int kt = warp;
+        if (kt < kts) load_q4_k(base + (int64_t)kt * Q4_K_TILE_BYTES, lane, ra);
+        while (kt < kts) {
+            const int k1 = kt + IMMA_WARPS, k2 = kt + 2 * IMMA_WARPS;
+            if (k1 < kts) load_q4_k(base + (int64_t)k1 * Q4_K_TILE_BYTES, lane, rb);
+            compute_q4_k<NT>(a, ra, kt, lane, acc);
+            if (k1 >= kts) break;
+            if (k2 < kts) load_q4_k(base + (int64_t)k2 * Q4_K_TILE_BYTES, lane, ra);
+            compute_q4_k<NT>(a, rb, k1, lane, acc);
+            kt = k2;
+        }
     } else if (sg.dtype == T_Q6_K) {
         const int kts = a.k >> 8;
         const uint8_t* base = sg.wt + (int64_t)rt * kts * Q6_K_TILE_BYTES;
-        for (int kt = warp; kt < kts; kt += IMMA_WARPS) tile_q6_k<NT>(a, base + (int64_t)kt * Q6_K_TILE_BYTES, kt, lane, acc);
+        Q6Regs ra, rb;
+        int kt = warp;
+        if (kt < kts) load_q6_k(base + (int64_t)kt * Q6_K_TILE_BYTES, lane, ra);
+        while (kt < kts) {
+            const int k1 = kt + IMMA_WARPS, k2 = kt + 2 * IMMA_WARPS;
+            if (k1 < kts) load_q6_k(base + (int64_t)k1 * Q6_K_TILE_BYTES, lane, rb);
+            compute_q6_k<NT>(a, ra, kt, lane, acc);
+            if (k1 >= kts) break;
+            if (k2 < kts) load_q6_k(base + (int64_t)k2 * Q6_K_TILE_BYTES, lane, ra);
+            compute_q6_k<NT>(a, rb, k1, lane, acc);
+            kt = k2;
+        }
     } else {
         const int bpt = sg.bpt, kts = (a.k >> 5) / bpt, tb = bpt * 544;
         const uint8_t* base = sg.wt + (int64_t)rt * kts * tb;
@@ -452,46 +558,6 @@ __global__ void __launch_bounds__(IMMA_WARPS * 32) gemv_imma_kernel(const ImmaAr
     }
 }
 
-cudaError_t ActWorkspace::alloc(int k_max_) {
-    release();
-    k_max = (k_max_ + 255) / 256 * 256;
-    cudaError_t e;
-    if ((e = cudaMalloc((void**)&xq, (size_t)NCP_MAX * k_max)) != cudaSuccess) return e;
-    if ((e = cudaMalloc((void**)&colscale, (size_t)(k_max / 32) * NCP_MAX * 4)) != cudaSuccess) return e;
-    if ((e = cudaMalloc((void**)&xsum, (size_t)(k_max / 32) * NCP_MAX * 4)) != cudaSuccess) return e;
-    if ((e = cudaMalloc((void**)&cinit16, (size_t)(k_max / 16) * NCP_MAX * 4)) != cudaSuccess) return e;
-    // unused digit columns are read (and multiplied by zero sums): keep them finite
-    cudaMemset(xq, 0, (size_t)NCP_MAX * k_max);
-    cudaMemset(colscale, 0, (size_t)(k_max / 32) * NCP_MAX * 4);
-    cudaMemset(xsum, 0, (size_t)(k_max / 32) * NCP_MAX * 4);
-    cudaMemset(cinit16, 0, (size_t)(k_max / 16) * NCP_MAX * 4);
-    return cudaDeviceSynchronize();
-}
-
-void ActWorkspace::release() {
-    if (xq) cudaFree(xq);
-    if (colscale) cudaFree(colscale);
-    if (xsum) cudaFree(xsum);
-    if (cinit16) cudaFree(cinit16);
-    xq = nullptr; colscale = nullptr; xsum = nullptr; cinit16 = nullptr; k_max = 0;
-}
-
-cudaError_t launch_quant_gemv(const float* x, int ldx, ImmaArgs& a, const ActWorkspace& ws, bool requantize, cudaStream_t st) {
-    if (a.m <= 0) return cudaSuccess;
-    if (a.m > 16 || a.k > ws.k_max) return cudaErrorInvalidValue;
-    // 3 digits while they fit one 8-column n-tile (m <= 2), else 2 digits
-    a.digits = a.m <= 2 ? 3 : 2;
-    const int cols = a.m * a.digits;
-    a.ncp = cols <= 8 ? 8 : cols <= 16 ? 16 : 32;
-    a.eb = (a.k % 256 == 0) ? 256 : 32;
-    a.xq = ws.xq; a.colscale = ws.colscale; a.xsum = ws.xsum; a.cinit16 = ws.cinit16;
-    if (requantize) {
-        cudaError_t e = launch_act_quant(x, ldx, a.m, a.k, a.digits, a.eb, a.ncp, ws.xq, ws.colscale, ws.xsum, ws.cinit16, st);
-        if (e != cudaSuccess) return e;
-    }
-    return launch_gemv_imma(a, st);
-}
-
 cudaError_t launch_gemv_imma(const ImmaArgs& a, cudaStream_t st) {
     if (a.m <= 0) return cudaSuccess;
     int tiles = 0;
@@ -503,6 +569,17 @@ cudaError_t launch_gemv_imma(const ImmaArgs& a, cudaStream_t st) {
     else if (nt == 4) gemv_imma_kernel<4><<<tiles, IMMA_WARPS * 32, 0, st>>>(a);
     else return cudaErrorInvalidValue;
     return count_launch_and_check();
+}
+
+cudaError_t launch_quant_gemv(const float* x, int ldx, ImmaArgs& a, const ActWorkspace& ws, bool requantize, cudaStream_t st) {
+    if (a.m <= 0) return cudaSuccess;
+    if (a.m > 16 || a.k > ws.k_max) return cudaErrorInvalidValue;
+    imma_plan(a, ws);
+    if (requantize) {
+        cudaError_t e = launch_act_quant(x, ldx, a, st);
+        if (e != cudaSuccess) return e;
+    }
+    return launch_gemv_imma(a, st);
 }
 
 }  // namespace sp

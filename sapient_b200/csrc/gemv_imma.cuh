@@ -51,10 +51,16 @@ struct ImmaArgs {
     int digits;   // 2 or 3
     int ncp;      // padded digit columns = 8 * NT
     int eb;       // columns per activation exponent block: 256 or 32
-    const int8_t* xq;       // [ncp][k] digits, fragment order inside each 32-block
+    int kp;       // k rounded up to 256: column stride of xq
+    // Digits: xq[col][kp]; inside each 256-column tile the bytes are ordered [t 0..3][block 0..7][8 B], the 8 B
+    // of (t, block) being columns 4t..4t+3 and 16+4t..16+4t+3 of that 32-block (one lane's B fragment).
+    const int8_t* xq;
     const float* colscale;  // [k / eb][ncp]
-    const int32_t* xsum;    // [k / 32][ncp] digit sums per 32-block
-    const int32_t* cinit16; // [k / 16][ncp] = -32 * digit sums per 16-block (Q6_K zero point)
+    // Digit sums S of every 32-block (xs32d) and 16-block (xs16d) of a tile, split as S = a + 64 b with a in
+    // [-32, 31]: records [k / 256][ncp][32 B] = { a[0..7], 0 x 8, b[0..7], 0 x 8 } resp. { a[0..15], b[0..15] }.
+    // They feed one extra mma per tile for the Q4_K minimum term and the Q6_K zero point.
+    const int8_t* xs32d;
+    const int8_t* xs16d;
     const float* res;       // optional residual for segment 0 (may alias its y)
     int ldres;
     int pad_;

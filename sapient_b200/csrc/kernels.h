@@ -49,16 +49,18 @@ bool imma_supported(int dtype, int64_t k);
 size_t imma_tiled_bytes(int dtype, int64_t n, int64_t k);
 int imma_q8_bpt(int64_t k);
 cudaError_t launch_repack(int dtype, const uint8_t* raw, int64_t n, int64_t k, uint8_t* tiled, cudaStream_t st);
-cudaError_t launch_act_quant(const float* x, int ldx, int m, int k, int digits, int eb, int ncp, int8_t* xq, float* colscale,
-                             int32_t* xsum, int32_t* cinit16, cudaStream_t st);
+struct ActWorkspace;
+// Fills digits / ncp / eb / kp and the table pointers of `a` from a.m, a.k and the workspace.
+void imma_plan(ImmaArgs& a, const ActWorkspace& ws);
+cudaError_t launch_act_quant(const float* x, int ldx, const ImmaArgs& a, cudaStream_t st);
 cudaError_t launch_gemv_imma(const ImmaArgs& a, cudaStream_t st);
 
 // Workspace of the activation digits for up to 16 activation rows of k_max columns.
 struct ActWorkspace {
     int8_t* xq = nullptr;
     float* colscale = nullptr;
-    int32_t* xsum = nullptr;
-    int32_t* cinit16 = nullptr;
+    int8_t* xs32d = nullptr;
+    int8_t* xs16d = nullptr;
     int k_max = 0;
     static constexpr int NCP_MAX = 32;
     cudaError_t alloc(int k_max_);
