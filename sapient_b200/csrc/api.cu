@@ -338,8 +338,13 @@ int32_t sp_cuda_attention(int32_t device, const float* q, const float* k, const 
     KvGeom g{};
     g.pool = dpool.as<__half>(); g.page_table = dpt.as<int32_t>(); g.n_pages = n_pages; g.n_kv = (int)Hkv;
     g.head_dim = (int)hd; g.max_pages = n_pages;
+    // decode-shaped calls split the keys over several blocks, like the engine does
+    const int splits = sq <= 4 ? 8 : 1;
+    DevBuf dscr;
+    SP_CUDA_TRY(dscr.alloc(attention_scratch_floats((int)sq, (int)H, splits, (int)hd) * 4));
     SP_CUDA_TRY(launch_attention(dq.as<float>(), (int)(H * hd), dout.as<float>(), (int)(H * hd), (int)sq, (int)H,
-                                 dslot.as<int32_t>(), dpos.as<int32_t>(), g, 0, 1.0f / sqrtf((float)hd), 0));
+                                 dslot.as<int32_t>(), dpos.as<int32_t>(), g, 0, 1.0f / sqrtf((float)hd), splits,
+                                 dscr.as<float>(), 0));
     SP_CUDA_TRY(cudaMemcpy(qt.data(), dout.p, qt.size() * 4, cudaMemcpyDeviceToHost));
     for (int64_t h = 0; h < H; ++h)
         for (int64_t t = 0; t < sq; ++t)

@@ -51,6 +51,7 @@ Engine::~Engine() {
     if (d_tokens_) cudaFree(d_tokens_);
     for (auto& kv : tensors_) { if (kv.second.d) cudaFree(kv.second.d); if (kv.second.tiled) cudaFree(kv.second.tiled); }
     ws_.release();
+    if (att_scratch_) cudaFree(att_scratch_);
     for (void* p : owned_) cudaFree(p);
     void* bufs[] = {kv_.pool, d_page_table_, x_, h_, qkv_, attn_, gu_, mid_, sel_, logits_, trace_, d_ids_, d_argmax_,
                     d_tok_slot_, d_tok_pos_, cos_sin_};
@@ -245,6 +246,7 @@ int Engine::finalize() {
     SP_CUDA_TRY(cudaMalloc((void**)&gu_, T * (size_t)d.ffn * 2 * 4));
     SP_CUDA_TRY(cudaMalloc((void**)&mid_, T * (size_t)d.ffn * 4));
     SP_CUDA_TRY(cudaMalloc((void**)&sel_, T * hid * 4));
+    SP_CUDA_TRY(cudaMalloc((void**)&att_scratch_, attention_scratch_floats(ATT_SPLIT_TOKENS, H, ATT_SPLITS, hd) * 4));
     logit_rows_ = std::min<int>(32, d.max_tokens);
     SP_CUDA_TRY(cudaMalloc((void**)&logits_, (size_t)logit_rows_ * d.vocab * 4));
     SP_CUDA_TRY(cudaMalloc((void**)&d_ids_, T * 4));

@@ -105,6 +105,10 @@ class Engine {
     const float* lm_bias_ = nullptr;
 
     ActWorkspace ws_;          // activation digits of the current GEMV input
+    // split-K attention: decode-shaped calls (T <= ATT_SPLIT_TOKENS) split the keys over ATT_SPLITS blocks
+    static constexpr int ATT_SPLITS = 16, ATT_SPLIT_TOKENS = 32;
+    float* att_scratch_ = nullptr;
+    int attention(int l, int T);
     int repack_weights();
 
     // paged KV cache

@@ -111,6 +111,15 @@ int Engine::gemv(const float* x, int ldx, int m, int k, const DevTensor* w0, con
     return SP_OK;
 }
 
+int Engine::attention(int l, int T) {
+    const int H = d.n_heads, Hkv = d.n_kv_heads, hd = d.head_dim;
+    const int qkv_ld = (H + 2 * Hkv) * hd;
+    const int splits = T <= ATT_SPLIT_TOKENS ? ATT_SPLITS : 1;
+    SP_LAUNCH(F_ATTN, launch_attention(qkv_, qkv_ld, attn_, H * hd, T, H, d_tok_slot_, d_tok_pos_, kv_, l, 1.0f / sqrtf((float)hd),
+                                       splits, att_scratch_, stream));
+    return SP_OK;
+}
+
 int Engine::layer_llama(const LayerW& w, int l, int T) {
     const int H = d.n_heads, Hkv = d.n_kv_heads, hd = d.head_dim, hid = d.hidden, ffn = d.ffn;
     const int qkv_ld = (H + 2 * Hkv) * hd;
@@ -118,8 +127,7 @@ int Engine::layer_llama(const LayerW& w, int l, int T) {
     SP_TRY(gemv(h_, hid, T, hid, w.q, w.qb, qkv_, qkv_ld, w.k, w.kb, qkv_ + (size_t)H * hd, w.v, w.vb,
                 qkv_ + (size_t)(H + Hkv) * hd));
     SP_LAUNCH(F_ROPE, launch_rope_kv_append(qkv_, T, H, Hkv, hd, d.rotary_dim, cos_sin_, d_tok_slot_, d_tok_pos_, kv_, l, stream));
-    SP_LAUNCH(F_ATTN, launch_attention(qkv_, qkv_ld, attn_, H * hd, T, H, d_tok_slot_, d_tok_pos_, kv_, l,
-                                       1.0f / sqrtf((float)hd), stream));
+    SP_TRY(attention(l, T));
     SP_TRY(gemv(attn_, H * hd, T, H * hd, w.o, w.ob, x_, hid, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, x_));
     SP_LAUNCH(F_NORM, launch_rms_norm(x_, w.n2w, T, hid, d.norm_eps, h_, stream));
     SP_TRY(gemv(h_, hid, T, hid, w.gate, nullptr, gu_, 2 * ffn, w.up, nullptr, gu_ + ffn));
@@ -135,8 +143,7 @@ int Engine::layer_phi(const LayerW& w, int l, int T) {
     SP_TRY(gemv(h_, hid, T, hid, w.q, w.qb, qkv_, qkv_ld, w.k, w.kb, qkv_ + (size_t)H * hd, w.v, w.vb,
                 qkv_ + (size_t)(H + Hkv) * hd));
     SP_LAUNCH(F_ROPE, launch_rope_kv_append(qkv_, T, H, Hkv, hd, d.rotary_dim, cos_sin_, d_tok_slot_, d_tok_pos_, kv_, l, stream));
-    SP_LAUNCH(F_ATTN, launch_attention(qkv_, qkv_ld, attn_, H * hd, T, H, d_tok_slot_, d_tok_pos_, kv_, l,
-                                       1.0f / sqrtf((float)hd), stream));
+    SP_TRY(attention(l, T));
     // parallel block: x + (attn_out + mlp(h)); both branches read the same normalised input h
     SP_TRY(gemv(h_, hid, T, hid, w.up, w.upb, mid_, ffn));
     SP_LAUNCH(F_ELEM, launch_gelu(mid_, (int64_t)T * ffn, stream));

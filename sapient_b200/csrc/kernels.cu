@@ -379,98 +379,6 @@ cudaError_t launch_rope(float* x, int n_tok, int n_heads, int head_dim, int rota
     return finish_launch();
 }
 
-// ─────────────────────────────── attention ──────────────────────────────────
-// One block per (head, token). Warps stride over the keys 0..pos of the token's slot;
-// each warp runs the reference's online-softmax recurrence on its subset with lanes
-// splitting head_dim in (even, odd) pairs, and the per-warp states are merged with the
-// usual log-sum-exp correction. K and V are fp16 in the paged cache, all math is f32.
-constexpr int ATT_WARPS = 4;
-constexpr int ATT_MAX_PAIRS = 4;  // head_dim <= 256
-
-__global__ void __launch_bounds__(ATT_WARPS * 32)
-attention_kernel(const float* __restrict__ q, int ldq, float* __restrict__ out, int ldo, int n_heads,
-                 const int32_t* __restrict__ tok_slot, const int32_t* __restrict__ tok_pos, KvGeom kv, int layer,
-                 float scale) {
-    __shared__ float sh_m[ATT_WARPS], sh_l[ATT_WARPS];
-    __shared__ float sh_o[ATT_WARPS][256];
-    const int h = blockIdx.x, t = blockIdx.y;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int hd = kv.head_dim, npairs = hd >> 1;
-    const int slot = tok_slot[t], n_keys = tok_pos[t] + 1;
-    const int kv_h = h / (n_heads / kv.n_kv);
-    const float* qrow = q + (int64_t)t * ldq + (int64_t)h * hd;
-    float2 qv[ATT_MAX_PAIRS], o[ATT_MAX_PAIRS];
-#pragma unroll
-    for (int i = 0; i < ATT_MAX_PAIRS; ++i) {
-        const int p = lane + 32 * i;
-        qv[i] = (p < npairs) ? make_float2(qrow[2 * p], qrow[2 * p + 1]) : make_float2(0.f, 0.f);
-        o[i] = make_float2(0.f, 0.f);
-    }
-    float m = -INFINITY, l = 0.f;
-    const int32_t* pt = kv.page_table + (int64_t)slot * kv.max_pages;
-    for (int key = warp; key < n_keys; key += ATT_WARPS) {
-        const int page = pt[key / KV_PAGE];
-        const __half* kp = kv.pool + kv_offset(kv, layer, page, 0, kv_h) + (int64_t)(key % KV_PAGE) * hd;
-        const __half* vp = kv.pool + kv_offset(kv, layer, page, 1, kv_h) + (int64_t)(key % KV_PAGE) * hd;
-        float part = 0.f;
-#pragma unroll
-        for (int i = 0; i < ATT_MAX_PAIRS; ++i) {
-            const int p = lane + 32 * i;
-            if (p < npairs) {
-                const float2 kf = __half22float2(reinterpret_cast<const __half2*>(kp)[p]);
-                part = fmaf(qv[i].x, kf.x, part);
-                part = fmaf(qv[i].y, kf.y, part);
-            }
-        }
-        const float s = warp_sum(part) * scale;
-        const float m_new = fmaxf(m, s);
-        const float pw = expf(s - m_new);
-        const float corr = expf(m - m_new);  // exp(-inf) = 0 on the first key
-#pragma unroll
-        for (int i = 0; i < ATT_MAX_PAIRS; ++i) {
-            const int p = lane + 32 * i;
-            if (p < npairs) {
-                const float2 vf = __half22float2(reinterpret_cast<const __half2*>(vp)[p]);
-                o[i].x = fmaf(pw, vf.x, corr * o[i].x);
-                o[i].y = fmaf(pw, vf.y, corr * o[i].y);
-            }
-        }
-        l = fmaf(corr, l, pw);
-        m = m_new;
-    }
-    if (lane == 0) { sh_m[warp] = m; sh_l[warp] = l; }
-#pragma unroll
-    for (int i = 0; i < ATT_MAX_PAIRS; ++i) {
-        const int p = lane + 32 * i;
-        if (p < npairs) { sh_o[warp][2 * p] = o[i].x; sh_o[warp][2 * p + 1] = o[i].y; }
-    }
-    __syncthreads();
-    float M = sh_m[0];
-#pragma unroll
-    for (int w = 1; w < ATT_WARPS; ++w) M = fmaxf(M, sh_m[w]);
-    float L = 0.f, cw[ATT_WARPS];
-#pragma unroll
-    for (int w = 0; w < ATT_WARPS; ++w) {
-        cw[w] = (sh_m[w] == -INFINITY) ? 0.f : expf(sh_m[w] - M);
-        L = fmaf(cw[w], sh_l[w], L);
-    }
-    const float inv = (L == 0.f) ? 0.f : 1.0f / L;
-    for (int e = threadIdx.x; e < hd; e += blockDim.x) {
-        float acc = 0.f;
-#pragma unroll
-        for (int w = 0; w < ATT_WARPS; ++w) acc = fmaf(cw[w], sh_o[w][e], acc);
-        out[(int64_t)t * ldo + (int64_t)h * hd + e] = acc * inv;
-    }
-}
-
-cudaError_t launch_attention(const float* q, int ldq, float* out, int ldo, int n_tok, int n_heads, const int32_t* tok_slot,
-                             const int32_t* tok_pos, KvGeom kv, int layer, float scale, cudaStream_t st) {
-    if (n_tok == 0) return cudaSuccess;
-    attention_kernel<<<dim3(n_heads, n_tok), ATT_WARPS * 32, 0, st>>>(q, ldq, out, ldo, n_heads, tok_slot, tok_pos, kv, layer,
-                                                                      scale);
-    return finish_launch();
-}
-
 // ─────────────────────────────── elementwise ─────────────────────────────────
 __device__ __forceinline__ float silu_f(float v) { return v / (1.0f + expf(-v)); }
 __device__ __forceinline__ float gelu_f(float v) {

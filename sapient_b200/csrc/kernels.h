@@ -85,9 +85,12 @@ cudaError_t launch_rope_kv_append(float* qkv, int n_tok, int n_heads, int n_kv, 
 // Rotation only (no cache): x[T, n_heads*hd] in place. Used by the standalone RoPE op.
 cudaError_t launch_rope(float* x, int n_tok, int n_heads, int head_dim, int rotary_dim, const float2* cos_sin,
                         const int32_t* tok_pos, int ld, cudaStream_t st);
-// Causal GQA attention of each token against keys 0..pos of its slot, online softmax.
+// Causal GQA attention of each token against keys 0..pos of its slot, online softmax, keys split over
+// n_splits blocks per (head, token). n_splits > 1 needs `scratch` of attention_scratch_floats() floats.
+size_t attention_scratch_floats(int n_tok, int n_heads, int n_splits, int head_dim);
 cudaError_t launch_attention(const float* q, int ldq, float* out, int ldo, int n_tok, int n_heads, const int32_t* tok_slot,
-                             const int32_t* tok_pos, KvGeom kv, int layer, float scale, cudaStream_t st);
+                             const int32_t* tok_pos, KvGeom kv, int layer, float scale, int n_splits, float* scratch,
+                             cudaStream_t st);
 cudaError_t launch_swiglu(const float* gate_up, int ld, int ffn, int rows, float* out, cudaStream_t st);
 cudaError_t launch_gelu(float* x, int64_t n, cudaStream_t st);
 cudaError_t launch_silu(float* x, int64_t n, cudaStream_t st);

@@ -58,9 +58,9 @@ def test_graph_replay_and_profiling_are_bitwise_neutral():
         before = ops.launch_count()
         logits, am = eng.decode_batch(ids, [0, 1, 2], want_logits=True, want_argmax=True)
         launched = ops.launch_count() - before
-        # per layer: 2 norms, rope+kv, attention, swiglu, 4 x (activation digits + GEMV); plus embed, final norm,
-        # digits + lm_head, argmax
-        assert launched == 2 * 13 + 5, launched
+        # per layer: 2 norms, rope+kv, attention (split + merge), swiglu, 4 x (activation digits + GEMV); plus embed,
+        # final norm, digits + lm_head, argmax
+        assert launched == 2 * 14 + 5, launched
         outs.append((logits.copy(), am.copy()))
         for s in range(3):
             assert eng.truncate_cache(lens[s], s) == lens[s]
