@@ -162,6 +162,15 @@ size_t attention_scratch_floats(int n_tok, int n_heads, int n_splits, int head_d
     return n_splits > 1 ? (size_t)n_tok * n_heads * n_splits * (head_dim + 2) : 0;
 }
 
+cudaError_t launch_attention_split(const float* q, int ldq, int n_tok, int n_heads, const int32_t* tok_slot, const int32_t* tok_pos,
+                                   KvGeom kv, int layer, float scale, int n_splits, float* scratch, cudaStream_t st) {
+    if (n_tok == 0) return cudaSuccess;
+    if (n_splits < 2 || !scratch) return cudaErrorInvalidValue;
+    attention_split_kernel<<<dim3(n_heads, n_tok, n_splits), ATT_WARPS * 32, 0, st>>>(q, ldq, nullptr, 0, n_heads, tok_slot, tok_pos, kv,
+                                                                                     layer, scale, n_splits, scratch);
+    return count_launch_and_check();
+}
+
 cudaError_t launch_attention(const float* q, int ldq, float* out, int ldo, int n_tok, int n_heads, const int32_t* tok_slot,
                              const int32_t* tok_pos, KvGeom kv, int layer, float scale, int n_splits, float* scratch,
                              cudaStream_t st) {

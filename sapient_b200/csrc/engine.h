@@ -83,7 +83,8 @@ class Engine {
   private:
     int run_chunk(const uint32_t* ids, const int32_t* slots, int T, int rows_from, float* logits_out, uint32_t* argmax_out);
     int enqueue_layers(int T);                       // embed + all layers for the staged token table
-    int enqueue_head(int rows_from, int r0, int rc); // final norm is done by the caller; lm_head + argmax of rc rows
+    // final norm is done by the caller; lm_head + argmax of rc rows (pre: digits of those rows already in the workspace)
+    int enqueue_head(int rows_from, int r0, int rc, const ImmaArgs* pre = nullptr);
     int enqueue_decode_step(int T);                  // embed, layers, final norm, lm_head, argmax for T <= logit_rows_ rows
     int launch_decode_step(int T);                   // the same through a cached CUDA graph when allowed
     void prof_begin(int fam);
@@ -95,7 +96,9 @@ class Engine {
     int layer_phi(const LayerW& w, int l, int T);
     int gemv(const float* x, int ldx, int m, int k, const DevTensor* w0, const float* b0, float* y0, int ldy0,
              const DevTensor* w1 = nullptr, const float* b1 = nullptr, float* y1 = nullptr, const DevTensor* w2 = nullptr,
-             const float* b2 = nullptr, float* y2 = nullptr, const float* res = nullptr);
+             const float* b2 = nullptr, float* y2 = nullptr, const float* res = nullptr, const ImmaArgs* pre = nullptr);
+    bool plan_digits(int m, int k, ImmaArgs& ia);
+    int attention_and_oproj(const LayerW& w, int l, int T);
 
     std::map<std::string, DevTensor> tensors_;
     std::vector<void*> owned_;  // extra device allocations (converted biases, ...)
@@ -108,7 +111,6 @@ class Engine {
     // split-K attention: decode-shaped calls (T <= ATT_SPLIT_TOKENS) split the keys over ATT_SPLITS blocks
     static constexpr int ATT_SPLITS = 16, ATT_SPLIT_TOKENS = 32;
     float* att_scratch_ = nullptr;
-    int attention(int l, int T);
     int repack_weights();
 
     // paged KV cache

@@ -63,95 +63,6 @@ int Engine::truncate(int slot, size_t n, size_t* kept) {
     return SP_OK;
 }
 
-int Engine::gemv(const float* x, int ldx, int m, int k, const DevTensor* w0, const float* b0, float* y0, int ldy0,
-                 const DevTensor* w1, const float* b1, float* y1, const DevTensor* w2, const float* b2, float* y2,
-                 const float* res) {
-    const DevTensor* ws[3] = {w0, w1, w2};
-    const float* bs[3] = {b0, b1, b2};
-    float* ys[3] = {y0, y1, y2};
-    bool tiled = true;
-    for (int i = 0; i < 3 && ws[i]; ++i) tiled = tiled && ws[i]->tiled != nullptr;
-    if (tiled) {
-        // tensor-core path: digits of up to 16 activation rows at a time, all segments share them
-        for (int m0 = 0; m0 < m; m0 += 16) {
-            ImmaArgs ia{};
-            ia.k = k; ia.m = std::min(16, m - m0);
-            ia.res = res ? res + (size_t)m0 * ldy0 : nullptr;
-            ia.ldres = ldy0;
-            ia.nseg = 0;
-            for (int i = 0; i < 3 && ws[i]; ++i) {
-                ImmaSeg& sgm = ia.seg[i];
-                sgm.wt = ws[i]->tiled; sgm.bias = bs[i]; sgm.y = ys[i] + (size_t)m0 * ldy0; sgm.dtype = ws[i]->dtype;
-                sgm.n = (int)ws[i]->dims[0]; sgm.ldy = ldy0; sgm.bpt = imma_q8_bpt(k);
-                ia.nseg++;
-            }
-            imma_plan(ia, ws_);
-            SP_LAUNCH(F_ELEM, launch_act_quant(x + (size_t)m0 * ldx, ldx, ia, stream));
-            SP_LAUNCH(F_GEMV, launch_gemv_imma(ia, stream));
-        }
-        return SP_OK;
-    }
-    if (w1 && (w0->tiled || w1->tiled || (w2 && w2->tiled))) {
-        // mixed layouts: one launch per matrix
-        SP_TRY(gemv(x, ldx, m, k, w0, b0, y0, ldy0, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, res));
-        SP_TRY(gemv(x, ldx, m, k, w1, b1, y1, ldy0));
-        if (w2) SP_TRY(gemv(x, ldx, m, k, w2, b2, y2, ldy0));
-        return SP_OK;
-    }
-    GemvArgs a{};
-    a.x = x; a.ldx = ldx; a.m = m; a.k = k; a.res = res; a.ldres = ldy0;
-    a.nseg = 0;
-    for (int i = 0; i < 3; ++i) {
-        if (!ws[i]) break;
-        a.seg[i].w = ws[i]->d; a.seg[i].bias = bs[i]; a.seg[i].y = ys[i]; a.seg[i].dtype = ws[i]->dtype;
-        a.seg[i].n = (int)ws[i]->dims[0]; a.seg[i].ldy = ldy0;
-        a.nseg++;
-    }
-    SP_LAUNCH(F_GEMV, launch_gemv(a, stream));
-    return SP_OK;
-}
-
-int Engine::attention(int l, int T) {
-    const int H = d.n_heads, Hkv = d.n_kv_heads, hd = d.head_dim;
-    const int qkv_ld = (H + 2 * Hkv) * hd;
-    const int splits = T <= ATT_SPLIT_TOKENS ? ATT_SPLITS : 1;
-    SP_LAUNCH(F_ATTN, launch_attention(qkv_, qkv_ld, attn_, H * hd, T, H, d_tok_slot_, d_tok_pos_, kv_, l, 1.0f / sqrtf((float)hd),
-                                       splits, att_scratch_, stream));
-    return SP_OK;
-}
-
-int Engine::layer_llama(const LayerW& w, int l, int T) {
-    const int H = d.n_heads, Hkv = d.n_kv_heads, hd = d.head_dim, hid = d.hidden, ffn = d.ffn;
-    const int qkv_ld = (H + 2 * Hkv) * hd;
-    SP_LAUNCH(F_NORM, launch_rms_norm(x_, w.n1w, T, hid, d.norm_eps, h_, stream));
-    SP_TRY(gemv(h_, hid, T, hid, w.q, w.qb, qkv_, qkv_ld, w.k, w.kb, qkv_ + (size_t)H * hd, w.v, w.vb,
-                qkv_ + (size_t)(H + Hkv) * hd));
-    SP_LAUNCH(F_ROPE, launch_rope_kv_append(qkv_, T, H, Hkv, hd, d.rotary_dim, cos_sin_, d_tok_slot_, d_tok_pos_, kv_, l, stream));
-    SP_TRY(attention(l, T));
-    SP_TRY(gemv(attn_, H * hd, T, H * hd, w.o, w.ob, x_, hid, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, x_));
-    SP_LAUNCH(F_NORM, launch_rms_norm(x_, w.n2w, T, hid, d.norm_eps, h_, stream));
-    SP_TRY(gemv(h_, hid, T, hid, w.gate, nullptr, gu_, 2 * ffn, w.up, nullptr, gu_ + ffn));
-    SP_LAUNCH(F_ELEM, launch_swiglu(gu_, 2 * ffn, ffn, T, mid_, stream));
-    SP_TRY(gemv(mid_, ffn, T, ffn, w.down, nullptr, x_, hid, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, x_));
-    return SP_OK;
-}
-
-int Engine::layer_phi(const LayerW& w, int l, int T) {
-    const int H = d.n_heads, Hkv = d.n_kv_heads, hd = d.head_dim, hid = d.hidden, ffn = d.ffn;
-    const int qkv_ld = (H + 2 * Hkv) * hd;
-    SP_LAUNCH(F_NORM, launch_layer_norm(x_, w.n1w, w.n1b, T, hid, d.norm_eps, h_, stream));
-    SP_TRY(gemv(h_, hid, T, hid, w.q, w.qb, qkv_, qkv_ld, w.k, w.kb, qkv_ + (size_t)H * hd, w.v, w.vb,
-                qkv_ + (size_t)(H + Hkv) * hd));
-    SP_LAUNCH(F_ROPE, launch_rope_kv_append(qkv_, T, H, Hkv, hd, d.rotary_dim, cos_sin_, d_tok_slot_, d_tok_pos_, kv_, l, stream));
-    SP_TRY(attention(l, T));
-    // parallel block: x + (attn_out + mlp(h)); both branches read the same normalised input h
-    SP_TRY(gemv(h_, hid, T, hid, w.up, w.upb, mid_, ffn));
-    SP_LAUNCH(F_ELEM, launch_gelu(mid_, (int64_t)T * ffn, stream));
-    SP_TRY(gemv(attn_, H * hd, T, H * hd, w.o, w.ob, x_, hid, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, x_));
-    SP_TRY(gemv(mid_, ffn, T, ffn, w.down, w.downb, x_, hid, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, x_));
-    return SP_OK;
-}
-
 int Engine::enqueue_layers(int T) {
     const int hid = d.hidden;
     SP_LAUNCH(F_EMBED, launch_embed(embed_->dtype, embed_->d, hid, d_ids_, T, x_, stream));
@@ -165,13 +76,14 @@ int Engine::enqueue_layers(int T) {
 }
 
 // lm_head over rows [r0, r0+rc) of the normalised selection sel_, plus their argmax.
-int Engine::enqueue_head(int rows_from, int r0, int rc) {
+int Engine::enqueue_head(int rows_from, int r0, int rc, const ImmaArgs* pre) {
     (void)rows_from;
     const int V = d.vocab, hid = d.hidden;
     // lm_head rows beyond the vocabulary (if the table is larger) are not computed: n = V
     DevTensor head = *lm_head_;
     head.dims[0] = V;
-    SP_TRY(gemv(sel_ + (size_t)r0 * hid, hid, rc, hid, &head, lm_bias_, logits_, V));
+    SP_TRY(gemv(sel_ + (size_t)r0 * hid, hid, rc, hid, &head, lm_bias_, logits_, V, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr,
+                nullptr, pre));
     SP_LAUNCH(F_ARGMAX, launch_argmax(logits_, rc, V, V, d_argmax_, stream));
     return SP_OK;
 }
@@ -179,6 +91,11 @@ int Engine::enqueue_head(int rows_from, int r0, int rc) {
 int Engine::enqueue_decode_step(int T) {
     const int hid = d.hidden;
     SP_TRY(enqueue_layers(T));
+    ImmaArgs ia;
+    if (lm_head_->tiled && plan_digits(T, hid, ia)) {
+        SP_LAUNCH(F_NORM, launch_norm_quant(x_, hid, final_w_, final_b_, d.arch == 1, d.norm_eps, nullptr, 0, ia, stream));
+        return enqueue_head(0, 0, T, &ia);
+    }
     if (d.arch == 1) SP_LAUNCH(F_NORM, launch_layer_norm(x_, final_w_, final_b_, T, hid, d.norm_eps, sel_, stream));
     else SP_LAUNCH(F_NORM, launch_rms_norm(x_, final_w_, T, hid, d.norm_eps, sel_, stream));
     return enqueue_head(0, 0, T);

@@ -1,0 +1,179 @@
+// Per-layer launch sequences of the resident engine.
+//   Llama/Qwen: crates/sapient-models/src/forward/llama.rs:400-539
+//   Phi-2     : crates/sapient-models/src/forward/phi.rs:373-503
+//
+// Decode-shaped steps (T <= 16 rows) run fused: every kernel that produces a GEMV input (norm,
+// SwiGLU / GELU, the split-K attention merge) emits the int8 digits the tensor-core GEMV consumes,
+// so a layer is 10 launches: norm+digits, qkv, rope+kv, attention split, merge+digits, o,
+// norm+digits, gate|up, swiglu+digits, down.
+#include <algorithm>
+
+#include "engine.h"
+#include "sp_common.cuh"
+
+namespace sp {
+
+#define SP_TRY(expr)                  \
+    do {                              \
+        int _s = (expr);              \
+        if (_s != SP_OK) return _s;   \
+    } while (0)
+
+#define SP_LAUNCH(fam, expr)              \
+    do {                                  \
+        if (fam_mask & (1u << (fam))) {   \
+            prof_begin(fam);              \
+            SP_CUDA_TRY(expr);            \
+            prof_end(fam);                \
+        }                                 \
+    } while (0)
+
+// Plans the digit workspace for m rows of k columns; true when the fused producers may be used
+// (all rows fit the workspace at once).
+bool Engine::plan_digits(int m, int k, ImmaArgs& ia) {
+    ia = ImmaArgs{};
+    ia.m = m;
+    ia.k = k;
+    if (m > 16 || k > ws_.k_max) return false;
+    imma_plan(ia, ws_);
+    return true;
+}
+
+// y_i[m, n_i] = x[m, k] · W_iᵀ (+ bias_i) for up to three matrices sharing x; `res` is added to the first.
+// pre != null: the digits of x are already in the workspace (planned as *pre).
+int Engine::gemv(const float* x, int ldx, int m, int k, const DevTensor* w0, const float* b0, float* y0, int ldy0,
+                 const DevTensor* w1, const float* b1, float* y1, const DevTensor* w2, const float* b2, float* y2,
+                 const float* res, const ImmaArgs* pre) {
+    const DevTensor* ws[3] = {w0, w1, w2};
+    const float* bs[3] = {b0, b1, b2};
+    float* ys[3] = {y0, y1, y2};
+    bool tiled = true;
+    for (int i = 0; i < 3 && ws[i]; ++i) tiled = tiled && ws[i]->tiled != nullptr;
+    if (tiled) {
+        // tensor-core path: digits of up to 16 activation rows at a time, all segments share them
+        for (int m0 = 0; m0 < m; m0 += 16) {
+            ImmaArgs ia{};
+            if (pre) ia = *pre;
+            ia.k = k; ia.m = std::min(16, m - m0);
+            ia.res = res ? res + (size_t)m0 * ldy0 : nullptr;
+            ia.ldres = ldy0;
+            ia.nseg = 0;
+            for (int i = 0; i < 3 && ws[i]; ++i) {
+                ImmaSeg& sgm = ia.seg[i];
+                sgm.wt = ws[i]->tiled; sgm.bias = bs[i]; sgm.y = ys[i] + (size_t)m0 * ldy0; sgm.dtype = ws[i]->dtype;
+                sgm.n = (int)ws[i]->dims[0]; sgm.ldy = ldy0; sgm.bpt = imma_q8_bpt(k);
+                ia.nseg++;
+            }
+            if (!pre) {
+                imma_plan(ia, ws_);
+                SP_LAUNCH(F_ELEM, launch_act_quant(x + (size_t)m0 * ldx, ldx, ia, stream));
+            }
+            SP_LAUNCH(F_GEMV, launch_gemv_imma(ia, stream));
+        }
+        return SP_OK;
+    }
+    if (pre) { set_error("internal: pre-quantised input for a weight without tiles"); return SP_ERR_STATE; }
+    if (w1 && (w0->tiled || w1->tiled || (w2 && w2->tiled))) {
+        // mixed layouts: one launch per matrix
+        SP_TRY(gemv(x, ldx, m, k, w0, b0, y0, ldy0, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, res));
+        SP_TRY(gemv(x, ldx, m, k, w1, b1, y1, ldy0));
+        if (w2) SP_TRY(gemv(x, ldx, m, k, w2, b2, y2, ldy0));
+        return SP_OK;
+    }
+    GemvArgs a{};
+    a.x = x; a.ldx = ldx; a.m = m; a.k = k; a.res = res; a.ldres = ldy0;
+    a.nseg = 0;
+    for (int i = 0; i < 3; ++i) {
+        if (!ws[i]) break;
+        a.seg[i].w = ws[i]->d; a.seg[i].bias = bs[i]; a.seg[i].y = ys[i]; a.seg[i].dtype = ws[i]->dtype;
+        a.seg[i].n = (int)ws[i]->dims[0]; a.seg[i].ldy = ldy0;
+        a.nseg++;
+    }
+    SP_LAUNCH(F_GEMV, launch_gemv(a, stream));
+    return SP_OK;
+}
+
+static inline bool all_tiled(const DevTensor* a, const DevTensor* b = nullptr, const DevTensor* c = nullptr) {
+    return a->tiled && (!b || b->tiled) && (!c || c->tiled);
+}
+
+// Attention of the T staged tokens, then the output projection added into x_ (x += W_o attn (+ b_o)).
+int Engine::attention_and_oproj(const LayerW& w, int l, int T) {
+    const int H = d.n_heads, Hkv = d.n_kv_heads, hd = d.head_dim, hid = d.hidden;
+    const int qkv_ld = (H + 2 * Hkv) * hd;
+    const float scale = 1.0f / sqrtf((float)hd);
+    const int splits = T <= ATT_SPLIT_TOKENS ? ATT_SPLITS : 1;
+    ImmaArgs ia;
+    if (splits > 1 && !trace_on && all_tiled(w.o) && plan_digits(T, H * hd, ia)) {
+        SP_LAUNCH(F_ATTN, launch_attention_split(qkv_, qkv_ld, T, H, d_tok_slot_, d_tok_pos_, kv_, l, scale, splits, att_scratch_, stream));
+        SP_LAUNCH(F_ATTN, launch_attn_merge_quant(att_scratch_, H, splits, hd, nullptr, 0, ia, stream));
+        return gemv(attn_, H * hd, T, H * hd, w.o, w.ob, x_, hid, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, x_, &ia);
+    }
+    SP_LAUNCH(F_ATTN, launch_attention(qkv_, qkv_ld, attn_, H * hd, T, H, d_tok_slot_, d_tok_pos_, kv_, l, scale, splits, att_scratch_,
+                                       stream));
+    return gemv(attn_, H * hd, T, H * hd, w.o, w.ob, x_, hid, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, x_);
+}
+
+int Engine::layer_llama(const LayerW& w, int l, int T) {
+    const int H = d.n_heads, Hkv = d.n_kv_heads, hd = d.head_dim, hid = d.hidden, ffn = d.ffn;
+    const int qkv_ld = (H + 2 * Hkv) * hd;
+    ImmaArgs ia;
+    if (all_tiled(w.q, w.k, w.v) && plan_digits(T, hid, ia)) {
+        SP_LAUNCH(F_NORM, launch_norm_quant(x_, hid, w.n1w, nullptr, false, d.norm_eps, nullptr, 0, ia, stream));
+        SP_TRY(gemv(h_, hid, T, hid, w.q, w.qb, qkv_, qkv_ld, w.k, w.kb, qkv_ + (size_t)H * hd, w.v, w.vb,
+                    qkv_ + (size_t)(H + Hkv) * hd, nullptr, &ia));
+    } else {
+        SP_LAUNCH(F_NORM, launch_rms_norm(x_, w.n1w, T, hid, d.norm_eps, h_, stream));
+        SP_TRY(gemv(h_, hid, T, hid, w.q, w.qb, qkv_, qkv_ld, w.k, w.kb, qkv_ + (size_t)H * hd, w.v, w.vb,
+                    qkv_ + (size_t)(H + Hkv) * hd));
+    }
+    SP_LAUNCH(F_ROPE, launch_rope_kv_append(qkv_, T, H, Hkv, hd, d.rotary_dim, cos_sin_, d_tok_slot_, d_tok_pos_, kv_, l, stream));
+    SP_TRY(attention_and_oproj(w, l, T));
+    if (all_tiled(w.gate, w.up) && plan_digits(T, hid, ia)) {
+        SP_LAUNCH(F_NORM, launch_norm_quant(x_, hid, w.n2w, nullptr, false, d.norm_eps, nullptr, 0, ia, stream));
+        SP_TRY(gemv(h_, hid, T, hid, w.gate, nullptr, gu_, 2 * ffn, w.up, nullptr, gu_ + ffn, nullptr, nullptr, nullptr, nullptr, &ia));
+    } else {
+        SP_LAUNCH(F_NORM, launch_rms_norm(x_, w.n2w, T, hid, d.norm_eps, h_, stream));
+        SP_TRY(gemv(h_, hid, T, hid, w.gate, nullptr, gu_, 2 * ffn, w.up, nullptr, gu_ + ffn));
+    }
+    if (all_tiled(w.down) && plan_digits(T, ffn, ia)) {
+        SP_LAUNCH(F_ELEM, launch_act_fn_quant(gu_, 2 * ffn, ffn, 0, ia, stream));
+        SP_TRY(gemv(mid_, ffn, T, ffn, w.down, nullptr, x_, hid, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, x_, &ia));
+    } else {
+        SP_LAUNCH(F_ELEM, launch_swiglu(gu_, 2 * ffn, ffn, T, mid_, stream));
+        SP_TRY(gemv(mid_, ffn, T, ffn, w.down, nullptr, x_, hid, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, x_));
+    }
+    return SP_OK;
+}
+
+int Engine::layer_phi(const LayerW& w, int l, int T) {
+    const int H = d.n_heads, Hkv = d.n_kv_heads, hd = d.head_dim, hid = d.hidden, ffn = d.ffn;
+    const int qkv_ld = (H + 2 * Hkv) * hd;
+    // parallel block: x + (attn_out + mlp(h)); both branches read the same normalised input h
+    ImmaArgs ia;
+    if (all_tiled(w.q, w.k, w.v) && all_tiled(w.up) && plan_digits(T, hid, ia)) {
+        SP_LAUNCH(F_NORM, launch_norm_quant(x_, hid, w.n1w, w.n1b, true, d.norm_eps, nullptr, 0, ia, stream));
+        SP_TRY(gemv(h_, hid, T, hid, w.q, w.qb, qkv_, qkv_ld, w.k, w.kb, qkv_ + (size_t)H * hd, w.v, w.vb,
+                    qkv_ + (size_t)(H + Hkv) * hd, nullptr, &ia));
+        SP_TRY(gemv(h_, hid, T, hid, w.up, w.upb, gu_, ffn, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, &ia));
+    } else {
+        SP_LAUNCH(F_NORM, launch_layer_norm(x_, w.n1w, w.n1b, T, hid, d.norm_eps, h_, stream));
+        SP_TRY(gemv(h_, hid, T, hid, w.q, w.qb, qkv_, qkv_ld, w.k, w.kb, qkv_ + (size_t)H * hd, w.v, w.vb,
+                    qkv_ + (size_t)(H + Hkv) * hd));
+        SP_TRY(gemv(h_, hid, T, hid, w.up, w.upb, gu_, ffn));
+    }
+    SP_LAUNCH(F_ROPE, launch_rope_kv_append(qkv_, T, H, Hkv, hd, d.rotary_dim, cos_sin_, d_tok_slot_, d_tok_pos_, kv_, l, stream));
+    // the MLP's fc1 output waits in gu_ while the workspace serves the attention output projection
+    SP_TRY(attention_and_oproj(w, l, T));
+    if (all_tiled(w.down) && plan_digits(T, ffn, ia)) {
+        SP_LAUNCH(F_ELEM, launch_act_fn_quant(gu_, ffn, ffn, 1, ia, stream));
+        SP_TRY(gemv(mid_, ffn, T, ffn, w.down, w.downb, x_, hid, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, x_, &ia));
+    } else {
+        SP_CUDA_TRY(cudaMemcpyAsync(mid_, gu_, (size_t)T * ffn * 4, cudaMemcpyDeviceToDevice, stream));
+        SP_LAUNCH(F_ELEM, launch_gelu(mid_, (int64_t)T * ffn, stream));
+        SP_TRY(gemv(mid_, ffn, T, ffn, w.down, w.downb, x_, hid, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, x_));
+    }
+    return SP_OK;
+}
+
+}  // namespace sp

@@ -141,33 +141,37 @@ cudaError_t launch_repack(int dtype, const uint8_t* raw, int64_t n, int64_t k, u
 }
 
 // ─────────────────────────── activation digits ───────────────────────────────
-// One warp per (256 columns, activation row); lane handles 8 consecutive columns.
-__global__ void __launch_bounds__(32) act_quant_kernel(const float* __restrict__ x, int ldx, int k, int kp, int digits, int eb,
-                                                       int ncp, int8_t* __restrict__ xq, float* __restrict__ colscale,
-                                                       int8_t* __restrict__ xs32d, int8_t* __restrict__ xs16d) {
-    const int lane = threadIdx.x, m = blockIdx.y, tile = blockIdx.x;
-    const int k0 = tile * 256 + lane * 8;
-    const bool live = k0 < k;
-    float v[8];
+// Where the digits of one GEMV input go (see gemv_imma.cuh for the layouts).
+struct QuantOut {
+    int k, kp, digits, eb, ncp;
+    int8_t* xq;
+    float* colscale;
+    int8_t* xs32d;
+    int8_t* xs16d;
+};
+__host__ inline QuantOut quant_out(const ImmaArgs& a) {
+    QuantOut q;
+    q.k = a.k; q.kp = a.kp; q.digits = a.digits; q.eb = a.eb; q.ncp = a.ncp;
+    q.xq = const_cast<int8_t*>(a.xq); q.colscale = const_cast<float*>(a.colscale);
+    q.xs32d = const_cast<int8_t*>(a.xs32d); q.xs16d = const_cast<int8_t*>(a.xs16d);
+    return q;
+}
+
+// One warp converts 256 columns (tile) of activation row m: lane holds the 8 consecutive columns
+// tile * 256 + lane * 8 .. +7 in v (zeros when !live). All 32 lanes must call.
+__device__ __forceinline__ void quantize_chunk(const float (&v)[8], bool live, int lane, int tile, int m, const QuantOut& qo) {
     float amax = 0.f;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) v[i] = 0.f;
-    if (live) {
-        const float4 a = *reinterpret_cast<const float4*>(x + (int64_t)m * ldx + k0);
-        const float4 b = *reinterpret_cast<const float4*>(x + (int64_t)m * ldx + k0 + 4);
-        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
-    }
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
     // exponent block: the 4 lanes of a 32-column block, or the whole warp
     amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
     amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));
-    if (eb == 256) {
+    if (qo.eb == 256) {
         amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 4));
         amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 8));
         amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 16));
     }
-    const int P = 8 * digits - 2;
+    const int digits = qo.digits, P = 8 * digits - 2;
     float up = 0.f, down = 0.f;  // x * up -> fixed point; digit 0 scale = down
     if (amax > 0.f && amax < INFINITY) {
         int e = ilogbf(amax) + 1;          // amax < 2^e
@@ -193,18 +197,18 @@ __global__ void __launch_bounds__(32) act_quant_kernel(const float* __restrict__
         else { w1[0] |= (uint32_t)(q0 & 255) << sh; w1[1] |= (uint32_t)(q1 & 255) << sh; w1[2] |= (uint32_t)(q2 & 255) << sh; }
     }
     const int a4 = lane & 3, blk = lane >> 2;       // 32-block of the tile
-    const int h = a4 >> 1, t0 = 2 * (a4 & 1);       // columns 16h + 4t + i of the block go to byte 8t' ... see gemv_imma.cuh
+    const int h = a4 >> 1, t0 = 2 * (a4 & 1);       // lane's columns are 16h + 4t0 .. and 16h + 4(t0+1) .. of the block
 #pragma unroll
     for (int d = 0; d < 3; ++d) {
         const int s16 = sum[d] + __shfl_xor_sync(0xFFFFFFFFu, sum[d], 1);
         const int s32 = s16 + __shfl_xor_sync(0xFFFFFFFFu, s16, 2);
         if (d < digits && live) {
             const int col = m * digits + d;
-            int8_t* dst = xq + (int64_t)col * kp + (int64_t)tile * 256 + blk * 8 + 4 * h;
+            int8_t* dst = qo.xq + (int64_t)col * qo.kp + (int64_t)tile * 256 + blk * 8 + 4 * h;
             *reinterpret_cast<uint32_t*>(dst + t0 * 64) = w0[d];
             *reinterpret_cast<uint32_t*>(dst + (t0 + 1) * 64) = w1[d];
-            int8_t* r32 = xs32d + ((int64_t)tile * ncp + col) * 32;
-            int8_t* r16 = xs16d + ((int64_t)tile * ncp + col) * 32;
+            int8_t* r32 = qo.xs32d + ((int64_t)tile * qo.ncp + col) * 32;
+            int8_t* r16 = qo.xs16d + ((int64_t)tile * qo.ncp + col) * 32;
             if ((lane & 1) == 0) {
                 const int a = ((s16 + 32) & 63) - 32;
                 r16[lane >> 1] = (int8_t)a;
@@ -217,14 +221,155 @@ __global__ void __launch_bounds__(32) act_quant_kernel(const float* __restrict__
             }
         }
     }
-    const bool writer = (eb == 256) ? (lane == 0) : (a4 == 0);
+    const bool writer = (qo.eb == 256) ? (lane == 0) : (a4 == 0);
     if (writer && live) {
+        const int k0 = tile * 256 + lane * 8;
         float s = down;
         for (int d = 0; d < digits; ++d) {
-            colscale[(int64_t)(k0 / eb) * ncp + m * digits + d] = s;
+            qo.colscale[(int64_t)(k0 / qo.eb) * qo.ncp + m * digits + d] = s;
             s *= 256.f;
         }
     }
+}
+
+__device__ __forceinline__ void load8(const float* p, float (&v)[8]) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void store8(float* p, const float (&v)[8]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+
+// Plain conversion: one warp per (256 columns, activation row).
+__global__ void __launch_bounds__(32) act_quant_kernel(const float* __restrict__ x, int ldx, QuantOut qo) {
+    const int lane = threadIdx.x, m = blockIdx.y, tile = blockIdx.x;
+    const int k0 = tile * 256 + lane * 8;
+    const bool live = k0 < qo.k;
+    float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (live) load8(x + (int64_t)m * ldx + k0, v);
+    quantize_chunk(v, live, lane, tile, m, qo);
+}
+
+// RMSNorm / LayerNorm of one activation row per block, emitting the digits of the normalised row (and, when
+// y != null, its f32 values). Arithmetic of the norm as in crates/sapient-backends/cpu/src/kernels/layernorm.rs:17-105.
+template <bool LAYER_NORM>
+__global__ void __launch_bounds__(256) norm_quant_kernel(const float* __restrict__ x, int ldx, const float* __restrict__ w,
+                                                         const float* __restrict__ b, float eps, float* __restrict__ y, int ldy,
+                                                         QuantOut qo) {
+    __shared__ float sh[8];
+    const int m = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const float* row = x + (int64_t)m * ldx;
+    const int k = qo.k, tiles = (k + 255) / 256;
+    auto block_sum = [&](float v) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+        __syncthreads();
+        if (lane == 0) sh[warp] = v;
+        __syncthreads();
+        float t = lane < 8 ? sh[lane] : 0.f;
+#pragma unroll
+        for (int o = 4; o > 0; o >>= 1) t += __shfl_xor_sync(0xFFFFFFFFu, t, o);
+        return __shfl_sync(0xFFFFFFFFu, t, 0);
+    };
+    float mean = 0.f;
+    if (LAYER_NORM) {
+        float s = 0.f;
+        for (int i = threadIdx.x * 4; i < k; i += 1024) {
+            const float4 a = *reinterpret_cast<const float4*>(row + i);
+            s += (a.x + a.y) + (a.z + a.w);
+        }
+        mean = block_sum(s) / (float)k;
+    }
+    float ss = 0.f;
+    for (int i = threadIdx.x * 4; i < k; i += 1024) {
+        const float4 a = *reinterpret_cast<const float4*>(row + i);
+        const float c0 = a.x - mean, c1 = a.y - mean, c2 = a.z - mean, c3 = a.w - mean;
+        ss = fmaf(c0, c0, ss); ss = fmaf(c1, c1, ss); ss = fmaf(c2, c2, ss); ss = fmaf(c3, c3, ss);
+    }
+    const float inv = 1.0f / sqrtf(block_sum(ss) / (float)k + eps);
+    for (int tile = warp; tile < tiles; tile += 8) {
+        const int k0 = tile * 256 + lane * 8;
+        const bool live = k0 < k;
+        float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        if (live) {
+            float xv[8], wv[8];
+            load8(row + k0, xv);
+            load8(w + k0, wv);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = __fmul_rn(__fmul_rn(xv[i] - mean, inv), wv[i]);
+            if (LAYER_NORM && b) {
+                float bv[8];
+                load8(b + k0, bv);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] = __fadd_rn(v[i], bv[i]);
+            }
+            if (y) store8(y + (int64_t)m * ldy + k0, v);
+        }
+        quantize_chunk(v, live, lane, tile, m, qo);
+    }
+}
+
+// SwiGLU (act == 0: silu(gate) * up from gu[m][0..ffn) and gu[m][ffn..2ffn)) or tanh-GELU (act == 1: of gu[m][0..ffn))
+// emitting the digits of the result; one warp per (256 columns, row). Formulas: kernels/elementwise.rs:120-143.
+__global__ void __launch_bounds__(32) act_fn_quant_kernel(const float* __restrict__ gu, int ld, int ffn, int act, QuantOut qo) {
+    const int lane = threadIdx.x, m = blockIdx.y, tile = blockIdx.x;
+    const int k0 = tile * 256 + lane * 8;
+    const bool live = k0 < ffn;
+    float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (live) {
+        float g[8];
+        load8(gu + (int64_t)m * ld + k0, g);
+        if (act == 0) {
+            float u[8];
+            load8(gu + (int64_t)m * ld + ffn + k0, u);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = __fmul_rn(g[i] / (1.0f + expf(-g[i])), u[i]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float t = g[i];
+                const float inner = __fmul_rn(0.79788456f, __fadd_rn(t, __fmul_rn(__fmul_rn(__fmul_rn(0.044715f, t), t), t)));
+                v[i] = __fmul_rn(__fmul_rn(0.5f, t), __fadd_rn(1.0f, tanhf(inner)));
+            }
+        }
+    }
+    quantize_chunk(v, live, lane, tile, m, qo);
+}
+
+// Merge of the split-K attention partials (see attention.cu) emitting the digits of the attention output row;
+// one warp per (256 columns of the [n_heads * hd] row, token). part: [tok][head][split][hd + 2].
+__global__ void __launch_bounds__(32) attn_merge_quant_kernel(const float* __restrict__ part, int n_heads, int n_splits, int hd,
+                                                              float* __restrict__ out, int ldo, QuantOut qo) {
+    const int lane = threadIdx.x, m = blockIdx.y, tile = blockIdx.x;
+    const int k0 = tile * 256 + lane * 8;
+    const bool live = k0 < qo.k;
+    float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (live) {
+        const int h = k0 / hd, e0 = k0 - h * hd;  // hd % 8 == 0: the 8 columns lie in one head
+        const float* src = part + ((int64_t)m * n_heads + h) * n_splits * (hd + 2);
+        float M = -INFINITY;
+        for (int s = 0; s < n_splits; ++s) M = fmaxf(M, src[(int64_t)s * (hd + 2)]);
+        float L = 0.f;
+        for (int s = 0; s < n_splits; ++s) {
+            const float ms = src[(int64_t)s * (hd + 2)];
+            if (ms != -INFINITY) {
+                const float c = expf(ms - M);
+                L = fmaf(c, src[(int64_t)s * (hd + 2) + 1], L);
+                const float* o = src + (int64_t)s * (hd + 2) + 2 + e0;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] = fmaf(c, o[i], v[i]);
+            }
+        }
+        const float inv = (L == 0.f) ? 0.f : 1.0f / L;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] *= inv;
+        if (out) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) out[(int64_t)m * ldo + k0 + i] = v[i];
+        }
+    }
+    quantize_chunk(v, live, lane, tile, m, qo);
 }
 
 void imma_plan(ImmaArgs& a, const ActWorkspace& ws) {
@@ -239,9 +384,28 @@ void imma_plan(ImmaArgs& a, const ActWorkspace& ws) {
 
 cudaError_t launch_act_quant(const float* x, int ldx, const ImmaArgs& a, cudaStream_t st) {
     if (a.m <= 0) return cudaSuccess;
-    act_quant_kernel<<<dim3(a.kp / 256, a.m), 32, 0, st>>>(x, ldx, a.k, a.kp, a.digits, a.eb, a.ncp, const_cast<int8_t*>(a.xq),
-                                                            const_cast<float*>(a.colscale), const_cast<int8_t*>(a.xs32d),
-                                                            const_cast<int8_t*>(a.xs16d));
+    act_quant_kernel<<<dim3(a.kp / 256, a.m), 32, 0, st>>>(x, ldx, quant_out(a));
+    return count_launch_and_check();
+}
+
+cudaError_t launch_norm_quant(const float* x, int ldx, const float* w, const float* b, bool layer_norm, float eps, float* y, int ldy,
+                              const ImmaArgs& a, cudaStream_t st) {
+    if (a.m <= 0) return cudaSuccess;
+    if (layer_norm) norm_quant_kernel<true><<<a.m, 256, 0, st>>>(x, ldx, w, b, eps, y, ldy, quant_out(a));
+    else norm_quant_kernel<false><<<a.m, 256, 0, st>>>(x, ldx, w, nullptr, eps, y, ldy, quant_out(a));
+    return count_launch_and_check();
+}
+
+cudaError_t launch_act_fn_quant(const float* gu, int ld, int ffn, int act, const ImmaArgs& a, cudaStream_t st) {
+    if (a.m <= 0) return cudaSuccess;
+    act_fn_quant_kernel<<<dim3(a.kp / 256, a.m), 32, 0, st>>>(gu, ld, ffn, act, quant_out(a));
+    return count_launch_and_check();
+}
+
+cudaError_t launch_attn_merge_quant(const float* part, int n_heads, int n_splits, int hd, float* out, int ldo, const ImmaArgs& a,
+                                    cudaStream_t st) {
+    if (a.m <= 0) return cudaSuccess;
+    attn_merge_quant_kernel<<<dim3(a.kp / 256, a.m), 32, 0, st>>>(part, n_heads, n_splits, hd, out, ldo, quant_out(a));
     return count_launch_and_check();
 }
 

@@ -54,6 +54,16 @@ struct ActWorkspace;
 void imma_plan(ImmaArgs& a, const ActWorkspace& ws);
 cudaError_t launch_act_quant(const float* x, int ldx, const ImmaArgs& a, cudaStream_t st);
 cudaError_t launch_gemv_imma(const ImmaArgs& a, cudaStream_t st);
+// Producers that emit the digits of a GEMV input directly (a: planned ImmaArgs; a.m rows, a.k columns):
+// RMSNorm / LayerNorm of x (y optional f32 copy), SwiGLU (act 0) / tanh-GELU (act 1) of gu, merged split-K attention.
+cudaError_t launch_norm_quant(const float* x, int ldx, const float* w, const float* b, bool layer_norm, float eps, float* y, int ldy,
+                              const ImmaArgs& a, cudaStream_t st);
+cudaError_t launch_act_fn_quant(const float* gu, int ld, int ffn, int act, const ImmaArgs& a, cudaStream_t st);
+cudaError_t launch_attn_merge_quant(const float* part, int n_heads, int n_splits, int hd, float* out, int ldo, const ImmaArgs& a,
+                                    cudaStream_t st);
+// The split phase of launch_attention alone (partials to scratch); n_splits > 1.
+cudaError_t launch_attention_split(const float* q, int ldq, int n_tok, int n_heads, const int32_t* tok_slot, const int32_t* tok_pos,
+                                   KvGeom kv, int layer, float scale, int n_splits, float* scratch, cudaStream_t st);
 
 // Workspace of the activation digits for up to 16 activation rows of k_max columns.
 struct ActWorkspace {
