@@ -13,12 +13,17 @@
 // (2 digits) of each block's maximum instead of f32.
 #include "gemv_imma.cuh"
 
+#include <atomic>
+
 #include "kernels.h"
 #include "sp_common.cuh"
 
 namespace sp {
 
 cudaError_t count_launch_and_check();  // kernels.cu
+
+// 0: pick per launch (streaming kernel when it qualifies); 2: always the per-tile-row kernel.
+static std::atomic<int> g_imma_kernel{0};
 
 // ───────────────────────────── weight repack ────────────────────────────────
 __device__ __forceinline__ uint32_t ld_word_2B(const uint8_t* p) {
@@ -450,19 +455,25 @@ __device__ __forceinline__ void imma_k16(int (&d)[4], uint32_t a0, uint32_t a1, 
 }
 
 __device__ __forceinline__ uint4 ldg_u4(const void* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
+__device__ __forceinline__ uint4 ld_u4(const void* p) { return *reinterpret_cast<const uint4*>(p); }
 __device__ __forceinline__ int byte_u(uint32_t w, int i) { return (int)((w >> (8 * i)) & 0xFFu); }
 __device__ __forceinline__ int byte_s(uint32_t w, int i) { return (int)(int8_t)((w >> (8 * i)) & 0xFFu); }
 
 constexpr int IMMA_WARPS = 8;
 
-// B fragments of one 256-column tile: for n-tile nt, words [2 * blk] and [2 * blk + 1] are the k 4t.. and k 16+4t..
-// digit words of 32-block blk for digit column nt * 8 + g. Columns past the live ones read zeros.
+// Everything of the activation side that one lane needs for one 256-column tile and n-tile:
+// w[2 * blk], w[2 * blk + 1] = the k 4t.. and k 16+4t.. digit words of 32-block blk for digit column nt * 8 + g;
+// ra / rb = word t of the a / b halves of the digit-sum record (xs32d or xs16d); cs = scales of columns 2t, 2t+1.
 template <int NT>
 struct BFrag {
     uint32_t w[NT][16];
+    uint32_t ra32[NT], rb32[NT], ra16[NT], rb16[NT];
+    float2 cs[NT];
 };
+
+// From global memory (digits laid out as in gemv_imma.cuh). Columns past the live ones read zeros.
 template <int NT>
-__device__ __forceinline__ void load_b256(const ImmaArgs& a, int kt, int g, int t, BFrag<NT>& b) {
+__device__ __forceinline__ void load_b_global(const ImmaArgs& a, int kt, int g, int t, bool q4, bool q6, BFrag<NT>& b) {
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
         const int col = nt * 8 + g;
@@ -477,6 +488,12 @@ __device__ __forceinline__ void load_b256(const ImmaArgs& a, int kt, int g, int 
 #pragma unroll
             for (int i = 0; i < 16; ++i) b.w[nt][i] = 0u;
         }
+        const int64_t rec = ((int64_t)kt * a.ncp + col) * 32 + 4 * t;
+        b.ra32[nt] = q4 ? __ldg(reinterpret_cast<const uint32_t*>(a.xs32d + rec)) : 0u;
+        b.rb32[nt] = q4 ? __ldg(reinterpret_cast<const uint32_t*>(a.xs32d + rec + 16)) : 0u;
+        b.ra16[nt] = q6 ? __ldg(reinterpret_cast<const uint32_t*>(a.xs16d + rec)) : 0u;
+        b.rb16[nt] = q6 ? __ldg(reinterpret_cast<const uint32_t*>(a.xs16d + rec + 16)) : 0u;
+        b.cs[nt] = __ldg(reinterpret_cast<const float2*>(a.colscale + (int64_t)kt * a.ncp + nt * 8 + 2 * t));
     }
 }
 
@@ -485,19 +502,18 @@ struct Q4Regs {
     uint4 q[4];
     uint4 h0, h1;
 };
+template <bool GLOBAL>
 __device__ __forceinline__ void load_q4_k(const uint8_t* tile, int lane, Q4Regs& r) {
     const int g = lane >> 2;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) r.q[j] = ldg_u4(tile + j * 512 + lane * 16);
-    r.h0 = ldg_u4(tile + 2048 + g * 16);
-    r.h1 = ldg_u4(tile + 2048 + (g + 8) * 16);
+    for (int j = 0; j < 4; ++j) r.q[j] = GLOBAL ? ldg_u4(tile + j * 512 + lane * 16) : ld_u4(tile + j * 512 + lane * 16);
+    r.h0 = GLOBAL ? ldg_u4(tile + 2048 + g * 16) : ld_u4(tile + 2048 + g * 16);
+    r.h1 = GLOBAL ? ldg_u4(tile + 2048 + (g + 8) * 16) : ld_u4(tile + 2048 + (g + 8) * 16);
 }
 
 template <int NT>
-__device__ __forceinline__ void compute_q4_k(const ImmaArgs& a, const Q4Regs& r, int kt, int lane, float (&acc)[NT][4]) {
-    const int g = lane >> 2, t = lane & 3;
-    BFrag<NT> b;
-    load_b256<NT>(a, kt, g, t, b);
+__device__ __forceinline__ void compute_q4_k(const Q4Regs& r, const BFrag<NT>& b, int lane, float (&acc)[NT][4]) {
+    const int t = lane & 3;
     // 6-bit scales / mins of rows g and g+8 unpacked to one byte each (sub-blocks 0..3 | 4..7)
     uint32_t sc[2][2], mn[2][2];
     {
@@ -537,12 +553,10 @@ __device__ __forceinline__ void compute_q4_k(const ImmaArgs& a, const Q4Regs& r,
     const float d1 = half_bits_to_float((uint16_t)(r.h1.x & 0xFFFFu)), dm1 = half_bits_to_float((uint16_t)(r.h1.x >> 16));
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
-        const int8_t* rec = a.xs32d + ((int64_t)kt * a.ncp + nt * 8 + g) * 32 + 4 * t;
-        const uint32_t ba = __ldg(reinterpret_cast<const uint32_t*>(rec)), bb = __ldg(reinterpret_cast<const uint32_t*>(rec + 16));
         int ca[4], cb[4];
-        imma_k16(ca, am0, am1, ba, 0, 0, 0, 0);
-        imma_k16(cb, am0, am1, bb, 0, 0, 0, 0);
-        const float2 cs = __ldg(reinterpret_cast<const float2*>(a.colscale + (int64_t)kt * a.ncp + nt * 8 + 2 * t));
+        imma_k16(ca, am0, am1, b.ra32[nt], 0, 0, 0, 0);
+        imma_k16(cb, am0, am1, b.rb32[nt], 0, 0, 0, 0);
+        const float2 cs = b.cs[nt];
         acc[nt][0] = fmaf(cs.x, d0 * (float)D[nt][0] - dm0 * (float)(ca[0] + 64 * cb[0]), acc[nt][0]);
         acc[nt][1] = fmaf(cs.y, d0 * (float)D[nt][1] - dm0 * (float)(ca[1] + 64 * cb[1]), acc[nt][1]);
         acc[nt][2] = fmaf(cs.x, d1 * (float)D[nt][2] - dm1 * (float)(ca[2] + 64 * cb[2]), acc[nt][2]);
@@ -556,24 +570,23 @@ struct Q6Regs {
     uint4 s0, s1;
     uint32_t dd;  // d of row g | d of row g+8 << 16
 };
+template <bool GLOBAL>
 __device__ __forceinline__ void load_q6_k(const uint8_t* tile, int lane, Q6Regs& r) {
     const int g = lane >> 2;
 #pragma unroll
     for (int i = 0; i < 6; ++i) {
-        const uint4 v = ldg_u4(tile + i * 512 + lane * 16);
+        const uint4 v = GLOBAL ? ldg_u4(tile + i * 512 + lane * 16) : ld_u4(tile + i * 512 + lane * 16);
         r.w[4 * i] = v.x; r.w[4 * i + 1] = v.y; r.w[4 * i + 2] = v.z; r.w[4 * i + 3] = v.w;
     }
-    r.s0 = ldg_u4(tile + 3072 + g * 16);
-    r.s1 = ldg_u4(tile + 3072 + (g + 8) * 16);
-    r.dd = (uint32_t)__ldg(reinterpret_cast<const uint16_t*>(tile + 3328 + 2 * g)) |
-           ((uint32_t)__ldg(reinterpret_cast<const uint16_t*>(tile + 3328 + 2 * (g + 8))) << 16);
+    r.s0 = GLOBAL ? ldg_u4(tile + 3072 + g * 16) : ld_u4(tile + 3072 + g * 16);
+    r.s1 = GLOBAL ? ldg_u4(tile + 3072 + (g + 8) * 16) : ld_u4(tile + 3072 + (g + 8) * 16);
+    const uint16_t* dp = reinterpret_cast<const uint16_t*>(tile + 3328);
+    r.dd = GLOBAL ? ((uint32_t)__ldg(dp + g) | ((uint32_t)__ldg(dp + g + 8) << 16)) : ((uint32_t)dp[g] | ((uint32_t)dp[g + 8] << 16));
 }
 
 template <int NT>
-__device__ __forceinline__ void compute_q6_k(const ImmaArgs& a, const Q6Regs& r, int kt, int lane, float (&acc)[NT][4]) {
-    const int g = lane >> 2, t = lane & 3;
-    BFrag<NT> b;
-    load_b256<NT>(a, kt, g, t, b);
+__device__ __forceinline__ void compute_q6_k(const Q6Regs& r, const BFrag<NT>& b, int lane, float (&acc)[NT][4]) {
+    const int t = lane & 3;
     const uint32_t sw0[4] = {r.s0.x, r.s0.y, r.s0.z, r.s0.w}, sw1[4] = {r.s1.x, r.s1.y, r.s1.z, r.s1.w};
     int D[NT][4];
 #pragma unroll
@@ -611,12 +624,10 @@ __device__ __forceinline__ void compute_q6_k(const ImmaArgs& a, const Q6Regs& r,
     const uint32_t az1 = t == 0 ? r.s1.x : t == 1 ? r.s1.y : t == 2 ? r.s1.z : r.s1.w;  // ... of row g+8
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
-        const int8_t* rec = a.xs16d + ((int64_t)kt * a.ncp + nt * 8 + g) * 32 + 4 * t;
-        const uint32_t ba = __ldg(reinterpret_cast<const uint32_t*>(rec)), bb = __ldg(reinterpret_cast<const uint32_t*>(rec + 16));
         int ca[4], cb[4];
-        imma_k16(ca, az0, az1, ba, 0, 0, 0, 0);
-        imma_k16(cb, az0, az1, bb, 0, 0, 0, 0);
-        const float2 cs = __ldg(reinterpret_cast<const float2*>(a.colscale + (int64_t)kt * a.ncp + nt * 8 + 2 * t));
+        imma_k16(ca, az0, az1, b.ra16[nt], 0, 0, 0, 0);
+        imma_k16(cb, az0, az1, b.rb16[nt], 0, 0, 0, 0);
+        const float2 cs = b.cs[nt];
         acc[nt][0] = fmaf(cs.x * d0, (float)(D[nt][0] - 32 * (ca[0] + 64 * cb[0])), acc[nt][0]);
         acc[nt][1] = fmaf(cs.y * d0, (float)(D[nt][1] - 32 * (ca[1] + 64 * cb[1])), acc[nt][1]);
         acc[nt][2] = fmaf(cs.x * d1, (float)(D[nt][2] - 32 * (ca[2] + 64 * cb[2])), acc[nt][2]);
@@ -624,7 +635,47 @@ __device__ __forceinline__ void compute_q6_k(const ImmaArgs& a, const Q6Regs& r,
     }
 }
 
-// ── Q8_0: one tile = bpt 32-blocks; kt counts tiles ──
+// ── Q8_0, 8 blocks per tile, operands as for the K-quants (used by the streaming kernel) ──
+struct Q8Regs {
+    uint4 q[8];
+    uint4 d0, d1;  // 8 f16 scales of row g / row g+8
+};
+template <bool GLOBAL>
+__device__ __forceinline__ void load_q8_0(const uint8_t* tile, int lane, Q8Regs& r) {
+    const int g = lane >> 2;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) r.q[j] = GLOBAL ? ldg_u4(tile + j * 512 + lane * 16) : ld_u4(tile + j * 512 + lane * 16);
+    r.d0 = GLOBAL ? ldg_u4(tile + 4096 + g * 16) : ld_u4(tile + 4096 + g * 16);
+    r.d1 = GLOBAL ? ldg_u4(tile + 4096 + (g + 8) * 16) : ld_u4(tile + 4096 + (g + 8) * 16);
+}
+template <int NT>
+__device__ __forceinline__ void compute_q8_0(const Q8Regs& r, const BFrag<NT>& b, float (&acc)[NT][4]) {
+    const uint32_t dw0[4] = {r.d0.x, r.d0.y, r.d0.z, r.d0.w}, dw1[4] = {r.d1.x, r.d1.y, r.d1.z, r.d1.w};
+    float f[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) f[nt][e] = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const float d0 = half_bits_to_float((uint16_t)((dw0[j >> 1] >> (16 * (j & 1))) & 0xFFFFu));
+        const float d1 = half_bits_to_float((uint16_t)((dw1[j >> 1] >> (16 * (j & 1))) & 0xFFFFu));
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            int c[4];
+            imma_k32(c, r.q[j].x, r.q[j].z, r.q[j].y, r.q[j].w, b.w[nt][2 * j], b.w[nt][2 * j + 1], 0, 0, 0, 0);
+            f[nt][0] = fmaf(d0, (float)c[0], f[nt][0]); f[nt][1] = fmaf(d0, (float)c[1], f[nt][1]);
+            f[nt][2] = fmaf(d1, (float)c[2], f[nt][2]); f[nt][3] = fmaf(d1, (float)c[3], f[nt][3]);
+        }
+    }
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+        acc[nt][0] = fmaf(b.cs[nt].x, f[nt][0], acc[nt][0]); acc[nt][1] = fmaf(b.cs[nt].y, f[nt][1], acc[nt][1]);
+        acc[nt][2] = fmaf(b.cs[nt].x, f[nt][2], acc[nt][2]); acc[nt][3] = fmaf(b.cs[nt].y, f[nt][3], acc[nt][3]);
+    }
+}
+
+// ── Q8_0 with any number of blocks per tile (K not a multiple of 256) ──
 template <int NT>
 __device__ __forceinline__ void tile_q8_0(const ImmaArgs& a, const uint8_t* tile, int kt, int bpt, int lane, float (&acc)[NT][4]) {
     const int g = lane >> 2, t = lane & 3;
@@ -650,12 +701,31 @@ __device__ __forceinline__ void tile_q8_0(const ImmaArgs& a, const uint8_t* tile
     }
 }
 
-// One CTA per tile row (16 weight rows); its warps split the k-tiles and prefetch the next tile's
-// weight registers before computing the current one.
+// Writes y for the 16 rows of tile row rt from the per-warp partial sums in red[warp][nt][e][lane].
+template <int NT, int WARPS>
+__device__ __forceinline__ void reduce_store(const ImmaArgs& a, const ImmaSeg& sg, bool first_seg, int rt, const float* red) {
+    for (int idx = threadIdx.x; idx < 16 * a.m; idx += blockDim.x) {
+        const int r = idx & 15, m = idx >> 4;
+        const int64_t row = (int64_t)rt * 16 + r;
+        if (row >= sg.n) continue;
+        float v = 0.f;
+        for (int d = 0; d < a.digits; ++d) {
+            const int col = m * a.digits + d, nt = col >> 3, cc = col & 7;
+            const int e = (r < 8 ? 0 : 2) + (cc & 1), ln = (r & 7) * 4 + (cc >> 1);
+#pragma unroll
+            for (int w = 0; w < WARPS; ++w) v += red[((w * NT + nt) * 4 + e) * 32 + ln];
+        }
+        if (sg.bias) v += sg.bias[row];
+        if (first_seg && a.res) v += a.res[(int64_t)m * a.ldres + row];
+        sg.y[(int64_t)m * sg.ldy + row] = v;
+    }
+}
+
+// Kernel A (any shape): one CTA per tile row; its 8 warps split the k-tiles, operands straight from global memory.
 template <int NT>
 __global__ void __launch_bounds__(IMMA_WARPS * 32, (NT <= 2 ? 2 : 1)) gemv_imma_kernel(const ImmaArgs a) {
-    __shared__ float red[IMMA_WARPS][NT][4][32];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    __shared__ float red[IMMA_WARPS * NT * 4 * 32];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     int rt = blockIdx.x, s = 0;
     while (s < a.nseg - 1 && rt >= (a.seg[s].n + 15) / 16) { rt -= (a.seg[s].n + 15) / 16; ++s; }
     const ImmaSeg& sg = a.seg[s];
@@ -668,31 +738,29 @@ __global__ void __launch_bounds__(IMMA_WARPS * 32, (NT <= 2 ? 2 : 1)) gemv_imma_
         const int kts = a.k >> 8;
         const uint8_t* base = sg.wt + (int64_t)rt * kts * Q4_K_TILE_BYTES;
         Q4Regs ra, rb;
+        BFrag<NT> b;
         int kt = warp;
-        if (kt < kts) load_q4_k(base + (int64_t)kt * Q4_K_TILE_BYTES, lane, ra);
+        if (kt < kts) load_q4_k<true>(base + (int64_t)kt * Q4_K_TILE_BYTES, lane, ra);
         while (kt < kts) {
             const int k1 = kt + IMMA_WARPS, k2 = kt + 2 * IMMA_WARPS;
-            if (k1 < kts) load_q4_k(base + (int64_t)k1 * Q4_K_TILE_BYTES, lane, rb);
-            compute_q4_k<NT>(a, ra, kt, lane, acc);
+            if (k1 < kts) load_q4_k<true>(base + (int64_t)k1 * Q4_K_TILE_BYTES, lane, rb);
+            load_b_global<NT>(a, kt, g, t, true, false, b);
+            compute_q4_k<NT>(ra, b, lane, acc);
             if (k1 >= kts) break;
-            if (k2 < kts) load_q4_k(base + (int64_t)k2 * Q4_K_TILE_BYTES, lane, ra);
-            compute_q4_k<NT>(a, rb, k1, lane, acc);
+            if (k2 < kts) load_q4_k<true>(base + (int64_t)k2 * Q4_K_TILE_BYTES, lane, ra);
+            load_b_global<NT>(a, k1, g, t, true, false, b);
+            compute_q4_k<NT>(rb, b, lane, acc);
             kt = k2;
         }
     } else if (sg.dtype == T_Q6_K) {
         const int kts = a.k >> 8;
         const uint8_t* base = sg.wt + (int64_t)rt * kts * Q6_K_TILE_BYTES;
-        Q6Regs ra, rb;
-        int kt = warp;
-        if (kt < kts) load_q6_k(base + (int64_t)kt * Q6_K_TILE_BYTES, lane, ra);
-        while (kt < kts) {
-            const int k1 = kt + IMMA_WARPS, k2 = kt + 2 * IMMA_WARPS;
-            if (k1 < kts) load_q6_k(base + (int64_t)k1 * Q6_K_TILE_BYTES, lane, rb);
-            compute_q6_k<NT>(a, ra, kt, lane, acc);
-            if (k1 >= kts) break;
-            if (k2 < kts) load_q6_k(base + (int64_t)k2 * Q6_K_TILE_BYTES, lane, ra);
-            compute_q6_k<NT>(a, rb, k1, lane, acc);
-            kt = k2;
+        Q6Regs ra;
+        BFrag<NT> b;
+        for (int kt = warp; kt < kts; kt += IMMA_WARPS) {
+            load_q6_k<true>(base + (int64_t)kt * Q6_K_TILE_BYTES, lane, ra);
+            load_b_global<NT>(a, kt, g, t, false, true, b);
+            compute_q6_k<NT>(ra, b, lane, acc);
         }
     } else {
         const int bpt = sg.bpt, kts = (a.k >> 5) / bpt, tb = bpt * 544;
@@ -702,24 +770,193 @@ __global__ void __launch_bounds__(IMMA_WARPS * 32, (NT <= 2 ? 2 : 1)) gemv_imma_
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) red[warp][nt][e][lane] = acc[nt][e];
+        for (int e = 0; e < 4; ++e) red[((warp * NT + nt) * 4 + e) * 32 + lane] = acc[nt][e];
     __syncthreads();
-    // element (row r of the tile, activation m): sum over warps and over the row's digit columns
-    for (int idx = threadIdx.x; idx < 16 * a.m; idx += blockDim.x) {
-        const int r = idx & 15, m = idx >> 4;
-        const int64_t row = (int64_t)rt * 16 + r;
-        if (row >= sg.n) continue;
-        float v = 0.f;
-        for (int d = 0; d < a.digits; ++d) {
-            const int col = m * a.digits + d, nt = col >> 3, cc = col & 7;
-            const int e = (r < 8 ? 0 : 2) + (cc & 1), ln = (r & 7) * 4 + (cc >> 1);
-#pragma unroll
-            for (int w = 0; w < IMMA_WARPS; ++w) v += red[w][nt][e][ln];
+    reduce_store<NT, IMMA_WARPS>(a, sg, s == 0, rt, red);
+}
+
+// ── Kernel B (k % 256 == 0, digits fit shared memory): persistent streaming kernel ──
+// One CTA per SM with 16 warps. Warp w owns k-tiles w, w+16, ... of every tile row the CTA visits
+// (rows blockIdx.x, +gridDim.x, ...), so consecutive tiles of a warp are weight data only: they flow
+// through a per-warp ring of cp.async stages (STAGES deep) while the activation digits, digit-sum
+// records and column scales of the whole row sit in shared memory, loaded once per CTA. The weight
+// prefetch is issued before the grid-dependency wait, so under programmatic dependent launch it
+// overlaps the kernel that produces the activations.
+constexpr int STREAM_WARPS = 16;
+constexpr int STREAM_STAGES = 3;
+
+struct StreamPlan {
+    int stage_bytes;   // ring slot size: largest tile among the segments
+    int xq_off, rec32_off, rec16_off, cs_off, red_off, total;  // byte offsets in dynamic shared memory
+    int total_tiles;   // tile rows over all segments
+};
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+    const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+template <int NT>
+__global__ void __launch_bounds__(STREAM_WARPS * 32, 1) gemv_imma_stream_kernel(const ImmaArgs a, const StreamPlan p) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int kts = a.k >> 8;
+    const int nk = kts > warp ? (kts - warp + STREAM_WARPS - 1) / STREAM_WARPS : 0;     // my k-tiles per tile row
+    const int n_rows = p.total_tiles > (int)blockIdx.x ? (p.total_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    const int total = n_rows * nk;                                                      // my tiles, in visiting order
+    uint8_t* ring = smem + (size_t)warp * STREAM_STAGES * p.stage_bytes;
+
+    // tile i of this warp -> (segment, tile row within the segment, k-tile)
+    auto locate = [&](int i, int& s, int& rt, int& kt) {
+        const int it = i / nk;
+        kt = warp + STREAM_WARPS * (i - it * nk);
+        rt = blockIdx.x + it * gridDim.x;
+        s = 0;
+        while (s < a.nseg - 1 && rt >= (a.seg[s].n + 15) / 16) { rt -= (a.seg[s].n + 15) / 16; ++s; }
+    };
+    auto tile_bytes = [&](int dtype) { return dtype == T_Q4_K ? Q4_K_TILE_BYTES : dtype == T_Q6_K ? Q6_K_TILE_BYTES : 4352; };
+    auto issue = [&](int i) {
+        if (i < total) {
+            int s, rt, kt;
+            locate(i, s, rt, kt);
+            const int tb = tile_bytes(a.seg[s].dtype);
+            const uint8_t* src = a.seg[s].wt + ((int64_t)rt * kts + kt) * tb;
+            uint8_t* dst = ring + (size_t)(i % STREAM_STAGES) * p.stage_bytes;
+            for (int c = lane; c < tb / 16; c += 32) cp_async16(dst + c * 16, src + c * 16);
         }
-        if (sg.bias) v += sg.bias[row];
-        if (s == 0 && a.res) v += a.res[(int64_t)m * a.ldres + row];
-        sg.y[(int64_t)m * sg.ldy + row] = v;
+        cp_async_commit();
+    };
+#pragma unroll
+    for (int i = 0; i < STREAM_STAGES - 1; ++i) issue(i);
+
+    // everything below depends on the kernel that produced the activations
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;\n" ::);
+    const int ncols = a.m * a.digits;
+    {
+        int8_t* xs = reinterpret_cast<int8_t*>(smem + p.xq_off);
+        const int vec_per_col = a.kp / 16;
+        for (int i = threadIdx.x; i < ncols * vec_per_col; i += blockDim.x) {
+            const int c = i / vec_per_col, v = i - c * vec_per_col;
+            reinterpret_cast<uint4*>(xs)[i] = ldg_u4(a.xq + (int64_t)c * a.kp + (int64_t)v * 16);
+        }
+        // records [kt][col][32 B] -> shared [kt][ncols][32 B]; scales [kt][ncp] -> shared [kt][ncp]
+        uint4* r32 = reinterpret_cast<uint4*>(smem + p.rec32_off);
+        uint4* r16 = reinterpret_cast<uint4*>(smem + p.rec16_off);
+        for (int i = threadIdx.x; i < kts * ncols * 2; i += blockDim.x) {
+            const int kt = i / (ncols * 2), rem = i - kt * ncols * 2;
+            const int64_t src = ((int64_t)kt * a.ncp) * 32 + (int64_t)rem * 16;
+            r32[i] = ldg_u4(a.xs32d + src);
+            r16[i] = ldg_u4(a.xs16d + src);
+        }
+        float* cs = reinterpret_cast<float*>(smem + p.cs_off);
+        for (int i = threadIdx.x; i < kts * a.ncp; i += blockDim.x) cs[i] = __ldg(a.colscale + i);
     }
+    __syncthreads();
+
+    const int8_t* xs = reinterpret_cast<const int8_t*>(smem + p.xq_off);
+    const uint8_t* r32 = smem + p.rec32_off;
+    const uint8_t* r16 = smem + p.rec16_off;
+    const float* css = reinterpret_cast<const float*>(smem + p.cs_off);
+    float* red = reinterpret_cast<float*>(smem + p.red_off);
+    float acc[NT][4];
+    int i = 0;
+    for (int it = 0; it < n_rows; ++it) {
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[nt][e] = 0.f;
+        int s = 0, rt = 0, kt = 0;
+        for (int j = 0; j < nk; ++j, ++i) {
+            issue(i + STREAM_STAGES - 1);
+            cp_async_wait<STREAM_STAGES - 1>();
+            __syncwarp();
+            locate(i, s, rt, kt);
+            const int dtype = a.seg[s].dtype;
+            const uint8_t* tile = ring + (size_t)(i % STREAM_STAGES) * p.stage_bytes;
+            BFrag<NT> b;
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                const int col = nt * 8 + g;
+                if (col < ncols) {
+                    const int8_t* base = xs + (size_t)col * a.kp + (size_t)kt * 256 + t * 64;
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const uint4 v = ld_u4(base + 16 * q);
+                        b.w[nt][4 * q] = v.x; b.w[nt][4 * q + 1] = v.y; b.w[nt][4 * q + 2] = v.z; b.w[nt][4 * q + 3] = v.w;
+                    }
+                    const size_t rec = ((size_t)kt * ncols + col) * 32 + 4 * t;
+                    b.ra32[nt] = *reinterpret_cast<const uint32_t*>(r32 + rec);
+                    b.rb32[nt] = *reinterpret_cast<const uint32_t*>(r32 + rec + 16);
+                    b.ra16[nt] = *reinterpret_cast<const uint32_t*>(r16 + rec);
+                    b.rb16[nt] = *reinterpret_cast<const uint32_t*>(r16 + rec + 16);
+                } else {
+#pragma unroll
+                    for (int q = 0; q < 16; ++q) b.w[nt][q] = 0u;
+                    b.ra32[nt] = b.rb32[nt] = b.ra16[nt] = b.rb16[nt] = 0u;
+                }
+                b.cs[nt] = *reinterpret_cast<const float2*>(css + (size_t)kt * a.ncp + nt * 8 + 2 * t);
+            }
+            if (dtype == T_Q4_K) {
+                Q4Regs r;
+                load_q4_k<false>(tile, lane, r);
+                compute_q4_k<NT>(r, b, lane, acc);
+            } else if (dtype == T_Q6_K) {
+                Q6Regs r;
+                load_q6_k<false>(tile, lane, r);
+                compute_q6_k<NT>(r, b, lane, acc);
+            } else {
+                Q8Regs r;
+                load_q8_0<false>(tile, lane, r);
+                compute_q8_0<NT>(r, b, acc);
+            }
+            __syncwarp();  // the stage is free for the copy issued next iteration
+        }
+        // every warp visits the same tile rows: locate the row even when this warp had no k-tile
+        rt = blockIdx.x + it * gridDim.x;
+        s = 0;
+        while (s < a.nseg - 1 && rt >= (a.seg[s].n + 15) / 16) { rt -= (a.seg[s].n + 15) / 16; ++s; }
+        float* rbuf = red + (size_t)(it & 1) * STREAM_WARPS * NT * 128;
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) rbuf[((warp * NT + nt) * 4 + e) * 32 + lane] = acc[nt][e];
+        __syncthreads();
+        reduce_store<NT, STREAM_WARPS>(a, a.seg[s], s == 0, rt, rbuf);
+    }
+    cp_async_wait<0>();
+}
+
+static int g_sm_count = 0;
+static bool g_stream_attr[3] = {false, false, false};
+
+// Shared-memory layout of the streaming kernel, or total == 0 when the launch does not qualify.
+static StreamPlan plan_stream(const ImmaArgs& a) {
+    StreamPlan p{};
+    if (a.k % 256 != 0 || a.ncp > 16) return p;
+    const int kts = a.k / 256, ncols = a.m * a.digits, nt = a.ncp / 8;
+    int stage = 0, tiles = 0;
+    for (int s = 0; s < a.nseg; ++s) {
+        const int dt = a.seg[s].dtype;
+        if (dt != T_Q4_K && dt != T_Q6_K && dt != T_Q8_0) return p;
+        stage = stage > (dt == T_Q4_K ? Q4_K_TILE_BYTES : dt == T_Q6_K ? Q6_K_TILE_BYTES : 4352)
+                    ? stage : (dt == T_Q4_K ? Q4_K_TILE_BYTES : dt == T_Q6_K ? Q6_K_TILE_BYTES : 4352);
+        tiles += (a.seg[s].n + 15) / 16;
+    }
+    int off = STREAM_WARPS * STREAM_STAGES * stage;
+    p.stage_bytes = stage;
+    p.xq_off = off; off += ncols * a.kp;
+    p.rec32_off = off; off += kts * ncols * 32;
+    p.rec16_off = off; off += kts * ncols * 32;
+    p.cs_off = off; off += kts * a.ncp * 4;
+    off = (off + 15) / 16 * 16;
+    p.red_off = off; off += 2 * STREAM_WARPS * nt * 128 * 4;
+    p.total_tiles = tiles;
+    p.total = off <= 200 * 1024 ? off : 0;
+    return p;
 }
 
 cudaError_t launch_gemv_imma(const ImmaArgs& a, cudaStream_t st) {
@@ -728,12 +965,33 @@ cudaError_t launch_gemv_imma(const ImmaArgs& a, cudaStream_t st) {
     for (int s = 0; s < a.nseg; ++s) tiles += (a.seg[s].n + 15) / 16;
     if (tiles == 0) return cudaSuccess;
     const int nt = a.ncp / 8;
+    const StreamPlan p = g_imma_kernel.load() == 2 ? StreamPlan{} : plan_stream(a);
+    if (p.total > 0) {
+        if (g_sm_count == 0) {
+            int dev = 0;
+            cudaGetDevice(&dev);
+            cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
+            if (g_sm_count <= 0) g_sm_count = 148;
+        }
+        const int grid = tiles < g_sm_count ? tiles : g_sm_count;
+        if (!g_stream_attr[nt]) {
+            cudaError_t e = nt == 1 ? cudaFuncSetAttribute(gemv_imma_stream_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)
+                                    : cudaFuncSetAttribute(gemv_imma_stream_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+            if (e != cudaSuccess) return e;
+            g_stream_attr[nt] = true;
+        }
+        if (nt == 1) gemv_imma_stream_kernel<1><<<grid, STREAM_WARPS * 32, p.total, st>>>(a, p);
+        else gemv_imma_stream_kernel<2><<<grid, STREAM_WARPS * 32, p.total, st>>>(a, p);
+        return count_launch_and_check();
+    }
     if (nt == 1) gemv_imma_kernel<1><<<tiles, IMMA_WARPS * 32, 0, st>>>(a);
     else if (nt == 2) gemv_imma_kernel<2><<<tiles, IMMA_WARPS * 32, 0, st>>>(a);
     else if (nt == 4) gemv_imma_kernel<4><<<tiles, IMMA_WARPS * 32, 0, st>>>(a);
     else return cudaErrorInvalidValue;
     return count_launch_and_check();
 }
+
+void imma_select_kernel(int which) { g_imma_kernel.store(which); }
 
 cudaError_t launch_quant_gemv(const float* x, int ldx, ImmaArgs& a, const ActWorkspace& ws, bool requantize, cudaStream_t st) {
     if (a.m <= 0) return cudaSuccess;

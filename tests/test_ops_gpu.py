@@ -51,7 +51,7 @@ MATMUL_CASES = [(1, 1536, 512), (3, 256, 48), (17, 256, 48), (1, 256, 1), (2, 51
                 (8, 2048, 64), (9, 512, 16), (32, 1024, 40)]
 
 
-@pytest.fixture(params=[0, 1], ids=["tensor-core", "cuda-core"])
+@pytest.fixture(params=[0, 1, 2], ids=["tensor-core-stream", "cuda-core", "tensor-core-rowtile"])
 def gemv_path(request):
     ops.set_gemv_path(request.param)
     yield request.param
