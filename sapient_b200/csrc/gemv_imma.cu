@@ -777,60 +777,91 @@ __global__ void __launch_bounds__(IMMA_WARPS * 32, (NT <= 2 ? 2 : 1)) gemv_imma_
 
 // ── Kernel B (k % 256 == 0, digits fit shared memory): persistent streaming kernel ──
 // One CTA per SM with 16 warps. Warp w owns k-tiles w, w+16, ... of every tile row the CTA visits
-// (rows blockIdx.x, +gridDim.x, ...), so consecutive tiles of a warp are weight data only: they flow
-// through a per-warp ring of cp.async stages (STAGES deep) while the activation digits, digit-sum
-// records and column scales of the whole row sit in shared memory, loaded once per CTA. The weight
-// prefetch is issued before the grid-dependency wait, so under programmatic dependent launch it
-// overlaps the kernel that produces the activations.
+// (rows blockIdx.x, +gridDim.x, ...), so consecutive tiles of a warp are weight data only: each is one
+// contiguous 2.3-4.3 KB tile fetched by a single TMA bulk copy (cp.async.bulk, mbarrier completion) into a
+// per-warp ring of STREAM_STAGES slots, while the activation digits, digit-sum records and column scales of
+// the whole row sit in shared memory, loaded once per CTA. The weight prefetch is issued before the
+// grid-dependency wait, so under programmatic dependent launch it overlaps the kernel that produces the
+// activations.
 constexpr int STREAM_WARPS = 16;
-constexpr int STREAM_STAGES = 3;
+constexpr int STREAM_MAX_STAGES = 4;
+constexpr int STREAM_SMEM_LIMIT = 220 * 1024;
+constexpr int STREAM_SPIN_LIMIT = 1 << 20;  // mbarrier polls before a wait gives up (~ a second)
+
+// Set when a bounded wait in a kernel of this file ran out; host code reads and clears it.
+__device__ int g_imma_timeout = 0;
 
 struct StreamPlan {
-    int stage_bytes;   // ring slot size: largest tile among the segments
-    int xq_off, rec32_off, rec16_off, cs_off, red_off, total;  // byte offsets in dynamic shared memory
+    int stage_bytes;   // ring slot size: largest tile among the segments, multiple of 128
+    int stages;        // ring depth per warp (2..4, as many as fit)
+    int bar_off, xq_off, rec32_off, rec16_off, cs_off, red_off, total;  // byte offsets in dynamic shared memory
     int total_tiles;   // tile rows over all segments
 };
 
-__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
-    const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem));
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
 }
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, int bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_copy_g2s(void* dst, const void* src, int bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(smem_u32(dst)),
+                 "l"(src), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+// Bounded wait for phase `parity` of the barrier; false when the limit ran out.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    const uint32_t addr = smem_u32(bar);
+    for (int spin = 0; spin < STREAM_SPIN_LIMIT; ++spin) {
+        uint32_t ok;
+        asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+                     : "=r"(ok)
+                     : "r"(addr), "r"(parity)
+                     : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
 
 template <int NT>
 __global__ void __launch_bounds__(STREAM_WARPS * 32, 1) gemv_imma_stream_kernel(const ImmaArgs a, const StreamPlan p) {
-    extern __shared__ __align__(16) uint8_t smem[];
+    extern __shared__ __align__(128) uint8_t smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int kts = a.k >> 8;
     const int nk = kts > warp ? (kts - warp + STREAM_WARPS - 1) / STREAM_WARPS : 0;     // my k-tiles per tile row
     const int n_rows = p.total_tiles > (int)blockIdx.x ? (p.total_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-    const int total = n_rows * nk;                                                      // my tiles, in visiting order
-    uint8_t* ring = smem + (size_t)warp * STREAM_STAGES * p.stage_bytes;
-
-    // tile i of this warp -> (segment, tile row within the segment, k-tile)
-    auto locate = [&](int i, int& s, int& rt, int& kt) {
-        const int it = i / nk;
-        kt = warp + STREAM_WARPS * (i - it * nk);
-        rt = blockIdx.x + it * gridDim.x;
-        s = 0;
-        while (s < a.nseg - 1 && rt >= (a.seg[s].n + 15) / 16) { rt -= (a.seg[s].n + 15) / 16; ++s; }
-    };
+    uint8_t* ring = smem + (size_t)warp * p.stages * p.stage_bytes;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + p.bar_off) + warp * STREAM_MAX_STAGES;
     auto tile_bytes = [&](int dtype) { return dtype == T_Q4_K ? Q4_K_TILE_BYTES : dtype == T_Q6_K ? Q6_K_TILE_BYTES : 4352; };
-    auto issue = [&](int i) {
-        if (i < total) {
-            int s, rt, kt;
-            locate(i, s, rt, kt);
-            const int tb = tile_bytes(a.seg[s].dtype);
-            const uint8_t* src = a.seg[s].wt + ((int64_t)rt * kts + kt) * tb;
-            uint8_t* dst = ring + (size_t)(i % STREAM_STAGES) * p.stage_bytes;
-            for (int c = lane; c < tb / 16; c += 32) cp_async16(dst + c * 16, src + c * 16);
+    auto seg_tiles = [&](int s) { return (a.seg[s].n + 15) / 16; };
+
+    if (lane == 0)
+        for (int s = 0; s < p.stages; ++s) mbar_init(&bars[s], 1);
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    __syncwarp();
+
+    // producer cursor: the next tile to fetch = (segment ps, tile row pr of it, k-tile index pj of this warp)
+    int ps = 0, pr = blockIdx.x, pj = 0, p_left = n_rows * nk, p_slot = 0;
+    while (ps < a.nseg - 1 && pr >= seg_tiles(ps)) { pr -= seg_tiles(ps); ++ps; }
+    auto issue = [&]() {
+        if (p_left > 0 && lane == 0) {
+            const int tb = tile_bytes(a.seg[ps].dtype);
+            const uint8_t* src = a.seg[ps].wt + ((int64_t)pr * kts + warp + STREAM_WARPS * pj) * tb;
+            mbar_expect_tx(&bars[p_slot], tb);
+            bulk_copy_g2s(ring + (size_t)p_slot * p.stage_bytes, src, tb, &bars[p_slot]);
         }
-        cp_async_commit();
+        if (p_left > 0) {
+            --p_left;
+            p_slot = p_slot + 1 == p.stages ? 0 : p_slot + 1;
+            if (++pj == nk) {
+                pj = 0;
+                pr += gridDim.x;
+                while (ps < a.nseg - 1 && pr >= seg_tiles(ps)) { pr -= seg_tiles(ps); ++ps; }
+            }
+        }
     };
-#pragma unroll
-    for (int i = 0; i < STREAM_STAGES - 1; ++i) issue(i);
+    for (int i = 0; i < p.stages - 1; ++i) issue();
 
     // everything below depends on the kernel that produced the activations
     asm volatile("griddepcontrol.wait;\n" ::: "memory");
@@ -863,20 +894,22 @@ __global__ void __launch_bounds__(STREAM_WARPS * 32, 1) gemv_imma_stream_kernel(
     const float* css = reinterpret_cast<const float*>(smem + p.cs_off);
     float* red = reinterpret_cast<float*>(smem + p.red_off);
     float acc[NT][4];
-    int i = 0;
+    int c_slot = 0;
+    uint32_t c_parity = 0;
+    bool ok = true;
+    int s = 0, rt = blockIdx.x;
+    while (s < a.nseg - 1 && rt >= seg_tiles(s)) { rt -= seg_tiles(s); ++s; }
     for (int it = 0; it < n_rows; ++it) {
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
             for (int e = 0; e < 4; ++e) acc[nt][e] = 0.f;
-        int s = 0, rt = 0, kt = 0;
-        for (int j = 0; j < nk; ++j, ++i) {
-            issue(i + STREAM_STAGES - 1);
-            cp_async_wait<STREAM_STAGES - 1>();
-            __syncwarp();
-            locate(i, s, rt, kt);
-            const int dtype = a.seg[s].dtype;
-            const uint8_t* tile = ring + (size_t)(i % STREAM_STAGES) * p.stage_bytes;
+        const int dtype = a.seg[s].dtype;
+        for (int j = 0; j < nk; ++j) {
+            issue();
+            ok = ok && mbar_wait(&bars[c_slot], c_parity);
+            const int kt = warp + STREAM_WARPS * j;
+            const uint8_t* tile = ring + (size_t)c_slot * p.stage_bytes;
             BFrag<NT> b;
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
@@ -913,21 +946,42 @@ __global__ void __launch_bounds__(STREAM_WARPS * 32, 1) gemv_imma_stream_kernel(
                 load_q8_0<false>(tile, lane, r);
                 compute_q8_0<NT>(r, b, acc);
             }
-            __syncwarp();  // the stage is free for the copy issued next iteration
+            __syncwarp();  // all lanes are done reading the slot before lane 0 refills it
+            if (++c_slot == p.stages) { c_slot = 0; c_parity ^= 1u; }
         }
-        // every warp visits the same tile rows: locate the row even when this warp had no k-tile
-        rt = blockIdx.x + it * gridDim.x;
-        s = 0;
-        while (s < a.nseg - 1 && rt >= (a.seg[s].n + 15) / 16) { rt -= (a.seg[s].n + 15) / 16; ++s; }
         float* rbuf = red + (size_t)(it & 1) * STREAM_WARPS * NT * 128;
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
             for (int e = 0; e < 4; ++e) rbuf[((warp * NT + nt) * 4 + e) * 32 + lane] = acc[nt][e];
         __syncthreads();
-        reduce_store<NT, STREAM_WARPS>(a, a.seg[s], s == 0, rt, rbuf);
+        // 16 rows x m outputs, each the sum of STREAM_WARPS x digits partials: `grp` threads per output
+        {
+            int mp = 1;
+            while (mp < a.m) mp <<= 1;
+            const int grp = 32 / mp > 0 ? 32 / mp : 1;
+            const int out = threadIdx.x / grp, sub = threadIdx.x - out * grp;
+            const int r = out & 15, m = out >> 4;
+            float v = 0.f;
+            if (m < a.m) {
+                for (int q = sub; q < STREAM_WARPS * a.digits; q += grp) {
+                    const int w = q / a.digits, col = m * a.digits + (q - w * a.digits), nt = col >> 3, cc = col & 7;
+                    v += rbuf[((w * NT + nt) * 4 + (r < 8 ? 0 : 2) + (cc & 1)) * 32 + (r & 7) * 4 + (cc >> 1)];
+                }
+            }
+            for (int o = grp >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+            const int64_t row = (int64_t)rt * 16 + r;
+            if (sub == 0 && m < a.m && row < a.seg[s].n) {
+                const ImmaSeg& sg = a.seg[s];
+                if (sg.bias) v += sg.bias[row];
+                if (s == 0 && a.res) v += a.res[(int64_t)m * a.ldres + row];
+                sg.y[(int64_t)m * sg.ldy + row] = v;
+            }
+        }
+        rt += gridDim.x;
+        while (s < a.nseg - 1 && rt >= seg_tiles(s)) { rt -= seg_tiles(s); ++s; }
     }
-    cp_async_wait<0>();
+    if (!ok && lane == 0) atomicExch(&g_imma_timeout, 1);
 }
 
 static int g_sm_count = 0;
@@ -946,16 +1000,23 @@ static StreamPlan plan_stream(const ImmaArgs& a) {
                     ? stage : (dt == T_Q4_K ? Q4_K_TILE_BYTES : dt == T_Q6_K ? Q6_K_TILE_BYTES : 4352);
         tiles += (a.seg[s].n + 15) / 16;
     }
-    int off = STREAM_WARPS * STREAM_STAGES * stage;
+    stage = (stage + 127) / 128 * 128;
     p.stage_bytes = stage;
-    p.xq_off = off; off += ncols * a.kp;
-    p.rec32_off = off; off += kts * ncols * 32;
-    p.rec16_off = off; off += kts * ncols * 32;
-    p.cs_off = off; off += kts * a.ncp * 4;
-    off = (off + 15) / 16 * 16;
-    p.red_off = off; off += 2 * STREAM_WARPS * nt * 128 * 4;
+    for (int stages = STREAM_MAX_STAGES; stages >= 2; --stages) {
+        int off = STREAM_WARPS * stages * stage;
+        p.stages = stages;
+        p.bar_off = off; off += STREAM_WARPS * STREAM_MAX_STAGES * 8;
+        p.xq_off = off; off += ncols * a.kp;
+        p.rec32_off = off; off += kts * ncols * 32;
+        p.rec16_off = off; off += kts * ncols * 32;
+        p.cs_off = off; off += kts * a.ncp * 4;
+        off = (off + 15) / 16 * 16;
+        p.red_off = off; off += 2 * STREAM_WARPS * nt * 128 * 4;
+        p.total = off;
+        if (off <= STREAM_SMEM_LIMIT) break;
+        p.total = 0;
+    }
     p.total_tiles = tiles;
-    p.total = off <= 200 * 1024 ? off : 0;
     return p;
 }
 
@@ -975,8 +1036,8 @@ cudaError_t launch_gemv_imma(const ImmaArgs& a, cudaStream_t st) {
         }
         const int grid = tiles < g_sm_count ? tiles : g_sm_count;
         if (!g_stream_attr[nt]) {
-            cudaError_t e = nt == 1 ? cudaFuncSetAttribute(gemv_imma_stream_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)
-                                    : cudaFuncSetAttribute(gemv_imma_stream_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+            cudaError_t e = nt == 1 ? cudaFuncSetAttribute(gemv_imma_stream_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, STREAM_SMEM_LIMIT)
+                                    : cudaFuncSetAttribute(gemv_imma_stream_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, STREAM_SMEM_LIMIT);
             if (e != cudaSuccess) return e;
             g_stream_attr[nt] = true;
         }
