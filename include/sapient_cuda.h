@@ -62,9 +62,9 @@ int32_t sp_cuda_dequant(const SpWeight* w, float* out_host);
 int32_t sp_cuda_matmul_nt(const SpWeight* w, const float* x_host, int64_t m, float* y_host);
 /* Same with device buffers on `stream` (a cudaStream_t, or NULL for the default stream); no synchronisation. */
 int32_t sp_cuda_matmul_nt_dev(const SpWeight* w, const float* x_dev, int64_t m, float* y_dev, void* stream);
-/* Which GEMV kernel runs: 0 (default) tensor-core GEMV on tile-repacked weights, persistent streaming kernel where it
- * qualifies; 1 the CUDA-core GEMV on the raw blocks (op-level calls only; an independent second implementation for
- * cross-checks); 2 tensor-core GEMV, always the one-CTA-per-tile-row kernel. Process-wide. */
+/* Which GEMV kernel runs: 0 (default) and 2: tensor-core GEMV on tile-repacked weights, one CTA per 16-row tile row;
+ * 1: the CUDA-core GEMV on the raw blocks (op-level calls only; an independent second implementation for
+ * cross-checks); 3: tensor-core GEMV, persistent TMA-streaming kernel where the shape qualifies. Process-wide. */
 int32_t sp_cuda_set_gemv_path(int32_t path);
 /* Device address and byte size of the resident blocks (for benchmarks that rotate buffers). */
 int32_t sp_cuda_weight_info(const SpWeight* w, int32_t* dtype, int64_t* n, int64_t* k, size_t* nbytes);

@@ -124,9 +124,9 @@ int32_t sp_cuda_device_count(void) {
 uint64_t sp_cuda_launch_count(void) { return launch_count(); }
 
 int32_t sp_cuda_set_gemv_path(int32_t path) {
-    if (path < 0 || path > 2) { set_error("gemv path must be 0, 1 or 2"); return SP_ERR_ARG; }
+    if (path < 0 || path > 3) { set_error("gemv path must be 0..3"); return SP_ERR_ARG; }
     g_gemv_path.store(path == 1 ? 1 : 0);
-    imma_select_kernel(path == 2 ? 2 : 0);
+    imma_select_kernel(path == 3 ? 3 : 0);
     return SP_OK;
 }
 

@@ -8,6 +8,7 @@
 // splits by a second small kernel. K and V are fp16 in the cache, all arithmetic is f32.
 // With one split the block writes the output row directly.
 #include "kernels.h"
+#include "pdl.cuh"
 #include "sp_common.cuh"
 
 namespace sp {
@@ -29,6 +30,8 @@ attention_split_kernel(const float* __restrict__ q, int ldq, float* __restrict__
                        float scale, int n_splits, float* __restrict__ part) {
     __shared__ float sh_m[ATT_WARPS], sh_l[ATT_WARPS];
     __shared__ float sh_o[ATT_WARPS][256];
+    pdl_wait();
+    pdl_trigger();
     const int h = blockIdx.x, t = blockIdx.y, sp = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int hd = kv.head_dim, npairs = hd >> 1;
@@ -166,8 +169,9 @@ cudaError_t launch_attention_split(const float* q, int ldq, int n_tok, int n_hea
                                    KvGeom kv, int layer, float scale, int n_splits, float* scratch, cudaStream_t st) {
     if (n_tok == 0) return cudaSuccess;
     if (n_splits < 2 || !scratch) return cudaErrorInvalidValue;
-    attention_split_kernel<<<dim3(n_heads, n_tok, n_splits), ATT_WARPS * 32, 0, st>>>(q, ldq, nullptr, 0, n_heads, tok_slot, tok_pos, kv,
-                                                                                     layer, scale, n_splits, scratch);
+    cudaError_t le = launch_pdl(attention_split_kernel, dim3(n_heads, n_tok, n_splits), dim3(ATT_WARPS * 32), 0, st, q, ldq,
+                                (float*)nullptr, 0, n_heads, tok_slot, tok_pos, kv, layer, scale, n_splits, scratch);
+    if (le != cudaSuccess) return le;
     return count_launch_and_check();
 }
 
@@ -176,8 +180,9 @@ cudaError_t launch_attention(const float* q, int ldq, float* out, int ldo, int n
                              cudaStream_t st) {
     if (n_tok == 0) return cudaSuccess;
     if (n_splits < 1 || (n_splits > 1 && !scratch)) return cudaErrorInvalidValue;
-    attention_split_kernel<<<dim3(n_heads, n_tok, n_splits), ATT_WARPS * 32, 0, st>>>(q, ldq, out, ldo, n_heads, tok_slot, tok_pos,
-                                                                                     kv, layer, scale, n_splits, scratch);
+    cudaError_t le = launch_pdl(attention_split_kernel, dim3(n_heads, n_tok, n_splits), dim3(ATT_WARPS * 32), 0, st, q, ldq, out, ldo,
+                                n_heads, tok_slot, tok_pos, kv, layer, scale, n_splits, scratch);
+    if (le != cudaSuccess) return le;
     cudaError_t e = count_launch_and_check();
     if (e != cudaSuccess || n_splits == 1) return e;
     attention_merge_kernel<<<dim3(n_heads, n_tok), 128, 0, st>>>(scratch, n_heads, n_splits, kv.head_dim, out, ldo);

@@ -10,6 +10,7 @@
 #include <cstring>
 
 #include "engine.h"
+#include "pdl.cuh"
 #include "sp_common.cuh"
 
 namespace sp {
@@ -23,6 +24,8 @@ namespace sp {
 // After a greedy step: the argmax becomes the next input token, positions advance, the token is logged.
 __global__ void advance_greedy_kernel(const uint32_t* __restrict__ argmax, uint32_t* __restrict__ ids,
                                       int32_t* __restrict__ pos, uint32_t* __restrict__ log, int b) {
+    pdl_wait();
+    pdl_trigger();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < b) {
         const uint32_t t = argmax[i];
@@ -191,7 +194,8 @@ int Engine::decode_greedy(const uint32_t* first_ids, const int32_t* slots, int b
     }
     for (int s = 0; s < steps; ++s) {
         SP_TRY(launch_decode_step(b));
-        advance_greedy_kernel<<<(b + 127) / 128, 128, 0, stream>>>(d_argmax_, d_ids_, d_tok_pos_, d_tokens_ + (size_t)s * b, b);
+        SP_CUDA_TRY(launch_pdl(advance_greedy_kernel, dim3((b + 127) / 128), dim3(128), 0, stream, (const uint32_t*)d_argmax_, d_ids_,
+                               d_tok_pos_, d_tokens_ + (size_t)s * b, b));
         SP_CUDA_TRY(cudaGetLastError());
         adjust_launch_count(1);
     }

@@ -16,8 +16,23 @@
 #include "sp_common.cuh"
 
 #include <atomic>
+#include <cstdlib>
+
+#include "pdl.cuh"
 
 namespace sp {
+
+static std::atomic<int> g_pdl{-1};
+bool pdl_enabled() {
+    int v = g_pdl.load();
+    if (v < 0) {
+        const char* e = std::getenv("SAPIENT_CUDA_PDL");
+        v = (e && e[0] == '0') ? 0 : 1;
+        g_pdl.store(v);
+    }
+    return v != 0;
+}
+void pdl_set_enabled(bool on) { g_pdl.store(on ? 1 : 0); }
 
 static std::atomic<uint64_t> g_launches{0};
 uint64_t launch_count() { return g_launches.load(); }
@@ -52,6 +67,8 @@ cudaError_t launch_dequant(int dtype, const uint8_t* w, int64_t n, int64_t k, fl
 // ─────────────────────────────── embedding ──────────────────────────────────
 __global__ void embed_kernel(int dtype, const uint8_t* __restrict__ table, int64_t hidden, int64_t rb,
                              const uint32_t* __restrict__ ids, float* __restrict__ out) {
+    pdl_wait();
+    pdl_trigger();
     const int t = blockIdx.x;
     const uint8_t* row = table + (int64_t)ids[t] * rb;
     for (int64_t c = threadIdx.x; c < hidden; c += blockDim.x) out[(int64_t)t * hidden + c] = dequant_elem(dtype, row, c);
@@ -60,7 +77,8 @@ __global__ void embed_kernel(int dtype, const uint8_t* __restrict__ table, int64
 cudaError_t launch_embed(int dtype, const uint8_t* table, int64_t hidden, const uint32_t* ids, int n_tok, float* out,
                          cudaStream_t st) {
     if (n_tok == 0) return cudaSuccess;
-    embed_kernel<<<n_tok, 256, 0, st>>>(dtype, table, hidden, row_bytes(dtype, hidden), ids, out);
+    cudaError_t le = launch_pdl(embed_kernel, dim3(n_tok), dim3(256), 0, st, dtype, table, hidden, row_bytes(dtype, hidden), ids, out);
+    if (le != cudaSuccess) return le;
     return finish_launch();
 }
 
@@ -320,6 +338,8 @@ __device__ __forceinline__ int64_t kv_offset(const KvGeom& kv, int layer, int pa
 __global__ void rope_kv_append_kernel(float* __restrict__ qkv, int n_heads, int n_kv, int head_dim, int rotary_dim,
                                       const float2* __restrict__ cos_sin, const int32_t* __restrict__ tok_slot,
                                       const int32_t* __restrict__ tok_pos, KvGeom kv, int layer) {
+    pdl_wait();
+    pdl_trigger();
     const int t = blockIdx.x, j = blockIdx.y;
     const int pos = tok_pos[t], slot = tok_slot[t];
     const int half = rotary_dim >> 1;
@@ -354,8 +374,9 @@ cudaError_t launch_rope_kv_append(float* qkv, int n_tok, int n_heads, int n_kv, 
                                   const float2* cos_sin, const int32_t* tok_slot, const int32_t* tok_pos, KvGeom kv,
                                   int layer, cudaStream_t st) {
     if (n_tok == 0) return cudaSuccess;
-    rope_kv_append_kernel<<<dim3(n_tok, n_heads + 2 * n_kv), 64, 0, st>>>(qkv, n_heads, n_kv, head_dim, rotary_dim, cos_sin,
-                                                                           tok_slot, tok_pos, kv, layer);
+    cudaError_t le = launch_pdl(rope_kv_append_kernel, dim3(n_tok, n_heads + 2 * n_kv), dim3(64), 0, st, qkv, n_heads, n_kv, head_dim,
+                                rotary_dim, cos_sin, tok_slot, tok_pos, kv, layer);
+    if (le != cudaSuccess) return le;
     return finish_launch();
 }
 
@@ -441,6 +462,8 @@ cudaError_t launch_mul(const float* a, const float* b, float* y, int64_t n, cuda
 // ─────────────────────────────── argmax ─────────────────────────────────────
 // Ties resolve to the LAST index holding the maximum, like Iterator::max_by.
 __global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ logits, int n, int ld, uint32_t* __restrict__ out) {
+    pdl_wait();
+    pdl_trigger();
     __shared__ float sv[32];
     __shared__ int si[32];
     const float* row = logits + (int64_t)blockIdx.x * ld;
@@ -476,7 +499,8 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ 
 
 cudaError_t launch_argmax(const float* logits, int rows, int n, int ld, uint32_t* out, cudaStream_t st) {
     if (rows == 0) return cudaSuccess;
-    argmax_kernel<<<rows, 1024, 0, st>>>(logits, n, ld, out);
+    cudaError_t le = launch_pdl(argmax_kernel, dim3(rows), dim3(1024), 0, st, logits, n, ld, out);
+    if (le != cudaSuccess) return le;
     return finish_launch();
 }
 

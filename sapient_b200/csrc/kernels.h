@@ -54,8 +54,8 @@ struct ActWorkspace;
 void imma_plan(ImmaArgs& a, const ActWorkspace& ws);
 cudaError_t launch_act_quant(const float* x, int ldx, const ImmaArgs& a, cudaStream_t st);
 cudaError_t launch_gemv_imma(const ImmaArgs& a, cudaStream_t st);
-// 0: choose per launch (the persistent streaming kernel when k % 256 == 0 and the digits fit shared memory);
-// 2: always the one-CTA-per-tile-row kernel.
+// 0: the one-CTA-per-tile-row kernel; 3: the persistent TMA-streaming kernel when k % 256 == 0 and the digits fit
+// shared memory.
 void imma_select_kernel(int which);
 // Producers that emit the digits of a GEMV input directly (a: planned ImmaArgs; a.m rows, a.k columns):
 // RMSNorm / LayerNorm of x (y optional f32 copy), SwiGLU (act 0) / tanh-GELU (act 1) of gu, merged split-K attention.

@@ -51,7 +51,7 @@ MATMUL_CASES = [(1, 1536, 512), (3, 256, 48), (17, 256, 48), (1, 256, 1), (2, 51
                 (8, 2048, 64), (9, 512, 16), (32, 1024, 40)]
 
 
-@pytest.fixture(params=[0, 1, 2], ids=["tensor-core-stream", "cuda-core", "tensor-core-rowtile"])
+@pytest.fixture(params=[0, 1, 3], ids=["tensor-core-rowtile", "cuda-core", "tensor-core-stream"])
 def gemv_path(request):
     ops.set_gemv_path(request.param)
     yield request.param
