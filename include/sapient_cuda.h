@@ -79,6 +79,22 @@ int32_t sp_cuda_rope(int32_t device, const float* x, int64_t n_heads, int64_t se
 /* causal GQA attention: q [H, sq, hd], k/v [Hkv, sk, hd] (f32, stored as fp16 pages on the device), out [H, sq, hd] */
 int32_t sp_cuda_attention(int32_t device, const float* q, const float* k, const float* v, int64_t n_heads,
                           int64_t n_kv_heads, int64_t sq, int64_t sk, int64_t head_dim, float* out);
+/* No counterpart in the reference: the same split-K attention for callers that must not allocate device memory
+ * (a serving loop whose memory pool owns the whole device, or code where an allocation's device-wide
+ * synchronisation would stall other streams). Every pointer is a DEVICE pointer the caller owns:
+ * d_q [n_tok, ldq] and d_out [n_tok, ldo] hold n_heads * head_dim floats per row; d_kv_pool is the fp16 page pool
+ * [layer][page][K|V][n_kv_heads][16 tokens][head_dim]; d_page_table [slots, max_pages]; d_tok_slot / d_tok_pos give
+ * each row's sequence slot and position (keys 0..pos are attended). The per-split partials live in a fixed array
+ * inside the library, SP_ATTENTION_STATIC_MAX_FLOATS floats per device: a call needing more
+ * (n_tok * n_heads * n_splits * (head_dim + 2) when n_splits > 1) fails with SP_ERR_SHAPE. The array is shared by
+ * all calls on a device, so calls must not overlap in time; it needs no clearing between calls. The first call on
+ * a device resolves the array's address and should be made before any stream capture. Launches on `stream`
+ * (a cudaStream_t, NULL = default stream) and returns without synchronising. */
+#define SP_ATTENTION_STATIC_MAX_FLOATS (1u << 20)
+int32_t sp_cuda_attention_paged_static(int32_t device, const float* d_q, int32_t ldq, float* d_out, int32_t ldo, int32_t n_tok,
+                                       int32_t n_heads, int32_t n_kv_heads, int32_t head_dim, const int32_t* d_tok_slot,
+                                       const int32_t* d_tok_pos, const void* d_kv_pool, const int32_t* d_page_table,
+                                       int32_t n_pages, int32_t max_pages, int32_t layer, int32_t n_splits, void* stream);
 int32_t sp_cuda_silu(int32_t device, const float* x, int64_t n, float* y);
 int32_t sp_cuda_gelu(int32_t device, const float* x, int64_t n, float* y);
 int32_t sp_cuda_add(int32_t device, const float* a, const float* b, int64_t n, float* y);

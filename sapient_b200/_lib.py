@@ -49,6 +49,8 @@ SIGNATURES = {
     "sp_cuda_layer_norm": (_i32, [_i32, _vp, _vp, _vp, _i64, _i64, _f, _vp]),
     "sp_cuda_rope": (_i32, [_i32, _vp, _i64, _i64, _i64, _vp, _f, _i64, _vp]),
     "sp_cuda_attention": (_i32, [_i32, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp]),
+    "sp_cuda_attention_paged_static": (_i32, [_i32, _vp, _i32, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _i32, _i32,
+                                              _i32, _i32, _vp]),
     "sp_cuda_silu": (_i32, [_i32, _vp, _i64, _vp]),
     "sp_cuda_gelu": (_i32, [_i32, _vp, _i64, _vp]),
     "sp_cuda_add": (_i32, [_i32, _vp, _vp, _i64, _vp]),
