@@ -51,21 +51,30 @@ attention_split_kernel(const float* __restrict__ q, int ldq, float* __restrict__
     float m = -INFINITY, l = 0.f;
     const int32_t* pt = kv.page_table + (int64_t)slot * kv.max_pages;
     for (int key0 = k_begin + warp * ATT_KEYS; key0 < k_end; key0 += ATT_WARPS * ATT_KEYS) {
-        const __half2* kp[ATT_KEYS];
-        const __half2* vp[ATT_KEYS];
+        // all K and V fragments of the four keys are requested before any arithmetic, so the V loads do not wait
+        // for the scores
+        __half2 kr[ATT_KEYS][ATT_MAX_PAIRS], vr[ATT_KEYS][ATT_MAX_PAIRS];
         float s[ATT_KEYS];
 #pragma unroll
         for (int j = 0; j < ATT_KEYS; ++j) {
             const int key = min(key0 + j, k_end - 1);  // tail keys repeat the last one and get weight 0
             const int page = pt[key / KV_PAGE];
-            kp[j] = reinterpret_cast<const __half2*>(kv.pool + kv_off(kv, layer, page, 0, kv_h) + (int64_t)(key % KV_PAGE) * hd);
-            vp[j] = reinterpret_cast<const __half2*>(kv.pool + kv_off(kv, layer, page, 1, kv_h) + (int64_t)(key % KV_PAGE) * hd);
-            float part_dot = 0.f;
+            const __half2* kp = reinterpret_cast<const __half2*>(kv.pool + kv_off(kv, layer, page, 0, kv_h) + (int64_t)(key % KV_PAGE) * hd);
+            const __half2* vp = reinterpret_cast<const __half2*>(kv.pool + kv_off(kv, layer, page, 1, kv_h) + (int64_t)(key % KV_PAGE) * hd);
 #pragma unroll
             for (int i = 0; i < ATT_MAX_PAIRS; ++i) {
                 const int p = lane + 32 * i;
-                if (p < npairs) {
-                    const float2 kf = __half22float2(kp[j][p]);
+                kr[j][i] = (p < npairs) ? kp[p] : __half2();
+                vr[j][i] = (p < npairs) ? vp[p] : __half2();
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < ATT_KEYS; ++j) {
+            float part_dot = 0.f;
+#pragma unroll
+            for (int i = 0; i < ATT_MAX_PAIRS; ++i) {
+                if (lane + 32 * i < npairs) {
+                    const float2 kf = __half22float2(kr[j][i]);
                     part_dot = fmaf(qv[i].x, kf.x, part_dot);
                     part_dot = fmaf(qv[i].y, kf.y, part_dot);
                 }
@@ -88,12 +97,11 @@ attention_split_kernel(const float* __restrict__ q, int ldq, float* __restrict__
         for (int j = 0; j < ATT_KEYS; ++j) { pw[j] = expf(s[j] - m_new); psum += pw[j]; }
 #pragma unroll
         for (int i = 0; i < ATT_MAX_PAIRS; ++i) {
-            const int p = lane + 32 * i;
-            if (p < npairs) {
+            if (lane + 32 * i < npairs) {
                 float ox = corr * o[i].x, oy = corr * o[i].y;
 #pragma unroll
                 for (int j = 0; j < ATT_KEYS; ++j) {
-                    const float2 vf = __half22float2(vp[j][p]);
+                    const float2 vf = __half22float2(vr[j][i]);
                     ox = fmaf(pw[j], vf.x, ox);
                     oy = fmaf(pw[j], vf.y, oy);
                 }

@@ -259,11 +259,12 @@ __global__ void __launch_bounds__(32) act_quant_kernel(const float* __restrict__
 
 // RMSNorm / LayerNorm of one activation row per block, emitting the digits of the normalised row (and, when
 // y != null, its f32 values). Arithmetic of the norm as in crates/sapient-backends/cpu/src/kernels/layernorm.rs:17-105.
+constexpr int NORM_WARPS = 16;
 template <bool LAYER_NORM>
-__global__ void __launch_bounds__(256) norm_quant_kernel(const float* __restrict__ x, int ldx, const float* __restrict__ w,
-                                                         const float* __restrict__ b, float eps, float* __restrict__ y, int ldy,
-                                                         QuantOut qo) {
-    __shared__ float sh[8];
+__global__ void __launch_bounds__(NORM_WARPS * 32) norm_quant_kernel(const float* __restrict__ x, int ldx, const float* __restrict__ w,
+                                                                     const float* __restrict__ b, float eps, float* __restrict__ y, int ldy,
+                                                                     QuantOut qo) {
+    __shared__ float sh[NORM_WARPS];
     pdl_wait();
     pdl_trigger();
     const int m = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -275,34 +276,58 @@ __global__ void __launch_bounds__(256) norm_quant_kernel(const float* __restrict
         __syncthreads();
         if (lane == 0) sh[warp] = v;
         __syncthreads();
-        float t = lane < 8 ? sh[lane] : 0.f;
+        float t = lane < NORM_WARPS ? sh[lane] : 0.f;
 #pragma unroll
-        for (int o = 4; o > 0; o >>= 1) t += __shfl_xor_sync(0xFFFFFFFFu, t, o);
+        for (int o = NORM_WARPS / 2; o > 0; o >>= 1) t += __shfl_xor_sync(0xFFFFFFFFu, t, o);
         return __shfl_sync(0xFFFFFFFFu, t, 0);
     };
+    // Each warp owns the 256-column tiles warp, warp + 16, ...; a lane's 8 columns of the warp's first tile stay in
+    // registers across the passes (rows of up to 4096 columns are read once).
+    const int kf = warp * 256 + lane * 8;
+    const bool have_first = kf < k;
+    float xf[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (have_first) load8(row + kf, xf);
     float mean = 0.f;
     if (LAYER_NORM) {
         float s = 0.f;
-        for (int i = threadIdx.x * 4; i < k; i += 1024) {
-            const float4 a = *reinterpret_cast<const float4*>(row + i);
-            s += (a.x + a.y) + (a.z + a.w);
+        if (have_first) s = ((xf[0] + xf[1]) + (xf[2] + xf[3])) + ((xf[4] + xf[5]) + (xf[6] + xf[7]));
+        for (int tile = warp + NORM_WARPS; tile < tiles; tile += NORM_WARPS) {
+            const int k0 = tile * 256 + lane * 8;
+            if (k0 < k) {
+                float xv[8];
+                load8(row + k0, xv);
+                s += ((xv[0] + xv[1]) + (xv[2] + xv[3])) + ((xv[4] + xv[5]) + (xv[6] + xv[7]));
+            }
         }
         mean = block_sum(s) / (float)k;
     }
     float ss = 0.f;
-    for (int i = threadIdx.x * 4; i < k; i += 1024) {
-        const float4 a = *reinterpret_cast<const float4*>(row + i);
-        const float c0 = a.x - mean, c1 = a.y - mean, c2 = a.z - mean, c3 = a.w - mean;
-        ss = fmaf(c0, c0, ss); ss = fmaf(c1, c1, ss); ss = fmaf(c2, c2, ss); ss = fmaf(c3, c3, ss);
+    if (have_first) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { const float c = xf[i] - mean; ss = fmaf(c, c, ss); }
+    }
+    for (int tile = warp + NORM_WARPS; tile < tiles; tile += NORM_WARPS) {
+        const int k0 = tile * 256 + lane * 8;
+        if (k0 < k) {
+            float xv[8];
+            load8(row + k0, xv);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) { const float c = xv[i] - mean; ss = fmaf(c, c, ss); }
+        }
     }
     const float inv = 1.0f / sqrtf(block_sum(ss) / (float)k + eps);
-    for (int tile = warp; tile < tiles; tile += 8) {
+    for (int tile = warp; tile < tiles; tile += NORM_WARPS) {
         const int k0 = tile * 256 + lane * 8;
         const bool live = k0 < k;
         float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
         if (live) {
             float xv[8], wv[8];
-            load8(row + k0, xv);
+            if (tile == warp) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) xv[i] = xf[i];
+            } else {
+                load8(row + k0, xv);
+            }
             load8(w + k0, wv);
 #pragma unroll
             for (int i = 0; i < 8; ++i) v[i] = __fmul_rn(__fmul_rn(xv[i] - mean, inv), wv[i]);
@@ -348,40 +373,47 @@ __global__ void __launch_bounds__(32) act_fn_quant_kernel(const float* __restric
 }
 
 // Merge of the split-K attention partials (see attention.cu) emitting the digits of the attention output row;
-// one warp per (256 columns of the [n_heads * hd] row, token). part: [tok][head][split][hd + 2].
-__global__ void __launch_bounds__(32) attn_merge_quant_kernel(const float* __restrict__ part, int n_heads, int n_splits, int hd,
-                                                              float* __restrict__ out, int ldo, QuantOut qo) {
+// one block per (256 columns of the [n_heads * hd] row, token), one thread per column, warp 0 converts the
+// merged 256 values to digits. part: [tok][head][split][hd + 2]. Splits without keys carry m = -inf, l = 0, o = 0.
+constexpr int MERGE_MAX_SPLITS = 32;
+__global__ void __launch_bounds__(256) attn_merge_quant_kernel(const float* __restrict__ part, int n_heads, int n_splits, int hd,
+                                                               float* __restrict__ out, int ldo, QuantOut qo) {
+    __shared__ __align__(16) float sv[256];
     pdl_wait();
     pdl_trigger();
-    const int lane = threadIdx.x, m = blockIdx.y, tile = blockIdx.x;
-    const int k0 = tile * 256 + lane * 8;
-    const bool live = k0 < qo.k;
-    float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    if (live) {
-        const int h = k0 / hd, e0 = k0 - h * hd;  // hd % 8 == 0: the 8 columns lie in one head
+    const int m = blockIdx.y, tile = blockIdx.x;
+    const int col = tile * 256 + threadIdx.x;
+    float v = 0.f;
+    if (col < qo.k) {
+        const int h = col / hd, e = col - h * hd;
         const float* src = part + ((int64_t)m * n_heads + h) * n_splits * (hd + 2);
+        float ms[MERGE_MAX_SPLITS];
         float M = -INFINITY;
-        for (int s = 0; s < n_splits; ++s) M = fmaxf(M, src[(int64_t)s * (hd + 2)]);
-        float L = 0.f;
-        for (int s = 0; s < n_splits; ++s) {
-            const float ms = src[(int64_t)s * (hd + 2)];
-            if (ms != -INFINITY) {
-                const float c = expf(ms - M);
-                L = fmaf(c, src[(int64_t)s * (hd + 2) + 1], L);
-                const float* o = src + (int64_t)s * (hd + 2) + 2 + e0;
 #pragma unroll
-                for (int i = 0; i < 8; ++i) v[i] = fmaf(c, o[i], v[i]);
+        for (int s = 0; s < MERGE_MAX_SPLITS; ++s) {
+            ms[s] = s < n_splits ? src[(int64_t)s * (hd + 2)] : -INFINITY;
+            M = fmaxf(M, ms[s]);
+        }
+        float L = 0.f;
+#pragma unroll
+        for (int s = 0; s < MERGE_MAX_SPLITS; ++s) {
+            if (s < n_splits) {
+                const float c = (ms[s] == -INFINITY) ? 0.f : expf(ms[s] - M);
+                L = fmaf(c, src[(int64_t)s * (hd + 2) + 1], L);
+                v = fmaf(c, src[(int64_t)s * (hd + 2) + 2 + e], v);
             }
         }
-        const float inv = (L == 0.f) ? 0.f : 1.0f / L;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) v[i] *= inv;
-        if (out) {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) out[(int64_t)m * ldo + k0 + i] = v[i];
-        }
+        v *= (L == 0.f) ? 0.f : 1.0f / L;
+        if (out) out[(int64_t)m * ldo + col] = v;
     }
-    quantize_chunk(v, live, lane, tile, m, qo);
+    sv[threadIdx.x] = v;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        const int lane = threadIdx.x;
+        float w[8];
+        load8(sv + lane * 8, w);
+        quantize_chunk(w, tile * 256 + lane * 8 < qo.k, lane, tile, m, qo);
+    }
 }
 
 void imma_plan(ImmaArgs& a, const ActWorkspace& ws) {
@@ -403,8 +435,8 @@ cudaError_t launch_act_quant(const float* x, int ldx, const ImmaArgs& a, cudaStr
 cudaError_t launch_norm_quant(const float* x, int ldx, const float* w, const float* b, bool layer_norm, float eps, float* y, int ldy,
                               const ImmaArgs& a, cudaStream_t st) {
     if (a.m <= 0) return cudaSuccess;
-    cudaError_t le = layer_norm ? launch_pdl(norm_quant_kernel<true>, dim3(a.m), dim3(256), 0, st, x, ldx, w, b, eps, y, ldy, quant_out(a))
-                                : launch_pdl(norm_quant_kernel<false>, dim3(a.m), dim3(256), 0, st, x, ldx, w, (const float*)nullptr, eps, y,
+    cudaError_t le = layer_norm ? launch_pdl(norm_quant_kernel<true>, dim3(a.m), dim3(NORM_WARPS * 32), 0, st, x, ldx, w, b, eps, y, ldy, quant_out(a))
+                                : launch_pdl(norm_quant_kernel<false>, dim3(a.m), dim3(NORM_WARPS * 32), 0, st, x, ldx, w, (const float*)nullptr, eps, y,
                                              ldy, quant_out(a));
     if (le != cudaSuccess) return le;
     return count_launch_and_check();
@@ -420,7 +452,8 @@ cudaError_t launch_act_fn_quant(const float* gu, int ld, int ffn, int act, const
 cudaError_t launch_attn_merge_quant(const float* part, int n_heads, int n_splits, int hd, float* out, int ldo, const ImmaArgs& a,
                                     cudaStream_t st) {
     if (a.m <= 0) return cudaSuccess;
-    cudaError_t le = launch_pdl(attn_merge_quant_kernel, dim3(a.kp / 256, a.m), dim3(32), 0, st, part, n_heads, n_splits, hd, out, ldo,
+    if (n_splits > MERGE_MAX_SPLITS) return cudaErrorInvalidValue;
+    cudaError_t le = launch_pdl(attn_merge_quant_kernel, dim3(a.kp / 256, a.m), dim3(256), 0, st, part, n_heads, n_splits, hd, out, ldo,
                                 quant_out(a));
     if (le != cudaSuccess) return le;
     return count_launch_and_check();
