@@ -32,6 +32,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 MODEL = "llama8b"
+NCU_TRAFFIC_RATIO = 1.000  # dram bytes / algorithmic bytes of the GEMV kernel, from the committed ncu summary
 PROMPT = 128
 CPU_PROMPT = 4
 
@@ -285,9 +286,13 @@ def main() -> None:
                     "d2h_bytes_per_step": cfg["vocab"] * 4, "api": "ForwardEngine.forward_logits (full f32 logits to host)"},
             "gpu_launches": int(launches),
             "clocks": clocks,
-            "roofline": {"bound": "hbm", "kernel": "gemv_kernel (dequant-fused GEMV, M=1)", "achieved": achieved,
+            "roofline": {"bound": "hbm", "kernel": "gemv_imma_kernel<1> (dequant-fused tensor-core GEMV, M=1)", "achieved": achieved,
                          "peak": peaks["hbm_gbs"], "peak_source": peak_src, "unit": "GB/s",
-                         "frac": (achieved / peaks["hbm_gbs"]) if achieved else None, "traffic": None,
+                         "frac": (achieved / peaks["hbm_gbs"]) if achieved else None,
+                         # DRAM bytes per launch: ncu read+write on the 14336x4096 Q4_K and 4096x14336 Q6_K launches is
+                         # 0.999x / 1.000x their algorithmic bytes (profiles/gemv_imma_kernel_m1.md), scaled to the
+                         # average launch of the step
+                         "traffic": NCU_TRAFFIC_RATIO * wbytes / max(gemv_n / P, 1), "traffic_source": "ncu, scaled by bytes",
                          "algorithmic_bytes_per_step": wbytes, "launches_per_step": gemv_n / P,
                          "avg_launch_us": 1000.0 * gemv_ms / max(gemv_n, 1)},
             "step_roofline": {"bytes_per_step": wbytes + kv_bytes, "ideal_ms_at_8TBs": (wbytes + kv_bytes) / 8e12 * 1e3,
