@@ -136,6 +136,25 @@ int32_t sp_cuda_engine_finalize(SpEngine* e);
 int32_t sp_cuda_engine_from_gguf(const char* path, int32_t device, int32_t max_ctx, int32_t max_batch, SpEngine** out);
 int32_t sp_cuda_engine_desc(const SpEngine* e, SpModelDesc* out);
 void sp_cuda_engine_destroy(SpEngine* e);
+/* Tensor parallelism (one process per GPU; Llama/Qwen block only). An engine created with tp_size > 1 keeps, of every
+ * tensor handed to sp_cuda_engine_set_tensor in FULL, only its rank's slice: rows of q/k/v/gate/up and of lm_head
+ * (vocab / tp_size rows), columns of o_proj / down_proj on block boundaries; norms and the embedding table are
+ * replicated. After finalize every rank exports the CUDA IPC handle of its communication block (SP_TP_HANDLE_BYTES
+ * bytes), the caller gathers the handles of all ranks in rank order (any transport) and passes them to
+ * sp_cuda_engine_tp_connect on every rank. Column-split products are summed by pushing partial rows into every rank's
+ * block over NVLink from the GEMV epilogue, with bounded waits (SP_ERR_COMM when a peer does not arrive). All ranks must
+ * then make the same calls in the same order. Logit outputs hold this rank's vocabulary slice only
+ * (sp_cuda_engine_vocab_local: its size and first token id); argmax outputs are global token ids on every rank. */
+#define SP_TP_HANDLE_BYTES 64
+int32_t sp_cuda_engine_tp_handle(SpEngine* e, void* out, size_t cap);
+int32_t sp_cuda_engine_tp_connect(SpEngine* e, const void* handles, int32_t n_ranks);
+int32_t sp_cuda_engine_vocab_local(const SpEngine* e, int32_t* rows, int32_t* first);
+/* The slice rank `rank` of `size` keeps of one full tensor (host only, no device needed): writes the slice to out
+ * (may be NULL to query sizes), its dims to out_dims[ndim] and its byte size to *out_bytes. Replicated tensors come
+ * back whole. vocab bounds the rows of lm_head.weight. */
+int32_t sp_cuda_tp_shard(const char* hf_name, int32_t dtype, const int64_t* dims, int32_t ndim, const void* bytes, size_t nbytes,
+                         int32_t rank, int32_t size, int64_t vocab, void* out, size_t out_cap, int64_t* out_dims,
+                         size_t* out_bytes);
 /* Launch on this cudaStream_t instead of the engine's own stream (NULL restores it). */
 int32_t sp_cuda_engine_set_stream(SpEngine* e, void* stream);
 

@@ -14,6 +14,7 @@ LIB_PATH = os.path.join(HERE, "libsapient_cuda.so")
 # status codes of include/sapient_cuda.h
 SP_OK, SP_ERR_SHAPE, SP_ERR_DTYPE, SP_ERR_OOM, SP_ERR_CUDA, SP_ERR_KV_FULL = 0, 1, 2, 3, 4, 5
 SP_ERR_COMM, SP_ERR_ARG, SP_ERR_VOCAB, SP_ERR_STATE, SP_ERR_IO = 6, 7, 8, 9, 10
+SP_TP_HANDLE_BYTES = 64  # sizeof(cudaIpcMemHandle_t)
 
 
 class SapientCudaError(RuntimeError):
@@ -51,6 +52,10 @@ SIGNATURES = {
     "sp_cuda_attention": (_i32, [_i32, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp]),
     "sp_cuda_attention_paged_static": (_i32, [_i32, _vp, _i32, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _i32, _i32,
                                               _i32, _i32, _vp]),
+    "sp_cuda_engine_tp_handle": (_i32, [_vp, _vp, C.c_size_t]),
+    "sp_cuda_engine_tp_connect": (_i32, [_vp, _vp, _i32]),
+    "sp_cuda_engine_vocab_local": (_i32, [_vp, _vp, _vp]),
+    "sp_cuda_tp_shard": (_i32, [C.c_char_p, _i32, _vp, _i32, _vp, C.c_size_t, _i32, _i32, _i64, _vp, C.c_size_t, _vp, _vp]),
     "sp_cuda_silu": (_i32, [_i32, _vp, _i64, _vp]),
     "sp_cuda_gelu": (_i32, [_i32, _vp, _i64, _vp]),
     "sp_cuda_add": (_i32, [_i32, _vp, _vp, _i64, _vp]),

@@ -123,6 +123,56 @@ int32_t sp_cuda_device_count(void) {
 
 uint64_t sp_cuda_launch_count(void) { return launch_count(); }
 
+int32_t sp_cuda_engine_tp_handle(SpEngine* e, void* out, size_t cap) {
+    API_BEGIN
+    if (!e) { set_error("null engine"); return SP_ERR_ARG; }
+    return e->e->tp_handle(out, cap);
+    API_END
+}
+
+int32_t sp_cuda_engine_tp_connect(SpEngine* e, const void* handles, int32_t n_ranks) {
+    API_BEGIN
+    if (!e) { set_error("null engine"); return SP_ERR_ARG; }
+    return e->e->tp_connect(handles, n_ranks);
+    API_END
+}
+
+int32_t sp_cuda_engine_vocab_local(const SpEngine* e, int32_t* rows, int32_t* first) {
+    API_BEGIN
+    if (!e || !rows) { set_error("null argument"); return SP_ERR_ARG; }
+    *rows = e->e->vocab_local();
+    if (first) *first = e->e->d.tp_rank * e->e->vocab_local();
+    return SP_OK;
+    API_END
+}
+
+int32_t sp_cuda_tp_shard(const char* hf_name, int32_t dtype, const int64_t* dims, int32_t ndim, const void* bytes, size_t nbytes,
+                         int32_t rank, int32_t size, int64_t vocab, void* out, size_t out_cap, int64_t* out_dims, size_t* out_bytes) {
+    API_BEGIN
+    if (!hf_name || !dims || !bytes || !out_dims || !out_bytes || ndim < 1 || ndim > 2 || size < 1 || rank < 0 || rank >= size) {
+        set_error("tp_shard: bad argument");
+        return SP_ERR_ARG;
+    }
+    const int bb = block_bytes(dtype), be = block_elems(dtype);
+    if (bb == 0) { set_error("unsupported dtype"); return SP_ERR_DTYPE; }
+    int64_t numel = 1;
+    for (int i = 0; i < ndim; ++i) numel *= dims[i];
+    if (dims[ndim - 1] % be != 0 || (size_t)(numel / be * bb) != nbytes) { set_error("byte size does not match dtype and shape"); return SP_ERR_SHAPE; }
+    std::vector<uint8_t> sh;
+    std::vector<int64_t> sd;
+    bool sharded = false;
+    const int st = tp_shard_tensor(hf_name, dtype, dims, ndim, (const uint8_t*)bytes, rank, size, vocab, sh, sd, sharded);
+    if (st != SP_OK) return st;
+    for (int i = 0; i < ndim; ++i) out_dims[i] = sd[i];
+    *out_bytes = sharded ? sh.size() : nbytes;
+    if (out) {
+        if (out_cap < *out_bytes) { set_error("tp_shard: output buffer too small"); return SP_ERR_ARG; }
+        std::memcpy(out, sharded ? sh.data() : (const uint8_t*)bytes, *out_bytes);
+    }
+    return SP_OK;
+    API_END
+}
+
 int32_t sp_cuda_set_gemv_path(int32_t path) {
     if (path < 0 || path > 3) { set_error("gemv path must be 0..3"); return SP_ERR_ARG; }
     g_gemv_path.store(path == 1 ? 1 : 0);
@@ -432,7 +482,7 @@ int32_t sp_cuda_engine_from_gguf(const char* path, int32_t device, int32_t max_c
 
 int32_t sp_cuda_engine_desc(const SpEngine* e, SpModelDesc* out) {
     if (!e || !out) { set_error("null argument"); return SP_ERR_ARG; }
-    *out = e->e->d;
+    *out = e->e->g;  // as given at creation (under tensor parallelism the engine works on its shard of it)
     return SP_OK;
 }
 

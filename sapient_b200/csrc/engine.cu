@@ -39,6 +39,12 @@ Engine::Engine(const SpModelDesc& desc) : d(desc) {
     if (d.max_tokens <= 0) d.max_tokens = 256;
     if (d.tp_size <= 0) d.tp_size = 1;
     if (d.rotary_dim <= 0) d.rotary_dim = d.head_dim;
+    g = d;
+    if (d.tp_size > 1) {  // from here on d describes this rank's shard (validated in finalize)
+        d.n_heads /= d.tp_size;
+        d.n_kv_heads /= d.tp_size;
+        d.ffn /= d.tp_size;
+    }
     seq_len.assign(d.max_batch, 0);
 }
 
@@ -51,6 +57,7 @@ Engine::~Engine() {
     if (d_tokens_) cudaFree(d_tokens_);
     for (auto& kv : tensors_) { if (kv.second.d) cudaFree(kv.second.d); if (kv.second.tiled) cudaFree(kv.second.tiled); }
     ws_.release();
+    tp_release();
     if (att_scratch_) cudaFree(att_scratch_);
     for (void* p : owned_) cudaFree(p);
     void* bufs[] = {kv_.pool, d_page_table_, x_, h_, qkv_, attn_, gu_, mid_, sel_, logits_, trace_, d_ids_, d_argmax_,
@@ -75,17 +82,30 @@ int Engine::set_tensor(const char* name, int dtype, const int64_t* dims, int ndi
     const int64_t want = t.numel() / be * bb;
     if ((int64_t)nbytes != want) { set_error(std::string("byte size mismatch for ") + name); return SP_ERR_SHAPE; }
     std::string nm(name);
-    std::vector<uint8_t> conv;
+    std::vector<uint8_t> conv, shard;
     const uint8_t* src = (const uint8_t*)bytes;
+    if (d.tp_size > 1) {
+        if (d.tp_size > TP_MAX_RANKS || d.tp_rank < 0 || d.tp_rank >= d.tp_size) { set_error("bad tensor-parallel rank / size"); return SP_ERR_ARG; }
+        std::vector<int64_t> sd;
+        bool sharded = false;
+        const int st = tp_shard_tensor(nm, dtype, dims, ndim, src, d.tp_rank, d.tp_size, d.vocab, shard, sd, sharded);
+        if (st != SP_OK) return st;
+        if (sharded) {
+            t.dims = sd;
+            src = shard.data();
+            nbytes = shard.size();
+        }
+    }
+    const int64_t inner_l = t.dims.back();
     const bool skip = nm.find("norm") != std::string::npos || nm.find("bias") != std::string::npos ||
                       nm.find("embed") != std::string::npos || nm.find("lm_head") != std::string::npos;
     if (ndim == 2 && !skip && (dtype == T_F16 || dtype == T_BF16) && t.numel() >= 32 && t.numel() % 32 == 0 &&
-        inner % 32 == 0) {
+        inner_l % 32 == 0) {
         // online Q8_0 quantisation, block by block along rows
         const int64_t n = t.numel();
         conv.resize((size_t)(n / 32 * 34));
         float tmp[32];
-        const uint16_t* h = (const uint16_t*)bytes;
+        const uint16_t* h = (const uint16_t*)src;
         for (int64_t b = 0; b < n / 32; ++b) {
             for (int i = 0; i < 32; ++i) {
                 const uint16_t v = h[b * 32 + i];
@@ -159,6 +179,17 @@ int Engine::repack_weights() {
 int Engine::finalize() {
     if (finalized) return SP_OK;
     SP_CUDA_TRY(cudaSetDevice(d.device));
+    if (d.tp_size > 1) {
+        if (d.arch != 0) { set_error("tensor parallelism covers the Llama/Qwen block only"); return SP_ERR_ARG; }
+        if (g.n_heads % d.tp_size || g.n_kv_heads % d.tp_size || g.ffn % d.tp_size || g.vocab % d.tp_size ||
+            (g.vocab / d.tp_size) % 16 != 0) {
+            set_error("tensor parallel: heads, kv heads, ffn and vocab / 16 must divide by the rank count");
+            return SP_ERR_SHAPE;
+        }
+        if (d.max_tokens > 0 && std::min<int>(32, d.max_tokens) > TP_ARGMAX_ROWS) { set_error("internal: logit rows"); return SP_ERR_STATE; }
+    }
+    vocab_l_ = d.vocab / d.tp_size;
+    vocab_off_ = d.tp_rank * vocab_l_;
     if (d.n_layers <= 0 || d.hidden <= 0 || d.n_heads <= 0 || d.n_kv_heads <= 0 || d.head_dim <= 0 || d.vocab <= 0 ||
         d.max_ctx <= 0 || d.n_heads % d.n_kv_heads != 0 || d.head_dim % 2 != 0 || d.head_dim > 256 ||
         d.rotary_dim % 2 != 0 || d.rotary_dim > d.head_dim || d.hidden % 4 != 0 || d.ffn % 4 != 0) {
@@ -182,7 +213,8 @@ int Engine::finalize() {
     }
     lm_head_ = find("lm_head.weight");  // tied fallback: crates/sapient-models/src/weights.rs:88-109
     if (!lm_head_) lm_head_ = embed_;
-    if (lm_head_->dims.size() != 2 || lm_head_->dims[1] != hid || lm_head_->dims[0] < d.vocab) {
+    if (d.tp_size > 1 && lm_head_ == embed_) { set_error("tensor parallel: tied output head is not supported"); return SP_ERR_ARG; }
+    if (lm_head_->dims.size() != 2 || lm_head_->dims[1] != hid || lm_head_->dims[0] < vocab_l_) {
         set_error("mis-shaped lm_head.weight");
         return SP_ERR_STATE;
     }
@@ -248,7 +280,7 @@ int Engine::finalize() {
     SP_CUDA_TRY(cudaMalloc((void**)&sel_, T * hid * 4));
     SP_CUDA_TRY(cudaMalloc((void**)&att_scratch_, attention_scratch_floats(ATT_SPLIT_TOKENS, H, ATT_SPLITS, hd) * 4));
     logit_rows_ = std::min<int>(32, d.max_tokens);
-    SP_CUDA_TRY(cudaMalloc((void**)&logits_, (size_t)logit_rows_ * d.vocab * 4));
+    SP_CUDA_TRY(cudaMalloc((void**)&logits_, (size_t)logit_rows_ * vocab_l_ * 4));
     SP_CUDA_TRY(cudaMalloc((void**)&d_ids_, T * 4));
     SP_CUDA_TRY(cudaMalloc((void**)&d_argmax_, T * 4));
     SP_CUDA_TRY(cudaMalloc((void**)&d_tok_slot_, T * 4));
@@ -256,7 +288,11 @@ int Engine::finalize() {
     SP_CUDA_TRY(cudaMallocHost((void**)&p_ids_, T * 4));
     SP_CUDA_TRY(cudaMallocHost((void**)&p_slot_, T * 4));
     SP_CUDA_TRY(cudaMallocHost((void**)&p_pos_, T * 4));
-    SP_CUDA_TRY(cudaMallocHost((void**)&p_logits_, (size_t)logit_rows_ * d.vocab * 4));
+    SP_CUDA_TRY(cudaMallocHost((void**)&p_logits_, (size_t)logit_rows_ * vocab_l_ * 4));
+    {
+        const int st = tp_alloc();
+        if (st != SP_OK) return st;
+    }
     SP_CUDA_TRY(cudaMallocHost((void**)&p_argmax_, T * 4));
     // RoPE table: theta = pos / base^(2i/rotary_dim) in f32, as crates/sapient-backends/cpu/src/kernels/rope.rs:40-43,118-121.
     const int half = d.rotary_dim / 2;

@@ -13,6 +13,7 @@
 
 #include "../../include/sapient_cuda.h"
 #include "kernels.h"
+#include "tp.cuh"
 
 namespace sp {
 
@@ -27,6 +28,10 @@ const char* get_error();
             return _e == cudaErrorMemoryAllocation ? SP_ERR_OOM : SP_ERR_CUDA;                     \
         }                                                                                          \
     } while (0)
+
+// The slice of a full tensor that rank `rank` of `size` keeps (tp.cu); sharded == false: the tensor is replicated.
+int tp_shard_tensor(const std::string& name, int dtype, const int64_t* dims, int ndim, const uint8_t* bytes, int rank, int size,
+                    int64_t vocab, std::vector<uint8_t>& out, std::vector<int64_t>& out_dims, bool& sharded);
 
 struct DevTensor {
     int dtype = 0;
@@ -71,7 +76,13 @@ class Engine {
     int profile_read(double* ms, uint64_t* launches, int cap);
     void profile_reset();
 
-    SpModelDesc d;
+    // Tensor parallelism (tp.cuh): d holds this rank's LOCAL head / ffn counts, g the description as given.
+    int tp_handle(void* out, size_t cap);           // CUDA IPC handle of this rank's communication block
+    int tp_connect(const void* handles, int n);     // map every rank's block (handles in rank order)
+    int tp_check();                                 // SP_ERR_COMM if a wait on a peer gave up
+    int vocab_local() const { return vocab_l_; }
+
+    SpModelDesc d, g;
     cudaStream_t own_stream = nullptr, stream = nullptr;
     bool finalized = false;
     bool trace_on = false;
@@ -94,9 +105,21 @@ class Engine {
     const float* find_f32(const std::string& name, int64_t n);
     int layer_llama(const LayerW& w, int l, int T);
     int layer_phi(const LayerW& w, int l, int T);
+    // tp_sum: the matrix is column-split over the ranks; y0 (= res) receives res + the sum of all ranks' products
     int gemv(const float* x, int ldx, int m, int k, const DevTensor* w0, const float* b0, float* y0, int ldy0,
              const DevTensor* w1 = nullptr, const float* b1 = nullptr, float* y1 = nullptr, const DevTensor* w2 = nullptr,
-             const float* b2 = nullptr, float* y2 = nullptr, const float* res = nullptr, const ImmaArgs* pre = nullptr);
+             const float* b2 = nullptr, float* y2 = nullptr, const float* res = nullptr, const ImmaArgs* pre = nullptr,
+             bool tp_sum = false);
+    size_t tp_block_bytes() const;
+    int tp_alloc();
+    void tp_release();
+    uint8_t* tp_block_ = nullptr;   // this rank's communication block
+    uint8_t* tp_state_ = nullptr;   // sequence counters, block counter, timeout flag
+    TpDev* d_tp_ = nullptr;         // device copy of the peer table
+    uint8_t* tp_peer_[TP_MAX_RANKS] = {};
+    bool tp_connected_ = false;
+    int vocab_l_ = 0, vocab_off_ = 0;
+    DevTensor head_view_;           // lm_head restricted to the rows this engine computes
     bool plan_digits(int m, int k, ImmaArgs& ia);
     int attention_and_oproj(const LayerW& w, int l, int T);
 

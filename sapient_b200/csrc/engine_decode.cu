@@ -205,7 +205,8 @@ int Engine::decode_greedy(const uint32_t* first_ids, const int32_t* slots, int b
         SP_CUDA_TRY(cudaMemcpyAsync(tmp.data(), d_tokens_, need_tok * 4, cudaMemcpyDeviceToHost, stream));
         SP_CUDA_TRY(cudaStreamSynchronize(stream));
         std::memcpy(tokens_out, tmp.data(), need_tok * 4);
-        return prof_flush();
+        SP_TRY(prof_flush());
+        return tp_check();
     }
     return SP_OK;  // asynchronous: the caller synchronises the stream
 }

@@ -78,13 +78,18 @@ int Engine::enqueue_layers(int T) {
 // lm_head over rows [r0, r0+rc) of the normalised selection sel_, plus their argmax.
 int Engine::enqueue_head(int rows_from, int r0, int rc, const ImmaArgs* pre) {
     (void)rows_from;
-    const int V = d.vocab, hid = d.hidden;
-    // lm_head rows beyond the vocabulary (if the table is larger) are not computed: n = V
+    const int V = vocab_l_, hid = d.hidden;
+    // lm_head rows beyond the vocabulary (if the table is larger) are not computed: n = V (this rank's slice under
+    // tensor parallelism)
     DevTensor head = *lm_head_;
     head.dims[0] = V;
     SP_TRY(gemv(sel_ + (size_t)r0 * hid, hid, rc, hid, &head, lm_bias_, logits_, V, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr,
                 nullptr, pre));
     SP_LAUNCH(F_ARGMAX, launch_argmax(logits_, rc, V, V, d_argmax_, stream));
+    if (d.tp_size > 1) {
+        if (!tp_connected_) { set_error("tensor-parallel engine used before tp_connect"); return SP_ERR_STATE; }
+        SP_LAUNCH(F_ARGMAX, launch_tp_argmax(logits_, V, rc, vocab_off_, d_argmax_, d_tp_, stream));
+    }
     return SP_OK;
 }
 
@@ -114,7 +119,7 @@ int Engine::run_chunk(const uint32_t* ids, const int32_t* slots, int T, int rows
         SP_CUDA_TRY(cudaMemcpyAsync(d_page_table_, h_page_table_.data(), h_page_table_.size() * 4, cudaMemcpyHostToDevice, stream));
         pages_dirty_ = false;
     }
-    const int hid = d.hidden, V = d.vocab;
+    const int hid = d.hidden, V = vocab_l_;
     if (trace_on && !trace_) SP_CUDA_TRY(cudaMalloc((void**)&trace_, (size_t)d.n_layers * d.max_tokens * hid * 4));
     const int rows = T - rows_from;
     const bool want = rows > 0 && (logits_out || argmax_out);
@@ -126,7 +131,8 @@ int Engine::run_chunk(const uint32_t* ids, const int32_t* slots, int T, int rows
         SP_CUDA_TRY(cudaStreamSynchronize(stream));
         if (logits_out) std::memcpy(logits_out, p_logits_, (size_t)T * V * 4);
         if (argmax_out) std::memcpy(argmax_out, p_argmax_, (size_t)T * 4);
-        return prof_flush();
+        SP_TRY(prof_flush());
+        return tp_check();
     }
     SP_TRY(enqueue_layers(T));
     if (want) {
@@ -144,7 +150,8 @@ int Engine::run_chunk(const uint32_t* ids, const int32_t* slots, int T, int rows
         }
     }
     SP_CUDA_TRY(cudaStreamSynchronize(stream));
-    return prof_flush();
+    SP_TRY(prof_flush());
+    return tp_check();
 }
 
 int Engine::forward(const uint32_t* ids, const int32_t* slots, int64_t n, bool want_all, float* logits_out,
@@ -182,7 +189,7 @@ int Engine::forward(const uint32_t* ids, const int32_t* slots, int64_t n, bool w
         uint32_t* ao = nullptr;
         if (want_all) {
             rows_from = 0;
-            lo = logits_out ? logits_out + (size_t)c0 * d.vocab : nullptr;
+            lo = logits_out ? logits_out + (size_t)c0 * vocab_l_ : nullptr;
             ao = argmax_out ? argmax_out + c0 : nullptr;
         } else {
             rows_from = last_chunk ? T - 1 : T;

@@ -43,7 +43,9 @@ bool Engine::plan_digits(int m, int k, ImmaArgs& ia) {
 // pre != null: the digits of x are already in the workspace (planned as *pre).
 int Engine::gemv(const float* x, int ldx, int m, int k, const DevTensor* w0, const float* b0, float* y0, int ldy0,
                  const DevTensor* w1, const float* b1, float* y1, const DevTensor* w2, const float* b2, float* y2,
-                 const float* res, const ImmaArgs* pre) {
+                 const float* res, const ImmaArgs* pre, bool tp_sum) {
+    tp_sum = tp_sum && d.tp_size > 1;
+    if (tp_sum && !tp_connected_) { set_error("tensor-parallel engine used before tp_connect"); return SP_ERR_STATE; }
     const DevTensor* ws[3] = {w0, w1, w2};
     const float* bs[3] = {b0, b1, b2};
     float* ys[3] = {y0, y1, y2};
@@ -55,8 +57,10 @@ int Engine::gemv(const float* x, int ldx, int m, int k, const DevTensor* w0, con
             ImmaArgs ia{};
             if (pre) ia = *pre;
             ia.k = k; ia.m = std::min(16, m - m0);
-            ia.res = res ? res + (size_t)m0 * ldy0 : nullptr;
+            ia.res = (res && !tp_sum) ? res + (size_t)m0 * ldy0 : nullptr;
             ia.ldres = ldy0;
+            ia.tp = tp_sum ? d_tp_ : nullptr;
+            ia.tp_row0 = m0;
             ia.nseg = 0;
             for (int i = 0; i < 3 && ws[i]; ++i) {
                 ImmaSeg& sgm = ia.seg[i];
@@ -70,8 +74,11 @@ int Engine::gemv(const float* x, int ldx, int m, int k, const DevTensor* w0, con
             }
             SP_LAUNCH(F_GEMV, launch_gemv_imma(ia, stream));
         }
+        // every rank now holds all ranks' partial rows: y0 = res + their sum (y0 and res are the residual stream)
+        if (tp_sum) SP_LAUNCH(F_ELEM, launch_tp_reduce(y0, ldy0, m, ldy0, d_tp_, stream));
         return SP_OK;
     }
+    if (tp_sum) { set_error("tensor parallel: column-split matrix without tiles"); return SP_ERR_STATE; }
     if (pre) { set_error("internal: pre-quantised input for a weight without tiles"); return SP_ERR_STATE; }
     if (w1 && (w0->tiled || w1->tiled || (w2 && w2->tiled))) {
         // mixed layouts: one launch per matrix
@@ -107,11 +114,11 @@ int Engine::attention_and_oproj(const LayerW& w, int l, int T) {
     if (splits > 1 && !trace_on && all_tiled(w.o) && plan_digits(T, H * hd, ia)) {
         SP_LAUNCH(F_ATTN, launch_attention_split(qkv_, qkv_ld, T, H, d_tok_slot_, d_tok_pos_, kv_, l, scale, splits, att_scratch_, stream));
         SP_LAUNCH(F_ATTN, launch_attn_merge_quant(att_scratch_, H, splits, hd, nullptr, 0, ia, stream));
-        return gemv(attn_, H * hd, T, H * hd, w.o, w.ob, x_, hid, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, x_, &ia);
+        return gemv(attn_, H * hd, T, H * hd, w.o, w.ob, x_, hid, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, x_, &ia, true);
     }
     SP_LAUNCH(F_ATTN, launch_attention(qkv_, qkv_ld, attn_, H * hd, T, H, d_tok_slot_, d_tok_pos_, kv_, l, scale, splits, att_scratch_,
                                        stream));
-    return gemv(attn_, H * hd, T, H * hd, w.o, w.ob, x_, hid, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, x_);
+    return gemv(attn_, H * hd, T, H * hd, w.o, w.ob, x_, hid, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, x_, nullptr, true);
 }
 
 int Engine::layer_llama(const LayerW& w, int l, int T) {
@@ -138,10 +145,10 @@ int Engine::layer_llama(const LayerW& w, int l, int T) {
     }
     if (all_tiled(w.down) && plan_digits(T, ffn, ia)) {
         SP_LAUNCH(F_ELEM, launch_act_fn_quant(gu_, 2 * ffn, ffn, 0, ia, stream));
-        SP_TRY(gemv(mid_, ffn, T, ffn, w.down, nullptr, x_, hid, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, x_, &ia));
+        SP_TRY(gemv(mid_, ffn, T, ffn, w.down, nullptr, x_, hid, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, x_, &ia, true));
     } else {
         SP_LAUNCH(F_ELEM, launch_swiglu(gu_, 2 * ffn, ffn, T, mid_, stream));
-        SP_TRY(gemv(mid_, ffn, T, ffn, w.down, nullptr, x_, hid, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, x_));
+        SP_TRY(gemv(mid_, ffn, T, ffn, w.down, nullptr, x_, hid, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, x_, nullptr, true));
     }
     return SP_OK;
 }

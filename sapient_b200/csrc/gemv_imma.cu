@@ -18,6 +18,7 @@
 #include "kernels.h"
 #include "pdl.cuh"
 #include "sp_common.cuh"
+#include "tp.cuh"
 
 namespace sp {
 
@@ -761,6 +762,14 @@ __device__ __forceinline__ void reduce_store(const ImmaArgs& a, const ImmaSeg& s
             for (int w = 0; w < WARPS; ++w) v += red[((w * NT + nt) * 4 + e) * 32 + ln];
         }
         if (sg.bias) v += sg.bias[row];
+        if (a.tp) {
+            // partial sum of a column-split matrix: straight into every rank's receive area (peer stores)
+            const TpDev& tp = *a.tp;
+            const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(tp.ar_seq) + 1u;
+            const int64_t off = (int64_t)(a.tp_row0 + m) * sg.ldy + row;
+            for (int p = 0; p < tp.size; ++p) tp_recv(tp, p, (int)(epoch & 1u), tp.rank)[off] = v;
+            continue;
+        }
         if (first_seg && a.res) v += a.res[(int64_t)m * a.ldres + row];
         sg.y[(int64_t)m * sg.ldy + row] = v;
     }
@@ -1084,7 +1093,7 @@ cudaError_t launch_gemv_imma(const ImmaArgs& a, cudaStream_t st) {
     const int nt = a.ncp / 8;
     // The persistent TMA-streaming kernel is opt-in: measured on B200 it trails the per-tile-row kernel
     // (132 vs 81 us on a 128256 x 4096 Q4_K matrix), so the default is the latter.
-    const StreamPlan p = g_imma_kernel.load() == 3 ? plan_stream(a) : StreamPlan{};
+    const StreamPlan p = (g_imma_kernel.load() == 3 && !a.tp) ? plan_stream(a) : StreamPlan{};
     if (p.total > 0) {
         if (g_sm_count == 0) {
             int dev = 0;

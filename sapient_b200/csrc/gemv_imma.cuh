@@ -63,7 +63,10 @@ struct ImmaArgs {
     const int8_t* xs16d;
     const float* res;       // optional residual for segment 0 (may alias its y)
     int ldres;
-    int pad_;
+    // Tensor-parallel column-split matrix (tp != null): segment 0's outputs are not stored to y but pushed, as partial
+    // sums, into the receive area of every rank (tp.cuh); tp_row0 = activation row of this launch's row 0.
+    int tp_row0;
+    const struct TpDev* tp;
 };
 
 }  // namespace sp

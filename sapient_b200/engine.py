@@ -33,11 +33,15 @@ class ForwardEngine:
         self._h = handle
         self.desc = desc
         self.vocab = desc.vocab
+        rows, first = C.c_int32(), C.c_int32()
+        check(lib().sp_cuda_engine_vocab_local(handle, C.byref(rows), C.byref(first)))
+        self.vocab_local, self.vocab_first = int(rows.value), int(first.value)  # this rank's slice of the logits
+        self._tp_group = None
 
     # ── construction ────────────────────────────────────────────────────────
     @classmethod
     def from_weights(cls, cfg: dict, weights: dict, device: int = 0, max_batch: int = 1, max_tokens: int = 256,
-                     kv_pages: int = 0) -> "ForwardEngine":
+                     kv_pages: int = 0, tp_rank: int = 0, tp_size: int = 1) -> "ForwardEngine":
         """cfg: arch ('llama'|'qwen2'|'phi2'), n_layers, hidden, n_heads, n_kv_heads, head_dim, ffn, vocab,
         max_ctx, rotary_dim (optional), norm_eps, rope_theta. weights: name -> (ggml dtype, dims, uint8 bytes)
         with HF names and [out, in] dims, as the reference's GGUF name map yields."""
@@ -47,7 +51,7 @@ class ForwardEngine:
         d.head_dim, d.ffn, d.vocab, d.max_ctx = cfg["head_dim"], cfg["ffn"], cfg["vocab"], cfg["max_ctx"]
         d.rotary_dim = cfg.get("rotary_dim") or cfg["head_dim"]
         d.norm_eps, d.rope_theta = cfg["norm_eps"], cfg["rope_theta"]
-        d.max_batch, d.max_tokens, d.device, d.tp_rank, d.tp_size, d.kv_pages = max_batch, max_tokens, device, 0, 1, kv_pages
+        d.max_batch, d.max_tokens, d.device, d.tp_rank, d.tp_size, d.kv_pages = max_batch, max_tokens, device, tp_rank, tp_size, kv_pages
         h = C.c_void_p()
         check(lib().sp_cuda_engine_create(C.byref(d), C.byref(h)))
         try:
@@ -82,30 +86,66 @@ class ForwardEngine:
         except Exception:
             pass
 
+    # ── tensor parallelism (one process per GPU) ────────────────────────────
+    def tp_handle(self) -> bytes:
+        """CUDA IPC handle of this rank's communication block (after finalize)."""
+        buf = (C.c_uint8 * _lib.SP_TP_HANDLE_BYTES)()
+        check(lib().sp_cuda_engine_tp_handle(self._h, buf, _lib.SP_TP_HANDLE_BYTES))
+        return bytes(buf)
+
+    def tp_connect(self, handles=None, group=None) -> None:
+        """Map every rank's communication block. Either pass the handles of all ranks in rank order, or a
+        torch.distributed process group (default group when both are None) over which they are gathered; with a
+        group, logit outputs are gathered to the full vocabulary as well."""
+        if handles is None:
+            import torch.distributed as dist
+
+            handles = [None] * dist.get_world_size(group)
+            dist.all_gather_object(handles, self.tp_handle(), group=group)
+            self._tp_group = group if group is not None else dist.group.WORLD
+        blob = b"".join(handles)
+        if len(blob) != self.desc.tp_size * _lib.SP_TP_HANDLE_BYTES:
+            raise SapientCudaError(_lib.SP_ERR_ARG, "tp_connect: one handle per rank expected")
+        arr = (C.c_uint8 * len(blob)).from_buffer_copy(blob)
+        check(lib().sp_cuda_engine_tp_connect(self._h, arr, self.desc.tp_size))
+
+    def _gather(self, local: np.ndarray) -> np.ndarray:
+        """Full-vocabulary logits from the ranks' slices (identity for a single-GPU engine or without a group)."""
+        if self.desc.tp_size <= 1 or self._tp_group is None:
+            return local
+        import torch
+        import torch.distributed as dist
+
+        dev = f"cuda:{self.desc.device}" if dist.get_backend(self._tp_group) == "nccl" else "cpu"
+        mine = torch.from_numpy(np.ascontiguousarray(local)).to(dev)
+        parts = [torch.empty_like(mine) for _ in range(self.desc.tp_size)]
+        dist.all_gather(parts, mine, group=self._tp_group)
+        return torch.cat(parts, dim=-1).cpu().numpy()
+
     # ── the reference's ForwardEngine surface ───────────────────────────────
     def forward_logits(self, input_ids, use_cache: bool = True) -> np.ndarray:
         ids = _ids(input_ids)
         if ids.size == 0:
             raise SapientCudaError(_lib.SP_ERR_ARG, "empty input")
-        out = np.empty(self.vocab, np.float32)
+        out = np.empty(self.vocab_local, np.float32)
         check(lib().sp_cuda_forward_logits(self._h, _p(ids), ids.size, int(use_cache), _p(out)))
-        return out
+        return self._gather(out)
 
     def forward_all_logits(self, input_ids) -> np.ndarray:
         ids = _ids(input_ids)
         if ids.size == 0:
             raise SapientCudaError(_lib.SP_ERR_ARG, "empty input")
-        out = np.empty((ids.size, self.vocab), np.float32)
+        out = np.empty((ids.size, self.vocab_local), np.float32)
         check(lib().sp_cuda_forward_all_logits(self._h, _p(ids), ids.size, _p(out)))
-        return out
+        return self._gather(out)
 
     def forward_all_logits_cached(self, input_ids) -> np.ndarray:
         ids = _ids(input_ids)
         if ids.size == 0:
             raise SapientCudaError(_lib.SP_ERR_ARG, "empty input")
-        out = np.empty((ids.size, self.vocab), np.float32)
+        out = np.empty((ids.size, self.vocab_local), np.float32)
         check(lib().sp_cuda_forward_all_logits_cached(self._h, _p(ids), ids.size, _p(out)))
-        return out
+        return self._gather(out)
 
     def reset_cache(self, slot: int = -1) -> None:
         check(lib().sp_cuda_reset_cache(self._h, slot))
@@ -136,7 +176,7 @@ class ForwardEngine:
         ids = _ids(input_ids)
         if ids.size == 0:
             raise SapientCudaError(_lib.SP_ERR_ARG, "empty input")
-        out = np.empty((ids.size, self.vocab) if all_positions else (self.vocab,), np.float32)
+        out = np.empty((ids.size, self.vocab_local) if all_positions else (self.vocab_local,), np.float32)
         check(lib().sp_cuda_forward_slot(self._h, slot, _p(ids), ids.size, int(all_positions), _p(out)))
         return out
 
@@ -145,7 +185,7 @@ class ForwardEngine:
         ids = _ids(input_ids)
         sl = np.ascontiguousarray(slots, dtype=np.int32).reshape(-1)
         assert ids.size == sl.size
-        logits = np.empty((ids.size, self.vocab), np.float32) if want_logits else None
+        logits = np.empty((ids.size, self.vocab_local), np.float32) if want_logits else None
         am = np.empty(ids.size, np.uint32) if want_argmax else None
         check(lib().sp_cuda_decode_batch(self._h, _p(ids), _p(sl), ids.size, _p(logits) if want_logits else None,
                                          _p(am) if want_argmax else None))

@@ -157,6 +157,9 @@ CONFIGS = {
     # tiny shapes for tests
     "tiny_llama": dict(arch="llama", n_layers=2, hidden=256, n_heads=4, n_kv_heads=2, head_dim=64, ffn=512,
                        vocab=320, norm_eps=1e-5, rope_theta=1e4, tied=False),
+    # splits over 2 ranks on 256-column block boundaries (o_proj K = 512, down_proj K = 1024)
+    "tiny_llama_tp": dict(arch="llama", n_layers=2, hidden=512, n_heads=8, n_kv_heads=2, head_dim=64, ffn=1024,
+                          vocab=320, norm_eps=1e-5, rope_theta=1e4, tied=False),
     "tiny_qwen": dict(arch="qwen2", n_layers=2, hidden=160, n_heads=5, n_kv_heads=1, head_dim=32, ffn=256,
                       vocab=200, norm_eps=1e-6, rope_theta=1e6, tied=True, qkv_bias=True),
     "tiny_phi2": dict(arch="phi2", n_layers=2, hidden=160, n_heads=4, n_kv_heads=4, head_dim=40, ffn=320,
