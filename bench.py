@@ -197,11 +197,18 @@ def main() -> None:
         raise SystemExit("bench.py needs a CUDA device: this backend has no CPU fallback")
     torch.cuda.set_device(local)
     if world > 1:
+        # NCCL prints its version banner on stdout at any debug level; stdout carries exactly one JSON line
+        os.environ.pop("NCCL_DEBUG", None)
+        if os.environ.get("SAPIENT_NCCL_DEBUG"):
+            os.environ["NCCL_DEBUG"] = os.environ["SAPIENT_NCCL_DEBUG"]
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
 
     cfg, W = build_weights(f"cuda:{local}")
     wbytes = step_weight_bytes(cfg, W)
-    eng = ForwardEngine.from_weights(cfg, W, device=local, max_batch=1, max_tokens=256)
+    # N > 1: ONE sequence, the model split over the N GPUs (tensor parallel, strong scaling)
+    eng = ForwardEngine.from_weights(cfg, W, device=local, max_batch=1, max_tokens=256, tp_rank=rank, tp_size=world)
+    if world > 1:
+        eng.tp_connect()  # IPC handles over the default process group
     # a real (non-default) stream: CUDA events below are recorded on the stream the kernels run on
     stream = torch.cuda.Stream(device=local)
     torch.cuda.set_stream(stream)
@@ -238,7 +245,7 @@ def main() -> None:
     if args.quick:  # launch-list / profiler runs: prefill + warm-up + timed steps only
         sampler.stop()
         if rank == 0:
-            print(json.dumps({"quick": True, "ms_per_step": dev_ms / K, "value": world * K / (dev_ms / 1000.0),
+            print(json.dumps({"quick": True, "ms_per_step": dev_ms / K, "value": K / (dev_ms / 1000.0),
                               "gpu_launches": int(launches)}), flush=True)
         eng.close()
         return
@@ -262,9 +269,10 @@ def main() -> None:
 
     # ── per-family device time: each family's launches of one step replayed alone as a CUDA graph ──
     P = 20
-    fam_ms = {f: eng.time_families(f, 1, P) for f in eng.PROFILE_FAMILIES}
+    # (single GPU only: under tensor parallelism a subset would separate the producers of an exchange from its consumers)
+    fam_ms = {f: eng.time_families(f, 1, P) for f in eng.PROFILE_FAMILIES} if world == 1 else {}
     fam_ms["all"] = eng.time_families("all", 1, P)
-    gemv_ms = fam_ms["gemv"] * P
+    gemv_ms = fam_ms.get("gemv", 0.0) * P
     gemv_n = (4 * cfg["n_layers"] + 1) * P
     eng.truncate_cache(PROMPT)
 
@@ -275,14 +283,15 @@ def main() -> None:
 
     if rank == 0:
         peaks, peak_src = measured_peaks()
-        value = world * K / (dev_ms / 1000.0)
+        value = K / (dev_ms / 1000.0)  # one sequence whatever the GPU count
+        wbytes_gpu = wbytes / world
         kv_bytes = 2 * cfg["n_layers"] * cfg["n_kv_heads"] * cfg["head_dim"] * 2 * kv_ctx_mid
-        achieved = (wbytes / 1e9) / ((gemv_ms / P) / 1000.0) if gemv_ms > 0 else None
+        achieved = (wbytes_gpu / 1e9) / ((gemv_ms / P) / 1000.0) if gemv_ms > 0 else None  # per GPU
         line = {
             "metric": "decode_tokens_per_s", "value": value, "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": Wm,
-            "ms_per_step": dev_ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-            "data": "synthetic", "config": config_dict(cfg, world, "replicas"),
-            "e2e": {"value": world * K / (e2e_ms / 1000.0), "unit": "tok/s", "h2d_bytes_per_step": 12,
+            "ms_per_step": dev_ms / K, "higher_is_better": True, "scaling": "strong" if world > 1 else "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic", "config": config_dict(cfg, world, f"tp{world}" if world > 1 else "single"),
+            "e2e": {"value": K / (e2e_ms / 1000.0), "unit": "tok/s", "h2d_bytes_per_step": 12,
                     "d2h_bytes_per_step": cfg["vocab"] * 4, "api": "ForwardEngine.forward_logits (full f32 logits to host)"},
             "gpu_launches": int(launches),
             "clocks": clocks,
@@ -292,12 +301,13 @@ def main() -> None:
                          # DRAM bytes per launch: ncu read+write on the 14336x4096 Q4_K and 4096x14336 Q6_K launches is
                          # 0.999x / 1.000x their algorithmic bytes (profiles/gemv_imma_kernel_m1.md), scaled to the
                          # average launch of the step
-                         "traffic": NCU_TRAFFIC_RATIO * wbytes / max(gemv_n / P, 1), "traffic_source": "ncu, scaled by bytes",
-                         "algorithmic_bytes_per_step": wbytes, "launches_per_step": gemv_n / P,
-                         "avg_launch_us": 1000.0 * gemv_ms / max(gemv_n, 1)},
-            "step_roofline": {"bytes_per_step": wbytes + kv_bytes, "ideal_ms_at_8TBs": (wbytes + kv_bytes) / 8e12 * 1e3,
-                              "frac_of_8TBs": ((wbytes + kv_bytes) / 8e12 * 1e3) / (dev_ms / K),
-                              "frac_of_measured_peak": ((wbytes + kv_bytes) / (peaks["hbm_gbs"] * 1e9) * 1e3) / (dev_ms / K)},
+                         "traffic": NCU_TRAFFIC_RATIO * wbytes_gpu / max(gemv_n / P, 1), "traffic_source": "ncu, scaled by bytes",
+                         "algorithmic_bytes_per_step": wbytes_gpu, "launches_per_step": gemv_n / P,
+                         "avg_launch_us": (1000.0 * gemv_ms / max(gemv_n, 1)) if gemv_ms > 0 else None},
+            "step_roofline": {"bytes_per_step_per_gpu": (wbytes + kv_bytes) / world,
+                              "ideal_ms_at_8TBs": (wbytes + kv_bytes) / world / 8e12 * 1e3,
+                              "frac_of_8TBs": ((wbytes + kv_bytes) / world / 8e12 * 1e3) / (dev_ms / K),
+                              "frac_of_measured_peak": ((wbytes + kv_bytes) / world / (peaks["hbm_gbs"] * 1e9) * 1e3) / (dev_ms / K)},
             "family_ms_per_step": fam_ms,
         }
         if not args.no_cpu_baseline:

@@ -118,6 +118,9 @@ class Engine {
     TpDev* d_tp_ = nullptr;         // device copy of the peer table
     uint8_t* tp_peer_[TP_MAX_RANKS] = {};
     bool tp_connected_ = false;
+    bool tp_pending_ = false;       // partial rows have been pushed, x_ still lacks their sum
+    const TpDev* tp_take() { const TpDev* t = tp_pending_ ? d_tp_ : nullptr; tp_pending_ = false; return t; }
+    int tp_resolve(int T);          // stand-alone consumer when the next kernel is not the fused norm
     int vocab_l_ = 0, vocab_off_ = 0;
     DevTensor head_view_;           // lm_head restricted to the rows this engine computes
     bool plan_digits(int m, int k, ImmaArgs& ia);

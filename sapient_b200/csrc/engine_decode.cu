@@ -110,6 +110,11 @@ int Engine::launch_decode_step(int T) {
 int Engine::time_families(unsigned mask, int T, int reps, float* ms_per_step) {
     if (!finalized) { set_error("engine not finalised"); return SP_ERR_STATE; }
     if (T <= 0 || T > logit_rows_ || reps <= 0 || !ms_per_step) { set_error("time_families: bad argument"); return SP_ERR_ARG; }
+    if (d.tp_size > 1 && (mask & ((1u << F_COUNT) - 1)) != (1u << F_COUNT) - 1) {
+        // a subset would run the producers of an exchange without its consumers (or the reverse)
+        set_error("time_families: under tensor parallelism only the whole step can be timed");
+        return SP_ERR_ARG;
+    }
     SP_CUDA_TRY(cudaSetDevice(d.device));
     SP_CUDA_TRY(cudaStreamSynchronize(stream));
     const bool prof = profile_on, tr = trace_on;

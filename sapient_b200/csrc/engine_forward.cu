@@ -68,6 +68,7 @@ int Engine::enqueue_layers(int T) {
     SP_LAUNCH(F_EMBED, launch_embed(embed_->dtype, embed_->d, hid, d_ids_, T, x_, stream));
     for (int l = 0; l < d.n_layers; ++l) {
         SP_TRY(d.arch == 1 ? layer_phi(layers_[l], l, T) : layer_llama(layers_[l], l, T));
+        if (trace_on) SP_TRY(tp_resolve(T));
         if (trace_on)
             SP_CUDA_TRY(cudaMemcpyAsync(trace_ + (size_t)l * d.max_tokens * hid, x_, (size_t)T * hid * 4, cudaMemcpyDeviceToDevice, stream));
     }
@@ -98,9 +99,10 @@ int Engine::enqueue_decode_step(int T) {
     SP_TRY(enqueue_layers(T));
     ImmaArgs ia;
     if (lm_head_->tiled && plan_digits(T, hid, ia)) {
-        SP_LAUNCH(F_NORM, launch_norm_quant(x_, hid, final_w_, final_b_, d.arch == 1, d.norm_eps, nullptr, 0, ia, stream));
+        SP_LAUNCH(F_NORM, launch_norm_quant(x_, hid, final_w_, final_b_, d.arch == 1, d.norm_eps, nullptr, 0, ia, stream, tp_take()));
         return enqueue_head(0, 0, T, &ia);
     }
+    SP_TRY(tp_resolve(T));
     if (d.arch == 1) SP_LAUNCH(F_NORM, launch_layer_norm(x_, final_w_, final_b_, T, hid, d.norm_eps, sel_, stream));
     else SP_LAUNCH(F_NORM, launch_rms_norm(x_, final_w_, T, hid, d.norm_eps, sel_, stream));
     return enqueue_head(0, 0, T);
@@ -135,6 +137,7 @@ int Engine::run_chunk(const uint32_t* ids, const int32_t* slots, int T, int rows
         return tp_check();
     }
     SP_TRY(enqueue_layers(T));
+    SP_TRY(tp_resolve(T));
     if (want) {
         const float* src = x_ + (size_t)rows_from * hid;
         if (d.arch == 1) SP_LAUNCH(F_NORM, launch_layer_norm(src, final_w_, final_b_, rows, hid, d.norm_eps, sel_, stream));

@@ -28,6 +28,13 @@ namespace sp {
         }                                 \
     } while (0)
 
+int Engine::tp_resolve(int T) {
+    if (!tp_pending_) return SP_OK;
+    tp_pending_ = false;
+    SP_LAUNCH(F_NORM, launch_tp_reduce(x_, d.hidden, T, d.hidden, d_tp_, stream));
+    return SP_OK;
+}
+
 // Plans the digit workspace for m rows of k columns; true when the fused producers may be used
 // (all rows fit the workspace at once).
 bool Engine::plan_digits(int m, int k, ImmaArgs& ia) {
@@ -74,8 +81,11 @@ int Engine::gemv(const float* x, int ldx, int m, int k, const DevTensor* w0, con
             }
             SP_LAUNCH(F_GEMV, launch_gemv_imma(ia, stream));
         }
-        // every rank now holds all ranks' partial rows: y0 = res + their sum (y0 and res are the residual stream)
-        if (tp_sum) SP_LAUNCH(F_ELEM, launch_tp_reduce(y0, ldy0, m, ldy0, d_tp_, stream));
+        // the partial rows are on their way to every rank; whoever reads y0 next adds their sum first
+        if (tp_sum) {
+            if (y0 != x_ || res != x_) { set_error("internal: tensor-parallel sum outside the residual stream"); return SP_ERR_STATE; }
+            tp_pending_ = true;
+        }
         return SP_OK;
     }
     if (tp_sum) { set_error("tensor parallel: column-split matrix without tiles"); return SP_ERR_STATE; }
@@ -126,10 +136,11 @@ int Engine::layer_llama(const LayerW& w, int l, int T) {
     const int qkv_ld = (H + 2 * Hkv) * hd;
     ImmaArgs ia;
     if (all_tiled(w.q, w.k, w.v) && plan_digits(T, hid, ia)) {
-        SP_LAUNCH(F_NORM, launch_norm_quant(x_, hid, w.n1w, nullptr, false, d.norm_eps, nullptr, 0, ia, stream));
+        SP_LAUNCH(F_NORM, launch_norm_quant(x_, hid, w.n1w, nullptr, false, d.norm_eps, nullptr, 0, ia, stream, tp_take()));
         SP_TRY(gemv(h_, hid, T, hid, w.q, w.qb, qkv_, qkv_ld, w.k, w.kb, qkv_ + (size_t)H * hd, w.v, w.vb,
                     qkv_ + (size_t)(H + Hkv) * hd, nullptr, &ia));
     } else {
+        SP_TRY(tp_resolve(T));
         SP_LAUNCH(F_NORM, launch_rms_norm(x_, w.n1w, T, hid, d.norm_eps, h_, stream));
         SP_TRY(gemv(h_, hid, T, hid, w.q, w.qb, qkv_, qkv_ld, w.k, w.kb, qkv_ + (size_t)H * hd, w.v, w.vb,
                     qkv_ + (size_t)(H + Hkv) * hd));
@@ -137,9 +148,10 @@ int Engine::layer_llama(const LayerW& w, int l, int T) {
     SP_LAUNCH(F_ROPE, launch_rope_kv_append(qkv_, T, H, Hkv, hd, d.rotary_dim, cos_sin_, d_tok_slot_, d_tok_pos_, kv_, l, stream));
     SP_TRY(attention_and_oproj(w, l, T));
     if (all_tiled(w.gate, w.up) && plan_digits(T, hid, ia)) {
-        SP_LAUNCH(F_NORM, launch_norm_quant(x_, hid, w.n2w, nullptr, false, d.norm_eps, nullptr, 0, ia, stream));
+        SP_LAUNCH(F_NORM, launch_norm_quant(x_, hid, w.n2w, nullptr, false, d.norm_eps, nullptr, 0, ia, stream, tp_take()));
         SP_TRY(gemv(h_, hid, T, hid, w.gate, nullptr, gu_, 2 * ffn, w.up, nullptr, gu_ + ffn, nullptr, nullptr, nullptr, nullptr, &ia));
     } else {
+        SP_TRY(tp_resolve(T));
         SP_LAUNCH(F_NORM, launch_rms_norm(x_, w.n2w, T, hid, d.norm_eps, h_, stream));
         SP_TRY(gemv(h_, hid, T, hid, w.gate, nullptr, gu_, 2 * ffn, w.up, nullptr, gu_ + ffn));
     }

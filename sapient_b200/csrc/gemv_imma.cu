@@ -262,13 +262,16 @@ __global__ void __launch_bounds__(32) act_quant_kernel(const float* __restrict__
 // y != null, its f32 values). Arithmetic of the norm as in crates/sapient-backends/cpu/src/kernels/layernorm.rs:17-105.
 constexpr int NORM_WARPS = 16;
 template <bool LAYER_NORM>
-__global__ void __launch_bounds__(NORM_WARPS * 32) norm_quant_kernel(const float* __restrict__ x, int ldx, const float* __restrict__ w,
+__global__ void __launch_bounds__(NORM_WARPS * 32) norm_quant_kernel(float* x, int ldx, const float* __restrict__ w,
                                                                      const float* __restrict__ b, float eps, float* __restrict__ y, int ldy,
-                                                                     QuantOut qo) {
+                                                                     QuantOut qo, const TpDev* tp) {
     __shared__ float sh[NORM_WARPS];
     pdl_wait();
     pdl_trigger();
     const int m = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // tensor parallel: the row still lacks the sum of the ranks' partial products (o_proj / down_proj); add it first
+    uint32_t tp_epoch = 0;
+    if (tp) tp_epoch = tp_consume_row(*tp, x, (int64_t)m * ldx, m, qo.k);
     const float* row = x + (int64_t)m * ldx;
     const int k = qo.k, tiles = (k + 255) / 256;
     auto block_sum = [&](float v) {
@@ -342,6 +345,7 @@ __global__ void __launch_bounds__(NORM_WARPS * 32) norm_quant_kernel(const float
         }
         quantize_chunk(v, live, lane, tile, m, qo);
     }
+    if (tp) tp_consume_done(*tp, tp_epoch, gridDim.x);
 }
 
 // SwiGLU (act == 0: silu(gate) * up from gu[m][0..ffn) and gu[m][ffn..2ffn)) or tanh-GELU (act == 1: of gu[m][0..ffn))
@@ -434,11 +438,13 @@ cudaError_t launch_act_quant(const float* x, int ldx, const ImmaArgs& a, cudaStr
 }
 
 cudaError_t launch_norm_quant(const float* x, int ldx, const float* w, const float* b, bool layer_norm, float eps, float* y, int ldy,
-                              const ImmaArgs& a, cudaStream_t st) {
+                              const ImmaArgs& a, cudaStream_t st, const TpDev* tp) {
     if (a.m <= 0) return cudaSuccess;
-    cudaError_t le = layer_norm ? launch_pdl(norm_quant_kernel<true>, dim3(a.m), dim3(NORM_WARPS * 32), 0, st, x, ldx, w, b, eps, y, ldy, quant_out(a))
-                                : launch_pdl(norm_quant_kernel<false>, dim3(a.m), dim3(NORM_WARPS * 32), 0, st, x, ldx, w, (const float*)nullptr, eps, y,
-                                             ldy, quant_out(a));
+    float* xm = const_cast<float*>(x);  // written only when tp != null (the pending sum is added in place)
+    cudaError_t le = layer_norm ? launch_pdl(norm_quant_kernel<true>, dim3(a.m), dim3(NORM_WARPS * 32), 0, st, xm, ldx, w, b, eps, y,
+                                             ldy, quant_out(a), tp)
+                                : launch_pdl(norm_quant_kernel<false>, dim3(a.m), dim3(NORM_WARPS * 32), 0, st, xm, ldx, w,
+                                             (const float*)nullptr, eps, y, ldy, quant_out(a), tp);
     if (le != cudaSuccess) return le;
     return count_launch_and_check();
 }
@@ -767,7 +773,8 @@ __device__ __forceinline__ void reduce_store(const ImmaArgs& a, const ImmaSeg& s
             const TpDev& tp = *a.tp;
             const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(tp.ar_seq) + 1u;
             const int64_t off = (int64_t)(a.tp_row0 + m) * sg.ldy + row;
-            for (int p = 0; p < tp.size; ++p) tp_recv(tp, p, (int)(epoch & 1u), tp.rank)[off] = v;
+            const unsigned long long word = tp_word(v, epoch);  // value and arrival mark in one 64-bit store
+            for (int p = 0; p < tp.size; ++p) tp_recv(tp, p, (int)(epoch & 1u), tp.rank)[off] = word;
             continue;
         }
         if (first_seg && a.res) v += a.res[(int64_t)m * a.ldres + row];

@@ -64,8 +64,10 @@ struct ImmaArgs {
     const float* res;       // optional residual for segment 0 (may alias its y)
     int ldres;
     // Tensor-parallel column-split matrix (tp != null): segment 0's outputs are not stored to y but pushed, as partial
-    // sums, into the receive area of every rank (tp.cuh); tp_row0 = activation row of this launch's row 0.
+    // sums tagged with the exchange number, into the receive area of every rank (tp.cuh); tp_row0 = activation row of
+    // this launch's row 0.
     int tp_row0;
+    int pad_;
     const struct TpDev* tp;
 };
 

@@ -59,8 +59,9 @@ cudaError_t launch_gemv_imma(const ImmaArgs& a, cudaStream_t st);
 void imma_select_kernel(int which);
 // Producers that emit the digits of a GEMV input directly (a: planned ImmaArgs; a.m rows, a.k columns):
 // RMSNorm / LayerNorm of x (y optional f32 copy), SwiGLU (act 0) / tanh-GELU (act 1) of gu, merged split-K attention.
+// tp != null: x first receives the pending tensor-parallel sum (tp.cuh), in place.
 cudaError_t launch_norm_quant(const float* x, int ldx, const float* w, const float* b, bool layer_norm, float eps, float* y, int ldy,
-                              const ImmaArgs& a, cudaStream_t st);
+                              const ImmaArgs& a, cudaStream_t st, const struct TpDev* tp = nullptr);
 cudaError_t launch_act_fn_quant(const float* gu, int ld, int ffn, int act, const ImmaArgs& a, cudaStream_t st);
 cudaError_t launch_attn_merge_quant(const float* part, int n_heads, int n_splits, int hd, float* out, int ldo, const ImmaArgs& a,
                                     cudaStream_t st);

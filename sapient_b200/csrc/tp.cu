@@ -73,37 +73,14 @@ int tp_shard_tensor(const std::string& nm, int dtype, const int64_t* dims, int n
 }
 
 // ───────────────────────────── exchange kernels ─────────────────────────────
-// x[row, :] += sum over ranks of the partial rows that the row-split GEMV pushed; one block per activation row.
+// x[row, :] += sum over ranks of the partial rows that the column-split GEMV pushed; one block per activation row.
+// Used where the next kernel is not the fused norm (prefill-shaped steps, tracing).
 __global__ void __launch_bounds__(256) tp_reduce_kernel(float* __restrict__ x, int ldx, int dim, const TpDev* __restrict__ tpp) {
     pdl_wait();
     pdl_trigger();
     const TpDev& tp = *tpp;
-    const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(tp.ar_seq) + 1u;
-    const int slot = (int)(epoch & 1u), tid = threadIdx.x;
-    if (blockIdx.x == 0 && tid < tp.size) {
-        __threadfence_system();  // the GEMV's stores to the peers are complete (previous kernel); order the flag behind them
-        *tp_flag(tp, TP_OFF_AR_FLAGS, tid, slot, tp.rank) = epoch;
-    }
-    if (tid < tp.size) {
-        if (!tp_wait_flag(tp_flag(tp, TP_OFF_AR_FLAGS, tp.rank, slot, tid), epoch)) atomicExch(tp.timeout, 1);
-        __threadfence_system();
-    }
-    __syncthreads();
-    const int row = blockIdx.x;
-    for (int i = tid * 4; i < dim; i += 256 * 4) {
-        float4 acc = *reinterpret_cast<const float4*>(x + (int64_t)row * ldx + i);
-        for (int s = 0; s < tp.size; ++s) {
-            const float4 p = __ldcg(reinterpret_cast<const float4*>(tp_recv(tp, tp.rank, slot, s) + (int64_t)row * dim + i));
-            acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
-        }
-        *reinterpret_cast<float4*>(x + (int64_t)row * ldx + i) = acc;
-    }
-    __syncthreads();
-    if (tid == 0 && atomicAdd(tp.done, 1u) == gridDim.x - 1) {
-        *tp.done = 0u;
-        __threadfence();
-        *reinterpret_cast<volatile uint32_t*>(tp.ar_seq) = epoch;  // every block has read the old value by now
-    }
+    const uint32_t epoch = tp_consume_row(tp, x, (int64_t)blockIdx.x * ldx, blockIdx.x, dim);
+    tp_consume_done(tp, epoch, gridDim.x);
 }
 
 cudaError_t launch_tp_reduce(float* x, int ldx, int rows, int dim, const TpDev* tp, cudaStream_t st) {
@@ -165,7 +142,7 @@ cudaError_t launch_tp_argmax(const float* logits, int ld, int rows, int vocab_of
 }
 
 // ───────────────────────────── engine side ─────────────────────────────
-size_t Engine::tp_block_bytes() const { return TP_OFF_RECV + (size_t)2 * d.tp_size * d.max_tokens * d.hidden * 4; }
+size_t Engine::tp_block_bytes() const { return TP_OFF_RECV + (size_t)2 * d.tp_size * d.max_tokens * d.hidden * 8; }
 
 int Engine::tp_alloc() {
     if (d.tp_size <= 1) return SP_OK;

@@ -6,16 +6,19 @@
 //
 // Every rank owns one communication block (a single cudaMalloc, exported with a CUDA IPC handle and mapped by
 // every peer):
-//     ar_flags[2][8]   u32   all-reduce arrival flags, indexed [slot][source rank]
-//     am_flags[2][8]   u32   arg-max arrival flags
+//     am_flags[2][8]   u32   arg-max arrival flags, indexed [slot][source rank]
 //     am_vals [2][8][32] float2 (value, index bits) arg-max candidates per logit row
-//     recv    [2][size][max_tokens * hidden] f32   partial sums pushed by every source rank
-// The sum is a push: the row-split GEMV stores each output element straight into recv[slot][my rank] of EVERY rank
-// (plain stores to peer pointers from the tensor-core kernel's epilogue); the kernel that consumes the sum then
-// raises this rank's flag on every peer, waits (bounded) until all sources have raised theirs here, and adds the
-// partials from LOCAL memory in rank order, so every rank computes bit-identical activations.
+//     recv    [2][size][max_tokens * hidden] u64   partial sums pushed by every source rank
+// The sum is a push with the arrival flag inside the data: the column-split GEMV stores each output element
+// straight into recv[slot][my rank] of EVERY rank (plain 64-bit stores to peer pointers from the tensor-core
+// kernel's epilogue) as one word = (exchange number << 32) | float bits. A 64-bit store is a single copy, so a
+// reader that sees the exchange number also sees the value: no fence, no separate flag, no extra kernel. The
+// kernel that consumes the sum — the following RMSNorm, or a small stand-alone kernel — polls (bounded) the
+// words of its row in LOCAL memory until all carry the current exchange number and adds the values in rank
+// order, so every rank computes bit-identical activations.
 // slot = epoch & 1 where epoch counts the exchanges; a rank cannot be more than one exchange ahead of a peer
-// (it needs that peer's flag to finish the current one), so two slots are enough.
+// (it needs that peer's words to finish the current one), so two slots are enough, and a word left over from
+// two exchanges ago never matches.
 // Waits are bounded: after TP_SPIN_LIMIT polls a kernel records the failure in `timeout` and goes on, the host
 // reports SP_ERR_COMM. Peer memory is only ever written, with plain stores; nothing is loaded from a peer.
 #pragma once
@@ -28,7 +31,6 @@ constexpr int TP_MAX_RANKS = 8;
 constexpr int TP_ARGMAX_ROWS = 32;
 constexpr int TP_SPIN_LIMIT = 1 << 22;  // polls of ~0.25 us each: about a second
 
-constexpr size_t TP_OFF_AR_FLAGS = 0;
 constexpr size_t TP_OFF_AM_FLAGS = 256;
 constexpr size_t TP_OFF_AM_VALS = 512;
 constexpr size_t TP_OFF_RECV = 8192;
@@ -43,8 +45,11 @@ struct TpDev {
     int* timeout;                      // local: set when a wait gave up
 };
 
-__device__ __forceinline__ float* tp_recv(const TpDev& tp, int on_rank, int slot, int src) {
-    return reinterpret_cast<float*>(tp.base[on_rank] + TP_OFF_RECV) + ((int64_t)slot * tp.size + src) * tp.slot_floats;
+__device__ __forceinline__ unsigned long long* tp_recv(const TpDev& tp, int on_rank, int slot, int src) {
+    return reinterpret_cast<unsigned long long*>(tp.base[on_rank] + TP_OFF_RECV) + ((int64_t)slot * tp.size + src) * tp.slot_floats;
+}
+__device__ __forceinline__ unsigned long long tp_word(float v, uint32_t epoch) {
+    return ((unsigned long long)epoch << 32) | (unsigned long long)__float_as_uint(v);
 }
 __device__ __forceinline__ volatile uint32_t* tp_flag(const TpDev& tp, size_t off, int on_rank, int slot, int src) {
     return reinterpret_cast<volatile uint32_t*>(tp.base[on_rank] + off) + slot * TP_MAX_RANKS + src;
@@ -57,6 +62,45 @@ __device__ __forceinline__ bool tp_wait_flag(volatile uint32_t* f, uint32_t epoc
         __nanosleep(200);
     }
     return false;
+}
+
+// Consumer side of one exchange, called by every thread of a block after the grid-dependency wait: adds the
+// partial rows of all sources to x[row, 0..dim) (dim % 4 == 0), polling each word until it carries this exchange's
+// number. Returns the epoch for tp_consume_done.
+__device__ __forceinline__ uint32_t tp_consume_row(const TpDev& tp, float* x, int64_t row_off_x, int row, int dim) {
+    const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(tp.ar_seq) + 1u;
+    const int slot = (int)(epoch & 1u);
+    bool ok = true;
+    for (int i = threadIdx.x * 4; i < dim; i += blockDim.x * 4) {
+        float4 acc = *reinterpret_cast<const float4*>(x + row_off_x + i);
+        for (int s = 0; s < tp.size; ++s) {
+            const volatile ulonglong2* src = reinterpret_cast<const volatile ulonglong2*>(tp_recv(tp, tp.rank, slot, s) + (int64_t)row * dim + i);
+            unsigned long long w0 = 0, w1 = 0, w2 = 0, w3 = 0;
+            int spins = 0;
+            for (;;) {
+                w0 = src[0].x; w1 = src[0].y; w2 = src[1].x; w3 = src[1].y;
+                if ((uint32_t)(w0 >> 32) == epoch && (uint32_t)(w1 >> 32) == epoch && (uint32_t)(w2 >> 32) == epoch &&
+                    (uint32_t)(w3 >> 32) == epoch)
+                    break;
+                if (++spins > TP_SPIN_LIMIT) { ok = false; break; }
+                __nanosleep(100);
+            }
+            acc.x += __uint_as_float((uint32_t)w0); acc.y += __uint_as_float((uint32_t)w1);
+            acc.z += __uint_as_float((uint32_t)w2); acc.w += __uint_as_float((uint32_t)w3);
+        }
+        *reinterpret_cast<float4*>(x + row_off_x + i) = acc;
+    }
+    if (!ok) atomicExch(tp.timeout, 1);
+    __syncthreads();  // the block's own stores to x are visible to all its threads from here on
+    return epoch;
+}
+// After every block of the consuming grid has called tp_consume_row: the last one publishes the new sequence number.
+__device__ __forceinline__ void tp_consume_done(const TpDev& tp, uint32_t epoch, unsigned n_blocks) {
+    if (threadIdx.x == 0 && atomicAdd(tp.done, 1u) == n_blocks - 1) {
+        *tp.done = 0u;
+        __threadfence();
+        *reinterpret_cast<volatile uint32_t*>(tp.ar_seq) = epoch;  // every block has read the old value by now
+    }
 }
 
 cudaError_t launch_tp_reduce(float* x, int ldx, int rows, int dim, const TpDev* tp, cudaStream_t st);
