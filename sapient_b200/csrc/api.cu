@@ -173,6 +173,13 @@ int32_t sp_cuda_tp_shard(const char* hf_name, int32_t dtype, const int64_t* dims
     API_END
 }
 
+static std::atomic<int> g_tc5{1};
+
+int32_t sp_cuda_set_large_m_gemm(int32_t on) {
+    g_tc5.store(on ? 1 : 0);
+    return SP_OK;
+}
+
 int32_t sp_cuda_set_gemv_path(int32_t path) {
     if (path < 0 || path > 3) { set_error("gemv path must be 0..3"); return SP_ERR_ARG; }
     g_gemv_path.store(path == 1 ? 1 : 0);
@@ -244,6 +251,14 @@ int32_t sp_cuda_matmul_nt_dev(const SpWeight* w, const float* x_dev, int64_t m, 
     if (!w || !x_dev || !y_dev || m < 0) { set_error("null argument"); return SP_ERR_ARG; }
     if (((uintptr_t)x_dev & 15) != 0) { set_error("x must be 16-byte aligned"); return SP_ERR_ARG; }
     SP_CUDA_TRY(cudaSetDevice(w->device));
+    if (w->tiled && g_gemv_path.load() == 0 && g_tc5.load() && m >= TC5_MIN_M && tc5_supported(w->dtype, w->k)) {
+        SpWeight* wm = const_cast<SpWeight*>(w);
+        SP_CUDA_TRY(wm->ws.ensure_xh((size_t)m * w->k));
+        SP_CUDA_TRY(launch_x_to_f16(x_dev, (int)w->k, (int)m, (int)w->k, wm->ws.xh, (cudaStream_t)stream));
+        SP_CUDA_TRY(launch_gemm_tc5(w->tiled, w->dtype, (int)w->n, (int)w->k, wm->ws.xh, (int)m, y_dev, (int)w->n, nullptr, nullptr, 0,
+                                    (cudaStream_t)stream));
+        return SP_OK;
+    }
     if (w->tiled && g_gemv_path.load() == 0) {
         for (int64_t m0 = 0; m0 < m; m0 += 16) {
             ImmaArgs ia{};

@@ -173,6 +173,7 @@ int Engine::repack_weights() {
         }
     }
     SP_CUDA_TRY(ws_.alloc(kmax));
+    if (d.max_tokens >= TC5_MIN_M) SP_CUDA_TRY(ws_.ensure_xh((size_t)d.max_tokens * kmax));
     return SP_OK;
 }
 

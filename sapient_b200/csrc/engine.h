@@ -87,6 +87,7 @@ class Engine {
     bool finalized = false;
     bool trace_on = false;
     bool use_graphs = true;
+    bool use_tc5 = true;   // large-M GEMM on tcgen05 (false: always the 16-row GEMV passes)
     bool profile_on = false;
     std::vector<int> seq_len;
     uint64_t weight_bytes = 0, kv_bytes = 0;

@@ -58,6 +58,18 @@ int Engine::gemv(const float* x, int ldx, int m, int k, const DevTensor* w0, con
     float* ys[3] = {y0, y1, y2};
     bool tiled = true;
     for (int i = 0; i < 3 && ws[i]; ++i) tiled = tiled && ws[i]->tiled != nullptr;
+    if (tiled && !tp_sum && !pre && m >= TC5_MIN_M && use_tc5 && ws_.xh && (size_t)m * k <= ws_.xh_elems) {
+        bool ok = true;
+        for (int i = 0; i < 3 && ws[i]; ++i) ok = ok && tc5_supported(ws[i]->dtype, k);
+        if (ok) {
+            // many rows: dequantise each weight tile once and multiply on the 5th-generation tensor cores
+            SP_LAUNCH(F_ELEM, launch_x_to_f16(x, ldx, m, k, ws_.xh, stream));
+            for (int i = 0; i < 3 && ws[i]; ++i)
+                SP_LAUNCH(F_GEMV, launch_gemm_tc5(ws[i]->tiled, ws[i]->dtype, (int)ws[i]->dims[0], k, ws_.xh, m, ys[i], ldy0, bs[i],
+                                                  i == 0 ? res : nullptr, ldy0, stream));
+            return SP_OK;
+        }
+    }
     if (tiled) {
         // tensor-core path: digits of up to 16 activation rows at a time, all segments share them
         for (int m0 = 0; m0 < m; m0 += 16) {

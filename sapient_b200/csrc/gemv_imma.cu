@@ -484,7 +484,19 @@ cudaError_t ActWorkspace::alloc(int k_max_) {
     return cudaDeviceSynchronize();
 }
 
+cudaError_t ActWorkspace::ensure_xh(size_t elems) {
+    if (elems <= xh_elems) return cudaSuccess;
+    if (xh) cudaFree(xh);
+    xh = nullptr;
+    xh_elems = 0;
+    cudaError_t e = cudaMalloc((void**)&xh, elems * sizeof(__half));
+    if (e == cudaSuccess) xh_elems = elems;
+    return e;
+}
+
 void ActWorkspace::release() {
+    if (xh) cudaFree(xh);
+    xh = nullptr; xh_elems = 0;
     if (xq) cudaFree(xq);
     if (colscale) cudaFree(colscale);
     if (xs32d) cudaFree(xs32d);

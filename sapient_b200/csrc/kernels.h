@@ -76,6 +76,9 @@ struct ActWorkspace {
     int8_t* xs32d = nullptr;
     int8_t* xs16d = nullptr;
     int k_max = 0;
+    __half* xh = nullptr;      // fp16 copy of the activations for the large-M tensor-core GEMM (gemm_tc5.cu)
+    size_t xh_elems = 0;
+    cudaError_t ensure_xh(size_t elems);  // grows the buffer (allocates: not during stream capture)
     static constexpr int NCP_MAX = 32;
     cudaError_t alloc(int k_max_);
     void release();
@@ -83,6 +86,14 @@ struct ActWorkspace {
 // Digits for x[m, k] (m <= 16) followed by the tensor-core GEMV over up to three weight segments sharing x.
 // Fills a.digits/ncp/eb/xq/...; a.seg/nseg/k/m/res must be set by the caller.
 cudaError_t launch_quant_gemv(const float* x, int ldx, ImmaArgs& a, const ActWorkspace& ws, bool requantize, cudaStream_t st);
+
+// Large-M dequant GEMM on tcgen05 / TMEM (gemm_tc5.cu): y[m, n] = x·Wᵀ (+ bias, + res) from the tiled weights and an
+// fp16 copy of the activations; k % 256 == 0, Q4_K / Q6_K / Q8_0.
+constexpr int TC5_MIN_M = 32;
+bool tc5_supported(int dtype, int64_t k);
+cudaError_t launch_x_to_f16(const float* x, int ldx, int m, int k, __half* out, cudaStream_t st);
+cudaError_t launch_gemm_tc5(const uint8_t* wt, int dtype, int n, int k, const __half* xh, int m, float* y, int ldy, const float* bias,
+                            const float* res, int ldres, cudaStream_t st);
 
 cudaError_t launch_dequant(int dtype, const uint8_t* w, int64_t n, int64_t k, float* out, cudaStream_t st);
 cudaError_t launch_gemv(const GemvArgs& a, cudaStream_t st);

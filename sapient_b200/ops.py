@@ -167,5 +167,10 @@ def set_gemv_path(path: int) -> None:
     check(lib().sp_cuda_set_gemv_path(path))
 
 
+def set_large_m_gemm(on: bool) -> None:
+    """Op-level matmuls with m >= 32 and k % 256 == 0 use the tcgen05 / TMEM dequant GEMM (default on)."""
+    check(lib().sp_cuda_set_large_m_gemm(int(on)))
+
+
 def launch_count() -> int:
     return int(lib().sp_cuda_launch_count())

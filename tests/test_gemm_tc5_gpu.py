@@ -1,0 +1,61 @@
+"""Large-M dequant GEMM on tcgen05 / TMEM (gemm_tc5.cu) through sp_cuda_matmul_nt, against the CPU oracle and
+against the 16-row tensor-core GEMV passes it replaces.
+
+Bar: 1e-3 relative L2 per op. The kernel rounds the (exactly dequantised) weights and the activations to fp16 and
+accumulates in fp32, so it lands near 2e-4."""
+import numpy as np
+import pytest
+
+from helpers import rel_l2
+from sapient_b200 import _lib, ops, synth
+
+pytestmark = pytest.mark.gpu
+Q8_0, Q4_K, Q6_K = synth.Q8_0, synth.Q4_K, synth.Q6_K
+
+
+def _large_m(on: bool) -> None:
+    _lib.check(_lib.lib().sp_cuda_set_large_m_gemm(int(on)))
+
+
+# (m, k, n): m not a multiple of 16 / over 256 (two CTA columns), n not a multiple of 128 / 16, several K chunks
+CASES = [(32, 256, 128), (48, 512, 200), (100, 1024, 130), (300, 768, 72), (512, 512, 384)]
+
+
+@pytest.mark.parametrize("dtype", [Q4_K, Q6_K, Q8_0])
+@pytest.mark.parametrize("m,k,n", CASES)
+def test_large_m_gemm_matches_oracle_and_gemv(oracle, dtype, m, k, n):
+    be, _ = synth.BLOCK[dtype]
+    rng = np.random.default_rng(m + k + n)
+    raw = synth.random_bit_blocks(dtype, n * k // be, seed=m + n + dtype)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    want = oracle.matmul_nt(x, raw, dtype, n)
+    try:
+        _large_m(True)
+        got = ops.matmul_nt(x, raw, dtype, n)
+        _large_m(False)
+        gemv = ops.matmul_nt(x, raw, dtype, n)
+    finally:
+        _large_m(True)
+    assert got.shape == (m, n) and np.all(np.isfinite(got))
+    assert rel_l2(gemv, want) < 3e-4
+    err = rel_l2(got, want)
+    assert err < 1e-3, err
+    assert err < 5e-4, err  # expected ~2e-4 (fp16 operands)
+    # every output element, not only the norm: a misplaced tile or a wrong swizzle shows up as O(1) errors
+    scale = np.abs(want).max()
+    assert np.abs(got - want).max() < 5e-3 * scale
+
+
+def test_large_m_gemm_quantised_gaussian_weights(oracle):
+    """Weights as the synthetic models have them (N(0, 0.02) quantised), activations with a few large entries."""
+    import torch
+
+    m, k, n = 64, 1024, 256
+    g = torch.Generator().manual_seed(5)
+    w = torch.randn(n, k, generator=g) * 0.02
+    raw = synth.quantize(Q4_K, w).reshape(-1).numpy()
+    x = torch.randn(m, k, generator=g).numpy().astype(np.float32)
+    x[3, 17] = 80.0
+    got = ops.matmul_nt(x, raw, Q4_K, n)
+    want = oracle.matmul_nt(x, raw, Q4_K, n)
+    assert rel_l2(got, want) < 5e-4
