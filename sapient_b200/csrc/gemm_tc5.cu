@@ -1,12 +1,13 @@
 // Large-M dequant GEMM on the 5th-generation tensor cores (tcgen05 + TMEM), for prefill and batched decode.
 //
-// y[m, n] = sum_k x[m, k] * W[n, k] for m >= 32 activation rows. The GEMV kernel (gemv_imma.cu) streams the whole
+// y[m, n] = sum_k x[m, k] * W[n, k] for m >= 64 activation rows. The GEMV kernel (gemv_imma.cu) streams the whole
 // weight matrix once per 16 activation rows; here a CTA dequantises each weight tile ONCE and multiplies it with up to
 // 256 activation rows:
 //   * CTA tile: 128 weight rows (the MMA's M) x NB <= 256 activation rows (the MMA's N), K walked in chunks of 64;
 //   * per chunk the 256 threads rebuild 128 x 64 weights from the tile-repacked ggml blocks (the same layout the GEMV
 //     reads, gemv_imma.cuh) — exact f32 dequantisation, rounded once to fp16 — into shared memory in the K-major
-//     128-byte-swizzled layout the tensor core reads, and copy the matching 64 columns of the fp16 activations;
+//     128-byte-swizzled layout the tensor core reads, and copy the matching 64 columns of the fp16 activations; the
+//     global loads of the next chunk are issued into registers before the current one is handed to the tensor core;
 //   * one thread issues four tcgen05.mma (128 x NB x 16, kind::f16, fp32 accumulation in tensor memory) and commits
 //     them to an mbarrier; two shared-memory stages let the next chunk be rebuilt while the MMAs run;
 //   * epilogue: tcgen05.ld brings the accumulators back (one weight row per thread, 16 activation rows per
@@ -87,62 +88,85 @@ __device__ __forceinline__ uint32_t pack_h2(float a, float b) {
     return (uint32_t)__half_as_ushort(__float2half_rn(a)) | ((uint32_t)__half_as_ushort(__float2half_rn(b)) << 16);
 }
 
-// 32 consecutive columns (half-chunk hh of chunk c) of weight row `row` of the CTA tile, dequantised from the tiled
-// layout into v[32].
+// The raw words one thread needs for 32 consecutive columns (half-chunk hh of 64-column group cq) of weight row rr of
+// a 16-row tile: fetched one chunk ahead (tc5_load), turned into f32 weights when the stage is free (tc5_compute).
+struct Tc5Raw {
+    uint32_t w[16];  // Q4_K / Q8_0: 8 words of nibbles / int8; Q6_K: 8 ql words + 8 qh words
+    uint4 hdr;       // Q4_K: d|dmin, 12 scale bytes; Q6_K: x = 2 int8 scales, y = d bits; Q8_0: x = d bits
+};
+
 template <int DT>
-__device__ __forceinline__ void tc5_dequant32(const uint8_t* tile, int rr, int cq, int hh, float (&v)[32]) {
+__device__ __forceinline__ void tc5_load(const uint8_t* tile, int rr, int cq, int hh, Tc5Raw& r) {
     const int g = rr & 7, hi8 = rr >> 3;
     const uint32_t* w32 = reinterpret_cast<const uint32_t*>(tile);
     if (DT == T_Q4_K) {
-        const uint4 hdr = *reinterpret_cast<const uint4*>(tile + 2048 + rr * 16);
-        const float d = half_bits_to_float((uint16_t)(hdr.x & 0xFFFFu)), dmin = half_bits_to_float((uint16_t)(hdr.x >> 16));
-        uint32_t sc, mn;
-        k4_scale_min(hdr.y, hdr.z, hdr.w, 2 * cq + hh, &sc, &mn);
-        const float dl = __fmul_rn(d, (float)sc), ml = __fmul_rn(dmin, (float)mn);
+        r.hdr = __ldg(reinterpret_cast<const uint4*>(tile + 2048 + rr * 16));
 #pragma unroll
         for (int h16 = 0; h16 < 2; ++h16)
 #pragma unroll
-            for (int t = 0; t < 4; ++t) {
-                const uint32_t w = w32[cq * 128 + (g * 4 + t) * 4 + hi8 * 2 + h16];
-#pragma unroll
-                for (int b = 0; b < 4; ++b) {
-                    const uint32_t byte = (w >> (8 * b)) & 0xFFu;
-                    const float q = (float)(hh ? (byte >> 4) : (byte & 15u));
-                    v[16 * h16 + 4 * t + b] = __fsub_rn(__fmul_rn(dl, q), ml);
-                }
-            }
+            for (int t = 0; t < 4; ++t) r.w[4 * h16 + t] = __ldg(w32 + cq * 128 + (g * 4 + t) * 4 + hi8 * 2 + h16);
     } else if (DT == T_Q8_0) {
         const int bb = 2 * cq + hh;
-        const float d = half_bits_to_float(*reinterpret_cast<const uint16_t*>(tile + 4096 + (rr * 8 + bb) * 2));
+        r.hdr.x = __ldg(reinterpret_cast<const uint16_t*>(tile + 4096 + (rr * 8 + bb) * 2));
 #pragma unroll
         for (int h16 = 0; h16 < 2; ++h16)
 #pragma unroll
-            for (int t = 0; t < 4; ++t) {
-                const uint32_t w = w32[bb * 128 + (g * 4 + t) * 4 + hi8 * 2 + h16];
-#pragma unroll
-                for (int b = 0; b < 4; ++b) v[16 * h16 + 4 * t + b] = __fmul_rn((float)(int8_t)((w >> (8 * b)) & 0xFFu), d);
-            }
+            for (int t = 0; t < 4; ++t) r.w[4 * h16 + t] = __ldg(w32 + bb * 128 + (g * 4 + t) * 4 + hi8 * 2 + h16);
     } else {  // Q6_K
         const int half = cq >> 1, quarter = 2 * (cq & 1) + hh;
-        const float d = half_bits_to_float(*reinterpret_cast<const uint16_t*>(tile + 3328 + rr * 2));
         const int8_t* scales = reinterpret_cast<const int8_t*>(tile + 3072 + rr * 16);
+        r.hdr.x = (uint32_t)(uint8_t)__ldg(scales + 8 * half + 2 * quarter) | ((uint32_t)(uint8_t)__ldg(scales + 8 * half + 1 + 2 * quarter) << 8);
+        r.hdr.y = __ldg(reinterpret_cast<const uint16_t*>(tile + 3328 + rr * 2));
 #pragma unroll
         for (int p = 0; p < 2; ++p) {
-            const float dsc = __fmul_rn(d, (float)scales[8 * half + p + 2 * quarter]);
             const int cc = (half << 1) | p;
+            const int sl = 6 * cc + (hh ? 1 : 0) + hi8 * 3, sh = 6 * cc + 2 + hi8 * 3;
 #pragma unroll
             for (int t = 0; t < 4; ++t) {
-                const int sl = 6 * cc + (hh ? 1 : 0) + hi8 * 3, sh = 6 * cc + 2 + hi8 * 3;
-                const uint32_t wl = w32[(sl >> 2) * 128 + (g * 4 + t) * 4 + (sl & 3)];
-                const uint32_t wh = w32[(sh >> 2) * 128 + (g * 4 + t) * 4 + (sh & 3)];
+                r.w[4 * p + t] = __ldg(w32 + (sl >> 2) * 128 + (g * 4 + t) * 4 + (sl & 3));
+                r.w[8 + 4 * p + t] = __ldg(w32 + (sh >> 2) * 128 + (g * 4 + t) * 4 + (sh & 3));
+            }
+        }
+    }
+}
+
+// Exact f32 dequantisation (every product rounded separately, as the reference does) of the 32 columns.
+template <int DT>
+__device__ __forceinline__ void tc5_compute(const Tc5Raw& r, int cq, int hh, float (&v)[32]) {
+    if (DT == T_Q4_K) {
+        const float d = half_bits_to_float((uint16_t)(r.hdr.x & 0xFFFFu)), dmin = half_bits_to_float((uint16_t)(r.hdr.x >> 16));
+        uint32_t sc, mn;
+        k4_scale_min(r.hdr.y, r.hdr.z, r.hdr.w, 2 * cq + hh, &sc, &mn);
+        const float dl = __fmul_rn(d, (float)sc), ml = __fmul_rn(dmin, (float)mn);
+#pragma unroll
+        for (int i = 0; i < 8; ++i)  // word i = (h16, t): bytes 16 h16 + 4 t .. + 3 of the group's 32 nibble bytes
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                const uint32_t byte = (r.w[i] >> (8 * b)) & 0xFFu;
+                const float q = (float)(hh ? (byte >> 4) : (byte & 15u));
+                v[4 * i + b] = __fsub_rn(__fmul_rn(dl, q), ml);
+            }
+    } else if (DT == T_Q8_0) {
+        const float d = half_bits_to_float((uint16_t)r.hdr.x);
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+#pragma unroll
+            for (int b = 0; b < 4; ++b) v[4 * i + b] = __fmul_rn((float)(int8_t)((r.w[i] >> (8 * b)) & 0xFFu), d);
+    } else {  // Q6_K
+        const int quarter = 2 * (cq & 1) + hh;
+        const float d = half_bits_to_float((uint16_t)r.hdr.y);
+#pragma unroll
+        for (int p = 0; p < 2; ++p) {
+            const float dsc = __fmul_rn(d, (float)(int8_t)((r.hdr.x >> (8 * p)) & 0xFFu));
+#pragma unroll
+            for (int t = 0; t < 4; ++t)
 #pragma unroll
                 for (int b = 0; b < 4; ++b) {
-                    const uint32_t lb = (wl >> (8 * b)) & 0xFFu, hb = (wh >> (8 * b)) & 0xFFu;
+                    const uint32_t lb = (r.w[4 * p + t] >> (8 * b)) & 0xFFu, hb = (r.w[8 + 4 * p + t] >> (8 * b)) & 0xFFu;
                     const uint32_t nib = (cq & 1) ? (lb >> 4) : (lb & 15u);
                     const int q = (int)(nib | (((hb >> (2 * quarter)) & 3u) << 4)) - 32;
                     v[16 * p + 4 * t + b] = __fmul_rn(dsc, (float)q);
                 }
-            }
         }
     }
 }
@@ -160,7 +184,7 @@ struct Tc5Args {
 };
 
 template <int DT>
-__global__ void __launch_bounds__(TC5_THREADS, 1) gemm_tc5_kernel(const Tc5Args a) {
+__global__ void __launch_bounds__(TC5_THREADS, 2) gemm_tc5_kernel(const Tc5Args a) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t mbar[2];
     __shared__ uint32_t tmem_slot;
@@ -197,6 +221,20 @@ __global__ void __launch_bounds__(TC5_THREADS, 1) gemm_tc5_kernel(const Tc5Args 
     const uint32_t idesc = tc5_idesc(nb);
     const int n_chunks = a.k / TC5_BK;
     bool ok = true;
+    constexpr int B_PER_THREAD = TC5_NB_MAX * 8 / TC5_THREADS;  // 16-byte pieces of the activation tile per thread
+    Tc5Raw raw;
+    uint4 braw[B_PER_THREAD];
+    auto fetch = [&](int c) {  // global loads of chunk c into registers
+        if (row_live) tc5_load<DT>(tile_row + (int64_t)(c >> 2) * TILE_BYTES, rr, c & 3, hh, raw);
+#pragma unroll
+        for (int i = 0; i < B_PER_THREAD; ++i) {
+            const int idx = tid + i * TC5_THREADS, r = idx >> 3, ch = idx & 7;
+            braw[i] = make_uint4(0u, 0u, 0u, 0u);
+            if (idx < nb * 8 && m0 + r < a.m)
+                braw[i] = __ldg(reinterpret_cast<const uint4*>(a.xh + (int64_t)(m0 + r) * a.k + (int64_t)c * TC5_BK + ch * 8));
+        }
+    };
+    fetch(0);
     for (int c = 0; c < n_chunks; ++c) {
         const int s = c & 1;
         uint8_t* As = smem + s * TC5_STAGE_BYTES;
@@ -205,7 +243,7 @@ __global__ void __launch_bounds__(TC5_THREADS, 1) gemm_tc5_kernel(const Tc5Args 
         // A: 32 dequantised weights of this thread's row, rounded to fp16, into the swizzled K-major tile
         {
             float v[32];
-            if (row_live) tc5_dequant32<DT>(tile_row + (int64_t)(c >> 2) * TILE_BYTES, rr, c & 3, hh, v);
+            if (row_live) tc5_compute<DT>(raw, c & 3, hh, v);
             else {
 #pragma unroll
                 for (int i = 0; i < 32; ++i) v[i] = 0.f;
@@ -219,12 +257,12 @@ __global__ void __launch_bounds__(TC5_THREADS, 1) gemm_tc5_kernel(const Tc5Args 
             }
         }
         // B: 64 columns of nb activation rows (fp16 already), 16 bytes per copy
-        for (int idx = tid; idx < nb * 8; idx += TC5_THREADS) {
-            const int r = idx >> 3, ch = idx & 7;
-            uint4 q = make_uint4(0u, 0u, 0u, 0u);
-            if (m0 + r < a.m) q = *reinterpret_cast<const uint4*>(a.xh + (int64_t)(m0 + r) * a.k + (int64_t)c * TC5_BK + ch * 8);
-            *reinterpret_cast<uint4*>(Bs + r * 128 + ((ch ^ (r & 7)) << 4)) = q;
+#pragma unroll
+        for (int i = 0; i < B_PER_THREAD; ++i) {
+            const int idx = tid + i * TC5_THREADS, r = idx >> 3, ch = idx & 7;
+            if (idx < nb * 8) *reinterpret_cast<uint4*>(Bs + r * 128 + ((ch ^ (r & 7)) << 4)) = braw[i];
         }
+        if (c + 1 < n_chunks) fetch(c + 1);  // in flight while this chunk is fenced, multiplied and the stage wait runs
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // generic-proxy stores -> visible to the tensor core
         asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
         __syncthreads();
