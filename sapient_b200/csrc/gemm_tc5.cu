@@ -4,7 +4,7 @@
 // weight matrix once per 16 activation rows; here a CTA dequantises each weight tile ONCE and multiplies it with up to
 // 256 activation rows:
 //   * CTA tile: 128 weight rows (the MMA's M) x NB <= 256 activation rows (the MMA's N), K walked in chunks of 64;
-//   * per chunk the 256 threads rebuild 128 x 64 weights from the tile-repacked ggml blocks (the same layout the GEMV
+//   * per chunk the 512 threads rebuild 128 x 64 weights from the tile-repacked ggml blocks (the same layout the GEMV
 //     reads, gemv_imma.cuh) — exact f32 dequantisation, rounded once to fp16 — into shared memory in the K-major
 //     128-byte-swizzled layout the tensor core reads, and copy the matching 64 columns of the fp16 activations; the
 //     global loads of the next chunk are issued into registers before the current one is handed to the tensor core;
@@ -26,7 +26,7 @@ namespace sp {
 
 cudaError_t count_launch_and_check();  // kernels.cu
 
-constexpr int TC5_THREADS = 256;
+constexpr int TC5_THREADS = 512;
 constexpr int TC5_BM = 128;                    // weight rows per CTA
 constexpr int TC5_BK = 64;                     // columns per chunk = one 128-byte swizzle row of fp16
 constexpr int TC5_NB_MAX = 256;                // activation rows per CTA
@@ -88,86 +88,76 @@ __device__ __forceinline__ uint32_t pack_h2(float a, float b) {
     return (uint32_t)__half_as_ushort(__float2half_rn(a)) | ((uint32_t)__half_as_ushort(__float2half_rn(b)) << 16);
 }
 
-// The raw words one thread needs for 32 consecutive columns (half-chunk hh of 64-column group cq) of weight row rr of
-// a 16-row tile: fetched one chunk ahead (tc5_load), turned into f32 weights when the stage is free (tc5_compute).
+// The raw words one thread needs for 16 consecutive columns — sixteenth-block (hh, h16) of 64-column group cq — of weight
+// row rr of a 16-row tile: fetched one chunk ahead (tc5_load), turned into f32 weights when the stage is free
+// (tc5_compute). hh selects the 32-column sub-block (low / high nibbles), h16 its first or second 16 columns.
 struct Tc5Raw {
-    uint32_t w[16];  // Q4_K / Q8_0: 8 words of nibbles / int8; Q6_K: 8 ql words + 8 qh words
-    uint4 hdr;       // Q4_K: d|dmin, 12 scale bytes; Q6_K: x = 2 int8 scales, y = d bits; Q8_0: x = d bits
+    uint32_t w[8];  // Q4_K / Q8_0: 4 words of nibbles / int8; Q6_K: 4 ql words + 4 qh words
+    uint4 hdr;      // Q4_K: d|dmin, 12 scale bytes; Q6_K: x = int8 scale, y = d bits; Q8_0: x = d bits
 };
 
 template <int DT>
-__device__ __forceinline__ void tc5_load(const uint8_t* tile, int rr, int cq, int hh, Tc5Raw& r) {
+__device__ __forceinline__ void tc5_load(const uint8_t* tile, int rr, int cq, int hh, int h16, Tc5Raw& r) {
     const int g = rr & 7, hi8 = rr >> 3;
     const uint32_t* w32 = reinterpret_cast<const uint32_t*>(tile);
     if (DT == T_Q4_K) {
         r.hdr = __ldg(reinterpret_cast<const uint4*>(tile + 2048 + rr * 16));
 #pragma unroll
-        for (int h16 = 0; h16 < 2; ++h16)
-#pragma unroll
-            for (int t = 0; t < 4; ++t) r.w[4 * h16 + t] = __ldg(w32 + cq * 128 + (g * 4 + t) * 4 + hi8 * 2 + h16);
+        for (int t = 0; t < 4; ++t) r.w[t] = __ldg(w32 + cq * 128 + (g * 4 + t) * 4 + hi8 * 2 + h16);
     } else if (DT == T_Q8_0) {
         const int bb = 2 * cq + hh;
         r.hdr.x = __ldg(reinterpret_cast<const uint16_t*>(tile + 4096 + (rr * 8 + bb) * 2));
 #pragma unroll
-        for (int h16 = 0; h16 < 2; ++h16)
-#pragma unroll
-            for (int t = 0; t < 4; ++t) r.w[4 * h16 + t] = __ldg(w32 + bb * 128 + (g * 4 + t) * 4 + hi8 * 2 + h16);
-    } else {  // Q6_K
+        for (int t = 0; t < 4; ++t) r.w[t] = __ldg(w32 + bb * 128 + (g * 4 + t) * 4 + hi8 * 2 + h16);
+    } else {  // Q6_K: h16 is p of the block layout (l = 16 p + 4 t + b)
         const int half = cq >> 1, quarter = 2 * (cq & 1) + hh;
         const int8_t* scales = reinterpret_cast<const int8_t*>(tile + 3072 + rr * 16);
-        r.hdr.x = (uint32_t)(uint8_t)__ldg(scales + 8 * half + 2 * quarter) | ((uint32_t)(uint8_t)__ldg(scales + 8 * half + 1 + 2 * quarter) << 8);
+        r.hdr.x = (uint32_t)(uint8_t)__ldg(scales + 8 * half + h16 + 2 * quarter);
         r.hdr.y = __ldg(reinterpret_cast<const uint16_t*>(tile + 3328 + rr * 2));
+        const int cc = (half << 1) | h16;
+        const int sl = 6 * cc + (hh ? 1 : 0) + hi8 * 3, sh = 6 * cc + 2 + hi8 * 3;
 #pragma unroll
-        for (int p = 0; p < 2; ++p) {
-            const int cc = (half << 1) | p;
-            const int sl = 6 * cc + (hh ? 1 : 0) + hi8 * 3, sh = 6 * cc + 2 + hi8 * 3;
-#pragma unroll
-            for (int t = 0; t < 4; ++t) {
-                r.w[4 * p + t] = __ldg(w32 + (sl >> 2) * 128 + (g * 4 + t) * 4 + (sl & 3));
-                r.w[8 + 4 * p + t] = __ldg(w32 + (sh >> 2) * 128 + (g * 4 + t) * 4 + (sh & 3));
-            }
+        for (int t = 0; t < 4; ++t) {
+            r.w[t] = __ldg(w32 + (sl >> 2) * 128 + (g * 4 + t) * 4 + (sl & 3));
+            r.w[4 + t] = __ldg(w32 + (sh >> 2) * 128 + (g * 4 + t) * 4 + (sh & 3));
         }
     }
 }
 
-// Exact f32 dequantisation (every product rounded separately, as the reference does) of the 32 columns.
+// Exact f32 dequantisation (every product rounded separately, as the reference does) of the 16 columns.
 template <int DT>
-__device__ __forceinline__ void tc5_compute(const Tc5Raw& r, int cq, int hh, float (&v)[32]) {
+__device__ __forceinline__ void tc5_compute(const Tc5Raw& r, int cq, int hh, float (&v)[16]) {
     if (DT == T_Q4_K) {
         const float d = half_bits_to_float((uint16_t)(r.hdr.x & 0xFFFFu)), dmin = half_bits_to_float((uint16_t)(r.hdr.x >> 16));
         uint32_t sc, mn;
         k4_scale_min(r.hdr.y, r.hdr.z, r.hdr.w, 2 * cq + hh, &sc, &mn);
         const float dl = __fmul_rn(d, (float)sc), ml = __fmul_rn(dmin, (float)mn);
 #pragma unroll
-        for (int i = 0; i < 8; ++i)  // word i = (h16, t): bytes 16 h16 + 4 t .. + 3 of the group's 32 nibble bytes
+        for (int t = 0; t < 4; ++t)
 #pragma unroll
             for (int b = 0; b < 4; ++b) {
-                const uint32_t byte = (r.w[i] >> (8 * b)) & 0xFFu;
+                const uint32_t byte = (r.w[t] >> (8 * b)) & 0xFFu;
                 const float q = (float)(hh ? (byte >> 4) : (byte & 15u));
-                v[4 * i + b] = __fsub_rn(__fmul_rn(dl, q), ml);
+                v[4 * t + b] = __fsub_rn(__fmul_rn(dl, q), ml);
             }
     } else if (DT == T_Q8_0) {
         const float d = half_bits_to_float((uint16_t)r.hdr.x);
 #pragma unroll
-        for (int i = 0; i < 8; ++i)
+        for (int t = 0; t < 4; ++t)
 #pragma unroll
-            for (int b = 0; b < 4; ++b) v[4 * i + b] = __fmul_rn((float)(int8_t)((r.w[i] >> (8 * b)) & 0xFFu), d);
+            for (int b = 0; b < 4; ++b) v[4 * t + b] = __fmul_rn((float)(int8_t)((r.w[t] >> (8 * b)) & 0xFFu), d);
     } else {  // Q6_K
         const int quarter = 2 * (cq & 1) + hh;
-        const float d = half_bits_to_float((uint16_t)r.hdr.y);
+        const float dsc = __fmul_rn(half_bits_to_float((uint16_t)r.hdr.y), (float)(int8_t)(r.hdr.x & 0xFFu));
 #pragma unroll
-        for (int p = 0; p < 2; ++p) {
-            const float dsc = __fmul_rn(d, (float)(int8_t)((r.hdr.x >> (8 * p)) & 0xFFu));
+        for (int t = 0; t < 4; ++t)
 #pragma unroll
-            for (int t = 0; t < 4; ++t)
-#pragma unroll
-                for (int b = 0; b < 4; ++b) {
-                    const uint32_t lb = (r.w[4 * p + t] >> (8 * b)) & 0xFFu, hb = (r.w[8 + 4 * p + t] >> (8 * b)) & 0xFFu;
-                    const uint32_t nib = (cq & 1) ? (lb >> 4) : (lb & 15u);
-                    const int q = (int)(nib | (((hb >> (2 * quarter)) & 3u) << 4)) - 32;
-                    v[16 * p + 4 * t + b] = __fmul_rn(dsc, (float)q);
-                }
-        }
+            for (int b = 0; b < 4; ++b) {
+                const uint32_t lb = (r.w[t] >> (8 * b)) & 0xFFu, hb = (r.w[4 + t] >> (8 * b)) & 0xFFu;
+                const uint32_t nib = (cq & 1) ? (lb >> 4) : (lb & 15u);
+                const int q = (int)(nib | (((hb >> (2 * quarter)) & 3u) << 4)) - 32;
+                v[4 * t + b] = __fmul_rn(dsc, (float)q);
+            }
     }
 }
 
@@ -184,7 +174,7 @@ struct Tc5Args {
 };
 
 template <int DT>
-__global__ void __launch_bounds__(TC5_THREADS, 2) gemm_tc5_kernel(const Tc5Args a) {
+__global__ void __launch_bounds__(TC5_THREADS, 1) gemm_tc5_kernel(const Tc5Args a) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t mbar[2];
     __shared__ uint32_t tmem_slot;
@@ -214,7 +204,7 @@ __global__ void __launch_bounds__(TC5_THREADS, 2) gemm_tc5_kernel(const Tc5Args 
     pdl_wait();  // activations come from the previous kernel
     pdl_trigger();
 
-    const int row = tid >> 1, hh = tid & 1;           // this thread's weight row of the tile and 32-column half
+    const int row = tid >> 2, hh = (tid >> 1) & 1, h16 = tid & 1;  // this thread's weight row of the tile and 16-column slice
     const int rt = (n0 >> 4) + (row >> 4), rr = row & 15;
     const bool row_live = rt < n_tile_rows;
     const uint8_t* tile_row = a.wt + (int64_t)rt * kts * TILE_BYTES;
@@ -225,7 +215,7 @@ __global__ void __launch_bounds__(TC5_THREADS, 2) gemm_tc5_kernel(const Tc5Args 
     Tc5Raw raw;
     uint4 braw[B_PER_THREAD];
     auto fetch = [&](int c) {  // global loads of chunk c into registers
-        if (row_live) tc5_load<DT>(tile_row + (int64_t)(c >> 2) * TILE_BYTES, rr, c & 3, hh, raw);
+        if (row_live) tc5_load<DT>(tile_row + (int64_t)(c >> 2) * TILE_BYTES, rr, c & 3, hh, h16, raw);
 #pragma unroll
         for (int i = 0; i < B_PER_THREAD; ++i) {
             const int idx = tid + i * TC5_THREADS, r = idx >> 3, ch = idx & 7;
@@ -240,19 +230,19 @@ __global__ void __launch_bounds__(TC5_THREADS, 2) gemm_tc5_kernel(const Tc5Args 
         uint8_t* As = smem + s * TC5_STAGE_BYTES;
         uint8_t* Bs = As + TC5_A_BYTES;
         if (c >= 2) ok = tc5_wait(&mbar[s], (uint32_t)(((c >> 1) - 1) & 1)) && ok;  // the MMAs of chunk c - 2 have read this stage
-        // A: 32 dequantised weights of this thread's row, rounded to fp16, into the swizzled K-major tile
+        // A: 16 dequantised weights of this thread's row, rounded to fp16, into the swizzled K-major tile
         {
-            float v[32];
+            float v[16];
             if (row_live) tc5_compute<DT>(raw, c & 3, hh, v);
             else {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) v[i] = 0.f;
+                for (int i = 0; i < 16; ++i) v[i] = 0.f;
             }
 #pragma unroll
-            for (int p = 0; p < 4; ++p) {
+            for (int p = 0; p < 2; ++p) {
                 const uint4 q = make_uint4(pack_h2(v[8 * p], v[8 * p + 1]), pack_h2(v[8 * p + 2], v[8 * p + 3]),
                                            pack_h2(v[8 * p + 4], v[8 * p + 5]), pack_h2(v[8 * p + 6], v[8 * p + 7]));
-                const int chunk16 = 4 * hh + p;
+                const int chunk16 = 4 * hh + 2 * h16 + p;
                 *reinterpret_cast<uint4*>(As + row * 128 + ((chunk16 ^ (row & 7)) << 4)) = q;
             }
         }
@@ -288,7 +278,7 @@ __global__ void __launch_bounds__(TC5_THREADS, 2) gemm_tc5_kernel(const Tc5Args 
         const int q4 = warp & 3;
         const int n = n0 + 32 * q4 + lane;
         const float bias = (a.bias && n < a.n) ? a.bias[n] : 0.f;
-        for (int gi = warp >> 2; gi < nb / 16; gi += 2) {
+        for (int gi = warp >> 2; gi < nb / 16; gi += TC5_THREADS / 128) {
             uint32_t r[16];
             const uint32_t taddr = tmem + ((uint32_t)(32 * q4) << 16) + (uint32_t)(gi * 16);
             asm volatile(
