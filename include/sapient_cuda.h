@@ -158,6 +158,11 @@ int32_t sp_cuda_engine_vocab_local(const SpEngine* e, int32_t* rows, int32_t* fi
 int32_t sp_cuda_tp_shard(const char* hf_name, int32_t dtype, const int64_t* dims, int32_t ndim, const void* bytes, size_t nbytes,
                          int32_t rank, int32_t size, int64_t vocab, void* out, size_t out_cap, int64_t* out_dims,
                          size_t* out_bytes);
+/* How new K / V rows are rounded into the fp16 page pool. 1 (default): through the reference's Q8_0 cache rounding first
+ * (per 32 values: scale = amax / 127 held as f16, value = round(x / scale) * scale; forward/common.rs:336-348,449-538;
+ * applies when head_dim % 32 == 0, where the reference keeps a Q8_0 cache), so attention reads what the reference's
+ * cache yields; 0: plain fp16 rounding of the f32 values. Only while every sequence is empty. */
+int32_t sp_cuda_engine_set_kv_rounding(SpEngine* e, int32_t mode);
 /* Launch on this cudaStream_t instead of the engine's own stream (NULL restores it). */
 int32_t sp_cuda_engine_set_stream(SpEngine* e, void* stream);
 

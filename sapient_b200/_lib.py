@@ -52,6 +52,7 @@ SIGNATURES = {
     "sp_cuda_attention": (_i32, [_i32, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp]),
     "sp_cuda_attention_paged_static": (_i32, [_i32, _vp, _i32, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _i32, _i32,
                                               _i32, _i32, _vp]),
+    "sp_cuda_engine_set_kv_rounding": (_i32, [_vp, _i32]),
     "sp_cuda_engine_tp_handle": (_i32, [_vp, _vp, C.c_size_t]),
     "sp_cuda_engine_tp_connect": (_i32, [_vp, _vp, _i32]),
     "sp_cuda_engine_vocab_local": (_i32, [_vp, _vp, _vp]),

@@ -1,0 +1,155 @@
+"""Measurements of the other workload shapes of the hot path (bench.py covers batch-1 decode of the
+Llama-3-8B shape). One JSON line per case; synthetic seeded weights and token ids throughout.
+
+    python -m sapient_b200.configs_bench c0        Qwen2.5-0.5B shape, batch-1 greedy decode (128-token prompt, 128 steps)
+    python -m sapient_b200.configs_bench c2        Phi-2 shape, Q8_0: 512-token prefill, then 256 decode steps
+    python -m sapient_b200.configs_bench c3b32     Llama-3-8B shape, 32 sequences decoded together (prompt 256 by default)
+    python -m sapient_b200.configs_bench c4        speculative decoding, Qwen2.5-1.5B-shaped target + 0.5B-shaped draft, k = 4
+
+Rooflines: bytes one step must stream (every weight matrix once + the KV entries read) over the measured HBM copy
+bandwidth (MEASURED_PEAKS.json next to the package, else 6650 GB/s) and over 8 TB/s.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import time
+
+import numpy as np
+
+from . import speculative, synth
+from .engine import ForwardEngine
+
+
+def _peak():
+    p = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    try:
+        return float(json.load(open(p))["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+def _weight_bytes(cfg, W) -> int:
+    total = sum(raw.size for name, (dt, dims, raw) in W.items() if len(dims) == 2 and "embed_tokens" not in name)
+    if cfg.get("tied"):
+        total += W["model.embed_tokens.weight"][2].size
+    return int(total)
+
+
+def _build(name: str, max_ctx: int, seed: int):
+    import torch
+
+    cfg, W = synth.build_model(synth.CONFIGS[name], seed=seed, device="cuda", max_ctx=max_ctx)
+    Wn = synth.weights_to_numpy(W)
+    del W
+    torch.cuda.empty_cache()
+    return cfg, Wn
+
+
+def _timed(stream, fn):
+    import torch
+
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record(stream)
+    fn()
+    e1.record(stream)
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1)
+
+
+def _engine(cfg, W, **kw):
+    import torch
+
+    eng = ForwardEngine.from_weights(cfg, W, **kw)
+    stream = torch.cuda.Stream()
+    torch.cuda.set_stream(stream)
+    eng.set_stream(stream.cuda_stream)
+    return eng, stream
+
+
+def _roof(bytes_per_step: float, ms_per_step: float) -> dict:
+    peak, src = _peak()
+    gbs = bytes_per_step / 1e9 / (ms_per_step / 1e3)
+    return {"bytes_per_step": int(bytes_per_step), "achieved_gbs": gbs, "frac_of_measured_peak": gbs / peak, "peak_gbs": peak,
+            "peak_source": src, "frac_of_8TBs": gbs / 8000.0}
+
+
+def decode_case(name: str, prompt_len: int, steps: int, batch: int, label: str, prefill_timed: bool = False) -> dict:
+    cfg, W = _build(name, max_ctx=prompt_len + steps + 64, seed=1000)
+    eng, stream = _engine(cfg, W, max_batch=batch, max_tokens=256)
+    rng = np.random.default_rng(0)
+    first = np.empty(batch, np.uint32)
+    prefill_ms = 0.0
+    for s in range(batch):
+        ids = rng.integers(0, cfg["vocab"], prompt_len).astype(np.uint32)
+        out = {}
+
+        def run(ids=ids, s=s, out=out):
+            out["lg"] = eng.forward_slot(s, ids)
+
+        prefill_ms += _timed(stream, run)
+        first[s] = int(np.flatnonzero(out["lg"] == out["lg"].max())[-1])
+    warm = 8
+    toks = eng.decode_greedy(first, list(range(batch)), warm)
+    ms = _timed(stream, lambda: eng.decode_greedy(toks[-1], list(range(batch)), steps, fetch=False))
+    kv_per_pos = 2 * cfg["n_layers"] * cfg["n_kv_heads"] * cfg["head_dim"] * 2
+    ctx_mid = prompt_len + warm + steps // 2
+    step_bytes = _weight_bytes(cfg, W) + batch * ctx_mid * kv_per_pos
+    line = {"case": label, "model": name, "batch": batch, "prompt_len": prompt_len, "steps": steps, "ms_per_step": ms / steps,
+            "tokens_per_s": batch * steps / (ms / 1e3), "roofline": _roof(step_bytes, ms / steps), "data": "synthetic"}
+    if prefill_timed:
+        line["prefill_tokens_per_s"] = batch * prompt_len / (prefill_ms / 1e3)
+        line["prefill_ms"] = prefill_ms
+    eng.close()
+    return line
+
+
+def spec_case(k: int, prompt_len: int, new_tokens: int) -> dict:
+    tcfg, tW = _build("qwen15b", max_ctx=prompt_len + new_tokens + 64, seed=4000)
+    dcfg, dW = _build("qwen05b", max_ctx=prompt_len + new_tokens + 64, seed=4001)
+    rng = np.random.default_rng(0)
+    prompt = rng.integers(0, tcfg["vocab"], prompt_len).astype(np.uint32)
+    out = {"case": "c4", "target": "qwen15b", "draft": "qwen05b", "k": k, "prompt_len": prompt_len, "new_tokens": new_tokens,
+           "data": "synthetic (independent random models: drafts are accepted only by chance)"}
+    # target-only greedy through the same host API, as the yardstick
+    eng, stream = _engine(tcfg, tW, max_tokens=256)
+    lg = eng.forward_logits(prompt, True)
+    t0 = time.perf_counter()
+    for _ in range(new_tokens):
+        lg = eng.forward_logits([speculative.greedy(lg)], True)
+    out["target_only_tokens_per_s"] = new_tokens / (time.perf_counter() - t0)
+    eng.close()
+    for tag, cfg_d, W_d in (("independent_draft", dcfg, dW), ("draft_equals_target", tcfg, tW)):
+        target, _ = _engine(tcfg, tW, max_tokens=256)
+        draft, _ = _engine(cfg_d, W_d, max_tokens=256)
+        t0 = time.perf_counter()
+        toks, st = speculative.generate(target, draft, prompt, new_tokens, k=k, seed=0)
+        dt = time.perf_counter() - t0
+        out[tag] = {"tokens_per_s": len(toks) / dt, "rounds": st.rounds, "drafted": st.drafted, "accepted_drafts": st.accepted_drafts,
+                    "tokens_per_round": len(toks) / max(st.rounds, 1)}
+        target.close()
+        draft.close()
+    return out
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("case", choices=["c0", "c2", "c3b32", "c4"])
+    ap.add_argument("--prompt", type=int, default=None)
+    ap.add_argument("--steps", type=int, default=None)
+    a = ap.parse_args()
+    if a.case == "c0":
+        line = decode_case("qwen05b", a.prompt or 128, a.steps or 128, 1, "c0", prefill_timed=True)
+    elif a.case == "c2":
+        line = decode_case("phi2", a.prompt or 512, a.steps or 256, 1, "c2", prefill_timed=True)
+    elif a.case == "c3b32":
+        line = decode_case("llama8b", a.prompt or 256, a.steps or 64, 32, "c3b32", prefill_timed=True)
+    else:
+        line = spec_case(4, a.prompt or 256, a.steps or 128)
+    print(json.dumps(line), flush=True)
+
+
+if __name__ == "__main__":
+    main()

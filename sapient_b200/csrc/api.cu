@@ -123,6 +123,19 @@ int32_t sp_cuda_device_count(void) {
 
 uint64_t sp_cuda_launch_count(void) { return launch_count(); }
 
+int32_t sp_cuda_engine_set_kv_rounding(SpEngine* e, int32_t mode) {
+    API_BEGIN
+    if (!e || mode < 0 || mode > 1) { set_error("bad argument"); return SP_ERR_ARG; }
+    for (int len : e->e->seq_len)
+        if (len != 0) { set_error("set_kv_rounding: the KV cache is not empty"); return SP_ERR_STATE; }
+    if (e->e->kv_round != mode) {
+        e->e->kv_round = mode;
+        e->e->drop_graphs();
+    }
+    return SP_OK;
+    API_END
+}
+
 int32_t sp_cuda_engine_tp_handle(SpEngine* e, void* out, size_t cap) {
     API_BEGIN
     if (!e) { set_error("null engine"); return SP_ERR_ARG; }

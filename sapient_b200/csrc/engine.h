@@ -80,6 +80,7 @@ class Engine {
     int tp_handle(void* out, size_t cap);           // CUDA IPC handle of this rank's communication block
     int tp_connect(const void* handles, int n);     // map every rank's block (handles in rank order)
     int tp_check();                                 // SP_ERR_COMM if a wait on a peer gave up
+    void drop_graphs();                             // forget the captured step graphs (a launch parameter changed)
     int vocab_local() const { return vocab_l_; }
 
     SpModelDesc d, g;
@@ -87,7 +88,10 @@ class Engine {
     bool finalized = false;
     bool trace_on = false;
     bool use_graphs = true;
-    bool use_tc5 = true;   // large-M GEMM on tcgen05 (false: always the 16-row GEMV passes)
+    bool use_tc5 = true;
+    // 1 (default): new K / V rows get the reference's Q8_0 cache rounding before they are stored as fp16 (head_dim % 32
+    // == 0, where the reference keeps a Q8_0 cache); 0: plain fp16 rounding. Change only while the caches are empty.
+    int kv_round = 1;   // large-M GEMM on tcgen05 (false: always the 16-row GEMV passes)
     bool profile_on = false;
     std::vector<int> seq_len;
     uint64_t weight_bytes = 0, kv_bytes = 0;

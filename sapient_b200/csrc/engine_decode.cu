@@ -82,6 +82,13 @@ void Engine::profile_reset() {
     for (int i = 0; i < F_COUNT; ++i) { prof_ms_[i] = 0; prof_n_[i] = 0; }
 }
 
+void Engine::drop_graphs() {
+    if (stream) cudaStreamSynchronize(stream);
+    for (auto& g : step_graphs_) cudaGraphExecDestroy(g.second);
+    step_graphs_.clear();
+    step_graph_kernels_.clear();
+}
+
 int Engine::launch_decode_step(int T) {
     if (!use_graphs || profile_on || trace_on) return enqueue_decode_step(T);
     auto it = step_graphs_.find(T);

@@ -157,7 +157,7 @@ int Engine::layer_llama(const LayerW& w, int l, int T) {
         SP_TRY(gemv(h_, hid, T, hid, w.q, w.qb, qkv_, qkv_ld, w.k, w.kb, qkv_ + (size_t)H * hd, w.v, w.vb,
                     qkv_ + (size_t)(H + Hkv) * hd));
     }
-    SP_LAUNCH(F_ROPE, launch_rope_kv_append(qkv_, T, H, Hkv, hd, d.rotary_dim, cos_sin_, d_tok_slot_, d_tok_pos_, kv_, l, stream));
+    SP_LAUNCH(F_ROPE, launch_rope_kv_append(qkv_, T, H, Hkv, hd, d.rotary_dim, cos_sin_, d_tok_slot_, d_tok_pos_, kv_, l, kv_round, stream));
     SP_TRY(attention_and_oproj(w, l, T));
     if (all_tiled(w.gate, w.up) && plan_digits(T, hid, ia)) {
         SP_LAUNCH(F_NORM, launch_norm_quant(x_, hid, w.n2w, nullptr, false, d.norm_eps, nullptr, 0, ia, stream, tp_take()));
@@ -193,7 +193,7 @@ int Engine::layer_phi(const LayerW& w, int l, int T) {
                     qkv_ + (size_t)(H + Hkv) * hd));
         SP_TRY(gemv(h_, hid, T, hid, w.up, w.upb, gu_, ffn));
     }
-    SP_LAUNCH(F_ROPE, launch_rope_kv_append(qkv_, T, H, Hkv, hd, d.rotary_dim, cos_sin_, d_tok_slot_, d_tok_pos_, kv_, l, stream));
+    SP_LAUNCH(F_ROPE, launch_rope_kv_append(qkv_, T, H, Hkv, hd, d.rotary_dim, cos_sin_, d_tok_slot_, d_tok_pos_, kv_, l, kv_round, stream));
     // the MLP's fc1 output waits in gu_ while the workspace serves the attention output projection
     SP_TRY(attention_and_oproj(w, l, T));
     if (all_tiled(w.down) && plan_digits(T, ffn, ia)) {

@@ -335,9 +335,14 @@ __device__ __forceinline__ int64_t kv_offset(const KvGeom& kv, int layer, int pa
     return ((((int64_t)layer * kv.n_pages + page) * 2 + which) * kv.n_kv + head) * (int64_t)(KV_PAGE * kv.head_dim);
 }
 
+// kv_round != 0 (head_dim % 32 == 0): before the fp16 store every 32-element block of the new K / V row goes through
+// the reference's Q8_0 cache rounding (scale = amax / 127 kept as f16, value = round(x / scale) * scale;
+// crates/sapient-models/src/forward/common.rs:336-348,449-538), so attention sees the values the reference's
+// quantised cache yields (to one extra fp16 rounding, 2^-12 relative).
 __global__ void rope_kv_append_kernel(float* __restrict__ qkv, int n_heads, int n_kv, int head_dim, int rotary_dim,
                                       const float2* __restrict__ cos_sin, const int32_t* __restrict__ tok_slot,
-                                      const int32_t* __restrict__ tok_pos, KvGeom kv, int layer) {
+                                      const int32_t* __restrict__ tok_pos, KvGeom kv, int layer, int kv_round) {
+    __shared__ float sh_row[256];
     pdl_wait();
     pdl_trigger();
     const int t = blockIdx.x, j = blockIdx.y;
@@ -365,17 +370,33 @@ __global__ void rope_kv_append_kernel(float* __restrict__ qkv, int n_heads, int 
             i0 = rotary_dim + 2 * (p - half); i1 = i0 + 1;
             o0 = v[i0]; o1 = v[i1];
         }
-        if (dst) { dst[i0] = __float2half_rn(o0); dst[i1] = __float2half_rn(o1); }
+        if (dst && kv_round) { sh_row[i0] = o0; sh_row[i1] = o1; }
+        else if (dst) { dst[i0] = __float2half_rn(o0); dst[i1] = __float2half_rn(o1); }
         else { v[i0] = o0; v[i1] = o1; }
+    }
+    if (dst && kv_round) {  // block-uniform
+        __syncthreads();
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
+        for (int b = warp; b < head_dim / 32; b += n_warps) {
+            const float x = sh_row[b * 32 + lane];
+            const float amax = warp_max(fabsf(x));
+            const float scale = amax / 127.0f;
+            const float inv = scale > 0.0f ? 1.0f / scale : 0.0f;
+            float r = roundf(x * inv);  // half away from zero, like f32::round
+            r = fminf(fmaxf(r, -127.0f), 127.0f);
+            const float d = __half2float(__float2half_rn(scale));
+            dst[b * 32 + lane] = __float2half_rn(__fmul_rn(r, d));
+        }
     }
 }
 
 cudaError_t launch_rope_kv_append(float* qkv, int n_tok, int n_heads, int n_kv, int head_dim, int rotary_dim,
                                   const float2* cos_sin, const int32_t* tok_slot, const int32_t* tok_pos, KvGeom kv,
-                                  int layer, cudaStream_t st) {
+                                  int layer, int kv_round, cudaStream_t st) {
     if (n_tok == 0) return cudaSuccess;
+    if (head_dim % 32 != 0 || head_dim > 256) kv_round = 0;
     cudaError_t le = launch_pdl(rope_kv_append_kernel, dim3(n_tok, n_heads + 2 * n_kv), dim3(64), 0, st, qkv, n_heads, n_kv, head_dim,
-                                rotary_dim, cos_sin, tok_slot, tok_pos, kv, layer);
+                                rotary_dim, cos_sin, tok_slot, tok_pos, kv, layer, kv_round);
     if (le != cudaSuccess) return le;
     return finish_launch();
 }

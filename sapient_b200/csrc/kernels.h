@@ -106,7 +106,7 @@ cudaError_t launch_layer_norm(const float* x, const float* w, const float* b, in
 // written as fp16 into the paged cache at (slot, pos) of each token.
 cudaError_t launch_rope_kv_append(float* qkv, int n_tok, int n_heads, int n_kv, int head_dim, int rotary_dim,
                                   const float2* cos_sin, const int32_t* tok_slot, const int32_t* tok_pos, KvGeom kv,
-                                  int layer, cudaStream_t st);
+                                  int layer, int kv_round, cudaStream_t st);
 // Rotation only (no cache): x[T, n_heads*hd] in place. Used by the standalone RoPE op.
 cudaError_t launch_rope(float* x, int n_tok, int n_heads, int head_dim, int rotary_dim, const float2* cos_sin,
                         const int32_t* tok_pos, int ld, cudaStream_t st);

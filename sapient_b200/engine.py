@@ -201,6 +201,11 @@ class ForwardEngine:
         check(lib().sp_cuda_decode_greedy(self._h, _p(ids), _p(sl), ids.size, steps, _p(out) if fetch else None))
         return out
 
+    def set_kv_rounding(self, reference_q8_0: bool) -> None:
+        """True (default): new K / V rows go through the reference's Q8_0 cache rounding before the fp16 store;
+        False: plain fp16. Only while the cache is empty."""
+        check(lib().sp_cuda_engine_set_kv_rounding(self._h, int(reference_q8_0)))
+
     def synchronize(self) -> None:
         check(lib().sp_cuda_engine_synchronize(self._h))
 

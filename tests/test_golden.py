@@ -58,6 +58,7 @@ def test_cuda_matches_golden_logits(name):
     eng = ForwardEngine.from_weights(cfg, W)
     for tag, bar in (("f16", 2e-3), ("ref", 2e-2)):
         eng.reset_cache()
+        eng.set_kv_rounding(tag == "ref")  # "f16": the oracle run with an fp16-rounded cache; "ref": the reference's Q8_0 cache
         got = [eng.forward_logits(G[f"{name}_ids"], True)]
         for t in G[f"{name}_tokens_{tag}"]:
             got.append(eng.forward_logits([t], True))
