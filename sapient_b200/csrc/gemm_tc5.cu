@@ -1,22 +1,29 @@
 // Large-M dequant GEMM on the 5th-generation tensor cores (tcgen05 + TMEM), for prefill and batched decode.
 //
-// y[m, n] = sum_k x[m, k] * W[n, k] for m >= 64 activation rows. The GEMV kernel (gemv_imma.cu) streams the whole
-// weight matrix once per 16 activation rows; here a CTA dequantises each weight tile ONCE and multiplies it with up to
-// 256 activation rows:
-//   * CTA tile: 128 weight rows (the MMA's M) x NB <= 256 activation rows (the MMA's N), K walked in chunks of 64;
-//   * per chunk the 512 threads rebuild 128 x 64 weights from the tile-repacked ggml blocks (the same layout the GEMV
-//     reads, gemv_imma.cuh) — exact f32 dequantisation, rounded once to fp16 — into shared memory in the K-major
-//     128-byte-swizzled layout the tensor core reads, and copy the matching 64 columns of the fp16 activations; the
-//     global loads of the next chunk are issued into registers before the current one is handed to the tensor core;
-//   * one thread issues four tcgen05.mma (128 x NB x 16, kind::f16, fp32 accumulation in tensor memory) and commits
-//     them to an mbarrier; two shared-memory stages let the next chunk be rebuilt while the MMAs run;
-//   * epilogue: tcgen05.ld brings the accumulators back (one weight row per thread, 16 activation rows per
+// y[m, n] = sum_k x[m, k] * W[n, k] for m >= TC5_MIN_M activation rows. The GEMV kernel (gemv_imma.cu) streams the whole
+// weight matrix once per 16 activation rows and its instruction count grows with the row count; here a CTA rebuilds
+// each weight tile ONCE, as fp16, and the tensor core multiplies it with up to 256 activation rows:
+//   * CTA tile: 128 weight rows (the MMA's M) x NB <= 256 activation rows (the MMA's N), K walked in chunks of 128
+//     through a ring of 2-4 shared-memory stages;
+//   * 16 producer warps, two per 16-row tile of the CTA tile (one per 64-column group of the stage): each lane reads the 16-byte pieces the tiled layout holds
+//     for it (coalesced) — 32 weights, rows g and g+8. It fetches the raw words of the NEXT chunk from the
+//     tile-repacked ggml blocks (the layout the GEMV reads, gemv_imma.cuh), waits for the stage to be
+//     free (mbarrier `empty`), converts the current words to fp16 (quants become exact floats by the 2^23 bit trick,
+//     one f32 multiply-add applies scale and minimum, one rounding to fp16), stores
+//     them in the K-major 128-byte-swizzled layout the tensor core reads, copies its share of the fp16 activations,
+//     and arrives on the stage's `full` mbarrier;
+//   * 1 thread issues, per chunk, eight tcgen05.mma (128 x NB x 16, kind::f16, fp32 accumulation in tensor memory)
+//     and commits them to the stage's `empty` mbarrier — no block-wide barrier anywhere in the loop;
+//   * 4 epilogue warps: tcgen05.ld brings the accumulators back (one weight row per thread, 16 activation rows per
 //     instruction), bias / residual are added and y is written with n contiguous across the warp.
-// fp16 rather than bf16 operands: same instruction kind and rate, and the 11-bit significand keeps the result
-// within 2e-4 relative L2 of the f32 reference (bf16 would sit at ~2e-3, above the 1e-3 parity bar).
+// fp16 rather than bf16 operands: same instruction kind and rate, and the 11-bit significand keeps the result within
+// ~2e-4 relative L2 of the f32 reference (bf16 would sit at ~2e-3, above the 1e-3 parity bar). Each weight is computed
+// in f32 from exact operands and rounded to fp16 once (Q8_0: the exact product of int8 and f16 scale, in half2).
 // Every wait on an mbarrier is bounded; on expiry the kernel raises g_tc5_timeout, still frees its tensor memory
 // and returns.
 #include <cuda_fp16.h>
+
+#include <algorithm>
 
 #include "kernels.h"
 #include "pdl.cuh"
@@ -26,14 +33,17 @@ namespace sp {
 
 cudaError_t count_launch_and_check();  // kernels.cu
 
-constexpr int TC5_THREADS = 512;
+constexpr int TC5_PRODUCER_WARPS = 16;        // two per 16-row tile: one per 64-column group of the stage
+constexpr int TC5_EPILOGUE_WARPS = 4;          // warp TC5_PRODUCER_WARPS, lane 0 also issues the MMAs
+constexpr int TC5_THREADS = 32 * (TC5_PRODUCER_WARPS + TC5_EPILOGUE_WARPS);
+constexpr int TC5_PRODUCERS = 32 * TC5_PRODUCER_WARPS;
+constexpr int TC5_MAX_STAGES = 4;
 constexpr int TC5_BM = 128;                    // weight rows per CTA
-constexpr int TC5_BK = 64;                     // columns per chunk = one 128-byte swizzle row of fp16
+constexpr int TC5_BK = 128;                    // columns per stage = two 128-byte swizzle rows of fp16 (two sub-tiles)
 constexpr int TC5_NB_MAX = 256;                // activation rows per CTA
-constexpr int TC5_A_BYTES = TC5_BM * 128;      // 16 KB
-constexpr int TC5_B_BYTES = TC5_NB_MAX * 128;  // 32 KB
-constexpr int TC5_STAGE_BYTES = TC5_A_BYTES + TC5_B_BYTES;
-constexpr int TC5_SMEM = 2 * TC5_STAGE_BYTES + 1024;  // + slack to align the stages to 1024 B
+constexpr int TC5_A_SUB = TC5_BM * 128;        // one 64-column sub-tile of the weights: 16 KB
+constexpr int TC5_A_BYTES = 2 * TC5_A_SUB;
+constexpr int TC5_SMEM_LIMIT = 200 * 1024;
 constexpr int TC5_SPIN_LIMIT = 1 << 22;
 
 __device__ int g_tc5_timeout = 0;
@@ -66,6 +76,14 @@ __device__ __forceinline__ void tc5_mma(uint32_t d_tmem, uint64_t adesc, uint64_
         : "memory");
 }
 
+__device__ __forceinline__ void tc5_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(tc5_smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void tc5_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(tc5_smem_u32(bar)) : "memory");
+}
+
 __device__ __forceinline__ bool tc5_wait(uint64_t* bar, uint32_t parity) {
     const uint32_t a = tc5_smem_u32(bar);
     for (int i = 0; i < TC5_SPIN_LIMIT; ++i) {
@@ -87,77 +105,132 @@ __device__ __forceinline__ bool tc5_wait(uint64_t* bar, uint32_t parity) {
 __device__ __forceinline__ uint32_t pack_h2(float a, float b) {
     return (uint32_t)__half_as_ushort(__float2half_rn(a)) | ((uint32_t)__half_as_ushort(__float2half_rn(b)) << 16);
 }
+__device__ __forceinline__ __half2 h2_bits(uint32_t u) { return *reinterpret_cast<__half2*>(&u); }
+__device__ __forceinline__ uint32_t bits_h2(__half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
 
-// The raw words one thread needs for 16 consecutive columns — sixteenth-block (hh, h16) of 64-column group cq — of weight
-// row rr of a 16-row tile: fetched one chunk ahead (tc5_load), turned into f32 weights when the stage is free
-// (tc5_compute). hh selects the 32-column sub-block (low / high nibbles), h16 its first or second 16 columns.
+// Bytes 0 and 2 (resp. 1 and 3) of v, each below 1024, as exact halves: the bit pattern 0x6400 | n is the half 1024 + n.
+__device__ __forceinline__ __half2 bytes02(uint32_t v, uint32_t mask, float bias) {
+    return __hsub2(h2_bits((v & mask) | 0x64006400u), __float2half2_rn(bias));
+}
+
+// Producer warp w of the CTA rebuilds 16-row tile w of the CTA's 8 tiles; lane (g = lane / 4, t = lane % 4) reads, per
+// 64-column chunk, exactly the 16-byte pieces the tile layout stores for it (coalesced: 512 B per warp and piece) and
+// gets 32 weights: rows g and g + 8, eight runs of 4 consecutive columns. Raw words are fetched one chunk ahead.
 struct Tc5Raw {
-    uint32_t w[8];  // Q4_K / Q8_0: 4 words of nibbles / int8; Q6_K: 4 ql words + 4 qh words
-    uint4 hdr;      // Q4_K: d|dmin, 12 scale bytes; Q6_K: x = int8 scale, y = d bits; Q8_0: x = d bits
+    uint4 q[3];     // Q4_K: q[0]; Q8_0: q[0], q[1] (two 32-blocks); Q6_K: three pieces = the 12 words of the chunk's half
+    uint4 hdr[2];   // rows g / g+8 — Q4_K: d|dmin + 12 scale bytes; Q6_K: 16 int8 scales; Q8_0: x = d of block 0 | block 1 << 16
+    uint32_t dd;    // Q6_K: d of row g | d of row g+8 << 16
 };
 
 template <int DT>
-__device__ __forceinline__ void tc5_load(const uint8_t* tile, int rr, int cq, int hh, int h16, Tc5Raw& r) {
-    const int g = rr & 7, hi8 = rr >> 3;
-    const uint32_t* w32 = reinterpret_cast<const uint32_t*>(tile);
+__device__ __forceinline__ void tc5_load(const uint8_t* tile, int lane, int cq, Tc5Raw& r) {
+    const int g = lane >> 2;
     if (DT == T_Q4_K) {
-        r.hdr = __ldg(reinterpret_cast<const uint4*>(tile + 2048 + rr * 16));
-#pragma unroll
-        for (int t = 0; t < 4; ++t) r.w[t] = __ldg(w32 + cq * 128 + (g * 4 + t) * 4 + hi8 * 2 + h16);
+        r.q[0] = __ldg(reinterpret_cast<const uint4*>(tile + cq * 512 + lane * 16));
+        r.hdr[0] = __ldg(reinterpret_cast<const uint4*>(tile + 2048 + g * 16));
+        r.hdr[1] = __ldg(reinterpret_cast<const uint4*>(tile + 2048 + (g + 8) * 16));
     } else if (DT == T_Q8_0) {
-        const int bb = 2 * cq + hh;
-        r.hdr.x = __ldg(reinterpret_cast<const uint16_t*>(tile + 4096 + (rr * 8 + bb) * 2));
+        r.q[0] = __ldg(reinterpret_cast<const uint4*>(tile + (2 * cq) * 512 + lane * 16));
+        r.q[1] = __ldg(reinterpret_cast<const uint4*>(tile + (2 * cq + 1) * 512 + lane * 16));
+        r.hdr[0].x = __ldg(reinterpret_cast<const uint32_t*>(tile + 4096 + (g * 8 + 2 * cq) * 2));        // d of blocks 2cq, 2cq+1
+        r.hdr[1].x = __ldg(reinterpret_cast<const uint32_t*>(tile + 4096 + ((g + 8) * 8 + 2 * cq) * 2));
+    } else {
+        const int half = cq >> 1;
 #pragma unroll
-        for (int t = 0; t < 4; ++t) r.w[t] = __ldg(w32 + bb * 128 + (g * 4 + t) * 4 + hi8 * 2 + h16);
-    } else {  // Q6_K: h16 is p of the block layout (l = 16 p + 4 t + b)
-        const int half = cq >> 1, quarter = 2 * (cq & 1) + hh;
-        const int8_t* scales = reinterpret_cast<const int8_t*>(tile + 3072 + rr * 16);
-        r.hdr.x = (uint32_t)(uint8_t)__ldg(scales + 8 * half + h16 + 2 * quarter);
-        r.hdr.y = __ldg(reinterpret_cast<const uint16_t*>(tile + 3328 + rr * 2));
-        const int cc = (half << 1) | h16;
-        const int sl = 6 * cc + (hh ? 1 : 0) + hi8 * 3, sh = 6 * cc + 2 + hi8 * 3;
-#pragma unroll
-        for (int t = 0; t < 4; ++t) {
-            r.w[t] = __ldg(w32 + (sl >> 2) * 128 + (g * 4 + t) * 4 + (sl & 3));
-            r.w[4 + t] = __ldg(w32 + (sh >> 2) * 128 + (g * 4 + t) * 4 + (sh & 3));
-        }
+        for (int i = 0; i < 3; ++i) r.q[i] = __ldg(reinterpret_cast<const uint4*>(tile + (3 * half + i) * 512 + lane * 16));
+        r.hdr[0] = __ldg(reinterpret_cast<const uint4*>(tile + 3072 + g * 16));
+        r.hdr[1] = __ldg(reinterpret_cast<const uint4*>(tile + 3072 + (g + 8) * 16));
+        const uint16_t* dp = reinterpret_cast<const uint16_t*>(tile + 3328);
+        r.dd = (uint32_t)__ldg(dp + g) | ((uint32_t)__ldg(dp + g + 8) << 16);
     }
 }
 
-// Exact f32 dequantisation (every product rounded separately, as the reference does) of the 16 columns.
+// Stores 4 consecutive fp16 weights (columns c0 .. c0+3 of the chunk, c0 % 4 == 0) of CTA-tile row `row` into the
+// swizzled K-major stage: e02 holds columns (c0, c0+2), e13 columns (c0+1, c0+3).
+__device__ __forceinline__ void tc5_store4(uint8_t* As, int row, int c0, __half2 e02, __half2 e13) {
+    const uint2 v = make_uint2(__byte_perm(bits_h2(e02), bits_h2(e13), 0x5410), __byte_perm(bits_h2(e02), bits_h2(e13), 0x7632));
+    *reinterpret_cast<uint2*>(As + row * 128 + ((((c0 >> 3) ^ (row & 7))) << 4) + (c0 & 4) * 2) = v;
+}
+
+// The same from four f32 values (one rounding to fp16 each).
+__device__ __forceinline__ void tc5_store4f(uint8_t* As, int row, int c0, float f0, float f1, float f2, float f3) {
+    const uint2 v = make_uint2(bits_h2(__floats2half2_rn(f0, f1)), bits_h2(__floats2half2_rn(f2, f3)));
+    *reinterpret_cast<uint2*>(As + row * 128 + ((((c0 >> 3) ^ (row & 7))) << 4) + (c0 & 4) * 2) = v;
+}
+
+// Byte b (< 256) of v as an exact f32: 0x4B000000 | n is the float 2^23 + n.
+__device__ __forceinline__ float byte_f32(uint32_t v, int b) {
+    return __uint_as_float(__byte_perm(v, 0x4B000000u, 0x7540 | b)) - 8388608.0f;
+}
+
+__device__ __forceinline__ uint32_t u4_word(const uint4& v, int i) { return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w; }
+
+// Converts the raw words of chunk group cq to fp16 and stores the thread's 32 weights; row0 = first CTA-tile row of
+// the warp's 16-row tile.
 template <int DT>
-__device__ __forceinline__ void tc5_compute(const Tc5Raw& r, int cq, int hh, float (&v)[16]) {
+__device__ __forceinline__ void tc5_convert_store(const Tc5Raw& r, int lane, int cq, int row0, uint8_t* As) {
+    const int g = lane >> 2, t = lane & 3;
     if (DT == T_Q4_K) {
-        const float d = half_bits_to_float((uint16_t)(r.hdr.x & 0xFFFFu)), dmin = half_bits_to_float((uint16_t)(r.hdr.x >> 16));
-        uint32_t sc, mn;
-        k4_scale_min(r.hdr.y, r.hdr.z, r.hdr.w, 2 * cq + hh, &sc, &mn);
-        const float dl = __fmul_rn(d, (float)sc), ml = __fmul_rn(dmin, (float)mn);
 #pragma unroll
-        for (int t = 0; t < 4; ++t)
+        for (int hi8 = 0; hi8 < 2; ++hi8) {
+            const uint4 hd = r.hdr[hi8];
+            const float d = half_bits_to_float((uint16_t)(hd.x & 0xFFFFu)), dmin = half_bits_to_float((uint16_t)(hd.x >> 16));
+            const int row = row0 + g + 8 * hi8;
 #pragma unroll
-            for (int b = 0; b < 4; ++b) {
-                const uint32_t byte = (r.w[t] >> (8 * b)) & 0xFFu;
-                const float q = (float)(hh ? (byte >> 4) : (byte & 15u));
-                v[4 * t + b] = __fsub_rn(__fmul_rn(dl, q), ml);
+            for (int hh = 0; hh < 2; ++hh) {  // low nibbles: sub-block 2 cq, high nibbles: 2 cq + 1
+                uint32_t sc, mn;
+                k4_scale_min(hd.y, hd.z, hd.w, 2 * cq + hh, &sc, &mn);
+                // d * sc and dmin * mn are exact in f32 (11-bit x 6-bit), the fused multiply-add rounds dl * q - ml once
+                const float dl = d * (float)sc, nml = -(dmin * (float)mn);
+#pragma unroll
+                for (int h16 = 0; h16 < 2; ++h16) {
+                    const uint32_t w = u4_word(r.q[0], 2 * hi8 + h16);
+                    const uint32_t v = (hh ? (w >> 4) : w) & 0x0F0F0F0Fu;
+                    tc5_store4f(As, row, 32 * hh + 16 * h16 + 4 * t, fmaf(byte_f32(v, 0), dl, nml), fmaf(byte_f32(v, 1), dl, nml),
+                                fmaf(byte_f32(v, 2), dl, nml), fmaf(byte_f32(v, 3), dl, nml));
+                }
             }
+        }
     } else if (DT == T_Q8_0) {
-        const float d = half_bits_to_float((uint16_t)r.hdr.x);
 #pragma unroll
-        for (int t = 0; t < 4; ++t)
+        for (int hi8 = 0; hi8 < 2; ++hi8) {
+            const int row = row0 + g + 8 * hi8;
 #pragma unroll
-            for (int b = 0; b < 4; ++b) v[4 * t + b] = __fmul_rn((float)(int8_t)((r.w[t] >> (8 * b)) & 0xFFu), d);
-    } else {  // Q6_K
-        const int quarter = 2 * (cq & 1) + hh;
-        const float dsc = __fmul_rn(half_bits_to_float((uint16_t)r.hdr.y), (float)(int8_t)(r.hdr.x & 0xFFu));
+            for (int blk = 0; blk < 2; ++blk) {
+                const __half2 d = __half2half2(__ushort_as_half((uint16_t)(r.hdr[hi8].x >> (16 * blk))));
 #pragma unroll
-        for (int t = 0; t < 4; ++t)
-#pragma unroll
-            for (int b = 0; b < 4; ++b) {
-                const uint32_t lb = (r.w[t] >> (8 * b)) & 0xFFu, hb = (r.w[4 + t] >> (8 * b)) & 0xFFu;
-                const uint32_t nib = (cq & 1) ? (lb >> 4) : (lb & 15u);
-                const int q = (int)(nib | (((hb >> (2 * quarter)) & 3u) << 4)) - 32;
-                v[4 * t + b] = __fmul_rn(dsc, (float)q);
+                for (int h16 = 0; h16 < 2; ++h16) {
+                    const uint32_t v = u4_word(r.q[blk], 2 * hi8 + h16) ^ 0x80808080u;  // int8 -> offset-128 unsigned
+                    tc5_store4(As, row, 32 * blk + 16 * h16 + 4 * t, __hmul2(bytes02(v, 0x00FF00FFu, 1152.f), d),
+                               __hmul2(bytes02(v >> 8, 0x00FF00FFu, 1152.f), d));
+                }
             }
+        }
+    } else {  // Q6_K
+        const int half = cq >> 1, odd = cq & 1;
+#pragma unroll
+        for (int hi8 = 0; hi8 < 2; ++hi8) {
+            const int row = row0 + g + 8 * hi8;
+            const float d = half_bits_to_float((uint16_t)(r.dd >> (16 * hi8)));
+            const uint4 sw = r.hdr[hi8];
+#pragma unroll
+            for (int p = 0; p < 2; ++p) {
+                // the 12 words of the half: for p = 0, 1: qlA_g, qlB_g, qh_g, qlA_g8, qlB_g8, qh_g8
+                const int base = 6 * p + 3 * hi8;
+                const uint32_t qh = u4_word(r.q[(base + 2) >> 2], (base + 2) & 3);
+#pragma unroll
+                for (int ab = 0; ab < 2; ++ab) {  // qlA: columns l, qlB: columns 32 + l  (l = 16 p + 4 t + b)
+                    const uint32_t ql = u4_word(r.q[(base + ab) >> 2], (base + ab) & 3);
+                    const int quarter = 2 * odd + ab;
+                    const int si = 8 * half + p + 2 * quarter;  // int8 scale index of the row
+                    const float scf = (float)(int8_t)((u4_word(sw, si >> 2) >> (8 * (si & 3))) & 0xFFu);
+                    const float dsc = d * scf;  // exact in f32 (11-bit x 8-bit); dsc * q rounds once
+                    const uint32_t q = ((odd ? (ql >> 4) : ql) & 0x0F0F0F0Fu) | (((qh >> (2 * quarter)) & 0x03030303u) << 4);
+                    tc5_store4f(As, row, 32 * ab + 16 * p + 4 * t, dsc * (byte_f32(q, 0) - 32.0f), dsc * (byte_f32(q, 1) - 32.0f),
+                                dsc * (byte_f32(q, 2) - 32.0f), dsc * (byte_f32(q, 3) - 32.0f));
+                }
+            }
+        }
     }
 }
 
@@ -171,30 +244,36 @@ struct Tc5Args {
     const float* bias;  // [n] or null
     const float* res;   // [m][ldres] or null (may alias y)
     int ldres;
+    int stage_bytes;    // TC5_A_BYTES + 256 * (widest activation tile of the launch, rounded to 16)
+    int stages;         // ring depth that fits shared memory (2..4)
 };
 
 template <int DT>
 __global__ void __launch_bounds__(TC5_THREADS, 1) gemm_tc5_kernel(const Tc5Args a) {
     extern __shared__ uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t mbar[2];
+    __shared__ __align__(8) uint64_t full[TC5_MAX_STAGES], empty[TC5_MAX_STAGES], done_bar;
     __shared__ uint32_t tmem_slot;
     constexpr int TILE_BYTES = DT == T_Q4_K ? Q4_K_TILE_BYTES : DT == T_Q6_K ? Q6_K_TILE_BYTES : 8 * 544;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     uint8_t* smem = smem_raw + ((1024u - (tc5_smem_u32(smem_raw) & 1023u)) & 1023u);
     const int n0 = blockIdx.x * TC5_BM, m0 = blockIdx.y * TC5_NB_MAX;
     const int rows_here = min(TC5_NB_MAX, a.m - m0);
-    const int nb = (rows_here + 15) & ~15;                       // the MMA's N
+    const int nb = (rows_here + 15) & ~15;  // the MMA's N
     const int tmem_cols = nb <= 32 ? 32 : nb <= 64 ? 64 : nb <= 128 ? 128 : 256;
     const int kts = a.k >> 8, n_tile_rows = (a.n + 15) >> 4;
+    const int n_chunks = a.k / TC5_BK;
 
-    if (warp == 0) {
+    if (warp == TC5_PRODUCER_WARPS) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tc5_smem_u32(&tmem_slot)), "r"(tmem_cols)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
     }
     if (tid == 0) {
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(tc5_smem_u32(&mbar[0])) : "memory");
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(tc5_smem_u32(&mbar[1])) : "memory");
+        for (int s = 0; s < a.stages; ++s) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(tc5_smem_u32(&full[s])), "r"(TC5_PRODUCER_WARPS) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(tc5_smem_u32(&empty[s])) : "memory");
+        }
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(tc5_smem_u32(&done_bar)) : "memory");
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
@@ -204,108 +283,107 @@ __global__ void __launch_bounds__(TC5_THREADS, 1) gemm_tc5_kernel(const Tc5Args 
     pdl_wait();  // activations come from the previous kernel
     pdl_trigger();
 
-    const int row = tid >> 2, hh = (tid >> 1) & 1, h16 = tid & 1;  // this thread's weight row of the tile and 16-column slice
-    const int rt = (n0 >> 4) + (row >> 4), rr = row & 15;
-    const bool row_live = rt < n_tile_rows;
-    const uint8_t* tile_row = a.wt + (int64_t)rt * kts * TILE_BYTES;
-    const uint32_t idesc = tc5_idesc(nb);
-    const int n_chunks = a.k / TC5_BK;
     bool ok = true;
-    constexpr int B_PER_THREAD = TC5_NB_MAX * 8 / TC5_THREADS;  // 16-byte pieces of the activation tile per thread
-    Tc5Raw raw;
-    uint4 braw[B_PER_THREAD];
-    auto fetch = [&](int c) {  // global loads of chunk c into registers
-        if (row_live) tc5_load<DT>(tile_row + (int64_t)(c >> 2) * TILE_BYTES, rr, c & 3, hh, h16, raw);
+    if (warp < TC5_PRODUCER_WARPS) {
+        // ── producers: warps 2 w and 2 w + 1 rebuild 16-row tile w of the CTA's eight, one 64-column group each ──
+        const int tile_w = warp >> 1, sub = warp & 1;
+        const int rt = (n0 >> 4) + tile_w;
+        const bool row_live = rt < n_tile_rows;
+        const uint8_t* tile_row = a.wt + (int64_t)rt * kts * TILE_BYTES;
+        constexpr int B_PER_THREAD = TC5_NB_MAX * 16 / TC5_PRODUCERS;  // 16-byte pieces of the activation tile per thread
+        Tc5Raw raw;
+        uint4 braw[B_PER_THREAD];
+        auto fetch = [&](int c) {  // global loads of stage-chunk c into registers (group 2 c + sub of the row's superblocks)
+            const int grp = 2 * c + sub;
+            if (row_live) tc5_load<DT>(tile_row + (int64_t)(grp >> 2) * TILE_BYTES, lane, grp & 3, raw);
 #pragma unroll
-        for (int i = 0; i < B_PER_THREAD; ++i) {
-            const int idx = tid + i * TC5_THREADS, r = idx >> 3, ch = idx & 7;
-            braw[i] = make_uint4(0u, 0u, 0u, 0u);
-            if (idx < nb * 8 && m0 + r < a.m)
-                braw[i] = __ldg(reinterpret_cast<const uint4*>(a.xh + (int64_t)(m0 + r) * a.k + (int64_t)c * TC5_BK + ch * 8));
-        }
-    };
-    fetch(0);
-    for (int c = 0; c < n_chunks; ++c) {
-        const int s = c & 1;
-        uint8_t* As = smem + s * TC5_STAGE_BYTES;
-        uint8_t* Bs = As + TC5_A_BYTES;
-        if (c >= 2) ok = tc5_wait(&mbar[s], (uint32_t)(((c >> 1) - 1) & 1)) && ok;  // the MMAs of chunk c - 2 have read this stage
-        // A: 16 dequantised weights of this thread's row, rounded to fp16, into the swizzled K-major tile
-        {
-            float v[16];
-            if (row_live) tc5_compute<DT>(raw, c & 3, hh, v);
+            for (int i = 0; i < B_PER_THREAD; ++i) {
+                const int idx = tid + i * TC5_PRODUCERS, r = idx >> 4, ch = idx & 15;
+                braw[i] = make_uint4(0u, 0u, 0u, 0u);
+                if (idx < nb * 16 && m0 + r < a.m)
+                    braw[i] = __ldg(reinterpret_cast<const uint4*>(a.xh + (int64_t)(m0 + r) * a.k + (int64_t)c * TC5_BK + ch * 8));
+            }
+        };
+        fetch(0);
+        for (int c = 0; c < n_chunks; ++c) {
+            const int s = c % a.stages, u = c / a.stages;
+            uint8_t* As = smem + (size_t)s * a.stage_bytes + sub * TC5_A_SUB;
+            uint8_t* Bs = smem + (size_t)s * a.stage_bytes + TC5_A_BYTES;  // two sub-tiles of nb rows x 128 B
+            if (u > 0) ok = ok && tc5_wait(&empty[s], (uint32_t)((u - 1) & 1));  // the MMAs of chunk c - stages have read this stage
+            if (row_live) tc5_convert_store<DT>(raw, lane, (2 * c + sub) & 3, 16 * tile_w, As);
             else {
+                // rows past the matrix: zeros (8 runs of 4 halves per thread, same addresses as a live tile)
+                const int g = lane >> 2, t = lane & 3;
 #pragma unroll
-                for (int i = 0; i < 16; ++i) v[i] = 0.f;
+                for (int i = 0; i < 8; ++i) tc5_store4(As, 16 * tile_w + g + 8 * (i >> 2), 16 * (i & 3) + 4 * t, __half2(), __half2());
             }
 #pragma unroll
-            for (int p = 0; p < 2; ++p) {
-                const uint4 q = make_uint4(pack_h2(v[8 * p], v[8 * p + 1]), pack_h2(v[8 * p + 2], v[8 * p + 3]),
-                                           pack_h2(v[8 * p + 4], v[8 * p + 5]), pack_h2(v[8 * p + 6], v[8 * p + 7]));
-                const int chunk16 = 4 * hh + 2 * h16 + p;
-                *reinterpret_cast<uint4*>(As + row * 128 + ((chunk16 ^ (row & 7)) << 4)) = q;
+            for (int i = 0; i < B_PER_THREAD; ++i) {
+                const int idx = tid + i * TC5_PRODUCERS, r = idx >> 4, ch = idx & 15;
+                if (idx < nb * 16) *reinterpret_cast<uint4*>(Bs + (ch >> 3) * (nb * 128) + r * 128 + (((ch & 7) ^ (r & 7)) << 4)) = braw[i];
             }
+            if (c + 1 < n_chunks) fetch(c + 1);
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // generic-proxy stores -> visible to the tensor core
+            __syncwarp();
+            if (lane == 0) tc5_arrive(&full[s]);
         }
-        // B: 64 columns of nb activation rows (fp16 already), 16 bytes per copy
-#pragma unroll
-        for (int i = 0; i < B_PER_THREAD; ++i) {
-            const int idx = tid + i * TC5_THREADS, r = idx >> 3, ch = idx & 7;
-            if (idx < nb * 8) *reinterpret_cast<uint4*>(Bs + r * 128 + ((ch ^ (r & 7)) << 4)) = braw[i];
-        }
-        if (c + 1 < n_chunks) fetch(c + 1);  // in flight while this chunk is fenced, multiplied and the stage wait runs
-        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // generic-proxy stores -> visible to the tensor core
-        asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-        __syncthreads();
-        if (tid == 0) {
+    } else if (warp == TC5_PRODUCER_WARPS && lane == 0) {
+        // ── MMA issuer ──
+        const uint32_t idesc = tc5_idesc(nb);
+        for (int c = 0; c < n_chunks; ++c) {
+            const int s = c % a.stages, u = c / a.stages;
+            ok = ok && tc5_wait(&full[s], (uint32_t)(u & 1));  // after one expired wait nothing else is waited for
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-            const uint64_t ad = tc5_desc(tc5_smem_u32(As)), bd = tc5_desc(tc5_smem_u32(Bs));
+            const uint32_t As = tc5_smem_u32(smem + (size_t)s * a.stage_bytes);
 #pragma unroll
-            for (int k = 0; k < TC5_BK / 16; ++k)  // 16 columns = 32 bytes further inside the swizzle row: +2 in units of 16 B
-                tc5_mma(tmem, ad + 2 * k, bd + 2 * k, idesc, (c > 0 || k > 0) ? 1u : 0u);
-            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(tc5_smem_u32(&mbar[s]))
-                         : "memory");
+            for (int h = 0; h < 2; ++h) {  // the two 64-column sub-tiles of the stage
+                const uint64_t ad = tc5_desc(As + h * TC5_A_SUB), bd = tc5_desc(As + TC5_A_BYTES + h * (nb * 128));
+#pragma unroll
+                for (int k = 0; k < 4; ++k)  // 16 columns = 32 bytes further inside the swizzle row: +2 in units of 16 B
+                    tc5_mma(tmem, ad + 2 * k, bd + 2 * k, idesc, (c > 0 || h > 0 || k > 0) ? 1u : 0u);
+            }
+            tc5_commit(&empty[s]);
         }
+        tc5_commit(&done_bar);  // arrives when every MMA above has completed
     }
-    // all MMAs are committed in order: the last commit covers every earlier one
-    {
-        const int last = n_chunks - 1;
-        ok = tc5_wait(&mbar[last & 1], (uint32_t)((last >> 1) & 1)) && ok;
-    }
-    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-    ok = __syncthreads_and(ok);  // one verdict for the block: the loads below are warp-collective
-    if (ok) {
-        // warp w reads TMEM lanes 32 (w % 4) .. +31 (= weight rows), 16 columns (= activation rows) per instruction
-        const int q4 = warp & 3;
-        const int n = n0 + 32 * q4 + lane;
-        const float bias = (a.bias && n < a.n) ? a.bias[n] : 0.f;
-        for (int gi = warp >> 2; gi < nb / 16; gi += TC5_THREADS / 128) {
-            uint32_t r[16];
-            const uint32_t taddr = tmem + ((uint32_t)(32 * q4) << 16) + (uint32_t)(gi * 16);
-            asm volatile(
-                "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
-                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
-                  "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-                : "r"(taddr)
-                : "memory");
-            asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-            if (n < a.n) {
+    if (warp >= TC5_PRODUCER_WARPS) {
+        // ── epilogue: warp q4 reads TMEM lanes 32 q4 .. +31 (= weight rows), 16 columns (= activation rows) at a time ──
+        __syncwarp();
+        ok = ok && tc5_wait(&done_bar, 0u);
+        ok = __all_sync(0xFFFFFFFFu, ok);  // one verdict for the warp: the loads below are warp-collective
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        if (ok) {
+            const int q4 = warp & 3;
+            const int n = n0 + 32 * q4 + lane;
+            const float bias = (a.bias && n < a.n) ? a.bias[n] : 0.f;
+            for (int gi = 0; gi < nb / 16; ++gi) {
+                uint32_t r[16];
+                const uint32_t taddr = tmem + ((uint32_t)(32 * q4) << 16) + (uint32_t)(gi * 16);
+                asm volatile(
+                    "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+                    : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+                      "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                    : "r"(taddr)
+                    : "memory");
+                asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+                if (n < a.n) {
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    const int m = m0 + gi * 16 + j;
-                    if (m < a.m) {
-                        float v = __uint_as_float(r[j]) + bias;
-                        if (a.res) v += a.res[(int64_t)m * a.ldres + n];
-                        a.y[(int64_t)m * a.ldy + n] = v;
+                    for (int j = 0; j < 16; ++j) {
+                        const int m = m0 + gi * 16 + j;
+                        if (m < a.m) {
+                            float v = __uint_as_float(r[j]) + bias;
+                            if (a.res) v += a.res[(int64_t)m * a.ldres + n];
+                            a.y[(int64_t)m * a.ldy + n] = v;
+                        }
                     }
                 }
             }
         }
-    } else if (tid == 0) {
-        atomicExch(&g_tc5_timeout, 1);
     }
+    if (!ok) atomicExch(&g_tc5_timeout, 1);
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
     __syncthreads();
-    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(tmem_cols) : "memory");
+    if (warp == TC5_PRODUCER_WARPS) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(tmem_cols) : "memory");
 }
 
 // x[m, k] f32 -> fp16, one thread per 8 columns.
@@ -336,21 +414,26 @@ cudaError_t launch_gemm_tc5(const uint8_t* wt, int dtype, int n, int k, const __
                             const float* res, int ldres, cudaStream_t st) {
     if (m <= 0 || n <= 0) return cudaSuccess;
     if (!tc5_supported(dtype, k)) return cudaErrorInvalidValue;
-    static bool attr_set[3] = {false, false, false};
-    Tc5Args a{wt, dtype, n, k, xh, m, y, ldy, bias, res, ldres};
+    static int attr_bytes[3] = {0, 0, 0};
+    const int nb_max = std::min(TC5_NB_MAX, (m + 15) & ~15);
+    const int stage_bytes = TC5_A_BYTES + nb_max * 256;
+    const int stages = std::max(2, std::min(TC5_MAX_STAGES, TC5_SMEM_LIMIT / stage_bytes));
+    const int smem_bytes = stages * stage_bytes + 1024;  // + slack to align the stages to 1024 B
+    Tc5Args a{wt, dtype, n, k, xh, m, y, ldy, bias, res, ldres, stage_bytes, stages};
     const dim3 grid((unsigned)((n + TC5_BM - 1) / TC5_BM), (unsigned)((m + TC5_NB_MAX - 1) / TC5_NB_MAX));
     cudaError_t le;
     const int which = dtype == T_Q4_K ? 0 : dtype == T_Q6_K ? 1 : 2;
-    if (!attr_set[which]) {
-        le = which == 0   ? cudaFuncSetAttribute(gemm_tc5_kernel<T_Q4_K>, cudaFuncAttributeMaxDynamicSharedMemorySize, TC5_SMEM)
-             : which == 1 ? cudaFuncSetAttribute(gemm_tc5_kernel<T_Q6_K>, cudaFuncAttributeMaxDynamicSharedMemorySize, TC5_SMEM)
-                          : cudaFuncSetAttribute(gemm_tc5_kernel<T_Q8_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, TC5_SMEM);
+    constexpr int SMEM_CAP = 2 * (TC5_A_BYTES + TC5_NB_MAX * 256) + 1024;  // the deepest ring the largest tile allows
+    if (attr_bytes[which] == 0) {  // once per format: allow the largest ring (193 KB)
+        le = which == 0   ? cudaFuncSetAttribute(gemm_tc5_kernel<T_Q4_K>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_CAP)
+             : which == 1 ? cudaFuncSetAttribute(gemm_tc5_kernel<T_Q6_K>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_CAP)
+                          : cudaFuncSetAttribute(gemm_tc5_kernel<T_Q8_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_CAP);
         if (le != cudaSuccess) return le;
-        attr_set[which] = true;
+        attr_bytes[which] = SMEM_CAP;
     }
-    if (which == 0) le = launch_pdl(gemm_tc5_kernel<T_Q4_K>, grid, dim3(TC5_THREADS), TC5_SMEM, st, a);
-    else if (which == 1) le = launch_pdl(gemm_tc5_kernel<T_Q6_K>, grid, dim3(TC5_THREADS), TC5_SMEM, st, a);
-    else le = launch_pdl(gemm_tc5_kernel<T_Q8_0>, grid, dim3(TC5_THREADS), TC5_SMEM, st, a);
+    if (which == 0) le = launch_pdl(gemm_tc5_kernel<T_Q4_K>, grid, dim3(TC5_THREADS), smem_bytes, st, a);
+    else if (which == 1) le = launch_pdl(gemm_tc5_kernel<T_Q6_K>, grid, dim3(TC5_THREADS), smem_bytes, st, a);
+    else le = launch_pdl(gemm_tc5_kernel<T_Q8_0>, grid, dim3(TC5_THREADS), smem_bytes, st, a);
     if (le != cudaSuccess) return le;
     return count_launch_and_check();
 }

@@ -795,8 +795,11 @@ __device__ __forceinline__ void reduce_store(const ImmaArgs& a, const ImmaSeg& s
 }
 
 // Kernel A (any shape): one CTA per tile row; its 8 warps split the k-tiles, operands straight from global memory.
-template <int NT>
-__global__ void __launch_bounds__(IMMA_WARPS * 32, (NT <= 2 ? 2 : 1)) gemv_imma_kernel(const ImmaArgs a) {
+// FMT: 0 = segments of any format; T_Q4_K / T_Q6_K = every segment of the launch has that format — the code for the
+// other formats is left out, which lets the M <= 2 instance fit 80 registers and run three CTAs (24 warps) per SM
+// instead of two.
+template <int NT, int FMT>
+__global__ void __launch_bounds__(IMMA_WARPS * 32, (NT == 1 ? (FMT != 0 ? 3 : 2) : NT == 2 ? 2 : 1)) gemv_imma_kernel(const ImmaArgs a) {
     __shared__ float red[IMMA_WARPS * NT * 4 * 32];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     int rt = blockIdx.x, s = 0;
@@ -807,7 +810,7 @@ __global__ void __launch_bounds__(IMMA_WARPS * 32, (NT <= 2 ? 2 : 1)) gemv_imma_
     for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
         for (int e = 0; e < 4; ++e) acc[nt][e] = 0.f;
-    if (sg.dtype == T_Q4_K) {
+    if (FMT == T_Q4_K || (FMT == 0 && sg.dtype == T_Q4_K)) {
         const int kts = a.k >> 8;
         const uint8_t* base = sg.wt + (int64_t)rt * kts * Q4_K_TILE_BYTES;
         Q4Regs ra, rb;
@@ -830,7 +833,7 @@ __global__ void __launch_bounds__(IMMA_WARPS * 32, (NT <= 2 ? 2 : 1)) gemv_imma_
             compute_q4_k<NT>(rb, b, lane, acc);
             kt = k2;
         }
-    } else if (sg.dtype == T_Q6_K) {
+    } else if (FMT == T_Q6_K || (FMT == 0 && sg.dtype == T_Q6_K)) {
         const int kts = a.k >> 8;
         const uint8_t* base = sg.wt + (int64_t)rt * kts * Q6_K_TILE_BYTES;
         Q6Regs ra;
@@ -843,7 +846,7 @@ __global__ void __launch_bounds__(IMMA_WARPS * 32, (NT <= 2 ? 2 : 1)) gemv_imma_
             load_b_global<NT>(a, kt, g, t, false, true, b);
             compute_q6_k<NT>(ra, b, lane, acc);
         }
-    } else {
+    } else if (FMT == 0) {
         const int bpt = sg.bpt, kts = (a.k >> 5) / bpt, tb = bpt * 544;
         const uint8_t* base = sg.wt + (int64_t)rt * kts * tb;
         pdl_wait();
@@ -1132,9 +1135,20 @@ cudaError_t launch_gemv_imma(const ImmaArgs& a, cudaStream_t st) {
         return count_launch_and_check();
     }
     cudaError_t le;
-    if (nt == 1) le = launch_pdl(gemv_imma_kernel<1>, dim3(tiles), dim3(IMMA_WARPS * 32), 0, st, a);
-    else if (nt == 2) le = launch_pdl(gemv_imma_kernel<2>, dim3(tiles), dim3(IMMA_WARPS * 32), 0, st, a);
-    else if (nt == 4) le = launch_pdl(gemv_imma_kernel<4>, dim3(tiles), dim3(IMMA_WARPS * 32), 0, st, a);
+    bool q4_only = true, q6_only = true;
+    for (int s = 0; s < a.nseg; ++s) {
+        q4_only = q4_only && a.seg[s].dtype == T_Q4_K;
+        q6_only = q6_only && a.seg[s].dtype == T_Q6_K;
+    }
+    // The 80-register single-format instances trade per-CTA speed for occupancy: they win once the grid is several
+    // waves deep (gate|up, lm_head) and lose on grids that fit the SMs at once (o_proj, down_proj), where one CTA's
+    // latency is the kernel's.
+    const bool deep = tiles >= 1024;
+    if (nt == 1 && q4_only && deep) le = launch_pdl(gemv_imma_kernel<1, T_Q4_K>, dim3(tiles), dim3(IMMA_WARPS * 32), 0, st, a);
+    else if (nt == 1 && q6_only && deep) le = launch_pdl(gemv_imma_kernel<1, T_Q6_K>, dim3(tiles), dim3(IMMA_WARPS * 32), 0, st, a);
+    else if (nt == 1) le = launch_pdl(gemv_imma_kernel<1, 0>, dim3(tiles), dim3(IMMA_WARPS * 32), 0, st, a);
+    else if (nt == 2) le = launch_pdl(gemv_imma_kernel<2, 0>, dim3(tiles), dim3(IMMA_WARPS * 32), 0, st, a);
+    else if (nt == 4) le = launch_pdl(gemv_imma_kernel<4, 0>, dim3(tiles), dim3(IMMA_WARPS * 32), 0, st, a);
     else return cudaErrorInvalidValue;
     if (le != cudaSuccess) return le;
     return count_launch_and_check();
