@@ -799,7 +799,7 @@ __device__ __forceinline__ void reduce_store(const ImmaArgs& a, const ImmaSeg& s
 // other formats is left out, which lets the M <= 2 instance fit 80 registers and run three CTAs (24 warps) per SM
 // instead of two.
 template <int NT, int FMT>
-__global__ void __launch_bounds__(IMMA_WARPS * 32, (NT == 1 ? (FMT != 0 ? 3 : 2) : NT == 2 ? 2 : 1)) gemv_imma_kernel(const ImmaArgs a) {
+__global__ void __launch_bounds__(IMMA_WARPS * 32, (NT == 1 && FMT != 0) ? 3 : 2) gemv_imma_kernel(const ImmaArgs a) {
     __shared__ float red[IMMA_WARPS * NT * 4 * 32];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     int rt = blockIdx.x, s = 0;
