@@ -111,7 +111,8 @@ __global__ void __launch_bounds__(32) tp_argmax_kernel(const float* __restrict__
     __syncwarp();
     if (lane < tp.size) *tp_flag(tp, TP_OFF_AM_FLAGS, lane, slot, tp.rank) = epoch;
     if (lane < tp.size) {
-        if (!tp_wait_flag(tp_flag(tp, TP_OFF_AM_FLAGS, tp.rank, slot, lane), epoch)) atomicExch(tp.timeout, 1);
+        const bool already = *reinterpret_cast<volatile int*>(tp.timeout) != 0;  // an earlier wait expired: do not wait again
+        if (!already && !tp_wait_flag(tp_flag(tp, TP_OFF_AM_FLAGS, tp.rank, slot, lane), epoch)) atomicExch(tp.timeout, 1);
         __threadfence_system();
     }
     __syncwarp();

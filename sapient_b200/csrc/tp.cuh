@@ -70,7 +70,9 @@ __device__ __forceinline__ bool tp_wait_flag(volatile uint32_t* f, uint32_t epoc
 __device__ __forceinline__ uint32_t tp_consume_row(const TpDev& tp, float* x, int64_t row_off_x, int row, int dim) {
     const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(tp.ar_seq) + 1u;
     const int slot = (int)(epoch & 1u);
-    bool ok = true;
+    // once any wait of this engine has expired (now or in an earlier kernel) nothing waits again: the step finishes
+    // with undefined values, the host sees the flag and reports SP_ERR_COMM
+    bool ok = *reinterpret_cast<volatile int*>(tp.timeout) == 0;
     for (int i = threadIdx.x * 4; i < dim; i += blockDim.x * 4) {
         float4 acc = *reinterpret_cast<const float4*>(x + row_off_x + i);
         for (int s = 0; s < tp.size; ++s) {
@@ -82,7 +84,7 @@ __device__ __forceinline__ uint32_t tp_consume_row(const TpDev& tp, float* x, in
                 if ((uint32_t)(w0 >> 32) == epoch && (uint32_t)(w1 >> 32) == epoch && (uint32_t)(w2 >> 32) == epoch &&
                     (uint32_t)(w3 >> 32) == epoch)
                     break;
-                if (++spins > TP_SPIN_LIMIT) { ok = false; break; }
+                if (!ok || ++spins > TP_SPIN_LIMIT) { ok = false; break; }
                 __nanosleep(100);
             }
             acc.x += __uint_as_float((uint32_t)w0); acc.y += __uint_as_float((uint32_t)w1);
