@@ -152,6 +152,10 @@ void sp_cuda_engine_destroy(SpEngine* e);
 int32_t sp_cuda_engine_tp_handle(SpEngine* e, void* out, size_t cap);
 int32_t sp_cuda_engine_tp_connect(SpEngine* e, const void* handles, int32_t n_ranks);
 int32_t sp_cuda_engine_vocab_local(const SpEngine* e, int32_t* rows, int32_t* first);
+/* Engines of ONE process (one per GPU, or several on one GPU for tests): the device address of a rank's communication
+ * block, and connecting with the blocks of all ranks in rank order instead of IPC handles. */
+int32_t sp_cuda_engine_tp_block(SpEngine* e, void** block);
+int32_t sp_cuda_engine_tp_connect_local(SpEngine* e, void* const* blocks, int32_t n_ranks);
 /* The slice rank `rank` of `size` keeps of one full tensor (host only, no device needed): writes the slice to out
  * (may be NULL to query sizes), its dims to out_dims[ndim] and its byte size to *out_bytes. Replicated tensors come
  * back whole. vocab bounds the rows of lm_head.weight. */

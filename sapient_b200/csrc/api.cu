@@ -150,6 +150,22 @@ int32_t sp_cuda_engine_tp_connect(SpEngine* e, const void* handles, int32_t n_ra
     API_END
 }
 
+int32_t sp_cuda_engine_tp_block(SpEngine* e, void** block) {
+    API_BEGIN
+    if (!e || !block) { set_error("null argument"); return SP_ERR_ARG; }
+    *block = e->e->tp_block();
+    if (!*block) { set_error("engine is not tensor parallel (or not finalised)"); return SP_ERR_STATE; }
+    return SP_OK;
+    API_END
+}
+
+int32_t sp_cuda_engine_tp_connect_local(SpEngine* e, void* const* blocks, int32_t n_ranks) {
+    API_BEGIN
+    if (!e) { set_error("null engine"); return SP_ERR_ARG; }
+    return e->e->tp_connect_ptrs(blocks, n_ranks);
+    API_END
+}
+
 int32_t sp_cuda_engine_vocab_local(const SpEngine* e, int32_t* rows, int32_t* first) {
     API_BEGIN
     if (!e || !rows) { set_error("null argument"); return SP_ERR_ARG; }

@@ -79,6 +79,8 @@ class Engine {
     // Tensor parallelism (tp.cuh): d holds this rank's LOCAL head / ffn counts, g the description as given.
     int tp_handle(void* out, size_t cap);           // CUDA IPC handle of this rank's communication block
     int tp_connect(const void* handles, int n);     // map every rank's block (handles in rank order)
+    int tp_connect_ptrs(void* const* blocks, int n); // the same for engines of ONE process: device pointers, no IPC
+    void* tp_block() const { return tp_block_; }
     int tp_check();                                 // SP_ERR_COMM if a wait on a peer gave up
     void drop_graphs();                             // forget the captured step graphs (a launch parameter changed)
     int vocab_local() const { return vocab_l_; }

@@ -200,6 +200,26 @@ int Engine::tp_connect(const void* handles, int n) {
     return SP_OK;
 }
 
+int Engine::tp_connect_ptrs(void* const* blocks, int n) {
+    if (d.tp_size <= 1 || !tp_block_) { set_error("engine is not tensor parallel (or not finalised)"); return SP_ERR_STATE; }
+    if (!blocks || n != d.tp_size) { set_error("tp_connect: need one block per rank"); return SP_ERR_ARG; }
+    if (tp_connected_) { set_error("tp_connect: already connected"); return SP_ERR_STATE; }
+    SP_CUDA_TRY(cudaSetDevice(d.device));
+    TpDev h{};
+    h.rank = d.tp_rank;
+    h.size = d.tp_size;
+    h.slot_floats = (int64_t)d.max_tokens * d.hidden;
+    for (int r = 0; r < n; ++r) {
+        if (!blocks[r]) { set_error("tp_connect: null block"); return SP_ERR_ARG; }
+        h.base[r] = r == d.tp_rank ? tp_block_ : (uint8_t*)blocks[r];  // tp_peer_ stays empty: nothing to close
+    }
+    uint32_t* st = (uint32_t*)tp_state_;
+    h.ar_seq = st; h.am_seq = st + 1; h.done = st + 2; h.timeout = (int*)(st + 3);
+    SP_CUDA_TRY(cudaMemcpy(d_tp_, &h, sizeof(h), cudaMemcpyHostToDevice));
+    tp_connected_ = true;
+    return SP_OK;
+}
+
 int Engine::tp_check() {
     if (d.tp_size <= 1) return SP_OK;
     int flag = 0;

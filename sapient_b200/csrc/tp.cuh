@@ -29,7 +29,7 @@ namespace sp {
 
 constexpr int TP_MAX_RANKS = 8;
 constexpr int TP_ARGMAX_ROWS = 32;
-constexpr int TP_SPIN_LIMIT = 1 << 22;  // polls of ~0.25 us each: about a second
+constexpr int TP_SPIN_LIMIT = 1 << 21;  // polls of ~0.5 us each: about a second
 
 constexpr size_t TP_OFF_AM_FLAGS = 256;
 constexpr size_t TP_OFF_AM_VALS = 512;

@@ -109,6 +109,17 @@ class ForwardEngine:
         arr = (C.c_uint8 * len(blob)).from_buffer_copy(blob)
         check(lib().sp_cuda_engine_tp_connect(self._h, arr, self.desc.tp_size))
 
+    def tp_block(self) -> int:
+        """Device address of this rank's communication block (for engines of one process)."""
+        p = C.c_void_p()
+        check(lib().sp_cuda_engine_tp_block(self._h, C.byref(p)))
+        return int(p.value)
+
+    def tp_connect_local(self, blocks) -> None:
+        """Connect with the blocks (tp_block() of every rank, in rank order) of engines living in this process."""
+        arr = (C.c_void_p * len(blocks))(*blocks)
+        check(lib().sp_cuda_engine_tp_connect_local(self._h, arr, len(blocks)))
+
     def _gather(self, local: np.ndarray) -> np.ndarray:
         """Full-vocabulary logits from the ranks' slices (identity for a single-GPU engine or without a group)."""
         if self.desc.tp_size <= 1 or self._tp_group is None:

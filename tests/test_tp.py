@@ -196,3 +196,35 @@ def test_two_gpu_engine_matches_single_gpu(tmp_path):
     if not np.array_equal(got["toks"], want_toks):
         first = int(np.flatnonzero(got["toks"].reshape(-1) != want_toks.reshape(-1))[0])
         assert first > 0, "diverged at the very first step"
+
+
+@pytest.mark.gpu
+def test_a_peer_that_never_arrives_ends_the_call_with_a_comm_error():
+    """Failure detection without faulting anything: two ranks' engines live in this process on one GPU, only rank 0 ever
+    runs. Its first exchange waits for partial rows that nobody sends; the bounded wait expires (about a second), the
+    kernels finish, the call returns SP_ERR_COMM, later waits are skipped, and the CUDA context stays usable."""
+    import time
+
+    from sapient_b200.engine import ForwardEngine
+
+    cfg, W = tiny_model("tiny_llama_tp")
+    a = ForwardEngine.from_weights(cfg, W, tp_rank=0, tp_size=2, max_tokens=8)
+    b = ForwardEngine.from_weights(cfg, W, tp_rank=1, tp_size=2, max_tokens=8)
+    blocks = [a.tp_block(), b.tp_block()]
+    a.tp_connect_local(blocks)
+    b.tp_connect_local(blocks)
+    t0 = time.perf_counter()
+    with pytest.raises(_lib.SapientCudaError) as err:
+        a.forward_logits([1, 2, 3], True)
+    dt = time.perf_counter() - t0
+    assert err.value.status == _lib.SP_ERR_COMM, err.value
+    assert dt < 30.0, dt
+    t0 = time.perf_counter()
+    with pytest.raises(_lib.SapientCudaError):
+        a.forward_logits([4], True)  # the flag is sticky: no further waiting
+    assert time.perf_counter() - t0 < 2.0
+    a.close()
+    b.close()
+    one = ForwardEngine.from_weights(cfg, W)  # the context is fine
+    assert np.all(np.isfinite(one.forward_logits([1, 2, 3], True)))
+    one.close()
