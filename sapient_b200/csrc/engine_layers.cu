@@ -64,9 +64,10 @@ int Engine::gemv(const float* x, int ldx, int m, int k, const DevTensor* w0, con
         if (ok) {
             // many rows: dequantise each weight tile once and multiply on the 5th-generation tensor cores
             SP_LAUNCH(F_ELEM, launch_x_to_f16(x, ldx, m, k, ws_.xh, stream));
-            for (int i = 0; i < 3 && ws[i]; ++i)
-                SP_LAUNCH(F_GEMV, launch_gemm_tc5(ws[i]->tiled, ws[i]->dtype, (int)ws[i]->dims[0], k, ws_.xh, m, ys[i], ldy0, bs[i],
-                                                  i == 0 ? res : nullptr, ldy0, stream));
+            Tc5Seg segs[3];
+            int ns = 0;
+            for (int i = 0; i < 3 && ws[i]; ++i) segs[ns++] = Tc5Seg{ws[i]->tiled, ys[i], bs[i], ws[i]->dtype, (int)ws[i]->dims[0]};
+            SP_LAUNCH(F_GEMV, launch_gemm_tc5_multi(segs, ns, k, ws_.xh, m, ldy0, res, ldy0, stream));
             return SP_OK;
         }
     }

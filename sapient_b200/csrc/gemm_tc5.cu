@@ -235,33 +235,41 @@ __device__ __forceinline__ void tc5_convert_store(const Tc5Raw& r, int lane, int
 }
 
 struct Tc5Args {
-    const uint8_t* wt;  // tiled weights
-    int dtype, n, k;    // n rows, k columns (k % 256 == 0)
+    Tc5Seg seg[3];      // up to three matrices sharing the activations (q|k|v, gate|up); CTAs are dealt to them in order
+    int nseg;
+    int k;              // columns (k % 256 == 0)
     const __half* xh;   // activations as fp16 [m][k]
     int m;
-    float* y;
     int ldy;
-    const float* bias;  // [n] or null
-    const float* res;   // [m][ldres] or null (may alias y)
+    const float* res;   // [m][ldres] or null, added to segment 0 (may alias its y)
     int ldres;
+    int ksplit;         // > 1: gridDim.z CTAs share a tile's K range and ADD their parts into y (y must already hold the
+                        // residual: res == y); the order of the f32 additions then varies from run to run
     int stage_bytes;    // TC5_A_BYTES + 256 * (widest activation tile of the launch, rounded to 16)
     int stages;         // ring depth that fits shared memory (2..4)
 };
 
-template <int DT>
 __global__ void __launch_bounds__(TC5_THREADS, 1) gemm_tc5_kernel(const Tc5Args a) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t full[TC5_MAX_STAGES], empty[TC5_MAX_STAGES], done_bar;
     __shared__ uint32_t tmem_slot;
-    constexpr int TILE_BYTES = DT == T_Q4_K ? Q4_K_TILE_BYTES : DT == T_Q6_K ? Q6_K_TILE_BYTES : 8 * 544;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     uint8_t* smem = smem_raw + ((1024u - (tc5_smem_u32(smem_raw) & 1023u)) & 1023u);
-    const int n0 = blockIdx.x * TC5_BM, m0 = blockIdx.y * TC5_NB_MAX;
+    // which matrix of the launch this CTA works on, and its 128-row tile there
+    int bx = blockIdx.x, si = 0;
+    while (si < a.nseg - 1 && bx >= (a.seg[si].n + TC5_BM - 1) / TC5_BM) { bx -= (a.seg[si].n + TC5_BM - 1) / TC5_BM; ++si; }
+    const Tc5Seg& sg = a.seg[si];
+    const int DT = sg.dtype;
+    const int TILE_BYTES = DT == T_Q4_K ? Q4_K_TILE_BYTES : DT == T_Q6_K ? Q6_K_TILE_BYTES : 8 * 544;
+    const int n0 = bx * TC5_BM, m0 = blockIdx.y * TC5_NB_MAX;
     const int rows_here = min(TC5_NB_MAX, a.m - m0);
     const int nb = (rows_here + 15) & ~15;  // the MMA's N
     const int tmem_cols = nb <= 32 ? 32 : nb <= 64 ? 64 : nb <= 128 ? 128 : 256;
-    const int kts = a.k >> 8, n_tile_rows = (a.n + 15) >> 4;
-    const int n_chunks = a.k / TC5_BK;
+    const int kts = a.k >> 8, n_tile_rows = (sg.n + 15) >> 4;
+    // this CTA's share of the K range (all of it unless the launch splits K)
+    const int all_chunks = a.k / TC5_BK;
+    const int c_begin = (int)((int64_t)blockIdx.z * all_chunks / a.ksplit), c_end = (int)((int64_t)(blockIdx.z + 1) * all_chunks / a.ksplit);
+    const int n_chunks = c_end - c_begin;
 
     if (warp == TC5_PRODUCER_WARPS) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tc5_smem_u32(&tmem_slot)), "r"(tmem_cols)
@@ -289,19 +297,24 @@ __global__ void __launch_bounds__(TC5_THREADS, 1) gemm_tc5_kernel(const Tc5Args 
         const int tile_w = warp >> 1, sub = warp & 1;
         const int rt = (n0 >> 4) + tile_w;
         const bool row_live = rt < n_tile_rows;
-        const uint8_t* tile_row = a.wt + (int64_t)rt * kts * TILE_BYTES;
+        const uint8_t* tile_row = sg.wt + (int64_t)rt * kts * TILE_BYTES;
         constexpr int B_PER_THREAD = TC5_NB_MAX * 16 / TC5_PRODUCERS;  // 16-byte pieces of the activation tile per thread
         Tc5Raw raw;
         uint4 braw[B_PER_THREAD];
         auto fetch = [&](int c) {  // global loads of stage-chunk c into registers (group 2 c + sub of the row's superblocks)
-            const int grp = 2 * c + sub;
-            if (row_live) tc5_load<DT>(tile_row + (int64_t)(grp >> 2) * TILE_BYTES, lane, grp & 3, raw);
+            const int grp = 2 * (c_begin + c) + sub;
+            if (row_live) {
+                const uint8_t* tile = tile_row + (int64_t)(grp >> 2) * TILE_BYTES;
+                if (DT == T_Q4_K) tc5_load<T_Q4_K>(tile, lane, grp & 3, raw);
+                else if (DT == T_Q6_K) tc5_load<T_Q6_K>(tile, lane, grp & 3, raw);
+                else tc5_load<T_Q8_0>(tile, lane, grp & 3, raw);
+            }
 #pragma unroll
             for (int i = 0; i < B_PER_THREAD; ++i) {
                 const int idx = tid + i * TC5_PRODUCERS, r = idx >> 4, ch = idx & 15;
                 braw[i] = make_uint4(0u, 0u, 0u, 0u);
                 if (idx < nb * 16 && m0 + r < a.m)
-                    braw[i] = __ldg(reinterpret_cast<const uint4*>(a.xh + (int64_t)(m0 + r) * a.k + (int64_t)c * TC5_BK + ch * 8));
+                    braw[i] = __ldg(reinterpret_cast<const uint4*>(a.xh + (int64_t)(m0 + r) * a.k + (int64_t)(c_begin + c) * TC5_BK + ch * 8));
             }
         };
         fetch(0);
@@ -310,8 +323,12 @@ __global__ void __launch_bounds__(TC5_THREADS, 1) gemm_tc5_kernel(const Tc5Args 
             uint8_t* As = smem + (size_t)s * a.stage_bytes + sub * TC5_A_SUB;
             uint8_t* Bs = smem + (size_t)s * a.stage_bytes + TC5_A_BYTES;  // two sub-tiles of nb rows x 128 B
             if (u > 0) ok = ok && tc5_wait(&empty[s], (uint32_t)((u - 1) & 1));  // the MMAs of chunk c - stages have read this stage
-            if (row_live) tc5_convert_store<DT>(raw, lane, (2 * c + sub) & 3, 16 * tile_w, As);
-            else {
+            if (row_live) {
+                const int cq = (2 * (c_begin + c) + sub) & 3;
+                if (DT == T_Q4_K) tc5_convert_store<T_Q4_K>(raw, lane, cq, 16 * tile_w, As);
+                else if (DT == T_Q6_K) tc5_convert_store<T_Q6_K>(raw, lane, cq, 16 * tile_w, As);
+                else tc5_convert_store<T_Q8_0>(raw, lane, cq, 16 * tile_w, As);
+            } else {
                 // rows past the matrix: zeros (8 runs of 4 halves per thread, same addresses as a live tile)
                 const int g = lane >> 2, t = lane & 3;
 #pragma unroll
@@ -355,7 +372,9 @@ __global__ void __launch_bounds__(TC5_THREADS, 1) gemm_tc5_kernel(const Tc5Args 
         if (ok) {
             const int q4 = warp & 3;
             const int n = n0 + 32 * q4 + lane;
-            const float bias = (a.bias && n < a.n) ? a.bias[n] : 0.f;
+            const float bias = (sg.bias && n < sg.n && blockIdx.z == 0) ? sg.bias[n] : 0.f;
+            const bool add_res = a.res && si == 0 && a.ksplit == 1;
+            float* yb = sg.y;
             for (int gi = 0; gi < nb / 16; ++gi) {
                 uint32_t r[16];
                 const uint32_t taddr = tmem + ((uint32_t)(32 * q4) << 16) + (uint32_t)(gi * 16);
@@ -366,14 +385,15 @@ __global__ void __launch_bounds__(TC5_THREADS, 1) gemm_tc5_kernel(const Tc5Args 
                     : "r"(taddr)
                     : "memory");
                 asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-                if (n < a.n) {
+                if (n < sg.n) {
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
                         const int m = m0 + gi * 16 + j;
                         if (m < a.m) {
                             float v = __uint_as_float(r[j]) + bias;
-                            if (a.res) v += a.res[(int64_t)m * a.ldres + n];
-                            a.y[(int64_t)m * a.ldy + n] = v;
+                            if (add_res) v += a.res[(int64_t)m * a.ldres + n];
+                            if (a.ksplit > 1) atomicAdd(yb + (int64_t)m * a.ldy + n, v);  // y already holds the residual
+                            else yb[(int64_t)m * a.ldy + n] = v;
                         }
                     }
                 }
@@ -410,32 +430,55 @@ cudaError_t launch_x_to_f16(const float* x, int ldx, int m, int k, __half* out, 
     return count_launch_and_check();
 }
 
-cudaError_t launch_gemm_tc5(const uint8_t* wt, int dtype, int n, int k, const __half* xh, int m, float* y, int ldy, const float* bias,
-                            const float* res, int ldres, cudaStream_t st) {
-    if (m <= 0 || n <= 0) return cudaSuccess;
-    if (!tc5_supported(dtype, k)) return cudaErrorInvalidValue;
-    static int attr_bytes[3] = {0, 0, 0};
+// Up to three matrices sharing the activations in one launch. res (added to segment 0) may alias its y; when it does
+// and the grid would leave most SMs idle, the K range is split over gridDim.z CTAs that add into y.
+cudaError_t launch_gemm_tc5_multi(const Tc5Seg* segs, int nseg, int k, const __half* xh, int m, int ldy, const float* res, int ldres,
+                                  cudaStream_t st) {
+    if (m <= 0 || nseg <= 0) return cudaSuccess;
+    if (nseg > 3 || k % 256 != 0) return cudaErrorInvalidValue;
+    Tc5Args a{};
+    int tiles = 0;
+    for (int i = 0; i < nseg; ++i) {
+        if (!tc5_supported(segs[i].dtype, k) || segs[i].n <= 0) return cudaErrorInvalidValue;
+        a.seg[i] = segs[i];
+        tiles += (segs[i].n + TC5_BM - 1) / TC5_BM;
+    }
+    static bool attr_set = false;
+    static int sm_count = 0;
+    if (sm_count == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+        if (sm_count <= 0) sm_count = 148;
+    }
     const int nb_max = std::min(TC5_NB_MAX, (m + 15) & ~15);
     const int stage_bytes = TC5_A_BYTES + nb_max * 256;
     const int stages = std::max(2, std::min(TC5_MAX_STAGES, TC5_SMEM_LIMIT / stage_bytes));
     const int smem_bytes = stages * stage_bytes + 1024;  // + slack to align the stages to 1024 B
-    Tc5Args a{wt, dtype, n, k, xh, m, y, ldy, bias, res, ldres, stage_bytes, stages};
-    const dim3 grid((unsigned)((n + TC5_BM - 1) / TC5_BM), (unsigned)((m + TC5_NB_MAX - 1) / TC5_NB_MAX));
-    cudaError_t le;
-    const int which = dtype == T_Q4_K ? 0 : dtype == T_Q6_K ? 1 : 2;
-    constexpr int SMEM_CAP = 2 * (TC5_A_BYTES + TC5_NB_MAX * 256) + 1024;  // the deepest ring the largest tile allows
-    if (attr_bytes[which] == 0) {  // once per format: allow the largest ring (193 KB)
-        le = which == 0   ? cudaFuncSetAttribute(gemm_tc5_kernel<T_Q4_K>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_CAP)
-             : which == 1 ? cudaFuncSetAttribute(gemm_tc5_kernel<T_Q6_K>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_CAP)
-                          : cudaFuncSetAttribute(gemm_tc5_kernel<T_Q8_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_CAP);
-        if (le != cudaSuccess) return le;
-        attr_bytes[which] = SMEM_CAP;
+    const int m_tiles = (m + TC5_NB_MAX - 1) / TC5_NB_MAX;
+    int ksplit = 1;
+    if (nseg == 1 && res && res == segs[0].y) {  // in-place residual: partial sums can simply be added
+        const int chunks = k / TC5_BK;
+        ksplit = std::max(1, std::min({8, sm_count / std::max(1, tiles * m_tiles), chunks / 4}));
     }
-    if (which == 0) le = launch_pdl(gemm_tc5_kernel<T_Q4_K>, grid, dim3(TC5_THREADS), smem_bytes, st, a);
-    else if (which == 1) le = launch_pdl(gemm_tc5_kernel<T_Q6_K>, grid, dim3(TC5_THREADS), smem_bytes, st, a);
-    else le = launch_pdl(gemm_tc5_kernel<T_Q8_0>, grid, dim3(TC5_THREADS), smem_bytes, st, a);
+    a.nseg = nseg; a.k = k; a.xh = xh; a.m = m; a.ldy = ldy; a.res = res; a.ldres = ldres; a.ksplit = ksplit;
+    a.stage_bytes = stage_bytes; a.stages = stages;
+    constexpr int SMEM_CAP = 2 * (TC5_A_BYTES + TC5_NB_MAX * 256) + 1024;  // the deepest ring the largest tile allows (193 KB)
+    cudaError_t le;
+    if (!attr_set) {
+        le = cudaFuncSetAttribute(gemm_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_CAP);
+        if (le != cudaSuccess) return le;
+        attr_set = true;
+    }
+    le = launch_pdl(gemm_tc5_kernel, dim3((unsigned)tiles, (unsigned)m_tiles, (unsigned)ksplit), dim3(TC5_THREADS), smem_bytes, st, a);
     if (le != cudaSuccess) return le;
     return count_launch_and_check();
+}
+
+cudaError_t launch_gemm_tc5(const uint8_t* wt, int dtype, int n, int k, const __half* xh, int m, float* y, int ldy, const float* bias,
+                            const float* res, int ldres, cudaStream_t st) {
+    Tc5Seg sg{wt, y, bias, dtype, n};
+    return launch_gemm_tc5_multi(&sg, 1, k, xh, m, ldy, res, ldres, st);
 }
 
 }  // namespace sp

@@ -94,6 +94,15 @@ bool tc5_supported(int dtype, int64_t k);
 cudaError_t launch_x_to_f16(const float* x, int ldx, int m, int k, __half* out, cudaStream_t st);
 cudaError_t launch_gemm_tc5(const uint8_t* wt, int dtype, int n, int k, const __half* xh, int m, float* y, int ldy, const float* bias,
                             const float* res, int ldres, cudaStream_t st);
+struct Tc5Seg {
+    const uint8_t* wt;  // tiled weights
+    float* y;           // output base: element (m, r) at y[m * ldy + r]
+    const float* bias;  // [n] or null
+    int dtype, n;       // format, rows
+};
+// Up to three matrices sharing the activations in ONE launch (q|k|v, gate|up); res is added to segment 0.
+cudaError_t launch_gemm_tc5_multi(const Tc5Seg* segs, int nseg, int k, const __half* xh, int m, int ldy, const float* res, int ldres,
+                                  cudaStream_t st);
 
 cudaError_t launch_dequant(int dtype, const uint8_t* w, int64_t n, int64_t k, float* out, cudaStream_t st);
 cudaError_t launch_gemv(const GemvArgs& a, cudaStream_t st);
