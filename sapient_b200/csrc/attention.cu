@@ -198,3 +198,166 @@ cudaError_t launch_attention(const float* q, int ldq, float* out, int ldo, int n
 }
 
 }  // namespace sp
+
+// ───────────────────────────── prefill: tiled attention on tensor cores ─────────────────────────────
+// Many query tokens of ONE sequence with consecutive positions (a prefill chunk). The split kernel above re-reads the
+// whole key range once per query token; here a block takes 64 query rows of one head (4 warps x 16 rows), walks the keys
+// in tiles of 64 (4 pages) staged in shared memory, and does both contractions with mma.sync.m16n8k16 (fp16 operands —
+// K and V are fp16 in the cache already, q and the softmax weights are rounded to fp16 — f32 accumulation), with the
+// reference's online-softmax recurrence (kernels/attention.rs:98-165) applied per 64-key tile.
+namespace sp {
+
+constexpr int FA_ROWS = 64, FA_KEYS = 64, FA_WARPS = 4;
+
+__device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_half2(float a, float b) {
+    const __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+// HD16 = head_dim / 16 (head_dim a multiple of 16, <= 128).
+template <int HD16>
+__global__ void __launch_bounds__(FA_WARPS * 32)
+attention_prefill_kernel(const float* __restrict__ q, int ldq, float* __restrict__ out, int ldo, int n_tok, int n_heads, int slot, int pos0,
+                         KvGeom kv, int layer, float scale) {
+    constexpr int HD = HD16 * 16, LD = HD + 8;  // padded row of the shared tiles (halves): conflict-free fragment loads
+    extern __shared__ __align__(16) __half fa_smem[];
+    __half* Ks = fa_smem;
+    __half* Vs = fa_smem + FA_KEYS * LD;
+    pdl_wait();
+    pdl_trigger();
+    const int h = blockIdx.x, t0 = blockIdx.y * FA_ROWS;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int kv_h = h / (n_heads / kv.n_kv);
+    const int32_t* pt = kv.page_table + (int64_t)slot * kv.max_pages;
+    // this thread's two query rows (rows past the chunk repeat the last one and are never written)
+    const int r0 = t0 + warp * 16 + g, r1 = r0 + 8;
+    const int q0 = min(r0, n_tok - 1), q1 = min(r1, n_tok - 1);
+    const int p0 = pos0 + q0, p1 = pos0 + q1;
+    uint32_t qa[HD16][4];
+    {
+        const float* a = q + (int64_t)q0 * ldq + (int64_t)h * HD;
+        const float* b = q + (int64_t)q1 * ldq + (int64_t)h * HD;
+#pragma unroll
+        for (int kd = 0; kd < HD16; ++kd) {
+            const float2 x0 = *reinterpret_cast<const float2*>(a + 16 * kd + 2 * t), x1 = *reinterpret_cast<const float2*>(b + 16 * kd + 2 * t);
+            const float2 x2 = *reinterpret_cast<const float2*>(a + 16 * kd + 8 + 2 * t), x3 = *reinterpret_cast<const float2*>(b + 16 * kd + 8 + 2 * t);
+            qa[kd][0] = pack_half2(x0.x * scale, x0.y * scale); qa[kd][1] = pack_half2(x1.x * scale, x1.y * scale);
+            qa[kd][2] = pack_half2(x2.x * scale, x2.y * scale); qa[kd][3] = pack_half2(x3.x * scale, x3.y * scale);
+        }
+    }
+    float o[2 * HD16][4];
+#pragma unroll
+    for (int i = 0; i < 2 * HD16; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+    const int last_pos = pos0 + min(t0 + FA_ROWS, n_tok) - 1;  // newest key any row of the block may see
+    for (int k0 = 0; k0 <= last_pos; k0 += FA_KEYS) {
+        __syncthreads();  // the previous tile has been consumed
+        for (int idx = threadIdx.x; idx < FA_KEYS * (HD / 8); idx += FA_WARPS * 32) {
+            const int kr = idx / (HD / 8), pc = idx - kr * (HD / 8);
+            const int key = k0 + kr;
+            uint4 kq = make_uint4(0u, 0u, 0u, 0u), vq = kq;
+            if (key <= last_pos) {
+                const int page = pt[key / KV_PAGE];
+                kq = *reinterpret_cast<const uint4*>(kv.pool + kv_off(kv, layer, page, 0, kv_h) + (int64_t)(key % KV_PAGE) * HD + pc * 8);
+                vq = *reinterpret_cast<const uint4*>(kv.pool + kv_off(kv, layer, page, 1, kv_h) + (int64_t)(key % KV_PAGE) * HD + pc * 8);
+            }
+            *reinterpret_cast<uint4*>(Ks + kr * LD + pc * 8) = kq;
+            *reinterpret_cast<uint4*>(Vs + kr * LD + pc * 8) = vq;
+        }
+        __syncthreads();
+        // S = (q * scale) K^T for 16 rows x 64 keys
+        float s[8][4];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+#pragma unroll
+            for (int kd = 0; kd < HD16; ++kd) {
+                const uint32_t b0 = *reinterpret_cast<const uint32_t*>(Ks + (8 * j + g) * LD + 16 * kd + 2 * t);
+                const uint32_t b1 = *reinterpret_cast<const uint32_t*>(Ks + (8 * j + g) * LD + 16 * kd + 8 + 2 * t);
+                mma_f16(s[j], qa[kd][0], qa[kd][1], qa[kd][2], qa[kd][3], b0, b1);
+            }
+        }
+        // causal mask and the tile's row maxima (row g: s[j][0..1], row g+8: s[j][2..3]; keys 8j + 2t, +1)
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int key = k0 + 8 * j + 2 * t;
+            if (key > p0) s[j][0] = -INFINITY;
+            if (key + 1 > p0) s[j][1] = -INFINITY;
+            if (key > p1) s[j][2] = -INFINITY;
+            if (key + 1 > p1) s[j][3] = -INFINITY;
+            mx0 = fmaxf(mx0, fmaxf(s[j][0], s[j][1]));
+            mx1 = fmaxf(mx1, fmaxf(s[j][2], s[j][3]));
+        }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xFFFFFFFFu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xFFFFFFFFu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xFFFFFFFFu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xFFFFFFFFu, mx1, 2));
+        const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
+        // a row whose keys of this tile are all masked keeps its state (n == m); key 0 is visible to every row, so
+        // after the first tile every maximum is finite
+        const float c0 = (n0 == -INFINITY) ? 1.f : expf(m0 - n0), c1 = (n1 == -INFINITY) ? 1.f : expf(m1 - n1);
+        float sum0 = 0.f, sum1 = 0.f;
+        uint32_t pa[4][4];  // softmax weights as fp16 A fragments: k-step kk covers keys 16 kk .. + 15
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const float e0 = (s[j][0] == -INFINITY) ? 0.f : expf(s[j][0] - n0), e1 = (s[j][1] == -INFINITY) ? 0.f : expf(s[j][1] - n0);
+            const float e2 = (s[j][2] == -INFINITY) ? 0.f : expf(s[j][2] - n1), e3 = (s[j][3] == -INFINITY) ? 0.f : expf(s[j][3] - n1);
+            sum0 += e0 + e1;
+            sum1 += e2 + e3;
+            pa[j >> 1][(j & 1) * 2] = pack_half2(e0, e1);
+            pa[j >> 1][(j & 1) * 2 + 1] = pack_half2(e2, e3);
+        }
+        sum0 += __shfl_xor_sync(0xFFFFFFFFu, sum0, 1); sum0 += __shfl_xor_sync(0xFFFFFFFFu, sum0, 2);
+        sum1 += __shfl_xor_sync(0xFFFFFFFFu, sum1, 1); sum1 += __shfl_xor_sync(0xFFFFFFFFu, sum1, 2);
+        l0 = fmaf(c0, l0, sum0); l1 = fmaf(c1, l1, sum1);
+        m0 = n0; m1 = n1;
+#pragma unroll
+        for (int nd = 0; nd < 2 * HD16; ++nd) { o[nd][0] *= c0; o[nd][1] *= c0; o[nd][2] *= c1; o[nd][3] *= c1; }
+        // O += P V: B fragments (keys x dims) come transposed out of the row-major V tile
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+#pragma unroll
+            for (int nd = 0; nd < 2 * HD16; nd += 2) {
+                uint32_t b0, b1, b2, b3;
+                const __half* src = Vs + (16 * kk + (lane & 15)) * LD + 8 * (nd + (lane >> 4));
+                const uint32_t addr = (uint32_t)__cvta_generic_to_shared(src);
+                asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                             : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3)
+                             : "r"(addr));
+                mma_f16(o[nd], pa[kk][0], pa[kk][1], pa[kk][2], pa[kk][3], b0, b1);
+                mma_f16(o[nd + 1], pa[kk][0], pa[kk][1], pa[kk][2], pa[kk][3], b2, b3);
+            }
+        }
+    }
+    const float i0 = (l0 == 0.f) ? 0.f : 1.0f / l0, i1 = (l1 == 0.f) ? 0.f : 1.0f / l1;
+#pragma unroll
+    for (int nd = 0; nd < 2 * HD16; ++nd) {
+        if (r0 < n_tok) *reinterpret_cast<float2*>(out + (int64_t)r0 * ldo + (int64_t)h * HD + 8 * nd + 2 * t) = make_float2(o[nd][0] * i0, o[nd][1] * i0);
+        if (r1 < n_tok) *reinterpret_cast<float2*>(out + (int64_t)r1 * ldo + (int64_t)h * HD + 8 * nd + 2 * t) = make_float2(o[nd][2] * i1, o[nd][3] * i1);
+    }
+}
+
+bool attention_prefill_supported(int head_dim) { return head_dim % 16 == 0 && head_dim >= 16 && head_dim <= 128; }
+
+// All n_tok tokens belong to sequence `slot` at positions pos0, pos0 + 1, ... (their keys are in the cache already).
+cudaError_t launch_attention_prefill(const float* q, int ldq, float* out, int ldo, int n_tok, int n_heads, int slot, int pos0, KvGeom kv,
+                                     int layer, float scale, cudaStream_t st) {
+    if (n_tok <= 0) return cudaSuccess;
+    if (!attention_prefill_supported(kv.head_dim)) return cudaErrorInvalidValue;
+    const int hd16 = kv.head_dim / 16;
+    const size_t smem = (size_t)2 * FA_KEYS * (kv.head_dim + 8) * sizeof(__half);
+    const dim3 grid(n_heads, (n_tok + FA_ROWS - 1) / FA_ROWS), block(FA_WARPS * 32);
+    cudaError_t le = cudaErrorInvalidValue;
+#define SP_FA(N) \
+    if (hd16 == N) le = launch_pdl(attention_prefill_kernel<N>, grid, block, smem, st, q, ldq, out, ldo, n_tok, n_heads, slot, pos0, kv, layer, scale)
+    SP_FA(1); SP_FA(2); SP_FA(3); SP_FA(4); SP_FA(5); SP_FA(6); SP_FA(7); SP_FA(8);
+#undef SP_FA
+    if (le != cudaSuccess) return le;
+    return count_launch_and_check();
+}
+
+}  // namespace sp

@@ -139,6 +139,13 @@ int Engine::attention_and_oproj(const LayerW& w, int l, int T) {
         SP_LAUNCH(F_ATTN, launch_attn_merge_quant(att_scratch_, H, splits, hd, nullptr, 0, ia, stream));
         return gemv(attn_, H * hd, T, H * hd, w.o, w.ob, x_, hid, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, x_, &ia, true);
     }
+    // a prefill chunk (one sequence, consecutive positions): the tiled tensor-core kernel
+    bool one_seq = splits == 1 && use_tc5 && attention_prefill_supported(hd);
+    for (int i = 1; one_seq && i < T; ++i) one_seq = p_slot_[i] == p_slot_[0] && p_pos_[i] == p_pos_[0] + i;
+    if (one_seq) {
+        SP_LAUNCH(F_ATTN, launch_attention_prefill(qkv_, qkv_ld, attn_, H * hd, T, H, p_slot_[0], p_pos_[0], kv_, l, scale, stream));
+        return gemv(attn_, H * hd, T, H * hd, w.o, w.ob, x_, hid, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, x_, nullptr, true);
+    }
     SP_LAUNCH(F_ATTN, launch_attention(qkv_, qkv_ld, attn_, H * hd, T, H, d_tok_slot_, d_tok_pos_, kv_, l, scale, splits, att_scratch_,
                                        stream));
     return gemv(attn_, H * hd, T, H * hd, w.o, w.ob, x_, hid, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, x_, nullptr, true);

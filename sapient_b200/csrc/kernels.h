@@ -69,6 +69,11 @@ cudaError_t launch_attn_merge_quant(const float* part, int n_heads, int n_splits
 cudaError_t launch_attention_split(const float* q, int ldq, int n_tok, int n_heads, const int32_t* tok_slot, const int32_t* tok_pos,
                                    KvGeom kv, int layer, float scale, int n_splits, float* scratch, cudaStream_t st);
 
+// Prefill attention on tensor cores: n_tok tokens of one sequence at consecutive positions pos0.. (keys already cached).
+bool attention_prefill_supported(int head_dim);
+cudaError_t launch_attention_prefill(const float* q, int ldq, float* out, int ldo, int n_tok, int n_heads, int slot, int pos0, KvGeom kv,
+                                     int layer, float scale, cudaStream_t st);
+
 // Workspace of the activation digits for up to 16 activation rows of k_max columns.
 struct ActWorkspace {
     int8_t* xq = nullptr;
