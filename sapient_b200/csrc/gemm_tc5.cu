@@ -10,8 +10,9 @@
 //     tile-repacked ggml blocks (the layout the GEMV reads, gemv_imma.cuh), waits for the stage to be
 //     free (mbarrier `empty`), converts the current words to fp16 (quants become exact floats by the 2^23 bit trick,
 //     one f32 multiply-add applies scale and minimum, one rounding to fp16), stores
-//     them in the K-major 128-byte-swizzled layout the tensor core reads, copies its share of the fp16 activations,
-//     and arrives on the stage's `full` mbarrier;
+//     them in the K-major 128-byte-swizzled layout the tensor core reads, and arrives on the stage's `full` mbarrier;
+//     one producer thread also has TMA fetch the stage's activation tile (cp.async.bulk.tensor.2d with the 128-byte
+//     swizzle, completing on the same mbarrier by byte count; rows past the matrix arrive as zeros);
 //   * 1 thread issues, per chunk, eight tcgen05.mma (128 x NB x 16, kind::f16, fp32 accumulation in tensor memory)
 //     and commits them to the stage's `empty` mbarrier — no block-wide barrier anywhere in the loop;
 //   * 4 epilogue warps: tcgen05.ld brings the accumulators back (one weight row per thread, 16 activation rows per
@@ -21,6 +22,7 @@
 // in f32 from exact operands and rounded to fp16 once (Q8_0: the exact product of int8 and f16 scale, in half2).
 // Every wait on an mbarrier is bounded; on expiry the kernel raises g_tc5_timeout, still frees its tensor memory
 // and returns.
+#include <cuda.h>
 #include <cuda_fp16.h>
 
 #include <algorithm>
@@ -249,7 +251,7 @@ struct Tc5Args {
     int stages;         // ring depth that fits shared memory (2..4)
 };
 
-__global__ void __launch_bounds__(TC5_THREADS, 1) gemm_tc5_kernel(const Tc5Args a) {
+__global__ void __launch_bounds__(TC5_THREADS, 1) gemm_tc5_kernel(const Tc5Args a, const __grid_constant__ CUtensorMap tmap_x) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t full[TC5_MAX_STAGES], empty[TC5_MAX_STAGES], done_bar;
     __shared__ uint32_t tmem_slot;
@@ -278,7 +280,8 @@ __global__ void __launch_bounds__(TC5_THREADS, 1) gemm_tc5_kernel(const Tc5Args 
     }
     if (tid == 0) {
         for (int s = 0; s < a.stages; ++s) {
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(tc5_smem_u32(&full[s])), "r"(TC5_PRODUCER_WARPS) : "memory");
+            // 16 producer warps + the thread that announces the TMA bytes
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(tc5_smem_u32(&full[s])), "r"(TC5_PRODUCER_WARPS + 1) : "memory");
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(tc5_smem_u32(&empty[s])) : "memory");
         }
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(tc5_smem_u32(&done_bar)) : "memory");
@@ -298,9 +301,7 @@ __global__ void __launch_bounds__(TC5_THREADS, 1) gemm_tc5_kernel(const Tc5Args 
         const int rt = (n0 >> 4) + tile_w;
         const bool row_live = rt < n_tile_rows;
         const uint8_t* tile_row = sg.wt + (int64_t)rt * kts * TILE_BYTES;
-        constexpr int B_PER_THREAD = TC5_NB_MAX * 16 / TC5_PRODUCERS;  // 16-byte pieces of the activation tile per thread
         Tc5Raw raw;
-        uint4 braw[B_PER_THREAD];
         auto fetch = [&](int c) {  // global loads of stage-chunk c into registers (group 2 c + sub of the row's superblocks)
             const int grp = 2 * (c_begin + c) + sub;
             if (row_live) {
@@ -309,20 +310,26 @@ __global__ void __launch_bounds__(TC5_THREADS, 1) gemm_tc5_kernel(const Tc5Args 
                 else if (DT == T_Q6_K) tc5_load<T_Q6_K>(tile, lane, grp & 3, raw);
                 else tc5_load<T_Q8_0>(tile, lane, grp & 3, raw);
             }
-#pragma unroll
-            for (int i = 0; i < B_PER_THREAD; ++i) {
-                const int idx = tid + i * TC5_PRODUCERS, r = idx >> 4, ch = idx & 15;
-                braw[i] = make_uint4(0u, 0u, 0u, 0u);
-                if (idx < nb * 16 && m0 + r < a.m)
-                    braw[i] = __ldg(reinterpret_cast<const uint4*>(a.xh + (int64_t)(m0 + r) * a.k + (int64_t)(c_begin + c) * TC5_BK + ch * 8));
-            }
         };
         fetch(0);
+        const uint32_t b_bytes = (uint32_t)(a.stage_bytes - TC5_A_BYTES);  // both 64-column sub-tiles of the activations
         for (int c = 0; c < n_chunks; ++c) {
             const int s = c % a.stages, u = c / a.stages;
             uint8_t* As = smem + (size_t)s * a.stage_bytes + sub * TC5_A_SUB;
-            uint8_t* Bs = smem + (size_t)s * a.stage_bytes + TC5_A_BYTES;  // two sub-tiles of nb rows x 128 B
             if (u > 0) ok = ok && tc5_wait(&empty[s], (uint32_t)((u - 1) & 1));  // the MMAs of chunk c - stages have read this stage
+            if (tid == 0) {
+                // TMA: the stage's activation tile, two boxes of (64 columns x nb_max rows), counted in bytes on `full`
+                const uint32_t bar = tc5_smem_u32(&full[s]);
+                const uint32_t dst = tc5_smem_u32(smem + (size_t)s * a.stage_bytes + TC5_A_BYTES);
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(b_bytes) : "memory");
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+                    asm volatile(
+                        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::"r"(
+                            dst + h * (b_bytes / 2)),
+                        "l"(&tmap_x), "r"((c_begin + c) * TC5_BK + 64 * h), "r"(m0), "r"(bar)
+                        : "memory");
+            }
             if (row_live) {
                 const int cq = (2 * (c_begin + c) + sub) & 3;
                 if (DT == T_Q4_K) tc5_convert_store<T_Q4_K>(raw, lane, cq, 16 * tile_w, As);
@@ -333,11 +340,6 @@ __global__ void __launch_bounds__(TC5_THREADS, 1) gemm_tc5_kernel(const Tc5Args 
                 const int g = lane >> 2, t = lane & 3;
 #pragma unroll
                 for (int i = 0; i < 8; ++i) tc5_store4(As, 16 * tile_w + g + 8 * (i >> 2), 16 * (i & 3) + 4 * t, __half2(), __half2());
-            }
-#pragma unroll
-            for (int i = 0; i < B_PER_THREAD; ++i) {
-                const int idx = tid + i * TC5_PRODUCERS, r = idx >> 4, ch = idx & 15;
-                if (idx < nb * 16) *reinterpret_cast<uint4*>(Bs + (ch >> 3) * (nb * 128) + r * 128 + (((ch & 7) ^ (r & 7)) << 4)) = braw[i];
             }
             if (c + 1 < n_chunks) fetch(c + 1);
             asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // generic-proxy stores -> visible to the tensor core
@@ -354,7 +356,7 @@ __global__ void __launch_bounds__(TC5_THREADS, 1) gemm_tc5_kernel(const Tc5Args 
             const uint32_t As = tc5_smem_u32(smem + (size_t)s * a.stage_bytes);
 #pragma unroll
             for (int h = 0; h < 2; ++h) {  // the two 64-column sub-tiles of the stage
-                const uint64_t ad = tc5_desc(As + h * TC5_A_SUB), bd = tc5_desc(As + TC5_A_BYTES + h * (nb * 128));
+                const uint64_t ad = tc5_desc(As + h * TC5_A_SUB), bd = tc5_desc(As + TC5_A_BYTES + h * ((a.stage_bytes - TC5_A_BYTES) / 2));
 #pragma unroll
                 for (int k = 0; k < 4; ++k)  // 16 columns = 32 bytes further inside the swizzle row: +2 in units of 16 B
                     tc5_mma(tmem, ad + 2 * k, bd + 2 * k, idesc, (c > 0 || h > 0 || k > 0) ? 1u : 0u);
@@ -430,6 +432,10 @@ cudaError_t launch_x_to_f16(const float* x, int ldx, int m, int k, __half* out, 
     return count_launch_and_check();
 }
 
+typedef CUresult (*PFN_encodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                    const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
 // Up to three matrices sharing the activations in one launch. res (added to segment 0) may alias its y; when it does
 // and the grid would leave most SMs idle, the K range is split over gridDim.z CTAs that add into y.
 cudaError_t launch_gemm_tc5_multi(const Tc5Seg* segs, int nseg, int k, const __half* xh, int m, int ldy, const float* res, int ldres,
@@ -461,6 +467,24 @@ cudaError_t launch_gemm_tc5_multi(const Tc5Seg* segs, int nseg, int k, const __h
         const int chunks = k / TC5_BK;
         ksplit = std::max(1, std::min({8, sm_count / std::max(1, tiles * m_tiles), chunks / 4}));
     }
+    // TMA descriptor of the fp16 activations [m][k]: boxes of 64 columns x nb_max rows, 128-byte swizzle, zero fill
+    static PFN_encodeTiled encode = nullptr;
+    if (!encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess || !fn) return cudaErrorNotSupported;
+        encode = reinterpret_cast<PFN_encodeTiled>(fn);
+    }
+    CUtensorMap tmap;
+    {
+        const cuuint64_t gdim[2] = {(cuuint64_t)k, (cuuint64_t)m};
+        const cuuint64_t gstride[1] = {(cuuint64_t)k * sizeof(__half)};
+        const cuuint32_t box[2] = {64u, (cuuint32_t)nb_max};
+        const cuuint32_t estr[2] = {1u, 1u};
+        if (encode(&tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half*>(xh), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return cudaErrorInvalidValue;
+    }
     a.nseg = nseg; a.k = k; a.xh = xh; a.m = m; a.ldy = ldy; a.res = res; a.ldres = ldres; a.ksplit = ksplit;
     a.stage_bytes = stage_bytes; a.stages = stages;
     constexpr int SMEM_CAP = 2 * (TC5_A_BYTES + TC5_NB_MAX * 256) + 1024;  // the deepest ring the largest tile allows (193 KB)
@@ -470,7 +494,7 @@ cudaError_t launch_gemm_tc5_multi(const Tc5Seg* segs, int nseg, int k, const __h
         if (le != cudaSuccess) return le;
         attr_set = true;
     }
-    le = launch_pdl(gemm_tc5_kernel, dim3((unsigned)tiles, (unsigned)m_tiles, (unsigned)ksplit), dim3(TC5_THREADS), smem_bytes, st, a);
+    le = launch_pdl(gemm_tc5_kernel, dim3((unsigned)tiles, (unsigned)m_tiles, (unsigned)ksplit), dim3(TC5_THREADS), smem_bytes, st, a, tmap);
     if (le != cudaSuccess) return le;
     return count_launch_and_check();
 }
