@@ -154,57 +154,79 @@ __device__ __forceinline__ void tc5_store4(uint8_t* As, int row, int c0, __half2
     *reinterpret_cast<uint2*>(As + row * 128 + ((((c0 >> 3) ^ (row & 7))) << 4) + (c0 & 4) * 2) = v;
 }
 
-// The same from four f32 values (one rounding to fp16 each).
-__device__ __forceinline__ void tc5_store4f(uint8_t* As, int row, int c0, float f0, float f1, float f2, float f3) {
-    const uint2 v = make_uint2(bits_h2(__floats2half2_rn(f0, f1)), bits_h2(__floats2half2_rn(f2, f3)));
-    *reinterpret_cast<uint2*>(As + row * 128 + ((((c0 >> 3) ^ (row & 7))) << 4) + (c0 & 4) * 2) = v;
-}
+// Byte b (< 128) of v as the float 0.5 + n / 256: bit pattern 0x3F000000 | n << 16. With it a weight s * n + c costs one
+// byte permute and one fused multiply-add: fmaf(half_plus(v, b), 256 s, c - 128 s).
+__device__ __forceinline__ float half_plus(uint32_t v, int b) { return __uint_as_float(__byte_perm(v, 0x3F000000u, 0x7044 | (b << 8))); }
 
-// Byte b (< 256) of v as an exact f32: 0x4B000000 | n is the float 2^23 + n.
+// Byte b of v as an exact f32 (0x4B000000 | n is the float 2^23 + n).
 __device__ __forceinline__ float byte_f32(uint32_t v, int b) {
     return __uint_as_float(__byte_perm(v, 0x4B000000u, 0x7540 | b)) - 8388608.0f;
 }
 
 __device__ __forceinline__ uint32_t u4_word(const uint4& v, int i) { return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w; }
 
-// Converts the raw words of chunk group cq to fp16 and stores the thread's 32 weights; row0 = first CTA-tile row of
-// the warp's 16-row tile.
+// A thread's stores into the swizzled stage. Lane (g, t) owns, in rows g and g + 8 of its warp's 16-row tile, the four
+// column runs 16 cg + 4 t .. + 3 (cg = 0..3) of the 64-column group. With
+//   bsw = shared address of (tile row g, byte 8 (t & 1)) | ((t >> 1) ^ g) << 4
+// run cg of row g + 8 hi8 sits at (bsw ^ cg << 5) + 1024 hi8: the 16-byte slot 2 cg + (t >> 1) xor-ed with row % 8 = g.
+template <int HI8>
+__device__ __forceinline__ void tc5_sts(uint32_t addr, uint32_t x, uint32_t y) {
+    asm volatile("st.shared.v2.b32 [%0 + %3], {%1, %2};\n" ::"r"(addr), "r"(x), "r"(y), "n"(HI8 * 1024) : "memory");
+}
+__device__ __forceinline__ void tc5_sts(uint32_t addr, int hi8, uint32_t x, uint32_t y) {
+    if (hi8) tc5_sts<1>(addr, x, y);
+    else tc5_sts<0>(addr, x, y);
+}
+__device__ __forceinline__ void tc5_sts4f(uint32_t addr, int hi8, float f0, float f1, float f2, float f3) {
+    tc5_sts(addr, hi8, bits_h2(__floats2half2_rn(f0, f1)), bits_h2(__floats2half2_rn(f2, f3)));
+}
+
+// Converts the raw words of chunk group cq to fp16 and stores the thread's 32 weights.
 template <int DT>
-__device__ __forceinline__ void tc5_convert_store(const Tc5Raw& r, int lane, int cq, int row0, uint8_t* As) {
-    const int g = lane >> 2, t = lane & 3;
+__device__ __forceinline__ void tc5_convert_store(const Tc5Raw& r, int cq, uint32_t bsw) {
+    const uint32_t run[4] = {bsw, bsw ^ 32u, bsw ^ 64u, bsw ^ 96u};
     if (DT == T_Q4_K) {
 #pragma unroll
         for (int hi8 = 0; hi8 < 2; ++hi8) {
             const uint4 hd = r.hdr[hi8];
             const float d = half_bits_to_float((uint16_t)(hd.x & 0xFFFFu)), dmin = half_bits_to_float((uint16_t)(hd.x >> 16));
-            const int row = row0 + g + 8 * hi8;
+            // the 6-bit (scale, minimum) pairs of sub-blocks 2 cq and 2 cq + 1, one per byte
+            uint32_t sc2, mn2;
+            if (cq < 2) {
+                sc2 = (hd.y >> (16 * cq)) & 0x3F3Fu;
+                mn2 = (hd.z >> (16 * cq)) & 0x3F3Fu;
+            } else {
+                const int sh = 16 * (cq - 2);
+                const uint32_t x = hd.w >> sh;
+                sc2 = (x & 0x0F0Fu) | (((hd.y >> sh) >> 2) & 0x3030u);
+                mn2 = ((x >> 4) & 0x0F0Fu) | (((hd.z >> sh) >> 2) & 0x3030u);
+            }
 #pragma unroll
             for (int hh = 0; hh < 2; ++hh) {  // low nibbles: sub-block 2 cq, high nibbles: 2 cq + 1
-                uint32_t sc, mn;
-                k4_scale_min(hd.y, hd.z, hd.w, 2 * cq + hh, &sc, &mn);
-                // d * sc and dmin * mn are exact in f32 (11-bit x 6-bit), the fused multiply-add rounds dl * q - ml once
-                const float dl = d * (float)sc, nml = -(dmin * (float)mn);
+                // d * sc and dmin * mn are exact in f32 (11-bit x 6-bit); weight = dl * q - ml, rounded to fp16 once
+                const float dl = d * byte_f32(sc2, hh), ml = dmin * byte_f32(mn2, hh);
+                const float s256 = 256.0f * dl, c = fmaf(-128.0f, dl, -ml);
 #pragma unroll
                 for (int h16 = 0; h16 < 2; ++h16) {
                     const uint32_t w = u4_word(r.q[0], 2 * hi8 + h16);
                     const uint32_t v = (hh ? (w >> 4) : w) & 0x0F0F0F0Fu;
-                    tc5_store4f(As, row, 32 * hh + 16 * h16 + 4 * t, fmaf(byte_f32(v, 0), dl, nml), fmaf(byte_f32(v, 1), dl, nml),
-                                fmaf(byte_f32(v, 2), dl, nml), fmaf(byte_f32(v, 3), dl, nml));
+                    tc5_sts4f(run[2 * hh + h16], hi8, fmaf(half_plus(v, 0), s256, c), fmaf(half_plus(v, 1), s256, c),
+                              fmaf(half_plus(v, 2), s256, c), fmaf(half_plus(v, 3), s256, c));
                 }
             }
         }
     } else if (DT == T_Q8_0) {
 #pragma unroll
         for (int hi8 = 0; hi8 < 2; ++hi8) {
-            const int row = row0 + g + 8 * hi8;
 #pragma unroll
             for (int blk = 0; blk < 2; ++blk) {
                 const __half2 d = __half2half2(__ushort_as_half((uint16_t)(r.hdr[hi8].x >> (16 * blk))));
 #pragma unroll
                 for (int h16 = 0; h16 < 2; ++h16) {
                     const uint32_t v = u4_word(r.q[blk], 2 * hi8 + h16) ^ 0x80808080u;  // int8 -> offset-128 unsigned
-                    tc5_store4(As, row, 32 * blk + 16 * h16 + 4 * t, __hmul2(bytes02(v, 0x00FF00FFu, 1152.f), d),
-                               __hmul2(bytes02(v >> 8, 0x00FF00FFu, 1152.f), d));
+                    const uint32_t e02 = bits_h2(__hmul2(bytes02(v, 0x00FF00FFu, 1152.f), d));       // columns +0, +2
+                    const uint32_t e13 = bits_h2(__hmul2(bytes02(v >> 8, 0x00FF00FFu, 1152.f), d));  // columns +1, +3
+                    tc5_sts(run[2 * blk + h16], hi8, __byte_perm(e02, e13, 0x5410), __byte_perm(e02, e13, 0x7632));
                 }
             }
         }
@@ -212,9 +234,9 @@ __device__ __forceinline__ void tc5_convert_store(const Tc5Raw& r, int lane, int
         const int half = cq >> 1, odd = cq & 1;
 #pragma unroll
         for (int hi8 = 0; hi8 < 2; ++hi8) {
-            const int row = row0 + g + 8 * hi8;
             const float d = half_bits_to_float((uint16_t)(r.dd >> (16 * hi8)));
-            const uint4 sw = r.hdr[hi8];
+            // int8 scales 8 half + 4 odd + 2 ab + p of the row: one word
+            const uint32_t sw = u4_word(r.hdr[hi8], 2 * half + odd);
 #pragma unroll
             for (int p = 0; p < 2; ++p) {
                 // the 12 words of the half: for p = 0, 1: qlA_g, qlB_g, qh_g, qlA_g8, qlB_g8, qh_g8
@@ -224,12 +246,12 @@ __device__ __forceinline__ void tc5_convert_store(const Tc5Raw& r, int lane, int
                 for (int ab = 0; ab < 2; ++ab) {  // qlA: columns l, qlB: columns 32 + l  (l = 16 p + 4 t + b)
                     const uint32_t ql = u4_word(r.q[(base + ab) >> 2], (base + ab) & 3);
                     const int quarter = 2 * odd + ab;
-                    const int si = 8 * half + p + 2 * quarter;  // int8 scale index of the row
-                    const float scf = (float)(int8_t)((u4_word(sw, si >> 2) >> (8 * (si & 3))) & 0xFFu);
-                    const float dsc = d * scf;  // exact in f32 (11-bit x 8-bit); dsc * q rounds once
+                    const float dsc = d * (float)(int8_t)((sw >> (8 * (2 * ab + p))) & 0xFFu);  // exact in f32 (11-bit x 8-bit)
+                    // dsc * (q - 32) = 256 dsc * (0.5 + q / 256) - 160 dsc: both constants exact, one rounding in the fma
+                    const float s256 = 256.0f * dsc, c = -160.0f * dsc;
                     const uint32_t q = ((odd ? (ql >> 4) : ql) & 0x0F0F0F0Fu) | (((qh >> (2 * quarter)) & 0x03030303u) << 4);
-                    tc5_store4f(As, row, 32 * ab + 16 * p + 4 * t, dsc * (byte_f32(q, 0) - 32.0f), dsc * (byte_f32(q, 1) - 32.0f),
-                                dsc * (byte_f32(q, 2) - 32.0f), dsc * (byte_f32(q, 3) - 32.0f));
+                    tc5_sts4f(run[2 * ab + p], hi8, fmaf(half_plus(q, 0), s256, c), fmaf(half_plus(q, 1), s256, c),
+                              fmaf(half_plus(q, 2), s256, c), fmaf(half_plus(q, 3), s256, c));
                 }
             }
         }
@@ -301,6 +323,9 @@ __global__ void __launch_bounds__(TC5_THREADS, 1) gemm_tc5_kernel(const Tc5Args 
         const int rt = (n0 >> 4) + tile_w;
         const bool row_live = rt < n_tile_rows;
         const uint8_t* tile_row = sg.wt + (int64_t)rt * kts * TILE_BYTES;
+        // where this lane's runs start inside a 64-column stage group (see tc5_sts)
+        const uint32_t thread_off = (uint32_t)(tile_w * 2048 + (lane >> 2) * 128 + (lane & 1) * 8);
+        const uint32_t thread_sw = (uint32_t)((((lane & 3) >> 1) ^ (lane >> 2)) << 4);
         Tc5Raw raw;
         auto fetch = [&](int c) {  // global loads of stage-chunk c into registers (group 2 c + sub of the row's superblocks)
             const int grp = 2 * (c_begin + c) + sub;
@@ -332,9 +357,10 @@ __global__ void __launch_bounds__(TC5_THREADS, 1) gemm_tc5_kernel(const Tc5Args 
             }
             if (row_live) {
                 const int cq = (2 * (c_begin + c) + sub) & 3;
-                if (DT == T_Q4_K) tc5_convert_store<T_Q4_K>(raw, lane, cq, 16 * tile_w, As);
-                else if (DT == T_Q6_K) tc5_convert_store<T_Q6_K>(raw, lane, cq, 16 * tile_w, As);
-                else tc5_convert_store<T_Q8_0>(raw, lane, cq, 16 * tile_w, As);
+                const uint32_t bsw = (tc5_smem_u32(As) + thread_off) | thread_sw;
+                if (DT == T_Q4_K) tc5_convert_store<T_Q4_K>(raw, cq, bsw);
+                else if (DT == T_Q6_K) tc5_convert_store<T_Q6_K>(raw, cq, bsw);
+                else tc5_convert_store<T_Q8_0>(raw, cq, bsw);
             } else {
                 // rows past the matrix: zeros (8 runs of 4 halves per thread, same addresses as a live tile)
                 const int g = lane >> 2, t = lane & 3;
