@@ -5,18 +5,20 @@
 // each weight tile ONCE, as fp16, and the tensor core multiplies it with up to 256 activation rows:
 //   * CTA tile: 128 weight rows (the MMA's M) x NB <= 256 activation rows (the MMA's N), K walked in chunks of 128
 //     through a ring of 2-4 shared-memory stages;
-//   * 16 producer warps, two per 16-row tile of the CTA tile (one per 64-column group of the stage): each lane reads the 16-byte pieces the tiled layout holds
-//     for it (coalesced) — 32 weights, rows g and g+8. It fetches the raw words of the NEXT chunk from the
-//     tile-repacked ggml blocks (the layout the GEMV reads, gemv_imma.cuh), waits for the stage to be
-//     free (mbarrier `empty`), converts the current words to fp16 (quants become exact floats by the 2^23 bit trick,
-//     one f32 multiply-add applies scale and minimum, one rounding to fp16), stores
-//     them in the K-major 128-byte-swizzled layout the tensor core reads, and arrives on the stage's `full` mbarrier;
+//   * 16 producer warps, two per 16-row tile of the CTA tile (one per 64-column group of the stage): each lane reads
+//     the 16-byte pieces the tiled layout holds for it (coalesced) — 32 weights, rows g and g+8 — from the
+//     tile-repacked ggml blocks (the layout the GEMV reads, gemv_imma.cuh). The raw words of the NEXT chunk are in
+//     flight in a second register set while the warp waits for the stage to be free (mbarrier `empty`), converts the
+//     current words to fp16 (quants become exact floats by bit tricks, one f32 multiply-add applies scale and
+//     minimum, one rounding to fp16), stores them in the K-major 128-byte-swizzled layout the tensor core reads, and
+//     arrives on the stage's `full` mbarrier;
 //     one producer thread also has TMA fetch the stage's activation tile (cp.async.bulk.tensor.2d with the 128-byte
 //     swizzle, completing on the same mbarrier by byte count; rows past the matrix arrive as zeros);
 //   * 1 thread issues, per chunk, eight tcgen05.mma (128 x NB x 16, kind::f16, fp32 accumulation in tensor memory)
 //     and commits them to the stage's `empty` mbarrier — no block-wide barrier anywhere in the loop;
-//   * 4 epilogue warps: tcgen05.ld brings the accumulators back (one weight row per thread, 16 activation rows per
-//     instruction), bias / residual are added and y is written with n contiguous across the warp.
+//   * epilogue, by the 16 producer warps once the last chunk is handed over: tcgen05.ld brings the accumulators back
+//     (one weight row per thread, 16 activation rows per instruction; warp w serves TMEM lanes 32 (w % 4) .. +31),
+//     bias / residual are added and y is written with n contiguous across the warp.
 // fp16 rather than bf16 operands: same instruction kind and rate, and the 11-bit significand keeps the result within
 // ~2e-4 relative L2 of the f32 reference (bf16 would sit at ~2e-3, above the 1e-3 parity bar). Each weight is computed
 // in f32 from exact operands and rounded to fp16 once (Q8_0: the exact product of int8 and f16 scale, in half2).
@@ -36,8 +38,7 @@ namespace sp {
 cudaError_t count_launch_and_check();  // kernels.cu
 
 constexpr int TC5_PRODUCER_WARPS = 16;        // two per 16-row tile: one per 64-column group of the stage
-constexpr int TC5_EPILOGUE_WARPS = 4;          // warp TC5_PRODUCER_WARPS, lane 0 also issues the MMAs
-constexpr int TC5_THREADS = 32 * (TC5_PRODUCER_WARPS + TC5_EPILOGUE_WARPS);
+constexpr int TC5_THREADS = 32 * (TC5_PRODUCER_WARPS + 1);  // + the warp that owns the tensor memory; its lane 0 issues the MMAs
 constexpr int TC5_PRODUCERS = 32 * TC5_PRODUCER_WARPS;
 constexpr int TC5_MAX_STAGES = 4;
 constexpr int TC5_BM = 128;                    // weight rows per CTA
@@ -124,26 +125,42 @@ struct Tc5Raw {
     uint32_t dd;    // Q6_K: d of row g | d of row g+8 << 16
 };
 
+// Read-only global loads as volatile asm: they stay where the code puts them (a chunk ahead of their use).
+__device__ __forceinline__ uint4 tc5_ldg16(const uint8_t* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint32_t tc5_ldg4(const uint8_t* p) {
+    uint32_t v;
+    asm volatile("ld.global.nc.u32 %0, [%1];\n" : "=r"(v) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint32_t tc5_ldg2(const uint8_t* p) {
+    uint16_t v;
+    asm volatile("ld.global.nc.u16 %0, [%1];\n" : "=h"(v) : "l"(p));
+    return v;
+}
+
 template <int DT>
 __device__ __forceinline__ void tc5_load(const uint8_t* tile, int lane, int cq, Tc5Raw& r) {
     const int g = lane >> 2;
     if (DT == T_Q4_K) {
-        r.q[0] = __ldg(reinterpret_cast<const uint4*>(tile + cq * 512 + lane * 16));
-        r.hdr[0] = __ldg(reinterpret_cast<const uint4*>(tile + 2048 + g * 16));
-        r.hdr[1] = __ldg(reinterpret_cast<const uint4*>(tile + 2048 + (g + 8) * 16));
+        r.q[0] = tc5_ldg16(tile + cq * 512 + lane * 16);
+        r.hdr[0] = tc5_ldg16(tile + 2048 + g * 16);
+        r.hdr[1] = tc5_ldg16(tile + 2048 + (g + 8) * 16);
     } else if (DT == T_Q8_0) {
-        r.q[0] = __ldg(reinterpret_cast<const uint4*>(tile + (2 * cq) * 512 + lane * 16));
-        r.q[1] = __ldg(reinterpret_cast<const uint4*>(tile + (2 * cq + 1) * 512 + lane * 16));
-        r.hdr[0].x = __ldg(reinterpret_cast<const uint32_t*>(tile + 4096 + (g * 8 + 2 * cq) * 2));        // d of blocks 2cq, 2cq+1
-        r.hdr[1].x = __ldg(reinterpret_cast<const uint32_t*>(tile + 4096 + ((g + 8) * 8 + 2 * cq) * 2));
+        r.q[0] = tc5_ldg16(tile + (2 * cq) * 512 + lane * 16);
+        r.q[1] = tc5_ldg16(tile + (2 * cq + 1) * 512 + lane * 16);
+        r.hdr[0].x = tc5_ldg4(tile + 4096 + (g * 8 + 2 * cq) * 2);        // d of blocks 2cq, 2cq+1
+        r.hdr[1].x = tc5_ldg4(tile + 4096 + ((g + 8) * 8 + 2 * cq) * 2);
     } else {
         const int half = cq >> 1;
 #pragma unroll
-        for (int i = 0; i < 3; ++i) r.q[i] = __ldg(reinterpret_cast<const uint4*>(tile + (3 * half + i) * 512 + lane * 16));
-        r.hdr[0] = __ldg(reinterpret_cast<const uint4*>(tile + 3072 + g * 16));
-        r.hdr[1] = __ldg(reinterpret_cast<const uint4*>(tile + 3072 + (g + 8) * 16));
-        const uint16_t* dp = reinterpret_cast<const uint16_t*>(tile + 3328);
-        r.dd = (uint32_t)__ldg(dp + g) | ((uint32_t)__ldg(dp + g + 8) << 16);
+        for (int i = 0; i < 3; ++i) r.q[i] = tc5_ldg16(tile + (3 * half + i) * 512 + lane * 16);
+        r.hdr[0] = tc5_ldg16(tile + 3072 + g * 16);
+        r.hdr[1] = tc5_ldg16(tile + 3072 + (g + 8) * 16);
+        r.dd = tc5_ldg2(tile + 3328 + 2 * g) | (tc5_ldg2(tile + 3328 + 2 * (g + 8)) << 16);
     }
 }
 
@@ -201,17 +218,27 @@ __device__ __forceinline__ void tc5_convert_store(const Tc5Raw& r, int cq, uint3
                 sc2 = (x & 0x0F0Fu) | (((hd.y >> sh) >> 2) & 0x3030u);
                 mn2 = ((x >> 4) & 0x0F0Fu) | (((hd.z >> sh) >> 2) & 0x3030u);
             }
+            // Nibbles become floats two at a time: (w & 0x000F000F) | 0x64006400 is the half pair (1024 + q, 1024 + q') of
+            // bytes 0 and 2, with mask 0x00F000F0 it is (1024 + 16 q, ..) of their high nibbles; the halves widen to f32
+            // exactly. d * sc and dmin * mn are exact in f32 (11-bit x 6-bit), so weight = dl * q - ml comes out of one
+            // fused multiply-add against a constant that is itself rounded once in f32 (2^-14 dl at most, far below the
+            // fp16 rounding that follows).
+            float sl[2], cl[2];
 #pragma unroll
             for (int hh = 0; hh < 2; ++hh) {  // low nibbles: sub-block 2 cq, high nibbles: 2 cq + 1
-                // d * sc and dmin * mn are exact in f32 (11-bit x 6-bit); weight = dl * q - ml, rounded to fp16 once
                 const float dl = d * byte_f32(sc2, hh), ml = dmin * byte_f32(mn2, hh);
-                const float s256 = 256.0f * dl, c = fmaf(-128.0f, dl, -ml);
+                sl[hh] = hh ? 0.0625f * dl : dl;
+                cl[hh] = fmaf(hh ? -64.0f : -1024.0f, dl, -ml);
+            }
 #pragma unroll
-                for (int h16 = 0; h16 < 2; ++h16) {
-                    const uint32_t w = u4_word(r.q[0], 2 * hi8 + h16);
-                    const uint32_t v = (hh ? (w >> 4) : w) & 0x0F0F0F0Fu;
-                    tc5_sts4f(run[2 * hh + h16], hi8, fmaf(half_plus(v, 0), s256, c), fmaf(half_plus(v, 1), s256, c),
-                              fmaf(half_plus(v, 2), s256, c), fmaf(half_plus(v, 3), s256, c));
+            for (int h16 = 0; h16 < 2; ++h16) {
+                const uint32_t w = u4_word(r.q[0], 2 * hi8 + h16), w8 = w >> 8;
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh) {
+                    const uint32_t mask = hh ? 0x00F000F0u : 0x000F000Fu;
+                    const __half2 p02 = h2_bits((w & mask) | 0x64006400u), p13 = h2_bits((w8 & mask) | 0x64006400u);
+                    tc5_sts4f(run[2 * hh + h16], hi8, fmaf(__low2float(p02), sl[hh], cl[hh]), fmaf(__low2float(p13), sl[hh], cl[hh]),
+                              fmaf(__high2float(p02), sl[hh], cl[hh]), fmaf(__high2float(p13), sl[hh], cl[hh]));
                 }
             }
         }
@@ -326,20 +353,19 @@ __global__ void __launch_bounds__(TC5_THREADS, 1) gemm_tc5_kernel(const Tc5Args 
         // where this lane's runs start inside a 64-column stage group (see tc5_sts)
         const uint32_t thread_off = (uint32_t)(tile_w * 2048 + (lane >> 2) * 128 + (lane & 1) * 8);
         const uint32_t thread_sw = (uint32_t)((((lane & 3) >> 1) ^ (lane >> 2)) << 4);
-        Tc5Raw raw;
-        auto fetch = [&](int c) {  // global loads of stage-chunk c into registers (group 2 c + sub of the row's superblocks)
+        auto fetch = [&](int c, Tc5Raw& raw) {  // global loads of stage-chunk c (group 2 c + sub of the row's superblocks)
             const int grp = 2 * (c_begin + c) + sub;
-            if (row_live) {
+            if (row_live && c < n_chunks) {
                 const uint8_t* tile = tile_row + (int64_t)(grp >> 2) * TILE_BYTES;
                 if (DT == T_Q4_K) tc5_load<T_Q4_K>(tile, lane, grp & 3, raw);
                 else if (DT == T_Q6_K) tc5_load<T_Q6_K>(tile, lane, grp & 3, raw);
                 else tc5_load<T_Q8_0>(tile, lane, grp & 3, raw);
             }
         };
-        fetch(0);
         const uint32_t b_bytes = (uint32_t)(a.stage_bytes - TC5_A_BYTES);  // both 64-column sub-tiles of the activations
-        for (int c = 0; c < n_chunks; ++c) {
-            const int s = c % a.stages, u = c / a.stages;
+        int s = -1, u = 0;  // stage of the current chunk and the number of times the ring has wrapped
+        auto build = [&](int c, const Tc5Raw& raw) {  // chunk c: wait for its stage, start the activation copy, rebuild the weights
+            if (++s == a.stages) { s = 0; ++u; }
             uint8_t* As = smem + (size_t)s * a.stage_bytes + sub * TC5_A_SUB;
             if (u > 0) ok = ok && tc5_wait(&empty[s], (uint32_t)((u - 1) & 1));  // the MMAs of chunk c - stages have read this stage
             if (tid == 0) {
@@ -367,10 +393,18 @@ __global__ void __launch_bounds__(TC5_THREADS, 1) gemm_tc5_kernel(const Tc5Args 
 #pragma unroll
                 for (int i = 0; i < 8; ++i) tc5_store4(As, 16 * tile_w + g + 8 * (i >> 2), 16 * (i & 3) + 4 * t, __half2(), __half2());
             }
-            if (c + 1 < n_chunks) fetch(c + 1);
             asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // generic-proxy stores -> visible to the tensor core
             __syncwarp();
             if (lane == 0) tc5_arrive(&full[s]);
+        };
+        // two register sets: the loads of chunk c + 1 are in flight while chunk c is rebuilt
+        Tc5Raw raw_a, raw_b;
+        fetch(0, raw_a);
+        for (int c = 0; c < n_chunks; c += 2) {
+            fetch(c + 1, raw_b);
+            build(c, raw_a);
+            fetch(c + 2, raw_a);
+            if (c + 1 < n_chunks) build(c + 1, raw_b);
         }
     } else if (warp == TC5_PRODUCER_WARPS && lane == 0) {
         // ── MMA issuer ──
@@ -391,8 +425,9 @@ __global__ void __launch_bounds__(TC5_THREADS, 1) gemm_tc5_kernel(const Tc5Args 
         }
         tc5_commit(&done_bar);  // arrives when every MMA above has completed
     }
-    if (warp >= TC5_PRODUCER_WARPS) {
-        // ── epilogue: warp q4 reads TMEM lanes 32 q4 .. +31 (= weight rows), 16 columns (= activation rows) at a time ──
+    if (warp < TC5_PRODUCER_WARPS) {
+        // ── epilogue, by the producers once their last chunk is handed over: warp w reads TMEM lanes 32 (w % 4) .. +31
+        //    (= weight rows), 16 columns (= activation rows) at a time, column groups w / 4, w / 4 + 4, .. ──
         __syncwarp();
         ok = ok && tc5_wait(&done_bar, 0u);
         ok = __all_sync(0xFFFFFFFFu, ok);  // one verdict for the warp: the loads below are warp-collective
@@ -403,7 +438,7 @@ __global__ void __launch_bounds__(TC5_THREADS, 1) gemm_tc5_kernel(const Tc5Args 
             const float bias = (sg.bias && n < sg.n && blockIdx.z == 0) ? sg.bias[n] : 0.f;
             const bool add_res = a.res && si == 0 && a.ksplit == 1;
             float* yb = sg.y;
-            for (int gi = 0; gi < nb / 16; ++gi) {
+            for (int gi = warp >> 2; gi < nb / 16; gi += TC5_PRODUCER_WARPS / 4) {
                 uint32_t r[16];
                 const uint32_t taddr = tmem + ((uint32_t)(32 * q4) << 16) + (uint32_t)(gi * 16);
                 asm volatile(
