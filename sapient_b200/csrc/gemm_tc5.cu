@@ -38,15 +38,17 @@ namespace sp {
 cudaError_t count_launch_and_check();  // kernels.cu
 
 constexpr int TC5_PRODUCER_WARPS = 16;        // two per 16-row tile: one per 64-column group of the stage
-constexpr int TC5_THREADS = 32 * (TC5_PRODUCER_WARPS + 1);  // + the warp that owns the tensor memory; its lane 0 issues the MMAs
-constexpr int TC5_PRODUCERS = 32 * TC5_PRODUCER_WARPS;
-constexpr int TC5_MAX_STAGES = 4;
+constexpr int TC5_THREADS = 32 * (TC5_PRODUCER_WARPS + 2);  // + the MMA warp + the TMA warp
+// Warp 0 (the oldest, which the scheduler favours) owns the tensor memory and its lane 0 issues the MMAs; warp 1 lane 0 runs the TMA.
+constexpr int TC5_MMA_WARP = 0, TC5_FIRST_PRODUCER = 2;
+constexpr int TC5_MAX_STAGES = 8;              // ring of activation tiles in shared memory
+constexpr int TC5_A_STAGES = 4;                // ring of weight tiles in tensor memory, 64 columns (128 fp16 per row) each
+constexpr int TC5_TMEM_COLS = 512;             // columns 0 .. 255: accumulators; 256 + 64 s ..: weight stage s
 constexpr int TC5_BM = 128;                    // weight rows per CTA
-constexpr int TC5_BK = 128;                    // columns per stage = two 128-byte swizzle rows of fp16 (two sub-tiles)
+constexpr int TC5_BK = 128;                    // columns per stage = two 128-byte swizzle rows of fp16 activations
 constexpr int TC5_NB_MAX = 256;                // activation rows per CTA
-constexpr int TC5_A_SUB = TC5_BM * 128;        // one 64-column sub-tile of the weights: 16 KB
-constexpr int TC5_A_BYTES = 2 * TC5_A_SUB;
-constexpr int TC5_SMEM_LIMIT = 200 * 1024;
+constexpr int TC5_SMEM_LIMIT = 192 * 1024;
+constexpr int TC5_SMEM_MIN = 120 * 1024;       // more than half an SM's shared memory: one CTA per SM, which owns all of its tensor memory
 constexpr int TC5_SPIN_LIMIT = 1 << 22;
 
 __device__ int g_tc5_timeout = 0;
@@ -77,6 +79,35 @@ __device__ __forceinline__ void tc5_mma(uint32_t d_tmem, uint64_t adesc, uint64_
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
         "}\n" ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");
+}
+
+// The same with the A operand (weights) read from tensor memory: lane = weight row, 8 columns = 16 fp16 along K.
+__device__ __forceinline__ void tc5_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
+        "}\n" ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// The same, always accumulating.
+__device__ __forceinline__ void tc5_mma_ts_acc(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.eq.u32 p, 1, 1;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
+        "}\n" ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc)
+        : "memory");
+}
+
+// 16 lanes x 8 columns of tensor memory from a warp, in the layout of an mma accumulator fragment: lane (g, t) gives
+// columns 2 t, 2 t + 1 of lane g (v[0], v[1]) and of lane g + 8 (v[2], v[3]).
+__device__ __forceinline__ void tc5_tmem_st(uint32_t taddr, const uint32_t (&v)[4]) {
+    asm volatile("tcgen05.st.sync.aligned.16x256b.x1.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3])
+                 : "memory");
 }
 
 __device__ __forceinline__ void tc5_commit(uint64_t* bar) {
@@ -164,13 +195,6 @@ __device__ __forceinline__ void tc5_load(const uint8_t* tile, int lane, int cq, 
     }
 }
 
-// Stores 4 consecutive fp16 weights (columns c0 .. c0+3 of the chunk, c0 % 4 == 0) of CTA-tile row `row` into the
-// swizzled K-major stage: e02 holds columns (c0, c0+2), e13 columns (c0+1, c0+3).
-__device__ __forceinline__ void tc5_store4(uint8_t* As, int row, int c0, __half2 e02, __half2 e13) {
-    const uint2 v = make_uint2(__byte_perm(bits_h2(e02), bits_h2(e13), 0x5410), __byte_perm(bits_h2(e02), bits_h2(e13), 0x7632));
-    *reinterpret_cast<uint2*>(As + row * 128 + ((((c0 >> 3) ^ (row & 7))) << 4) + (c0 & 4) * 2) = v;
-}
-
 // Byte b (< 128) of v as the float 0.5 + n / 256: bit pattern 0x3F000000 | n << 16. With it a weight s * n + c costs one
 // byte permute and one fused multiply-add: fmaf(half_plus(v, b), 256 s, c - 128 s).
 __device__ __forceinline__ float half_plus(uint32_t v, int b) { return __uint_as_float(__byte_perm(v, 0x3F000000u, 0x7044 | (b << 8))); }
@@ -182,26 +206,20 @@ __device__ __forceinline__ float byte_f32(uint32_t v, int b) {
 
 __device__ __forceinline__ uint32_t u4_word(const uint4& v, int i) { return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w; }
 
-// A thread's stores into the swizzled stage. Lane (g, t) owns, in rows g and g + 8 of its warp's 16-row tile, the four
-// column runs 16 cg + 4 t .. + 3 (cg = 0..3) of the 64-column group. With
-//   bsw = shared address of (tile row g, byte 8 (t & 1)) | ((t >> 1) ^ g) << 4
-// run cg of row g + 8 hi8 sits at (bsw ^ cg << 5) + 1024 hi8: the 16-byte slot 2 cg + (t >> 1) xor-ed with row % 8 = g.
-template <int HI8>
-__device__ __forceinline__ void tc5_sts(uint32_t addr, uint32_t x, uint32_t y) {
-    asm volatile("st.shared.v2.b32 [%0 + %3], {%1, %2};\n" ::"r"(addr), "r"(x), "r"(y), "n"(HI8 * 1024) : "memory");
+// A thread's 32 rebuilt weights: o[cg] is its share of columns 16 cg .. 16 cg + 15 of the 64-column group, as the four
+// words tc5_tmem_st takes: lane (g, t) holds columns 16 cg + 4 t .. + 3 of tile rows g (words 0, 1) and g + 8 (2, 3).
+typedef uint32_t Tc5Out[4][4];
+__device__ __forceinline__ void tc5_put(Tc5Out& o, int cg, int hi8, uint32_t c01, uint32_t c23) {
+    o[cg][2 * hi8] = c01;
+    o[cg][2 * hi8 + 1] = c23;
 }
-__device__ __forceinline__ void tc5_sts(uint32_t addr, int hi8, uint32_t x, uint32_t y) {
-    if (hi8) tc5_sts<1>(addr, x, y);
-    else tc5_sts<0>(addr, x, y);
-}
-__device__ __forceinline__ void tc5_sts4f(uint32_t addr, int hi8, float f0, float f1, float f2, float f3) {
-    tc5_sts(addr, hi8, bits_h2(__floats2half2_rn(f0, f1)), bits_h2(__floats2half2_rn(f2, f3)));
+__device__ __forceinline__ void tc5_put4f(Tc5Out& o, int cg, int hi8, float f0, float f1, float f2, float f3) {
+    tc5_put(o, cg, hi8, bits_h2(__floats2half2_rn(f0, f1)), bits_h2(__floats2half2_rn(f2, f3)));
 }
 
-// Converts the raw words of chunk group cq to fp16 and stores the thread's 32 weights.
+// Converts the raw words of chunk group cq to the thread's 32 fp16 weights.
 template <int DT>
-__device__ __forceinline__ void tc5_convert_store(const Tc5Raw& r, int cq, uint32_t bsw) {
-    const uint32_t run[4] = {bsw, bsw ^ 32u, bsw ^ 64u, bsw ^ 96u};
+__device__ __forceinline__ void tc5_convert(const Tc5Raw& r, int cq, Tc5Out& o) {
     if (DT == T_Q4_K) {
 #pragma unroll
         for (int hi8 = 0; hi8 < 2; ++hi8) {
@@ -237,7 +255,7 @@ __device__ __forceinline__ void tc5_convert_store(const Tc5Raw& r, int cq, uint3
                 for (int hh = 0; hh < 2; ++hh) {
                     const uint32_t mask = hh ? 0x00F000F0u : 0x000F000Fu;
                     const __half2 p02 = h2_bits((w & mask) | 0x64006400u), p13 = h2_bits((w8 & mask) | 0x64006400u);
-                    tc5_sts4f(run[2 * hh + h16], hi8, fmaf(__low2float(p02), sl[hh], cl[hh]), fmaf(__low2float(p13), sl[hh], cl[hh]),
+                    tc5_put4f(o, 2 * hh + h16, hi8, fmaf(__low2float(p02), sl[hh], cl[hh]), fmaf(__low2float(p13), sl[hh], cl[hh]),
                               fmaf(__high2float(p02), sl[hh], cl[hh]), fmaf(__high2float(p13), sl[hh], cl[hh]));
                 }
             }
@@ -253,7 +271,7 @@ __device__ __forceinline__ void tc5_convert_store(const Tc5Raw& r, int cq, uint3
                     const uint32_t v = u4_word(r.q[blk], 2 * hi8 + h16) ^ 0x80808080u;  // int8 -> offset-128 unsigned
                     const uint32_t e02 = bits_h2(__hmul2(bytes02(v, 0x00FF00FFu, 1152.f), d));       // columns +0, +2
                     const uint32_t e13 = bits_h2(__hmul2(bytes02(v >> 8, 0x00FF00FFu, 1152.f), d));  // columns +1, +3
-                    tc5_sts(run[2 * blk + h16], hi8, __byte_perm(e02, e13, 0x5410), __byte_perm(e02, e13, 0x7632));
+                    tc5_put(o, 2 * blk + h16, hi8, __byte_perm(e02, e13, 0x5410), __byte_perm(e02, e13, 0x7632));
                 }
             }
         }
@@ -277,7 +295,7 @@ __device__ __forceinline__ void tc5_convert_store(const Tc5Raw& r, int cq, uint3
                     // dsc * (q - 32) = 256 dsc * (0.5 + q / 256) - 160 dsc: both constants exact, one rounding in the fma
                     const float s256 = 256.0f * dsc, c = -160.0f * dsc;
                     const uint32_t q = ((odd ? (ql >> 4) : ql) & 0x0F0F0F0Fu) | (((qh >> (2 * quarter)) & 0x03030303u) << 4);
-                    tc5_sts4f(run[2 * ab + p], hi8, fmaf(half_plus(q, 0), s256, c), fmaf(half_plus(q, 1), s256, c),
+                    tc5_put4f(o, 2 * ab + p, hi8, fmaf(half_plus(q, 0), s256, c), fmaf(half_plus(q, 1), s256, c),
                               fmaf(half_plus(q, 2), s256, c), fmaf(half_plus(q, 3), s256, c));
                 }
             }
@@ -296,13 +314,13 @@ struct Tc5Args {
     int ldres;
     int ksplit;         // > 1: gridDim.z CTAs share a tile's K range and ADD their parts into y (y must already hold the
                         // residual: res == y); the order of the f32 additions then varies from run to run
-    int stage_bytes;    // TC5_A_BYTES + 256 * (widest activation tile of the launch, rounded to 16)
-    int stages;         // ring depth that fits shared memory (2..4)
+    int stage_bytes;    // 256 * (widest activation tile of the launch, rounded to 16): two boxes of 64 columns
+    int stages;         // depth of the activation ring that fits shared memory (3..8)
 };
 
 __global__ void __launch_bounds__(TC5_THREADS, 1) gemm_tc5_kernel(const Tc5Args a, const __grid_constant__ CUtensorMap tmap_x) {
     extern __shared__ uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t full[TC5_MAX_STAGES], empty[TC5_MAX_STAGES], done_bar;
+    __shared__ __align__(8) uint64_t full_a[TC5_A_STAGES], empty_a[TC5_A_STAGES], full_b[TC5_MAX_STAGES], empty_b[TC5_MAX_STAGES], done_bar;
     __shared__ uint32_t tmem_slot;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     uint8_t* smem = smem_raw + ((1024u - (tc5_smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -315,23 +333,25 @@ __global__ void __launch_bounds__(TC5_THREADS, 1) gemm_tc5_kernel(const Tc5Args 
     const int n0 = bx * TC5_BM, m0 = blockIdx.y * TC5_NB_MAX;
     const int rows_here = min(TC5_NB_MAX, a.m - m0);
     const int nb = (rows_here + 15) & ~15;  // the MMA's N
-    const int tmem_cols = nb <= 32 ? 32 : nb <= 64 ? 64 : nb <= 128 ? 128 : 256;
     const int kts = a.k >> 8, n_tile_rows = (sg.n + 15) >> 4;
     // this CTA's share of the K range (all of it unless the launch splits K)
     const int all_chunks = a.k / TC5_BK;
     const int c_begin = (int)((int64_t)blockIdx.z * all_chunks / a.ksplit), c_end = (int)((int64_t)(blockIdx.z + 1) * all_chunks / a.ksplit);
     const int n_chunks = c_end - c_begin;
 
-    if (warp == TC5_PRODUCER_WARPS) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tc5_smem_u32(&tmem_slot)), "r"(tmem_cols)
+    if (warp == TC5_MMA_WARP) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tc5_smem_u32(&tmem_slot)), "r"(TC5_TMEM_COLS)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
     }
     if (tid == 0) {
+        for (int s = 0; s < TC5_A_STAGES; ++s) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(tc5_smem_u32(&full_a[s])), "r"(TC5_PRODUCER_WARPS) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(tc5_smem_u32(&empty_a[s])) : "memory");
+        }
         for (int s = 0; s < a.stages; ++s) {
-            // 16 producer warps + the thread that announces the TMA bytes
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(tc5_smem_u32(&full[s])), "r"(TC5_PRODUCER_WARPS + 1) : "memory");
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(tc5_smem_u32(&empty[s])) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(tc5_smem_u32(&full_b[s])) : "memory");  // the TMA thread, + bytes
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(tc5_smem_u32(&empty_b[s])) : "memory");
         }
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(tc5_smem_u32(&done_bar)) : "memory");
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -344,15 +364,16 @@ __global__ void __launch_bounds__(TC5_THREADS, 1) gemm_tc5_kernel(const Tc5Args 
     pdl_trigger();
 
     bool ok = true;
-    if (warp < TC5_PRODUCER_WARPS) {
-        // ── producers: warps 2 w and 2 w + 1 rebuild 16-row tile w of the CTA's eight, one 64-column group each ──
-        const int tile_w = warp >> 1, sub = warp & 1;
+    const int pw = warp - TC5_FIRST_PRODUCER;  // producer index 0..15 (negative: the two service warps)
+    if (pw >= 0) {
+        // ── producers: a warp may touch only the 32 tensor-memory lanes of its quarter (warp % 4); the four producers of
+        //    a quarter take its two 16-row tiles x the two 64-column groups of each chunk ──
+        const int tile_w = 2 * (warp & 3) + ((pw >> 2) & 1), sub = pw >> 3;
         const int rt = (n0 >> 4) + tile_w;
         const bool row_live = rt < n_tile_rows;
         const uint8_t* tile_row = sg.wt + (int64_t)rt * kts * TILE_BYTES;
-        // where this lane's runs start inside a 64-column stage group (see tc5_sts)
-        const uint32_t thread_off = (uint32_t)(tile_w * 2048 + (lane >> 2) * 128 + (lane & 1) * 8);
-        const uint32_t thread_sw = (uint32_t)((((lane & 3) >> 1) ^ (lane >> 2)) << 4);
+        // lanes 16 tile_w .. + 15, columns of stage 0 of the weight ring
+        const uint32_t a_base = tmem + ((uint32_t)(16 * tile_w) << 16) + (uint32_t)(TC5_NB_MAX + 32 * sub);
         auto fetch = [&](int c, Tc5Raw& raw) {  // global loads of stage-chunk c (group 2 c + sub of the row's superblocks)
             const int grp = 2 * (c_begin + c) + sub;
             if (row_live && c < n_chunks) {
@@ -362,40 +383,27 @@ __global__ void __launch_bounds__(TC5_THREADS, 1) gemm_tc5_kernel(const Tc5Args 
                 else tc5_load<T_Q8_0>(tile, lane, grp & 3, raw);
             }
         };
-        const uint32_t b_bytes = (uint32_t)(a.stage_bytes - TC5_A_BYTES);  // both 64-column sub-tiles of the activations
         int s = -1, u = 0;  // stage of the current chunk and the number of times the ring has wrapped
-        auto build = [&](int c, const Tc5Raw& raw) {  // chunk c: wait for its stage, start the activation copy, rebuild the weights
-            if (++s == a.stages) { s = 0; ++u; }
-            uint8_t* As = smem + (size_t)s * a.stage_bytes + sub * TC5_A_SUB;
-            if (u > 0) ok = ok && tc5_wait(&empty[s], (uint32_t)((u - 1) & 1));  // the MMAs of chunk c - stages have read this stage
-            if (tid == 0) {
-                // TMA: the stage's activation tile, two boxes of (64 columns x nb_max rows), counted in bytes on `full`
-                const uint32_t bar = tc5_smem_u32(&full[s]);
-                const uint32_t dst = tc5_smem_u32(smem + (size_t)s * a.stage_bytes + TC5_A_BYTES);
-                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(b_bytes) : "memory");
-#pragma unroll
-                for (int h = 0; h < 2; ++h)
-                    asm volatile(
-                        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::"r"(
-                            dst + h * (b_bytes / 2)),
-                        "l"(&tmap_x), "r"((c_begin + c) * TC5_BK + 64 * h), "r"(m0), "r"(bar)
-                        : "memory");
-            }
+        auto build = [&](int c, const Tc5Raw& raw) {  // chunk c: rebuild the weights in registers, wait for its stage, store
+            if (++s == TC5_A_STAGES) { s = 0; ++u; }
+            Tc5Out o;
             if (row_live) {
                 const int cq = (2 * (c_begin + c) + sub) & 3;
-                const uint32_t bsw = (tc5_smem_u32(As) + thread_off) | thread_sw;
-                if (DT == T_Q4_K) tc5_convert_store<T_Q4_K>(raw, cq, bsw);
-                else if (DT == T_Q6_K) tc5_convert_store<T_Q6_K>(raw, cq, bsw);
-                else tc5_convert_store<T_Q8_0>(raw, cq, bsw);
+                if (DT == T_Q4_K) tc5_convert<T_Q4_K>(raw, cq, o);
+                else if (DT == T_Q6_K) tc5_convert<T_Q6_K>(raw, cq, o);
+                else tc5_convert<T_Q8_0>(raw, cq, o);
             } else {
-                // rows past the matrix: zeros (8 runs of 4 halves per thread, same addresses as a live tile)
-                const int g = lane >> 2, t = lane & 3;
 #pragma unroll
-                for (int i = 0; i < 8; ++i) tc5_store4(As, 16 * tile_w + g + 8 * (i >> 2), 16 * (i & 3) + 4 * t, __half2(), __half2());
+                for (int i = 0; i < 16; ++i) o[i >> 2][i & 3] = 0u;  // rows past the matrix
             }
-            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // generic-proxy stores -> visible to the tensor core
+            if (u > 0) ok = ok && tc5_wait(&empty_a[s], (uint32_t)((u - 1) & 1));  // the MMAs of chunk c - 4 have read this stage
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+#pragma unroll
+            for (int cg = 0; cg < 4; ++cg) tc5_tmem_st(a_base + (uint32_t)(64 * s + 8 * cg), o[cg]);
+            asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
             __syncwarp();
-            if (lane == 0) tc5_arrive(&full[s]);
+            if (lane == 0) tc5_arrive(&full_a[s]);
         };
         // two register sets: the loads of chunk c + 1 are in flight while chunk c is rebuilt
         Tc5Raw raw_a, raw_b;
@@ -406,28 +414,58 @@ __global__ void __launch_bounds__(TC5_THREADS, 1) gemm_tc5_kernel(const Tc5Args 
             fetch(c + 2, raw_a);
             if (c + 1 < n_chunks) build(c + 1, raw_b);
         }
-    } else if (warp == TC5_PRODUCER_WARPS && lane == 0) {
-        // ── MMA issuer ──
-        const uint32_t idesc = tc5_idesc(nb);
-        for (int c = 0; c < n_chunks; ++c) {
-            const int s = c % a.stages, u = c / a.stages;
-            ok = ok && tc5_wait(&full[s], (uint32_t)(u & 1));  // after one expired wait nothing else is waited for
-            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-            const uint32_t As = tc5_smem_u32(smem + (size_t)s * a.stage_bytes);
+    } else if (warp == TC5_MMA_WARP) {
+        if (lane == 0) {
+            // ── MMA issuer ──
+            // The issuing thread is the serial part of the pipeline: per chunk two waits, eight MMAs whose operands are one
+            // add away from per-stage bases, two commits.
+            const uint32_t idesc = tc5_idesc(nb);
+            const uint64_t bd0 = tc5_desc(tc5_smem_u32(smem));
+            const uint32_t bd_hi = (uint32_t)(bd0 >> 32), bd_lo0 = (uint32_t)bd0;
+            const uint32_t stage16 = (uint32_t)a.stage_bytes >> 4, half16 = stage16 >> 1;
+            uint32_t accumulate = 0u;
+            for (int c = 0, sa = 0, ua = 0, sb = 0, ub = 0; c < n_chunks; ++c, ++sa, ++sb) {
+                if (sa == TC5_A_STAGES) { sa = 0; ++ua; }
+                if (sb == a.stages) { sb = 0; ++ub; }
+                ok = ok && tc5_wait(&full_b[sb], (uint32_t)(ub & 1));  // after one expired wait nothing else is waited for
+                ok = ok && tc5_wait(&full_a[sa], (uint32_t)(ua & 1));
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                const uint32_t bd_lo = bd_lo0 + (uint32_t)sb * stage16;  // the address field: no carry out of the low word
+                const uint32_t At = tmem + (uint32_t)(TC5_NB_MAX + 64 * sa);
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {  // the two 64-column sub-tiles of the stage
-                const uint64_t ad = tc5_desc(As + h * TC5_A_SUB), bd = tc5_desc(As + TC5_A_BYTES + h * ((a.stage_bytes - TC5_A_BYTES) / 2));
-#pragma unroll
-                for (int k = 0; k < 4; ++k)  // 16 columns = 32 bytes further inside the swizzle row: +2 in units of 16 B
-                    tc5_mma(tmem, ad + 2 * k, bd + 2 * k, idesc, (c > 0 || h > 0 || k > 0) ? 1u : 0u);
+                for (int i = 0; i < 8; ++i) {  // 16 columns each: 8 columns of tensor memory, 32 bytes inside the swizzle row (+2 x 16 B)
+                    const uint32_t lo = bd_lo + (uint32_t)(i >> 2) * half16 + 2u * (i & 3);
+                    uint64_t bd;
+                    asm("mov.b64 %0, {%1, %2};\n" : "=l"(bd) : "r"(lo), "r"(bd_hi));
+                    if (i == 0) tc5_mma_ts(tmem, At, bd, idesc, accumulate);
+                    else tc5_mma_ts_acc(tmem, At + 8u * i, bd, idesc);
+                }
+                accumulate = 1u;
+                tc5_commit(&empty_a[sa]);
+                tc5_commit(&empty_b[sb]);
             }
-            tc5_commit(&empty[s]);
+            tc5_commit(&done_bar);  // arrives when every MMA above has completed
         }
-        tc5_commit(&done_bar);  // arrives when every MMA above has completed
+    } else if (lane == 0) {
+        // ── TMA: per chunk the activation tile as two boxes of (64 columns x nb_max rows), counted in bytes on `full_b` ──
+        for (int c = 0, sb = 0, ub = 0; c < n_chunks; ++c, ++sb) {
+            if (sb == a.stages) { sb = 0; ++ub; }
+            if (ub > 0) ok = ok && tc5_wait(&empty_b[sb], (uint32_t)((ub - 1) & 1));
+            const uint32_t bar = tc5_smem_u32(&full_b[sb]);
+            const uint32_t dst = tc5_smem_u32(smem + (size_t)sb * a.stage_bytes);
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(a.stage_bytes) : "memory");
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+                asm volatile(
+                    "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::"r"(
+                        dst + h * (a.stage_bytes / 2)),
+                    "l"(&tmap_x), "r"((c_begin + c) * TC5_BK + 64 * h), "r"(m0), "r"(bar)
+                    : "memory");
+        }
     }
-    if (warp < TC5_PRODUCER_WARPS) {
+    if (pw >= 0) {
         // ── epilogue, by the producers once their last chunk is handed over: warp w reads TMEM lanes 32 (w % 4) .. +31
-        //    (= weight rows), 16 columns (= activation rows) at a time, column groups w / 4, w / 4 + 4, .. ──
+        //    (= weight rows), 16 columns (= activation rows) at a time, column groups pw / 4, pw / 4 + 4, .. ──
         __syncwarp();
         ok = ok && tc5_wait(&done_bar, 0u);
         ok = __all_sync(0xFFFFFFFFu, ok);  // one verdict for the warp: the loads below are warp-collective
@@ -438,7 +476,7 @@ __global__ void __launch_bounds__(TC5_THREADS, 1) gemm_tc5_kernel(const Tc5Args 
             const float bias = (sg.bias && n < sg.n && blockIdx.z == 0) ? sg.bias[n] : 0.f;
             const bool add_res = a.res && si == 0 && a.ksplit == 1;
             float* yb = sg.y;
-            for (int gi = warp >> 2; gi < nb / 16; gi += TC5_PRODUCER_WARPS / 4) {
+            for (int gi = pw >> 2; gi < nb / 16; gi += TC5_PRODUCER_WARPS / 4) {
                 uint32_t r[16];
                 const uint32_t taddr = tmem + ((uint32_t)(32 * q4) << 16) + (uint32_t)(gi * 16);
                 asm volatile(
@@ -466,7 +504,7 @@ __global__ void __launch_bounds__(TC5_THREADS, 1) gemm_tc5_kernel(const Tc5Args 
     if (!ok) atomicExch(&g_tc5_timeout, 1);
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
     __syncthreads();
-    if (warp == TC5_PRODUCER_WARPS) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(tmem_cols) : "memory");
+    if (warp == TC5_MMA_WARP) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(TC5_TMEM_COLS) : "memory");
 }
 
 // x[m, k] f32 -> fp16, one thread per 8 columns.
@@ -519,9 +557,9 @@ cudaError_t launch_gemm_tc5_multi(const Tc5Seg* segs, int nseg, int k, const __h
         if (sm_count <= 0) sm_count = 148;
     }
     const int nb_max = std::min(TC5_NB_MAX, (m + 15) & ~15);
-    const int stage_bytes = TC5_A_BYTES + nb_max * 256;
-    const int stages = std::max(2, std::min(TC5_MAX_STAGES, TC5_SMEM_LIMIT / stage_bytes));
-    const int smem_bytes = stages * stage_bytes + 1024;  // + slack to align the stages to 1024 B
+    const int stage_bytes = nb_max * 256;
+    const int stages = std::min(TC5_MAX_STAGES, TC5_SMEM_LIMIT / stage_bytes);
+    const int smem_bytes = std::max(stages * stage_bytes + 1024, TC5_SMEM_MIN);  // + slack to align the stages to 1024 B
     const int m_tiles = (m + TC5_NB_MAX - 1) / TC5_NB_MAX;
     int ksplit = 1;
     if (nseg == 1 && res && res == segs[0].y) {  // in-place residual: partial sums can simply be added
@@ -548,7 +586,7 @@ cudaError_t launch_gemm_tc5_multi(const Tc5Seg* segs, int nseg, int k, const __h
     }
     a.nseg = nseg; a.k = k; a.xh = xh; a.m = m; a.ldy = ldy; a.res = res; a.ldres = ldres; a.ksplit = ksplit;
     a.stage_bytes = stage_bytes; a.stages = stages;
-    constexpr int SMEM_CAP = 2 * (TC5_A_BYTES + TC5_NB_MAX * 256) + 1024;  // the deepest ring the largest tile allows (193 KB)
+    constexpr int SMEM_CAP = TC5_SMEM_LIMIT + 1024;
     cudaError_t le;
     if (!attr_set) {
         le = cudaFuncSetAttribute(gemm_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_CAP);
