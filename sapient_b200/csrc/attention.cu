@@ -222,8 +222,8 @@ __device__ __forceinline__ uint32_t pack_half2(float a, float b) {
 // HD16 = head_dim / 16 (head_dim a multiple of 16, <= 128).
 template <int HD16>
 __global__ void __launch_bounds__(FA_WARPS * 32)
-attention_prefill_kernel(const float* __restrict__ q, int ldq, float* __restrict__ out, int ldo, int n_tok, int n_heads, int slot, int pos0,
-                         KvGeom kv, int layer, float scale) {
+attention_prefill_kernel(const float* __restrict__ q, int ldq, float* __restrict__ out, __half* __restrict__ out_h, int ldo, int n_tok,
+                         int n_heads, int slot, int pos0, KvGeom kv, int layer, float scale) {
     constexpr int HD = HD16 * 16, LD = HD + 8;  // padded row of the shared tiles (halves): conflict-free fragment loads
     extern __shared__ __align__(16) __half fa_smem[];
     __half* Ks = fa_smem;
@@ -336,16 +336,23 @@ attention_prefill_kernel(const float* __restrict__ q, int ldq, float* __restrict
     const float i0 = (l0 == 0.f) ? 0.f : 1.0f / l0, i1 = (l1 == 0.f) ? 0.f : 1.0f / l1;
 #pragma unroll
     for (int nd = 0; nd < 2 * HD16; ++nd) {
-        if (r0 < n_tok) *reinterpret_cast<float2*>(out + (int64_t)r0 * ldo + (int64_t)h * HD + 8 * nd + 2 * t) = make_float2(o[nd][0] * i0, o[nd][1] * i0);
-        if (r1 < n_tok) *reinterpret_cast<float2*>(out + (int64_t)r1 * ldo + (int64_t)h * HD + 8 * nd + 2 * t) = make_float2(o[nd][2] * i1, o[nd][3] * i1);
+        const int64_t c = (int64_t)h * HD + 8 * nd + 2 * t;
+        if (out_h) {  // fp16 rows for the tensor-core output projection
+            if (r0 < n_tok) *reinterpret_cast<__half2*>(out_h + (int64_t)r0 * ldo + c) = __floats2half2_rn(o[nd][0] * i0, o[nd][1] * i0);
+            if (r1 < n_tok) *reinterpret_cast<__half2*>(out_h + (int64_t)r1 * ldo + c) = __floats2half2_rn(o[nd][2] * i1, o[nd][3] * i1);
+        } else {
+            if (r0 < n_tok) *reinterpret_cast<float2*>(out + (int64_t)r0 * ldo + c) = make_float2(o[nd][0] * i0, o[nd][1] * i0);
+            if (r1 < n_tok) *reinterpret_cast<float2*>(out + (int64_t)r1 * ldo + c) = make_float2(o[nd][2] * i1, o[nd][3] * i1);
+        }
     }
 }
 
 bool attention_prefill_supported(int head_dim) { return head_dim % 16 == 0 && head_dim >= 16 && head_dim <= 128; }
 
 // All n_tok tokens belong to sequence `slot` at positions pos0, pos0 + 1, ... (their keys are in the cache already).
+// out_h != null: the rows go out as fp16 to out_h (same row stride) instead of f32 to out.
 cudaError_t launch_attention_prefill(const float* q, int ldq, float* out, int ldo, int n_tok, int n_heads, int slot, int pos0, KvGeom kv,
-                                     int layer, float scale, cudaStream_t st) {
+                                     int layer, float scale, cudaStream_t st, __half* out_h) {
     if (n_tok <= 0) return cudaSuccess;
     if (!attention_prefill_supported(kv.head_dim)) return cudaErrorInvalidValue;
     const int hd16 = kv.head_dim / 16;
@@ -353,7 +360,7 @@ cudaError_t launch_attention_prefill(const float* q, int ldq, float* out, int ld
     const dim3 grid(n_heads, (n_tok + FA_ROWS - 1) / FA_ROWS), block(FA_WARPS * 32);
     cudaError_t le = cudaErrorInvalidValue;
 #define SP_FA(N) \
-    if (hd16 == N) le = launch_pdl(attention_prefill_kernel<N>, grid, block, smem, st, q, ldq, out, ldo, n_tok, n_heads, slot, pos0, kv, layer, scale)
+    if (hd16 == N) le = launch_pdl(attention_prefill_kernel<N>, grid, block, smem, st, q, ldq, out, out_h, ldo, n_tok, n_heads, slot, pos0, kv, layer, scale)
     SP_FA(1); SP_FA(2); SP_FA(3); SP_FA(4); SP_FA(5); SP_FA(6); SP_FA(7); SP_FA(8);
 #undef SP_FA
     if (le != cudaSuccess) return le;

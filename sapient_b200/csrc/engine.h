@@ -117,6 +117,12 @@ class Engine {
              const DevTensor* w1 = nullptr, const float* b1 = nullptr, float* y1 = nullptr, const DevTensor* w2 = nullptr,
              const float* b2 = nullptr, float* y2 = nullptr, const float* res = nullptr, const ImmaArgs* pre = nullptr,
              bool tp_sum = false);
+    // Many-row steps on one GPU: the producers (norm, attention, activation) write fp16 rows straight into the GEMM's
+    // input buffer; big_m says whether these matrices take that path, gemm_xh multiplies what the buffer holds.
+    bool big_m(int m, int k, const DevTensor* w0, const DevTensor* w1 = nullptr, const DevTensor* w2 = nullptr) const;
+    int gemm_xh(int m, int k, const DevTensor* w0, const float* b0, float* y0, int ldy0, const DevTensor* w1 = nullptr,
+                const float* b1 = nullptr, float* y1 = nullptr, const DevTensor* w2 = nullptr, const float* b2 = nullptr,
+                float* y2 = nullptr, const float* res = nullptr);
     size_t tp_block_bytes() const;
     int tp_alloc();
     void tp_release();

@@ -123,6 +123,26 @@ int Engine::gemv(const float* x, int ldx, int m, int k, const DevTensor* w0, con
     return SP_OK;
 }
 
+bool Engine::big_m(int m, int k, const DevTensor* w0, const DevTensor* w1, const DevTensor* w2) const {
+    if (m < TC5_MIN_M || !use_tc5 || d.tp_size > 1 || !ws_.xh || (size_t)m * k > ws_.xh_elems) return false;
+    const DevTensor* ws[3] = {w0, w1, w2};
+    for (int i = 0; i < 3 && ws[i]; ++i)
+        if (!ws[i]->tiled || !tc5_supported(ws[i]->dtype, k)) return false;
+    return true;
+}
+
+int Engine::gemm_xh(int m, int k, const DevTensor* w0, const float* b0, float* y0, int ldy0, const DevTensor* w1, const float* b1,
+                    float* y1, const DevTensor* w2, const float* b2, float* y2, const float* res) {
+    const DevTensor* ws[3] = {w0, w1, w2};
+    const float* bs[3] = {b0, b1, b2};
+    float* ys[3] = {y0, y1, y2};
+    Tc5Seg segs[3];
+    int ns = 0;
+    for (int i = 0; i < 3 && ws[i]; ++i) segs[ns++] = Tc5Seg{ws[i]->tiled, ys[i], bs[i], ws[i]->dtype, (int)ws[i]->dims[0]};
+    SP_LAUNCH(F_GEMV, launch_gemm_tc5_multi(segs, ns, k, ws_.xh, m, ldy0, res, ldy0, stream));
+    return SP_OK;
+}
+
 static inline bool all_tiled(const DevTensor* a, const DevTensor* b = nullptr, const DevTensor* c = nullptr) {
     return a->tiled && (!b || b->tiled) && (!c || c->tiled);
 }
@@ -142,6 +162,10 @@ int Engine::attention_and_oproj(const LayerW& w, int l, int T) {
     // a prefill chunk (one sequence, consecutive positions): the tiled tensor-core kernel
     bool one_seq = splits == 1 && use_tc5 && attention_prefill_supported(hd);
     for (int i = 1; one_seq && i < T; ++i) one_seq = p_slot_[i] == p_slot_[0] && p_pos_[i] == p_pos_[0] + i;
+    if (one_seq && big_m(T, H * hd, w.o)) {
+        SP_LAUNCH(F_ATTN, launch_attention_prefill(qkv_, qkv_ld, nullptr, H * hd, T, H, p_slot_[0], p_pos_[0], kv_, l, scale, stream, ws_.xh));
+        return gemm_xh(T, H * hd, w.o, w.ob, x_, hid, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, x_);
+    }
     if (one_seq) {
         SP_LAUNCH(F_ATTN, launch_attention_prefill(qkv_, qkv_ld, attn_, H * hd, T, H, p_slot_[0], p_pos_[0], kv_, l, scale, stream));
         return gemv(attn_, H * hd, T, H * hd, w.o, w.ob, x_, hid, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, x_, nullptr, true);
@@ -155,7 +179,10 @@ int Engine::layer_llama(const LayerW& w, int l, int T) {
     const int H = d.n_heads, Hkv = d.n_kv_heads, hd = d.head_dim, hid = d.hidden, ffn = d.ffn;
     const int qkv_ld = (H + 2 * Hkv) * hd;
     ImmaArgs ia;
-    if (all_tiled(w.q, w.k, w.v) && plan_digits(T, hid, ia)) {
+    if (big_m(T, hid, w.q, w.k, w.v)) {
+        SP_LAUNCH(F_NORM, launch_rms_norm_f16(x_, w.n1w, T, hid, d.norm_eps, ws_.xh, stream));
+        SP_TRY(gemm_xh(T, hid, w.q, w.qb, qkv_, qkv_ld, w.k, w.kb, qkv_ + (size_t)H * hd, w.v, w.vb, qkv_ + (size_t)(H + Hkv) * hd));
+    } else if (all_tiled(w.q, w.k, w.v) && plan_digits(T, hid, ia)) {
         SP_LAUNCH(F_NORM, launch_norm_quant(x_, hid, w.n1w, nullptr, false, d.norm_eps, nullptr, 0, ia, stream, tp_take()));
         SP_TRY(gemv(h_, hid, T, hid, w.q, w.qb, qkv_, qkv_ld, w.k, w.kb, qkv_ + (size_t)H * hd, w.v, w.vb,
                     qkv_ + (size_t)(H + Hkv) * hd, nullptr, &ia));
@@ -167,7 +194,10 @@ int Engine::layer_llama(const LayerW& w, int l, int T) {
     }
     SP_LAUNCH(F_ROPE, launch_rope_kv_append(qkv_, T, H, Hkv, hd, d.rotary_dim, cos_sin_, d_tok_slot_, d_tok_pos_, kv_, l, kv_round, stream));
     SP_TRY(attention_and_oproj(w, l, T));
-    if (all_tiled(w.gate, w.up) && plan_digits(T, hid, ia)) {
+    if (big_m(T, hid, w.gate, w.up)) {
+        SP_LAUNCH(F_NORM, launch_rms_norm_f16(x_, w.n2w, T, hid, d.norm_eps, ws_.xh, stream));
+        SP_TRY(gemm_xh(T, hid, w.gate, nullptr, gu_, 2 * ffn, w.up, nullptr, gu_ + ffn));
+    } else if (all_tiled(w.gate, w.up) && plan_digits(T, hid, ia)) {
         SP_LAUNCH(F_NORM, launch_norm_quant(x_, hid, w.n2w, nullptr, false, d.norm_eps, nullptr, 0, ia, stream, tp_take()));
         SP_TRY(gemv(h_, hid, T, hid, w.gate, nullptr, gu_, 2 * ffn, w.up, nullptr, gu_ + ffn, nullptr, nullptr, nullptr, nullptr, &ia));
     } else {
@@ -175,7 +205,10 @@ int Engine::layer_llama(const LayerW& w, int l, int T) {
         SP_LAUNCH(F_NORM, launch_rms_norm(x_, w.n2w, T, hid, d.norm_eps, h_, stream));
         SP_TRY(gemv(h_, hid, T, hid, w.gate, nullptr, gu_, 2 * ffn, w.up, nullptr, gu_ + ffn));
     }
-    if (all_tiled(w.down) && plan_digits(T, ffn, ia)) {
+    if (big_m(T, ffn, w.down)) {
+        SP_LAUNCH(F_ELEM, launch_act_f16(gu_, 2 * ffn, ffn, T, 0, ws_.xh, stream));
+        SP_TRY(gemm_xh(T, ffn, w.down, nullptr, x_, hid, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, x_));
+    } else if (all_tiled(w.down) && plan_digits(T, ffn, ia)) {
         SP_LAUNCH(F_ELEM, launch_act_fn_quant(gu_, 2 * ffn, ffn, 0, ia, stream));
         SP_TRY(gemv(mid_, ffn, T, ffn, w.down, nullptr, x_, hid, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, x_, &ia, true));
     } else {
@@ -190,7 +223,11 @@ int Engine::layer_phi(const LayerW& w, int l, int T) {
     const int qkv_ld = (H + 2 * Hkv) * hd;
     // parallel block: x + (attn_out + mlp(h)); both branches read the same normalised input h
     ImmaArgs ia;
-    if (all_tiled(w.q, w.k, w.v) && all_tiled(w.up) && plan_digits(T, hid, ia)) {
+    if (big_m(T, hid, w.q, w.k, w.v) && big_m(T, hid, w.up)) {
+        SP_LAUNCH(F_NORM, launch_layer_norm_f16(x_, w.n1w, w.n1b, T, hid, d.norm_eps, ws_.xh, stream));
+        SP_TRY(gemm_xh(T, hid, w.q, w.qb, qkv_, qkv_ld, w.k, w.kb, qkv_ + (size_t)H * hd, w.v, w.vb, qkv_ + (size_t)(H + Hkv) * hd));
+        SP_TRY(gemm_xh(T, hid, w.up, w.upb, gu_, ffn));
+    } else if (all_tiled(w.q, w.k, w.v) && all_tiled(w.up) && plan_digits(T, hid, ia)) {
         SP_LAUNCH(F_NORM, launch_norm_quant(x_, hid, w.n1w, w.n1b, true, d.norm_eps, nullptr, 0, ia, stream));
         SP_TRY(gemv(h_, hid, T, hid, w.q, w.qb, qkv_, qkv_ld, w.k, w.kb, qkv_ + (size_t)H * hd, w.v, w.vb,
                     qkv_ + (size_t)(H + Hkv) * hd, nullptr, &ia));
@@ -204,7 +241,10 @@ int Engine::layer_phi(const LayerW& w, int l, int T) {
     SP_LAUNCH(F_ROPE, launch_rope_kv_append(qkv_, T, H, Hkv, hd, d.rotary_dim, cos_sin_, d_tok_slot_, d_tok_pos_, kv_, l, kv_round, stream));
     // the MLP's fc1 output waits in gu_ while the workspace serves the attention output projection
     SP_TRY(attention_and_oproj(w, l, T));
-    if (all_tiled(w.down) && plan_digits(T, ffn, ia)) {
+    if (big_m(T, ffn, w.down)) {
+        SP_LAUNCH(F_ELEM, launch_act_f16(gu_, ffn, ffn, T, 1, ws_.xh, stream));
+        SP_TRY(gemm_xh(T, ffn, w.down, w.downb, x_, hid, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, x_));
+    } else if (all_tiled(w.down) && plan_digits(T, ffn, ia)) {
         SP_LAUNCH(F_ELEM, launch_act_fn_quant(gu_, ffn, ffn, 1, ia, stream));
         SP_TRY(gemv(mid_, ffn, T, ffn, w.down, w.downb, x_, hid, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, x_, &ia));
     } else {

@@ -278,20 +278,24 @@ __device__ __forceinline__ float block_sum(float v, float* sh) {
     return t;
 }
 
+// yh != null: the row goes out as fp16 (input of the tensor-core GEMM) instead of f32.
 __global__ void rms_norm_kernel(const float* __restrict__ x, const float* __restrict__ w, int dim, float eps,
-                                float* __restrict__ y) {
+                                float* __restrict__ y, __half* __restrict__ yh) {
     __shared__ float sh[32];
     const float* s = x + (int64_t)blockIdx.x * dim;
     float acc = 0.f;
     for (int i = threadIdx.x; i < dim; i += blockDim.x) acc = fmaf(s[i], s[i], acc);
     const float sum = block_sum(acc, sh);
     const float inv = 1.0f / sqrtf(sum / (float)dim + eps);
-    for (int i = threadIdx.x; i < dim; i += blockDim.x)
-        y[(int64_t)blockIdx.x * dim + i] = __fmul_rn(__fmul_rn(s[i], inv), w ? w[i] : 1.0f);
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+        const float v = __fmul_rn(__fmul_rn(s[i], inv), w ? w[i] : 1.0f);
+        if (yh) yh[(int64_t)blockIdx.x * dim + i] = __float2half_rn(v);
+        else y[(int64_t)blockIdx.x * dim + i] = v;
+    }
 }
 
 __global__ void layer_norm_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ b,
-                                  int dim, float eps, float* __restrict__ y) {
+                                  int dim, float eps, float* __restrict__ y, __half* __restrict__ yh) {
     __shared__ float sh[32];
     const float* s = x + (int64_t)blockIdx.x * dim;
     float acc = 0.f;
@@ -305,19 +309,31 @@ __global__ void layer_norm_kernel(const float* __restrict__ x, const float* __re
         float v = __fmul_rn(s[i] - mean, inv);
         if (w) v = __fmul_rn(v, w[i]);
         if (b) v = __fadd_rn(v, b[i]);
-        y[(int64_t)blockIdx.x * dim + i] = v;
+        if (yh) yh[(int64_t)blockIdx.x * dim + i] = __float2half_rn(v);
+        else y[(int64_t)blockIdx.x * dim + i] = v;
     }
 }
 
 cudaError_t launch_rms_norm(const float* x, const float* w, int rows, int dim, float eps, float* y, cudaStream_t st) {
     if (rows == 0) return cudaSuccess;
-    rms_norm_kernel<<<rows, 256, 0, st>>>(x, w, dim, eps, y);
+    rms_norm_kernel<<<rows, 256, 0, st>>>(x, w, dim, eps, y, nullptr);
+    return finish_launch();
+}
+cudaError_t launch_rms_norm_f16(const float* x, const float* w, int rows, int dim, float eps, __half* yh, cudaStream_t st) {
+    if (rows == 0) return cudaSuccess;
+    rms_norm_kernel<<<rows, 256, 0, st>>>(x, w, dim, eps, nullptr, yh);
+    return finish_launch();
+}
+cudaError_t launch_layer_norm_f16(const float* x, const float* w, const float* b, int rows, int dim, float eps, __half* yh,
+                                  cudaStream_t st) {
+    if (rows == 0) return cudaSuccess;
+    layer_norm_kernel<<<rows, 256, 0, st>>>(x, w, b, dim, eps, nullptr, yh);
     return finish_launch();
 }
 cudaError_t launch_layer_norm(const float* x, const float* w, const float* b, int rows, int dim, float eps, float* y,
                               cudaStream_t st) {
     if (rows == 0) return cudaSuccess;
-    layer_norm_kernel<<<rows, 256, 0, st>>>(x, w, b, dim, eps, y);
+    layer_norm_kernel<<<rows, 256, 0, st>>>(x, w, b, dim, eps, y, nullptr);
     return finish_launch();
 }
 
@@ -435,6 +451,25 @@ __global__ void swiglu_kernel(const float* __restrict__ gu, int ld, int ffn, int
         out[i] = __fmul_rn(silu_f(g), u);
     }
 }
+// The MLP activation straight to fp16 [rows][ffn]: kind 0 = silu(gate) * up with gate | up side by side in a row of gu,
+// kind 1 = gelu. Two columns per thread.
+__global__ void act_f16_kernel(const float* __restrict__ gu, int ld, int ffn, int64_t total2, int kind, __half2* __restrict__ out) {
+    const int half_ffn = ffn >> 1;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total2; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / half_ffn, c = 2 * (i - r * half_ffn);
+        const float2 g = *reinterpret_cast<const float2*>(gu + r * ld + c);
+        float a0, a1;
+        if (kind == 0) {
+            const float2 u = *reinterpret_cast<const float2*>(gu + r * ld + ffn + c);
+            a0 = __fmul_rn(silu_f(g.x), u.x);
+            a1 = __fmul_rn(silu_f(g.y), u.y);
+        } else {
+            a0 = gelu_f(g.x);
+            a1 = gelu_f(g.y);
+        }
+        out[i] = __floats2half2_rn(a0, a1);
+    }
+}
 __global__ void gelu_kernel(float* x, int64_t n) {
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) x[i] = gelu_f(x[i]);
 }
@@ -457,6 +492,13 @@ cudaError_t launch_swiglu(const float* gate_up, int ld, int ffn, int rows, float
     const int64_t total = (int64_t)rows * ffn;
     if (total == 0) return cudaSuccess;
     swiglu_kernel<<<ew_blocks(total), 256, 0, st>>>(gate_up, ld, ffn, total, out);
+    return finish_launch();
+}
+cudaError_t launch_act_f16(const float* gu, int ld, int ffn, int rows, int kind, __half* out, cudaStream_t st) {
+    const int64_t total2 = (int64_t)rows * ffn / 2;
+    if (total2 == 0) return cudaSuccess;
+    if ((ffn & 1) || (ld & 1)) return cudaErrorInvalidValue;
+    act_f16_kernel<<<ew_blocks(total2), 256, 0, st>>>(gu, ld, ffn, total2, kind, reinterpret_cast<__half2*>(out));
     return finish_launch();
 }
 cudaError_t launch_gelu(float* x, int64_t n, cudaStream_t st) {

@@ -72,7 +72,7 @@ cudaError_t launch_attention_split(const float* q, int ldq, int n_tok, int n_hea
 // Prefill attention on tensor cores: n_tok tokens of one sequence at consecutive positions pos0.. (keys already cached).
 bool attention_prefill_supported(int head_dim);
 cudaError_t launch_attention_prefill(const float* q, int ldq, float* out, int ldo, int n_tok, int n_heads, int slot, int pos0, KvGeom kv,
-                                     int layer, float scale, cudaStream_t st);
+                                     int layer, float scale, cudaStream_t st, __half* out_h = nullptr);
 
 // Workspace of the activation digits for up to 16 activation rows of k_max columns.
 struct ActWorkspace {
@@ -114,6 +114,10 @@ cudaError_t launch_gemv(const GemvArgs& a, cudaStream_t st);
 cudaError_t launch_embed(int dtype, const uint8_t* table, int64_t hidden, const uint32_t* ids, int n_tok, float* out,
                          cudaStream_t st);
 cudaError_t launch_rms_norm(const float* x, const float* w, int rows, int dim, float eps, float* y, cudaStream_t st);
+cudaError_t launch_rms_norm_f16(const float* x, const float* w, int rows, int dim, float eps, __half* yh, cudaStream_t st);
+cudaError_t launch_layer_norm_f16(const float* x, const float* w, const float* b, int rows, int dim, float eps, __half* yh,
+                                  cudaStream_t st);
+cudaError_t launch_act_f16(const float* gu, int ld, int ffn, int rows, int kind, __half* out, cudaStream_t st);
 cudaError_t launch_layer_norm(const float* x, const float* w, const float* b, int rows, int dim, float eps, float* y,
                               cudaStream_t st);
 // In-place NEOX rotation of the q heads of qkv[T, (H+2Hkv)*hd]; rotated k and raw v are
