@@ -94,7 +94,7 @@ cudaError_t launch_quant_gemv(const float* x, int ldx, ImmaArgs& a, const ActWor
 
 // Large-M dequant GEMM on tcgen05 / TMEM (gemm_tc5.cu): y[m, n] = x·Wᵀ (+ bias, + res) from the tiled weights and an
 // fp16 copy of the activations; k % 256 == 0, Q4_K / Q6_K / Q8_0.
-constexpr int TC5_MIN_M = 64;  // below this the 16-row GEMV passes are faster (measured: 94 vs 64 us at m = 32, 96 vs 128 at 64)
+constexpr int TC5_MIN_M = 17;  // up to 16 rows one GEMV pass is faster; from 17 rows on (two passes) the tcgen05 GEMM wins (measured at 32 rows: 5.6 vs 7.1 ms per decode step of the 8B shape)
 bool tc5_supported(int dtype, int64_t k);
 cudaError_t launch_x_to_f16(const float* x, int ldx, int m, int k, __half* out, cudaStream_t st);
 cudaError_t launch_gemm_tc5(const uint8_t* wt, int dtype, int n, int k, const __half* xh, int m, float* y, int ldy, const float* bias,

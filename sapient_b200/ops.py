@@ -168,7 +168,7 @@ def set_gemv_path(path: int) -> None:
 
 
 def set_large_m_gemm(on: bool) -> None:
-    """Op-level matmuls with m >= 64 and k % 256 == 0 use the tcgen05 / TMEM dequant GEMM (default on)."""
+    """Op-level matmuls with m >= 17 and k % 256 == 0 use the tcgen05 / TMEM dequant GEMM (default on)."""
     check(lib().sp_cuda_set_large_m_gemm(int(on)))
 
 

@@ -18,7 +18,7 @@ def _large_m(on: bool) -> None:
 
 
 # (m, k, n): m not a multiple of 16 / over 256 (two CTA columns), n not a multiple of 128 / 16, several K chunks
-CASES = [(64, 256, 128), (80, 512, 200), (100, 1024, 130), (300, 768, 72), (512, 512, 384)]
+CASES = [(17, 256, 48), (32, 512, 144), (40, 256, 128), (64, 256, 128), (80, 512, 200), (100, 1024, 130), (300, 768, 72), (512, 512, 384)]
 
 
 @pytest.mark.parametrize("dtype", [Q4_K, Q6_K, Q8_0])

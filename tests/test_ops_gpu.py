@@ -71,8 +71,9 @@ def test_matmul_nt_random_bits(oracle, gemv_path, dtype, m, k, n):
     err = rel_l2(got, want)
     assert err < REL_L2_BAR, err
     # cuda-core: f32 accumulation in a different order. tensor-core: exact integer products, activations held
-    # to 2^-23 (m <= 2, three digits) or 2^-15 (two digits) of each 256-column block's maximum.
-    assert err < (2e-5 if gemv_path == 1 or m <= 2 else 3e-4), err
+    # to 2^-23 (m <= 2, three digits) or 2^-15 (two digits) of each 256-column block's maximum; from 17 rows on the
+    # tcgen05 GEMM with weights and activations rounded once to fp16.
+    assert err < (2e-5 if gemv_path == 1 or m <= 2 else 3e-4 if m <= 16 else 5e-4), err
 
 
 @pytest.mark.parametrize("dtype", [Q4_K, Q6_K, Q8_0])
