@@ -312,8 +312,11 @@ struct Tc5Args {
     int ldy;
     const float* res;   // [m][ldres] or null, added to segment 0 (may alias its y)
     int ldres;
-    int ksplit;         // > 1: gridDim.z CTAs share a tile's K range and ADD their parts into y (y must already hold the
-                        // residual: res == y); the order of the f32 additions then varies from run to run
+    // Work items = (128-row weight tile, 256-row activation tile) pairs, m_tiles consecutive items per weight tile.
+    // CTAs 0 .. full_items-1 take one item each over the whole K range; the items after them (the last, partial wave
+    // of the grid) are each shared by tail_split CTAs that take a part of the K range and ADD into y, which must hold
+    // the residual (res == y) or zeros beforehand; the order of those f32 additions varies from run to run.
+    int m_tiles, full_items, tail_split;
     int stage_bytes;    // 256 * (widest activation tile of the launch, rounded to 16): two boxes of 64 columns
     int stages;         // depth of the activation ring that fits shared memory (3..8)
 };
@@ -325,18 +328,25 @@ __global__ void __launch_bounds__(TC5_THREADS, 1) gemm_tc5_kernel(const Tc5Args 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     uint8_t* smem = smem_raw + ((1024u - (tc5_smem_u32(smem_raw) & 1023u)) & 1023u);
     // which matrix of the launch this CTA works on, and its 128-row tile there
-    int bx = blockIdx.x, si = 0;
+    int item = blockIdx.x, part = 0, parts = 1;
+    if (item >= a.full_items) {
+        const int t = item - a.full_items;
+        item = a.full_items + t / a.tail_split;
+        part = t % a.tail_split;
+        parts = a.tail_split;
+    }
+    int bx = item / a.m_tiles, si = 0;
     while (si < a.nseg - 1 && bx >= (a.seg[si].n + TC5_BM - 1) / TC5_BM) { bx -= (a.seg[si].n + TC5_BM - 1) / TC5_BM; ++si; }
     const Tc5Seg& sg = a.seg[si];
     const int DT = sg.dtype;
     const int TILE_BYTES = DT == T_Q4_K ? Q4_K_TILE_BYTES : DT == T_Q6_K ? Q6_K_TILE_BYTES : 8 * 544;
-    const int n0 = bx * TC5_BM, m0 = blockIdx.y * TC5_NB_MAX;
+    const int n0 = bx * TC5_BM, m0 = (item % a.m_tiles) * TC5_NB_MAX;
     const int rows_here = min(TC5_NB_MAX, a.m - m0);
     const int nb = (rows_here + 15) & ~15;  // the MMA's N
     const int kts = a.k >> 8, n_tile_rows = (sg.n + 15) >> 4;
     // this CTA's share of the K range (all of it unless the launch splits K)
     const int all_chunks = a.k / TC5_BK;
-    const int c_begin = (int)((int64_t)blockIdx.z * all_chunks / a.ksplit), c_end = (int)((int64_t)(blockIdx.z + 1) * all_chunks / a.ksplit);
+    const int c_begin = (int)((int64_t)part * all_chunks / parts), c_end = (int)((int64_t)(part + 1) * all_chunks / parts);
     const int n_chunks = c_end - c_begin;
 
     if (warp == TC5_MMA_WARP) {
@@ -473,8 +483,8 @@ __global__ void __launch_bounds__(TC5_THREADS, 1) gemm_tc5_kernel(const Tc5Args 
         if (ok) {
             const int q4 = warp & 3;
             const int n = n0 + 32 * q4 + lane;
-            const float bias = (sg.bias && n < sg.n && blockIdx.z == 0) ? sg.bias[n] : 0.f;
-            const bool add_res = a.res && si == 0 && a.ksplit == 1;
+            const float bias = (sg.bias && n < sg.n && part == 0) ? sg.bias[n] : 0.f;
+            const bool add_res = a.res && si == 0 && parts == 1;
             float* yb = sg.y;
             for (int gi = pw >> 2; gi < nb / 16; gi += TC5_PRODUCER_WARPS / 4) {
                 uint32_t r[16];
@@ -493,7 +503,7 @@ __global__ void __launch_bounds__(TC5_THREADS, 1) gemm_tc5_kernel(const Tc5Args 
                         if (m < a.m) {
                             float v = __uint_as_float(r[j]) + bias;
                             if (add_res) v += a.res[(int64_t)m * a.ldres + n];
-                            if (a.ksplit > 1) atomicAdd(yb + (int64_t)m * a.ldy + n, v);  // y already holds the residual
+                            if (parts > 1) atomicAdd(yb + (int64_t)m * a.ldy + n, v);  // y already holds the residual or zeros
                             else yb[(int64_t)m * a.ldy + n] = v;
                         }
                     }
@@ -531,12 +541,24 @@ cudaError_t launch_x_to_f16(const float* x, int ldx, int m, int k, __half* out, 
     return count_launch_and_check();
 }
 
+// Zeros columns [c0, c0 + nc) of rows 0 .. rows-1 of y (row stride ld): the tiles whose K range is shared.
+__global__ void zero_cols_kernel(float* __restrict__ y, int ld, int rows, int c0, int nc) {
+    pdl_wait();
+    pdl_trigger();
+    const int64_t total = (int64_t)rows * nc;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / nc;
+        y[r * ld + c0 + (i - r * nc)] = 0.f;
+    }
+}
+
 typedef CUresult (*PFN_encodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                     const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                     CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-// Up to three matrices sharing the activations in one launch. res (added to segment 0) may alias its y; when it does
-// and the grid would leave most SMs idle, the K range is split over gridDim.z CTAs that add into y.
+// Up to three matrices sharing the activations in one launch. res (added to segment 0) may alias its y. The items of the
+// grid's last, partial wave are split along K over as many CTAs as fill the SMs (see Tc5Args), unless there is a
+// residual that is not in place.
 cudaError_t launch_gemm_tc5_multi(const Tc5Seg* segs, int nseg, int k, const __half* xh, int m, int ldy, const float* res, int ldres,
                                   cudaStream_t st) {
     if (m <= 0 || nseg <= 0) return cudaSuccess;
@@ -561,10 +583,17 @@ cudaError_t launch_gemm_tc5_multi(const Tc5Seg* segs, int nseg, int k, const __h
     const int stages = std::min(TC5_MAX_STAGES, TC5_SMEM_LIMIT / stage_bytes);
     const int smem_bytes = std::max(stages * stage_bytes + 1024, TC5_SMEM_MIN);  // + slack to align the stages to 1024 B
     const int m_tiles = (m + TC5_NB_MAX - 1) / TC5_NB_MAX;
-    int ksplit = 1;
-    if (nseg == 1 && res && res == segs[0].y) {  // in-place residual: partial sums can simply be added
-        const int chunks = k / TC5_BK;
-        ksplit = std::max(1, std::min({8, sm_count / std::max(1, tiles * m_tiles), chunks / 4}));
+    const int chunks = k / TC5_BK, items = tiles * m_tiles;
+    int full_items = items, tail_split = 1;
+    const bool in_place = nseg == 1 && res && res == segs[0].y;
+    if (!res || in_place) {
+        int tail = items % sm_count;
+        if (tail > 0) {
+            int first = (items - tail) / m_tiles * m_tiles;  // whole weight tiles only
+            tail = items - first;
+            const int ts = std::min({8, sm_count / tail, chunks / 4});
+            if (ts >= 2) { full_items = first; tail_split = ts; }
+        }
     }
     // TMA descriptor of the fp16 activations [m][k]: boxes of 64 columns x nb_max rows, 128-byte swizzle, zero fill
     static PFN_encodeTiled encode = nullptr;
@@ -584,7 +613,8 @@ cudaError_t launch_gemm_tc5_multi(const Tc5Seg* segs, int nseg, int k, const __h
                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
             return cudaErrorInvalidValue;
     }
-    a.nseg = nseg; a.k = k; a.xh = xh; a.m = m; a.ldy = ldy; a.res = res; a.ldres = ldres; a.ksplit = ksplit;
+    a.nseg = nseg; a.k = k; a.xh = xh; a.m = m; a.ldy = ldy; a.res = res; a.ldres = ldres;
+    a.m_tiles = m_tiles; a.full_items = full_items; a.tail_split = tail_split;
     a.stage_bytes = stage_bytes; a.stages = stages;
     constexpr int SMEM_CAP = TC5_SMEM_LIMIT + 1024;
     cudaError_t le;
@@ -593,7 +623,25 @@ cudaError_t launch_gemm_tc5_multi(const Tc5Seg* segs, int nseg, int k, const __h
         if (le != cudaSuccess) return le;
         attr_set = true;
     }
-    le = launch_pdl(gemm_tc5_kernel, dim3((unsigned)tiles, (unsigned)m_tiles, (unsigned)ksplit), dim3(TC5_THREADS), smem_bytes, st, a, tmap);
+    if (tail_split > 1 && !in_place) {
+        // the shared tiles' outputs start from zero
+        int t0 = 0;  // first weight tile of the segment, counted over the launch
+        for (int i = 0; i < nseg; ++i) {
+            const int nt = (segs[i].n + TC5_BM - 1) / TC5_BM;
+            const int first = std::max(full_items / m_tiles, t0) - t0;  // first shared tile inside this segment
+            if (first < nt) {
+                const int c0 = first * TC5_BM, nc = segs[i].n - c0;
+                const int64_t total = (int64_t)m * nc;
+                le = launch_pdl(zero_cols_kernel, dim3((unsigned)std::min<int64_t>((total + 255) / 256, 1184)), dim3(256), 0, st, segs[i].y, ldy, m, c0, nc);
+                if (le != cudaSuccess) return le;
+                le = count_launch_and_check();
+                if (le != cudaSuccess) return le;
+            }
+            t0 += nt;
+        }
+    }
+    const int grid = full_items + (items - full_items) * tail_split;
+    le = launch_pdl(gemm_tc5_kernel, dim3((unsigned)grid), dim3(TC5_THREADS), smem_bytes, st, a, tmap);
     if (le != cudaSuccess) return le;
     return count_launch_and_check();
 }
