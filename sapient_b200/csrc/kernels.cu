@@ -319,15 +319,87 @@ cudaError_t launch_rms_norm(const float* x, const float* w, int rows, int dim, f
     rms_norm_kernel<<<rows, 256, 0, st>>>(x, w, dim, eps, y, nullptr);
     return finish_launch();
 }
+// Row norm to fp16 for many rows: the row is read once with 16-byte loads and stays in registers (up to eight float4 per
+// thread, blockDim.x >= dim / 32), the result goes out as four halves per store. dim % 4 == 0.
+template <bool LAYER_NORM>
+__global__ void __launch_bounds__(1024) norm_rows_f16_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ b,
+                                                             int dim, float eps, __half* __restrict__ yh) {
+    __shared__ float sh[32];
+    pdl_wait();
+    pdl_trigger();
+    const float4* s = reinterpret_cast<const float4*>(x + (int64_t)blockIdx.x * dim);
+    const int n4 = dim >> 2;
+    float4 v[8];
+    float acc = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        v[i] = c < n4 ? s[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+        acc += LAYER_NORM ? (v[i].x + v[i].y) + (v[i].z + v[i].w) : fmaf(v[i].x, v[i].x, fmaf(v[i].y, v[i].y, fmaf(v[i].z, v[i].z, v[i].w * v[i].w)));
+    }
+    float mean = 0.f, inv;
+    if (LAYER_NORM) {
+        mean = block_sum(acc, sh) / (float)dim;
+        float va = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            if (threadIdx.x + i * blockDim.x < n4) {
+                const float d0 = v[i].x - mean, d1 = v[i].y - mean, d2 = v[i].z - mean, d3 = v[i].w - mean;
+                va += fmaf(d0, d0, fmaf(d1, d1, fmaf(d2, d2, d3 * d3)));
+            }
+        }
+        inv = 1.0f / sqrtf(block_sum(va, sh) / (float)dim + eps);
+    } else {
+        inv = 1.0f / sqrtf(block_sum(acc, sh) / (float)dim + eps);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        if (c < n4) {
+            const float4 ww = w ? reinterpret_cast<const float4*>(w)[c] : make_float4(1.f, 1.f, 1.f, 1.f);
+            float o0, o1, o2, o3;
+            if (LAYER_NORM) {
+                const float4 bb = b ? reinterpret_cast<const float4*>(b)[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+                o0 = __fmul_rn(v[i].x - mean, inv); o1 = __fmul_rn(v[i].y - mean, inv);
+                o2 = __fmul_rn(v[i].z - mean, inv); o3 = __fmul_rn(v[i].w - mean, inv);
+                if (w) { o0 = __fmul_rn(o0, ww.x); o1 = __fmul_rn(o1, ww.y); o2 = __fmul_rn(o2, ww.z); o3 = __fmul_rn(o3, ww.w); }
+                o0 = __fadd_rn(o0, bb.x); o1 = __fadd_rn(o1, bb.y); o2 = __fadd_rn(o2, bb.z); o3 = __fadd_rn(o3, bb.w);
+            } else {
+                o0 = __fmul_rn(__fmul_rn(v[i].x, inv), ww.x); o1 = __fmul_rn(__fmul_rn(v[i].y, inv), ww.y);
+                o2 = __fmul_rn(__fmul_rn(v[i].z, inv), ww.z); o3 = __fmul_rn(__fmul_rn(v[i].w, inv), ww.w);
+            }
+            const __half2 h01 = __floats2half2_rn(o0, o1), h23 = __floats2half2_rn(o2, o3);
+            reinterpret_cast<uint2*>(yh + (int64_t)blockIdx.x * dim)[c] =
+                make_uint2(*reinterpret_cast<const uint32_t*>(&h01), *reinterpret_cast<const uint32_t*>(&h23));
+        }
+    }
+}
+
+static inline int norm_rows_threads(int dim) {  // 0: the shape does not fit the register-resident kernel
+    if (dim % 4 != 0 || dim > 32768) return 0;
+    const int t = ((dim / 32 + 31) / 32) * 32;
+    return t < 32 ? 32 : t;
+}
+
 cudaError_t launch_rms_norm_f16(const float* x, const float* w, int rows, int dim, float eps, __half* yh, cudaStream_t st) {
     if (rows == 0) return cudaSuccess;
-    rms_norm_kernel<<<rows, 256, 0, st>>>(x, w, dim, eps, nullptr, yh);
+    if (const int t = norm_rows_threads(dim)) {
+        cudaError_t le = launch_pdl(norm_rows_f16_kernel<false>, dim3(rows), dim3(t), 0, st, x, w, (const float*)nullptr, dim, eps, yh);
+        if (le != cudaSuccess) return le;
+    } else {
+        rms_norm_kernel<<<rows, 256, 0, st>>>(x, w, dim, eps, nullptr, yh);
+    }
     return finish_launch();
 }
 cudaError_t launch_layer_norm_f16(const float* x, const float* w, const float* b, int rows, int dim, float eps, __half* yh,
                                   cudaStream_t st) {
     if (rows == 0) return cudaSuccess;
-    layer_norm_kernel<<<rows, 256, 0, st>>>(x, w, b, dim, eps, nullptr, yh);
+    if (const int t = norm_rows_threads(dim)) {
+        cudaError_t le = launch_pdl(norm_rows_f16_kernel<true>, dim3(rows), dim3(t), 0, st, x, w, b, dim, eps, yh);
+        if (le != cudaSuccess) return le;
+    } else {
+        layer_norm_kernel<<<rows, 256, 0, st>>>(x, w, b, dim, eps, nullptr, yh);
+    }
     return finish_launch();
 }
 cudaError_t launch_layer_norm(const float* x, const float* w, const float* b, int rows, int dim, float eps, float* y,
@@ -406,11 +478,71 @@ __global__ void rope_kv_append_kernel(float* __restrict__ qkv, int n_heads, int 
     }
 }
 
+// The same for many tokens: one warp per (token, head), eight heads per block.
+__global__ void __launch_bounds__(256) rope_kv_append_rows_kernel(float* __restrict__ qkv, int n_heads, int n_kv, int head_dim, int rotary_dim,
+                                                                  const float2* __restrict__ cos_sin, const int32_t* __restrict__ tok_slot,
+                                                                  const int32_t* __restrict__ tok_pos, KvGeom kv, int layer, int kv_round) {
+    __shared__ float sh_rows[8][256];
+    pdl_wait();
+    pdl_trigger();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x, j = blockIdx.y * 8 + warp;
+    if (j >= n_heads + 2 * n_kv) return;
+    float* sh_row = sh_rows[warp];
+    const int pos = tok_pos[t], slot = tok_slot[t];
+    const int half = rotary_dim >> 1;
+    const int ld = (n_heads + 2 * n_kv) * head_dim;
+    float* v = qkv + (int64_t)t * ld + (int64_t)j * head_dim;
+    __half* dst = nullptr;
+    bool rotate = true;
+    if (j >= n_heads) {
+        const int which = (j >= n_heads + n_kv) ? 1 : 0;
+        const int head = j - n_heads - which * n_kv;
+        const int page = kv.page_table[(int64_t)slot * kv.max_pages + pos / KV_PAGE];
+        dst = kv.pool + kv_offset(kv, layer, page, which, head) + (int64_t)(pos % KV_PAGE) * head_dim;
+        rotate = (which == 0);
+    }
+    for (int p = lane; p < head_dim / 2; p += 32) {
+        int i0, i1;
+        float o0, o1;
+        if (p < half) {
+            i0 = p; i1 = p + half;
+            if (rotate) rope_pair(v[i0], v[i1], cos_sin[(int64_t)pos * half + p], &o0, &o1);
+            else { o0 = v[i0]; o1 = v[i1]; }
+        } else {
+            i0 = rotary_dim + 2 * (p - half); i1 = i0 + 1;
+            o0 = v[i0]; o1 = v[i1];
+        }
+        if (dst && kv_round) { sh_row[i0] = o0; sh_row[i1] = o1; }
+        else if (dst) { dst[i0] = __float2half_rn(o0); dst[i1] = __float2half_rn(o1); }
+        else { v[i0] = o0; v[i1] = o1; }
+    }
+    if (dst && kv_round) {  // warp-uniform
+        __syncwarp();
+        for (int b = 0; b < head_dim / 32; ++b) {
+            const float x = sh_row[b * 32 + lane];
+            const float amax = warp_max(fabsf(x));
+            const float scale = amax / 127.0f;
+            const float inv = scale > 0.0f ? 1.0f / scale : 0.0f;
+            float r = roundf(x * inv);  // half away from zero, like f32::round
+            r = fminf(fmaxf(r, -127.0f), 127.0f);
+            const float d = __half2float(__float2half_rn(scale));
+            dst[b * 32 + lane] = __float2half_rn(__fmul_rn(r, d));
+        }
+    }
+}
+
 cudaError_t launch_rope_kv_append(float* qkv, int n_tok, int n_heads, int n_kv, int head_dim, int rotary_dim,
                                   const float2* cos_sin, const int32_t* tok_slot, const int32_t* tok_pos, KvGeom kv,
                                   int layer, int kv_round, cudaStream_t st) {
     if (n_tok == 0) return cudaSuccess;
     if (head_dim % 32 != 0 || head_dim > 256) kv_round = 0;
+    if (n_tok >= 32) {
+        cudaError_t le = launch_pdl(rope_kv_append_rows_kernel, dim3(n_tok, (n_heads + 2 * n_kv + 7) / 8), dim3(256), 0, st, qkv, n_heads, n_kv,
+                                    head_dim, rotary_dim, cos_sin, tok_slot, tok_pos, kv, layer, kv_round);
+        if (le != cudaSuccess) return le;
+        return finish_launch();
+    }
     cudaError_t le = launch_pdl(rope_kv_append_kernel, dim3(n_tok, n_heads + 2 * n_kv), dim3(64), 0, st, qkv, n_heads, n_kv, head_dim,
                                 rotary_dim, cos_sin, tok_slot, tok_pos, kv, layer, kv_round);
     if (le != cudaSuccess) return le;
@@ -454,6 +586,8 @@ __global__ void swiglu_kernel(const float* __restrict__ gu, int ld, int ffn, int
 // The MLP activation straight to fp16 [rows][ffn]: kind 0 = silu(gate) * up with gate | up side by side in a row of gu,
 // kind 1 = gelu. Two columns per thread.
 __global__ void act_f16_kernel(const float* __restrict__ gu, int ld, int ffn, int64_t total2, int kind, __half2* __restrict__ out) {
+    pdl_wait();
+    pdl_trigger();
     const int half_ffn = ffn >> 1;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total2; i += (int64_t)gridDim.x * blockDim.x) {
         const int64_t r = i / half_ffn, c = 2 * (i - r * half_ffn);
@@ -498,7 +632,8 @@ cudaError_t launch_act_f16(const float* gu, int ld, int ffn, int rows, int kind,
     const int64_t total2 = (int64_t)rows * ffn / 2;
     if (total2 == 0) return cudaSuccess;
     if ((ffn & 1) || (ld & 1)) return cudaErrorInvalidValue;
-    act_f16_kernel<<<ew_blocks(total2), 256, 0, st>>>(gu, ld, ffn, total2, kind, reinterpret_cast<__half2*>(out));
+    cudaError_t le = launch_pdl(act_f16_kernel, dim3(ew_blocks(total2)), dim3(256), 0, st, gu, ld, ffn, total2, kind, reinterpret_cast<__half2*>(out));
+    if (le != cudaSuccess) return le;
     return finish_launch();
 }
 cudaError_t launch_gelu(float* x, int64_t n, cudaStream_t st) {
