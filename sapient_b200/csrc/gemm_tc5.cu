@@ -303,6 +303,53 @@ __device__ __forceinline__ void tc5_convert(const Tc5Raw& r, int cq, Tc5Out& o) 
     }
 }
 
+// One producer warp's pass over the CTA's chunks, for one weight format. Chunk c takes the 64-column group
+// (2 (c_begin + c) + sub) % 4 of the superblock tile (2 (c_begin + c) + sub) / 4 of the warp's row of tiles.
+template <int DT>
+__device__ __forceinline__ bool tc5_produce(const uint8_t* tile_row, bool row_live, int c_begin, int n_chunks, int sub, int lane,
+                                            uint32_t a_base, uint64_t* full_a, uint64_t* empty_a) {
+    constexpr int TILE_BYTES = DT == T_Q4_K ? Q4_K_TILE_BYTES : DT == T_Q6_K ? Q6_K_TILE_BYTES : 8 * 544;
+    bool ok = true;
+    const int grp0 = 2 * c_begin + sub;
+    const uint8_t* tile = tile_row + (int64_t)(grp0 >> 2) * TILE_BYTES;  // tile and group of the next fetch: + 2 groups per chunk
+    int cq_f = grp0 & 3, cq_b = cq_f;                                    // cq_b: group of the next rebuild
+    auto fetch = [&](int c, Tc5Raw& raw) {  // global loads of chunk c
+        if (row_live && c < n_chunks) tc5_load<DT>(tile, lane, cq_f, raw);
+        cq_f ^= 2;
+        if (cq_f < 2) tile += TILE_BYTES;
+    };
+    int s = -1, u = 0;  // stage of the current chunk and the number of times the ring has wrapped
+    auto build = [&](const Tc5Raw& raw) {  // next chunk: rebuild the weights in registers, wait for its stage, store
+        if (++s == TC5_A_STAGES) { s = 0; ++u; }
+        Tc5Out o;
+        if (row_live) {
+            tc5_convert<DT>(raw, cq_b, o);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) o[i >> 2][i & 3] = 0u;  // rows past the matrix
+        }
+        cq_b ^= 2;
+        if (u > 0) ok = ok && tc5_wait(&empty_a[s], (uint32_t)((u - 1) & 1));  // the MMAs of chunk c - 4 have read this stage
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+#pragma unroll
+        for (int cg = 0; cg < 4; ++cg) tc5_tmem_st(a_base + (uint32_t)(64 * s + 8 * cg), o[cg]);
+        asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+        asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+        __syncwarp();
+        if (lane == 0) tc5_arrive(&full_a[s]);
+    };
+    // two register sets: the loads of chunk c + 1 are in flight while chunk c is rebuilt
+    Tc5Raw raw_a, raw_b;
+    fetch(0, raw_a);
+    for (int c = 0; c < n_chunks; c += 2) {
+        fetch(c + 1, raw_b);
+        build(raw_a);
+        fetch(c + 2, raw_a);
+        if (c + 1 < n_chunks) build(raw_b);
+    }
+    return ok;
+}
+
 struct Tc5Args {
     Tc5Seg seg[3];      // up to three matrices sharing the activations (q|k|v, gate|up); CTAs are dealt to them in order
     int nseg;
@@ -384,46 +431,9 @@ __global__ void __launch_bounds__(TC5_THREADS, 1) gemm_tc5_kernel(const Tc5Args 
         const uint8_t* tile_row = sg.wt + (int64_t)rt * kts * TILE_BYTES;
         // lanes 16 tile_w .. + 15, columns of stage 0 of the weight ring
         const uint32_t a_base = tmem + ((uint32_t)(16 * tile_w) << 16) + (uint32_t)(TC5_NB_MAX + 32 * sub);
-        auto fetch = [&](int c, Tc5Raw& raw) {  // global loads of stage-chunk c (group 2 c + sub of the row's superblocks)
-            const int grp = 2 * (c_begin + c) + sub;
-            if (row_live && c < n_chunks) {
-                const uint8_t* tile = tile_row + (int64_t)(grp >> 2) * TILE_BYTES;
-                if (DT == T_Q4_K) tc5_load<T_Q4_K>(tile, lane, grp & 3, raw);
-                else if (DT == T_Q6_K) tc5_load<T_Q6_K>(tile, lane, grp & 3, raw);
-                else tc5_load<T_Q8_0>(tile, lane, grp & 3, raw);
-            }
-        };
-        int s = -1, u = 0;  // stage of the current chunk and the number of times the ring has wrapped
-        auto build = [&](int c, const Tc5Raw& raw) {  // chunk c: rebuild the weights in registers, wait for its stage, store
-            if (++s == TC5_A_STAGES) { s = 0; ++u; }
-            Tc5Out o;
-            if (row_live) {
-                const int cq = (2 * (c_begin + c) + sub) & 3;
-                if (DT == T_Q4_K) tc5_convert<T_Q4_K>(raw, cq, o);
-                else if (DT == T_Q6_K) tc5_convert<T_Q6_K>(raw, cq, o);
-                else tc5_convert<T_Q8_0>(raw, cq, o);
-            } else {
-#pragma unroll
-                for (int i = 0; i < 16; ++i) o[i >> 2][i & 3] = 0u;  // rows past the matrix
-            }
-            if (u > 0) ok = ok && tc5_wait(&empty_a[s], (uint32_t)((u - 1) & 1));  // the MMAs of chunk c - 4 have read this stage
-            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-#pragma unroll
-            for (int cg = 0; cg < 4; ++cg) tc5_tmem_st(a_base + (uint32_t)(64 * s + 8 * cg), o[cg]);
-            asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
-            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-            __syncwarp();
-            if (lane == 0) tc5_arrive(&full_a[s]);
-        };
-        // two register sets: the loads of chunk c + 1 are in flight while chunk c is rebuilt
-        Tc5Raw raw_a, raw_b;
-        fetch(0, raw_a);
-        for (int c = 0; c < n_chunks; c += 2) {
-            fetch(c + 1, raw_b);
-            build(c, raw_a);
-            fetch(c + 2, raw_a);
-            if (c + 1 < n_chunks) build(c + 1, raw_b);
-        }
+        if (DT == T_Q4_K) ok = tc5_produce<T_Q4_K>(tile_row, row_live, c_begin, n_chunks, sub, lane, a_base, full_a, empty_a);
+        else if (DT == T_Q6_K) ok = tc5_produce<T_Q6_K>(tile_row, row_live, c_begin, n_chunks, sub, lane, a_base, full_a, empty_a);
+        else ok = tc5_produce<T_Q8_0>(tile_row, row_live, c_begin, n_chunks, sub, lane, a_base, full_a, empty_a);
     } else if (warp == TC5_MMA_WARP) {
         if (lane == 0) {
             // ── MMA issuer ──
