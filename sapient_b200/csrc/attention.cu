@@ -226,8 +226,8 @@ attention_prefill_kernel(const float* __restrict__ q, int ldq, float* __restrict
                          int n_heads, int slot, int pos0, KvGeom kv, int layer, float scale) {
     constexpr int HD = HD16 * 16, LD = HD + 8;  // padded row of the shared tiles (halves): conflict-free fragment loads
     extern __shared__ __align__(16) __half fa_smem[];
-    __half* Ks = fa_smem;
-    __half* Vs = fa_smem + FA_KEYS * LD;
+    // two (K, V) tile buffers: cp.async fills one while the tensor cores work on the other
+    constexpr int TILE = FA_KEYS * LD;
     pdl_wait();
     pdl_trigger();
     const int h = blockIdx.x, t0 = blockIdx.y * FA_ROWS;
@@ -255,21 +255,35 @@ attention_prefill_kernel(const float* __restrict__ q, int ldq, float* __restrict
     for (int i = 0; i < 2 * HD16; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
     const int last_pos = pos0 + min(t0 + FA_ROWS, n_tok) - 1;  // newest key any row of the block may see
-    for (int k0 = 0; k0 <= last_pos; k0 += FA_KEYS) {
-        __syncthreads();  // the previous tile has been consumed
+    auto fetch_tile = [&](int k0, int buf) {  // asynchronous copy of keys k0 .. k0 + 63 (zeros past the newest visible key)
+        __half* Kd = fa_smem + (2 * buf) * TILE;
+        __half* Vd = Kd + TILE;
         for (int idx = threadIdx.x; idx < FA_KEYS * (HD / 8); idx += FA_WARPS * 32) {
             const int kr = idx / (HD / 8), pc = idx - kr * (HD / 8);
             const int key = k0 + kr;
-            uint4 kq = make_uint4(0u, 0u, 0u, 0u), vq = kq;
-            if (key <= last_pos) {
-                const int page = pt[key / KV_PAGE];
-                kq = *reinterpret_cast<const uint4*>(kv.pool + kv_off(kv, layer, page, 0, kv_h) + (int64_t)(key % KV_PAGE) * HD + pc * 8);
-                vq = *reinterpret_cast<const uint4*>(kv.pool + kv_off(kv, layer, page, 1, kv_h) + (int64_t)(key % KV_PAGE) * HD + pc * 8);
-            }
-            *reinterpret_cast<uint4*>(Ks + kr * LD + pc * 8) = kq;
-            *reinterpret_cast<uint4*>(Vs + kr * LD + pc * 8) = vq;
+            const bool live = key <= last_pos;
+            const int page = live ? pt[key / KV_PAGE] : 0;
+            const int64_t in_page = (int64_t)((live ? key : 0) % KV_PAGE) * HD + pc * 8;
+            const __half* ksrc = kv.pool + kv_off(kv, layer, page, 0, kv_h) + in_page;
+            const __half* vsrc = kv.pool + kv_off(kv, layer, page, 1, kv_h) + in_page;
+            const uint32_t kd = (uint32_t)__cvta_generic_to_shared(Kd + kr * LD + pc * 8), vd = (uint32_t)__cvta_generic_to_shared(Vd + kr * LD + pc * 8);
+            const int bytes = live ? 16 : 0;  // 0: nothing is read, the 16 bytes are zero-filled
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(kd), "l"(ksrc), "r"(bytes) : "memory");
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(vd), "l"(vsrc), "r"(bytes) : "memory");
         }
-        __syncthreads();
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
+    };
+    fetch_tile(0, 0);
+    for (int k0 = 0, buf = 0; k0 <= last_pos; k0 += FA_KEYS, buf ^= 1) {
+        const __half* Ks = fa_smem + (2 * buf) * TILE;
+        const __half* Vs = Ks + TILE;
+        if (k0 + FA_KEYS <= last_pos) {
+            fetch_tile(k0 + FA_KEYS, buf ^ 1);  // that buffer's previous tile was consumed before the barrier that ended the last iteration
+            asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+        }
+        __syncthreads();  // everyone's copies of this tile have landed
         // S = (q * scale) K^T for 16 rows x 64 keys
         float s[8][4];
 #pragma unroll
@@ -332,6 +346,7 @@ attention_prefill_kernel(const float* __restrict__ q, int ldq, float* __restrict
                 mma_f16(o[nd + 1], pa[kk][0], pa[kk][1], pa[kk][2], pa[kk][3], b2, b3);
             }
         }
+        __syncthreads();  // this tile's buffer may be refilled from the next iteration on
     }
     const float i0 = (l0 == 0.f) ? 0.f : 1.0f / l0, i1 = (l1 == 0.f) ? 0.f : 1.0f / l1;
 #pragma unroll
@@ -356,10 +371,18 @@ cudaError_t launch_attention_prefill(const float* q, int ldq, float* out, int ld
     if (n_tok <= 0) return cudaSuccess;
     if (!attention_prefill_supported(kv.head_dim)) return cudaErrorInvalidValue;
     const int hd16 = kv.head_dim / 16;
-    const size_t smem = (size_t)2 * FA_KEYS * (kv.head_dim + 8) * sizeof(__half);
+    const size_t smem = (size_t)4 * FA_KEYS * (kv.head_dim + 8) * sizeof(__half);  // two (K, V) tile buffers
     const dim3 grid(n_heads, (n_tok + FA_ROWS - 1) / FA_ROWS), block(FA_WARPS * 32);
     cudaError_t le = cudaErrorInvalidValue;
-#define SP_FA(N) \
+#define SP_FA(N)                                                                                                        \
+    if (hd16 == N) {                                                                                                    \
+        static bool big_smem = false;                                                                                   \
+        if (smem > 48 * 1024 && !big_smem) {                                                                            \
+            le = cudaFuncSetAttribute(attention_prefill_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024); \
+            if (le != cudaSuccess) return le;                                                                           \
+            big_smem = true;                                                                                            \
+        }                                                                                                               \
+    }                                                                                                                   \
     if (hd16 == N) le = launch_pdl(attention_prefill_kernel<N>, grid, block, smem, st, q, ldq, out, out_h, ldo, n_tok, n_heads, slot, pos0, kv, layer, scale)
     SP_FA(1); SP_FA(2); SP_FA(3); SP_FA(4); SP_FA(5); SP_FA(6); SP_FA(7); SP_FA(8);
 #undef SP_FA
