@@ -78,7 +78,8 @@ def _roof(bytes_per_step: float, ms_per_step: float) -> dict:
 
 def decode_case(name: str, prompt_len: int, steps: int, batch: int, label: str, prefill_timed: bool = False) -> dict:
     cfg, W = _build(name, max_ctx=prompt_len + steps + 64, seed=1000)
-    eng, stream = _engine(cfg, W, max_batch=batch, max_tokens=256)
+    # rows per forward step: a whole prompt of up to 512 tokens in one step (fewer, fuller launches of the large-M GEMM)
+    eng, stream = _engine(cfg, W, max_batch=batch, max_tokens=max(256, min(prompt_len, 512)))
     rng = np.random.default_rng(0)
     first = np.empty(batch, np.uint32)
     prefill_ms = 0.0
