@@ -303,33 +303,26 @@ __device__ __forceinline__ void tc5_convert(const Tc5Raw& r, int cq, Tc5Out& o) 
     }
 }
 
-// One producer warp's pass over the CTA's chunks, for one weight format. Chunk c takes the 64-column group
-// (2 (c_begin + c) + sub) % 4 of the superblock tile (2 (c_begin + c) + sub) / 4 of the warp's row of tiles.
-template <int DT>
-__device__ __forceinline__ bool tc5_produce(const uint8_t* tile_row, bool row_live, int c_begin, int n_chunks, int sub, int lane,
-                                            uint32_t a_base, uint64_t* full_a, uint64_t* empty_a) {
+// One producer warp's pass over the CTA's chunks, for one weight format and one of the two 64-column groups of a
+// chunk. c_begin and n_chunks are even, so the warp alternates between groups SUB and SUB + 2 of a superblock tile and
+// moves to the next tile every second chunk: all offsets inside a tile are compile-time constants.
+template <int DT, int SUB>
+__device__ __forceinline__ bool tc5_produce(const uint8_t* tile_row, bool row_live, int c_begin, int n_chunks, int lane, uint32_t a_base,
+                                            uint64_t* full_a, uint64_t* empty_a) {
     constexpr int TILE_BYTES = DT == T_Q4_K ? Q4_K_TILE_BYTES : DT == T_Q6_K ? Q6_K_TILE_BYTES : 8 * 544;
     bool ok = true;
-    const int grp0 = 2 * c_begin + sub;
-    const uint8_t* tile = tile_row + (int64_t)(grp0 >> 2) * TILE_BYTES;  // tile and group of the next fetch: + 2 groups per chunk
-    int cq_f = grp0 & 3, cq_b = cq_f;                                    // cq_b: group of the next rebuild
-    auto fetch = [&](int c, Tc5Raw& raw) {  // global loads of chunk c
-        if (row_live && c < n_chunks) tc5_load<DT>(tile, lane, cq_f, raw);
-        cq_f ^= 2;
-        if (cq_f < 2) tile += TILE_BYTES;
-    };
+    const uint8_t* tile = tile_row + (int64_t)(c_begin >> 1) * TILE_BYTES;
     int s = -1, u = 0;  // stage of the current chunk and the number of times the ring has wrapped
-    auto build = [&](const Tc5Raw& raw) {  // next chunk: rebuild the weights in registers, wait for its stage, store
+    auto build = [&](const Tc5Raw& raw, int cq) {  // next chunk: rebuild the weights in registers, wait for its stage, store
         if (++s == TC5_A_STAGES) { s = 0; ++u; }
         Tc5Out o;
         if (row_live) {
-            tc5_convert<DT>(raw, cq_b, o);
+            tc5_convert<DT>(raw, cq, o);
         } else {
 #pragma unroll
             for (int i = 0; i < 16; ++i) o[i >> 2][i & 3] = 0u;  // rows past the matrix
         }
-        cq_b ^= 2;
-        if (u > 0) ok = ok && tc5_wait(&empty_a[s], (uint32_t)((u - 1) & 1));  // the MMAs of chunk c - 4 have read this stage
+        if (u > 0) ok = ok && tc5_wait(&empty_a[s], (uint32_t)((u - 1) & 1));  // the MMAs of the chunk 4 back have read this stage
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
 #pragma unroll
         for (int cg = 0; cg < 4; ++cg) tc5_tmem_st(a_base + (uint32_t)(64 * s + 8 * cg), o[cg]);
@@ -338,14 +331,15 @@ __device__ __forceinline__ bool tc5_produce(const uint8_t* tile_row, bool row_li
         __syncwarp();
         if (lane == 0) tc5_arrive(&full_a[s]);
     };
-    // two register sets: the loads of chunk c + 1 are in flight while chunk c is rebuilt
+    // two register sets: the loads of the next chunk are in flight while a chunk is rebuilt
     Tc5Raw raw_a, raw_b;
-    fetch(0, raw_a);
+    if (row_live) tc5_load<DT>(tile, lane, SUB, raw_a);
     for (int c = 0; c < n_chunks; c += 2) {
-        fetch(c + 1, raw_b);
-        build(raw_a);
-        fetch(c + 2, raw_a);
-        if (c + 1 < n_chunks) build(raw_b);
+        if (row_live) tc5_load<DT>(tile, lane, SUB + 2, raw_b);
+        build(raw_a, SUB);
+        tile += TILE_BYTES;
+        if (row_live && c + 2 < n_chunks) tc5_load<DT>(tile, lane, SUB, raw_a);
+        build(raw_b, SUB + 2);
     }
     return ok;
 }
@@ -393,7 +387,8 @@ __global__ void __launch_bounds__(TC5_THREADS, 1) gemm_tc5_kernel(const Tc5Args 
     const int kts = a.k >> 8, n_tile_rows = (sg.n + 15) >> 4;
     // this CTA's share of the K range (all of it unless the launch splits K)
     const int all_chunks = a.k / TC5_BK;
-    const int c_begin = (int)((int64_t)part * all_chunks / parts), c_end = (int)((int64_t)(part + 1) * all_chunks / parts);
+    // even boundaries (all_chunks is even): a producer warp then always starts on the first half of a superblock tile
+    const int c_begin = (int)((int64_t)part * all_chunks / parts) & ~1, c_end = (int)((int64_t)(part + 1) * all_chunks / parts) & ~1;
     const int n_chunks = c_end - c_begin;
 
     if (warp == TC5_MMA_WARP) {
@@ -431,9 +426,13 @@ __global__ void __launch_bounds__(TC5_THREADS, 1) gemm_tc5_kernel(const Tc5Args 
         const uint8_t* tile_row = sg.wt + (int64_t)rt * kts * TILE_BYTES;
         // lanes 16 tile_w .. + 15, columns of stage 0 of the weight ring
         const uint32_t a_base = tmem + ((uint32_t)(16 * tile_w) << 16) + (uint32_t)(TC5_NB_MAX + 32 * sub);
-        if (DT == T_Q4_K) ok = tc5_produce<T_Q4_K>(tile_row, row_live, c_begin, n_chunks, sub, lane, a_base, full_a, empty_a);
-        else if (DT == T_Q6_K) ok = tc5_produce<T_Q6_K>(tile_row, row_live, c_begin, n_chunks, sub, lane, a_base, full_a, empty_a);
-        else ok = tc5_produce<T_Q8_0>(tile_row, row_live, c_begin, n_chunks, sub, lane, a_base, full_a, empty_a);
+#define SP_PRODUCE(T)                                                                                            \
+    ok = sub ? tc5_produce<T, 1>(tile_row, row_live, c_begin, n_chunks, lane, a_base, full_a, empty_a)          \
+             : tc5_produce<T, 0>(tile_row, row_live, c_begin, n_chunks, lane, a_base, full_a, empty_a)
+        if (DT == T_Q4_K) SP_PRODUCE(T_Q4_K);
+        else if (DT == T_Q6_K) SP_PRODUCE(T_Q6_K);
+        else SP_PRODUCE(T_Q8_0);
+#undef SP_PRODUCE
     } else if (warp == TC5_MMA_WARP) {
         if (lane == 0) {
             // ── MMA issuer ──
