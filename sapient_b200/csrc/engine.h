@@ -91,6 +91,7 @@ class Engine {
     bool trace_on = false;
     bool use_graphs = true;
     bool use_tc5 = true;
+    bool graph_step_ = false;  // a step is being captured: its kernels may take positions only from device memory
     // 1 (default): new K / V rows get the reference's Q8_0 cache rounding before they are stored as fp16 (head_dim % 32
     // == 0, where the reference keeps a Q8_0 cache); 0: plain fp16 rounding. Change only while the caches are empty.
     int kv_round = 1;   // large-M GEMM on tcgen05 (false: always the 16-row GEMV passes)
@@ -147,7 +148,7 @@ class Engine {
     const float* lm_bias_ = nullptr;
 
     ActWorkspace ws_;          // activation digits of the current GEMV input
-    // split-K attention: decode-shaped calls (T <= ATT_SPLIT_TOKENS) split the keys over ATT_SPLITS blocks
+    // split-K attention: steps of up to 16 rows split the keys over up to ATT_SPLITS blocks (scratch sized for ATT_SPLIT_TOKENS rows)
     static constexpr int ATT_SPLITS = 16, ATT_SPLIT_TOKENS = 32;
     float* att_scratch_ = nullptr;
     int repack_weights();

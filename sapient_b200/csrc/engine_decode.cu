@@ -96,7 +96,9 @@ int Engine::launch_decode_step(int T) {
         cudaGraph_t graph = nullptr;
         const uint64_t before = launch_count();
         SP_CUDA_TRY(cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal));
+        graph_step_ = true;
         const int st = enqueue_decode_step(T);
+        graph_step_ = false;
         const cudaError_t ce = cudaStreamEndCapture(stream, &graph);
         const int64_t captured = (int64_t)(launch_count() - before);
         adjust_launch_count(-captured);  // captured, not executed

@@ -6,6 +6,7 @@
 // SwiGLU / GELU, the split-K attention merge) emits the int8 digits the tensor-core GEMV consumes,
 // so a layer is 10 launches: norm+digits, qkv, rope+kv, attention split, merge+digits, o,
 // norm+digits, gate|up, swiglu+digits, down.
+#include <cstdlib>
 #include <algorithm>
 
 #include "engine.h"
@@ -152,7 +153,11 @@ int Engine::attention_and_oproj(const LayerW& w, int l, int T) {
     const int H = d.n_heads, Hkv = d.n_kv_heads, hd = d.head_dim, hid = d.hidden;
     const int qkv_ld = (H + 2 * Hkv) * hd;
     const float scale = 1.0f / sqrtf((float)hd);
-    const int splits = T <= ATT_SPLIT_TOKENS ? ATT_SPLITS : 1;
+    // Keys are split over several blocks only while (token, head) pairs alone leave SMs idle: 16 ways for one or two
+    // rows, fewer as the rows grow, not at all from 17 rows on (measured on the 8B shape at context 300: 16 rows 0.89 ms
+    // of attention per step with 4 splits against 1.37 with 16; 32 rows 0.54 ms unsplit against 2.34).
+    int splits = 1;
+    if (T <= 16) splits = H * T <= 64 ? ATT_SPLITS : H * T <= 128 ? 8 : 4;
     ImmaArgs ia;
     if (splits > 1 && !trace_on && all_tiled(w.o) && plan_digits(T, H * hd, ia)) {
         SP_LAUNCH(F_ATTN, launch_attention_split(qkv_, qkv_ld, T, H, d_tok_slot_, d_tok_pos_, kv_, l, scale, splits, att_scratch_, stream));
@@ -160,7 +165,8 @@ int Engine::attention_and_oproj(const LayerW& w, int l, int T) {
         return gemv(attn_, H * hd, T, H * hd, w.o, w.ob, x_, hid, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, x_, &ia, true);
     }
     // a prefill chunk (one sequence, consecutive positions): the tiled tensor-core kernel
-    bool one_seq = splits == 1 && use_tc5 && attention_prefill_supported(hd);
+    // (takes the sequence and its first position as launch arguments: not inside a captured step, which is replayed)
+    bool one_seq = splits == 1 && !graph_step_ && use_tc5 && attention_prefill_supported(hd);
     for (int i = 1; one_seq && i < T; ++i) one_seq = p_slot_[i] == p_slot_[0] && p_pos_[i] == p_pos_[0] + i;
     if (one_seq && big_m(T, H * hd, w.o)) {
         SP_LAUNCH(F_ATTN, launch_attention_prefill(qkv_, qkv_ld, nullptr, H * hd, T, H, p_slot_[0], p_pos_[0], kv_, l, scale, stream, ws_.xh));

@@ -1,6 +1,7 @@
-"""Prefill attention on tensor cores (attention_prefill_kernel): engines whose chunk size puts the prompt through the
-tiled kernel (more than 32 tokens of one sequence per chunk) against engines that feed the same prompt in chunks of
-32 tokens (the per-token kernel), and against the oracle."""
+"""Prefill attention on tensor cores (attention_prefill_kernel): engines that put a whole prompt through the tiled
+kernel (one sequence, more than 16 tokens per step, launched directly) against engines that feed the same prompt in
+chunks of 32 tokens through replayed step graphs (the per-token kernel, which reads positions from device memory),
+and against the oracle."""
 import numpy as np
 import pytest
 
@@ -17,6 +18,7 @@ def test_tiled_prefill_attention_matches_per_token_kernel_and_oracle(oracle, nam
     ids = np.random.default_rng(n_prompt).integers(0, cfg["vocab"], n_prompt).astype(np.uint32)
     big = ForwardEngine.from_weights(cfg, W, max_tokens=256)     # whole prompt in one chunk: tiled kernel
     small = ForwardEngine.from_weights(cfg, W, max_tokens=32)    # chunks of 32: per-token kernel
+    big.set_graphs(False)  # direct launches: the tiled kernel takes the first position as an argument
     for e in (big, small):
         e.set_kv_rounding(False)  # continuous cache rounding: this test is about the kernels
     a = big.forward_all_logits(ids)
@@ -32,3 +34,18 @@ def test_tiled_prefill_attention_matches_per_token_kernel_and_oracle(oracle, nam
     assert np.abs(big.forward_logits([5], True) - small.forward_logits([5], True)).max() < 2e-3
     big.close()
     small.close()
+
+
+def test_replayed_step_graphs_do_not_freeze_positions():
+    """The same number of rows at two different cache positions: the second call replays the step graph captured by
+    the first, so nothing in it may depend on the positions the first call had."""
+    cfg, W = tiny_model("tiny_llama", max_ctx=256)
+    rng = np.random.default_rng(9)
+    first, second = (rng.integers(0, cfg["vocab"], 40).astype(np.uint32) for _ in range(2))
+    graphs = ForwardEngine.from_weights(cfg, W, max_tokens=64)
+    direct = ForwardEngine.from_weights(cfg, W, max_tokens=64)
+    direct.set_graphs(False)
+    for e in (graphs, direct):
+        e.set_kv_rounding(False)
+    assert np.abs(graphs.forward_all_logits(first) - direct.forward_all_logits(first)).max() < 2e-3
+    assert np.abs(graphs.forward_all_logits_cached(second) - direct.forward_all_logits_cached(second)).max() < 2e-3
