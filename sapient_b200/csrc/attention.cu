@@ -376,7 +376,8 @@ cudaError_t launch_attention_prefill(const float* q, int ldq, float* out, int ld
     cudaError_t le = cudaErrorInvalidValue;
 #define SP_FA(N)                                                                                                        \
     if (hd16 == N) {                                                                                                    \
-        static bool big_smem = false;                                                                                   \
+        static bool big_smem_dev[SP_MAX_DEVICES] = {};                                                                  \
+        bool& big_smem = big_smem_dev[current_device_index()];                                                          \
         if (smem > 48 * 1024 && !big_smem) {                                                                            \
             le = cudaFuncSetAttribute(attention_prefill_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024); \
             if (le != cudaSuccess) return le;                                                                           \

@@ -579,7 +579,7 @@ cudaError_t launch_gemm_tc5_multi(const Tc5Seg* segs, int nseg, int k, const __h
         a.seg[i] = segs[i];
         tiles += (segs[i].n + TC5_BM - 1) / TC5_BM;
     }
-    static bool attr_set = false;
+    static bool attr_set[SP_MAX_DEVICES] = {};
     static int sm_count = 0;
     if (sm_count == 0) {
         int dev = 0;
@@ -627,10 +627,10 @@ cudaError_t launch_gemm_tc5_multi(const Tc5Seg* segs, int nseg, int k, const __h
     a.stage_bytes = stage_bytes; a.stages = stages;
     constexpr int SMEM_CAP = TC5_SMEM_LIMIT + 1024;
     cudaError_t le;
-    if (!attr_set) {
+    if (bool& set = attr_set[current_device_index()]; !set) {
         le = cudaFuncSetAttribute(gemm_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_CAP);
         if (le != cudaSuccess) return le;
-        attr_set = true;
+        set = true;
     }
     if (tail_split > 1 && !in_place) {
         // the shared tiles' outputs start from zero

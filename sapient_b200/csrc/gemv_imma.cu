@@ -1072,7 +1072,7 @@ __global__ void __launch_bounds__(STREAM_WARPS * 32, 1) gemv_imma_stream_kernel(
 }
 
 static int g_sm_count = 0;
-static bool g_stream_attr[3] = {false, false, false};
+static bool g_stream_attr[SP_MAX_DEVICES][3] = {};
 
 // Shared-memory layout of the streaming kernel, or total == 0 when the launch does not qualify.
 static StreamPlan plan_stream(const ImmaArgs& a) {
@@ -1124,11 +1124,11 @@ cudaError_t launch_gemv_imma(const ImmaArgs& a, cudaStream_t st) {
             if (g_sm_count <= 0) g_sm_count = 148;
         }
         const int grid = tiles < g_sm_count ? tiles : g_sm_count;
-        if (!g_stream_attr[nt]) {
+        if (bool& attr = g_stream_attr[current_device_index()][nt]; !attr) {
             cudaError_t e = nt == 1 ? cudaFuncSetAttribute(gemv_imma_stream_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, STREAM_SMEM_LIMIT)
                                     : cudaFuncSetAttribute(gemv_imma_stream_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, STREAM_SMEM_LIMIT);
             if (e != cudaSuccess) return e;
-            g_stream_attr[nt] = true;
+            attr = true;
         }
         if (nt == 1) gemv_imma_stream_kernel<1><<<grid, STREAM_WARPS * 32, p.total, st>>>(a, p);
         else gemv_imma_stream_kernel<2><<<grid, STREAM_WARPS * 32, p.total, st>>>(a, p);

@@ -14,6 +14,15 @@
 
 namespace sp {
 
+// Function attributes (the opt-in to large dynamic shared memory) belong to a device: one flag per device of the process.
+constexpr int SP_MAX_DEVICES = 64;
+inline int current_device_index() {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    return dev >= 0 && dev < SP_MAX_DEVICES ? dev : 0;
+}
+
+
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;\n" ::); }
 

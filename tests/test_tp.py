@@ -228,3 +228,24 @@ def test_a_peer_that_never_arrives_ends_the_call_with_a_comm_error():
     one = ForwardEngine.from_weights(cfg, W)  # the context is fine
     assert np.all(np.isfinite(one.forward_logits([1, 2, 3], True)))
     one.close()
+
+
+@pytest.mark.gpu
+def test_one_process_can_run_many_row_steps_on_two_devices():
+    """Kernel attributes (large dynamic shared memory) are per device: a second device in the same process must get
+    them too. 40-row steps go through the tcgen05 GEMM and the tiled prefill attention."""
+    import torch
+
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    from sapient_b200.engine import ForwardEngine
+
+    cfg, W = tiny_model("tiny_llama")
+    ids = np.random.default_rng(2).integers(0, cfg["vocab"], 40).astype(np.uint32)
+    outs = []
+    for dev in (0, 1):
+        eng = ForwardEngine.from_weights(cfg, W, device=dev, max_tokens=64)
+        eng.set_graphs(False)
+        outs.append(eng.forward_all_logits(ids))
+        eng.close()
+    assert np.abs(outs[0] - outs[1]).max() < 2e-3
