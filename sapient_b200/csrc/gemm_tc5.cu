@@ -173,10 +173,19 @@ __device__ __forceinline__ uint32_t tc5_ldg2(const uint8_t* p) {
     return v;
 }
 
+// Q8_0 rows whose width is a multiple of 128 but not of 256 are tiled four 32-blocks (128 columns) at a time: one tile
+// per chunk, its 64-column groups 0 and 1 are what a wider tile calls groups cq and cq + 2.
+constexpr int T_Q8_0_HALF = 1000 + T_Q8_0;
+
 template <int DT>
 __device__ __forceinline__ void tc5_load(const uint8_t* tile, int lane, int cq, Tc5Raw& r) {
     const int g = lane >> 2;
-    if (DT == T_Q4_K) {
+    if (DT == T_Q8_0_HALF) {
+        r.q[0] = tc5_ldg16(tile + (2 * cq) * 512 + lane * 16);
+        r.q[1] = tc5_ldg16(tile + (2 * cq + 1) * 512 + lane * 16);
+        r.hdr[0].x = tc5_ldg4(tile + 2048 + (g * 4 + 2 * cq) * 2);        // d of blocks 2cq, 2cq+1
+        r.hdr[1].x = tc5_ldg4(tile + 2048 + ((g + 8) * 4 + 2 * cq) * 2);
+    } else if (DT == T_Q4_K) {
         r.q[0] = tc5_ldg16(tile + cq * 512 + lane * 16);
         r.hdr[0] = tc5_ldg16(tile + 2048 + g * 16);
         r.hdr[1] = tc5_ldg16(tile + 2048 + (g + 8) * 16);
@@ -260,7 +269,7 @@ __device__ __forceinline__ void tc5_convert(const Tc5Raw& r, int cq, Tc5Out& o) 
                 }
             }
         }
-    } else if (DT == T_Q8_0) {
+    } else if (DT == T_Q8_0 || DT == T_Q8_0_HALF) {
 #pragma unroll
         for (int hi8 = 0; hi8 < 2; ++hi8) {
 #pragma unroll
@@ -309,9 +318,10 @@ __device__ __forceinline__ void tc5_convert(const Tc5Raw& r, int cq, Tc5Out& o) 
 template <int DT, int SUB>
 __device__ __forceinline__ bool tc5_produce(const uint8_t* tile_row, bool row_live, int c_begin, int n_chunks, int lane, uint32_t a_base,
                                             uint64_t* full_a, uint64_t* empty_a) {
-    constexpr int TILE_BYTES = DT == T_Q4_K ? Q4_K_TILE_BYTES : DT == T_Q6_K ? Q6_K_TILE_BYTES : 8 * 544;
+    constexpr bool HALF = DT == T_Q8_0_HALF;  // one tile per chunk: group SUB of every tile, any c_begin and n_chunks
+    constexpr int TILE_BYTES = DT == T_Q4_K ? Q4_K_TILE_BYTES : DT == T_Q6_K ? Q6_K_TILE_BYTES : HALF ? 4 * 544 : 8 * 544;
     bool ok = true;
-    const uint8_t* tile = tile_row + (int64_t)(c_begin >> 1) * TILE_BYTES;
+    const uint8_t* tile = tile_row + (int64_t)(HALF ? c_begin : c_begin >> 1) * TILE_BYTES;
     int s = -1, u = 0;  // stage of the current chunk and the number of times the ring has wrapped
     auto build = [&](const Tc5Raw& raw, int cq) {  // next chunk: rebuild the weights in registers, wait for its stage, store
         if (++s == TC5_A_STAGES) { s = 0; ++u; }
@@ -335,11 +345,19 @@ __device__ __forceinline__ bool tc5_produce(const uint8_t* tile_row, bool row_li
     Tc5Raw raw_a, raw_b;
     if (row_live) tc5_load<DT>(tile, lane, SUB, raw_a);
     for (int c = 0; c < n_chunks; c += 2) {
-        if (row_live) tc5_load<DT>(tile, lane, SUB + 2, raw_b);
-        build(raw_a, SUB);
-        tile += TILE_BYTES;
-        if (row_live && c + 2 < n_chunks) tc5_load<DT>(tile, lane, SUB, raw_a);
-        build(raw_b, SUB + 2);
+        if (HALF) {
+            if (row_live && c + 1 < n_chunks) tc5_load<DT>(tile + TILE_BYTES, lane, SUB, raw_b);
+            build(raw_a, SUB);
+            tile += 2 * TILE_BYTES;
+            if (row_live && c + 2 < n_chunks) tc5_load<DT>(tile, lane, SUB, raw_a);
+            if (c + 1 < n_chunks) build(raw_b, SUB);
+        } else {
+            if (row_live) tc5_load<DT>(tile, lane, SUB + 2, raw_b);
+            build(raw_a, SUB);
+            tile += TILE_BYTES;
+            if (row_live && c + 2 < n_chunks) tc5_load<DT>(tile, lane, SUB, raw_a);
+            build(raw_b, SUB + 2);
+        }
     }
     return ok;
 }
@@ -347,7 +365,7 @@ __device__ __forceinline__ bool tc5_produce(const uint8_t* tile_row, bool row_li
 struct Tc5Args {
     Tc5Seg seg[3];      // up to three matrices sharing the activations (q|k|v, gate|up); CTAs are dealt to them in order
     int nseg;
-    int k;              // columns (k % 256 == 0)
+    int k;              // columns (k % 256 == 0; Q8_0 alone: k % 128 == 0)
     const __half* xh;   // activations as fp16 [m][k]
     int m;
     int ldy;
@@ -379,16 +397,18 @@ __global__ void __launch_bounds__(TC5_THREADS, 1) gemm_tc5_kernel(const Tc5Args 
     int bx = item / a.m_tiles, si = 0;
     while (si < a.nseg - 1 && bx >= (a.seg[si].n + TC5_BM - 1) / TC5_BM) { bx -= (a.seg[si].n + TC5_BM - 1) / TC5_BM; ++si; }
     const Tc5Seg& sg = a.seg[si];
-    const int DT = sg.dtype;
-    const int TILE_BYTES = DT == T_Q4_K ? Q4_K_TILE_BYTES : DT == T_Q6_K ? Q6_K_TILE_BYTES : 8 * 544;
+    const int DT = (sg.dtype == T_Q8_0 && (a.k & 255)) ? T_Q8_0_HALF : sg.dtype;
+    const int TILE_BYTES = DT == T_Q4_K ? Q4_K_TILE_BYTES : DT == T_Q6_K ? Q6_K_TILE_BYTES : 8 * 544;  // per 256 columns
     const int n0 = bx * TC5_BM, m0 = (item % a.m_tiles) * TC5_NB_MAX;
     const int rows_here = min(TC5_NB_MAX, a.m - m0);
     const int nb = (rows_here + 15) & ~15;  // the MMA's N
-    const int kts = a.k >> 8, n_tile_rows = (sg.n + 15) >> 4;
+    const int n_tile_rows = (sg.n + 15) >> 4;
+    const int64_t row_tile_bytes = (int64_t)(a.k >> 7) * (TILE_BYTES >> 1);  // one 16-row tile row: k / 256 tiles (Q8_0: k / 128 half tiles)
     // this CTA's share of the K range (all of it unless the launch splits K)
     const int all_chunks = a.k / TC5_BK;
     // even boundaries (all_chunks is even): a producer warp then always starts on the first half of a superblock tile
-    const int c_begin = (int)((int64_t)part * all_chunks / parts) & ~1, c_end = (int)((int64_t)(part + 1) * all_chunks / parts) & ~1;
+    const int even = (a.k & 255) ? ~0 : ~1;  // (widths that are odd multiples of 128 exist only with one tile per chunk)
+    const int c_begin = (int)((int64_t)part * all_chunks / parts) & even, c_end = (int)((int64_t)(part + 1) * all_chunks / parts) & even;
     const int n_chunks = c_end - c_begin;
 
     if (warp == TC5_MMA_WARP) {
@@ -423,7 +443,7 @@ __global__ void __launch_bounds__(TC5_THREADS, 1) gemm_tc5_kernel(const Tc5Args 
         const int tile_w = 2 * (warp & 3) + ((pw >> 2) & 1), sub = pw >> 3;
         const int rt = (n0 >> 4) + tile_w;
         const bool row_live = rt < n_tile_rows;
-        const uint8_t* tile_row = sg.wt + (int64_t)rt * kts * TILE_BYTES;
+        const uint8_t* tile_row = sg.wt + (int64_t)rt * row_tile_bytes;
         // lanes 16 tile_w .. + 15, columns of stage 0 of the weight ring
         const uint32_t a_base = tmem + ((uint32_t)(16 * tile_w) << 16) + (uint32_t)(TC5_NB_MAX + 32 * sub);
 #define SP_PRODUCE(T)                                                                                            \
@@ -431,7 +451,8 @@ __global__ void __launch_bounds__(TC5_THREADS, 1) gemm_tc5_kernel(const Tc5Args 
              : tc5_produce<T, 0>(tile_row, row_live, c_begin, n_chunks, lane, a_base, full_a, empty_a)
         if (DT == T_Q4_K) SP_PRODUCE(T_Q4_K);
         else if (DT == T_Q6_K) SP_PRODUCE(T_Q6_K);
-        else SP_PRODUCE(T_Q8_0);
+        else if (DT == T_Q8_0) SP_PRODUCE(T_Q8_0);
+        else SP_PRODUCE(T_Q8_0_HALF);
 #undef SP_PRODUCE
     } else if (warp == TC5_MMA_WARP) {
         if (lane == 0) {
@@ -540,7 +561,10 @@ __global__ void x_to_f16_kernel(const float* __restrict__ x, int ldx, int k, __h
         make_uint4(pack_h2(p0.x, p0.y), pack_h2(p0.z, p0.w), pack_h2(p1.x, p1.y), pack_h2(p1.z, p1.w));
 }
 
-bool tc5_supported(int dtype, int64_t k) { return k % 256 == 0 && (dtype == T_Q4_K || dtype == T_Q6_K || dtype == T_Q8_0); }
+bool tc5_supported(int dtype, int64_t k) {
+    if (dtype == T_Q8_0) return k % 128 == 0;  // the tiling switches to four blocks per tile when k is not a multiple of 256
+    return k % 256 == 0 && (dtype == T_Q4_K || dtype == T_Q6_K);
+}
 
 cudaError_t launch_x_to_f16(const float* x, int ldx, int m, int k, __half* out, cudaStream_t st) {
     if (m <= 0) return cudaSuccess;
@@ -571,7 +595,7 @@ typedef CUresult (*PFN_encodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_
 cudaError_t launch_gemm_tc5_multi(const Tc5Seg* segs, int nseg, int k, const __half* xh, int m, int ldy, const float* res, int ldres,
                                   cudaStream_t st) {
     if (m <= 0 || nseg <= 0) return cudaSuccess;
-    if (nseg > 3 || k % 256 != 0) return cudaErrorInvalidValue;
+    if (nseg > 3 || k % 128 != 0) return cudaErrorInvalidValue;
     Tc5Args a{};
     int tiles = 0;
     for (int i = 0; i < nseg; ++i) {

@@ -46,6 +46,19 @@ def test_large_m_gemm_matches_oracle_and_gemv(oracle, dtype, m, k, n):
     assert np.abs(got - want).max() < 5e-3 * scale
 
 
+@pytest.mark.parametrize("m,k,n", [(64, 128, 64), (40, 384, 130), (300, 896, 200), (33, 1152, 272)])
+def test_large_m_gemm_q8_0_widths_that_are_odd_multiples_of_128(oracle, m, k, n):
+    """Q8_0 rows tiled four blocks at a time (the Qwen2.5-0.5B width 896 is one): one tile per 128-column chunk."""
+    rng = np.random.default_rng(m + k + n)
+    raw = synth.random_bit_blocks(Q8_0, n * k // 32, seed=m + n)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    want = oracle.matmul_nt(x, raw, Q8_0, n)
+    got = ops.matmul_nt(x, raw, Q8_0, n)
+    assert got.shape == (m, n) and np.all(np.isfinite(got))
+    assert rel_l2(got, want) < 5e-4
+    assert np.abs(got - want).max() < 5e-3 * np.abs(want).max()
+
+
 def test_large_m_gemm_quantised_gaussian_weights(oracle):
     """Weights as the synthetic models have them (N(0, 0.02) quantised), activations with a few large entries."""
     import torch
