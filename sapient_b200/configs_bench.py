@@ -5,6 +5,8 @@ Llama-3-8B shape). One JSON line per case; synthetic seeded weights and token id
     python -m sapient_b200.configs_bench c2        Phi-2 shape, Q8_0: 512-token prefill, then 256 decode steps
     python -m sapient_b200.configs_bench c3b32     Llama-3-8B shape, 32 sequences decoded together (prompt 256 by default)
     python -m sapient_b200.configs_bench c4        speculative decoding, Qwen2.5-1.5B-shaped target + 0.5B-shaped draft, k = 4
+    python -m sapient_b200.configs_bench prefill --model llama8b --prompt 512
+                                                   one prompt through an engine whose step holds it whole: time and kernel families
 
 Rooflines: bytes one step must stream (every weight matrix once + the KV entries read) over the measured HBM copy
 bandwidth (MEASURED_PEAKS.json next to the package, else 6650 GB/s) and over 8 TB/s.
@@ -107,6 +109,21 @@ def decode_case(name: str, prompt_len: int, steps: int, batch: int, label: str, 
     return line
 
 
+def prefill_case(name: str, prompt_len: int, reps: int = 3) -> dict:
+    cfg, W = _build(name, max_ctx=prompt_len + 64, seed=3000)
+    eng, stream = _engine(cfg, W, max_tokens=min(prompt_len, 1024))
+    ids = np.random.default_rng(0).integers(0, cfg["vocab"], prompt_len).astype(np.uint32)
+    eng.forward_logits(ids, False)  # one-time allocations and attribute settings
+    ms = min(_timed(stream, lambda: eng.forward_logits(ids, False)) for _ in range(reps))
+    eng.set_profile(True)
+    eng.forward_logits(ids, False)
+    fam = {k: {"ms": round(v[0], 3), "launches": v[1]} for k, v in eng.profile_read().items()}
+    eng.set_profile(False)
+    eng.close()
+    return {"case": "prefill", "model": name, "prompt_len": prompt_len, "ms": ms, "tokens_per_s": prompt_len / (ms / 1e3),
+            "families": fam, "data": "synthetic"}
+
+
 def spec_case(k: int, prompt_len: int, new_tokens: int) -> dict:
     tcfg, tW = _build("qwen15b", max_ctx=prompt_len + new_tokens + 64, seed=4000)
     dcfg, dW = _build("qwen05b", max_ctx=prompt_len + new_tokens + 64, seed=4001)
@@ -137,7 +154,8 @@ def spec_case(k: int, prompt_len: int, new_tokens: int) -> dict:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["c0", "c2", "c3b32", "c4"])
+    ap.add_argument("case", choices=["c0", "c2", "c3b32", "c4", "prefill"])
+    ap.add_argument("--model", default="llama8b", choices=sorted(synth.CONFIGS))
     ap.add_argument("--prompt", type=int, default=None)
     ap.add_argument("--steps", type=int, default=None)
     a = ap.parse_args()
@@ -147,6 +165,8 @@ def main() -> None:
         line = decode_case("phi2", a.prompt or 512, a.steps or 256, 1, "c2", prefill_timed=True)
     elif a.case == "c3b32":
         line = decode_case("llama8b", a.prompt or 256, a.steps or 64, 32, "c3b32", prefill_timed=True)
+    elif a.case == "prefill":
+        line = prefill_case(a.model, a.prompt or 512)
     else:
         line = spec_case(4, a.prompt or 256, a.steps or 128)
     print(json.dumps(line), flush=True)
