@@ -584,25 +584,25 @@ __global__ void swiglu_kernel(const float* __restrict__ gu, int ld, int ffn, int
     }
 }
 // The MLP activation straight to fp16 [rows][ffn]: kind 0 = silu(gate) * up with gate | up side by side in a row of gu,
-// kind 1 = gelu. Two columns per thread.
-__global__ void act_f16_kernel(const float* __restrict__ gu, int ld, int ffn, int64_t total2, int kind, __half2* __restrict__ out) {
+// kind 1 = gelu. One row per blockIdx.y, four columns per thread (ffn % 4 == 0, ld % 4 == 0).
+__global__ void act_f16_kernel(const float* __restrict__ gu, int ld, int ffn, int kind, __half* __restrict__ out) {
     pdl_wait();
     pdl_trigger();
-    const int half_ffn = ffn >> 1;
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total2; i += (int64_t)gridDim.x * blockDim.x) {
-        const int64_t r = i / half_ffn, c = 2 * (i - r * half_ffn);
-        const float2 g = *reinterpret_cast<const float2*>(gu + r * ld + c);
-        float a0, a1;
-        if (kind == 0) {
-            const float2 u = *reinterpret_cast<const float2*>(gu + r * ld + ffn + c);
-            a0 = __fmul_rn(silu_f(g.x), u.x);
-            a1 = __fmul_rn(silu_f(g.y), u.y);
-        } else {
-            a0 = gelu_f(g.x);
-            a1 = gelu_f(g.y);
-        }
-        out[i] = __floats2half2_rn(a0, a1);
+    const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (c >= ffn) return;
+    const float* row = gu + (int64_t)blockIdx.y * ld;
+    const float4 g = *reinterpret_cast<const float4*>(row + c);
+    float a0, a1, a2, a3;
+    if (kind == 0) {
+        const float4 u = *reinterpret_cast<const float4*>(row + ffn + c);
+        a0 = __fmul_rn(silu_f(g.x), u.x); a1 = __fmul_rn(silu_f(g.y), u.y);
+        a2 = __fmul_rn(silu_f(g.z), u.z); a3 = __fmul_rn(silu_f(g.w), u.w);
+    } else {
+        a0 = gelu_f(g.x); a1 = gelu_f(g.y); a2 = gelu_f(g.z); a3 = gelu_f(g.w);
     }
+    const __half2 h01 = __floats2half2_rn(a0, a1), h23 = __floats2half2_rn(a2, a3);
+    *reinterpret_cast<uint2*>(out + (int64_t)blockIdx.y * ffn + c) =
+        make_uint2(*reinterpret_cast<const uint32_t*>(&h01), *reinterpret_cast<const uint32_t*>(&h23));
 }
 __global__ void gelu_kernel(float* x, int64_t n) {
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) x[i] = gelu_f(x[i]);
@@ -629,10 +629,9 @@ cudaError_t launch_swiglu(const float* gate_up, int ld, int ffn, int rows, float
     return finish_launch();
 }
 cudaError_t launch_act_f16(const float* gu, int ld, int ffn, int rows, int kind, __half* out, cudaStream_t st) {
-    const int64_t total2 = (int64_t)rows * ffn / 2;
-    if (total2 == 0) return cudaSuccess;
-    if ((ffn & 1) || (ld & 1)) return cudaErrorInvalidValue;
-    cudaError_t le = launch_pdl(act_f16_kernel, dim3(ew_blocks(total2)), dim3(256), 0, st, gu, ld, ffn, total2, kind, reinterpret_cast<__half2*>(out));
+    if (rows == 0 || ffn == 0) return cudaSuccess;
+    if ((ffn & 3) || (ld & 3)) return cudaErrorInvalidValue;
+    cudaError_t le = launch_pdl(act_f16_kernel, dim3((ffn / 4 + 255) / 256, rows), dim3(256), 0, st, gu, ld, ffn, kind, out);
     if (le != cudaSuccess) return le;
     return finish_launch();
 }
