@@ -66,7 +66,7 @@ int32_t sp_cuda_matmul_nt_dev(const SpWeight* w, const float* x_dev, int64_t m, 
  * 1: the CUDA-core GEMV on the raw blocks (op-level calls only; an independent second implementation for
  * cross-checks); 3: tensor-core GEMV, persistent TMA-streaming kernel where the shape qualifies. Process-wide. */
 int32_t sp_cuda_set_gemv_path(int32_t path);
-/* 1 (default): op-level matmuls with m >= 64 rows and k % 256 == 0 run the tcgen05 / TMEM dequant GEMM; 0: always the
+/* 1 (default): op-level matmuls with m >= 17 rows and k % 256 == 0 (Q8_0: k % 128 == 0) run the tcgen05 / TMEM dequant GEMM; 0: always the
  * 16-row GEMV passes (for cross-checks and timing comparisons). Process-wide; engines have their own switch. */
 int32_t sp_cuda_set_large_m_gemm(int32_t on);
 /* Device address and byte size of the resident blocks (for benchmarks that rotate buffers). */
