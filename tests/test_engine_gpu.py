@@ -205,3 +205,31 @@ def test_gguf_file_loads_to_the_same_engine(oracle, name, tmp_path):
     assert np.array_equal(a.forward_logits(ids, True), b.forward_logits(ids, True))
     assert a.desc.rotary_dim == cfg["rotary_dim"] and a.desc.head_dim == cfg["head_dim"]
     a.close(); b.close()
+
+
+def test_batched_decode_of_twenty_sequences_goes_through_the_large_m_path(oracle):
+    """From 17 rows on a decode step multiplies on the tcgen05 GEMM (fp16 operands) and attention runs unsplit: its rows
+    must agree with each sequence decoded alone on the integer GEMV path, to the fp16 rounding of the operands."""
+    cfg, W = tiny_model("tiny_llama")
+    B = 20
+    eng = ForwardEngine.from_weights(cfg, W, max_batch=B, max_tokens=32)
+    solo = ForwardEngine.from_weights(cfg, W)
+    for e in (eng, solo):
+        e.set_kv_rounding(False)  # continuous cache rounding: this test is about the kernels
+    prompts = [prompt(cfg, 2 + (i % 5), seed=40 + i) for i in range(B)]
+    toks = []
+    for i, p in enumerate(prompts):
+        toks.append(int(oracle.argmax(eng.forward_slot(i, p))))
+    toks = np.array(toks, np.uint32)
+    for step in range(3):
+        logits, am = eng.decode_batch(toks, np.arange(B), want_logits=True, want_argmax=True)
+        nxt = []
+        for i in range(B):
+            prompts[i] = np.append(prompts[i], toks[i])
+            solo.reset_cache()
+            w = solo.forward_logits(prompts[i], True)
+            assert np.max(np.abs(logits[i] - w)) < 5e-3, (step, i)
+            assert am[i] == oracle.argmax(logits[i])
+            nxt.append(int(oracle.argmax(w)))
+        toks = np.array(nxt, np.uint32)
+    eng.close(); solo.close()
