@@ -60,8 +60,20 @@ void sp_cuda_free_weight(SpWeight* w);
 int32_t sp_cuda_dequant(const SpWeight* w, float* out_host);
 /* Y[m,n] = X[m,k] · Wᵀ, host buffers (copies inside). */
 int32_t sp_cuda_matmul_nt(const SpWeight* w, const float* x_host, int64_t m, float* y_host);
-/* Same with device buffers on `stream` (a cudaStream_t, or NULL for the default stream); no synchronisation. */
+/* Same with device buffers on `stream` (a cudaStream_t, or NULL for the default stream); the launches are not waited
+ * for. The weight carries a private workspace (activation digits, and an fp16 copy of x for calls of 17 rows and
+ * more), so calls on one SpWeight must be ordered on ONE stream and never run from two threads at once; use one
+ * SpWeight per stream otherwise. The fp16 buffer grows on demand: the first call with a given (larger) m of 17 rows or
+ * more frees and allocates device memory, which waits for all work of the device — issue one such call per weight at
+ * set-up, before any stream capture. A bounded wait inside the 17+-row kernel that runs out leaves y stale; the
+ * condition is reported (SP_ERR_CUDA) by the next call of this library that synchronises: sp_cuda_matmul_nt,
+ * sp_cuda_check_kernels, or an engine call that returns host data. */
 int32_t sp_cuda_matmul_nt_dev(const SpWeight* w, const float* x_dev, int64_t m, float* y_dev, void* stream);
+/* Waits for all work of `device`, then reports (SP_ERR_CUDA, message in sp_cuda_last_error) whether a bounded wait
+ * inside one of this library's kernels ran out on that device since the last check; the flag is cleared by the report.
+ * The reference's GPU backend has no such condition to report (its wgpu queue has no device-side waits,
+ * crates/sapient-backends/wgpu/src/context.rs); this is the error channel of the asynchronous device-pointer calls. */
+int32_t sp_cuda_check_kernels(int32_t device);
 /* Which GEMV kernel runs: 0 (default) and 2: tensor-core GEMV on tile-repacked weights, one CTA per 16-row tile row;
  * 1: the CUDA-core GEMV on the raw blocks (op-level calls only; an independent second implementation for
  * cross-checks); 3: tensor-core GEMV, persistent TMA-streaming kernel where the shape qualifies. Process-wide. */

@@ -44,6 +44,7 @@ SIGNATURES = {
     "sp_cuda_dequant": (_i32, [_vp, _vp]),
     "sp_cuda_matmul_nt": (_i32, [_vp, _vp, _i64, _vp]),
     "sp_cuda_matmul_nt_dev": (_i32, [_vp, _vp, _i64, _vp, _vp]),
+    "sp_cuda_check_kernels": (_i32, [_i32]),
     "sp_cuda_set_gemv_path": (_i32, [_i32]),
     "sp_cuda_weight_info": (_i32, [_vp, C.POINTER(_i32), C.POINTER(_i64), C.POINTER(_i64), C.POINTER(_sz)]),
     "sp_cuda_rms_norm": (_i32, [_i32, _vp, _vp, _i64, _i64, _f, _vp]),

@@ -33,14 +33,24 @@ def _stale() -> bool:
 def build(force: bool = False, verbose: bool = False) -> str:
     if not force and not _stale():
         return OUT
-    objs = []
-    for src in SOURCES:
-        obj = os.path.join(CSRC, src.replace(".cu", ".o"))
-        cmd = ["nvcc", *FLAGS[:-1], "-c", os.path.join(CSRC, src), "-o", obj]
-        if verbose:
-            cmd.insert(1, "-Xptxas=-v")
-        subprocess.run(cmd, check=True)
-        objs.append(obj)
+    from concurrent.futures import ThreadPoolExecutor
+
+    headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".h", ".cuh"))]
+    headers.append(os.path.join(HERE, "..", "include", "sapient_cuda.h"))
+    newest_header = max(os.path.getmtime(h) for h in headers)
+
+    def compile_one(src: str) -> str:
+        path, obj = os.path.join(CSRC, src), os.path.join(CSRC, src.replace(".cu", ".o"))
+        fresh = os.path.exists(obj) and os.path.getmtime(obj) > max(os.path.getmtime(path), newest_header)
+        if force or verbose or not fresh:
+            cmd = ["nvcc", *FLAGS[:-1], "-c", path, "-o", obj]
+            if verbose:
+                cmd.insert(1, "-Xptxas=-v")
+            subprocess.run(cmd, check=True)
+        return obj
+
+    with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1)) as pool:
+        objs = list(pool.map(compile_one, SOURCES))
     subprocess.run(["nvcc", "--shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", OUT, *objs], check=True)
     return OUT
 

@@ -306,6 +306,22 @@ int32_t sp_cuda_matmul_nt_dev(const SpWeight* w, const float* x_dev, int64_t m, 
     API_END
 }
 
+static int check_kernel_flags() {
+    const int a = tc5_take_timeout(), b = imma_take_timeout();
+    if (a < 0 || b < 0) { set_error("could not read the kernels' timeout flags"); return SP_ERR_CUDA; }
+    if (a > 0) { set_error("tcgen05 GEMM: a bounded mbarrier wait expired, the outputs of that launch are not valid"); return SP_ERR_CUDA; }
+    if (b > 0) { set_error("streaming GEMV: a bounded mbarrier wait expired, the outputs of that launch are not valid"); return SP_ERR_CUDA; }
+    return SP_OK;
+}
+
+int32_t sp_cuda_check_kernels(int32_t device) {
+    API_BEGIN
+    SP_CUDA_TRY(cudaSetDevice(device));
+    SP_CUDA_TRY(cudaDeviceSynchronize());
+    return check_kernel_flags();
+    API_END
+}
+
 int32_t sp_cuda_matmul_nt(const SpWeight* w, const float* x_host, int64_t m, float* y_host) {
     API_BEGIN
     if (!w || !x_host || !y_host || m < 0) { set_error("null argument"); return SP_ERR_ARG; }
@@ -317,7 +333,7 @@ int32_t sp_cuda_matmul_nt(const SpWeight* w, const float* x_host, int64_t m, flo
     int st = sp_cuda_matmul_nt_dev(w, x.as<float>(), m, y.as<float>(), nullptr);
     if (st != SP_OK) return st;
     SP_CUDA_TRY(cudaMemcpy(y_host, y.p, (size_t)(m * w->n) * 4, cudaMemcpyDeviceToHost));
-    return SP_OK;
+    return check_kernel_flags();
     API_END
 }
 

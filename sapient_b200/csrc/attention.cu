@@ -376,12 +376,10 @@ cudaError_t launch_attention_prefill(const float* q, int ldq, float* out, int ld
     cudaError_t le = cudaErrorInvalidValue;
 #define SP_FA(N)                                                                                                        \
     if (hd16 == N) {                                                                                                    \
-        static bool big_smem_dev[SP_MAX_DEVICES] = {};                                                                  \
-        bool& big_smem = big_smem_dev[current_device_index()];                                                          \
-        if (smem > 48 * 1024 && !big_smem) {                                                                            \
-            le = cudaFuncSetAttribute(attention_prefill_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024); \
+        static PerDeviceOnce big_smem;                                                                                  \
+        if (smem > 48 * 1024) {                                                                                         \
+            le = big_smem.run([] { return cudaFuncSetAttribute(attention_prefill_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024); }); \
             if (le != cudaSuccess) return le;                                                                           \
-            big_smem = true;                                                                                            \
         }                                                                                                               \
     }                                                                                                                   \
     if (hd16 == N) le = launch_pdl(attention_prefill_kernel<N>, grid, block, smem, st, q, ldq, out, out_h, ldo, n_tok, n_heads, slot, pos0, kv, layer, scale)

@@ -82,6 +82,9 @@ class Engine {
     int tp_connect_ptrs(void* const* blocks, int n); // the same for engines of ONE process: device pointers, no IPC
     void* tp_block() const { return tp_block_; }
     int tp_check();                                 // SP_ERR_COMM if a wait on a peer gave up
+    // After a stream synchronise: SP_ERR_CUDA if a bounded mbarrier wait of one of this device's kernels ran out since
+    // the last check (the kernel's outputs are then stale), else tp_check().
+    int device_check();
     void drop_graphs();                             // forget the captured step graphs (a launch parameter changed)
     int vocab_local() const { return vocab_l_; }
 
@@ -90,11 +93,11 @@ class Engine {
     bool finalized = false;
     bool trace_on = false;
     bool use_graphs = true;
-    bool use_tc5 = true;
+    bool use_tc5 = true;       // steps of TC5_MIN_M rows and more on the tcgen05 GEMM (false: always 16-row GEMV passes)
     bool graph_step_ = false;  // a step is being captured: its kernels may take positions only from device memory
     // 1 (default): new K / V rows get the reference's Q8_0 cache rounding before they are stored as fp16 (head_dim % 32
     // == 0, where the reference keeps a Q8_0 cache); 0: plain fp16 rounding. Change only while the caches are empty.
-    int kv_round = 1;   // large-M GEMM on tcgen05 (false: always the 16-row GEMV passes)
+    int kv_round = 1;
     bool profile_on = false;
     std::vector<int> seq_len;
     uint64_t weight_bytes = 0, kv_bytes = 0;
@@ -133,6 +136,10 @@ class Engine {
     uint8_t* tp_peer_[TP_MAX_RANKS] = {};
     bool tp_connected_ = false;
     bool tp_pending_ = false;       // partial rows have been pushed, x_ still lacks their sum
+    // decode_greedy returned without waiting (tokens_out == null): copies out of the pinned staging buffers may still be
+    // queued on the stream. Every call that rewrites those buffers drains the stream first.
+    bool async_pending_ = false;
+    int drain_async();
     const TpDev* tp_take() { const TpDev* t = tp_pending_ ? d_tp_ : nullptr; tp_pending_ = false; return t; }
     int tp_resolve(int T);          // stand-alone consumer when the next kernel is not the fused norm
     int vocab_l_ = 0, vocab_off_ = 0;

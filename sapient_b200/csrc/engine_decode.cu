@@ -89,6 +89,14 @@ void Engine::drop_graphs() {
     step_graph_kernels_.clear();
 }
 
+int Engine::drain_async() {
+    if (!async_pending_) return SP_OK;
+    async_pending_ = false;
+    SP_CUDA_TRY(cudaStreamSynchronize(stream));
+    SP_TRY(prof_flush());
+    return device_check();
+}
+
 int Engine::launch_decode_step(int T) {
     if (!use_graphs || profile_on || trace_on) return enqueue_decode_step(T);
     auto it = step_graphs_.find(T);
@@ -125,6 +133,7 @@ int Engine::time_families(unsigned mask, int T, int reps, float* ms_per_step) {
         return SP_ERR_ARG;
     }
     SP_CUDA_TRY(cudaSetDevice(d.device));
+    SP_TRY(drain_async());
     SP_CUDA_TRY(cudaStreamSynchronize(stream));
     const bool prof = profile_on, tr = trace_on;
     profile_on = false;
@@ -136,7 +145,9 @@ int Engine::time_families(unsigned mask, int T, int reps, float* ms_per_step) {
     cudaError_t ce = cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal);
     int st = SP_OK;
     if (ce == cudaSuccess) {
+        graph_step_ = true;  // as in launch_decode_step: captured kernels take positions from device memory only
         st = enqueue_decode_step(T);
+        graph_step_ = false;
         ce = cudaStreamEndCapture(stream, &graph);
     }
     fam_mask = 0xFFFFFFFFu;
@@ -173,6 +184,7 @@ int Engine::decode_greedy(const uint32_t* first_ids, const int32_t* slots, int b
     if (!first_ids || !slots || b <= 0 || steps <= 0) { set_error("empty input"); return SP_ERR_ARG; }
     if (b > logit_rows_ || b > d.max_tokens) { set_error("decode_greedy: batch larger than the decode step capacity"); return SP_ERR_ARG; }
     SP_CUDA_TRY(cudaSetDevice(d.device));
+    SP_TRY(drain_async());
     for (int i = 0; i < b; ++i) {
         if (slots[i] < 0 || slots[i] >= d.max_batch) { set_error("slot out of range"); return SP_ERR_ARG; }
         for (int j = 0; j < i; ++j) if (slots[i] == slots[j]) { set_error("decode_greedy: a slot appears twice"); return SP_ERR_ARG; }
@@ -206,23 +218,34 @@ int Engine::decode_greedy(const uint32_t* first_ids, const int32_t* slots, int b
         SP_CUDA_TRY(cudaMemcpyAsync(d_page_table_, h_page_table_.data(), h_page_table_.size() * 4, cudaMemcpyHostToDevice, stream));
         pages_dirty_ = false;
     }
-    for (int s = 0; s < steps; ++s) {
-        SP_TRY(launch_decode_step(b));
-        SP_CUDA_TRY(launch_pdl(advance_greedy_kernel, dim3((b + 127) / 128), dim3(128), 0, stream, (const uint32_t*)d_argmax_, d_ids_,
-                               d_tok_pos_, d_tokens_ + (size_t)s * b, b));
-        SP_CUDA_TRY(cudaGetLastError());
+    int done = 0, st = SP_OK;
+    for (; done < steps && st == SP_OK; ++done) {
+        st = launch_decode_step(b);
+        if (st != SP_OK) break;
+        cudaError_t ce = launch_pdl(advance_greedy_kernel, dim3((b + 127) / 128), dim3(128), 0, stream, (const uint32_t*)d_argmax_, d_ids_,
+                                    d_tok_pos_, d_tokens_ + (size_t)done * b, b);
+        if (ce == cudaSuccess) ce = cudaGetLastError();
+        if (ce != cudaSuccess) { set_error(std::string("advance_greedy_kernel: ") + cudaGetErrorString(ce)); st = SP_ERR_CUDA; break; }
         adjust_launch_count(1);
     }
-    for (int i = 0; i < b; ++i) seq_len[slots[i]] += steps;
+    // the sequences now hold the steps that were enqueued completely; on an error the pages reserved for the rest go
+    // back to the pool (truncate to the length reached)
+    for (int i = 0; i < b; ++i) seq_len[slots[i]] += done;
+    if (st != SP_OK) {
+        cudaStreamSynchronize(stream);
+        for (int i = 0; i < b; ++i) { size_t kept; truncate(slots[i], (size_t)seq_len[slots[i]], &kept); }
+        return st;
+    }
     if (tokens_out) {
         std::vector<uint32_t> tmp(need_tok);
         SP_CUDA_TRY(cudaMemcpyAsync(tmp.data(), d_tokens_, need_tok * 4, cudaMemcpyDeviceToHost, stream));
         SP_CUDA_TRY(cudaStreamSynchronize(stream));
         std::memcpy(tokens_out, tmp.data(), need_tok * 4);
         SP_TRY(prof_flush());
-        return tp_check();
+        return device_check();
     }
-    return SP_OK;  // asynchronous: the caller synchronises the stream
+    async_pending_ = true;  // asynchronous: the caller synchronises the stream; the next call of this engine drains it
+    return SP_OK;
 }
 
 }  // namespace sp

@@ -134,7 +134,7 @@ int Engine::run_chunk(const uint32_t* ids, const int32_t* slots, int T, int rows
         if (logits_out) std::memcpy(logits_out, p_logits_, (size_t)T * V * 4);
         if (argmax_out) std::memcpy(argmax_out, p_argmax_, (size_t)T * 4);
         SP_TRY(prof_flush());
-        return tp_check();
+        return device_check();
     }
     SP_TRY(enqueue_layers(T));
     SP_TRY(tp_resolve(T));
@@ -154,7 +154,7 @@ int Engine::run_chunk(const uint32_t* ids, const int32_t* slots, int T, int rows
     }
     SP_CUDA_TRY(cudaStreamSynchronize(stream));
     SP_TRY(prof_flush());
-    return tp_check();
+    return device_check();
 }
 
 int Engine::forward(const uint32_t* ids, const int32_t* slots, int64_t n, bool want_all, float* logits_out,
@@ -162,6 +162,7 @@ int Engine::forward(const uint32_t* ids, const int32_t* slots, int64_t n, bool w
     if (!finalized) { set_error("engine not finalised"); return SP_ERR_STATE; }
     if (!ids || !slots || n <= 0) { set_error("empty input"); return SP_ERR_ARG; }
     SP_CUDA_TRY(cudaSetDevice(d.device));
+    SP_TRY(drain_async());
     // validate everything before touching any state
     std::vector<int> add(d.max_batch, 0);
     for (int64_t i = 0; i < n; ++i) {

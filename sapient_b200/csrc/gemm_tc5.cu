@@ -28,6 +28,7 @@
 #include <cuda_fp16.h>
 
 #include <algorithm>
+#include <atomic>
 
 #include "kernels.h"
 #include "pdl.cuh"
@@ -561,6 +562,21 @@ __global__ void x_to_f16_kernel(const float* __restrict__ x, int ldx, int k, __h
         make_uint4(pack_h2(p0.x, p0.y), pack_h2(p0.z, p0.w), pack_h2(p1.x, p1.y), pack_h2(p1.z, p1.w));
 }
 
+// Reads and clears the flag a bounded mbarrier wait of gemm_tc5_kernel raises when it runs out (the kernel then skips
+// its epilogue, so y is stale). Synchronous copy from the device the calling thread has current: call it only where
+// the stream has been synchronised already. 1 = a wait expired since the last call, 0 = none, -1 = CUDA error.
+static std::atomic<int> g_tc5_launched[SP_MAX_DEVICES];  // per device: a launch has happened since the flag was last read
+int tc5_take_timeout() {
+    if (g_tc5_launched[current_device_index()].exchange(0) == 0) return 0;
+    int flag = 0;
+    if (cudaMemcpyFromSymbol(&flag, g_tc5_timeout, sizeof(int)) != cudaSuccess) { cudaGetLastError(); return -1; }
+    if (flag) {
+        const int zero = 0;
+        cudaMemcpyToSymbol(g_tc5_timeout, &zero, sizeof(int));
+    }
+    return flag ? 1 : 0;
+}
+
 bool tc5_supported(int dtype, int64_t k) {
     if (dtype == T_Q8_0) return k % 128 == 0;  // the tiling switches to four blocks per tile when k is not a multiple of 256
     return k % 256 == 0 && (dtype == T_Q4_K || dtype == T_Q6_K);
@@ -603,14 +619,8 @@ cudaError_t launch_gemm_tc5_multi(const Tc5Seg* segs, int nseg, int k, const __h
         a.seg[i] = segs[i];
         tiles += (segs[i].n + TC5_BM - 1) / TC5_BM;
     }
-    static bool attr_set[SP_MAX_DEVICES] = {};
-    static int sm_count = 0;
-    if (sm_count == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
-        if (sm_count <= 0) sm_count = 148;
-    }
+    static PerDeviceOnce attr_once;
+    const int sm_count = device_sm_count();
     const int nb_max = std::min(TC5_NB_MAX, (m + 15) & ~15);
     const int stage_bytes = nb_max * 256;
     const int stages = std::min(TC5_MAX_STAGES, TC5_SMEM_LIMIT / stage_bytes);
@@ -629,13 +639,13 @@ cudaError_t launch_gemm_tc5_multi(const Tc5Seg* segs, int nseg, int k, const __h
         }
     }
     // TMA descriptor of the fp16 activations [m][k]: boxes of 64 columns x nb_max rows, 128-byte swizzle, zero fill
-    static PFN_encodeTiled encode = nullptr;
-    if (!encode) {
+    static const PFN_encodeTiled encode = [] {  // initialised once, thread-safe
         void* fn = nullptr;
         cudaDriverEntryPointQueryResult qres;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess || !fn) return cudaErrorNotSupported;
-        encode = reinterpret_cast<PFN_encodeTiled>(fn);
-    }
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess) fn = nullptr;
+        return reinterpret_cast<PFN_encodeTiled>(fn);
+    }();
+    if (!encode) return cudaErrorNotSupported;
     CUtensorMap tmap;
     {
         const cuuint64_t gdim[2] = {(cuuint64_t)k, (cuuint64_t)m};
@@ -651,11 +661,8 @@ cudaError_t launch_gemm_tc5_multi(const Tc5Seg* segs, int nseg, int k, const __h
     a.stage_bytes = stage_bytes; a.stages = stages;
     constexpr int SMEM_CAP = TC5_SMEM_LIMIT + 1024;
     cudaError_t le;
-    if (bool& set = attr_set[current_device_index()]; !set) {
-        le = cudaFuncSetAttribute(gemm_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_CAP);
-        if (le != cudaSuccess) return le;
-        set = true;
-    }
+    le = attr_once.run([] { return cudaFuncSetAttribute(gemm_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_CAP); });
+    if (le != cudaSuccess) return le;
     if (tail_split > 1 && !in_place) {
         // the shared tiles' outputs start from zero
         int t0 = 0;  // first weight tile of the segment, counted over the launch
@@ -674,6 +681,7 @@ cudaError_t launch_gemm_tc5_multi(const Tc5Seg* segs, int nseg, int k, const __h
         }
     }
     const int grid = full_items + (items - full_items) * tail_split;
+    g_tc5_launched[current_device_index()].store(1);
     le = launch_pdl(gemm_tc5_kernel, dim3((unsigned)grid), dim3(TC5_THREADS), smem_bytes, st, a, tmap);
     if (le != cudaSuccess) return le;
     return count_launch_and_check();

@@ -24,7 +24,7 @@ namespace sp {
 
 cudaError_t count_launch_and_check();  // kernels.cu
 
-// 0: pick per launch (streaming kernel when it qualifies); 2: always the per-tile-row kernel.
+// 0: the one-CTA-per-tile-row kernel (default); 3: the persistent streaming kernel for launches that qualify (plan_stream).
 static std::atomic<int> g_imma_kernel{0};
 
 // ───────────────────────────── weight repack ────────────────────────────────
@@ -872,7 +872,7 @@ __global__ void __launch_bounds__(IMMA_WARPS * 32, (NT == 1 && FMT != 0) ? 3 : 2
 constexpr int STREAM_WARPS = 16;
 constexpr int STREAM_MAX_STAGES = 4;
 constexpr int STREAM_SMEM_LIMIT = 220 * 1024;
-constexpr int STREAM_SPIN_LIMIT = 1 << 16;  // polls of up to ~20 us each before a wait gives up (~1 s)  // mbarrier polls before a wait gives up (~ a second)
+constexpr int STREAM_SPIN_LIMIT = 1 << 16;  // polls of up to ~20 us each (the try_wait time hint) before a wait gives up: about a second
 
 // Set when a bounded wait in a kernel of this file ran out; host code reads and clears it.
 __device__ int g_imma_timeout = 0;
@@ -1071,8 +1071,21 @@ __global__ void __launch_bounds__(STREAM_WARPS * 32, 1) gemv_imma_stream_kernel(
     if (!ok && lane == 0) atomicExch(&g_imma_timeout, 1);
 }
 
-static int g_sm_count = 0;
-static bool g_stream_attr[SP_MAX_DEVICES][3] = {};
+// Reads and clears g_imma_timeout (device the calling thread has current; call after a stream synchronise).
+// 1 = a bounded wait of the streaming kernel expired since the last call, 0 = none, -1 = CUDA error.
+static std::atomic<int> g_stream_launched[SP_MAX_DEVICES];  // per device: the streaming kernel has been launched since the flag was last read
+int imma_take_timeout() {
+    if (g_stream_launched[current_device_index()].exchange(0) == 0) return 0;
+    int flag = 0;
+    if (cudaMemcpyFromSymbol(&flag, g_imma_timeout, sizeof(int)) != cudaSuccess) { cudaGetLastError(); return -1; }
+    if (flag) {
+        const int zero = 0;
+        cudaMemcpyToSymbol(g_imma_timeout, &zero, sizeof(int));
+    }
+    return flag ? 1 : 0;
+}
+
+static PerDeviceOnce g_stream_attr[3];
 
 // Shared-memory layout of the streaming kernel, or total == 0 when the launch does not qualify.
 static StreamPlan plan_stream(const ImmaArgs& a) {
@@ -1117,19 +1130,16 @@ cudaError_t launch_gemv_imma(const ImmaArgs& a, cudaStream_t st) {
     // (132 vs 81 us on a 128256 x 4096 Q4_K matrix), so the default is the latter.
     const StreamPlan p = (g_imma_kernel.load() == 3 && !a.tp) ? plan_stream(a) : StreamPlan{};
     if (p.total > 0) {
-        if (g_sm_count == 0) {
-            int dev = 0;
-            cudaGetDevice(&dev);
-            cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
-            if (g_sm_count <= 0) g_sm_count = 148;
-        }
-        const int grid = tiles < g_sm_count ? tiles : g_sm_count;
-        if (bool& attr = g_stream_attr[current_device_index()][nt]; !attr) {
-            cudaError_t e = nt == 1 ? cudaFuncSetAttribute(gemv_imma_stream_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, STREAM_SMEM_LIMIT)
-                                    : cudaFuncSetAttribute(gemv_imma_stream_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, STREAM_SMEM_LIMIT);
+        const int sms = device_sm_count();
+        const int grid = tiles < sms ? tiles : sms;
+        {
+            const cudaError_t e = g_stream_attr[nt].run([nt] {
+                return nt == 1 ? cudaFuncSetAttribute(gemv_imma_stream_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, STREAM_SMEM_LIMIT)
+                               : cudaFuncSetAttribute(gemv_imma_stream_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, STREAM_SMEM_LIMIT);
+            });
             if (e != cudaSuccess) return e;
-            attr = true;
         }
+        g_stream_launched[current_device_index()].store(1);
         if (nt == 1) gemv_imma_stream_kernel<1><<<grid, STREAM_WARPS * 32, p.total, st>>>(a, p);
         else gemv_imma_stream_kernel<2><<<grid, STREAM_WARPS * 32, p.total, st>>>(a, p);
         return count_launch_and_check();

@@ -9,6 +9,7 @@
 #include <algorithm>
 #include <cmath>
 #include <cstdio>
+#include <cstdint>
 #include <cstring>
 #include <map>
 #include <string>
@@ -161,8 +162,18 @@ int sp_engine_from_gguf_impl(const char* path, int device, int max_ctx, int max_
     }
     if (!r.ok) { set_error("GGUF header truncated or malformed"); return SP_ERR_IO; }
     uint64_t alignment = 32;
-    if (meta.count("general.alignment") && meta["general.alignment"].num > 0) alignment = (uint64_t)meta["general.alignment"].num;
-    const size_t data_start = (size_t)((r.pos + alignment - 1) / alignment * alignment);
+    if (meta.count("general.alignment")) {
+        const double a = meta["general.alignment"].num;
+        // a power of two of sane size: anything else could wrap the offset arithmetic below
+        if (!(a >= 1 && a <= 65536) || ((uint64_t)a & ((uint64_t)a - 1)) != 0 || (double)(uint64_t)a != a) {
+            set_error("GGUF general.alignment must be a power of two in 1..65536");
+            return SP_ERR_IO;
+        }
+        alignment = (uint64_t)a;
+    }
+    const uint64_t data_start64 = ((uint64_t)r.pos + alignment - 1) / alignment * alignment;
+    if (data_start64 > buf.size()) { set_error("GGUF data section starts past the end of the file"); return SP_ERR_IO; }
+    const size_t data_start = (size_t)data_start64;
 
     // ── metadata -> description ──
     const std::string arch = meta.count("general.architecture") ? meta["general.architecture"].s : "llama";
@@ -213,11 +224,24 @@ int sp_engine_from_gguf_impl(const char* path, int device, int max_ctx, int max_
         if (!map_name(t.name, &hf)) continue;  // unknown tensors are skipped, as the reference does
         const int bb = sp::block_bytes(t.type), be = sp::block_elems(t.type);
         if (bb == 0) { set_error("tensor '" + t.name + "' has unsupported ggml type " + std::to_string(t.type)); return SP_ERR_DTYPE; }
-        int64_t numel = 1;
-        for (auto v : t.dims) numel *= v;
-        if (t.dims.empty() || t.dims[0] % be != 0) { set_error("tensor '" + t.name + "' inner dim is not a multiple of its block size"); return SP_ERR_SHAPE; }
-        const size_t nbytes = (size_t)(numel / be * bb);
-        if (data_start + t.offset + nbytes > buf.size()) { set_error("tensor '" + t.name + "' data out of file bounds"); return SP_ERR_IO; }
+        // dims and offset are raw 64-bit words of a downloaded file: every product and sum is checked before use
+        if (t.dims.empty()) { set_error("tensor '" + t.name + "' has no dimensions"); return SP_ERR_SHAPE; }
+        uint64_t numel = 1;
+        bool bad = false;
+        for (auto v : t.dims) {
+            if (v <= 0) { bad = true; break; }
+            if (numel > (uint64_t)INT64_MAX / (uint64_t)v) { bad = true; break; }
+            numel *= (uint64_t)v;
+        }
+        if (bad) { set_error("tensor '" + t.name + "' has a non-positive or overflowing shape"); return SP_ERR_SHAPE; }
+        if (t.dims[0] % be != 0) { set_error("tensor '" + t.name + "' inner dim is not a multiple of its block size"); return SP_ERR_SHAPE; }
+        const uint64_t nblocks = numel / (uint64_t)be;
+        const uint64_t avail = (uint64_t)buf.size() - data_start;
+        if (t.offset > avail || nblocks > (avail - t.offset) / (uint64_t)bb) {
+            set_error("tensor '" + t.name + "' data out of file bounds");
+            return SP_ERR_IO;
+        }
+        const size_t nbytes = (size_t)(nblocks * (uint64_t)bb);
         HostTensor h;
         h.dtype = t.type;
         h.data = buf.data() + data_start + t.offset;
@@ -264,7 +288,10 @@ int sp_engine_from_gguf_impl(const char* path, int device, int max_ctx, int max_
             const size_t at = key.find("qkv_proj.");
             const std::string base = key.substr(0, at), suffix = key.substr(at + 9);
             if (t.dims[0] != q_rows + 2 * kv_rows) { set_error("Phi qkv split for '" + key + "': unexpected row count"); return SP_ERR_SHAPE; }
+            // a 1-D tensor (bias) splits by elements: only unquantised types can be cut at any element
+            if (t.dims.size() != 2 && sp::block_elems(t.dtype) != 1) { set_error("Phi qkv split for '" + key + "': quantised 1-D tensor"); return SP_ERR_SHAPE; }
             const int64_t rb = t.dims.size() == 2 ? sp::row_bytes(t.dtype, t.dims[1]) : sp::block_bytes(t.dtype);
+            if ((uint64_t)t.dims[0] * (uint64_t)rb != (uint64_t)t.nbytes) { set_error("Phi qkv split for '" + key + "': byte count does not match the shape"); return SP_ERR_SHAPE; }
             const int64_t starts[3] = {0, q_rows, q_rows + kv_rows}, rows[3] = {q_rows, kv_rows, kv_rows};
             const char* nm[3] = {"q_proj.", "k_proj.", "v_proj."};
             for (int i = 0; i < 3; ++i) {

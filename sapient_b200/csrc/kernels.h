@@ -57,6 +57,10 @@ cudaError_t launch_gemv_imma(const ImmaArgs& a, cudaStream_t st);
 // 0: the one-CTA-per-tile-row kernel; 3: the persistent TMA-streaming kernel when k % 256 == 0 and the digits fit
 // shared memory.
 void imma_select_kernel(int which);
+// Bounded device-side waits (mbarrier waits of the streaming GEMV and of the tcgen05 GEMM) raise a per-device flag when
+// they run out. These read and clear it on the current device: 1 = expired since the last call, 0 = none, -1 = CUDA error.
+int imma_take_timeout();
+int tc5_take_timeout();
 // Producers that emit the digits of a GEMV input directly (a: planned ImmaArgs; a.m rows, a.k columns):
 // RMSNorm / LayerNorm of x (y optional f32 copy), SwiGLU (act 0) / tanh-GELU (act 1) of gu, merged split-K attention.
 // tp != null: x first receives the pending tensor-parallel sum (tp.cuh), in place.

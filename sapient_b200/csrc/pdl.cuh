@@ -10,6 +10,7 @@
 #pragma once
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <utility>
 
 namespace sp {
@@ -22,6 +23,35 @@ inline int current_device_index() {
     return dev >= 0 && dev < SP_MAX_DEVICES ? dev : 0;
 }
 
+
+// Multiprocessor count of the device the calling thread has current (cached per device; engines on different devices
+// and threads may ask concurrently).
+inline int device_sm_count() {
+    static std::atomic<int> cache[SP_MAX_DEVICES];
+    const int di = current_device_index();
+    int v = cache[di].load(std::memory_order_relaxed);
+    if (v == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
+        cache[di].store(v, std::memory_order_relaxed);
+    }
+    return v;
+}
+
+// One-time per-device function attributes (the opt-in to large dynamic shared memory): set() runs at least once per
+// device before the first launch there; a second thread racing the first may run it again, which is harmless.
+struct PerDeviceOnce {
+    std::atomic<bool> done[SP_MAX_DEVICES];
+    template <typename F>
+    cudaError_t run(F&& set) {
+        std::atomic<bool>& d = done[current_device_index()];
+        if (d.load(std::memory_order_acquire)) return cudaSuccess;
+        const cudaError_t e = set();
+        if (e == cudaSuccess) d.store(true, std::memory_order_release);
+        return e;
+    }
+};
 
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;\n" ::); }

@@ -220,6 +220,14 @@ int Engine::tp_connect_ptrs(void* const* blocks, int n) {
     return SP_OK;
 }
 
+int Engine::device_check() {
+    const int a = tc5_take_timeout(), b = imma_take_timeout();
+    if (a < 0 || b < 0) { set_error("could not read the kernels' timeout flags"); return SP_ERR_CUDA; }
+    if (a > 0) { set_error("tcgen05 GEMM: a bounded mbarrier wait expired, the outputs of that launch are not valid"); return SP_ERR_CUDA; }
+    if (b > 0) { set_error("streaming GEMV: a bounded mbarrier wait expired, the outputs of that launch are not valid"); return SP_ERR_CUDA; }
+    return tp_check();
+}
+
 int Engine::tp_check() {
     if (d.tp_size <= 1) return SP_OK;
     int flag = 0;

@@ -67,6 +67,46 @@ def test_gguf_errors_before_any_device_work(tmp_path):
     assert b"gpt2" in L.sp_cuda_last_error()
 
 
+def _raw_gguf(tensors, alignment=None, arch=b"llama", data=b""):
+    """A GGUF v3 file written by hand, so that fields the writer package would refuse can be set.
+    tensors: [(name, dims, ggml_type, offset)]; layout as crates/sapient-io/src/gguf.rs:517-578 reads it."""
+    import struct
+
+    def s(b):
+        return struct.pack("<Q", len(b)) + b
+
+    kv = [s(b"general.architecture") + struct.pack("<I", 8) + s(arch)]
+    if alignment is not None:
+        kv.append(s(b"general.alignment") + struct.pack("<I", 4) + struct.pack("<I", alignment & 0xFFFFFFFF))
+    out = b"GGUF" + struct.pack("<IQQ", 3, len(tensors), len(kv)) + b"".join(kv)
+    for name, dims, typ, off in tensors:
+        out += s(name) + struct.pack("<I", len(dims)) + b"".join(struct.pack("<Q", d & 0xFFFFFFFFFFFFFFFF) for d in dims)
+        out += struct.pack("<IQ", typ, off & 0xFFFFFFFFFFFFFFFF)
+    return out + b"\0" * 64 + data
+
+
+@pytest.mark.parametrize("tensors,alignment,status", [
+    ([(b"token_embd.weight", [32, 2], 0, 2**64 - 64)], None, _lib.SP_ERR_IO),       # offset that wraps the bounds sum
+    ([(b"token_embd.weight", [32, 2], 0, 2**40)], None, _lib.SP_ERR_IO),            # offset far past the file
+    ([(b"token_embd.weight", [2**62, 4], 0, 0)], None, _lib.SP_ERR_SHAPE),          # element count overflows 64 bits
+    ([(b"token_embd.weight", [32, -2], 0, 0)], None, _lib.SP_ERR_SHAPE),            # negative dim (as a u64: huge)
+    ([(b"token_embd.weight", [32, 0], 0, 0)], None, _lib.SP_ERR_SHAPE),             # empty dim
+    ([(b"token_embd.weight", [32, 2**40], 0, 0)], None, _lib.SP_ERR_IO),            # more blocks than the file holds
+    ([(b"token_embd.weight", [32, 2], 0, 0)], 0, _lib.SP_ERR_IO),                   # zero alignment
+    ([(b"token_embd.weight", [32, 2], 0, 0)], 48, _lib.SP_ERR_IO),                  # not a power of two
+    ([(b"token_embd.weight", [32, 2], 0, 0)], 1 << 30, _lib.SP_ERR_IO),             # absurd alignment
+])
+def test_gguf_crafted_headers_are_rejected(tmp_path, tensors, alignment, status):
+    """Offsets, dims and the alignment are raw words of a downloaded file; a header built to wrap the bounds arithmetic
+    must end in a status code before any byte outside the file is touched (the reference panics on the slice instead,
+    crates/sapient-io/src/gguf.rs:636-676)."""
+    L = _lib.lib()
+    h = C.c_void_p()
+    p = tmp_path / "crafted.gguf"
+    p.write_bytes(_raw_gguf(tensors, alignment, data=b"\0" * 256))
+    assert L.sp_cuda_engine_from_gguf(str(p).encode(), 0, 0, 1, C.byref(h)) == status, L.sp_cuda_last_error()
+
+
 def test_no_device_is_an_error_not_a_fallback():
     L = _lib.lib()
     if L.sp_cuda_device_count() > 0:
