@@ -2,7 +2,7 @@
 
     python oracle/build.py            # -> oracle/libsapient_oracle.so
 
-Flags: -O2 -ffp-contract=off keeps every rounding point of the restated Rust code
+Flags: -O3 -ffp-contract=off keeps every rounding point of the restated Rust code
 (Rust never contracts or reassociates float arithmetic); -mavx2 -mfma only makes
 the explicit fmaf calls of the restated AVX2 Q8_0 dot single instructions.
 """
@@ -19,7 +19,7 @@ def build_oracle(force: bool = False) -> str:
     if not force and os.path.exists(OUT) and os.path.getmtime(OUT) >= os.path.getmtime(SRC):
         return OUT
     cmd = [
-        "g++", "-std=c++17", "-O2", "-ffp-contract=off", "-fno-fast-math", "-mavx2", "-mfma",
+        "g++", "-std=c++17", "-O3", "-ffp-contract=off", "-fno-fast-math", "-mavx2", "-mfma",
         "-fopenmp", "-shared", "-fPIC", "-Wall", "-Wextra", "-o", OUT, SRC,
     ]
     subprocess.run(cmd, check=True)

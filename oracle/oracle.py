@@ -44,6 +44,8 @@ def lib():
             "so_byte_count": (i64, [C.c_int, i64]),
             "so_quantize_q8_0": (None, [vp, i64, vp]),
             "so_set_q8_mode": (None, [C.c_int]),
+            "so_set_kquant_order": (None, [C.c_int]),
+            "so_set_rows_at_once": (None, [C.c_int]),
             "so_dot_row": (C.c_float, [C.c_int, vp, vp, i64]),
             "so_matmul_nt": (C.c_int, [C.c_int, vp, vp, i64, i64, i64, vp]),
             "so_rms_norm": (None, [vp, vp, i64, i64, C.c_float, vp]),
@@ -75,6 +77,7 @@ def lib():
             "so_engine_forward_all_logits": (C.c_int, [vp, vp, i64, C.c_int, vp]),
             "so_engine_trace": (i64, [vp, C.c_int, vp]),
             "so_num_threads": (C.c_int, []),
+            "so_set_num_threads": (None, [C.c_int]),
         }
         for name, (res, args) in sig.items():
             fn = getattr(L, name)
@@ -122,6 +125,18 @@ def quantize_q8_0(x) -> np.ndarray:
 def set_q8_mode(mode: int) -> None:
     """0: the AVX2+FMA Q8_0 row dot (x86_64 default); 1: the portable scalar order."""
     lib().so_set_q8_mode(mode)
+
+
+def set_kquant_order(mode: int) -> None:
+    """0: the reference's evaluation order of the Q4_K / Q6_K row dots (one running accumulator over the row);
+    1: per-super-block partial sums added to the row total — a second valid order of the same products, used to
+    measure how far two correct implementations drift apart behind a step-function cache quantiser."""
+    lib().so_set_kquant_order(mode)
+
+
+def set_rows_at_once(on: bool) -> None:
+    """matmul_nt walks K-quant rows eight at a time (default, bit-identical, faster) or one at a time."""
+    lib().so_set_rows_at_once(int(on))
 
 
 def dot_row(dtype: int, row_blocks, x) -> float:
@@ -365,3 +380,16 @@ class OracleEngine:
 
 def num_threads() -> int:
     return int(lib().so_num_threads())
+
+
+def set_num_threads(n: int) -> None:
+    """Thread count of the oracle's parallel loops (the reference sizes its pool to all cores,
+    crates/sapient-backends/cpu/src/pool.rs). Launchers that export OMP_NUM_THREADS=1 would otherwise pin it to one."""
+    lib().so_set_num_threads(int(n))
+
+
+def use_all_cores() -> int:
+    """Sets the thread count to the cores this process may run on and returns it."""
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    set_num_threads(n)
+    return num_threads()

@@ -30,6 +30,7 @@
 #include <vector>
 
 #if defined(_OPENMP)
+#include <immintrin.h>
 #include <omp.h>
 #endif
 
@@ -406,9 +407,125 @@ float dot_q8_0_row_f32_scalar(const uint8_t* row, const float* x, int64_t k) {
     return acc;
 }
 
+// ── The same row dots, R rows at a time ─────────────────────────────────────
+// Pure speed-up of the checker: every row keeps its own accumulator and sees exactly the operations of the
+// single-row functions above, in the same order (nothing is contracted or reassociated: -ffp-contract=off, no
+// fast-math), so the results are bit-identical; the R independent dependency chains merely overlap in the pipeline
+// instead of each waiting for its own previous add. tests/test_oracle_kat.py compares the two paths bit for bit.
+constexpr int ROWS_R = 8;
+
+// Lanes of a 256-bit register = 8 consecutive weight rows; every lane runs the scalar sequence (separate multiply,
+// subtract, multiply, add: no fused operations).
+void dot_q4_k_rows(const uint8_t* rows, int64_t row_bytes, const float* x, int64_t k, float* out) {
+    __m256 acc = _mm256_setzero_ps();
+    int64_t x_off = 0;
+    for (int64_t b = 0; b < k / QK_K; ++b) {
+        const uint8_t* block[ROWS_R];
+        alignas(32) float d[ROWS_R], dmin[ROWS_R];
+        for (int r = 0; r < ROWS_R; ++r) {
+            block[r] = rows + r * row_bytes + b * Q4_K_BYTES;
+            d[r] = f16_to_f32(rd16(block[r]));
+            dmin[r] = f16_to_f32(rd16(block[r] + 2));
+        }
+        int q_off = 0, is = 0;
+        for (int g = 0; g < QK_K / 64; ++g) {
+            alignas(32) float d1[ROWS_R], m1v[ROWS_R], d2[ROWS_R], m2v[ROWS_R];
+            for (int r = 0; r < ROWS_R; ++r) {
+                uint8_t sc1, m1, sc2, m2;
+                get_scale_min_k4(is, block[r] + 4, &sc1, &m1);
+                d1[r] = d[r] * (float)sc1;
+                m1v[r] = dmin[r] * (float)m1;
+                get_scale_min_k4(is + 1, block[r] + 4, &sc2, &m2);
+                d2[r] = d[r] * (float)sc2;
+                m2v[r] = dmin[r] * (float)m2;
+            }
+            const __m256 vd1 = _mm256_load_ps(d1), vm1 = _mm256_load_ps(m1v), vd2 = _mm256_load_ps(d2), vm2 = _mm256_load_ps(m2v);
+            for (int l = 0; l < 32; ++l) {
+                const __m256i q = _mm256_setr_epi32(block[0][16 + q_off + l], block[1][16 + q_off + l], block[2][16 + q_off + l],
+                                                    block[3][16 + q_off + l], block[4][16 + q_off + l], block[5][16 + q_off + l],
+                                                    block[6][16 + q_off + l], block[7][16 + q_off + l]);
+                const __m256 lo = _mm256_cvtepi32_ps(_mm256_and_si256(q, _mm256_set1_epi32(0x0F)));
+                const __m256 hi = _mm256_cvtepi32_ps(_mm256_srli_epi32(q, 4));
+                const __m256 xa = _mm256_set1_ps(x[x_off + l]), xb = _mm256_set1_ps(x[x_off + l + 32]);
+                acc = _mm256_add_ps(acc, _mm256_mul_ps(_mm256_sub_ps(_mm256_mul_ps(vd1, lo), vm1), xa));
+                acc = _mm256_add_ps(acc, _mm256_mul_ps(_mm256_sub_ps(_mm256_mul_ps(vd2, hi), vm2), xb));
+            }
+            x_off += 64;
+            q_off += 32;
+            is += 2;
+        }
+    }
+    _mm256_storeu_ps(out, acc);
+}
+
+void dot_q6_k_rows(const uint8_t* rows, int64_t row_bytes, const float* x, int64_t k, float* out) {
+    __m256 acc = _mm256_setzero_ps();
+    int64_t x_off = 0;
+    for (int64_t b = 0; b < k / QK_K; ++b) {
+        const uint8_t* block[ROWS_R];
+        alignas(32) float d[ROWS_R];
+        for (int r = 0; r < ROWS_R; ++r) {
+            block[r] = rows + r * row_bytes + b * Q6_K_BYTES;
+            d[r] = f16_to_f32(rd16(block[r] + 208));
+        }
+        const __m256 vd = _mm256_load_ps(d);
+        int ql_off = 0, qh_off = 0, sc_base = 0;
+        for (int half = 0; half < QK_K / 128; ++half) {
+            for (int is = 0; is < 2; ++is) {
+                // d * sc for the four 16-wide scale groups this run of l uses (the product the scalar code forms first)
+                __m256 ds[4];
+                for (int q = 0; q < 4; ++q) {
+                    alignas(32) float t[ROWS_R];
+                    for (int r = 0; r < ROWS_R; ++r) t[r] = (float)(int8_t)block[r][192 + sc_base + is + 2 * q];
+                    ds[q] = _mm256_mul_ps(vd, _mm256_load_ps(t));
+                }
+                for (int l = 16 * is; l < 16 * is + 16; ++l) {
+                    __m256i la, lb, h;
+                    {
+                        const int oa = ql_off + l, ob = ql_off + l + 32, oh = 128 + qh_off + l;
+                        la = _mm256_setr_epi32(block[0][oa], block[1][oa], block[2][oa], block[3][oa], block[4][oa], block[5][oa], block[6][oa], block[7][oa]);
+                        lb = _mm256_setr_epi32(block[0][ob], block[1][ob], block[2][ob], block[3][ob], block[4][ob], block[5][ob], block[6][ob], block[7][ob]);
+                        h = _mm256_setr_epi32(block[0][oh], block[1][oh], block[2][oh], block[3][oh], block[4][oh], block[5][oh], block[6][oh], block[7][oh]);
+                    }
+                    const __m256i m4 = _mm256_set1_epi32(0x0F), m2 = _mm256_set1_epi32(3), off = _mm256_set1_epi32(32);
+                    const __m256i i1 = _mm256_sub_epi32(_mm256_or_si256(_mm256_and_si256(la, m4), _mm256_slli_epi32(_mm256_and_si256(h, m2), 4)), off);
+                    const __m256i i2 = _mm256_sub_epi32(_mm256_or_si256(_mm256_and_si256(lb, m4), _mm256_slli_epi32(_mm256_and_si256(_mm256_srli_epi32(h, 2), m2), 4)), off);
+                    const __m256i i3 = _mm256_sub_epi32(_mm256_or_si256(_mm256_srli_epi32(la, 4), _mm256_slli_epi32(_mm256_and_si256(_mm256_srli_epi32(h, 4), m2), 4)), off);
+                    const __m256i i4 = _mm256_sub_epi32(_mm256_or_si256(_mm256_srli_epi32(lb, 4), _mm256_slli_epi32(_mm256_and_si256(_mm256_srli_epi32(h, 6), m2), 4)), off);
+                    acc = _mm256_add_ps(acc, _mm256_mul_ps(_mm256_mul_ps(ds[0], _mm256_cvtepi32_ps(i1)), _mm256_set1_ps(x[x_off + l])));
+                    acc = _mm256_add_ps(acc, _mm256_mul_ps(_mm256_mul_ps(ds[1], _mm256_cvtepi32_ps(i2)), _mm256_set1_ps(x[x_off + l + 32])));
+                    acc = _mm256_add_ps(acc, _mm256_mul_ps(_mm256_mul_ps(ds[2], _mm256_cvtepi32_ps(i3)), _mm256_set1_ps(x[x_off + l + 64])));
+                    acc = _mm256_add_ps(acc, _mm256_mul_ps(_mm256_mul_ps(ds[3], _mm256_cvtepi32_ps(i4)), _mm256_set1_ps(x[x_off + l + 96])));
+                }
+            }
+            x_off += 128;
+            ql_off += 64;
+            qh_off += 32;
+            sc_base += 8;
+        }
+    }
+    _mm256_storeu_ps(out, acc);
+}
+
 int g_q8_mode = 0;  // 0 = AVX2+FMA order (what x86_64 CI runs), 1 = portable scalar order
+// 0 = the reference's order: one running f32 accumulator per output over the whole row. 1 = a second valid evaluation
+// order of the same products, for measuring how far two correct implementations drift apart: the sum of each
+// 256-element super-block is formed first and then added to the row total.
+int g_kquant_order = 0;
+int g_rows_at_once = 0;  // 1: matmul_nt walks K-quant rows ROWS_R at a time (tests; a timing run keeps the reference's one-row-per-call loop)
+
+float dot_kquant_row_blocked(int dtype, const uint8_t* row, const float* x, int64_t k) {
+    float acc = 0.0f;
+    const int64_t bb = dtype == T_Q4_K ? Q4_K_BYTES : Q6_K_BYTES;
+    for (int64_t b = 0; b < k / QK_K; ++b) {
+        const float part = dtype == T_Q4_K ? dot_q4_k_row_f32(row + b * bb, x + b * QK_K, QK_K) : dot_q6_k_row_f32(row + b * bb, x + b * QK_K, QK_K);
+        acc += part;
+    }
+    return acc;
+}
 
 float dot_row(int dtype, const uint8_t* row, const float* x, int64_t k) {
+    if (g_kquant_order == 1 && (dtype == T_Q4_K || dtype == T_Q6_K)) return dot_kquant_row_blocked(dtype, row, x, k);
     switch (dtype) {
         case T_Q4_K: return dot_q4_k_row_f32(row, x, k);
         case T_Q6_K: return dot_q6_k_row_f32(row, x, k);
@@ -446,6 +563,23 @@ int matmul_nt(int dtype, const float* x, const uint8_t* w, int64_t m, int64_t k,
         return 2;
     }
     const int64_t row_bytes = byte_count(dtype, k);
+    if ((dtype == T_Q4_K || dtype == T_Q6_K) && g_kquant_order == 0 && g_rows_at_once) {
+        // ROWS_R output rows at a time (bit-identical to the loop below, see dot_q4_k_rows)
+        const int64_t groups = n / ROWS_R;
+#pragma omp parallel for schedule(static)
+        for (int64_t gidx = 0; gidx < groups; ++gidx) {
+            const int64_t j = gidx * ROWS_R;
+            float o[ROWS_R];
+            for (int64_t i = 0; i < m; ++i) {
+                if (dtype == T_Q4_K) dot_q4_k_rows(w + j * row_bytes, row_bytes, x + i * k, k, o);
+                else dot_q6_k_rows(w + j * row_bytes, row_bytes, x + i * k, k, o);
+                for (int r = 0; r < ROWS_R; ++r) y[i * n + j + r] = o[r];
+            }
+        }
+        for (int64_t j = groups * ROWS_R; j < n; ++j)
+            for (int64_t i = 0; i < m; ++i) y[i * n + j] = dot_row(dtype, w + j * row_bytes, x + i * k, k);
+        return 0;
+    }
 #pragma omp parallel for schedule(static)
     for (int64_t j = 0; j < n; ++j) {
         const uint8_t* row = w + j * row_bytes;
@@ -1058,6 +1192,17 @@ int64_t so_engine_trace(void* ev, int layer, float* out) {
     std::memcpy(out, &e->trace[(size_t)(layer * n)], (size_t)n * 4);
     return e->trace_seq;
 }
+// Thread count of the parallel loops from here on (n <= 0: leave as is). Launchers such as torch.distributed.run
+// export OMP_NUM_THREADS=1 to their children; a timing run sets the count it wants explicitly.
+void so_set_num_threads(int n) {
+#if defined(_OPENMP)
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+void so_set_kquant_order(int mode) { g_kquant_order = mode ? 1 : 0; }
+void so_set_rows_at_once(int on) { g_rows_at_once = on ? 1 : 0; }
 int so_num_threads() {
 #if defined(_OPENMP)
     return omp_get_max_threads();

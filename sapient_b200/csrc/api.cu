@@ -285,7 +285,7 @@ int32_t sp_cuda_matmul_nt_dev(const SpWeight* w, const float* x_dev, int64_t m, 
         SP_CUDA_TRY(wm->ws.ensure_xh((size_t)m * w->k));
         SP_CUDA_TRY(launch_x_to_f16(x_dev, (int)w->k, (int)m, (int)w->k, wm->ws.xh, (cudaStream_t)stream));
         SP_CUDA_TRY(launch_gemm_tc5(w->tiled, w->dtype, (int)w->n, (int)w->k, wm->ws.xh, (int)m, y_dev, (int)w->n, nullptr, nullptr, 0,
-                                    (cudaStream_t)stream));
+                                    (cudaStream_t)stream, &wm->ws.tc5));
         return SP_OK;
     }
     if (w->tiled && g_gemv_path.load() == 0) {

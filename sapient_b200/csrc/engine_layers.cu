@@ -68,7 +68,7 @@ int Engine::gemv(const float* x, int ldx, int m, int k, const DevTensor* w0, con
             Tc5Seg segs[3];
             int ns = 0;
             for (int i = 0; i < 3 && ws[i]; ++i) segs[ns++] = Tc5Seg{ws[i]->tiled, ys[i], bs[i], ws[i]->dtype, (int)ws[i]->dims[0]};
-            SP_LAUNCH(F_GEMV, launch_gemm_tc5_multi(segs, ns, k, ws_.xh, m, ldy0, res, ldy0, stream));
+            SP_LAUNCH(F_GEMV, launch_gemm_tc5_multi(segs, ns, k, ws_.xh, m, ldy0, res, ldy0, stream, &ws_.tc5));
             return SP_OK;
         }
     }
@@ -140,7 +140,7 @@ int Engine::gemm_xh(int m, int k, const DevTensor* w0, const float* b0, float* y
     Tc5Seg segs[3];
     int ns = 0;
     for (int i = 0; i < 3 && ws[i]; ++i) segs[ns++] = Tc5Seg{ws[i]->tiled, ys[i], bs[i], ws[i]->dtype, (int)ws[i]->dims[0]};
-    SP_LAUNCH(F_GEMV, launch_gemm_tc5_multi(segs, ns, k, ws_.xh, m, ldy0, res, ldy0, stream));
+    SP_LAUNCH(F_GEMV, launch_gemm_tc5_multi(segs, ns, k, ws_.xh, m, ldy0, res, ldy0, stream, &ws_.tc5));
     return SP_OK;
 }
 

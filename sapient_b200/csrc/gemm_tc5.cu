@@ -374,9 +374,13 @@ struct Tc5Args {
     int ldres;
     // Work items = (128-row weight tile, 256-row activation tile) pairs, m_tiles consecutive items per weight tile.
     // CTAs 0 .. full_items-1 take one item each over the whole K range; the items after them (the last, partial wave
-    // of the grid) are each shared by tail_split CTAs that take a part of the K range and ADD into y, which must hold
-    // the residual (res == y) or zeros beforehand; the order of those f32 additions varies from run to run.
+    // of the grid) are each shared by tail_split CTAs that take a part of the K range. Each writes its partial tile to
+    // split_buf[(item - full_items) * tail_split + part][256 activation rows][128 weight rows]; the CTA that arrives
+    // last at split_cnt[item - full_items] adds the parts in part order (after the residual, when y holds it in place)
+    // and writes y: the order of the f32 additions is fixed, results do not vary from run to run.
     int m_tiles, full_items, tail_split;
+    float* split_buf;
+    unsigned* split_cnt;
     int stage_bytes;    // 256 * (widest activation tile of the launch, rounded to 16): two boxes of 64 columns
     int stages;         // depth of the activation ring that fits shared memory (3..8)
 };
@@ -385,6 +389,7 @@ __global__ void __launch_bounds__(TC5_THREADS, 1) gemm_tc5_kernel(const Tc5Args 
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t full_a[TC5_A_STAGES], empty_a[TC5_A_STAGES], full_b[TC5_MAX_STAGES], empty_b[TC5_MAX_STAGES], done_bar;
     __shared__ uint32_t tmem_slot;
+    __shared__ int split_last;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     uint8_t* smem = smem_raw + ((1024u - (tc5_smem_u32(smem_raw) & 1023u)) & 1023u);
     // which matrix of the launch this CTA works on, and its 128-row tile there
@@ -511,9 +516,10 @@ __global__ void __launch_bounds__(TC5_THREADS, 1) gemm_tc5_kernel(const Tc5Args 
         ok = ok && tc5_wait(&done_bar, 0u);
         ok = __all_sync(0xFFFFFFFFu, ok);  // one verdict for the warp: the loads below are warp-collective
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        const int q4 = warp & 3;
+        const int n = n0 + 32 * q4 + lane;
+        float* const pbuf = parts > 1 ? a.split_buf + ((size_t)(item - a.full_items) * parts + part) * (size_t)(TC5_NB_MAX * TC5_BM) : nullptr;
         if (ok) {
-            const int q4 = warp & 3;
-            const int n = n0 + 32 * q4 + lane;
             const float bias = (sg.bias && n < sg.n && part == 0) ? sg.bias[n] : 0.f;
             const bool add_res = a.res && si == 0 && parts == 1;
             float* yb = sg.y;
@@ -527,18 +533,43 @@ __global__ void __launch_bounds__(TC5_THREADS, 1) gemm_tc5_kernel(const Tc5Args 
                     : "r"(taddr)
                     : "memory");
                 asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-                if (n < sg.n) {
+                if (parts > 1) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) pbuf[(gi * 16 + j) * TC5_BM + 32 * q4 + lane] = __uint_as_float(r[j]) + bias;
+                } else if (n < sg.n) {
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
                         const int m = m0 + gi * 16 + j;
                         if (m < a.m) {
                             float v = __uint_as_float(r[j]) + bias;
                             if (add_res) v += a.res[(int64_t)m * a.ldres + n];
-                            if (parts > 1) atomicAdd(yb + (int64_t)m * a.ldy + n, v);  // y already holds the residual or zeros
-                            else yb[(int64_t)m * a.ldy + n] = v;
+                            yb[(int64_t)m * a.ldy + n] = v;
                         }
                     }
                 }
+            }
+        }
+        if (parts > 1) {
+            // Every producer warp comes here whatever its `ok` (the named barrier counts all 16 warps). The last CTA
+            // of the item to arrive sums the parts in part order: no CTA ever waits for another.
+            __threadfence();
+            asm volatile("bar.sync 1, %0;\n" ::"r"(TC5_PRODUCER_WARPS * 32) : "memory");
+            if (pw == 0 && lane == 0) split_last = atomicAdd(&a.split_cnt[item - a.full_items], 1u) == (unsigned)(parts - 1);
+            asm volatile("bar.sync 1, %0;\n" ::"r"(TC5_PRODUCER_WARPS * 32) : "memory");
+            if (split_last) {
+                __threadfence();
+                const float* all = a.split_buf + (size_t)(item - a.full_items) * parts * (size_t)(TC5_NB_MAX * TC5_BM);
+                const bool in_place = a.res && si == 0;  // y holds the residual (the launcher splits only when res == y)
+                for (int idx = pw * 32 + lane; idx < nb * TC5_BM; idx += TC5_PRODUCER_WARPS * 32) {
+                    const int mm = idx / TC5_BM, nn = idx - mm * TC5_BM;
+                    const int m = m0 + mm, nrow = n0 + nn;
+                    if (m < a.m && nrow < sg.n) {
+                        float v = in_place ? sg.y[(int64_t)m * a.ldy + nrow] : 0.f;
+                        for (int p2 = 0; p2 < parts; ++p2) v += __ldcg(all + (size_t)p2 * (TC5_NB_MAX * TC5_BM) + idx);
+                        sg.y[(int64_t)m * a.ldy + nrow] = v;
+                    }
+                }
+                if (pw == 0 && lane == 0) a.split_cnt[item - a.full_items] = 0u;  // ready for the next launch
             }
         }
     }
@@ -590,26 +621,32 @@ cudaError_t launch_x_to_f16(const float* x, int ldx, int m, int k, __half* out, 
     return count_launch_and_check();
 }
 
-// Zeros columns [c0, c0 + nc) of rows 0 .. rows-1 of y (row stride ld): the tiles whose K range is shared.
-__global__ void zero_cols_kernel(float* __restrict__ y, int ld, int rows, int c0, int nc) {
-    pdl_wait();
-    pdl_trigger();
-    const int64_t total = (int64_t)rows * nc;
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-        const int64_t r = i / nc;
-        y[r * ld + c0 + (i - r * nc)] = 0.f;
-    }
-}
-
 typedef CUresult (*PFN_encodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                     const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                     CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 // Up to three matrices sharing the activations in one launch. res (added to segment 0) may alias its y. The items of the
-// grid's last, partial wave are split along K over as many CTAs as fill the SMs (see Tc5Args), unless there is a
-// residual that is not in place.
+// grid's last, partial wave are split along K over as many CTAs as fill the SMs (see Tc5Args) when the caller provides
+// scratch for their partial tiles, unless there is a residual that is not in place.
+
+cudaError_t Tc5Scratch::alloc() {
+    release();
+    parts_cap = (size_t)device_sm_count();
+    cudaError_t e = cudaMalloc((void**)&buf, parts_cap * TC5_NB_MAX * TC5_BM * sizeof(float));
+    if (e == cudaSuccess) e = cudaMalloc((void**)&cnt, TC5_SPLIT_MAX_ITEMS * sizeof(unsigned));
+    if (e == cudaSuccess) e = cudaMemset(cnt, 0, TC5_SPLIT_MAX_ITEMS * sizeof(unsigned));
+    if (e != cudaSuccess) release();
+    return e;
+}
+
+void Tc5Scratch::release() {
+    if (buf) cudaFree(buf);
+    if (cnt) cudaFree(cnt);
+    buf = nullptr; cnt = nullptr; parts_cap = 0;
+}
+
 cudaError_t launch_gemm_tc5_multi(const Tc5Seg* segs, int nseg, int k, const __half* xh, int m, int ldy, const float* res, int ldres,
-                                  cudaStream_t st) {
+                                  cudaStream_t st, const Tc5Scratch* scratch) {
     if (m <= 0 || nseg <= 0) return cudaSuccess;
     if (nseg > 3 || k % 128 != 0) return cudaErrorInvalidValue;
     Tc5Args a{};
@@ -629,13 +666,13 @@ cudaError_t launch_gemm_tc5_multi(const Tc5Seg* segs, int nseg, int k, const __h
     const int chunks = k / TC5_BK, items = tiles * m_tiles;
     int full_items = items, tail_split = 1;
     const bool in_place = nseg == 1 && res && res == segs[0].y;
-    if (!res || in_place) {
+    if ((!res || in_place) && scratch && scratch->buf && scratch->cnt) {
         int tail = items % sm_count;
         if (tail > 0) {
             int first = (items - tail) / m_tiles * m_tiles;  // whole weight tiles only
             tail = items - first;
             const int ts = std::min({8, sm_count / tail, chunks / 4});
-            if (ts >= 2) { full_items = first; tail_split = ts; }
+            if (ts >= 2 && tail <= TC5_SPLIT_MAX_ITEMS && (size_t)tail * ts <= scratch->parts_cap) { full_items = first; tail_split = ts; }
         }
     }
     // TMA descriptor of the fp16 activations [m][k]: boxes of 64 columns x nb_max rows, 128-byte swizzle, zero fill
@@ -663,23 +700,7 @@ cudaError_t launch_gemm_tc5_multi(const Tc5Seg* segs, int nseg, int k, const __h
     cudaError_t le;
     le = attr_once.run([] { return cudaFuncSetAttribute(gemm_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_CAP); });
     if (le != cudaSuccess) return le;
-    if (tail_split > 1 && !in_place) {
-        // the shared tiles' outputs start from zero
-        int t0 = 0;  // first weight tile of the segment, counted over the launch
-        for (int i = 0; i < nseg; ++i) {
-            const int nt = (segs[i].n + TC5_BM - 1) / TC5_BM;
-            const int first = std::max(full_items / m_tiles, t0) - t0;  // first shared tile inside this segment
-            if (first < nt) {
-                const int c0 = first * TC5_BM, nc = segs[i].n - c0;
-                const int64_t total = (int64_t)m * nc;
-                le = launch_pdl(zero_cols_kernel, dim3((unsigned)std::min<int64_t>((total + 255) / 256, 1184)), dim3(256), 0, st, segs[i].y, ldy, m, c0, nc);
-                if (le != cudaSuccess) return le;
-                le = count_launch_and_check();
-                if (le != cudaSuccess) return le;
-            }
-            t0 += nt;
-        }
-    }
+    if (tail_split > 1) { a.split_buf = scratch->buf; a.split_cnt = scratch->cnt; }
     const int grid = full_items + (items - full_items) * tail_split;
     g_tc5_launched[current_device_index()].store(1);
     le = launch_pdl(gemm_tc5_kernel, dim3((unsigned)grid), dim3(TC5_THREADS), smem_bytes, st, a, tmap);
@@ -688,9 +709,9 @@ cudaError_t launch_gemm_tc5_multi(const Tc5Seg* segs, int nseg, int k, const __h
 }
 
 cudaError_t launch_gemm_tc5(const uint8_t* wt, int dtype, int n, int k, const __half* xh, int m, float* y, int ldy, const float* bias,
-                            const float* res, int ldres, cudaStream_t st) {
+                            const float* res, int ldres, cudaStream_t st, const Tc5Scratch* scratch) {
     Tc5Seg sg{wt, y, bias, dtype, n};
-    return launch_gemm_tc5_multi(&sg, 1, k, xh, m, ldy, res, ldres, st);
+    return launch_gemm_tc5_multi(&sg, 1, k, xh, m, ldy, res, ldres, st, scratch);
 }
 
 }  // namespace sp

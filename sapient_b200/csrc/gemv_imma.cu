@@ -491,12 +491,14 @@ cudaError_t ActWorkspace::ensure_xh(size_t elems) {
     xh_elems = 0;
     cudaError_t e = cudaMalloc((void**)&xh, elems * sizeof(__half));
     if (e == cudaSuccess) xh_elems = elems;
+    if (e == cudaSuccess && !tc5.buf) e = tc5.alloc();
     return e;
 }
 
 void ActWorkspace::release() {
     if (xh) cudaFree(xh);
     xh = nullptr; xh_elems = 0;
+    tc5.release();
     if (xq) cudaFree(xq);
     if (colscale) cudaFree(colscale);
     if (xs32d) cudaFree(xs32d);

@@ -78,6 +78,18 @@ bool attention_prefill_supported(int head_dim);
 cudaError_t launch_attention_prefill(const float* q, int ldq, float* out, int ldo, int n_tok, int n_heads, int slot, int pos0, KvGeom kv,
                                      int layer, float scale, cudaStream_t st, __half* out_h = nullptr);
 
+// Scratch of the GEMM's split last wave: one 256 x 128 f32 partial tile per CTA of that wave (at most one per SM:
+// 19 MB on a 148-SM device) and one arrival counter per shared work item. Owned by whoever owns the stream the launches
+// go to (an engine, an op-level weight): launches that may overlap on the device must not share one. Without scratch the
+// last wave is not split.
+constexpr int TC5_SPLIT_MAX_ITEMS = 256;
+struct Tc5Scratch {
+    float* buf = nullptr;
+    unsigned* cnt = nullptr;   // zero between launches
+    size_t parts_cap = 0;      // partial tiles buf holds
+    cudaError_t alloc();       // on the current device; not during stream capture
+    void release();
+};
 // Workspace of the activation digits for up to 16 activation rows of k_max columns.
 struct ActWorkspace {
     int8_t* xq = nullptr;
@@ -87,6 +99,7 @@ struct ActWorkspace {
     int k_max = 0;
     __half* xh = nullptr;      // fp16 copy of the activations for the large-M tensor-core GEMM (gemm_tc5.cu)
     size_t xh_elems = 0;
+    Tc5Scratch tc5;            // allocated with xh
     cudaError_t ensure_xh(size_t elems);  // grows the buffer (allocates: not during stream capture)
     static constexpr int NCP_MAX = 32;
     cudaError_t alloc(int k_max_);
@@ -102,7 +115,7 @@ constexpr int TC5_MIN_M = 17;  // up to 16 rows one GEMV pass is faster; from 17
 bool tc5_supported(int dtype, int64_t k);
 cudaError_t launch_x_to_f16(const float* x, int ldx, int m, int k, __half* out, cudaStream_t st);
 cudaError_t launch_gemm_tc5(const uint8_t* wt, int dtype, int n, int k, const __half* xh, int m, float* y, int ldy, const float* bias,
-                            const float* res, int ldres, cudaStream_t st);
+                            const float* res, int ldres, cudaStream_t st, const Tc5Scratch* scratch = nullptr);
 struct Tc5Seg {
     const uint8_t* wt;  // tiled weights
     float* y;           // output base: element (m, r) at y[m * ldy + r]
@@ -111,7 +124,7 @@ struct Tc5Seg {
 };
 // Up to three matrices sharing the activations in ONE launch (q|k|v, gate|up); res is added to segment 0.
 cudaError_t launch_gemm_tc5_multi(const Tc5Seg* segs, int nseg, int k, const __half* xh, int m, int ldy, const float* res, int ldres,
-                                  cudaStream_t st);
+                                  cudaStream_t st, const Tc5Scratch* scratch = nullptr);
 
 cudaError_t launch_dequant(int dtype, const uint8_t* w, int64_t n, int64_t k, float* out, cudaStream_t st);
 cudaError_t launch_gemv(const GemvArgs& a, cudaStream_t st);

@@ -17,4 +17,5 @@ def oracle():
     from oracle import oracle as o
 
     o.lib()
+    o.set_rows_at_once(True)  # eight K-quant rows per pass: bit-identical to the row-by-row loop (checked in test_oracle_kat.py)
     return o

@@ -1,19 +1,33 @@
-"""Full-size parity: the Qwen2.5-0.5B-shaped and the Llama-3-8B-shaped synthetic models (BASELINE configs) against the
-CPU oracle, teacher-forced with the oracle's tokens.
+"""Full-size parity: the synthetic models of the benchmark configurations at their own prompt and decode lengths,
+against the CPU oracle, teacher-forced with the oracle's greedy tokens.
 
-Two comparisons per model:
-  * kernels: both sides round new K / V rows to fp16 (continuous rounding). Bar: final logits within 2e-2 max-abs,
-    greedy top-1 agreement >= 99 %.
-  * reference configuration: the oracle keeps the reference's Q8_0 cache, the engine applies the same Q8_0 rounding
-    before its fp16 store (its default). That rounding is a step function: a 1e-7 difference in a K / V value moves a
-    whole int8 level (0.8 % of the block maximum), and 32 layers amplify such flips, so at the 8B shape the logits of
-    two correct implementations differ by ~0.1 (the oracle itself moves by ~0.36 when its cache is switched from
-    Q8_0 to fp16). The 2e-2 logit bar is therefore asserted on the kernels comparison and the greedy-agreement bar
-    everywhere; the deviation under the reference cache is printed and bounded loosely (0.5B shape: 1.7e-2 while the
-    48-token prompt went through the integer GEMV, 2.7e-2 now that steps of 17 rows and more use the tcgen05 GEMM
-    with fp16 operands, whose 3e-4 relative error flips a few more int8 levels; 8B shape: ~0.12).
-A CUDA pick counts as agreeing when it is the oracle's pick or the oracle's own logits rank it within 4e-2 of its
-maximum (random-init models have near-flat logits; ties in the 2nd digit carry no information about the kernels)."""
+    qwen05b  Qwen2.5-0.5B shape, 128-token prompt + 128 decode steps
+    llama8b  Llama-3-8B shape,   128-token prompt + 100 decode steps
+    phi2     Phi-2 shape,        128-token prompt +  64 decode steps
+    qwen15b  Qwen2.5-1.5B shape, 256-token prompt + 100 decode steps (the speculative target)
+
+Per model, two comparisons, both with the bars of the task written out and no per-model constants:
+
+  * fp16 cache on both sides (the oracle's kv_mode 1; the engine with the Q8_0 pre-rounding off). Every rounding on
+    the path is continuous, so this isolates the kernels. Bars: final logits within 2e-2 max-abs at every position
+    checked; the engine's greedy pick equals the oracle's (exact arg-max) on >= 99 % of the decode steps.
+
+  * the reference's own configuration: the oracle keeps the Q8_0 KV cache of forward/common.rs:449-538 (an f32 cache
+    where head_dim is not a multiple of 32), the engine rounds new K / V rows the same way before its fp16 store. That
+    quantiser is a step function: a difference of one unit in the last place of a K / V value can move an int8 level,
+    i.e. 0.8 % of the block's maximum, and the layers above amplify it. How much of that is inherent is MEASURED
+    here instead of assumed: the oracle is run a second time with nothing changed but the evaluation order of its
+    row dots (per-super-block partial sums for the K-quants, the portable scalar order for Q8_0 — both orders exist in
+    the reference for other targets), on the same tokens. The engine must stay as close to the reference as the
+    reference stays to itself: its worst logit deviation is at most max(2e-2, 2 x the oracle-vs-oracle deviation) — the
+    factor covers the scatter of a maximum over ~10^7 logits of two chaotic trajectories — and it agrees with the
+    oracle's greedy pick at least as often as the reordered oracle does, or on 99 % of the steps.
+
+Each run prints one line per comparison; with SAPIENT_PARITY_REPORT=<file> the numbers are appended there as JSON lines.
+"""
+import json
+import os
+
 import numpy as np
 import pytest
 
@@ -22,43 +36,88 @@ from sapient_b200.engine import ForwardEngine
 
 pytestmark = pytest.mark.gpu
 LOGIT_BAR = 2e-2
-MARGIN = 4e-2
+AGREE = 0.99
+SELF_FACTOR = 2.0
+
+CASES = [("qwen05b", 128, 128), ("llama8b", 128, 100), ("phi2", 128, 64), ("qwen15b", 256, 100)]
 
 
-def _run(oracle, cfg, Wn, ids, steps, reference_cache: bool):
-    eng = ForwardEngine.from_weights(cfg, Wn, max_tokens=64)
+def _oracle_run(oracle, cfg, Wn, ids, steps, kv_mode, tokens=None):
+    """Prompt logits + `steps` decode logits. tokens None: feeds its own greedy picks and returns them."""
+    ref = oracle.OracleEngine(cfg, Wn, kv_mode=kv_mode)
+    out = [ref.forward_logits(ids, True)]
+    fed = []
+    for s in range(steps):
+        tok = int(oracle.argmax(out[-1])) if tokens is None else int(tokens[s])
+        fed.append(tok)
+        out.append(ref.forward_logits([tok], True))
+    return np.stack(out), np.array(fed, np.uint32)
+
+
+def _cuda_run(cfg, Wn, ids, tokens, reference_cache):
+    eng = ForwardEngine.from_weights(cfg, Wn, max_tokens=256)
     eng.set_kv_rounding(reference_cache)
-    ref = oracle.OracleEngine(cfg, Wn, kv_mode=0 if reference_cache else 1)
-    got, want = eng.forward_logits(ids, True), ref.forward_logits(ids, True)
-    worst = float(np.abs(got - want).max())
-    agree = exact = 0
-    tok = int(oracle.argmax(want))
-    for _ in range(steps):
-        got, want = eng.forward_logits([tok], True), ref.forward_logits([tok], True)
-        worst = max(worst, float(np.abs(got - want).max()))
-        pick, ref_pick = int(oracle.argmax(got)), int(oracle.argmax(want))
-        exact += int(pick == ref_pick)
-        agree += int(pick == ref_pick or want.max() - want[pick] <= MARGIN)
-        tok = ref_pick  # teacher forcing
+    out = [eng.forward_logits(ids, True)]
+    for tok in tokens:
+        out.append(eng.forward_logits([int(tok)], True))
     eng.close()
-    return worst, exact, agree
+    return np.stack(out)
 
 
-@pytest.mark.parametrize("name,prompt_len,steps,ref_logit_bar", [("qwen05b", 48, 24, 0.05), ("llama8b", 16, 6, 0.25)])
-def test_full_size_model_logits_and_greedy_agreement(oracle, name, prompt_len, steps, ref_logit_bar):
+def _picks(oracle, logits):
+    return np.array([oracle.argmax(row) for row in logits])
+
+
+def _compare(oracle, got, want):
+    """(worst |dlogit|, rms dlogit, exact greedy agreements over the decode steps, median top-2 gap of `want`)."""
+    d = got.astype(np.float64) - want.astype(np.float64)
+    exact = int((_picks(oracle, got[:-1]) == _picks(oracle, want[:-1])).sum())  # row s chooses the token of step s
+    top2 = np.partition(want[:-1], -2, axis=1)[:, -2:]
+    return float(np.abs(d).max()), float(np.sqrt((d * d).mean())), exact, float(np.median(top2[:, 1] - top2[:, 0]))
+
+
+def _report(rec):
+    print(json.dumps(rec))
+    path = os.environ.get("SAPIENT_PARITY_REPORT")
+    if path:
+        with open(path, "a") as f:
+            f.write(json.dumps(rec) + "\n")
+
+
+@pytest.mark.parametrize("name,prompt_len,steps", CASES)
+def test_full_size_model_logits_and_greedy_agreement(oracle, name, prompt_len, steps):
     import torch
 
-    cfg, W = synth.build_model(synth.CONFIGS[name], seed=3000, device="cuda", max_ctx=256)
+    cfg, W = synth.build_model(synth.CONFIGS[name], seed=3000, device="cuda", max_ctx=512)
     Wn = synth.weights_to_numpy(W)
     del W
     torch.cuda.empty_cache()
     ids = np.random.default_rng(0).integers(0, cfg["vocab"], prompt_len).astype(np.uint32)
-    need = int(np.ceil(0.99 * steps))
-    worst, exact, agree = _run(oracle, cfg, Wn, ids, steps, reference_cache=False)
-    print(f"{name} fp16 cache both sides: worst |dlogit| = {worst:.2e}, exact top-1 {exact}/{steps}, within-margin {agree}/{steps}")
+    need = int(np.ceil(AGREE * steps))
+
+    # ── kernels: continuous (fp16) cache rounding on both sides ──
+    want, toks = _oracle_run(oracle, cfg, Wn, ids, steps, kv_mode=1)
+    got = _cuda_run(cfg, Wn, ids, toks, reference_cache=False)
+    worst, rms, exact, gap = _compare(oracle, got, want)
+    _report({"model": name, "prompt": prompt_len, "steps": steps, "cache": "fp16 both sides", "worst_dlogit": worst, "rms_dlogit": rms,
+             "exact_top1": exact, "median_top2_gap": gap, "logit_std": float(want.std())})
     assert worst < LOGIT_BAR, worst
-    assert agree >= need, (agree, steps)
-    worst, exact, agree = _run(oracle, cfg, Wn, ids, steps, reference_cache=True)
-    print(f"{name} reference Q8_0 cache: worst |dlogit| = {worst:.2e}, exact top-1 {exact}/{steps}, within-margin {agree}/{steps}")
-    assert worst < ref_logit_bar, worst
-    assert agree >= need, (agree, steps)
+    assert exact >= need, (exact, steps)
+
+    # ── the reference's configuration: Q8_0 cache in the oracle, the same rounding before the engine's fp16 store ──
+    want, toks = _oracle_run(oracle, cfg, Wn, ids, steps, kv_mode=0)
+    try:
+        oracle.set_kquant_order(1)
+        oracle.set_q8_mode(1)
+        other, _ = _oracle_run(oracle, cfg, Wn, ids, steps, kv_mode=0, tokens=toks)
+    finally:
+        oracle.set_kquant_order(0)
+        oracle.set_q8_mode(0)
+    self_worst, self_rms, self_exact, _ = _compare(oracle, other, want)
+    got = _cuda_run(cfg, Wn, ids, toks, reference_cache=True)
+    worst, rms, exact, gap = _compare(oracle, got, want)
+    _report({"model": name, "prompt": prompt_len, "steps": steps, "cache": "reference (Q8_0 where head_dim % 32 == 0)", "worst_dlogit": worst,
+             "rms_dlogit": rms, "exact_top1": exact, "oracle_reordered_worst_dlogit": self_worst, "oracle_reordered_rms_dlogit": self_rms,
+             "oracle_reordered_exact_top1": self_exact, "median_top2_gap": gap})
+    assert worst <= max(LOGIT_BAR, SELF_FACTOR * self_worst), (worst, self_worst)
+    assert exact >= min(need, self_exact), (exact, self_exact, steps)

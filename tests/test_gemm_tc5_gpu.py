@@ -72,3 +72,22 @@ def test_large_m_gemm_quantised_gaussian_weights(oracle):
     got = ops.matmul_nt(x, raw, Q4_K, n)
     want = oracle.matmul_nt(x, raw, Q4_K, n)
     assert rel_l2(got, want) < 5e-4
+
+
+@pytest.mark.parametrize("dtype,m,k,n", [(Q4_K, 64, 4096, 1024), (Q6_K, 200, 2048, 640), (Q8_0, 32, 4096, 300)])
+def test_split_last_wave_is_reproducible_bit_for_bit(oracle, dtype, m, k, n):
+    """Grids smaller than the GPU split each weight tile's K range over several CTAs. Their partial tiles are summed in
+    part order by the last CTA to arrive, so repeated calls give identical bits (an atomic-add tail would not), and
+    the result still meets the operator bar."""
+    be, _ = synth.BLOCK[dtype]
+    rng = np.random.default_rng(m + k + n)
+    raw = synth.random_bit_blocks(dtype, n * k // be, seed=k + n + dtype)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    w = ops.Weight(dtype, n, k, raw)
+    try:
+        runs = [w.matmul_nt(x) for _ in range(6)]
+    finally:
+        w.free()
+    for r in runs[1:]:
+        assert np.array_equal(r.view(np.uint32), runs[0].view(np.uint32))
+    assert rel_l2(runs[0], oracle.matmul_nt(x, raw, dtype, n)) < 5e-4

@@ -219,3 +219,36 @@ def test_synth_quantisers_roundtrip(oracle, dtype):
     err = np.abs(back - w.numpy()).max()
     tol = {Q4_K: 0.02 * 6 / 15, Q6_K: 0.02 * 6 / 31, Q8_0: 0.02 * 6 / 127}[dtype]
     assert err < tol, err
+
+
+@pytest.mark.parametrize("dtype,block_bytes", [(12, 144), (14, 210)])
+def test_rows_at_once_matmul_is_bit_identical_to_the_row_by_row_loop(oracle, dtype, block_bytes):
+    """The tests run the oracle's K-quant matmul eight rows at a time (one row per SIMD lane, each lane the scalar
+    operation sequence of kernels/quant.rs:625-652 / 2573-2613); the timing runs keep the reference's one-row loop.
+    Both must give the same bits, also for row counts that leave a remainder."""
+    rng = np.random.default_rng(5)
+    n, k = 67, 1024
+    w = rng.integers(0, 256, n * k // 256 * block_bytes, dtype=np.uint8).reshape(-1, block_bytes)
+    d = np.frombuffer(np.float16(rng.uniform(1e-3, 1e-2, len(w))).tobytes(), np.uint8).reshape(-1, 2)
+    if dtype == 12:
+        w[:, 0:2] = d
+        w[:, 2:4] = d[::-1]
+    else:
+        w[:, 208:210] = d
+    x = rng.standard_normal((3, k)).astype(np.float32)
+    try:
+        oracle.set_rows_at_once(False)
+        want = oracle.matmul_nt(x, w, dtype, n)
+        oracle.set_rows_at_once(True)
+        got = oracle.matmul_nt(x, w, dtype, n)
+    finally:
+        oracle.set_rows_at_once(True)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    # the second evaluation order differs in rounding only
+    try:
+        oracle.set_kquant_order(1)
+        alt = oracle.matmul_nt(x, w, dtype, n)
+    finally:
+        oracle.set_kquant_order(0)
+    assert not np.array_equal(alt.view(np.uint32), want.view(np.uint32))
+    assert np.abs(alt - want).max() <= 1e-5 * np.abs(want).max()
