@@ -74,9 +74,19 @@ int32_t sp_cuda_matmul_nt_dev(const SpWeight* w, const float* x_dev, int64_t m, 
  * The reference's GPU backend has no such condition to report (its wgpu queue has no device-side waits,
  * crates/sapient-backends/wgpu/src/context.rs); this is the error channel of the asynchronous device-pointer calls. */
 int32_t sp_cuda_check_kernels(int32_t device);
-/* Which GEMV kernel runs: 0 (default) and 2: tensor-core GEMV on tile-repacked weights, one CTA per 16-row tile row;
- * 1: the CUDA-core GEMV on the raw blocks (op-level calls only; an independent second implementation for
- * cross-checks); 3: tensor-core GEMV, persistent TMA-streaming kernel where the shape qualifies. Process-wide. */
+/* Precision of the activations in the tensor-core GEMV passes (steps that do not take the 17+-row GEMM). The reference
+ * multiplies f32 activations (kernels/matmul.rs:862-943); this backend splits each activation into int8 digits with one
+ * power-of-two scale per 256 (Q8_0: 32) columns. 0 (default): three digits (2^-23 of the block maximum) for steps of
+ * 1-2 rows, two digits (2^-15) and 16 rows per pass above. 1: three digits always, 10 rows per pass. Process-wide;
+ * engines drop their captured step graphs when it changes (sp_cuda_engine_set_graphs off/on). */
+int32_t sp_cuda_set_activation_digits(int32_t mode);
+/* Which GEMV kernel runs (process-wide; op-level calls — engines have sp_cuda_engine_set_ring):
+ *   0 (default): calls of 1-4 rows take the persistent ring GEMV (shared-memory ring fed by bulk copies, activation
+ *      digits built inside the kernel) where the shape fits, everything else the tensor-core GEMV with one CTA per
+ *      16-row tile row;
+ *   2: always the tile-row kernel;
+ *   1: the CUDA-core GEMV on the raw blocks (an independent second implementation for cross-checks);
+ *   3: the per-warp streaming variant of the tile-row kernel where the shape qualifies. */
 int32_t sp_cuda_set_gemv_path(int32_t path);
 /* 1 (default): op-level matmuls with m >= 17 rows and k % 256 == 0 (Q8_0: k % 128 == 0) run the tcgen05 / TMEM dequant GEMM; 0: always the
  * 16-row GEMV passes (for cross-checks and timing comparisons). Process-wide; engines have their own switch. */
@@ -204,6 +214,13 @@ int32_t sp_cuda_decode_greedy(SpEngine* e, const uint32_t* first_ids, const int3
 int32_t sp_cuda_engine_synchronize(SpEngine* e);
 /* Replay decode steps as CUDA graphs (default on). */
 int32_t sp_cuda_engine_set_graphs(SpEngine* e, int32_t on);
+/* Steps of 17 rows and more (prefill chunks, batched decode) on the tcgen05 GEMM, whose operands are rounded to fp16
+ * (default on; off: tensor-core GEMV passes on integer digits, slower, closer to the reference's f32 arithmetic — see
+ * sp_cuda_set_activation_digits). Drops the captured step graphs. */
+int32_t sp_cuda_engine_set_large_m_gemm(SpEngine* e, int32_t on);
+/* Steps of 1-4 rows on the persistent ring GEMV with the preceding norm / activation fused into it (default on; off: the
+ * tile-row GEMV with separate norm / activation kernels). Drops the captured step graphs. */
+int32_t sp_cuda_engine_set_ring(SpEngine* e, int32_t on);
 /* Per-kernel-family device timing (CUDA events around every launch; disables graphs while on). Families, in order:
  * gemv, attention, norm, rope_kv, elementwise, embed, argmax. Returns the family count; ms/launches accumulate
  * until reset (reset != 0 clears after reading). */

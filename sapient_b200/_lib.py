@@ -46,6 +46,7 @@ SIGNATURES = {
     "sp_cuda_matmul_nt_dev": (_i32, [_vp, _vp, _i64, _vp, _vp]),
     "sp_cuda_check_kernels": (_i32, [_i32]),
     "sp_cuda_set_gemv_path": (_i32, [_i32]),
+    "sp_cuda_set_activation_digits": (_i32, [_i32]),
     "sp_cuda_weight_info": (_i32, [_vp, C.POINTER(_i32), C.POINTER(_i64), C.POINTER(_i64), C.POINTER(_sz)]),
     "sp_cuda_rms_norm": (_i32, [_i32, _vp, _vp, _i64, _i64, _f, _vp]),
     "sp_cuda_layer_norm": (_i32, [_i32, _vp, _vp, _vp, _i64, _i64, _f, _vp]),
@@ -82,6 +83,8 @@ SIGNATURES = {
     "sp_cuda_decode_greedy": (_i32, [_vp, _vp, _vp, _i32, _i32, _vp]),
     "sp_cuda_engine_synchronize": (_i32, [_vp]),
     "sp_cuda_engine_set_graphs": (_i32, [_vp, _i32]),
+    "sp_cuda_engine_set_ring": (_i32, [_vp, _i32]),
+    "sp_cuda_engine_set_large_m_gemm": (_i32, [_vp, _i32]),
     "sp_cuda_engine_set_profile": (_i32, [_vp, _i32]),
     "sp_cuda_engine_profile_read": (_i32, [_vp, _vp, _vp, _i32, _i32]),
     "sp_cuda_engine_time_families": (_i32, [_vp, C.c_uint32, _i32, _i32, C.POINTER(C.c_float)]),

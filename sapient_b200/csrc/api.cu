@@ -21,6 +21,7 @@ struct SpWeight {
     size_t nbytes;
     uint8_t* tiled = nullptr;  // tile-repacked copy for the tensor-core GEMV (quantised types)
     ActWorkspace ws;           // activation digits for up to 16 rows
+    RingScratch ring;          // shared-row scratch of the ring GEMV (calls of 1-4 rows)
 };
 struct SpEngine {
     Engine* e;
@@ -31,6 +32,7 @@ int sp_engine_from_gguf_impl(const char* path, int device, int max_ctx, int max_
 namespace {
 
 std::atomic<int> g_gemv_path{0};  // 0: tensor-core GEMV on tiled weights; 1: CUDA-core GEMV on raw blocks
+std::atomic<int> g_ring{1};       // calls of 1-4 rows on the persistent ring GEMV where it fits
 
 #define API_BEGIN try {
 #define API_END                                                     \
@@ -209,9 +211,16 @@ int32_t sp_cuda_set_large_m_gemm(int32_t on) {
     return SP_OK;
 }
 
+int32_t sp_cuda_set_activation_digits(int32_t mode) {
+    if (mode < 0 || mode > 1) { set_error("activation digit mode must be 0 or 1"); return SP_ERR_ARG; }
+    imma_set_digit_mode(mode);
+    return SP_OK;
+}
+
 int32_t sp_cuda_set_gemv_path(int32_t path) {
     if (path < 0 || path > 3) { set_error("gemv path must be 0..3"); return SP_ERR_ARG; }
     g_gemv_path.store(path == 1 ? 1 : 0);
+    g_ring.store(path == 0 ? 1 : 0);
     imma_select_kernel(path == 3 ? 3 : 0);
     return SP_OK;
 }
@@ -231,12 +240,15 @@ int32_t sp_cuda_upload_weight(int32_t device, int32_t dtype, int64_t n, int64_t 
         if (ce == cudaSuccess) ce = launch_repack(dtype, w->d, n, k, w->tiled, 0);
         if (ce == cudaSuccess) ce = cudaStreamSynchronize(0);
         if (ce == cudaSuccess) ce = w->ws.alloc((int)k);
+        if (ce == cudaSuccess) ce = ring_device_init();
+        if (ce == cudaSuccess) ce = w->ring.alloc((int)((n + 15) / 16));
     }
     if (ce != cudaSuccess) {
         set_error(std::string("upload_weight: ") + cudaGetErrorString(ce));
         if (w->d) cudaFree(w->d);
         if (w->tiled) cudaFree(w->tiled);
         w->ws.release();
+        w->ring.release();
         delete w;
         return ce == cudaErrorMemoryAllocation ? SP_ERR_OOM : SP_ERR_CUDA;
     }
@@ -251,6 +263,7 @@ void sp_cuda_free_weight(SpWeight* w) {
     cudaFree(w->d);
     if (w->tiled) cudaFree(w->tiled);
     w->ws.release();
+    w->ring.release();
     delete w;
 }
 
@@ -288,10 +301,21 @@ int32_t sp_cuda_matmul_nt_dev(const SpWeight* w, const float* x_dev, int64_t m, 
                                     (cudaStream_t)stream, &wm->ws.tc5));
         return SP_OK;
     }
+    if (w->tiled && g_gemv_path.load() == 0 && g_ring.load() && m >= 1 && m <= 4) {
+        RingArgs ra{};
+        ra.nseg = 1;
+        ra.seg[0].wt = w->tiled; ra.seg[0].y = y_dev; ra.seg[0].dtype = w->dtype; ra.seg[0].n = (int)w->n; ra.seg[0].ldy = (int)w->n; ra.seg[0].bpt = 8;
+        ra.k = (int)w->k; ra.m = (int)m; ra.src = RING_SRC_PLAIN; ra.x = x_dev; ra.ldx = (int)w->k;
+        if (ring_plan(ra, w->ring)) {
+            SP_CUDA_TRY(launch_gemv_ring(ra, (cudaStream_t)stream));
+            return SP_OK;
+        }
+    }
     if (w->tiled && g_gemv_path.load() == 0) {
-        for (int64_t m0 = 0; m0 < m; m0 += 16) {
+        const int pass = imma_rows_per_pass();
+        for (int64_t m0 = 0; m0 < m; m0 += pass) {
             ImmaArgs ia{};
-            ia.k = (int)w->k; ia.m = (int)std::min<int64_t>(16, m - m0); ia.nseg = 1;
+            ia.k = (int)w->k; ia.m = (int)std::min<int64_t>(pass, m - m0); ia.nseg = 1;
             ia.seg[0].wt = w->tiled; ia.seg[0].y = y_dev + m0 * w->n; ia.seg[0].dtype = w->dtype; ia.seg[0].n = (int)w->n;
             ia.seg[0].ldy = (int)w->n; ia.seg[0].bpt = imma_q8_bpt(w->k);
             SP_CUDA_TRY(launch_quant_gemv(x_dev + m0 * w->k, (int)w->k, ia, w->ws, true, (cudaStream_t)stream));
@@ -635,6 +659,26 @@ int32_t sp_cuda_engine_set_graphs(SpEngine* e, int32_t on) {
     if (!e) { set_error("null engine"); return SP_ERR_ARG; }
     e->e->use_graphs = on != 0;
     return SP_OK;
+}
+
+int32_t sp_cuda_engine_set_large_m_gemm(SpEngine* e, int32_t on) {
+    API_BEGIN
+    if (!e) { set_error("null engine"); return SP_ERR_ARG; }
+    SP_CUDA_TRY(cudaSetDevice(e->e->d.device));
+    e->e->use_tc5 = on != 0;
+    e->e->drop_graphs();
+    return SP_OK;
+    API_END
+}
+
+int32_t sp_cuda_engine_set_ring(SpEngine* e, int32_t on) {
+    API_BEGIN
+    if (!e) { set_error("null engine"); return SP_ERR_ARG; }
+    SP_CUDA_TRY(cudaSetDevice(e->e->d.device));
+    e->e->use_ring = on != 0;
+    e->e->drop_graphs();  // captured steps hold the old kernel sequence
+    return SP_OK;
+    API_END
 }
 
 int32_t sp_cuda_engine_set_profile(SpEngine* e, int32_t on) {

@@ -149,6 +149,8 @@ attention_split_kernel(const float* __restrict__ q, int ldq, float* __restrict__
 
 __global__ void attention_merge_kernel(const float* __restrict__ part, int n_heads, int n_splits, int hd, float* __restrict__ out,
                                        int ldo) {
+    pdl_wait();
+    pdl_trigger();
     const int h = blockIdx.x, t = blockIdx.y;
     const float* src = part + ((int64_t)t * n_heads + h) * n_splits * (hd + 2);
     float M = -INFINITY;
@@ -193,7 +195,8 @@ cudaError_t launch_attention(const float* q, int ldq, float* out, int ldo, int n
     if (le != cudaSuccess) return le;
     cudaError_t e = count_launch_and_check();
     if (e != cudaSuccess || n_splits == 1) return e;
-    attention_merge_kernel<<<dim3(n_heads, n_tok), 128, 0, st>>>(scratch, n_heads, n_splits, kv.head_dim, out, ldo);
+    le = launch_pdl(attention_merge_kernel, dim3(n_heads, n_tok), dim3(128), 0, st, (const float*)scratch, n_heads, n_splits, kv.head_dim, out, ldo);
+    if (le != cudaSuccess) return le;
     return count_launch_and_check();
 }
 

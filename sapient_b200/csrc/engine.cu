@@ -59,6 +59,7 @@ Engine::~Engine() {
     ws_.release();
     tp_release();
     if (att_scratch_) cudaFree(att_scratch_);
+    ring_.release();
     for (void* p : owned_) cudaFree(p);
     void* bufs[] = {kv_.pool, d_page_table_, x_, h_, qkv_, attn_, gu_, mid_, sel_, logits_, trace_, d_ids_, d_argmax_,
                     d_tok_slot_, d_tok_pos_, cos_sin_};
@@ -174,6 +175,12 @@ int Engine::repack_weights() {
     }
     SP_CUDA_TRY(ws_.alloc(kmax));
     if (d.max_tokens >= TC5_MIN_M) SP_CUDA_TRY(ws_.ensure_xh((size_t)d.max_tokens * kmax));
+    {
+        // tile rows of the widest launch: q|k|v, gate|up (two segments), lm_head
+        const int64_t widest = std::max<int64_t>({(int64_t)d.vocab, 2 * (int64_t)d.ffn, (int64_t)(d.n_heads + 2 * d.n_kv_heads) * d.head_dim, (int64_t)d.hidden});
+        SP_CUDA_TRY(ring_device_init());
+        SP_CUDA_TRY(ring_.alloc((int)(widest / 16 + 8)));
+    }
     return SP_OK;
 }
 

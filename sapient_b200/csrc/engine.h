@@ -93,6 +93,7 @@ class Engine {
     bool finalized = false;
     bool trace_on = false;
     bool use_graphs = true;
+    bool use_ring = true;      // steps of 1-4 rows on the persistent ring GEMV (false: always the tile-row kernel)
     bool use_tc5 = true;       // steps of TC5_MIN_M rows and more on the tcgen05 GEMM (false: always 16-row GEMV passes)
     bool graph_step_ = false;  // a step is being captured: its kernels may take positions only from device memory
     // 1 (default): new K / V rows get the reference's Q8_0 cache rounding before they are stored as fp16 (head_dim % 32
@@ -123,6 +124,13 @@ class Engine {
              bool tp_sum = false);
     // Many-row steps on one GPU: the producers (norm, attention, activation) write fp16 rows straight into the GEMM's
     // input buffer; big_m says whether these matrices take that path, gemm_xh multiplies what the buffer holds.
+    // Steps of 1-4 rows on one GPU: the persistent ring GEMV (gemv_ring.cu) with the preceding norm / activation applied
+    // inside it. SP_OK with *done = true when it was launched, *done = false when the launch does not qualify (the
+    // caller then takes the tile-row kernel and its separate producers).
+    int try_ring(bool* done, int m, int k, int src, const float* x, int ldx, const float* nw, const float* nb, const DevTensor* w0,
+                 const float* b0, float* y0, int ldy, const DevTensor* w1 = nullptr, const float* b1 = nullptr, float* y1 = nullptr,
+                 const DevTensor* w2 = nullptr, const float* b2 = nullptr, float* y2 = nullptr, const float* res = nullptr);
+    RingScratch ring_;
     bool big_m(int m, int k, const DevTensor* w0, const DevTensor* w1 = nullptr, const DevTensor* w2 = nullptr) const;
     int gemm_xh(int m, int k, const DevTensor* w0, const float* b0, float* y0, int ldy0, const DevTensor* w1 = nullptr,
                 const float* b1 = nullptr, float* y1 = nullptr, const DevTensor* w2 = nullptr, const float* b2 = nullptr,

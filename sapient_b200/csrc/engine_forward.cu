@@ -98,6 +98,16 @@ int Engine::enqueue_decode_step(int T) {
     const int hid = d.hidden;
     SP_TRY(enqueue_layers(T));
     ImmaArgs ia;
+    {
+        DevTensor head = *lm_head_;
+        head.dims[0] = vocab_l_;
+        bool ringed = false;
+        SP_TRY(try_ring(&ringed, T, hid, d.arch == 1 ? RING_SRC_LN : RING_SRC_RMS, x_, hid, final_w_, final_b_, &head, lm_bias_, logits_, vocab_l_));
+        if (ringed) {
+            SP_LAUNCH(F_ARGMAX, launch_argmax(logits_, T, vocab_l_, vocab_l_, d_argmax_, stream));
+            return SP_OK;
+        }
+    }
     if (lm_head_->tiled && plan_digits(T, hid, ia)) {
         SP_LAUNCH(F_NORM, launch_norm_quant(x_, hid, final_w_, final_b_, d.arch == 1, d.norm_eps, nullptr, 0, ia, stream, tp_take()));
         return enqueue_head(0, 0, T, &ia);

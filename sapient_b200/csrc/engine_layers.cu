@@ -42,7 +42,7 @@ bool Engine::plan_digits(int m, int k, ImmaArgs& ia) {
     ia = ImmaArgs{};
     ia.m = m;
     ia.k = k;
-    if (m > 16 || k > ws_.k_max) return false;
+    if (m > imma_rows_per_pass() || k > ws_.k_max) return false;
     imma_plan(ia, ws_);
     return true;
 }
@@ -74,10 +74,11 @@ int Engine::gemv(const float* x, int ldx, int m, int k, const DevTensor* w0, con
     }
     if (tiled) {
         // tensor-core path: digits of up to 16 activation rows at a time, all segments share them
-        for (int m0 = 0; m0 < m; m0 += 16) {
+        const int pass = imma_rows_per_pass();
+        for (int m0 = 0; m0 < m; m0 += pass) {
             ImmaArgs ia{};
             if (pre) ia = *pre;
-            ia.k = k; ia.m = std::min(16, m - m0);
+            ia.k = k; ia.m = std::min(pass, m - m0);
             ia.res = (res && !tp_sum) ? res + (size_t)m0 * ldy0 : nullptr;
             ia.ldres = ldy0;
             ia.tp = tp_sum ? d_tp_ : nullptr;
@@ -124,6 +125,27 @@ int Engine::gemv(const float* x, int ldx, int m, int k, const DevTensor* w0, con
     return SP_OK;
 }
 
+int Engine::try_ring(bool* done, int m, int k, int src, const float* x, int ldx, const float* nw, const float* nb, const DevTensor* w0,
+                     const float* b0, float* y0, int ldy, const DevTensor* w1, const float* b1, float* y1, const DevTensor* w2,
+                     const float* b2, float* y2, const float* res) {
+    *done = false;
+    if (!use_ring || d.tp_size > 1 || trace_on || m > 4) return SP_OK;
+    const DevTensor* ws[3] = {w0, w1, w2};
+    const float* bs[3] = {b0, b1, b2};
+    float* ys[3] = {y0, y1, y2};
+    RingArgs ra{};
+    for (int i = 0; i < 3 && ws[i]; ++i) {
+        if (!ws[i]->tiled) return SP_OK;
+        ImmaSeg& sg = ra.seg[ra.nseg++];
+        sg.wt = ws[i]->tiled; sg.bias = bs[i]; sg.y = ys[i]; sg.dtype = ws[i]->dtype; sg.n = (int)ws[i]->dims[0]; sg.ldy = ldy; sg.bpt = 8;
+    }
+    ra.k = k; ra.m = m; ra.src = src; ra.x = x; ra.ldx = ldx; ra.nw = nw; ra.nb = nb; ra.eps = d.norm_eps; ra.res = res; ra.ldres = ldy;
+    if (!ring_plan(ra, ring_)) return SP_OK;
+    SP_LAUNCH(F_GEMV, launch_gemv_ring(ra, stream));
+    *done = true;
+    return SP_OK;
+}
+
 bool Engine::big_m(int m, int k, const DevTensor* w0, const DevTensor* w1, const DevTensor* w2) const {
     if (m < TC5_MIN_M || !use_tc5 || d.tp_size > 1 || !ws_.xh || (size_t)m * k > ws_.xh_elems) return false;
     const DevTensor* ws[3] = {w0, w1, w2};
@@ -157,8 +179,17 @@ int Engine::attention_and_oproj(const LayerW& w, int l, int T) {
     // rows, fewer as the rows grow, not at all from 17 rows on (measured on the 8B shape at context 300: 16 rows 0.89 ms
     // of attention per step with 4 splits against 1.37 with 16; 32 rows 0.54 ms unsplit against 2.34).
     int splits = 1;
-    if (T <= 16) splits = H * T <= 64 ? ATT_SPLITS : H * T <= 128 ? 8 : 4;
+    if (T <= imma_rows_per_pass()) splits = H * T <= 64 ? ATT_SPLITS : H * T <= 128 ? 8 : 4;
     ImmaArgs ia;
+    if (splits > 1 && use_ring && d.tp_size == 1 && !trace_on && T <= 4 && all_tiled(w.o)) {
+        // split-K attention merged to f32 rows; the output projection quantises them itself
+        SP_LAUNCH(F_ATTN, launch_attention(qkv_, qkv_ld, attn_, H * hd, T, H, d_tok_slot_, d_tok_pos_, kv_, l, scale, splits, att_scratch_, stream));
+        bool done = false;
+        SP_TRY(try_ring(&done, T, H * hd, RING_SRC_PLAIN, attn_, H * hd, nullptr, nullptr, w.o, w.ob, x_, hid, nullptr, nullptr, nullptr, nullptr,
+                        nullptr, nullptr, x_));
+        if (done) return SP_OK;
+        return gemv(attn_, H * hd, T, H * hd, w.o, w.ob, x_, hid, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, x_, nullptr, true);
+    }
     if (splits > 1 && !trace_on && all_tiled(w.o) && plan_digits(T, H * hd, ia)) {
         SP_LAUNCH(F_ATTN, launch_attention_split(qkv_, qkv_ld, T, H, d_tok_slot_, d_tok_pos_, kv_, l, scale, splits, att_scratch_, stream));
         SP_LAUNCH(F_ATTN, launch_attn_merge_quant(att_scratch_, H, splits, hd, nullptr, 0, ia, stream));
@@ -185,7 +216,11 @@ int Engine::layer_llama(const LayerW& w, int l, int T) {
     const int H = d.n_heads, Hkv = d.n_kv_heads, hd = d.head_dim, hid = d.hidden, ffn = d.ffn;
     const int qkv_ld = (H + 2 * Hkv) * hd;
     ImmaArgs ia;
-    if (big_m(T, hid, w.q, w.k, w.v)) {
+    bool ringed = false;
+    SP_TRY(try_ring(&ringed, T, hid, RING_SRC_RMS, x_, hid, w.n1w, nullptr, w.q, w.qb, qkv_, qkv_ld, w.k, w.kb, qkv_ + (size_t)H * hd, w.v, w.vb,
+                    qkv_ + (size_t)(H + Hkv) * hd));
+    if (ringed) {
+    } else if (big_m(T, hid, w.q, w.k, w.v)) {
         SP_LAUNCH(F_NORM, launch_rms_norm_f16(x_, w.n1w, T, hid, d.norm_eps, ws_.xh, stream));
         SP_TRY(gemm_xh(T, hid, w.q, w.qb, qkv_, qkv_ld, w.k, w.kb, qkv_ + (size_t)H * hd, w.v, w.vb, qkv_ + (size_t)(H + Hkv) * hd));
     } else if (all_tiled(w.q, w.k, w.v) && plan_digits(T, hid, ia)) {
@@ -200,7 +235,9 @@ int Engine::layer_llama(const LayerW& w, int l, int T) {
     }
     SP_LAUNCH(F_ROPE, launch_rope_kv_append(qkv_, T, H, Hkv, hd, d.rotary_dim, cos_sin_, d_tok_slot_, d_tok_pos_, kv_, l, kv_round, stream));
     SP_TRY(attention_and_oproj(w, l, T));
-    if (big_m(T, hid, w.gate, w.up)) {
+    SP_TRY(try_ring(&ringed, T, hid, RING_SRC_RMS, x_, hid, w.n2w, nullptr, w.gate, nullptr, gu_, 2 * ffn, w.up, nullptr, gu_ + ffn));
+    if (ringed) {
+    } else if (big_m(T, hid, w.gate, w.up)) {
         SP_LAUNCH(F_NORM, launch_rms_norm_f16(x_, w.n2w, T, hid, d.norm_eps, ws_.xh, stream));
         SP_TRY(gemm_xh(T, hid, w.gate, nullptr, gu_, 2 * ffn, w.up, nullptr, gu_ + ffn));
     } else if (all_tiled(w.gate, w.up) && plan_digits(T, hid, ia)) {
@@ -211,7 +248,10 @@ int Engine::layer_llama(const LayerW& w, int l, int T) {
         SP_LAUNCH(F_NORM, launch_rms_norm(x_, w.n2w, T, hid, d.norm_eps, h_, stream));
         SP_TRY(gemv(h_, hid, T, hid, w.gate, nullptr, gu_, 2 * ffn, w.up, nullptr, gu_ + ffn));
     }
-    if (big_m(T, ffn, w.down)) {
+    SP_TRY(try_ring(&ringed, T, ffn, RING_SRC_SWIGLU, gu_, 2 * ffn, nullptr, nullptr, w.down, nullptr, x_, hid, nullptr, nullptr, nullptr, nullptr, nullptr,
+                    nullptr, x_));
+    if (ringed) {
+    } else if (big_m(T, ffn, w.down)) {
         SP_LAUNCH(F_ELEM, launch_act_f16(gu_, 2 * ffn, ffn, T, 0, ws_.xh, stream));
         SP_TRY(gemm_xh(T, ffn, w.down, nullptr, x_, hid, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, x_));
     } else if (all_tiled(w.down) && plan_digits(T, ffn, ia)) {
@@ -229,7 +269,17 @@ int Engine::layer_phi(const LayerW& w, int l, int T) {
     const int qkv_ld = (H + 2 * Hkv) * hd;
     // parallel block: x + (attn_out + mlp(h)); both branches read the same normalised input h
     ImmaArgs ia;
-    if (big_m(T, hid, w.q, w.k, w.v) && big_m(T, hid, w.up)) {
+    bool ringed = false, ringed2 = false;
+    SP_TRY(try_ring(&ringed, T, hid, RING_SRC_LN, x_, hid, w.n1w, w.n1b, w.q, w.qb, qkv_, qkv_ld, w.k, w.kb, qkv_ + (size_t)H * hd, w.v, w.vb,
+                    qkv_ + (size_t)(H + Hkv) * hd));
+    if (ringed) SP_TRY(try_ring(&ringed2, T, hid, RING_SRC_LN, x_, hid, w.n1w, w.n1b, w.up, w.upb, gu_, ffn));
+    if (ringed && !ringed2) {
+        // fc1 does not fit the ring kernel: the separate norm feeds it
+        SP_LAUNCH(F_NORM, launch_layer_norm(x_, w.n1w, w.n1b, T, hid, d.norm_eps, h_, stream));
+        SP_TRY(gemv(h_, hid, T, hid, w.up, w.upb, gu_, ffn));
+    }
+    if (ringed) {
+    } else if (big_m(T, hid, w.q, w.k, w.v) && big_m(T, hid, w.up)) {
         SP_LAUNCH(F_NORM, launch_layer_norm_f16(x_, w.n1w, w.n1b, T, hid, d.norm_eps, ws_.xh, stream));
         SP_TRY(gemm_xh(T, hid, w.q, w.qb, qkv_, qkv_ld, w.k, w.kb, qkv_ + (size_t)H * hd, w.v, w.vb, qkv_ + (size_t)(H + Hkv) * hd));
         SP_TRY(gemm_xh(T, hid, w.up, w.upb, gu_, ffn));
@@ -247,7 +297,10 @@ int Engine::layer_phi(const LayerW& w, int l, int T) {
     SP_LAUNCH(F_ROPE, launch_rope_kv_append(qkv_, T, H, Hkv, hd, d.rotary_dim, cos_sin_, d_tok_slot_, d_tok_pos_, kv_, l, kv_round, stream));
     // the MLP's fc1 output waits in gu_ while the workspace serves the attention output projection
     SP_TRY(attention_and_oproj(w, l, T));
-    if (big_m(T, ffn, w.down)) {
+    SP_TRY(try_ring(&ringed, T, ffn, RING_SRC_GELU, gu_, ffn, nullptr, nullptr, w.down, w.downb, x_, hid, nullptr, nullptr, nullptr, nullptr, nullptr,
+                    nullptr, x_));
+    if (ringed) {
+    } else if (big_m(T, ffn, w.down)) {
         SP_LAUNCH(F_ELEM, launch_act_f16(gu_, ffn, ffn, T, 1, ws_.xh, stream));
         SP_TRY(gemm_xh(T, ffn, w.down, w.downb, x_, hid, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, x_));
     } else if (all_tiled(w.down) && plan_digits(T, ffn, ia)) {

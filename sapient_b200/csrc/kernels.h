@@ -57,10 +57,57 @@ cudaError_t launch_gemv_imma(const ImmaArgs& a, cudaStream_t st);
 // 0: the one-CTA-per-tile-row kernel; 3: the persistent TMA-streaming kernel when k % 256 == 0 and the digits fit
 // shared memory.
 void imma_select_kernel(int which);
+// Activation precision of the tensor-core GEMV passes (process-wide): 0 = 3 digits for 1-2 rows, 2 digits (16 rows per
+// pass) above; 1 = 3 digits always (10 rows per pass). imma_rows_per_pass() is the pass size that follows.
+void imma_set_digit_mode(int mode);
+int imma_rows_per_pass();
 // Bounded device-side waits (mbarrier waits of the streaming GEMV and of the tcgen05 GEMM) raise a per-device flag when
 // they run out. These read and clear it on the current device: 1 = expired since the last call, 0 = none, -1 = CUDA error.
 int imma_take_timeout();
 int tc5_take_timeout();
+// ── Persistent ring GEMV for steps of 1-4 rows (gemv_ring.cu) ──
+// Where the activations of a launch come from: f32 rows as they are, or through the operation that precedes the matrix
+// in the layer, applied by every CTA on its own copy.
+enum RingSrc : int { RING_SRC_PLAIN = 0, RING_SRC_RMS = 1, RING_SRC_LN = 2, RING_SRC_SWIGLU = 3, RING_SRC_GELU = 4 };
+constexpr int RING_MAX_STAGES = 6;
+// Scratch of tile rows shared between CTAs: two 16 x 4 partial blocks per CTA and one arrival counter per tile row of
+// the largest launch. Launches that may overlap on the device must not share one (one per engine / op-level weight).
+struct RingScratch {
+    float* part = nullptr;
+    unsigned* cnt = nullptr;   // zero between launches
+    int rows_cap = 0, ctas_cap = 0;
+    cudaError_t alloc(int max_rows);  // on the current device; not during stream capture
+    void release();
+};
+struct RingArgs {
+    ImmaSeg seg[3];       // wt, bias, y, dtype, n, ldy of up to three matrices sharing the activations (bpt unused: 8)
+    int nseg;
+    int k, m;             // k % 256 == 0, 1 <= m <= 4
+    int src;              // RingSrc
+    const float* x;       // [m][ldx] f32; SWIGLU: gate at column 0 and up at column k of each row; GELU: fc1 output
+    int ldx;
+    const float* nw;      // norm weight [k] (RMS, LN)
+    const float* nb;      // LayerNorm bias [k] or null
+    float eps;
+    const float* res;     // residual added to segment 0 (may alias its y) or null
+    int ldres;
+    // filled by ring_plan:
+    int digits, kt, total_tiles;
+    int seg_tile0[4], seg_row0[4];
+    int stage_bytes, stages, smem_total;
+    int off_bar, off_flush, off_cs, off_rec32, off_rec16, off_xq, off_stage;
+    float* fix_part;
+    unsigned* fix_cnt;
+    int* err;
+};
+// One-time per-device set-up of the ring kernel's error flag (host-mapped memory): call before the first launch on a
+// device, outside stream capture (engine finalize and weight upload do).
+cudaError_t ring_device_init();
+// share_sm: size the ring so that two CTAs fit an SM (this kernel's and the next kernel's prologue under programmatic
+// dependent launch). False when the launch cannot use this kernel (shape, formats, shared memory, scratch size).
+bool ring_plan(RingArgs& a, const RingScratch& sc, bool share_sm = true);
+cudaError_t launch_gemv_ring(RingArgs& a, cudaStream_t st);
+
 // Producers that emit the digits of a GEMV input directly (a: planned ImmaArgs; a.m rows, a.k columns):
 // RMSNorm / LayerNorm of x (y optional f32 copy), SwiGLU (act 0) / tanh-GELU (act 1) of gu, merged split-K attention.
 // tp != null: x first receives the pending tensor-parallel sum (tp.cuh), in place.

@@ -223,6 +223,14 @@ class ForwardEngine:
     def set_graphs(self, on: bool) -> None:
         check(lib().sp_cuda_engine_set_graphs(self._h, int(on)))
 
+    def set_large_m_gemm(self, on: bool) -> None:
+        """Steps of 17 rows and more on the tcgen05 GEMM with fp16 operands (default) or as integer-digit GEMV passes."""
+        check(lib().sp_cuda_engine_set_large_m_gemm(self._h, int(on)))
+
+    def set_ring(self, on: bool) -> None:
+        """Steps of 1-4 rows on the persistent ring GEMV (default) or on the tile-row GEMV with separate producers."""
+        check(lib().sp_cuda_engine_set_ring(self._h, int(on)))
+
     PROFILE_FAMILIES = ("gemv", "attention", "norm", "rope_kv", "elementwise", "embed", "argmax")
 
     def set_profile(self, on: bool) -> None:

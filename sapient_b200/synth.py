@@ -164,6 +164,13 @@ CONFIGS = {
                       vocab=200, norm_eps=1e-6, rope_theta=1e6, tied=True, qkv_bias=True),
     "tiny_phi2": dict(arch="phi2", n_layers=2, hidden=160, n_heads=4, n_kv_heads=4, head_dim=40, ffn=320,
                       vocab=96, norm_eps=1e-5, rope_theta=1e4, rotary_dim=16, tied=False),
+    # widths that are multiples of 256 (the 256-column tile kernels) with Phi-2's block: LayerNorm, partial RoPE, GELU,
+    # biases, head_dim 80
+    "tiny_phi2_wide": dict(arch="phi2", n_layers=2, hidden=640, n_heads=8, n_kv_heads=8, head_dim=80, ffn=1280,
+                           vocab=144, norm_eps=1e-5, rope_theta=1e4, rotary_dim=32, tied=False),
+    # Llama block whose rows span several 256-column tiles (hidden 768 = 3 tiles, ffn 2048 = 8 tiles)
+    "tiny_llama_wide": dict(arch="llama", n_layers=3, hidden=768, n_heads=6, n_kv_heads=2, head_dim=128, ffn=2048,
+                            vocab=1000, norm_eps=1e-5, rope_theta=5e5, tied=False),
 }
 
 

@@ -14,7 +14,7 @@ def last_argmax(v):
     return int(np.flatnonzero(v == v.max())[-1])
 
 
-@pytest.mark.parametrize("name", ["tiny_llama", "tiny_qwen", "tiny_phi2"])
+@pytest.mark.parametrize("name", ["tiny_llama", "tiny_qwen", "tiny_phi2", "tiny_phi2_wide", "tiny_llama_wide"])
 def test_greedy_loop_equals_stepwise_host_loop(oracle, name):
     cfg, W = tiny_model(name)
     eng = ForwardEngine.from_weights(cfg, W)

@@ -18,7 +18,7 @@ LOGIT_BAR = 2e-2
 # carry two int8 digits per activation (2^-15 of the block maximum) instead of three (2^-23), which moves logits
 # by ~1e-4. The reference's own chunked-vs-per-token gate is 5e-3 (wgpu_coherence.rs:556-600).
 INVARIANCE_BAR = 1e-3
-MODELS = ["tiny_llama", "tiny_qwen", "tiny_phi2"]
+MODELS = ["tiny_llama", "tiny_qwen", "tiny_phi2", "tiny_phi2_wide", "tiny_llama_wide"]
 
 
 def prompt(cfg, n, seed=0):

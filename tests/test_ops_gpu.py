@@ -48,10 +48,13 @@ def test_q6_k_canonical_block(oracle):
 
 # reference GPU-vs-CPU shapes (wgpu/tests/resident.rs:71-101,641-775) plus ragged row counts and every M bucket
 MATMUL_CASES = [(1, 1536, 512), (3, 256, 48), (17, 256, 48), (1, 256, 1), (2, 512, 9), (4, 1024, 33), (5, 768, 7),
-                (8, 2048, 64), (9, 512, 16), (32, 1024, 40)]
+                (8, 2048, 64), (9, 512, 16), (32, 1024, 40),
+                # more tiles than the GPU has SMs: every CTA of the persistent ring GEMV shares its first and last tile row
+                (1, 4096, 2400), (2, 14336, 1024), (4, 4096, 1000), (3, 1536, 2728)]
 
 
-@pytest.fixture(params=[0, 1, 3], ids=["tensor-core-rowtile", "cuda-core", "tensor-core-stream"])
+# 0: ring GEMV for 1-4 rows, tile-row kernel above; 2: tile-row kernel always
+@pytest.fixture(params=[0, 2, 1, 3], ids=["tensor-core-default", "tensor-core-rowtile", "cuda-core", "tensor-core-stream"])
 def gemv_path(request):
     ops.set_gemv_path(request.param)
     yield request.param

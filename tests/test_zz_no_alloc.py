@@ -39,11 +39,15 @@ def _static_attention(torch, q, k, v, n_splits):
     Hkv = k.shape[0]
     d, n_pages = _paged_inputs(torch, q, k, v)
     torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info()[0]
     st = _lib.lib().sp_cuda_attention_paged_static(
         0, d["q"].data_ptr(), H * hd, d["out"].data_ptr(), H * hd, sq, H, Hkv, hd, d["slot"].data_ptr(), d["pos"].data_ptr(),
         d["pool"].data_ptr(), d["pt"].data_ptr(), n_pages, n_pages, 0, n_splits, None)
     _lib.check(st)
     torch.cuda.synchronize()
+    # the call took no device memory (the driver's free-memory figure is unchanged; the very first call of a process
+    # may load the module that holds the scratch array, so only a drop larger than that array would be an allocation)
+    assert free_before - torch.cuda.mem_get_info()[0] <= (8 << 20), (free_before, torch.cuda.mem_get_info()[0])
     return d["out"].cpu().numpy().reshape(sq, H, hd).transpose(1, 0, 2)
 
 
