@@ -211,6 +211,17 @@ int32_t sp_cuda_decode_batch(SpEngine* e, const uint32_t* ids, const int32_t* sl
  * Pipeline::generate_* runs with SamplingStrategy::Greedy (crates/sapient-generate/src/pipeline.rs:540-659). */
 int32_t sp_cuda_decode_greedy(SpEngine* e, const uint32_t* first_ids, const int32_t* slots, int32_t b, int32_t steps,
                               uint32_t* tokens_out);
+/* Greedy speculative decoding of one sequence (slot 0 of both engines, which are reset first): the schedule of
+ * SpeculativePipeline with greedy sampling (crates/sapient-generate/src/speculative.rs:499-631; draft length `k` as
+ * crates/sapient-cli/src/server.rs:282-283) with both loops inside the library. Per round the draft runs k steps of the
+ * device-resident greedy loop, the target verifies in ONE forward of k + 1 rows (the token committed last + the k
+ * drafts), drafts are kept while they equal the target's arg-max (last maximum wins), the target's pick after them is
+ * committed as well, and both caches are rolled back to the committed tokens. The committed stream equals the target's
+ * own greedy decoding. tokens_out[max_new] receives the generated tokens (the prompt is not repeated), *n_out their
+ * count (generation stops after an id listed in eos_ids); stats, when not NULL, receives {rounds, drafted, accepted}.
+ * 1 <= k <= 15; both engines single-GPU with the same vocabulary. */
+int32_t sp_cuda_spec_greedy(SpEngine* target, SpEngine* draft, const uint32_t* prompt, size_t n_prompt, int32_t k, size_t max_new,
+                            const uint32_t* eos_ids, int32_t n_eos, uint32_t* tokens_out, size_t* n_out, uint64_t* stats);
 int32_t sp_cuda_engine_synchronize(SpEngine* e);
 /* Replay decode steps as CUDA graphs (default on). */
 int32_t sp_cuda_engine_set_graphs(SpEngine* e, int32_t on);

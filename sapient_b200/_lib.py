@@ -81,6 +81,7 @@ SIGNATURES = {
     "sp_cuda_forward_slot": (_i32, [_vp, _i32, _vp, _sz, _i32, _vp]),
     "sp_cuda_decode_batch": (_i32, [_vp, _vp, _vp, _i32, _vp, _vp]),
     "sp_cuda_decode_greedy": (_i32, [_vp, _vp, _vp, _i32, _i32, _vp]),
+    "sp_cuda_spec_greedy": (_i32, [_vp, _vp, _vp, _sz, _i32, _sz, _vp, _i32, _vp, C.POINTER(_sz), _vp]),
     "sp_cuda_engine_synchronize": (_i32, [_vp]),
     "sp_cuda_engine_set_graphs": (_i32, [_vp, _i32]),
     "sp_cuda_engine_set_ring": (_i32, [_vp, _i32]),

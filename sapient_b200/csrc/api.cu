@@ -28,6 +28,10 @@ struct SpEngine {
 };
 
 int sp_engine_from_gguf_impl(const char* path, int device, int max_ctx, int max_batch, Engine** out);  // gguf.cu
+namespace sp {
+int spec_greedy(Engine* target, Engine* draft, const uint32_t* prompt, size_t n_prompt, int k, size_t max_new, const uint32_t* eos,
+                int n_eos, uint32_t* tokens_out, size_t* n_out, uint64_t* stats);  // spec.cu
+}
 
 namespace {
 
@@ -643,6 +647,15 @@ int32_t sp_cuda_decode_greedy(SpEngine* e, const uint32_t* first_ids, const int3
     API_BEGIN
     if (!e) { set_error("null engine"); return SP_ERR_ARG; }
     return e->e->decode_greedy(first_ids, slots, b, steps, tokens_out);
+    API_END
+}
+
+int32_t sp_cuda_spec_greedy(SpEngine* target, SpEngine* draft, const uint32_t* prompt, size_t n_prompt, int32_t k, size_t max_new,
+                            const uint32_t* eos_ids, int32_t n_eos, uint32_t* tokens_out, size_t* n_out, uint64_t* stats) {
+    API_BEGIN
+    if (!target || !draft) { set_error("null engine"); return SP_ERR_ARG; }
+    if (n_eos < 0 || (n_eos > 0 && !eos_ids)) { set_error("spec_greedy: bad eos list"); return SP_ERR_ARG; }
+    return sp::spec_greedy(target->e, draft->e, prompt, n_prompt, k, max_new, eos_ids, n_eos, tokens_out, n_out, stats);
     API_END
 }
 

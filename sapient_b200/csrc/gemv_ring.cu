@@ -43,10 +43,11 @@ cudaError_t count_launch_and_check();  // kernels.cu
 void imma_note_ring_launch();          // gemv_imma.cu: arms imma_take_timeout
 int* imma_timeout_flag();              // gemv_imma.cu: device address of the flag on the current device
 
-constexpr int RING_CW = 8;                         // consumer warps = tiles per ring slot
+constexpr int RING_CW = 15;                        // consumer warps = tiles per ring slot (16 warps with the service warp:
+                                                   // four per scheduler, 128 registers per thread)
 constexpr int RING_THREADS = (RING_CW + 1) * 32;
-constexpr int RING_SPIN_LIMIT = 1 << 16;           // try_wait polls of up to ~20 us each: about a second
-constexpr int RING_SMEM_SHARED_SM = 112 * 1024;    // two CTAs (this kernel and the next one's prologue) per SM
+constexpr int RING_SPIN_LIMIT = 1 << 22;           // try_wait polls (each blocks for a short, implementation-defined time): a second or so
+constexpr int RING_SMEM_SHARED_SM = 112 * 1024;    // budget that leaves room for a second CTA on the SM
 constexpr int RING_SMEM_MAX = 200 * 1024;
 
 __device__ __forceinline__ uint32_t ring_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -68,9 +69,9 @@ __device__ __forceinline__ bool ring_wait(uint64_t* bar, uint32_t parity) {
     const uint32_t addr = ring_smem_u32(bar);
     for (int spin = 0; spin < RING_SPIN_LIMIT; ++spin) {
         uint32_t ok;
-        asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}\n"
+        asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
                      : "=r"(ok)
-                     : "r"(addr), "r"(parity), "r"(20000)
+                     : "r"(addr), "r"(parity)
                      : "memory");
         if (ok) return true;
     }
@@ -201,7 +202,7 @@ __device__ __forceinline__ void ring_load8(const float* p, float (&v)[8]) {
 }
 
 template <int NT>
-__global__ void __launch_bounds__(RING_THREADS, NT == 1 ? 2 : 1) gemv_ring_kernel(const RingArgs a) {
+__global__ void __launch_bounds__(RING_THREADS, 1) gemv_ring_kernel(const RingArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ float norm_red[RING_CW];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -331,33 +332,66 @@ __global__ void __launch_bounds__(RING_THREADS, NT == 1 ? 2 : 1) gemv_ring_kerne
         int ct = t_begin, cs = 0, cslot = 0;
         uint32_t cpar = 0;
         int retired = 0;
+        // position of the next tile inside its segment: (tile row, k tile), kept without divisions
+        int nrow = 0, nkt = 0;
+        {
+            int s0 = 0;
+            while (s0 < a.nseg - 1 && t_begin >= a.seg_tile0[s0 + 1]) ++s0;
+            const int local = t_begin - a.seg_tile0[s0];
+            nrow = local / KT;
+            nkt = local - nrow * KT;
+        }
         while (ct < t_end) {
+            const int seg_before = cs;
             const int len = chunk_len(ct, cs);
+            if (cs != seg_before) { nrow = 0; nkt = 0; }  // chunks never cross a segment: a new one starts at its first tile
             ok = ok && ring_wait(&empty[cslot], cpar);
             if (!ok) break;
             ++retired;
             const int tb = ring_tile_bytes(a.seg[cs].dtype);
             const uint8_t* slot_base = ring + (size_t)cslot * a.stage_bytes;
-            for (int w = 0; w < len; ++w) {
-                const int local = ct + w - a.seg_tile0[cs];
-                const int row = local / KT;
-                if (cs != cur_seg || row != cur_row) {
+            auto add_tile = [&](const float4 (&f)[NT]) {
+                if (cs != cur_seg || nrow != cur_row) {
                     flush();
                     cur_seg = cs;
-                    cur_row = row;
+                    cur_row = nrow;
                 }
-                const float4* frag = reinterpret_cast<const float4*>(slot_base + (size_t)w * tb);
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt) {
-                    const float4 f = frag[nt * 32 + lane];
-                    racc[nt][0] += f.x; racc[nt][1] += f.y; racc[nt][2] += f.z; racc[nt][3] += f.w;
+                    racc[nt][0] += f[nt].x; racc[nt][1] += f[nt].y; racc[nt][2] += f[nt].z; racc[nt][3] += f[nt].w;
                 }
-            }
-            __syncwarp();
-            if (pt < t_end) {
-                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // the slot's generic writes precede the async refill
-                issue();
-                ++issued;
+                if (++nkt == KT) { nkt = 0; ++nrow; }
+            };
+            auto rearm = [&]() {
+                if (pt < t_end) {
+                    __syncwarp();
+                    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // the slot's generic accesses precede the async refill
+                    issue();
+                    ++issued;
+                }
+            };
+            if (NT == 1) {
+                // all fragments of the slot into registers first, so that the slot is re-armed before they are summed
+                float4 fr[RING_CW][NT];
+                float guard = 0.f;
+#pragma unroll
+                for (int w = 0; w < RING_CW; ++w) {
+                    fr[w][0] = w < len ? reinterpret_cast<const float4*>(slot_base + (size_t)w * tb)[lane] : make_float4(0.f, 0.f, 0.f, 0.f);
+                    guard += fr[w][0].x;
+                }
+                asm volatile("" ::"f"(guard) : "memory");  // the loads have returned before the copy may overwrite the slot
+                rearm();
+#pragma unroll
+                for (int w = 0; w < RING_CW; ++w)
+                    if (w < len) add_tile(fr[w]);
+            } else {
+                for (int w = 0; w < len; ++w) {
+                    float4 f[NT];
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt) f[nt] = reinterpret_cast<const float4*>(slot_base + (size_t)w * tb)[nt * 32 + lane];
+                    add_tile(f);
+                }
+                rearm();
             }
             ct += len;
             if (++cslot == a.stages) { cslot = 0; cpar ^= 1u; }

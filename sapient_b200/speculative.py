@@ -167,3 +167,76 @@ def generate(target, draft, prompt: Sequence[int], max_new_tokens: int, k: int =
         if hit_eos:
             break
     return out[:max_new_tokens], state
+
+
+# ── greedy speculative decoding: k + 1 rows per verify pass ─────────────────────────────────────────────────────────
+@dataclass
+class GreedySpecStats:
+    rounds: int = 0
+    drafted: int = 0
+    accepted_drafts: int = 0
+
+
+def generate_greedy(target, draft, prompt: Sequence[int], max_new_tokens: int, k: int = 4, eos_ids: Sequence[int] = ()):
+    """Greedy speculative decoding through the ForwardEngine surface (forward_logits / forward_all_logits_cached /
+    truncate_cache), the host-side statement of the schedule sp_cuda_spec_greedy runs inside the library: the token
+    committed last is fed to the target TOGETHER with the k drafts (one k + 1 row verify pass per round instead of the
+    reference's k-row pass plus a single-token pass, speculative.rs:557,606), drafts are kept while they equal the
+    target's arg-max, the target's pick after them is committed too. Works with any engine pair (the CPU oracle's
+    included), so the CUDA loop can be checked against it token for token. Returns (new tokens, GreedySpecStats)."""
+    prompt = [int(t) for t in prompt]
+    if not prompt:
+        raise ValueError("generate_greedy: empty prompt")
+    target.reset_cache()
+    draft.reset_cache()
+    st = GreedySpecStats()
+    pending = greedy(target.forward_logits(prompt, True))
+    draft.forward_logits(prompt, True)
+    out: List[int] = [pending] if max_new_tokens > 0 else []
+    stop = max_new_tokens == 0 or pending in eos_ids
+    length = len(prompt)  # committed tokens held by both caches
+    while not stop and len(out) < max_new_tokens:
+        drafts: List[int] = []
+        tok = pending
+        for _ in range(k):
+            tok = greedy(draft.forward_logits([tok], True))
+            drafts.append(tok)
+        logits = np.asarray(target.forward_all_logits_cached([pending] + drafts)).reshape(k + 1, -1)
+        picks = [greedy(row) for row in logits]
+        n = 0
+        while n < k and drafts[n] == picks[n]:
+            n += 1
+        st.rounds += 1
+        st.drafted += k
+        st.accepted_drafts += n
+        for t in drafts[:n] + [picks[n]]:
+            if len(out) >= max_new_tokens or stop:
+                break
+            out.append(t)
+            stop = t in eos_ids
+        pending = picks[n]
+        target.truncate_cache(length + 1 + n)
+        if n < k:
+            draft.truncate_cache(length + 1 + n)
+        elif not stop and len(out) < max_new_tokens:
+            draft.forward_logits([drafts[-1]], True)
+        length += 1 + n
+    return out, st
+
+
+def generate_greedy_device(target, draft, prompt: Sequence[int], max_new_tokens: int, k: int = 4, eos_ids: Sequence[int] = ()):
+    """The same schedule run by sp_cuda_spec_greedy (CUDA engines of this package only): the draft's greedy loop stays
+    on the device and only token ids cross the host boundary. Returns (new tokens, GreedySpecStats)."""
+    import ctypes as C
+
+    from ._lib import check, lib
+
+    ids = np.ascontiguousarray(prompt, dtype=np.uint32).reshape(-1)
+    eos = np.ascontiguousarray(list(eos_ids), dtype=np.uint32).reshape(-1)
+    out = np.zeros(max(max_new_tokens, 1), np.uint32)
+    n_out = C.c_size_t()
+    stats = np.zeros(3, np.uint64)
+    check(lib().sp_cuda_spec_greedy(target._h, draft._h, ids.ctypes.data_as(C.c_void_p), ids.size, k, max_new_tokens,
+                                    eos.ctypes.data_as(C.c_void_p) if eos.size else None, eos.size, out.ctypes.data_as(C.c_void_p),
+                                    C.byref(n_out), stats.ctypes.data_as(C.c_void_p)))
+    return [int(t) for t in out[: n_out.value]], GreedySpecStats(int(stats[0]), int(stats[1]), int(stats[2]))

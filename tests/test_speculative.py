@@ -144,3 +144,58 @@ def test_verify_pass_is_one_batched_forward():
     eng.forward_logits([1], True)
     single = ops.launch_count() - n0
     assert batched == single  # same kernels per step whatever the row count
+
+
+# ── greedy schedule with a k + 1 row verify pass (generate_greedy / sp_cuda_spec_greedy) ──
+def test_greedy_schedule_equals_target_greedy_on_oracle(oracle):
+    cfg, Wt = tiny_model("tiny_llama", seed=7)
+    _, Wd = tiny_model("tiny_llama", seed=8)
+    prompt = _prompt(cfg)
+    ref = _greedy_decode(oracle_engine(oracle, cfg, Wt), prompt, 17)
+    target, draft = oracle_engine(oracle, cfg, Wt), oracle_engine(oracle, cfg, Wd)
+    out, st = sp.generate_greedy(target, draft, prompt, 17, k=4)
+    assert out == ref
+    assert st.drafted == 4 * st.rounds and 0 <= st.accepted_drafts <= st.drafted
+    # draft == target: every draft is accepted, k + 1 tokens per round after the first token
+    target, draft = oracle_engine(oracle, cfg, Wt), oracle_engine(oracle, cfg, Wt)
+    out, st = sp.generate_greedy(target, draft, prompt, 16, k=4)
+    assert out == ref[:16] and st.accepted_drafts == st.drafted == 4 * 3
+    # an EOS id ends the stream right after it
+    eos = ref[5]
+    out, _ = sp.generate_greedy(oracle_engine(oracle, cfg, Wt), oracle_engine(oracle, cfg, Wd), prompt, 17, k=4, eos_ids=[eos])
+    assert out == ref[: ref.index(eos) + 1]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", ["tiny_llama", "tiny_llama_wide", "tiny_phi2_wide"])
+def test_device_greedy_spec_equals_target_greedy(name):
+    """sp_cuda_spec_greedy (draft loop on the device, k + 1 row verify, arg-max ids only) against the target's own
+    greedy decoding and against the host-side statement of the same schedule."""
+    from sapient_b200.engine import ForwardEngine
+
+    cfg, Wt = tiny_model(name, seed=7, max_ctx=128)
+    _, Wd = tiny_model(name, seed=8, max_ctx=128)
+    prompt = _prompt(cfg, 10)
+    n_new = 48
+    ref = _greedy_decode(ForwardEngine.from_weights(cfg, Wt), prompt, n_new)
+    for Wdraft, all_accepted in ((Wd, False), (Wt, True)):
+        target, draft = ForwardEngine.from_weights(cfg, Wt), ForwardEngine.from_weights(cfg, Wdraft)
+        out, st = sp.generate_greedy_device(target, draft, prompt, n_new, k=4)
+        assert out == ref
+        t2, d2 = ForwardEngine.from_weights(cfg, Wt), ForwardEngine.from_weights(cfg, Wdraft)
+        out_h, st_h = sp.generate_greedy(t2, d2, prompt, n_new, k=4)
+        assert out_h == ref and (st_h.rounds, st_h.drafted, st_h.accepted_drafts) == (st.rounds, st.drafted, st.accepted_drafts)
+        if all_accepted:
+            assert st.accepted_drafts == st.drafted and st.rounds == -(-(n_new - 1) // 5)
+        for e in (target, draft, t2, d2):
+            e.close()
+    # generation stops after an EOS id; bad arguments are refused
+    target, draft = ForwardEngine.from_weights(cfg, Wt), ForwardEngine.from_weights(cfg, Wd)
+    out, _ = sp.generate_greedy_device(target, draft, prompt, n_new, k=4, eos_ids=[ref[7]])
+    assert out == ref[: ref.index(ref[7]) + 1]
+    from sapient_b200 import _lib
+
+    with pytest.raises(_lib.SapientCudaError):
+        sp.generate_greedy_device(target, draft, prompt, n_new, k=0)
+    with pytest.raises(_lib.SapientCudaError):
+        sp.generate_greedy_device(target, draft, [], n_new, k=4)
