@@ -81,12 +81,11 @@ int32_t sp_cuda_check_kernels(int32_t device);
  * engines drop their captured step graphs when it changes (sp_cuda_engine_set_graphs off/on). */
 int32_t sp_cuda_set_activation_digits(int32_t mode);
 /* Which GEMV kernel runs (process-wide; op-level calls — engines have sp_cuda_engine_set_ring):
- *   0 (default): calls of 1-4 rows take the persistent ring GEMV (shared-memory ring fed by bulk copies, activation
- *      digits built inside the kernel) where the shape fits, everything else the tensor-core GEMV with one CTA per
- *      16-row tile row;
- *   2: always the tile-row kernel;
+ *   0 (default) and 2: the tensor-core GEMV with one CTA per 16-row tile row;
  *   1: the CUDA-core GEMV on the raw blocks (an independent second implementation for cross-checks);
- *   3: the per-warp streaming variant of the tile-row kernel where the shape qualifies. */
+ *   3: the per-warp streaming variant of the tile-row kernel where the shape qualifies;
+ *   4: calls of 1-5 rows take the bulk-copy ring GEMV (persistent CTAs, shared-memory ring fed by cp.async.bulk,
+ *      activation digits built inside the kernel) where the shape fits. */
 int32_t sp_cuda_set_gemv_path(int32_t path);
 /* 1 (default): op-level matmuls with m >= 17 rows and k % 256 == 0 (Q8_0: k % 128 == 0) run the tcgen05 / TMEM dequant GEMM; 0: always the
  * 16-row GEMV passes (for cross-checks and timing comparisons). Process-wide; engines have their own switch. */
@@ -229,8 +228,8 @@ int32_t sp_cuda_engine_set_graphs(SpEngine* e, int32_t on);
  * (default on; off: tensor-core GEMV passes on integer digits, slower, closer to the reference's f32 arithmetic — see
  * sp_cuda_set_activation_digits). Drops the captured step graphs. */
 int32_t sp_cuda_engine_set_large_m_gemm(SpEngine* e, int32_t on);
-/* Steps of 1-4 rows on the persistent ring GEMV with the preceding norm / activation fused into it (default on; off: the
- * tile-row GEMV with separate norm / activation kernels). Drops the captured step graphs. */
+/* Steps of 1-5 rows on the bulk-copy ring GEMV with the preceding norm / activation fused into it (default off: it
+ * measures slower than the default kernels). Drops the captured step graphs. */
 int32_t sp_cuda_engine_set_ring(SpEngine* e, int32_t on);
 /* Per-kernel-family device timing (CUDA events around every launch; disables graphs while on). Families, in order:
  * gemv, attention, norm, rope_kv, elementwise, embed, argmax. Returns the family count; ms/launches accumulate

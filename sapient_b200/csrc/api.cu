@@ -36,7 +36,7 @@ int spec_greedy(Engine* target, Engine* draft, const uint32_t* prompt, size_t n_
 namespace {
 
 std::atomic<int> g_gemv_path{0};  // 0: tensor-core GEMV on tiled weights; 1: CUDA-core GEMV on raw blocks
-std::atomic<int> g_ring{1};       // calls of 1-4 rows on the persistent ring GEMV where it fits
+std::atomic<int> g_ring{0};       // calls of 1-5 rows on the bulk-copy ring GEMV where it fits (path 4)
 
 #define API_BEGIN try {
 #define API_END                                                     \
@@ -222,9 +222,9 @@ int32_t sp_cuda_set_activation_digits(int32_t mode) {
 }
 
 int32_t sp_cuda_set_gemv_path(int32_t path) {
-    if (path < 0 || path > 3) { set_error("gemv path must be 0..3"); return SP_ERR_ARG; }
+    if (path < 0 || path > 4) { set_error("gemv path must be 0..4"); return SP_ERR_ARG; }
     g_gemv_path.store(path == 1 ? 1 : 0);
-    g_ring.store(path == 0 ? 1 : 0);
+    g_ring.store(path == 4 ? 1 : 0);
     imma_select_kernel(path == 3 ? 3 : 0);
     return SP_OK;
 }
@@ -305,7 +305,7 @@ int32_t sp_cuda_matmul_nt_dev(const SpWeight* w, const float* x_dev, int64_t m, 
                                     (cudaStream_t)stream, &wm->ws.tc5));
         return SP_OK;
     }
-    if (w->tiled && g_gemv_path.load() == 0 && g_ring.load() && m >= 1 && m <= 4) {
+    if (w->tiled && g_gemv_path.load() == 0 && g_ring.load() && m >= 1 && m <= RING_MAX_M) {
         RingArgs ra{};
         ra.nseg = 1;
         ra.seg[0].wt = w->tiled; ra.seg[0].y = y_dev; ra.seg[0].dtype = w->dtype; ra.seg[0].n = (int)w->n; ra.seg[0].ldy = (int)w->n; ra.seg[0].bpt = 8;

@@ -93,7 +93,7 @@ class Engine {
     bool finalized = false;
     bool trace_on = false;
     bool use_graphs = true;
-    bool use_ring = true;      // steps of 1-4 rows on the persistent ring GEMV (false: always the tile-row kernel)
+    bool use_ring = false;     // steps of 1-5 rows on the bulk-copy ring GEMV (opt-in: measured slower than the tile-row kernels)
     bool use_tc5 = true;       // steps of TC5_MIN_M rows and more on the tcgen05 GEMM (false: always 16-row GEMV passes)
     bool graph_step_ = false;  // a step is being captured: its kernels may take positions only from device memory
     // 1 (default): new K / V rows get the reference's Q8_0 cache rounding before they are stored as fp16 (head_dim % 32

@@ -129,7 +129,7 @@ int Engine::try_ring(bool* done, int m, int k, int src, const float* x, int ldx,
                      const float* b0, float* y0, int ldy, const DevTensor* w1, const float* b1, float* y1, const DevTensor* w2,
                      const float* b2, float* y2, const float* res) {
     *done = false;
-    if (!use_ring || d.tp_size > 1 || trace_on || m > 4) return SP_OK;
+    if (!use_ring || d.tp_size > 1 || trace_on || m > RING_MAX_M) return SP_OK;
     const DevTensor* ws[3] = {w0, w1, w2};
     const float* bs[3] = {b0, b1, b2};
     float* ys[3] = {y0, y1, y2};
@@ -181,7 +181,7 @@ int Engine::attention_and_oproj(const LayerW& w, int l, int T) {
     int splits = 1;
     if (T <= imma_rows_per_pass()) splits = H * T <= 64 ? ATT_SPLITS : H * T <= 128 ? 8 : 4;
     ImmaArgs ia;
-    if (splits > 1 && use_ring && d.tp_size == 1 && !trace_on && T <= 4 && all_tiled(w.o)) {
+    if (splits > 1 && use_ring && d.tp_size == 1 && !trace_on && T <= RING_MAX_M && all_tiled(w.o)) {
         // split-K attention merged to f32 rows; the output projection quantises them itself
         SP_LAUNCH(F_ATTN, launch_attention(qkv_, qkv_ld, attn_, H * hd, T, H, d_tok_slot_, d_tok_pos_, kv_, l, scale, splits, att_scratch_, stream));
         bool done = false;

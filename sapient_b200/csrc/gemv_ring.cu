@@ -30,6 +30,8 @@
 // Every mbarrier wait is bounded; after an expired wait the CTA stops consuming, raises the error flag the host reads
 // (imma_take_timeout), waits — bounded again — for its copies in flight and returns.
 #include <atomic>
+#include <cstdio>
+#include <cstdlib>
 
 #include "gemv_imma.cuh"
 #include "gemv_imma_dev.cuh"
@@ -43,11 +45,13 @@ cudaError_t count_launch_and_check();  // kernels.cu
 void imma_note_ring_launch();          // gemv_imma.cu: arms imma_take_timeout
 int* imma_timeout_flag();              // gemv_imma.cu: device address of the flag on the current device
 
-constexpr int RING_CW = 15;                        // consumer warps = tiles per ring slot (16 warps with the service warp:
-                                                   // four per scheduler, 128 registers per thread)
-constexpr int RING_THREADS = (RING_CW + 1) * 32;
+// Consumer warps = tiles per ring slot. 15 (16 warps with the service warp: four per scheduler, up to 128 registers per
+// thread) for launches that mix weight formats; 23 (24 warps, 80 registers) when every segment has one K-quant format
+// and the per-format code fits the smaller register budget: the tile arithmetic is latency-bound per warp, so more
+// resident warps are worth more than a deeper ring.
+constexpr int RING_CW_MIXED = 15, RING_CW_SINGLE = 23;
+constexpr int RING_PART_FLOATS = 96;               // partial block of a shared tile row: 16 x 5 outputs, padded
 constexpr int RING_SPIN_LIMIT = 1 << 22;           // try_wait polls (each blocks for a short, implementation-defined time): a second or so
-constexpr int RING_SMEM_SHARED_SM = 112 * 1024;    // budget that leaves room for a second CTA on the SM
 constexpr int RING_SMEM_MAX = 200 * 1024;
 
 __device__ __forceinline__ uint32_t ring_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -65,8 +69,19 @@ __device__ __forceinline__ void ring_bulk_g2s(void* dst, const void* src, int by
                  "l"(src), "r"(bytes), "r"(ring_smem_u32(bar))
                  : "memory");
 }
-__device__ __forceinline__ bool ring_wait(uint64_t* bar, uint32_t parity) {
+__device__ __forceinline__ bool ring_wait(uint64_t* bar, uint32_t parity, int mode = 0) {
     const uint32_t addr = ring_smem_u32(bar);
+    if (mode) {
+        for (int spin = 0; spin < (1 << 26); ++spin) {
+            uint32_t ok;
+            asm volatile("{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+                         : "=r"(ok)
+                         : "r"(addr), "r"(parity)
+                         : "memory");
+            if (ok) return true;
+        }
+        return false;
+    }
     for (int spin = 0; spin < RING_SPIN_LIMIT; ++spin) {
         uint32_t ok;
         asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
@@ -77,7 +92,8 @@ __device__ __forceinline__ bool ring_wait(uint64_t* bar, uint32_t parity) {
     }
     return false;
 }
-__device__ __forceinline__ void ring_bar_consumers() { asm volatile("bar.sync 2, %0;\n" ::"r"(RING_CW * 32) : "memory"); }
+template <int CW>
+__device__ __forceinline__ void ring_bar_consumers() { asm volatile("bar.sync 2, %0;\n" ::"r"(CW * 32) : "memory"); }
 
 // ───────────────────────── activation digits in shared memory ─────────────────────────
 // Digits of tile kt, digit column col: a 256-byte record in fragment order [t 0..3][block 0..7][8 B] (gemv_imma.cuh),
@@ -162,23 +178,48 @@ __device__ __forceinline__ void ring_quantize_tile(const float (&v)[8], int lane
     }
 }
 
+// Per-lane constants of the B-fragment loads: byte offsets inside one k tile's block of digit records.
 template <int NT>
-__device__ __forceinline__ void ring_load_b(const RingDigits& q, int kt, int g, int t, BFrag<NT>& b) {
+struct RingLane {
+    int xoff[NT][4];   // digit words: record of the lane's column + its four 16-byte slots
+    int roff[NT];      // digit-sum records
+    int own[NT][2];    // activation row that digit column 8 nt + 2 t + e belongs to, or -1 past the live columns
+    bool live[NT];
+};
+template <int NT>
+__device__ __forceinline__ void ring_lane_init(RingLane<NT>& L, int g, int t, int ncols, int digits) {
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
         const int col = nt * 8 + g;
-        if (col < q.ncols) {
-            const int8_t* rec = q.xq + ((int64_t)kt * q.ncols + col) * 256;
+        L.live[nt] = col < ncols;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) L.xoff[nt][i] = col * 256 + 16 * ring_slot(t, i, col);
+        L.roff[nt] = col * 32 + 4 * t;
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const int c = nt * 8 + 2 * t + e;
+            L.own[nt][e] = c < ncols ? (digits == 3 ? c / 3 : c >> 1) : -1;
+        }
+    }
+}
+template <int NT, int FMT>
+__device__ __forceinline__ void ring_load_b(const RingDigits& q, const RingLane<NT>& L, int kt, int t, int dtype, BFrag<NT>& b) {
+    const int8_t* xb = q.xq + (int64_t)kt * q.ncols * 256;
+    const int8_t* r32 = q.rec32 + (int64_t)kt * q.ncols * 32;
+    const int8_t* r16 = q.rec16 + (int64_t)kt * q.ncols * 32;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+        if (L.live[nt]) {
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                const uint4 v = *reinterpret_cast<const uint4*>(rec + 16 * ring_slot(t, i, col));
+                const uint4 v = *reinterpret_cast<const uint4*>(xb + L.xoff[nt][i]);
                 b.w[nt][4 * i] = v.x; b.w[nt][4 * i + 1] = v.y; b.w[nt][4 * i + 2] = v.z; b.w[nt][4 * i + 3] = v.w;
             }
-            const int64_t r = ((int64_t)kt * q.ncols + col) * 32 + 4 * t;
-            b.ra32[nt] = *reinterpret_cast<const uint32_t*>(q.rec32 + r);
-            b.rb32[nt] = *reinterpret_cast<const uint32_t*>(q.rec32 + r + 16);
-            b.ra16[nt] = *reinterpret_cast<const uint32_t*>(q.rec16 + r);
-            b.rb16[nt] = *reinterpret_cast<const uint32_t*>(q.rec16 + r + 16);
+            const bool q4 = FMT == T_Q4_K || (FMT == 0 && dtype == T_Q4_K), q6 = FMT == T_Q6_K || (FMT == 0 && dtype == T_Q6_K);
+            b.ra32[nt] = q4 ? *reinterpret_cast<const uint32_t*>(r32 + L.roff[nt]) : 0u;
+            b.rb32[nt] = q4 ? *reinterpret_cast<const uint32_t*>(r32 + L.roff[nt] + 16) : 0u;
+            b.ra16[nt] = q6 ? *reinterpret_cast<const uint32_t*>(r16 + L.roff[nt]) : 0u;
+            b.rb16[nt] = q6 ? *reinterpret_cast<const uint32_t*>(r16 + L.roff[nt] + 16) : 0u;
         } else {
 #pragma unroll
             for (int i = 0; i < 16; ++i) b.w[nt][i] = 0u;
@@ -201,10 +242,72 @@ __device__ __forceinline__ void ring_load8(const float* p, float (&v)[8]) {
     v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
 }
 
-template <int NT>
-__global__ void __launch_bounds__(RING_THREADS, 1) gemv_ring_kernel(const RingArgs a) {
+// Hand-over of one finished tile row by the service warp (not inlined: it is a few hundred instructions that run once
+// per tile row, or once per CTA for the shared-row path). v0 / v1: the sums of outputs `lane` and `lane + 32` of the
+// row's 16 x m outputs (idx = 16 * activation row + weight row inside the tile row) over this CTA's tiles of the row.
+struct RowOut {
+    const RingArgs* a;
+    int t_begin, t_end, lane;
+};
+template <int R>
+__device__ __noinline__ void ring_row_out(const RowOut& ro, int seg, int row_in_seg, const float (&v)[R]) {
+    const RingArgs& a = *ro.a;
+    const int lane = ro.lane, KT = a.kt, n_out = 16 * a.m;
+    const int64_t T = a.total_tiles;
+    const ImmaSeg& sg = a.seg[seg];
+    auto finalize = [&](int idx, float val) {
+        const int r = idx & 15, mm = idx >> 4;
+        const int64_t row = (int64_t)row_in_seg * 16 + r;
+        if (idx >= n_out || row >= sg.n) return;
+        if (sg.bias) val += sg.bias[row];
+        if (seg == 0 && a.res) val += a.res[(int64_t)mm * a.ldres + row];
+        sg.y[(int64_t)mm * sg.ldy + row] = val;
+    };
+    const int rs = a.seg_tile0[seg] + row_in_seg * KT, re = rs + KT;  // the tile row's tiles, launch-wide numbering
+    if (ro.t_begin <= rs && re <= ro.t_end) {  // every tile of the row was this CTA's
+#pragma unroll
+        for (int r = 0; r < R; ++r) finalize(lane + 32 * r, v[r]);
+        return;
+    }
+    // shared with other CTAs: leave the partial sums, count the arrival; the last CTA adds the parts in CTA order
+    auto cta_begin = [&](int c) { return (int)(T * c / gridDim.x); };
+    auto cta_of = [&](int tile) {
+        int c = (int)(((int64_t)tile * gridDim.x) / T);
+        while (c + 1 < (int)gridDim.x && cta_begin(c + 1) <= tile) ++c;
+        while (c > 0 && cta_begin(c) > tile) --c;
+        return c;
+    };
+    const int slot = (rs <= ro.t_begin && ro.t_begin < re) ? 0 : 1;  // slot 0: the row holding the CTA's first tile
+    float* mine = a.fix_part + ((size_t)blockIdx.x * 2 + slot) * RING_PART_FLOATS;
+#pragma unroll
+    for (int r = 0; r < R; ++r) mine[lane + 32 * r] = v[r];
+    __threadfence();
+    __syncwarp();
+    const int c0 = cta_of(rs), c1 = cta_of(re - 1);
+    const int row_id = a.seg_row0[seg] + row_in_seg;
+    unsigned prev = 0;
+    if (lane == 0) prev = atomicAdd(&a.fix_cnt[row_id], 1u);
+    prev = __shfl_sync(0xFFFFFFFFu, prev, 0);
+    if (prev != (unsigned)(c1 - c0)) return;
+    __threadfence();
+    float s[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) s[r] = 0.f;
+    for (int c = c0; c <= c1; ++c) {
+        const int fb_tile = cta_begin(c);  // that CTA's first tile: inside this row -> its slot 0
+        const float* part = a.fix_part + ((size_t)c * 2 + ((rs <= fb_tile && fb_tile < re) ? 0 : 1)) * RING_PART_FLOATS;
+#pragma unroll
+        for (int r = 0; r < R; ++r) s[r] += __ldcg(part + lane + 32 * r);
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) finalize(lane + 32 * r, s[r]);
+    if (lane == 0) a.fix_cnt[row_id] = 0u;  // ready for the next launch
+}
+
+template <int NT, int CW, int FMT>
+__global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_ring_kernel(const __grid_constant__ RingArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
-    __shared__ float norm_red[RING_CW];
+    __shared__ float norm_red[CW];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + a.off_bar);
     uint64_t* empty = full + RING_MAX_STAGES;
@@ -213,19 +316,21 @@ __global__ void __launch_bounds__(RING_THREADS, 1) gemv_ring_kernel(const RingAr
     const int64_t T = a.total_tiles;
     const int t_begin = (int)(T * blockIdx.x / gridDim.x), t_end = (int)(T * (blockIdx.x + 1) / gridDim.x);
 
+    unsigned long long tk0 = 0;
+    if (a.dbg & 128) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tk0));
     if (threadIdx.x == 0) {
-        for (int s = 0; s < a.stages; ++s) { ring_mbar_init(&full[s], 1); ring_mbar_init(&empty[s], RING_CW); }
+        for (int s = 0; s < a.stages; ++s) { ring_mbar_init(&full[s], 1); ring_mbar_init(&empty[s], CW); }
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     __syncthreads();
 
-    // the sequence of ring slots: consecutive chunks of up to RING_CW tiles that do not cross a segment boundary
+    // the sequence of ring slots: consecutive chunks of up to CW tiles that do not cross a segment boundary
     auto chunk_len = [&](int t, int& s) {
         while (s < a.nseg - 1 && t >= a.seg_tile0[s + 1]) ++s;
-        return min(RING_CW, min(t_end, a.seg_tile0[s + 1]) - t);
+        return min(CW, min(t_end, a.seg_tile0[s + 1]) - t);
     };
 
-    if (warp == RING_CW) {
+    if (warp == CW) {
         // ───────────── service warp: producer of the ring, reducer of the fragments, writer of finished rows ─────────────
         int pt = t_begin, ps = 0, pslot = 0;  // producer cursor
         auto issue = [&]() {
@@ -234,99 +339,35 @@ __global__ void __launch_bounds__(RING_THREADS, 1) gemv_ring_kernel(const RingAr
                 const int tb = ring_tile_bytes(a.seg[ps].dtype);
                 const uint8_t* src = a.seg[ps].wt + (int64_t)(pt - a.seg_tile0[ps]) * tb;
                 ring_expect_tx(&full[pslot], len * tb);
-                ring_bulk_g2s(ring + (size_t)pslot * a.stage_bytes, src, len * tb, &full[pslot]);
+                if (a.dbg & 8) {
+                    for (int w = 0; w < len; ++w)
+                        ring_bulk_g2s(ring + (size_t)pslot * a.stage_bytes + (size_t)w * tb, src + (size_t)w * tb, tb, &full[pslot]);
+                } else {
+                    ring_bulk_g2s(ring + (size_t)pslot * a.stage_bytes, src, len * tb, &full[pslot]);
+                }
             }
             pt += len;
             pslot = pslot + 1 == a.stages ? 0 : pslot + 1;
         };
         int issued = 0;
         for (int i = 0; i < a.stages && pt < t_end; ++i) { issue(); ++issued; }
+        unsigned long long tk1 = 0, tk2 = 0, tk3 = 0, tk4 = 0;
+        if (a.dbg & 128) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tk1));
         pdl_wait();      // the residual (and the scratch of shared rows) belong to the previous kernel until here
         pdl_trigger();
+        if (a.dbg & 128) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tk2));
 
-        float racc[NT][4];
+        // Consumers hand over, per tile, the 16 x m outputs with the digit columns already added (80 floats at most):
+        // lane l of this warp owns outputs l, l + 32, l + 64 (output idx = 16 * activation row + weight row of the tile
+        // row); one or two activation rows need only the first.
+        constexpr int R = NT == 1 ? 1 : 3;
+        float racc[R];
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt) racc[nt][0] = racc[nt][1] = racc[nt][2] = racc[nt][3] = 0.f;
-        float* fb = reinterpret_cast<float*>(smem + a.off_flush);
-        const int first_row_tile = t_begin;  // the CTA's first tile row is the one holding this tile
+        for (int r = 0; r < R; ++r) racc[r] = 0.f;
+        const int n_out = 16 * a.m;
         int cur_seg = -1, cur_row = -1;       // tile row being summed: (segment, row inside the segment)
-
-        // finished value of output (row r of the tile row, activation row mm): bias, residual, store
-        auto finalize = [&](int sgi, int row_in_seg, int idx, float v) {
-            const ImmaSeg& sg = a.seg[sgi];
-            const int r = idx & 15, mm = idx >> 4;
-            const int64_t row = (int64_t)row_in_seg * 16 + r;
-            if (row >= sg.n) return;
-            if (sg.bias) v += sg.bias[row];
-            if (sgi == 0 && a.res) v += a.res[(int64_t)mm * a.ldres + row];
-            sg.y[(int64_t)mm * sg.ldy + row] = v;
-        };
-        auto cta_begin = [&](int c) { return (int)(T * c / gridDim.x); };
-        auto cta_of = [&](int tile) {
-            int c = (int)(((int64_t)tile * gridDim.x) / T);
-            while (c + 1 < (int)gridDim.x && cta_begin(c + 1) <= tile) ++c;
-            while (c > 0 && cta_begin(c) > tile) --c;
-            return c;
-        };
-        auto flush = [&]() {
-            if (cur_row < 0) return;
-#pragma unroll
-            for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-                for (int e = 0; e < 4; ++e) fb[(nt * 4 + e) * 32 + lane] = racc[nt][e];
-            __syncwarp();
-            const int rs = a.seg_tile0[cur_seg] + cur_row * KT, re = rs + KT;  // the tile row's tiles, launch-wide numbering
-            const bool owned = t_begin <= rs && re <= t_end;
-            const int n_out = 16 * a.m;
-            const int row_id = a.seg_row0[cur_seg] + cur_row;
-            bool last = false;
-            int c0 = 0, c1 = 0;
-            if (!owned) {
-                const int slot = (rs <= first_row_tile && first_row_tile < re) ? 0 : 1;
-                float* mine = a.fix_part + ((size_t)blockIdx.x * 2 + slot) * 64;
-                for (int idx = lane; idx < n_out; idx += 32) {
-                    const int r = idx & 15, mm = idx >> 4;
-                    float v = 0.f;
-                    for (int d = 0; d < a.digits; ++d) {
-                        const int col = mm * a.digits + d, nt = col >> 3, cc = col & 7;
-                        v += fb[((nt * 4) + (r < 8 ? 0 : 2) + (cc & 1)) * 32 + (r & 7) * 4 + (cc >> 1)];
-                    }
-                    mine[idx] = v;
-                }
-                __threadfence();
-                __syncwarp();
-                c0 = cta_of(rs);
-                c1 = cta_of(re - 1);
-                unsigned prev = 0;
-                if (lane == 0) prev = atomicAdd(&a.fix_cnt[row_id], 1u);
-                prev = __shfl_sync(0xFFFFFFFFu, prev, 0);
-                last = prev == (unsigned)(c1 - c0);
-                if (last) __threadfence();
-            }
-            if (owned || last) {
-                for (int idx = lane; idx < n_out; idx += 32) {
-                    float v = 0.f;
-                    if (owned) {
-                        const int r = idx & 15, mm = idx >> 4;
-                        for (int d = 0; d < a.digits; ++d) {
-                            const int col = mm * a.digits + d, nt = col >> 3, cc = col & 7;
-                            v += fb[((nt * 4) + (r < 8 ? 0 : 2) + (cc & 1)) * 32 + (r & 7) * 4 + (cc >> 1)];
-                        }
-                    } else {
-                        for (int c = c0; c <= c1; ++c) {
-                            const int fb_tile = cta_begin(c);  // that CTA's first tile: inside this row -> its slot 0
-                            const int slot = (rs <= fb_tile && fb_tile < re) ? 0 : 1;
-                            v += __ldcg(a.fix_part + ((size_t)c * 2 + slot) * 64 + idx);
-                        }
-                    }
-                    finalize(cur_seg, cur_row, idx, v);
-                }
-                if (last && lane == 0) a.fix_cnt[row_id] = 0u;  // ready for the next launch
-            }
-            __syncwarp();
-#pragma unroll
-            for (int nt = 0; nt < NT; ++nt) racc[nt][0] = racc[nt][1] = racc[nt][2] = racc[nt][3] = 0.f;
-        };
+        RowOut ro;
+        ro.a = &a; ro.t_begin = t_begin; ro.t_end = t_end; ro.lane = lane;
 
         bool ok = true;
         int ct = t_begin, cs = 0, cslot = 0;
@@ -335,9 +376,8 @@ __global__ void __launch_bounds__(RING_THREADS, 1) gemv_ring_kernel(const RingAr
         // position of the next tile inside its segment: (tile row, k tile), kept without divisions
         int nrow = 0, nkt = 0;
         {
-            int s0 = 0;
-            while (s0 < a.nseg - 1 && t_begin >= a.seg_tile0[s0 + 1]) ++s0;
-            const int local = t_begin - a.seg_tile0[s0];
+            while (cs < a.nseg - 1 && t_begin >= a.seg_tile0[cs + 1]) ++cs;  // the segment the range starts in
+            const int local = t_begin - a.seg_tile0[cs];
             nrow = local / KT;
             nkt = local - nrow * KT;
         }
@@ -350,53 +390,50 @@ __global__ void __launch_bounds__(RING_THREADS, 1) gemv_ring_kernel(const RingAr
             ++retired;
             const int tb = ring_tile_bytes(a.seg[cs].dtype);
             const uint8_t* slot_base = ring + (size_t)cslot * a.stage_bytes;
-            auto add_tile = [&](const float4 (&f)[NT]) {
-                if (cs != cur_seg || nrow != cur_row) {
-                    flush();
-                    cur_seg = cs;
-                    cur_row = nrow;
-                }
+            // the slot's hand-over values into registers, then the slot is re-armed, then they are summed
+            float v[CW][R];
+            float guard = 0.f;
 #pragma unroll
-                for (int nt = 0; nt < NT; ++nt) {
-                    racc[nt][0] += f[nt].x; racc[nt][1] += f[nt].y; racc[nt][2] += f[nt].z; racc[nt][3] += f[nt].w;
-                }
-                if (++nkt == KT) { nkt = 0; ++nrow; }
-            };
-            auto rearm = [&]() {
-                if (pt < t_end) {
-                    __syncwarp();
-                    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // the slot's generic accesses precede the async refill
-                    issue();
-                    ++issued;
-                }
-            };
-            if (NT == 1) {
-                // all fragments of the slot into registers first, so that the slot is re-armed before they are summed
-                float4 fr[RING_CW][NT];
-                float guard = 0.f;
+            for (int w = 0; w < CW; ++w) {
+                const float* f = reinterpret_cast<const float*>(slot_base + (size_t)w * tb);
 #pragma unroll
-                for (int w = 0; w < RING_CW; ++w) {
-                    fr[w][0] = w < len ? reinterpret_cast<const float4*>(slot_base + (size_t)w * tb)[lane] : make_float4(0.f, 0.f, 0.f, 0.f);
-                    guard += fr[w][0].x;
+                for (int r = 0; r < R; ++r) {
+                    v[w][r] = (w < len && lane + 32 * r < n_out && !(a.dbg & 16)) ? f[lane + 32 * r] : 0.f;
+                    guard += v[w][r];
                 }
-                asm volatile("" ::"f"(guard) : "memory");  // the loads have returned before the copy may overwrite the slot
-                rearm();
+            }
+            asm volatile("" ::"f"(guard) : "memory");  // the loads have returned before the copy may overwrite the slot
+            if (pt < t_end) {
+                __syncwarp();
+                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // the slot's generic accesses precede the async refill
+                issue();
+                ++issued;
+            }
 #pragma unroll
-                for (int w = 0; w < RING_CW; ++w)
-                    if (w < len) add_tile(fr[w]);
-            } else {
-                for (int w = 0; w < len; ++w) {
-                    float4 f[NT];
+            for (int w = 0; w < CW; ++w) {
+                if (w < len) {
+                    if (cs != cur_seg || nrow != cur_row) {
+                        if (cur_row >= 0 && !(a.dbg & 32)) ring_row_out<R>(ro, cur_seg, cur_row, racc);
 #pragma unroll
-                    for (int nt = 0; nt < NT; ++nt) f[nt] = reinterpret_cast<const float4*>(slot_base + (size_t)w * tb)[nt * 32 + lane];
-                    add_tile(f);
+                        for (int r = 0; r < R; ++r) racc[r] = 0.f;
+                        cur_seg = cs;
+                        cur_row = nrow;
+                    }
+#pragma unroll
+                    for (int r = 0; r < R; ++r) racc[r] += v[w][r];
+                    if (++nkt == KT) { nkt = 0; ++nrow; }
                 }
-                rearm();
             }
             ct += len;
             if (++cslot == a.stages) { cslot = 0; cpar ^= 1u; }
         }
-        if (ok) flush();
+        if (a.dbg & 128) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tk3));
+        if (ok && cur_row >= 0) ring_row_out<R>(ro, cur_seg, cur_row, racc);
+        if (a.dbg & 128) {
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tk4));
+            if (lane == 0 && (blockIdx.x == 0 || blockIdx.x == 77 || blockIdx.x == 147))
+                printf("cta %d: prime %llu wait %llu loop %llu tail %llu ns, chunks %d stages %d\n", blockIdx.x, tk1 - tk0, tk2 - tk1, tk3 - tk2, tk4 - tk3, retired, a.stages);
+        }
         if (!ok) {
             if (lane == 0) *reinterpret_cast<volatile int*>(a.err) = 1;  // host-mapped flag: a plain store
             // copies still in flight write into this CTA's shared memory: wait for them (bounded) before leaving
@@ -416,17 +453,17 @@ __global__ void __launch_bounds__(RING_THREADS, 1) gemv_ring_kernel(const RingAr
         q.cs = reinterpret_cast<float*>(smem + a.off_cs);
         q.ncols = a.m * a.digits; q.ncp = 8 * NT; q.digits = a.digits;
         // unused digit columns meet zero digits but their scales are read: keep them finite
-        for (int i = threadIdx.x; i < KT * 8 * NT; i += RING_CW * 32) q.cs[i] = 0.f;
-        ring_bar_consumers();
+        for (int i = threadIdx.x; i < KT * 8 * NT; i += CW * 32) q.cs[i] = 0.f;
+        ring_bar_consumers<CW>();
         auto block_sum = [&](float v) {
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
-            ring_bar_consumers();
+            ring_bar_consumers<CW>();
             if (lane == 0) norm_red[warp] = v;
-            ring_bar_consumers();
+            ring_bar_consumers<CW>();
             float s = 0.f;
 #pragma unroll
-            for (int w = 0; w < RING_CW; ++w) s += norm_red[w];
+            for (int w = 0; w < CW; ++w) s += norm_red[w];
             return s;
         };
         for (int mm = 0; mm < a.m; ++mm) {
@@ -435,7 +472,7 @@ __global__ void __launch_bounds__(RING_THREADS, 1) gemv_ring_kernel(const RingAr
             if (a.src == RING_SRC_RMS || a.src == RING_SRC_LN) {
                 if (a.src == RING_SRC_LN) {
                     float s = 0.f;
-                    for (int kt = warp; kt < KT; kt += RING_CW) {
+                    for (int kt = warp; kt < KT; kt += CW) {
                         float xv[8];
                         ring_load8(row + kt * 256 + lane * 8, xv);
                         s += ((xv[0] + xv[1]) + (xv[2] + xv[3])) + ((xv[4] + xv[5]) + (xv[6] + xv[7]));
@@ -443,7 +480,7 @@ __global__ void __launch_bounds__(RING_THREADS, 1) gemv_ring_kernel(const RingAr
                     mean = block_sum(s) / (float)a.k;
                 }
                 float ss = 0.f;
-                for (int kt = warp; kt < KT; kt += RING_CW) {
+                for (int kt = warp; kt < KT; kt += CW) {
                     float xv[8];
                     ring_load8(row + kt * 256 + lane * 8, xv);
 #pragma unroll
@@ -451,7 +488,7 @@ __global__ void __launch_bounds__(RING_THREADS, 1) gemv_ring_kernel(const RingAr
                 }
                 inv = 1.0f / sqrtf(block_sum(ss) / (float)a.k + a.eps);
             }
-            for (int kt = warp; kt < KT; kt += RING_CW) {
+            for (int kt = warp; kt < KT; kt += CW) {
                 const int k0 = kt * 256 + lane * 8;
                 float v[8];
                 ring_load8(row + k0, v);
@@ -478,7 +515,9 @@ __global__ void __launch_bounds__(RING_THREADS, 1) gemv_ring_kernel(const RingAr
                 ring_quantize_tile(v, lane, kt, mm, q);
             }
         }
-        ring_bar_consumers();  // every consumer sees the complete digits
+        ring_bar_consumers<CW>();  // every consumer sees the complete digits
+        RingLane<NT> L;
+        ring_lane_init<NT>(L, g, t, q.ncols, q.digits);
 
         bool ok = true;
         int ct = t_begin, cs = 0, slot = 0;
@@ -486,33 +525,44 @@ __global__ void __launch_bounds__(RING_THREADS, 1) gemv_ring_kernel(const RingAr
         while (ct < t_end) {
             const int len = chunk_len(ct, cs);
             if (warp < len && ok) {
-                ok = ring_wait(&full[slot], par);
-                if (ok) {
-                    const int dtype = a.seg[cs].dtype, tb = ring_tile_bytes(dtype);
+                ok = ring_wait(&full[slot], par, a.dbg & 2);
+                if (ok && !(a.dbg & 1)) {
+                    const int dtype = FMT ? FMT : a.seg[cs].dtype, tb = ring_tile_bytes(dtype);
                     const int kt = (ct + warp - a.seg_tile0[cs]) % KT;
                     uint8_t* tile = ring + (size_t)slot * a.stage_bytes + (size_t)warp * tb;
                     float acc[NT][4];
 #pragma unroll
                     for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
                     BFrag<NT> b;
-                    ring_load_b<NT>(q, kt, g, t, b);
-                    if (dtype == T_Q4_K) {
+                    ring_load_b<NT, FMT>(q, L, kt, t, dtype, b);
+                    if (FMT == T_Q4_K || (FMT == 0 && dtype == T_Q4_K)) {
                         Q4Regs r;
                         load_q4_k<false>(tile, lane, r);
                         compute_q4_k<NT>(r, b, lane, acc);
-                    } else if (dtype == T_Q6_K) {
+                    } else if (FMT == T_Q6_K || (FMT == 0 && dtype == T_Q6_K)) {
                         Q6Regs r;
                         load_q6_k<false>(tile, lane, r);
                         compute_q6_k<NT>(r, b, lane, acc);
-                    } else {
+                    } else if (FMT == 0) {
                         Q8Regs r;
                         load_q8_0<false>(tile, lane, r);
                         compute_q8_0<NT>(r, b, acc);
                     }
-                    __syncwarp();  // every lane has its tile bytes in registers: the fragment may overwrite them
-                    float4* frag = reinterpret_cast<float4*>(tile);
+                    __syncwarp();  // every lane has its tile bytes in registers: the hand-over values may overwrite them
+                    // outputs of this tile: for activation row mm the digit columns mm * digits .. are added; lane (g, t)
+                    // holds columns 8 nt + 2 t, + 1 of weight rows g (acc[.][0..1]) and g + 8 (acc[.][2..3])
+                    float* hand = reinterpret_cast<float*>(tile);
+                    for (int mm = 0; mm < a.m; ++mm) {
+                        float lo = 0.f, hi = 0.f;
 #pragma unroll
-                    for (int nt = 0; nt < NT; ++nt) frag[nt * 32 + lane] = make_float4(acc[nt][0], acc[nt][1], acc[nt][2], acc[nt][3]);
+                        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                            for (int e = 0; e < 2; ++e)
+                                if (L.own[nt][e] == mm) { lo += acc[nt][e]; hi += acc[nt][2 + e]; }
+                        lo += __shfl_xor_sync(0xFFFFFFFFu, lo, 1); lo += __shfl_xor_sync(0xFFFFFFFFu, lo, 2);
+                        hi += __shfl_xor_sync(0xFFFFFFFFu, hi, 1); hi += __shfl_xor_sync(0xFFFFFFFFu, hi, 2);
+                        if (t == 0) { hand[mm * 16 + g] = lo; hand[mm * 16 + 8 + g] = hi; }
+                    }
                 }
             }
             __syncwarp();
@@ -528,7 +578,7 @@ __global__ void __launch_bounds__(RING_THREADS, 1) gemv_ring_kernel(const RingAr
 cudaError_t RingScratch::alloc(int max_rows) {
     release();
     const int sms = device_sm_count();
-    cudaError_t e = cudaMalloc((void**)&part, (size_t)sms * 2 * 64 * sizeof(float));
+    cudaError_t e = cudaMalloc((void**)&part, (size_t)sms * 2 * RING_PART_FLOATS * sizeof(float));
     if (e == cudaSuccess) e = cudaMalloc((void**)&cnt, (size_t)(max_rows + 4) * sizeof(unsigned));
     if (e == cudaSuccess) e = cudaMemset(cnt, 0, (size_t)(max_rows + 4) * sizeof(unsigned));
     if (e == cudaSuccess) { rows_cap = max_rows + 4; ctas_cap = sms; }
@@ -543,16 +593,20 @@ void RingScratch::release() {
 
 // Fills the work split and the shared-memory layout; false when the launch does not fit this kernel.
 bool ring_plan(RingArgs& a, const RingScratch& sc, bool share_sm) {
-    if (a.k <= 0 || a.k % 256 != 0 || a.m < 1 || a.m > 4 || a.nseg < 1 || a.nseg > 3 || !sc.part || !sc.cnt) return false;
-    a.digits = a.m <= 2 ? 3 : 2;
+    (void)share_sm;
+    if (a.k <= 0 || a.k % 256 != 0 || a.m < 1 || a.m > RING_MAX_M || a.nseg < 1 || a.nseg > 3 || !sc.part || !sc.cnt) return false;
+    a.digits = 3;  // activations to 2^-23 of each block's maximum at every row count this kernel takes
     const int ncols = a.m * a.digits;
     const int nt = ncols <= 8 ? 1 : 2;
     a.kt = a.k / 256;
     int tiles = 0, rows = 0, max_tb = 0;
+    bool all_q4 = true, all_q6 = true;
     for (int s = 0; s < a.nseg; ++s) {
         const int dt = a.seg[s].dtype;
         if (dt != T_Q4_K && dt != T_Q6_K && dt != T_Q8_0) return false;
         if (a.seg[s].n <= 0) return false;
+        all_q4 = all_q4 && dt == T_Q4_K;
+        all_q6 = all_q6 && dt == T_Q6_K;
         a.seg_tile0[s] = tiles;
         a.seg_row0[s] = rows;
         const int r = (a.seg[s].n + 15) / 16;
@@ -573,35 +627,47 @@ bool ring_plan(RingArgs& a, const RingScratch& sc, bool share_sm) {
     a.off_xq = off; off += a.kt * ncols * 256;
     off = (off + 127) / 128 * 128;
     a.off_stage = off;
-    a.stage_bytes = (RING_CW * max_tb + 127) / 128 * 128;
-    const int budget = share_sm ? RING_SMEM_SHARED_SM : RING_SMEM_MAX;
-    int stages = (budget - off) / a.stage_bytes;
-    if (stages < 2) stages = (RING_SMEM_MAX - off) / a.stage_bytes;  // does not fit beside a second CTA: take the SM alone
-    if (stages < 2) return false;
-    a.stages = std::min(stages, RING_MAX_STAGES);
-    a.smem_total = off + a.stages * a.stage_bytes;
-    a.fix_part = sc.part;
-    a.fix_cnt = sc.cnt;
-    return true;
+    static const int forced = [] { const char* e = std::getenv("SAPIENT_RING_STAGES"); return e ? atoi(e) : 0; }();
+    static const int dbg = [] { const char* e = std::getenv("SAPIENT_RING_DEBUG"); return e ? atoi(e) : 0; }();
+    a.dbg = dbg;
+    // the wide single-format instance when its ring still has two slots, else the 15-consumer instance
+    const int fmt = all_q4 ? T_Q4_K : all_q6 ? T_Q6_K : 0;
+    for (int cw : {fmt && nt == 1 && !(dbg & 64) ? RING_CW_SINGLE : RING_CW_MIXED, RING_CW_MIXED}) {
+        a.cw = cw;
+        a.fmt = cw == RING_CW_SINGLE ? fmt : 0;
+        a.stage_bytes = (cw * max_tb + 127) / 128 * 128;
+        const int stages = (RING_SMEM_MAX - off) / a.stage_bytes;
+        if (stages < 2) continue;
+        a.stages = std::min(stages, RING_MAX_STAGES);
+        if (forced >= 2) a.stages = std::min(a.stages, forced);
+        a.smem_total = off + a.stages * a.stage_bytes;
+        a.fix_part = sc.part;
+        a.fix_cnt = sc.cnt;
+        return true;
+    }
+    return false;
 }
 
-static PerDeviceOnce g_ring_attr[2];
+template <int NT, int CW, int FMT>
+static cudaError_t ring_launch_instance(const RingArgs& a, int grid, cudaStream_t st) {
+    static PerDeviceOnce attr;
+    cudaError_t e = attr.run([] { return cudaFuncSetAttribute(gemv_ring_kernel<NT, CW, FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, RING_SMEM_MAX); });
+    if (e != cudaSuccess) return e;
+    return launch_pdl(gemv_ring_kernel<NT, CW, FMT>, dim3(grid), dim3((CW + 1) * 32), (size_t)a.smem_total, st, a);
+}
 
 cudaError_t launch_gemv_ring(RingArgs& a, cudaStream_t st) {
     const int nt = a.m * a.digits <= 8 ? 1 : 2;
     const int sms = device_sm_count();
     // at least one full ring slot of work per CTA
-    int grid = std::min(sms, std::max(1, a.total_tiles / RING_CW));
+    const int grid = std::min(sms, std::max(1, a.total_tiles / a.cw));
     a.err = imma_timeout_flag();
     if (!a.err) return cudaErrorInvalidValue;
-    cudaError_t e = g_ring_attr[nt - 1].run([nt] {
-        return nt == 1 ? cudaFuncSetAttribute(gemv_ring_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, RING_SMEM_MAX)
-                       : cudaFuncSetAttribute(gemv_ring_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, RING_SMEM_MAX);
-    });
-    if (e != cudaSuccess) return e;
-    imma_note_ring_launch();
-    e = nt == 1 ? launch_pdl(gemv_ring_kernel<1>, dim3(grid), dim3(RING_THREADS), (size_t)a.smem_total, st, a)
-                : launch_pdl(gemv_ring_kernel<2>, dim3(grid), dim3(RING_THREADS), (size_t)a.smem_total, st, a);
+    cudaError_t e;
+    if (nt == 2) e = ring_launch_instance<2, RING_CW_MIXED, 0>(a, grid, st);
+    else if (a.cw == RING_CW_SINGLE && a.fmt == T_Q4_K) e = ring_launch_instance<1, RING_CW_SINGLE, T_Q4_K>(a, grid, st);
+    else if (a.cw == RING_CW_SINGLE && a.fmt == T_Q6_K) e = ring_launch_instance<1, RING_CW_SINGLE, T_Q6_K>(a, grid, st);
+    else e = ring_launch_instance<1, RING_CW_MIXED, 0>(a, grid, st);
     if (e != cudaSuccess) return e;
     return count_launch_and_check();
 }

@@ -65,12 +65,13 @@ int imma_rows_per_pass();
 // they run out. These read and clear it on the current device: 1 = expired since the last call, 0 = none, -1 = CUDA error.
 int imma_take_timeout();
 int tc5_take_timeout();
-// ── Persistent ring GEMV for steps of 1-4 rows (gemv_ring.cu) ──
+// ── Persistent ring GEMV for steps of 1-5 rows (gemv_ring.cu) ──
 // Where the activations of a launch come from: f32 rows as they are, or through the operation that precedes the matrix
 // in the layer, applied by every CTA on its own copy.
 enum RingSrc : int { RING_SRC_PLAIN = 0, RING_SRC_RMS = 1, RING_SRC_LN = 2, RING_SRC_SWIGLU = 3, RING_SRC_GELU = 4 };
 constexpr int RING_MAX_STAGES = 6;
-// Scratch of tile rows shared between CTAs: two 16 x 4 partial blocks per CTA and one arrival counter per tile row of
+constexpr int RING_MAX_M = 5;  // activation rows per launch: three digit columns each, two 8-column n-tiles
+// Scratch of tile rows shared between CTAs: two 16 x 5 partial blocks per CTA and one arrival counter per tile row of
 // the largest launch. Launches that may overlap on the device must not share one (one per engine / op-level weight).
 struct RingScratch {
     float* part = nullptr;
@@ -82,7 +83,7 @@ struct RingScratch {
 struct RingArgs {
     ImmaSeg seg[3];       // wt, bias, y, dtype, n, ldy of up to three matrices sharing the activations (bpt unused: 8)
     int nseg;
-    int k, m;             // k % 256 == 0, 1 <= m <= 4
+    int k, m;             // k % 256 == 0, 1 <= m <= RING_MAX_M
     int src;              // RingSrc
     const float* x;       // [m][ldx] f32; SWIGLU: gate at column 0 and up at column k of each row; GELU: fc1 output
     int ldx;
@@ -95,17 +96,19 @@ struct RingArgs {
     int digits, kt, total_tiles;
     int seg_tile0[4], seg_row0[4];
     int stage_bytes, stages, smem_total;
+    int cw, fmt;          // consumer warps of the instance; its single weight format (0: mixed)
     int off_bar, off_flush, off_cs, off_rec32, off_rec16, off_xq, off_stage;
     float* fix_part;
     unsigned* fix_cnt;
     int* err;
+    int dbg;              // experiments: bit 0 = consumers skip the arithmetic
 };
 // One-time per-device set-up of the ring kernel's error flag (host-mapped memory): call before the first launch on a
 // device, outside stream capture (engine finalize and weight upload do).
 cudaError_t ring_device_init();
 // share_sm: size the ring so that two CTAs fit an SM (this kernel's and the next kernel's prologue under programmatic
 // dependent launch). False when the launch cannot use this kernel (shape, formats, shared memory, scratch size).
-bool ring_plan(RingArgs& a, const RingScratch& sc, bool share_sm = true);
+bool ring_plan(RingArgs& a, const RingScratch& sc, bool share_sm = false);
 cudaError_t launch_gemv_ring(RingArgs& a, cudaStream_t st);
 
 // Producers that emit the digits of a GEMV input directly (a: planned ImmaArgs; a.m rows, a.k columns):

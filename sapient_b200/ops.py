@@ -163,7 +163,8 @@ def argmax(logits, device: int = 0) -> np.ndarray:
 
 
 def set_gemv_path(path: int) -> None:
-    """0: tensor-core GEMV on tile-repacked weights (default); 1: CUDA-core GEMV on raw blocks."""
+    """0: tensor-core GEMV on tile-repacked weights (default); 1: CUDA-core GEMV on raw blocks; 3: per-warp streaming
+    variant; 4: bulk-copy ring GEMV for calls of 1-5 rows."""
     check(lib().sp_cuda_set_gemv_path(path))
 
 
