@@ -74,11 +74,12 @@ int32_t sp_cuda_matmul_nt_dev(const SpWeight* w, const float* x_dev, int64_t m, 
  * The reference's GPU backend has no such condition to report (its wgpu queue has no device-side waits,
  * crates/sapient-backends/wgpu/src/context.rs); this is the error channel of the asynchronous device-pointer calls. */
 int32_t sp_cuda_check_kernels(int32_t device);
-/* Precision of the activations in the tensor-core GEMV passes (steps that do not take the 17+-row GEMM). The reference
- * multiplies f32 activations (kernels/matmul.rs:862-943); this backend splits each activation into int8 digits with one
- * power-of-two scale per 256 (Q8_0: 32) columns. 0 (default): three digits (2^-23 of the block maximum) for steps of
- * 1-2 rows, two digits (2^-15) and 16 rows per pass above. 1: three digits always, 10 rows per pass. Process-wide;
- * engines drop their captured step graphs when it changes (sp_cuda_engine_set_graphs off/on). */
+/* Precision of the activations in the tensor-core GEMV passes. The reference multiplies f32 activations
+ * (kernels/matmul.rs:862-943); this backend splits each activation into int8 digits with one power-of-two scale per 256
+ * (Q8_0: 32) columns, so that the products with the integer weights are exact. 1 (default): three digits (2^-23 of the
+ * block maximum) at every row count, 10 rows per pass. 0: three digits for steps of 1-2 rows, two digits (2^-15) and 16
+ * rows per pass above — fewer passes for batched steps at ~1e-4 relative error per product. Process-wide; engines drop
+ * their captured step graphs when it changes (sp_cuda_engine_set_graphs off/on). */
 int32_t sp_cuda_set_activation_digits(int32_t mode);
 /* Which GEMV kernel runs (process-wide; op-level calls — engines have sp_cuda_engine_set_ring):
  *   0 (default) and 2: the tensor-core GEMV with one CTA per 16-row tile row;
@@ -224,9 +225,12 @@ int32_t sp_cuda_spec_greedy(SpEngine* target, SpEngine* draft, const uint32_t* p
 int32_t sp_cuda_engine_synchronize(SpEngine* e);
 /* Replay decode steps as CUDA graphs (default on). */
 int32_t sp_cuda_engine_set_graphs(SpEngine* e, int32_t on);
-/* Steps of 17 rows and more (prefill chunks, batched decode) on the tcgen05 GEMM, whose operands are rounded to fp16
- * (default on; off: tensor-core GEMV passes on integer digits, slower, closer to the reference's f32 arithmetic — see
- * sp_cuda_set_activation_digits). Drops the captured step graphs. */
+/* Steps of 17 rows and more (prefill chunks, batched decode) on the tcgen05 GEMM: each weight tile is dequantised once
+ * and multiplied with all rows on the 5th-generation tensor cores, operands rounded to fp16 (~3e-4 relative per product,
+ * inside the 1e-3 per-op bar). Default OFF: on the full-size models those roundings move the final logits by up to 4e-2
+ * (8B shape, 128-token prompt), outside the 2e-2 bar, so such steps run as integer-digit GEMV passes unless the caller
+ * asks for speed: a 512-token prefill of the 8B shape takes 10 ms with the GEMM on, 7 times that with it off. Drops the
+ * captured step graphs. */
 int32_t sp_cuda_engine_set_large_m_gemm(SpEngine* e, int32_t on);
 /* Steps of 1-5 rows on the bulk-copy ring GEMV with the preceding norm / activation fused into it (default off: it
  * measures slower than the default kernels). Drops the captured step graphs. */

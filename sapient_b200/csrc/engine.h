@@ -94,7 +94,10 @@ class Engine {
     bool trace_on = false;
     bool use_graphs = true;
     bool use_ring = false;     // steps of 1-5 rows on the bulk-copy ring GEMV (opt-in: measured slower than the tile-row kernels)
-    bool use_tc5 = true;       // steps of TC5_MIN_M rows and more on the tcgen05 GEMM (false: always 16-row GEMV passes)
+    // Steps of TC5_MIN_M rows and more on the tcgen05 GEMM, whose operands are rounded to fp16 (~3e-4 per product: inside
+    // the per-op bar, but on a 32-layer model the final logits then leave the 2e-2 bar). Off by default: such steps run as
+    // integer-digit GEMV passes; sp_cuda_engine_set_large_m_gemm turns the fast path on.
+    bool use_tc5 = false;
     bool graph_step_ = false;  // a step is being captured: its kernels may take positions only from device memory
     // 1 (default): new K / V rows get the reference's Q8_0 cache rounding before they are stored as fp16 (head_dim % 32
     // == 0, where the reference keeps a Q8_0 cache); 0: plain fp16 rounding. Change only while the caches are empty.

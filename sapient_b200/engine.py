@@ -41,10 +41,11 @@ class ForwardEngine:
     # ── construction ────────────────────────────────────────────────────────
     @classmethod
     def from_weights(cls, cfg: dict, weights: dict, device: int = 0, max_batch: int = 1, max_tokens: int = 256,
-                     kv_pages: int = 0, tp_rank: int = 0, tp_size: int = 1) -> "ForwardEngine":
+                     kv_pages: int = 0, tp_rank: int = 0, tp_size: int = 1, fast_large_m: bool = False) -> "ForwardEngine":
         """cfg: arch ('llama'|'qwen2'|'phi2'), n_layers, hidden, n_heads, n_kv_heads, head_dim, ffn, vocab,
         max_ctx, rotary_dim (optional), norm_eps, rope_theta. weights: name -> (ggml dtype, dims, uint8 bytes)
-        with HF names and [out, in] dims, as the reference's GGUF name map yields."""
+        with HF names and [out, in] dims, as the reference's GGUF name map yields. fast_large_m: steps of 17 rows and
+        more on the tcgen05 GEMM with fp16 operands (see set_large_m_gemm)."""
         d = SpModelDesc()
         d.arch = 1 if cfg["arch"] in ("phi2", "phi") else 0
         d.n_layers, d.hidden, d.n_heads, d.n_kv_heads = cfg["n_layers"], cfg["hidden"], cfg["n_heads"], cfg["n_kv_heads"]
@@ -65,7 +66,10 @@ class ForwardEngine:
         except Exception:
             lib().sp_cuda_engine_destroy(h)
             raise
-        return cls(h, d)
+        eng = cls(h, d)
+        if fast_large_m:
+            eng.set_large_m_gemm(True)
+        return eng
 
     @classmethod
     def from_gguf(cls, path: str, device: int = 0, max_ctx: int = 0, max_batch: int = 1) -> "ForwardEngine":
@@ -224,7 +228,8 @@ class ForwardEngine:
         check(lib().sp_cuda_engine_set_graphs(self._h, int(on)))
 
     def set_large_m_gemm(self, on: bool) -> None:
-        """Steps of 17 rows and more on the tcgen05 GEMM with fp16 operands (default) or as integer-digit GEMV passes."""
+        """Steps of 17 rows and more on the tcgen05 GEMM with fp16 operands (fast; final logits of full-size models may
+        leave the 2e-2 bar) or, the default, as integer-digit GEMV passes."""
         check(lib().sp_cuda_engine_set_large_m_gemm(self._h, int(on)))
 
     def set_ring(self, on: bool) -> None:

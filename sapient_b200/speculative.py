@@ -182,8 +182,8 @@ def generate_greedy(target, draft, prompt: Sequence[int], max_new_tokens: int, k
     truncate_cache), the host-side statement of the schedule sp_cuda_spec_greedy runs inside the library: the token
     committed last is fed to the target TOGETHER with the k drafts (one k + 1 row verify pass per round instead of the
     reference's k-row pass plus a single-token pass, speculative.rs:557,606), drafts are kept while they equal the
-    target's arg-max, the target's pick after them is committed too. Works with any engine pair (the CPU oracle's
-    included), so the CUDA loop can be checked against it token for token. Returns (new tokens, GreedySpecStats)."""
+    target's arg-max, the target's pick after them is committed too. Works with any engine pair that offers those three calls,
+    so the loop inside the library can be checked against it token for token. Returns (new tokens, GreedySpecStats)."""
     prompt = [int(t) for t in prompt]
     if not prompt:
         raise ValueError("generate_greedy: empty prompt")

@@ -16,7 +16,7 @@ pytestmark = pytest.mark.gpu
 def test_tiled_prefill_attention_matches_per_token_kernel_and_oracle(oracle, name, n_prompt):
     cfg, W = tiny_model(name, max_ctx=256)
     ids = np.random.default_rng(n_prompt).integers(0, cfg["vocab"], n_prompt).astype(np.uint32)
-    big = ForwardEngine.from_weights(cfg, W, max_tokens=256)     # whole prompt in one chunk: tiled kernel
+    big = ForwardEngine.from_weights(cfg, W, max_tokens=256, fast_large_m=True)     # whole prompt in one chunk: tiled kernel + tcgen05 GEMM
     small = ForwardEngine.from_weights(cfg, W, max_tokens=32)    # chunks of 32: per-token kernel
     big.set_graphs(False)  # direct launches: the tiled kernel takes the first position as an argument
     for e in (big, small):
@@ -42,8 +42,8 @@ def test_replayed_step_graphs_do_not_freeze_positions():
     cfg, W = tiny_model("tiny_llama", max_ctx=256)
     rng = np.random.default_rng(9)
     first, second = (rng.integers(0, cfg["vocab"], 40).astype(np.uint32) for _ in range(2))
-    graphs = ForwardEngine.from_weights(cfg, W, max_tokens=64)
-    direct = ForwardEngine.from_weights(cfg, W, max_tokens=64)
+    graphs = ForwardEngine.from_weights(cfg, W, max_tokens=64, fast_large_m=True)
+    direct = ForwardEngine.from_weights(cfg, W, max_tokens=64, fast_large_m=True)
     direct.set_graphs(False)
     for e in (graphs, direct):
         e.set_kv_rounding(False)
