@@ -152,6 +152,88 @@ def cpu_decode_rate(cfg, W, steps: int, budget_s: float, prompt_len: int = CPU_P
     return done / dt, done, threads, fed
 
 
+B32_BATCH, B32_PROMPT, B32_WARM, B32_STEPS = 32, 1024, 4, 24
+
+
+def batch32_section(cfg, W, wbytes: int, local: int, rank: int, world: int, stream, barrier, peaks) -> dict:
+    """The other half of the metric: 32 sequences with 1024-token prompts decoded together over the paged fp16 KV cache
+    (the tensor-parallel configuration of the benchmark at its own sizes; one GPU holds it whole, N GPUs split it).
+    Two timings of the same step at context ~1024: the default exact path (integer-digit GEMV passes of 10 rows) and
+    the opt-in tcgen05 GEMM (fp16 operands). Prompts are prefilled untimed through the tcgen05 path either way."""
+    import torch
+
+    from sapient_b200.engine import ForwardEngine
+
+    eng = ForwardEngine.from_weights(cfg, W, device=local, max_batch=B32_BATCH, max_tokens=512, tp_rank=rank, tp_size=world)
+    if world > 1:
+        eng.tp_connect()
+    eng.set_stream(stream.cuda_stream)
+    rng = np.random.default_rng(32)
+    eng.set_large_m_gemm(world == 1)  # untimed prefill: fast path where it exists (single GPU)
+    first = np.empty(B32_BATCH, np.uint32)
+    for s in range(B32_BATCH):
+        lg = eng.forward_slot(s, rng.integers(0, cfg["vocab"], B32_PROMPT).astype(np.uint32))
+        first[s] = int(np.flatnonzero(lg == lg.max())[-1]) + eng.vocab_first
+    if world > 1:
+        # every rank must feed the same first tokens: take rank 0's choice of its own vocabulary slice (any valid id does)
+        import torch.distributed as dist
+
+        t = torch.from_numpy(first.astype(np.int64)).to(f"cuda:{local}")
+        dist.broadcast(t, 0)
+        first = t.cpu().numpy().astype(np.uint32)
+    slots = list(range(B32_BATCH))
+    out = {"batch": B32_BATCH, "prompt_len": B32_PROMPT, "steps": B32_STEPS, "model": MODEL, "kv": "fp16 paged/16"}
+    kv_per_pos = 2 * cfg["n_layers"] * cfg["n_kv_heads"] * cfg["head_dim"] * 2
+    modes = [("exact", False)] + ([("tcgen05", True)] if world == 1 else [])
+    for tag, fast in modes:
+        for s in slots:
+            eng.truncate_cache(B32_PROMPT, s)
+        eng.set_large_m_gemm(fast)
+        toks = eng.decode_greedy(first, slots, B32_WARM)
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        ev0.record(stream)
+        eng.decode_greedy(toks[-1], slots, B32_STEPS, fetch=False)
+        ev1.record(stream)
+        barrier()
+        ms = ev0.elapsed_time(ev1)
+        if world > 1:
+            import torch.distributed as dist
+
+            t = torch.tensor([ms], device=f"cuda:{local}", dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t[0])
+        ctx_mid = B32_PROMPT + B32_WARM + B32_STEPS // 2
+        step_bytes = (wbytes + B32_BATCH * ctx_mid * kv_per_pos) / world
+        gbs = step_bytes / 1e9 / (ms / B32_STEPS / 1e3)
+        out[tag] = {"tokens_per_s": B32_BATCH * B32_STEPS / (ms / 1e3), "ms_per_step": ms / B32_STEPS, "context": ctx_mid,
+                    "bytes_per_step_per_gpu": int(step_bytes), "achieved_gbs_per_gpu": gbs, "frac_of_measured_peak": gbs / peaks["hbm_gbs"],
+                    "frac_of_8TBs": gbs / 8000.0}
+    out["exact"]["path"] = "integer-digit tensor-core GEMV passes of 10 rows (three digits), the default"
+    if "tcgen05" in out:
+        out["tcgen05"]["path"] = "tcgen05 / TMEM dequant GEMM, fp16 operands (opt-in)"
+    eng.close()
+    return out
+
+
+def sweep_section() -> list:
+    """Operator sweep of the standalone dequant-matmul: achieved GB/s at M = 1 and TFLOP/s at M = 512 for the four
+    benchmark shapes and the three block formats (weights rotated through more than twice the L2, CUDA events on the
+    launching stream)."""
+    from sapient_b200 import sweep
+
+    rows = []
+    for dt in ("q4_k", "q6_k", "q8_0"):
+        for n, k in sweep.SHAPES:
+            big = n * k > (1 << 28)
+            r1 = sweep.run_case(dt, n, k, 1, 24 if big else 60, 3, None, 0)
+            r512 = sweep.run_case(dt, n, k, 512, 8 if big else 20, 2, 2 if big else None, 0)
+            rows.append({"dtype": dt, "n": n, "k": k, "m1_us": round(r1["us"], 2), "m1_gbs": round(r1["gbs"], 1),
+                         "m1_frac_of_measured_peak": round(r1["frac_of_hbm_peak"], 3), "m512_us": round(r512["us"], 1),
+                         "m512_tflops": round(r512["tflops"], 1)})
+    return rows
+
+
 def config_dict(cfg, n_gpus: int, mode: str) -> dict:
     return {"workload": f"{MODEL} (Llama-3-8B-shaped, L32 h4096 32q/8kv hd128 ffn14336 V128256) Q4_K_M-like GGUF blocks, "
                         f"batch-1 greedy decode after a {PROMPT}-token random prompt, fp16 paged KV (16-token pages)",
@@ -189,6 +271,8 @@ def main() -> None:
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--quick", action="store_true", help="prefill + warm-up + timed device loop only (for profiler runs)")
+    ap.add_argument("--no-batch32", action="store_true", help="skip the 32-sequence decode section")
+    ap.add_argument("--no-sweep", action="store_true", help="skip the operator sweep section")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -295,6 +379,15 @@ def main() -> None:
     gemv_n = (4 * cfg["n_layers"] + 1) * P
     eng.truncate_cache(PROMPT)
 
+    # ── the other sections of the metric (extra keys of the same line) ──
+    eng.close()
+    peaks_now, _ = measured_peaks()
+    sections = {}
+    if not args.no_batch32:
+        sections["batch32"] = batch32_section(cfg, W, wbytes, local, rank, world, stream, barrier, peaks_now)
+    if not args.no_sweep and world == 1:
+        sections["sweep"] = sweep_section()
+
     t = torch.tensor([dev_ms, e2e_s * 1000.0], device=f"cuda:{local}", dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -329,6 +422,10 @@ def main() -> None:
                               "frac_of_measured_peak": ((wbytes + kv_bytes) / world / (peaks["hbm_gbs"] * 1e9) * 1e3) / (dev_ms / K)},
             "family_ms_per_step": fam_ms,
         }
+        if sections.get("batch32"):
+            line["batch32"] = sections["batch32"]
+        if sections.get("sweep"):
+            line["sweep"] = sections["sweep"]
         if not args.no_cpu_baseline:
             rate, done, threads, fed = cpu_decode_rate(cfg, W, 8, 25.0)
             line["cpu_baseline"] = {"value": rate, "unit": "tok/s", "cores": threads, "kind": "port",

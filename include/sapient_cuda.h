@@ -178,6 +178,14 @@ int32_t sp_cuda_engine_vocab_local(const SpEngine* e, int32_t* rows, int32_t* fi
  * block, and connecting with the blocks of all ranks in rank order instead of IPC handles. */
 int32_t sp_cuda_engine_tp_block(SpEngine* e, void** block);
 int32_t sp_cuda_engine_tp_connect_local(SpEngine* e, void* const* blocks, int32_t n_ranks);
+/* How long a kernel waits for a peer's partial rows before it gives up (default 5000 ms; the step then ends with
+ * SP_ERR_COMM). Long enough for a peer that is still capturing its first step graph or finishing a prefill; a
+ * supervisor that detects failures on the host can lower it. Takes effect with the next launch. */
+int32_t sp_cuda_engine_tp_set_wait_ms(SpEngine* e, int32_t ms);
+/* After SP_ERR_COMM, or to restart a group: exchange counters, arrival marks and the sticky error flag back to their
+ * initial state. EVERY rank calls it, with a host-side barrier before (no rank still inside a step) and after (no rank
+ * starts a step before all have cleared). The KV caches are untouched: truncate or reset them as the caller sees fit. */
+int32_t sp_cuda_engine_tp_reset(SpEngine* e);
 /* The slice rank `rank` of `size` keeps of one full tensor (host only, no device needed): writes the slice to out
  * (may be NULL to query sizes), its dims to out_dims[ndim] and its byte size to *out_bytes. Replicated tensors come
  * back whole. vocab bounds the rows of lm_head.weight. */

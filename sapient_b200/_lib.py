@@ -58,6 +58,8 @@ SIGNATURES = {
     "sp_cuda_engine_tp_handle": (_i32, [_vp, _vp, C.c_size_t]),
     "sp_cuda_engine_tp_connect": (_i32, [_vp, _vp, _i32]),
     "sp_cuda_engine_vocab_local": (_i32, [_vp, _vp, _vp]),
+    "sp_cuda_engine_tp_set_wait_ms": (_i32, [_vp, _i32]),
+    "sp_cuda_engine_tp_reset": (_i32, [_vp]),
     "sp_cuda_engine_tp_block": (_i32, [_vp, _vp]),
     "sp_cuda_engine_tp_connect_local": (_i32, [_vp, _vp, _i32]),
     "sp_cuda_tp_shard": (_i32, [C.c_char_p, _i32, _vp, _i32, _vp, C.c_size_t, _i32, _i32, _i64, _vp, C.c_size_t, _vp, _vp]),

@@ -674,6 +674,20 @@ int32_t sp_cuda_engine_set_graphs(SpEngine* e, int32_t on) {
     return SP_OK;
 }
 
+int32_t sp_cuda_engine_tp_set_wait_ms(SpEngine* e, int32_t ms) {
+    API_BEGIN
+    if (!e) { set_error("null engine"); return SP_ERR_ARG; }
+    return e->e->tp_set_wait_ms(ms);
+    API_END
+}
+
+int32_t sp_cuda_engine_tp_reset(SpEngine* e) {
+    API_BEGIN
+    if (!e) { set_error("null engine"); return SP_ERR_ARG; }
+    return e->e->tp_reset();
+    API_END
+}
+
 int32_t sp_cuda_engine_set_large_m_gemm(SpEngine* e, int32_t on) {
     API_BEGIN
     if (!e) { set_error("null engine"); return SP_ERR_ARG; }

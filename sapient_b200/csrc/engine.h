@@ -82,6 +82,8 @@ class Engine {
     int tp_connect_ptrs(void* const* blocks, int n); // the same for engines of ONE process: device pointers, no IPC
     void* tp_block() const { return tp_block_; }
     int tp_check();                                 // SP_ERR_COMM if a wait on a peer gave up
+    int tp_set_wait_ms(int ms);                     // bound of the device-side waits on peers
+    int tp_reset();                                 // counters, marks and the sticky flag back to the initial state
     // After a stream synchronise: SP_ERR_CUDA if a bounded mbarrier wait of one of this device's kernels ran out since
     // the last check (the kernel's outputs are then stale), else tp_check().
     int device_check();
@@ -138,6 +140,9 @@ class Engine {
     int gemm_xh(int m, int k, const DevTensor* w0, const float* b0, float* y0, int ldy0, const DevTensor* w1 = nullptr,
                 const float* b1 = nullptr, float* y1 = nullptr, const DevTensor* w2 = nullptr, const float* b2 = nullptr,
                 float* y2 = nullptr, const float* res = nullptr);
+    // The same for a column-split matrix (o_proj, down_proj) whose product is added into the residual stream x_: on one
+    // GPU in place; under tensor parallelism the partial product goes to scratch and is pushed to every rank.
+    int gemm_xh_sum(int m, int k, const DevTensor* w, const float* b);
     size_t tp_block_bytes() const;
     int tp_alloc();
     void tp_release();
@@ -146,6 +151,7 @@ class Engine {
     TpDev* d_tp_ = nullptr;         // device copy of the peer table
     uint8_t* tp_peer_[TP_MAX_RANKS] = {};
     bool tp_connected_ = false;
+    uint64_t tp_wait_ns_ = TP_WAIT_NS_DEFAULT;
     bool tp_pending_ = false;       // partial rows have been pushed, x_ still lacks their sum
     // decode_greedy returned without waiting (tokens_out == null): copies out of the pinned staging buffers may still be
     // queued on the stream. Every call that rewrites those buffers drains the stream first.

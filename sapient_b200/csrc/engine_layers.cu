@@ -147,7 +147,7 @@ int Engine::try_ring(bool* done, int m, int k, int src, const float* x, int ldx,
 }
 
 bool Engine::big_m(int m, int k, const DevTensor* w0, const DevTensor* w1, const DevTensor* w2) const {
-    if (m < TC5_MIN_M || !use_tc5 || d.tp_size > 1 || !ws_.xh || (size_t)m * k > ws_.xh_elems) return false;
+    if (m < TC5_MIN_M || !use_tc5 || !ws_.xh || (size_t)m * k > ws_.xh_elems) return false;
     const DevTensor* ws[3] = {w0, w1, w2};
     for (int i = 0; i < 3 && ws[i]; ++i)
         if (!ws[i]->tiled || !tc5_supported(ws[i]->dtype, k)) return false;
@@ -163,6 +163,16 @@ int Engine::gemm_xh(int m, int k, const DevTensor* w0, const float* b0, float* y
     int ns = 0;
     for (int i = 0; i < 3 && ws[i]; ++i) segs[ns++] = Tc5Seg{ws[i]->tiled, ys[i], bs[i], ws[i]->dtype, (int)ws[i]->dims[0]};
     SP_LAUNCH(F_GEMV, launch_gemm_tc5_multi(segs, ns, k, ws_.xh, m, ldy0, res, ldy0, stream, &ws_.tc5));
+    return SP_OK;
+}
+
+int Engine::gemm_xh_sum(int m, int k, const DevTensor* w, const float* b) {
+    if (d.tp_size <= 1) return gemm_xh(m, k, w, b, x_, d.hidden, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, x_);
+    if (!tp_connected_) { set_error("tensor-parallel engine used before tp_connect"); return SP_ERR_STATE; }
+    // the partial product of this rank's columns (the bias once, on rank 0) to scratch, then to every rank's receive area
+    SP_TRY(gemm_xh(m, k, w, d.tp_rank == 0 ? b : nullptr, h_, d.hidden));
+    SP_LAUNCH(F_GEMV, launch_tp_push(h_, d.hidden, m, d.hidden, d_tp_, stream));
+    tp_pending_ = true;
     return SP_OK;
 }
 
@@ -201,7 +211,7 @@ int Engine::attention_and_oproj(const LayerW& w, int l, int T) {
     for (int i = 1; one_seq && i < T; ++i) one_seq = p_slot_[i] == p_slot_[0] && p_pos_[i] == p_pos_[0] + i;
     if (one_seq && big_m(T, H * hd, w.o)) {
         SP_LAUNCH(F_ATTN, launch_attention_prefill(qkv_, qkv_ld, nullptr, H * hd, T, H, p_slot_[0], p_pos_[0], kv_, l, scale, stream, ws_.xh));
-        return gemm_xh(T, H * hd, w.o, w.ob, x_, hid, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, x_);
+        return gemm_xh_sum(T, H * hd, w.o, w.ob);
     }
     if (one_seq) {
         SP_LAUNCH(F_ATTN, launch_attention_prefill(qkv_, qkv_ld, attn_, H * hd, T, H, p_slot_[0], p_pos_[0], kv_, l, scale, stream));
@@ -221,6 +231,7 @@ int Engine::layer_llama(const LayerW& w, int l, int T) {
                     qkv_ + (size_t)(H + Hkv) * hd));
     if (ringed) {
     } else if (big_m(T, hid, w.q, w.k, w.v)) {
+        SP_TRY(tp_resolve(T));
         SP_LAUNCH(F_NORM, launch_rms_norm_f16(x_, w.n1w, T, hid, d.norm_eps, ws_.xh, stream));
         SP_TRY(gemm_xh(T, hid, w.q, w.qb, qkv_, qkv_ld, w.k, w.kb, qkv_ + (size_t)H * hd, w.v, w.vb, qkv_ + (size_t)(H + Hkv) * hd));
     } else if (all_tiled(w.q, w.k, w.v) && plan_digits(T, hid, ia)) {
@@ -238,6 +249,7 @@ int Engine::layer_llama(const LayerW& w, int l, int T) {
     SP_TRY(try_ring(&ringed, T, hid, RING_SRC_RMS, x_, hid, w.n2w, nullptr, w.gate, nullptr, gu_, 2 * ffn, w.up, nullptr, gu_ + ffn));
     if (ringed) {
     } else if (big_m(T, hid, w.gate, w.up)) {
+        SP_TRY(tp_resolve(T));
         SP_LAUNCH(F_NORM, launch_rms_norm_f16(x_, w.n2w, T, hid, d.norm_eps, ws_.xh, stream));
         SP_TRY(gemm_xh(T, hid, w.gate, nullptr, gu_, 2 * ffn, w.up, nullptr, gu_ + ffn));
     } else if (all_tiled(w.gate, w.up) && plan_digits(T, hid, ia)) {
@@ -253,7 +265,7 @@ int Engine::layer_llama(const LayerW& w, int l, int T) {
     if (ringed) {
     } else if (big_m(T, ffn, w.down)) {
         SP_LAUNCH(F_ELEM, launch_act_f16(gu_, 2 * ffn, ffn, T, 0, ws_.xh, stream));
-        SP_TRY(gemm_xh(T, ffn, w.down, nullptr, x_, hid, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, x_));
+        SP_TRY(gemm_xh_sum(T, ffn, w.down, nullptr));
     } else if (all_tiled(w.down) && plan_digits(T, ffn, ia)) {
         SP_LAUNCH(F_ELEM, launch_act_fn_quant(gu_, 2 * ffn, ffn, 0, ia, stream));
         SP_TRY(gemv(mid_, ffn, T, ffn, w.down, nullptr, x_, hid, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, x_, &ia, true));

@@ -3,6 +3,7 @@
 #include "tp.cuh"
 
 #include <algorithm>
+#include <cstddef>
 #include <cstring>
 
 #include "engine.h"
@@ -91,6 +92,34 @@ cudaError_t launch_tp_reduce(float* x, int ldx, int rows, int dim, const TpDev* 
     return count_launch_and_check();
 }
 
+// Partial rows of a column-split product computed by a kernel that cannot push them itself (the tcgen05 GEMM): two
+// elements per thread, one 128-bit store per peer, each element tagged with the exchange number like the GEMV's.
+__global__ void __launch_bounds__(256) tp_push_kernel(const float* __restrict__ part, int ld, int rows, int dim, const TpDev* __restrict__ tpp) {
+    pdl_wait();
+    pdl_trigger();
+    const TpDev& tp = *tpp;
+    const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(tp.ar_seq) + 1u;
+    const int slot = (int)(epoch & 1u);
+    const int64_t pairs = (int64_t)rows * dim / 2;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < pairs; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = (2 * i) / dim, c = 2 * i - r * dim;
+        const float2 v = *reinterpret_cast<const float2*>(part + r * ld + c);
+        ulonglong2 w;
+        w.x = tp_word(v.x, epoch);
+        w.y = tp_word(v.y, epoch);
+        for (int p = 0; p < tp.size; ++p) *reinterpret_cast<ulonglong2*>(tp_recv(tp, p, slot, tp.rank) + r * dim + c) = w;
+    }
+}
+
+cudaError_t launch_tp_push(const float* part, int ld, int rows, int dim, const TpDev* tp, cudaStream_t st) {
+    if (rows <= 0) return cudaSuccess;
+    if (dim % 2 != 0 || ld % 2 != 0) return cudaErrorInvalidValue;
+    const int64_t pairs = (int64_t)rows * dim / 2;
+    cudaError_t le = launch_pdl(tp_push_kernel, dim3((unsigned)std::min<int64_t>((pairs + 255) / 256, 148 * 8)), dim3(256), 0, st, part, ld, rows, dim, tp);
+    if (le != cudaSuccess) return le;
+    return count_launch_and_check();
+}
+
 // Global arg-max of `rows` logit rows whose vocabulary is split over the ranks: every rank publishes
 // (max value, global index) of its slice, then all pick the largest value, the largest index among equals
 // (the reference's tie rule: the last maximum wins, crates/sapient-generate/src/sampler.rs:161-168).
@@ -112,7 +141,7 @@ __global__ void __launch_bounds__(32) tp_argmax_kernel(const float* __restrict__
     if (lane < tp.size) *tp_flag(tp, TP_OFF_AM_FLAGS, lane, slot, tp.rank) = epoch;
     if (lane < tp.size) {
         const bool already = *reinterpret_cast<volatile int*>(tp.timeout) != 0;  // an earlier wait expired: do not wait again
-        if (!already && !tp_wait_flag(tp_flag(tp, TP_OFF_AM_FLAGS, tp.rank, slot, lane), epoch)) atomicExch(tp.timeout, 1);
+        if (!already && !tp_wait_flag(tp_flag(tp, TP_OFF_AM_FLAGS, tp.rank, slot, lane), epoch, tp.wait_ns)) atomicExch(tp.timeout, 1);
         __threadfence_system();
     }
     __syncwarp();
@@ -195,6 +224,7 @@ int Engine::tp_connect(const void* handles, int n) {
     }
     uint32_t* st = (uint32_t*)tp_state_;
     h.ar_seq = st; h.am_seq = st + 1; h.done = st + 2; h.timeout = (int*)(st + 3);
+    h.wait_ns = tp_wait_ns_;
     SP_CUDA_TRY(cudaMemcpy(d_tp_, &h, sizeof(h), cudaMemcpyHostToDevice));
     tp_connected_ = true;
     return SP_OK;
@@ -215,8 +245,34 @@ int Engine::tp_connect_ptrs(void* const* blocks, int n) {
     }
     uint32_t* st = (uint32_t*)tp_state_;
     h.ar_seq = st; h.am_seq = st + 1; h.done = st + 2; h.timeout = (int*)(st + 3);
+    h.wait_ns = tp_wait_ns_;
     SP_CUDA_TRY(cudaMemcpy(d_tp_, &h, sizeof(h), cudaMemcpyHostToDevice));
     tp_connected_ = true;
+    return SP_OK;
+}
+
+// A new bound for the waits on peers (takes effect with the next launch; captured step graphs read it from device memory).
+int Engine::tp_set_wait_ms(int ms) {
+    if (ms <= 0) { set_error("tp_set_wait_ms: the bound must be positive"); return SP_ERR_ARG; }
+    tp_wait_ns_ = (uint64_t)ms * 1000000ull;
+    if (!tp_connected_) return SP_OK;
+    SP_CUDA_TRY(cudaSetDevice(d.device));
+    SP_CUDA_TRY(cudaStreamSynchronize(stream));
+    SP_CUDA_TRY(cudaMemcpy((uint8_t*)d_tp_ + offsetof(TpDev, wait_ns), &tp_wait_ns_, sizeof(uint64_t), cudaMemcpyHostToDevice));
+    return SP_OK;
+}
+
+// After SP_ERR_COMM (or to restart cleanly): exchange counters, arrival marks and the sticky flag back to their initial
+// state. Every rank must call it, with a host barrier before (no rank still inside a step) and after (no rank starts a
+// step before all have cleared): the epochs of the ranks must agree again.
+int Engine::tp_reset() {
+    if (d.tp_size <= 1 || !tp_block_) { set_error("engine is not tensor parallel (or not finalised)"); return SP_ERR_STATE; }
+    SP_CUDA_TRY(cudaSetDevice(d.device));
+    SP_CUDA_TRY(cudaStreamSynchronize(stream));
+    SP_CUDA_TRY(cudaMemset(tp_block_, 0, tp_block_bytes()));
+    SP_CUDA_TRY(cudaMemset(tp_state_, 0, 64));
+    tp_pending_ = false;
+    SP_CUDA_TRY(cudaDeviceSynchronize());
     return SP_OK;
 }
 

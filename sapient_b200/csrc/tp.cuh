@@ -19,8 +19,9 @@
 // slot = epoch & 1 where epoch counts the exchanges; a rank cannot be more than one exchange ahead of a peer
 // (it needs that peer's words to finish the current one), so two slots are enough, and a word left over from
 // two exchanges ago never matches.
-// Waits are bounded: after TP_SPIN_LIMIT polls a kernel records the failure in `timeout` and goes on, the host
-// reports SP_ERR_COMM. Peer memory is only ever written, with plain stores; nothing is loaded from a peer.
+// Waits are bounded in time (TpDev::wait_ns of the device's global timer, 5 s unless the host sets another bound: long
+// enough for a peer that is still capturing its first step graph, short enough to end a step whose peer has gone): a
+// kernel whose wait runs out records the failure in `timeout` and goes on, the host reports SP_ERR_COMM. Peer memory is only ever written, with plain stores; nothing is loaded from a peer.
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -29,7 +30,7 @@ namespace sp {
 
 constexpr int TP_MAX_RANKS = 8;
 constexpr int TP_ARGMAX_ROWS = 32;
-constexpr int TP_SPIN_LIMIT = 1 << 21;  // polls of ~0.5 us each: about a second
+constexpr uint64_t TP_WAIT_NS_DEFAULT = 5ull * 1000 * 1000 * 1000;  // how long a kernel waits for a peer before it gives up
 
 constexpr size_t TP_OFF_AM_FLAGS = 256;
 constexpr size_t TP_OFF_AM_VALS = 512;
@@ -43,7 +44,14 @@ struct TpDev {
     uint32_t* am_seq;
     uint32_t* done;                    // local: block counter of the consuming kernel
     int* timeout;                      // local: set when a wait gave up
+    uint64_t wait_ns;                  // bound of every wait, in nanoseconds of the device's global timer
 };
+
+__device__ __forceinline__ uint64_t tp_now_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
 
 __device__ __forceinline__ unsigned long long* tp_recv(const TpDev& tp, int on_rank, int slot, int src) {
     return reinterpret_cast<unsigned long long*>(tp.base[on_rank] + TP_OFF_RECV) + ((int64_t)slot * tp.size + src) * tp.slot_floats;
@@ -55,13 +63,14 @@ __device__ __forceinline__ volatile uint32_t* tp_flag(const TpDev& tp, size_t of
     return reinterpret_cast<volatile uint32_t*>(tp.base[on_rank] + off) + slot * TP_MAX_RANKS + src;
 }
 
-// Polls a flag in local memory until it holds `epoch`; false after TP_SPIN_LIMIT polls.
-__device__ __forceinline__ bool tp_wait_flag(volatile uint32_t* f, uint32_t epoch) {
-    for (int i = 0; i < TP_SPIN_LIMIT; ++i) {
+// Polls a flag in local memory until it holds `epoch`; false once wait_ns have passed.
+__device__ __forceinline__ bool tp_wait_flag(volatile uint32_t* f, uint32_t epoch, uint64_t wait_ns) {
+    const uint64_t t0 = tp_now_ns();
+    for (;;) {
         if (*f == epoch) return true;
+        if (tp_now_ns() - t0 > wait_ns) return false;
         __nanosleep(200);
     }
-    return false;
 }
 
 // Consumer side of one exchange, called by every thread of a block after the grid-dependency wait: adds the
@@ -78,13 +87,16 @@ __device__ __forceinline__ uint32_t tp_consume_row(const TpDev& tp, float* x, in
         for (int s = 0; s < tp.size; ++s) {
             const volatile ulonglong2* src = reinterpret_cast<const volatile ulonglong2*>(tp_recv(tp, tp.rank, slot, s) + (int64_t)row * dim + i);
             unsigned long long w0 = 0, w1 = 0, w2 = 0, w3 = 0;
-            int spins = 0;
+            uint64_t t0 = 0;  // read on the first miss only: the common case costs no timer access
             for (;;) {
                 w0 = src[0].x; w1 = src[0].y; w2 = src[1].x; w3 = src[1].y;
                 if ((uint32_t)(w0 >> 32) == epoch && (uint32_t)(w1 >> 32) == epoch && (uint32_t)(w2 >> 32) == epoch &&
                     (uint32_t)(w3 >> 32) == epoch)
                     break;
-                if (!ok || ++spins > TP_SPIN_LIMIT) { ok = false; break; }
+                if (!ok) break;
+                const uint64_t now = tp_now_ns();
+                if (t0 == 0) t0 = now;
+                else if (now - t0 > tp.wait_ns) { ok = false; break; }
                 __nanosleep(100);
             }
             acc.x += __uint_as_float((uint32_t)w0); acc.y += __uint_as_float((uint32_t)w1);
@@ -106,6 +118,9 @@ __device__ __forceinline__ void tp_consume_done(const TpDev& tp, uint32_t epoch,
 }
 
 cudaError_t launch_tp_reduce(float* x, int ldx, int rows, int dim, const TpDev* tp, cudaStream_t st);
+// Pushes the partial rows part[rows][dim] (row stride ld) of a column-split product into every rank's receive area, as
+// the GEMV epilogue does for its own outputs; the consumer is launch_tp_reduce or the fused norm.
+cudaError_t launch_tp_push(const float* part, int ld, int rows, int dim, const TpDev* tp, cudaStream_t st);
 cudaError_t launch_tp_argmax(const float* logits, int ld, int rows, int vocab_off, uint32_t* argmax, const TpDev* tp, cudaStream_t st);
 
 }  // namespace sp

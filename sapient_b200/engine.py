@@ -113,6 +113,15 @@ class ForwardEngine:
         arr = (C.c_uint8 * len(blob)).from_buffer_copy(blob)
         check(lib().sp_cuda_engine_tp_connect(self._h, arr, self.desc.tp_size))
 
+    def tp_set_wait_ms(self, ms: int) -> None:
+        """Bound of the device-side waits on peers (default 5000 ms)."""
+        check(lib().sp_cuda_engine_tp_set_wait_ms(self._h, int(ms)))
+
+    def tp_reset(self) -> None:
+        """Exchange counters, arrival marks and the sticky error flag back to their initial state. Every rank calls it,
+        with a host barrier before and after."""
+        check(lib().sp_cuda_engine_tp_reset(self._h))
+
     def tp_block(self) -> int:
         """Device address of this rank's communication block (for engines of one process)."""
         p = C.c_void_p()
