@@ -147,6 +147,128 @@ attention_split_kernel(const float* __restrict__ q, int ldq, float* __restrict__
     }
 }
 
+// The same for grouped-query attention: a block serves ONE KV head — warp w the w-th query head of its group — over
+// the split's keys, so the K / V rows of a (token, KV head, split) are fetched from HBM once and reach the other query
+// heads of the group through L1 (the kernel above re-reads them once per query head: 4 x the KV bytes on the Llama-3
+// shape, which at 32 sequences x 1024 keys no longer fit the L2). Each warp owns its head: no cross-warp merge.
+constexpr int ATT_GQA_WARPS = 8;
+__global__ void __launch_bounds__(ATT_GQA_WARPS * 32)
+attention_gqa_kernel(const float* __restrict__ q, int ldq, float* __restrict__ out, int ldo, int n_heads, const int32_t* __restrict__ tok_slot,
+                     const int32_t* __restrict__ tok_pos, KvGeom kv, int layer, float scale, int n_splits, float* __restrict__ part) {
+    pdl_wait();
+    pdl_trigger();
+    const int kv_h = blockIdx.x, t = blockIdx.y, sp = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
+    const int hd = kv.head_dim, npairs = hd >> 1, group = n_heads / kv.n_kv;
+    const int slot = tok_slot[t], n_keys = tok_pos[t] + 1;
+    const int per = (n_keys + n_splits - 1) / n_splits;
+    const int k_begin = sp * per, k_end = min(n_keys, k_begin + per);
+    const int32_t* pt = kv.page_table + (int64_t)slot * kv.max_pages;
+    for (int gi = warp; gi < group; gi += n_warps) {
+        const int h = kv_h * group + gi;
+        const float* qrow = q + (int64_t)t * ldq + (int64_t)h * hd;
+        float2 qv[ATT_MAX_PAIRS], o[ATT_MAX_PAIRS];
+#pragma unroll
+        for (int i = 0; i < ATT_MAX_PAIRS; ++i) {
+            const int p = lane + 32 * i;
+            qv[i] = (p < npairs) ? make_float2(qrow[2 * p], qrow[2 * p + 1]) : make_float2(0.f, 0.f);
+            o[i] = make_float2(0.f, 0.f);
+        }
+        float m = -INFINITY, l = 0.f;
+        for (int key0 = k_begin; key0 < k_end; key0 += ATT_KEYS) {
+            __half2 kr[ATT_KEYS][ATT_MAX_PAIRS], vr[ATT_KEYS][ATT_MAX_PAIRS];
+            float s[ATT_KEYS];
+#pragma unroll
+            for (int j = 0; j < ATT_KEYS; ++j) {
+                const int key = min(key0 + j, k_end - 1);  // tail keys repeat the last one and get weight 0
+                const int page = pt[key / KV_PAGE];
+                const __half2* kp = reinterpret_cast<const __half2*>(kv.pool + kv_off(kv, layer, page, 0, kv_h) + (int64_t)(key % KV_PAGE) * hd);
+                const __half2* vp = reinterpret_cast<const __half2*>(kv.pool + kv_off(kv, layer, page, 1, kv_h) + (int64_t)(key % KV_PAGE) * hd);
+#pragma unroll
+                for (int i = 0; i < ATT_MAX_PAIRS; ++i) {
+                    const int p = lane + 32 * i;
+                    kr[j][i] = (p < npairs) ? kp[p] : __half2();
+                    vr[j][i] = (p < npairs) ? vp[p] : __half2();
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < ATT_KEYS; ++j) {
+                float part_dot = 0.f;
+#pragma unroll
+                for (int i = 0; i < ATT_MAX_PAIRS; ++i) {
+                    if (lane + 32 * i < npairs) {
+                        const float2 kf = __half22float2(kr[j][i]);
+                        part_dot = fmaf(qv[i].x, kf.x, part_dot);
+                        part_dot = fmaf(qv[i].y, kf.y, part_dot);
+                    }
+                }
+                s[j] = part_dot;
+            }
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1)
+#pragma unroll
+                for (int j = 0; j < ATT_KEYS; ++j) s[j] += __shfl_xor_sync(0xFFFFFFFFu, s[j], off);
+            float m_new = m;
+#pragma unroll
+            for (int j = 0; j < ATT_KEYS; ++j) {
+                s[j] = (key0 + j < k_end) ? s[j] * scale : -INFINITY;
+                m_new = fmaxf(m_new, s[j]);
+            }
+            const float corr = expf(m - m_new);
+            float pw[ATT_KEYS], psum = 0.f;
+#pragma unroll
+            for (int j = 0; j < ATT_KEYS; ++j) { pw[j] = expf(s[j] - m_new); psum += pw[j]; }
+#pragma unroll
+            for (int i = 0; i < ATT_MAX_PAIRS; ++i) {
+                if (lane + 32 * i < npairs) {
+                    float ox = corr * o[i].x, oy = corr * o[i].y;
+#pragma unroll
+                    for (int j = 0; j < ATT_KEYS; ++j) {
+                        const float2 vf = __half22float2(vr[j][i]);
+                        ox = fmaf(pw[j], vf.x, ox);
+                        oy = fmaf(pw[j], vf.y, oy);
+                    }
+                    o[i].x = ox; o[i].y = oy;
+                }
+            }
+            l = fmaf(corr, l, psum);
+            m = m_new;
+        }
+        if (n_splits == 1) {
+            const float inv = (l == 0.f) ? 0.f : 1.0f / l;
+            float* dst = out + (int64_t)t * ldo + (int64_t)h * hd;
+#pragma unroll
+            for (int i = 0; i < ATT_MAX_PAIRS; ++i) {
+                const int p = lane + 32 * i;
+                if (p < npairs) *reinterpret_cast<float2*>(dst + 2 * p) = make_float2(o[i].x * inv, o[i].y * inv);
+            }
+        } else {
+            float* dst = part + (((int64_t)t * n_heads + h) * n_splits + sp) * (hd + 2);
+            if (lane == 0) { dst[0] = m; dst[1] = l; }  // an empty key range leaves m = -inf, l = 0, o = 0
+#pragma unroll
+            for (int i = 0; i < ATT_MAX_PAIRS; ++i) {
+                const int p = lane + 32 * i;
+                if (p < npairs) { dst[2 + 2 * p] = o[i].x; dst[3 + 2 * p] = o[i].y; }
+            }
+        }
+    }
+}
+
+// Which of the two kernels a launch takes: the grouped one when several query heads share a KV head.
+// ctx_hint: an upper bound of the longest context among the tokens (0: unknown). Short work is latency-bound and runs
+// faster with the four warps of a block sharing one head's keys; from a few thousand (token, key) pairs on the KV bytes
+// matter and the grouped kernel wins.
+static cudaError_t launch_split_phase(const float* q, int ldq, float* out, int ldo, int n_tok, int n_heads, const int32_t* tok_slot,
+                                      const int32_t* tok_pos, KvGeom kv, int layer, float scale, int n_splits, float* scratch, cudaStream_t st,
+                                      int ctx_hint) {
+    const int group = kv.n_kv > 0 ? n_heads / kv.n_kv : 1;
+    if (group >= 2 && n_heads % kv.n_kv == 0 && (int64_t)n_tok * ctx_hint >= 4096)
+        return launch_pdl(attention_gqa_kernel, dim3(kv.n_kv, n_tok, n_splits), dim3(32 * (group < ATT_GQA_WARPS ? group : ATT_GQA_WARPS)), 0, st,
+                          q, ldq, out, ldo, n_heads, tok_slot, tok_pos, kv, layer, scale, n_splits, scratch);
+    return launch_pdl(attention_split_kernel, dim3(n_heads, n_tok, n_splits), dim3(ATT_WARPS * 32), 0, st, q, ldq, out, ldo, n_heads, tok_slot,
+                      tok_pos, kv, layer, scale, n_splits, scratch);
+}
+
 __global__ void attention_merge_kernel(const float* __restrict__ part, int n_heads, int n_splits, int hd, float* __restrict__ out,
                                        int ldo) {
     pdl_wait();
@@ -176,22 +298,20 @@ size_t attention_scratch_floats(int n_tok, int n_heads, int n_splits, int head_d
 }
 
 cudaError_t launch_attention_split(const float* q, int ldq, int n_tok, int n_heads, const int32_t* tok_slot, const int32_t* tok_pos,
-                                   KvGeom kv, int layer, float scale, int n_splits, float* scratch, cudaStream_t st) {
+                                   KvGeom kv, int layer, float scale, int n_splits, float* scratch, cudaStream_t st, int ctx_hint) {
     if (n_tok == 0) return cudaSuccess;
     if (n_splits < 2 || !scratch) return cudaErrorInvalidValue;
-    cudaError_t le = launch_pdl(attention_split_kernel, dim3(n_heads, n_tok, n_splits), dim3(ATT_WARPS * 32), 0, st, q, ldq,
-                                (float*)nullptr, 0, n_heads, tok_slot, tok_pos, kv, layer, scale, n_splits, scratch);
+    cudaError_t le = launch_split_phase(q, ldq, nullptr, 0, n_tok, n_heads, tok_slot, tok_pos, kv, layer, scale, n_splits, scratch, st, ctx_hint);
     if (le != cudaSuccess) return le;
     return count_launch_and_check();
 }
 
 cudaError_t launch_attention(const float* q, int ldq, float* out, int ldo, int n_tok, int n_heads, const int32_t* tok_slot,
                              const int32_t* tok_pos, KvGeom kv, int layer, float scale, int n_splits, float* scratch,
-                             cudaStream_t st) {
+                             cudaStream_t st, int ctx_hint) {
     if (n_tok == 0) return cudaSuccess;
     if (n_splits < 1 || (n_splits > 1 && !scratch)) return cudaErrorInvalidValue;
-    cudaError_t le = launch_pdl(attention_split_kernel, dim3(n_heads, n_tok, n_splits), dim3(ATT_WARPS * 32), 0, st, q, ldq, out, ldo,
-                                n_heads, tok_slot, tok_pos, kv, layer, scale, n_splits, scratch);
+    cudaError_t le = launch_split_phase(q, ldq, out, ldo, n_tok, n_heads, tok_slot, tok_pos, kv, layer, scale, n_splits, scratch, st, ctx_hint);
     if (le != cudaSuccess) return le;
     cudaError_t e = count_launch_and_check();
     if (e != cudaSuccess || n_splits == 1) return e;

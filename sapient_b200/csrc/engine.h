@@ -201,8 +201,11 @@ class Engine {
     uint32_t* d_tokens_ = nullptr;
     size_t d_tokens_cap_ = 0;
     // CUDA graphs of one decode step, keyed by token count
+    // keyed by (rows, attention split count): the split count follows the longest context of the step, see step_splits()
     std::map<int, cudaGraphExec_t> step_graphs_;
     std::map<int, int64_t> step_graph_kernels_;
+    int step_ctx_ = 0;            // upper bound of the longest context among the staged tokens (host-side knowledge)
+    int step_splits(int T) const; // key ranges per (token, head) of the decode-shaped attention
     // profiling: event pairs per launch, resolved after a synchronise
     struct ProfRec { int fam; cudaEvent_t a, b; };
     std::vector<ProfRec> prof_recs_;

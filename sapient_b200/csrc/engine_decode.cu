@@ -99,7 +99,8 @@ int Engine::drain_async() {
 
 int Engine::launch_decode_step(int T) {
     if (!use_graphs || profile_on || trace_on) return enqueue_decode_step(T);
-    auto it = step_graphs_.find(T);
+    const int key = T * 64 + step_splits(T);
+    auto it = step_graphs_.find(key);
     if (it == step_graphs_.end()) {
         cudaGraph_t graph = nullptr;
         const uint64_t before = launch_count();
@@ -110,17 +111,17 @@ int Engine::launch_decode_step(int T) {
         const cudaError_t ce = cudaStreamEndCapture(stream, &graph);
         const int64_t captured = (int64_t)(launch_count() - before);
         adjust_launch_count(-captured);  // captured, not executed
-        step_graph_kernels_[T] = captured;
+        step_graph_kernels_[key] = captured;
         if (st != SP_OK) { if (graph) cudaGraphDestroy(graph); return st; }
         if (ce != cudaSuccess) { set_error(std::string("graph capture: ") + cudaGetErrorString(ce)); return SP_ERR_CUDA; }
         cudaGraphExec_t exec = nullptr;
         const cudaError_t ie = cudaGraphInstantiate(&exec, graph, 0);
         cudaGraphDestroy(graph);
         if (ie != cudaSuccess) { set_error(std::string("graph instantiate: ") + cudaGetErrorString(ie)); return SP_ERR_CUDA; }
-        it = step_graphs_.emplace(T, exec).first;
+        it = step_graphs_.emplace(key, exec).first;
     }
     SP_CUDA_TRY(cudaGraphLaunch(it->second, stream));
-    adjust_launch_count(step_graph_kernels_[T]);
+    adjust_launch_count(step_graph_kernels_[key]);
     return SP_OK;
 }
 
@@ -218,8 +219,10 @@ int Engine::decode_greedy(const uint32_t* first_ids, const int32_t* slots, int b
         SP_CUDA_TRY(cudaMemcpyAsync(d_page_table_, h_page_table_.data(), h_page_table_.size() * 4, cudaMemcpyHostToDevice, stream));
         pages_dirty_ = false;
     }
-    int done = 0, st = SP_OK;
+    int done = 0, st = SP_OK, ctx0 = 0;
+    for (int i = 0; i < b; ++i) ctx0 = std::max(ctx0, seq_len[slots[i]]);
     for (; done < steps && st == SP_OK; ++done) {
+        step_ctx_ = ctx0 + done + 1;
         st = launch_decode_step(b);
         if (st != SP_OK) break;
         cudaError_t ce = launch_pdl(advance_greedy_kernel, dim3((b + 127) / 128), dim3(128), 0, stream, (const uint32_t*)d_argmax_, d_ids_,

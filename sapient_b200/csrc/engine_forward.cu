@@ -197,6 +197,8 @@ int Engine::forward(const uint32_t* ids, const int32_t* slots, int64_t n, bool w
             p_pos_[i] = seq_len[s]++;
             SP_TRY(alloc_pages(s, seq_len[s]));
         }
+        step_ctx_ = 0;
+        for (int i = 0; i < T; ++i) step_ctx_ = std::max(step_ctx_, p_pos_[i] + 1);
         const bool last_chunk = c0 + T >= n;
         int rows_from;
         float* lo = nullptr;

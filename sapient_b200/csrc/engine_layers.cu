@@ -180,6 +180,21 @@ static inline bool all_tiled(const DevTensor* a, const DevTensor* b = nullptr, c
     return a->tiled && (!b || b->tiled) && (!c || c->tiled);
 }
 
+// Keys are split over several blocks while (token, head) pairs alone leave SMs idle — 16 ways for one or two rows, fewer
+// as the rows grow — and, whatever the row count, so that no block walks more than ~128 keys: at 32 sequences x 1024
+// keys the unsplit kernel is a chain of 260 dependent iterations per block (measured 6 ms of attention per step of the
+// 8B shape; the KV bytes need 0.7 ms). The count is a power of two up to 16 and part of the step graph's key.
+int Engine::step_splits(int T) const {
+    int splits = 1;
+    if (T <= imma_rows_per_pass()) splits = d.n_heads * T <= 64 ? ATT_SPLITS : d.n_heads * T <= 128 ? 8 : 4;
+    if (T <= ATT_SPLIT_TOKENS) {
+        int by_ctx = 1;
+        while (by_ctx < ATT_SPLITS && by_ctx * 128 < step_ctx_) by_ctx <<= 1;
+        splits = std::max(splits, by_ctx);
+    }
+    return splits;
+}
+
 // Attention of the T staged tokens, then the output projection added into x_ (x += W_o attn (+ b_o)).
 int Engine::attention_and_oproj(const LayerW& w, int l, int T) {
     const int H = d.n_heads, Hkv = d.n_kv_heads, hd = d.head_dim, hid = d.hidden;
@@ -188,12 +203,11 @@ int Engine::attention_and_oproj(const LayerW& w, int l, int T) {
     // Keys are split over several blocks only while (token, head) pairs alone leave SMs idle: 16 ways for one or two
     // rows, fewer as the rows grow, not at all from 17 rows on (measured on the 8B shape at context 300: 16 rows 0.89 ms
     // of attention per step with 4 splits against 1.37 with 16; 32 rows 0.54 ms unsplit against 2.34).
-    int splits = 1;
-    if (T <= imma_rows_per_pass()) splits = H * T <= 64 ? ATT_SPLITS : H * T <= 128 ? 8 : 4;
+    const int splits = step_splits(T);
     ImmaArgs ia;
     if (splits > 1 && use_ring && d.tp_size == 1 && !trace_on && T <= RING_MAX_M && all_tiled(w.o)) {
         // split-K attention merged to f32 rows; the output projection quantises them itself
-        SP_LAUNCH(F_ATTN, launch_attention(qkv_, qkv_ld, attn_, H * hd, T, H, d_tok_slot_, d_tok_pos_, kv_, l, scale, splits, att_scratch_, stream));
+        SP_LAUNCH(F_ATTN, launch_attention(qkv_, qkv_ld, attn_, H * hd, T, H, d_tok_slot_, d_tok_pos_, kv_, l, scale, splits, att_scratch_, stream, step_ctx_));
         bool done = false;
         SP_TRY(try_ring(&done, T, H * hd, RING_SRC_PLAIN, attn_, H * hd, nullptr, nullptr, w.o, w.ob, x_, hid, nullptr, nullptr, nullptr, nullptr,
                         nullptr, nullptr, x_));
@@ -201,7 +215,7 @@ int Engine::attention_and_oproj(const LayerW& w, int l, int T) {
         return gemv(attn_, H * hd, T, H * hd, w.o, w.ob, x_, hid, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, x_, nullptr, true);
     }
     if (splits > 1 && !trace_on && all_tiled(w.o) && plan_digits(T, H * hd, ia)) {
-        SP_LAUNCH(F_ATTN, launch_attention_split(qkv_, qkv_ld, T, H, d_tok_slot_, d_tok_pos_, kv_, l, scale, splits, att_scratch_, stream));
+        SP_LAUNCH(F_ATTN, launch_attention_split(qkv_, qkv_ld, T, H, d_tok_slot_, d_tok_pos_, kv_, l, scale, splits, att_scratch_, stream, step_ctx_));
         SP_LAUNCH(F_ATTN, launch_attn_merge_quant(att_scratch_, H, splits, hd, nullptr, 0, ia, stream));
         return gemv(attn_, H * hd, T, H * hd, w.o, w.ob, x_, hid, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, x_, &ia, true);
     }
@@ -218,7 +232,7 @@ int Engine::attention_and_oproj(const LayerW& w, int l, int T) {
         return gemv(attn_, H * hd, T, H * hd, w.o, w.ob, x_, hid, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, x_, nullptr, true);
     }
     SP_LAUNCH(F_ATTN, launch_attention(qkv_, qkv_ld, attn_, H * hd, T, H, d_tok_slot_, d_tok_pos_, kv_, l, scale, splits, att_scratch_,
-                                       stream));
+                                       stream, step_ctx_));
     return gemv(attn_, H * hd, T, H * hd, w.o, w.ob, x_, hid, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, x_, nullptr, true);
 }
 

@@ -121,7 +121,7 @@ cudaError_t launch_attn_merge_quant(const float* part, int n_heads, int n_splits
                                     cudaStream_t st);
 // The split phase of launch_attention alone (partials to scratch); n_splits > 1.
 cudaError_t launch_attention_split(const float* q, int ldq, int n_tok, int n_heads, const int32_t* tok_slot, const int32_t* tok_pos,
-                                   KvGeom kv, int layer, float scale, int n_splits, float* scratch, cudaStream_t st);
+                                   KvGeom kv, int layer, float scale, int n_splits, float* scratch, cudaStream_t st, int ctx_hint = 0);
 
 // Prefill attention on tensor cores: n_tok tokens of one sequence at consecutive positions pos0.. (keys already cached).
 bool attention_prefill_supported(int head_dim);
@@ -198,9 +198,10 @@ cudaError_t launch_rope(float* x, int n_tok, int n_heads, int head_dim, int rota
 // Causal GQA attention of each token against keys 0..pos of its slot, online softmax, keys split over
 // n_splits blocks per (head, token). n_splits > 1 needs `scratch` of attention_scratch_floats() floats.
 size_t attention_scratch_floats(int n_tok, int n_heads, int n_splits, int head_dim);
+// ctx_hint: upper bound of the longest context among the tokens (0: unknown); picks the kernel variant, not the result's meaning.
 cudaError_t launch_attention(const float* q, int ldq, float* out, int ldo, int n_tok, int n_heads, const int32_t* tok_slot,
                              const int32_t* tok_pos, KvGeom kv, int layer, float scale, int n_splits, float* scratch,
-                             cudaStream_t st);
+                             cudaStream_t st, int ctx_hint = 0);
 cudaError_t launch_swiglu(const float* gate_up, int ld, int ffn, int rows, float* out, cudaStream_t st);
 cudaError_t launch_gelu(float* x, int64_t n, cudaStream_t st);
 cudaError_t launch_silu(float* x, int64_t n, cudaStream_t st);

@@ -187,10 +187,12 @@ def weight_dtype(cfg: dict, role: str, layer: int, k: int) -> int:
     return Q4_K
 
 
-def build_model(cfg: dict, seed: int, device: str = "cpu", max_ctx: int | None = None) -> tuple[dict, dict]:
+def build_model(cfg: dict, seed: int, device: str = "cpu", max_ctx: int | None = None, embed_float=None) -> tuple[dict, dict]:
     """Random-init N(0, 0.02) weights quantised per block. Returns (cfg, weights) where
     weights maps HF-style names (the keys the reference's GGUF name map produces,
-    crates/sapient-models/src/gguf_weights.rs:360-455) to (dtype, dims, uint8 tensor)."""
+    crates/sapient-models/src/gguf_weights.rs:360-455) to (dtype, dims, uint8 tensor).
+    embed_float: a [vocab, hidden] f32 tensor to quantise as the token embedding (and tied output head) instead of a
+    fresh random one."""
     cfg = dict(cfg)
     cfg.setdefault("rotary_dim", cfg["head_dim"])
     cfg["max_ctx"] = max_ctx or cfg.get("max_ctx", 4096)
@@ -215,7 +217,14 @@ def build_model(cfg: dict, seed: int, device: str = "cpu", max_ctx: int | None =
         W[name] = (F32, [n], v.contiguous().view(torch.uint8).reshape(-1))
 
     phi = cfg["arch"] == "phi2"
-    mat("model.embed_tokens", V, hid, "embed")
+    if embed_float is not None:
+        assert tuple(embed_float.shape) == (V, hid)
+        dt = weight_dtype(cfg, "embed", 0, hid)
+        rows_per = max(1, (1 << 26) // hid)
+        parts = [quantize(dt, embed_float[r0:r0 + rows_per].to(device=device, dtype=torch.float32)) for r0 in range(0, V, rows_per)]
+        W["model.embed_tokens.weight"] = (dt, [V, hid], torch.cat(parts, 0).reshape(-1))
+    else:
+        mat("model.embed_tokens", V, hid, "embed")
     for l in range(cfg["n_layers"]):
         p = f"model.layers.{l}"
         vec(p + ".input_layernorm.weight", hid, 1.0, 0.05)
@@ -246,6 +255,24 @@ def build_model(cfg: dict, seed: int, device: str = "cpu", max_ctx: int | None =
     if not cfg.get("tied"):
         mat("lm_head", V, hid, "output")
     return cfg, W
+
+
+def build_spec_pair(target: str = "qwen15b", draft: str = "qwen05b", seed: int = 4000, device: str = "cpu", max_ctx: int | None = None):
+    """Target and draft models of the speculative-decoding configuration: both random-init from separate seeds, tied
+    embeddings, and the draft's embedding / output matrix is the target's projected by a fixed random
+    hidden_t -> hidden_d matrix with N(0, 1 / hidden_t) entries (the projection is applied to the target's f32
+    embedding before either is quantised). Returns ((cfg_t, W_t), (cfg_d, W_d))."""
+    ct, cd = CONFIGS[target], CONFIGS[draft]
+    assert ct["vocab"] == cd["vocab"] and ct.get("tied") and cd.get("tied")
+    g = torch.Generator(device=device)
+    g.manual_seed(seed + 7)
+    V, ht, hd_ = ct["vocab"], ct["hidden"], cd["hidden"]
+    emb_t = torch.randn(V, ht, generator=g, device=device, dtype=torch.float32) * 0.02
+    proj = torch.randn(ht, hd_, generator=g, device=device, dtype=torch.float32) / (ht ** 0.5)
+    emb_d = emb_t @ proj
+    t = build_model(ct, seed, device, max_ctx, embed_float=emb_t)
+    d = build_model(cd, seed + 1, device, max_ctx, embed_float=emb_d)
+    return t, d
 
 
 def weights_to_numpy(W: dict) -> dict:

@@ -235,3 +235,33 @@ def test_batched_decode_of_twenty_sequences_goes_through_the_large_m_path(oracle
             nxt.append(int(oracle.argmax(w)))
         toks = np.array(nxt, np.uint32)
     eng.close(); solo.close()
+
+
+@pytest.mark.parametrize("name", ["tiny_llama", "tiny_qwen", "tiny_llama_wide"])
+def test_batched_decode_at_longer_context_takes_the_grouped_attention_kernel(oracle, name):
+    """32 sequences x ~130 cached keys: enough (token, key) pairs for the grouped-query kernel (one block per KV head, a
+    warp per query head of its group, keys split by context). Its rows must equal each sequence decoded alone — a
+    1-row step at the same context takes the other kernel — to rounding, and sit on the oracle."""
+    cfg, W = tiny_model(name, max_ctx=192)
+    B = 32
+    eng = ForwardEngine.from_weights(cfg, W, max_batch=B, max_tokens=64)
+    solo = ForwardEngine.from_weights(cfg, W, max_tokens=64)
+    for e in (eng, solo):
+        e.set_kv_rounding(False)
+    prompts = [prompt(cfg, 128 + (i % 7), seed=100 + i) for i in range(B)]
+    toks = np.array([int(oracle.argmax(eng.forward_slot(i, p))) for i, p in enumerate(prompts)], np.uint32)
+    for step in range(2):
+        logits, am = eng.decode_batch(toks, np.arange(B), want_logits=True, want_argmax=True)
+        nxt = []
+        for i in range(B):
+            prompts[i] = np.append(prompts[i], toks[i])
+            if i % 8 == 0:  # every eighth sequence against the single-sequence engine and the oracle
+                solo.reset_cache()
+                w = solo.forward_logits(prompts[i], True)
+                assert np.max(np.abs(logits[i] - w)) < 2e-4, (step, i)
+                ref = oracle_engine(oracle, cfg, W, kv_mode=1).forward_logits(prompts[i], True)
+                assert np.max(np.abs(logits[i] - ref)) < 3e-3, (step, i)
+            assert am[i] == oracle.argmax(logits[i])
+            nxt.append(int(am[i]))
+        toks = np.array(nxt, np.uint32)
+    eng.close(); solo.close()
