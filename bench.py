@@ -169,7 +169,7 @@ def batch32_section(cfg, W, wbytes: int, local: int, rank: int, world: int, stre
         eng.tp_connect()
     eng.set_stream(stream.cuda_stream)
     rng = np.random.default_rng(32)
-    eng.set_large_m_gemm(world == 1)  # untimed prefill: fast path where it exists (single GPU)
+    eng.set_large_m_gemm(True)  # untimed prefill through the tcgen05 path
     first = np.empty(B32_BATCH, np.uint32)
     for s in range(B32_BATCH):
         lg = eng.forward_slot(s, rng.integers(0, cfg["vocab"], B32_PROMPT).astype(np.uint32))
@@ -184,7 +184,7 @@ def batch32_section(cfg, W, wbytes: int, local: int, rank: int, world: int, stre
     slots = list(range(B32_BATCH))
     out = {"batch": B32_BATCH, "prompt_len": B32_PROMPT, "steps": B32_STEPS, "model": MODEL, "kv": "fp16 paged/16"}
     kv_per_pos = 2 * cfg["n_layers"] * cfg["n_kv_heads"] * cfg["head_dim"] * 2
-    modes = [("exact", False)] + ([("tcgen05", True)] if world == 1 else [])
+    modes = [("exact", False), ("tcgen05", True)]
     for tag, fast in modes:
         for s in slots:
             eng.truncate_cache(B32_PROMPT, s)
