@@ -337,6 +337,60 @@ float dot_q4_k_row_f32(const uint8_t* row, const float* x, int64_t k) {
     return acc;
 }
 
+// kernels/quant.rs:104-114,197-205 — Q4_0: per block (lo * x[j] + hi * x[j + 16]) summed, times d; blocks added in order.
+float dot_q4_0_row_f32(const uint8_t* row, const float* x, int64_t k) {
+    float acc = 0.0f;
+    for (int64_t b = 0; b < k / QK; ++b) {
+        const uint8_t* block = row + b * Q4_0_BYTES;
+        const float d = f16_to_f32(rd16(block));
+        float bacc = 0.0f;
+        for (int j = 0; j < QK / 2; ++j) {
+            const int lo = (int)(block[2 + j] & 0x0F) - 8;
+            const int hi = (int)(block[2 + j] >> 4) - 8;
+            bacc += (float)lo * x[b * QK + j] + (float)hi * x[b * QK + j + QK / 2];
+        }
+        acc += bacc * d;
+    }
+    return acc;
+}
+
+// kernels/quant.rs:1626-1665 — Q5_K scalar row dot (the fifth bit is per element: bit planes of qh[l]).
+float dot_q5_k_row_f32(const uint8_t* row, const float* x, int64_t k) {
+    float acc = 0.0f;
+    int64_t x_off = 0;
+    for (int64_t b = 0; b < k / QK_K; ++b) {
+        const uint8_t* block = row + b * Q5_K_BYTES;
+        const float d = f16_to_f32(rd16(block));
+        const float dmin = f16_to_f32(rd16(block + 2));
+        const uint8_t* scales = block + 4;
+        const uint8_t* qh = block + 16;
+        const uint8_t* ql = block + 48;
+        int ql_off = 0, is = 0;
+        uint8_t u1 = 1, u2 = 2;
+        for (int g = 0; g < QK_K / 64; ++g) {
+            uint8_t sc1, m1, sc2, m2;
+            get_scale_min_k4(is, scales, &sc1, &m1);
+            const float d1 = d * (float)sc1;
+            const float m1v = dmin * (float)m1;
+            get_scale_min_k4(is + 1, scales, &sc2, &m2);
+            const float d2 = d * (float)sc2;
+            const float m2v = dmin * (float)m2;
+            for (int l = 0; l < 32; ++l) {
+                const float hi1 = (qh[l] & u1) ? 16.0f : 0.0f;
+                const float hi2 = (qh[l] & u2) ? 16.0f : 0.0f;
+                acc += (d1 * ((float)(ql[ql_off + l] & 0x0F) + hi1) - m1v) * x[x_off + l];
+                acc += (d2 * ((float)(ql[ql_off + l] >> 4) + hi2) - m2v) * x[x_off + l + 32];
+            }
+            x_off += 64;
+            ql_off += 32;
+            is += 2;
+            u1 <<= 2;
+            u2 <<= 2;
+        }
+    }
+    return acc;
+}
+
 // kernels/quant.rs:2573-2613
 float dot_q6_k_row_f32(const uint8_t* row, const float* x, int64_t k) {
     float acc = 0.0f;
@@ -529,6 +583,8 @@ float dot_row(int dtype, const uint8_t* row, const float* x, int64_t k) {
     switch (dtype) {
         case T_Q4_K: return dot_q4_k_row_f32(row, x, k);
         case T_Q6_K: return dot_q6_k_row_f32(row, x, k);
+        case T_Q4_0: return dot_q4_0_row_f32(row, x, k);
+        case T_Q5_K: return dot_q5_k_row_f32(row, x, k);
         case T_Q8_0: return g_q8_mode == 0 ? dot_q8_0_row_f32_avx2(row, x, k) : dot_q8_0_row_f32_scalar(row, x, k);
         default: return std::numeric_limits<float>::quiet_NaN();
     }
@@ -541,9 +597,9 @@ float dot_row(int dtype, const uint8_t* row, const float* x, int64_t k) {
 // Status: 0 ok, 1 = k not a multiple of the block size (SapientError::Internal),
 // 2 = unsupported dtype.
 int matmul_nt(int dtype, const float* x, const uint8_t* w, int64_t m, int64_t k, int64_t n, float* y) {
-    if (dtype == T_Q4_K || dtype == T_Q6_K) {
+    if (dtype == T_Q4_K || dtype == T_Q5_K || dtype == T_Q6_K) {
         if (k % 256 != 0) return 1;
-    } else if (dtype == T_Q8_0) {
+    } else if (dtype == T_Q8_0 || dtype == T_Q4_0) {
         if (k % 32 != 0) return 1;
     } else if (dtype == T_F32 || dtype == T_F16 || dtype == T_BF16) {
         // Float weights are not reached by the quantised configurations; a plain

@@ -66,9 +66,9 @@ int check_weight_shape(int dtype, int64_t n, int64_t k, size_t nbytes) {
     const int be = block_elems(dtype), bb = block_bytes(dtype);
     if (bb == 0) { set_error("unsupported dtype"); return SP_ERR_DTYPE; }
     if (n < 0 || k <= 0) { set_error("bad shape"); return SP_ERR_SHAPE; }
-    if (dtype == T_Q4_K || dtype == T_Q6_K) {
+    if (dtype == T_Q4_K || dtype == T_Q5_K || dtype == T_Q6_K) {
         if (k % 256 != 0) { set_error("k must be a multiple of 256"); return SP_ERR_SHAPE; }
-    } else if (dtype == T_Q8_0) {
+    } else if (dtype == T_Q8_0 || dtype == T_Q4_0) {
         if (k % 32 != 0) { set_error("k must be a multiple of the block size (32)"); return SP_ERR_SHAPE; }
     } else if (k % 4 != 0) {
         set_error("k must be a multiple of 4");

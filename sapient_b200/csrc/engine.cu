@@ -59,6 +59,7 @@ Engine::~Engine() {
     ws_.release();
     tp_release();
     if (att_scratch_) cudaFree(att_scratch_);
+    if (argmax_scratch_) cudaFree(argmax_scratch_);
     ring_.release();
     for (void* p : owned_) cudaFree(p);
     void* bufs[] = {kv_.pool, d_page_table_, x_, h_, qkv_, attn_, gu_, mid_, sel_, logits_, trace_, d_ids_, d_argmax_,
@@ -291,6 +292,8 @@ int Engine::finalize() {
     SP_CUDA_TRY(cudaMalloc((void**)&logits_, (size_t)logit_rows_ * vocab_l_ * 4));
     SP_CUDA_TRY(cudaMalloc((void**)&d_ids_, T * 4));
     SP_CUDA_TRY(cudaMalloc((void**)&d_argmax_, T * 4));
+    SP_CUDA_TRY(cudaMalloc(&argmax_scratch_, argmax_scratch_bytes()));
+    SP_CUDA_TRY(cudaMemset(argmax_scratch_, 0, argmax_scratch_bytes()));
     SP_CUDA_TRY(cudaMalloc((void**)&d_tok_slot_, T * 4));
     SP_CUDA_TRY(cudaMalloc((void**)&d_tok_pos_, T * 4));
     SP_CUDA_TRY(cudaMallocHost((void**)&p_ids_, T * 4));

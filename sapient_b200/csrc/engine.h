@@ -188,6 +188,7 @@ class Engine {
     float *x_ = nullptr, *h_ = nullptr, *qkv_ = nullptr, *attn_ = nullptr, *gu_ = nullptr, *mid_ = nullptr, *sel_ = nullptr,
           *logits_ = nullptr, *trace_ = nullptr;
     uint32_t *d_ids_ = nullptr, *d_argmax_ = nullptr;
+    void* argmax_scratch_ = nullptr;  // candidates and arrival counters of the multi-block arg-max
     int32_t *d_tok_slot_ = nullptr, *d_tok_pos_ = nullptr;
     float2* cos_sin_ = nullptr;
     int trace_tokens_ = 0;

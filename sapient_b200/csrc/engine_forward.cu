@@ -86,7 +86,7 @@ int Engine::enqueue_head(int rows_from, int r0, int rc, const ImmaArgs* pre) {
     head.dims[0] = V;
     SP_TRY(gemv(sel_ + (size_t)r0 * hid, hid, rc, hid, &head, lm_bias_, logits_, V, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr,
                 nullptr, pre));
-    SP_LAUNCH(F_ARGMAX, launch_argmax(logits_, rc, V, V, d_argmax_, stream));
+    SP_LAUNCH(F_ARGMAX, launch_argmax(logits_, rc, V, V, d_argmax_, stream, argmax_scratch_));
     if (d.tp_size > 1) {
         if (!tp_connected_) { set_error("tensor-parallel engine used before tp_connect"); return SP_ERR_STATE; }
         SP_LAUNCH(F_ARGMAX, launch_tp_argmax(logits_, V, rc, vocab_off_, d_argmax_, d_tp_, stream));
@@ -104,7 +104,7 @@ int Engine::enqueue_decode_step(int T) {
         bool ringed = false;
         SP_TRY(try_ring(&ringed, T, hid, d.arch == 1 ? RING_SRC_LN : RING_SRC_RMS, x_, hid, final_w_, final_b_, &head, lm_bias_, logits_, vocab_l_));
         if (ringed) {
-            SP_LAUNCH(F_ARGMAX, launch_argmax(logits_, T, vocab_l_, vocab_l_, d_argmax_, stream));
+            SP_LAUNCH(F_ARGMAX, launch_argmax(logits_, T, vocab_l_, vocab_l_, d_argmax_, stream, argmax_scratch_));
             return SP_OK;
         }
     }

@@ -694,9 +694,77 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ 
     }
 }
 
-cudaError_t launch_argmax(const float* logits, int rows, int n, int ld, uint32_t* out, cudaStream_t st) {
+// The same over ARGMAX_PARTS blocks per row: each block scans one slice, leaves its (value, index) candidate in scratch
+// and counts its arrival; the last block of the row picks among the candidates. "Greatest value, among equals the
+// greatest index" is associative and commutative, so the result does not depend on the order of arrival.
+// scratch: [rows][ARGMAX_PARTS] float2 (value, index bits) followed by [rows] arrival counters (zero between launches).
+__global__ void __launch_bounds__(256) argmax_parts_kernel(const float* __restrict__ logits, int n, int ld, uint32_t* __restrict__ out,
+                                                          float2* __restrict__ cand, unsigned* __restrict__ cnt) {
+    pdl_wait();
+    pdl_trigger();
+    __shared__ float sv[8];
+    __shared__ int si[8];
+    __shared__ bool last;
+    const int row_i = blockIdx.y, part = blockIdx.x, parts = gridDim.x;
+    const float* row = logits + (int64_t)row_i * ld;
+    const int per = (n + parts - 1) / parts, lo = part * per, hi = min(n, lo + per);
+    auto better = [](float v, int i, float bv, int b) { return i >= 0 && (b < 0 || v > bv || (v == bv && i > b)); };
+    float best = -INFINITY;
+    int bi = -1;
+    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+        const float v = row[i];
+        if (bi < 0 || v >= best) { best = v; bi = i; }
+    }
+    auto warp_reduce = [&]() {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xFFFFFFFFu, best, o);
+            const int oi = __shfl_xor_sync(0xFFFFFFFFu, bi, o);
+            if (better(ov, oi, best, bi)) { best = ov; bi = oi; }
+        }
+    };
+    warp_reduce();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (lane == 0) { sv[warp] = best; si[warp] = bi; }
+    __syncthreads();
+    if (warp == 0) {
+        best = lane < 8 ? sv[lane] : -INFINITY;
+        bi = lane < 8 ? si[lane] : -1;
+        warp_reduce();
+        if (lane == 0) {
+            cand[(int64_t)row_i * parts + part] = make_float2(best, __int_as_float(bi));
+            __threadfence();
+            last = atomicAdd(&cnt[row_i], 1u) == (unsigned)(parts - 1);
+        }
+    }
+    __syncthreads();
+    if (!last || warp != 0) return;
+    __threadfence();
+    best = -INFINITY;
+    bi = -1;
+    for (int p = lane; p < parts; p += 32) {
+        const float2 c = __ldcg(&cand[(int64_t)row_i * parts + p]);
+        const int ci = __float_as_int(c.y);
+        if (better(c.x, ci, best, bi)) { best = c.x; bi = ci; }
+    }
+    warp_reduce();
+    if (lane == 0) {
+        out[row_i] = (uint32_t)(bi < 0 ? 0 : bi);
+        cnt[row_i] = 0u;
+    }
+}
+
+cudaError_t launch_argmax(const float* logits, int rows, int n, int ld, uint32_t* out, cudaStream_t st, void* scratch) {
     if (rows == 0) return cudaSuccess;
-    cudaError_t le = launch_pdl(argmax_kernel, dim3(rows), dim3(1024), 0, st, logits, n, ld, out);
+    cudaError_t le;
+    if (scratch && n >= 8192) {
+        float2* cand = reinterpret_cast<float2*>(scratch);
+        unsigned* cnt = reinterpret_cast<unsigned*>(cand + (size_t)ARGMAX_MAX_ROWS * ARGMAX_PARTS);
+        if (rows > ARGMAX_MAX_ROWS) return cudaErrorInvalidValue;
+        le = launch_pdl(argmax_parts_kernel, dim3(ARGMAX_PARTS, rows), dim3(256), 0, st, logits, n, ld, out, cand, cnt);
+    } else {
+        le = launch_pdl(argmax_kernel, dim3(rows), dim3(1024), 0, st, logits, n, ld, out);
+    }
     if (le != cudaSuccess) return le;
     return finish_launch();
 }

@@ -208,7 +208,11 @@ cudaError_t launch_silu(float* x, int64_t n, cudaStream_t st);
 cudaError_t launch_add(const float* a, const float* b, float* y, int64_t n, cudaStream_t st);
 cudaError_t launch_mul(const float* a, const float* b, float* y, int64_t n, cudaStream_t st);
 // Row-wise argmax with the reference's tie rule (the LAST maximum wins).
-cudaError_t launch_argmax(const float* logits, int rows, int n, int ld, uint32_t* out, cudaStream_t st);
+// scratch (optional, argmax_scratch_bytes() of zeroed device memory owned by the caller's stream): rows of 8192 columns
+// and more are then scanned by ARGMAX_PARTS blocks each instead of one.
+constexpr int ARGMAX_PARTS = 64, ARGMAX_MAX_ROWS = 64;
+inline size_t argmax_scratch_bytes() { return (size_t)ARGMAX_MAX_ROWS * ARGMAX_PARTS * 8 + ARGMAX_MAX_ROWS * 4; }
+cudaError_t launch_argmax(const float* logits, int rows, int n, int ld, uint32_t* out, cudaStream_t st, void* scratch = nullptr);
 cudaError_t launch_gather_rows(const float* src, int ld, const int32_t* rows, int n_rows, int dim, float* dst,
                                cudaStream_t st);
 

@@ -12,21 +12,25 @@
 
 namespace sp {
 
-enum : int { T_F32 = 0, T_F16 = 1, T_Q8_0 = 8, T_Q4_K = 12, T_Q6_K = 14, T_BF16 = 30 };
+enum : int { T_F32 = 0, T_F16 = 1, T_Q4_0 = 2, T_Q8_0 = 8, T_Q4_K = 12, T_Q5_K = 13, T_Q6_K = 14, T_BF16 = 30 };
+constexpr int Q4_0_BYTES = 18;
 constexpr int Q8_0_BYTES = 34;
 constexpr int Q4_K_BYTES = 144;
+constexpr int Q5_K_BYTES = 176;
 constexpr int Q6_K_BYTES = 210;
 constexpr int KV_PAGE = 16;  // tokens per KV page
 
 __host__ __device__ inline int block_elems(int dtype) {
-    return (dtype == T_Q4_K || dtype == T_Q6_K) ? 256 : (dtype == T_Q8_0 ? 32 : 1);
+    return (dtype == T_Q4_K || dtype == T_Q5_K || dtype == T_Q6_K) ? 256 : ((dtype == T_Q8_0 || dtype == T_Q4_0) ? 32 : 1);
 }
 __host__ __device__ inline int block_bytes(int dtype) {
     switch (dtype) {
         case T_F32: return 4;
         case T_F16: case T_BF16: return 2;
+        case T_Q4_0: return Q4_0_BYTES;
         case T_Q8_0: return Q8_0_BYTES;
         case T_Q4_K: return Q4_K_BYTES;
+        case T_Q5_K: return Q5_K_BYTES;
         case T_Q6_K: return Q6_K_BYTES;
         default: return 0;
     }
@@ -82,6 +86,37 @@ __device__ __forceinline__ float dequant_q4_k_elem(const uint8_t* row, int64_t i
     return __fsub_rn(__fmul_rn(dl, q), ml);
 }
 
+// Q4_0 (crates/sapient-core/src/tensor.rs:362-377): 18 bytes per 32 weights = f16 d + 16 nibble bytes; elements 0..15
+// are the low nibbles, 16..31 the high nibbles, value (q - 8) * d.
+__device__ __forceinline__ float dequant_q4_0_elem(const uint8_t* row, int64_t i) {
+    const uint8_t* blk = row + (i >> 5) * Q4_0_BYTES;
+    const int j = (int)(i & 31);
+    const float d = half_bits_to_float(ld_u16(blk));
+    const uint8_t b = blk[2 + (j & 15)];
+    const int q = (int)(j < 16 ? (b & 0x0F) : (b >> 4)) - 8;
+    return __fmul_rn((float)q, d);
+}
+
+// Q5_K (crates/sapient-core/src/tensor.rs:421-467): 176 bytes per 256 weights = f16 d, f16 dmin, scales[12] (the Q4_K
+// 6-bit packing), qh[32], qs[128]. Per 64-group g: low nibbles of qs[32 g + l] are sub-block 2 g, high nibbles 2 g + 1;
+// the fifth bit of element l is PER ELEMENT, bit (2 g) resp. (2 g + 1) of qh[l]. Value d * sc * (q + 16 * bit) - dmin * m.
+__device__ __forceinline__ float dequant_q5_k_elem(const uint8_t* row, int64_t i) {
+    const uint8_t* blk = row + (i >> 8) * Q5_K_BYTES;
+    const int r = (int)(i & 255);
+    const int g = r >> 6, hi = (r >> 5) & 1, l = r & 31;
+    const float d = half_bits_to_float(ld_u16(blk));
+    const float dmin = half_bits_to_float(ld_u16(blk + 2));
+    const uint32_t* s32 = reinterpret_cast<const uint32_t*>(blk + 4);
+    uint32_t sc, mn;
+    k4_scale_min(s32[0], s32[1], s32[2], 2 * g + hi, &sc, &mn);
+    const float dl = __fmul_rn(d, (float)sc);
+    const float ml = __fmul_rn(dmin, (float)mn);
+    const uint8_t qb = blk[48 + 32 * g + l];
+    const float fifth = ((blk[16 + l] >> (2 * g + hi)) & 1u) ? 16.0f : 0.0f;
+    const float q = __fadd_rn((float)(hi ? (qb >> 4) : (qb & 0x0F)), fifth);
+    return __fsub_rn(__fmul_rn(dl, q), ml);
+}
+
 __device__ __forceinline__ float dequant_q6_k_elem(const uint8_t* row, int64_t i) {
     const uint8_t* blk = row + (i >> 8) * Q6_K_BYTES;
     const int r = (int)(i & 255);
@@ -98,7 +133,9 @@ __device__ __forceinline__ float dequant_q6_k_elem(const uint8_t* row, int64_t i
 __device__ __forceinline__ float dequant_elem(int dtype, const uint8_t* row, int64_t i) {
     switch (dtype) {
         case T_Q4_K: return dequant_q4_k_elem(row, i);
+        case T_Q5_K: return dequant_q5_k_elem(row, i);
         case T_Q6_K: return dequant_q6_k_elem(row, i);
+        case T_Q4_0: return dequant_q4_0_elem(row, i);
         case T_Q8_0: return dequant_q8_0_elem(row, i);
         case T_F16: return half_bits_to_float(ld_u16(row + 2 * i));
         case T_BF16: return __uint_as_float((uint32_t)ld_u16(row + 2 * i) << 16);

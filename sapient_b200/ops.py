@@ -12,7 +12,7 @@ import numpy as np
 from . import _lib
 from ._lib import SapientCudaError, check, lib
 
-F32, F16, Q8_0, Q4_K, Q6_K, BF16 = 0, 1, 8, 12, 14, 30
+F32, F16, Q4_0, Q8_0, Q4_K, Q5_K, Q6_K, BF16 = 0, 1, 2, 8, 12, 13, 14, 30
 
 
 def _p(a: np.ndarray):

@@ -16,10 +16,10 @@ import numpy as np
 import torch
 
 # ggml type codes (crates/sapient-io/src/gguf.rs:88-129).
-F32, F16, Q8_0, Q4_K, Q6_K = 0, 1, 8, 12, 14
-BLOCK = {Q8_0: (32, 34), Q4_K: (256, 144), Q6_K: (256, 210), F32: (1, 4), F16: (1, 2)}
-BPW = {Q8_0: 34 / 32, Q4_K: 144 / 256, Q6_K: 210 / 256, F32: 4.0, F16: 2.0}
-TYPE_NAME = {F32: "f32", F16: "f16", Q8_0: "q8_0", Q4_K: "q4_k", Q6_K: "q6_k"}
+F32, F16, Q4_0, Q8_0, Q4_K, Q5_K, Q6_K, BF16 = 0, 1, 2, 8, 12, 13, 14, 30
+BLOCK = {Q8_0: (32, 34), Q4_K: (256, 144), Q6_K: (256, 210), F32: (1, 4), F16: (1, 2), Q4_0: (32, 18), Q5_K: (256, 176), BF16: (1, 2)}
+BPW = {Q8_0: 34 / 32, Q4_K: 144 / 256, Q6_K: 210 / 256, F32: 4.0, F16: 2.0, Q4_0: 18 / 32, Q5_K: 176 / 256, BF16: 2.0}
+TYPE_NAME = {F32: "f32", F16: "f16", Q8_0: "q8_0", Q4_K: "q4_k", Q6_K: "q6_k", Q4_0: "q4_0", Q5_K: "q5_k", BF16: "bf16"}
 
 
 def byte_count(dtype: int, numel: int) -> int:
@@ -112,6 +112,8 @@ def quantize(dtype: int, w: torch.Tensor) -> torch.Tensor:
         return w.float().contiguous().view(torch.uint8).reshape(*w.shape[:-1], w.shape[-1] * 4)
     if dtype == F16:
         return w.to(torch.float16).contiguous().view(torch.uint8).reshape(*w.shape[:-1], w.shape[-1] * 2)
+    if dtype == BF16:
+        return w.to(torch.bfloat16).contiguous().view(torch.uint8).reshape(*w.shape[:-1], w.shape[-1] * 2)
     raise ValueError(f"unsupported dtype {dtype}")
 
 
@@ -135,6 +137,11 @@ def random_bit_blocks(dtype: int, nblocks: int, seed: int) -> np.ndarray:
         out[:, 2:4] = f16(nblocks, 1e-4)
     elif dtype == Q6_K:
         out[:, 208:210] = f16(nblocks, 1e-5)
+    elif dtype == Q4_0:
+        out[:, 0:2] = f16(nblocks, 1e-2)
+    elif dtype == Q5_K:
+        out[:, 0:2] = f16(nblocks, 1e-4)
+        out[:, 2:4] = f16(nblocks, 1e-4)
     else:
         raise ValueError(dtype)
     return out.reshape(-1)

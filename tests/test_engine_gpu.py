@@ -265,3 +265,38 @@ def test_batched_decode_at_longer_context_takes_the_grouped_attention_kernel(ora
             nxt.append(int(am[i]))
         toks = np.array(nxt, np.uint32)
     eng.close(); solo.close()
+
+
+@pytest.mark.parametrize("ftype", ["f16", "bf16"])
+def test_float_linears_are_quantised_to_q8_0_at_load_like_the_reference(oracle, ftype):
+    """forward/common.rs:39-86: 2-D F16 / BF16 weight matrices (not norms, biases, the embedding table or lm_head) are
+    quantised to Q8_0 once at load with quantize_q8_0_block (kernels/quant.rs:223-235). An engine handed the float
+    tensors must equal, bit for bit, an engine handed the Q8_0 blocks the oracle's quantiser makes of them."""
+    import torch
+
+    cfg, W = tiny_model("tiny_llama")
+    g = torch.Generator().manual_seed(3)
+    Wf, Wq = dict(W), dict(W)
+    n_conv = 0
+    for name, (dt, dims, raw) in W.items():
+        if len(dims) != 2 or any(s in name for s in ("norm", "bias", "embed", "lm_head")):
+            continue
+        w = torch.randn(dims[0], dims[1], generator=g) * 0.02
+        if ftype == "f16":
+            h = w.to(torch.float16)
+            Wf[name] = (synth.F16, dims, h.view(torch.uint8).reshape(-1).numpy())
+        else:
+            h = w.to(torch.bfloat16)
+            Wf[name] = (synth.BF16, dims, h.view(torch.uint8).reshape(-1).numpy())
+        Wq[name] = (synth.Q8_0, dims, oracle.quantize_q8_0(h.float().numpy().reshape(-1)))
+        n_conv += 1
+    assert n_conv == 7 * cfg["n_layers"]
+    a, b = ForwardEngine.from_weights(cfg, Wf), ForwardEngine.from_weights(cfg, Wq)
+    ids = prompt(cfg, 9, 6)
+    assert np.array_equal(a.forward_logits(ids, True), b.forward_logits(ids, True))
+    assert np.array_equal(a.forward_logits([3], True), b.forward_logits([3], True))
+    assert a.resident_bytes()[0] == b.resident_bytes()[0]  # stored as Q8_0, not as floats
+    ref = oracle_engine(oracle, cfg, Wq, kv_mode=0)
+    ref.forward_logits(ids, True)
+    assert np.abs(a.forward_logits([4], True) - ref.forward_logits([3, 4], True)).max() < LOGIT_BAR
+    a.close(); b.close()

@@ -230,3 +230,46 @@ def test_kernels_were_launched():
     before = ops.launch_count()
     ops.silu(np.ones(8, np.float32))
     assert ops.launch_count() == before + 1
+
+
+# ── the other block formats the reference's loader keeps packed: Q4_0 and Q5_K ──
+Q4_0, Q5_K = synth.Q4_0, synth.Q5_K
+
+
+@pytest.mark.parametrize("dtype", [Q4_0, Q5_K])
+def test_q4_0_and_q5_k_dequant_bit_exact_and_matmul(oracle, dtype):
+    """Q4_0 (tensor.rs:362-377) and Q5_K with its per-element fifth bit (tensor.rs:421-467; the reference's own
+    regression test for that bit: tensor.rs:796-824): dequantised values bit for bit on random-bit blocks, matmul_nt
+    (kernels/quant.rs:104-114,1626-1665 row dots) within the operator bar. These formats run on the CUDA-core GEMV."""
+    be, _ = synth.BLOCK[dtype]
+    n, k = 37, 4 * 256
+    raw = synth.random_bit_blocks(dtype, n * k // be, seed=200 + dtype)
+    w = ops.Weight(dtype, n, k, raw)
+    got = w.dequant()
+    want = oracle.dequant(dtype, raw, n * k).reshape(n, k)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    rng = np.random.default_rng(dtype)
+    for m in (1, 3, 9, 20):
+        x = rng.standard_normal((m, k)).astype(np.float32)
+        assert rel_l2(w.matmul_nt(x), oracle.matmul_nt(x, raw, dtype, n)) < 2e-5
+    # one row gathered from a Q5_K / Q4_0 embedding table
+    assert np.array_equal(w.embed([5, 0, 36]).view(np.uint32), want[[5, 0, 36]].view(np.uint32))
+    w.free()
+    with pytest.raises(_lib.SapientCudaError):
+        ops.Weight(dtype, 1, 48 if dtype == Q4_0 else 128, raw[:27 if dtype == Q4_0 else 88])
+
+
+def test_q5_k_fifth_bit_is_per_element(oracle):
+    """The reference's regression case (tensor.rs:796-824): d = 1, dmin = 0, every sub-block scale 1; qh[5] bit 0 sets
+    element 5, qh[0] bit 2 (the first plane of the second 64-group) sets element 64, ql[3] = 2 gives element 3 the value 2;
+    everything else is 0."""
+    block = np.zeros(176, np.uint8)
+    block[0:2] = np.array([1.0], np.float16).view(np.uint8)
+    block[4:8] = 1    # 6-bit scales of sub-blocks 0..3
+    block[12:16] = 1  # low nibbles: scales of sub-blocks 4..7
+    block[16 + 5] = 0b00000001
+    block[16 + 0] = 0b00000100
+    block[48 + 3] = 0x02
+    got = ops.Weight(Q5_K, 1, 256, block).dequant().reshape(-1)
+    assert np.array_equal(got, oracle.dequant(Q5_K, block, 256))
+    assert got[3] == 2.0 and got[5] == 16.0 and got[64] == 16.0 and np.count_nonzero(got) == 3
