@@ -260,6 +260,12 @@ int32_t sp_cuda_seq_len(const SpEngine* e, int32_t slot, size_t* len);
 int32_t sp_cuda_backend_label(const SpEngine* e, char* buf, size_t cap);
 /* Keep the hidden state after every layer of each forward chunk (for per-layer parity checks); off by default. */
 int32_t sp_cuda_engine_set_trace(SpEngine* e, int32_t on);
+/* Weight upload accounting: seconds the engine spent moving tensor bytes to the device (host pages -> two pinned staging
+ * buffers -> asynchronous copies on a dedicated stream, the host filling one buffer while the other is in flight) and the
+ * bytes moved. sp_cuda_engine_from_gguf maps the file, so these are the only copies of the weights made on the host;
+ * the llama q / k row un-permute runs as a device-side gather and the Phi qkv split as three row ranges of one mapping
+ * (the reference does both on the host: crates/sapient-models/src/gguf_weights.rs:114-154,273-311). */
+int32_t sp_cuda_engine_load_stats(const SpEngine* e, double* seconds, uint64_t* bytes);
 /* Hidden state after `layer` of the most recent forward chunk, [n_tokens, hidden] to host; returns rows in *n_tokens. */
 int32_t sp_cuda_debug_layer_out(SpEngine* e, int32_t layer, float* out, size_t cap_floats, int32_t* n_tokens);
 /* Number of kernels this library has launched since process start (all engines and ops). */

@@ -99,6 +99,7 @@ SIGNATURES = {
     "sp_cuda_debug_layer_out": (_i32, [_vp, _i32, _vp, _sz, C.POINTER(_i32)]),
     "sp_cuda_launch_count": (C.c_uint64, []),
     "sp_cuda_engine_resident_bytes": (_i32, [_vp, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
+    "sp_cuda_engine_load_stats": (_i32, [_vp, C.POINTER(C.c_double), C.POINTER(C.c_uint64)]),
 }
 
 _lib = None

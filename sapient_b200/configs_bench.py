@@ -178,9 +178,41 @@ def spec_case(k: int, prompt_len: int, new_tokens: int) -> dict:
     return out
 
 
+def load_case(name: str) -> dict:
+    """Load path: the model written as a GGUF file (tmpfs when there is one), then sp_cuda_engine_from_gguf timed end to
+    end — map the file, parse, stage the tensors through pinned buffers, un-permute / repack on the device, allocate."""
+    import tempfile
+
+    import torch
+
+    cfg, W = synth.build_model(synth.CONFIGS[name], seed=3000, device="cuda", max_ctx=512)
+    Wc = {k: (dt, dims, t.cpu()) for k, (dt, dims, t) in W.items()}
+    del W
+    torch.cuda.empty_cache()
+    d = "/dev/shm" if os.path.isdir("/dev/shm") else tempfile.gettempdir()
+    path = os.path.join(d, f"sapient_{name}.gguf")
+    t0 = time.perf_counter()
+    synth.write_gguf(path, cfg, Wc)
+    write_s = time.perf_counter() - t0
+    size = os.path.getsize(path)
+    out = {"case": "load", "model": name, "file_bytes": size, "write_s": write_s, "runs": []}
+    try:
+        for _ in range(2):
+            t0 = time.perf_counter()
+            eng = ForwardEngine.from_gguf(path, max_ctx=512)
+            total = time.perf_counter() - t0
+            sec, nb = eng.load_stats()
+            out["runs"].append({"from_gguf_s": total, "upload_s": sec, "upload_bytes": nb, "upload_gbs": nb / 1e9 / max(sec, 1e-9),
+                                "overall_gbs": size / 1e9 / total})
+            eng.close()
+    finally:
+        os.remove(path)
+    return out
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["c0", "c2", "c3b32", "c4", "prefill"])
+    ap.add_argument("case", choices=["c0", "c2", "c3b32", "c4", "prefill", "load"])
     ap.add_argument("--model", default="llama8b", choices=sorted(synth.CONFIGS))
     ap.add_argument("--prompt", type=int, default=None)
     ap.add_argument("--steps", type=int, default=None)
@@ -193,6 +225,8 @@ def main() -> None:
         line = decode_case("llama8b", a.prompt or 256, a.steps or 64, 32, "c3b32", prefill_timed=True)
     elif a.case == "prefill":
         line = prefill_case(a.model, a.prompt or 512)
+    elif a.case == "load":
+        line = load_case(a.model)
     else:
         line = spec_case(4, a.prompt or 256, a.steps or 512)
     print(json.dumps(line), flush=True)

@@ -674,6 +674,13 @@ int32_t sp_cuda_engine_set_graphs(SpEngine* e, int32_t on) {
     return SP_OK;
 }
 
+int32_t sp_cuda_engine_load_stats(const SpEngine* e, double* seconds, uint64_t* bytes) {
+    if (!e) { set_error("null engine"); return SP_ERR_ARG; }
+    if (seconds) *seconds = e->e->load_seconds;
+    if (bytes) *bytes = e->e->load_bytes;
+    return SP_OK;
+}
+
 int32_t sp_cuda_engine_tp_set_wait_ms(SpEngine* e, int32_t ms) {
     API_BEGIN
     if (!e) { set_error("null engine"); return SP_ERR_ARG; }

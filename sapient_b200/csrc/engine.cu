@@ -3,6 +3,7 @@
 
 #include <algorithm>
 #include <cmath>
+#include <chrono>
 #include <cstring>
 
 #include "sp_common.cuh"
@@ -68,9 +69,63 @@ Engine::~Engine() {
     void* pinned[] = {p_ids_, p_slot_, p_pos_, p_logits_, p_argmax_};
     for (void* p : pinned) if (p) cudaFreeHost(p);
     if (own_stream) cudaStreamDestroy(own_stream);
+    release_staging();
+}
+
+// dst[r] = src[map(r)] for rows of row_bytes bytes (a multiple of 2): the llama q/k un-permute as a gather.
+// HF row h*D + a*half + b comes from GGUF row h*D + 2b + a.
+__global__ void unpermute_rows_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, int64_t rows, int64_t row_bytes, int head_dim) {
+    const int half = head_dim / 2;
+    for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+        const int64_t h = r / head_dim, in_head = r - h * head_dim;
+        const int a = (int)(in_head / half), b = (int)(in_head - (int64_t)a * half);
+        const int64_t from = h * head_dim + 2 * b + a;
+        const uint16_t* s = reinterpret_cast<const uint16_t*>(src + from * row_bytes);
+        uint16_t* t = reinterpret_cast<uint16_t*>(dst + r * row_bytes);
+        for (int64_t i = threadIdx.x; i < row_bytes / 2; i += blockDim.x) t[i] = s[i];
+    }
+}
+
+int Engine::upload_staged(uint8_t* dst, const uint8_t* src, size_t nbytes) {
+    if (!load_stream_) {
+        SP_CUDA_TRY(cudaStreamCreateWithFlags(&load_stream_, cudaStreamNonBlocking));
+        for (int i = 0; i < 2; ++i) {
+            SP_CUDA_TRY(cudaMallocHost((void**)&stage_[i], STAGE_BYTES));
+            SP_CUDA_TRY(cudaEventCreateWithFlags(&stage_ev_[i], cudaEventDisableTiming));
+        }
+    }
+    const auto t0 = std::chrono::steady_clock::now();
+    for (size_t off = 0; off < nbytes; off += STAGE_BYTES) {
+        const size_t n = std::min(STAGE_BYTES, nbytes - off);
+        const int b = stage_next_;
+        stage_next_ ^= 1;
+        SP_CUDA_TRY(cudaEventSynchronize(stage_ev_[b]));  // the copy that last used this buffer has left it
+        std::memcpy(stage_[b], src + off, n);             // page-cache / mmap pages -> pinned memory
+        SP_CUDA_TRY(cudaMemcpyAsync(dst + off, stage_[b], n, cudaMemcpyHostToDevice, load_stream_));
+        SP_CUDA_TRY(cudaEventRecord(stage_ev_[b], load_stream_));
+    }
+    load_seconds += std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+    load_bytes += nbytes;
+    return SP_OK;
+}
+
+void Engine::release_staging() {
+    if (load_stream_) cudaStreamSynchronize(load_stream_);
+    for (int i = 0; i < 2; ++i) {
+        if (stage_[i]) cudaFreeHost(stage_[i]);
+        if (stage_ev_[i]) cudaEventDestroy(stage_ev_[i]);
+        stage_[i] = nullptr;
+        stage_ev_[i] = nullptr;
+    }
+    if (load_stream_) cudaStreamDestroy(load_stream_);
+    load_stream_ = nullptr;
 }
 
 int Engine::set_tensor(const char* name, int dtype, const int64_t* dims, int ndim, const void* bytes, size_t nbytes) {
+    return set_tensor_ex(name, dtype, dims, ndim, bytes, nbytes, 0);
+}
+
+int Engine::set_tensor_ex(const char* name, int dtype, const int64_t* dims, int ndim, const void* bytes, size_t nbytes, int unpermute_heads) {
     if (!name || !dims || !bytes || ndim < 1 || ndim > 2) { set_error("set_tensor: bad argument"); return SP_ERR_ARG; }
     if (finalized) { set_error("set_tensor after finalize"); return SP_ERR_STATE; }
     SP_CUDA_TRY(cudaSetDevice(d.device));
@@ -122,9 +177,32 @@ int Engine::set_tensor(const char* name, int dtype, const int64_t* dims, int ndi
     }
     t.nbytes = nbytes;
     SP_CUDA_TRY(cudaMalloc((void**)&t.d, nbytes + 16));
-    SP_CUDA_TRY(cudaMemcpy(t.d, src, nbytes, cudaMemcpyHostToDevice));
+    if (unpermute_heads > 0 && ndim == 2) {
+        // rows arrive in the GGUF llama order: upload as they are, put them in place on the device
+        const int heads_here = unpermute_heads / (d.tp_size > 1 ? d.tp_size : 1);  // a row shard keeps whole heads
+        const int64_t rows = t.dims[0], rb = row_bytes(t.dtype, t.dims[1]);
+        if (heads_here <= 0 || rows % heads_here != 0 || ((rows / heads_here) & 1) || (rb & 1)) {
+            cudaFree(t.d);
+            set_error(std::string("un-permute: rows of ") + name + " do not form whole heads");
+            return SP_ERR_SHAPE;
+        }
+        uint8_t* tmp = nullptr;
+        SP_CUDA_TRY(cudaMalloc((void**)&tmp, nbytes + 16));
+        int st = upload_staged(tmp, src, nbytes);
+        if (st == SP_OK) {
+            unpermute_rows_kernel<<<(unsigned)std::min<int64_t>(rows, 4096), 128, 0, load_stream_>>>(tmp, t.d, rows, rb, (int)(rows / heads_here));
+            if (cudaGetLastError() != cudaSuccess || cudaStreamSynchronize(load_stream_) != cudaSuccess) { set_error("un-permute kernel failed"); st = SP_ERR_CUDA; }
+        }
+        cudaFree(tmp);
+        if (st != SP_OK) { cudaFree(t.d); return st; }
+    } else {
+        const int st = upload_staged(t.d, src, nbytes);
+        if (st != SP_OK) { cudaFree(t.d); return st; }
+        // conv / shard are host temporaries of this call: the copy out of them must have been staged (it has: every byte
+        // went through memcpy into pinned memory before upload_staged returned)
+    }
     auto it = tensors_.find(nm);
-    if (it != tensors_.end()) { cudaFree(it->second.d); weight_bytes -= it->second.nbytes; }
+    if (it != tensors_.end()) { cudaStreamSynchronize(load_stream_); cudaFree(it->second.d); weight_bytes -= it->second.nbytes; }
     weight_bytes += nbytes;
     tensors_[nm] = t;
     return SP_OK;
@@ -188,6 +266,8 @@ int Engine::repack_weights() {
 int Engine::finalize() {
     if (finalized) return SP_OK;
     SP_CUDA_TRY(cudaSetDevice(d.device));
+    if (load_stream_) SP_CUDA_TRY(cudaStreamSynchronize(load_stream_));  // every weight has landed
+    release_staging();
     if (d.tp_size > 1) {
         if (d.arch != 0) { set_error("tensor parallelism covers the Llama/Qwen block only"); return SP_ERR_ARG; }
         if (g.n_heads % d.tp_size || g.n_kv_heads % d.tp_size || g.ffn % d.tp_size || g.vocab % d.tp_size ||

@@ -55,6 +55,13 @@ class Engine {
     explicit Engine(const SpModelDesc& d);
     ~Engine();
     int set_tensor(const char* name, int dtype, const int64_t* dims, int ndim, const void* bytes, size_t nbytes);
+    // The same with the rows of each head still in the GGUF llama order (row h*D + 2b + a holds HF row h*D + a*D/2 + b,
+    // crates/sapient-models/src/gguf_weights.rs:98-154): unpermute_heads > 0 names the head count of this (full) tensor;
+    // the rows are put in place by a device-side gather after the upload.
+    int set_tensor_ex(const char* name, int dtype, const int64_t* dims, int ndim, const void* bytes, size_t nbytes, int unpermute_heads);
+    // Seconds spent in host->device transfers of weights (pinned double-buffered staging) and bytes moved.
+    double load_seconds = 0.0;
+    uint64_t load_bytes = 0;
     int finalize();
     // Appends n tokens (ids[i] to slot slots[i]; consecutive entries of one slot take consecutive
     // positions). want_all: logits for every token, else only for the last token. Either output may be null.
@@ -164,6 +171,15 @@ class Engine {
     bool plan_digits(int m, int k, ImmaArgs& ia);
     int attention_and_oproj(const LayerW& w, int l, int T);
 
+    // Weight upload: two pinned staging buffers, copies enqueued on a dedicated stream; the host fills one buffer while the
+    // other is in flight. Released at finalize.
+    static constexpr size_t STAGE_BYTES = 32u << 20;
+    uint8_t* stage_[2] = {nullptr, nullptr};
+    cudaEvent_t stage_ev_[2] = {nullptr, nullptr};
+    cudaStream_t load_stream_ = nullptr;
+    int stage_next_ = 0;
+    int upload_staged(uint8_t* dst, const uint8_t* src, size_t nbytes);
+    void release_staging();
     std::map<std::string, DevTensor> tensors_;
     std::vector<void*> owned_;  // extra device allocations (converted biases, ...)
     std::vector<LayerW> layers_;

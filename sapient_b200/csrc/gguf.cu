@@ -9,6 +9,10 @@
 #include <algorithm>
 #include <cmath>
 #include <cstdio>
+#include <fcntl.h>
+#include <sys/mman.h>
+#include <sys/stat.h>
+#include <unistd.h>
 #include <cstdint>
 #include <cstring>
 #include <map>
@@ -117,23 +121,36 @@ bool map_name(const std::string& g, std::string* hf) {
 struct HostTensor {
     int dtype;
     std::vector<int64_t> dims;  // HF order [out, in] / [n]
-    std::vector<uint8_t> own;   // set when the bytes were rearranged
-    const uint8_t* data;
+    const uint8_t* data;        // inside the file mapping
     size_t nbytes;
+    int unpermute_heads = 0;    // > 0: llama-order q / k rows, put in place on the device after the upload
 };
 
 }  // namespace
 
 int sp_engine_from_gguf_impl(const char* path, int device, int max_ctx, int max_batch, sp::Engine** out) {
-    FILE* f = std::fopen(path, "rb");
-    if (!f) { set_error(std::string("cannot open ") + path); return SP_ERR_IO; }
-    std::fseek(f, 0, SEEK_END);
-    const long fsz = std::ftell(f);
-    std::fseek(f, 0, SEEK_SET);
-    std::vector<uint8_t> buf((size_t)(fsz > 0 ? fsz : 0));
-    const size_t got = buf.empty() ? 0 : std::fread(buf.data(), 1, buf.size(), f);
-    std::fclose(f);
-    if (got != buf.size() || buf.size() < 24) { set_error("GGUF file truncated"); return SP_ERR_IO; }
+    // The file is mapped, not read: tensor bytes go from the page cache straight into the engine's pinned staging
+    // buffers (the reference maps its GGUF files as well, crates/sapient-models/src/forward/mod.rs:223-240).
+    struct Mapping {
+        const uint8_t* p = nullptr;
+        size_t n = 0;
+        int fd = -1;
+        ~Mapping() {
+            if (p) munmap((void*)p, n);
+            if (fd >= 0) close(fd);
+        }
+        const uint8_t* data() const { return p; }
+        size_t size() const { return n; }
+    } buf;
+    buf.fd = open(path, O_RDONLY);
+    if (buf.fd < 0) { set_error(std::string("cannot open ") + path); return SP_ERR_IO; }
+    struct stat sb;
+    if (fstat(buf.fd, &sb) != 0 || sb.st_size < 24) { set_error("GGUF file truncated"); return SP_ERR_IO; }
+    buf.n = (size_t)sb.st_size;
+    void* mp = mmap(nullptr, buf.n, PROT_READ, MAP_PRIVATE, buf.fd, 0);
+    if (mp == MAP_FAILED) { buf.n = 0; set_error(std::string("cannot map ") + path); return SP_ERR_IO; }
+    buf.p = (const uint8_t*)mp;
+    madvise(mp, buf.n, MADV_SEQUENTIAL);
 
     Reader r{buf.data(), buf.size()};
     if (r.u32() != 0x46554747u) { set_error("bad GGUF magic"); return SP_ERR_IO; }
@@ -265,17 +282,7 @@ int sp_engine_from_gguf_impl(const char* path, int device, int max_ctx, int max_
             HostTensor& h = kv.second;
             const int hd = d.head_dim;
             if (h.dims.size() != 2 || hd < 2 || hd % 2 != 0 || (int64_t)nh * hd != h.dims[0]) continue;  // left as is
-            const int64_t rb = sp::row_bytes(h.dtype, h.dims[1]);
-            std::vector<uint8_t> dst((size_t)(h.dims[0] * rb));
-            const int half = hd / 2;
-            for (int hh = 0; hh < nh; ++hh)
-                for (int a = 0; a < 2; ++a)
-                    for (int b = 0; b < half; ++b) {
-                        const int64_t hf_row = (int64_t)hh * hd + a * half + b, gg_row = (int64_t)hh * hd + b * 2 + a;
-                        std::memcpy(&dst[(size_t)(hf_row * rb)], h.data + gg_row * rb, (size_t)rb);
-                    }
-            h.own = std::move(dst);
-            h.data = h.own.data();
+            h.unpermute_heads = nh;
         }
     }
     if (is_phi) {
@@ -299,9 +306,8 @@ int sp_engine_from_gguf_impl(const char* path, int device, int max_ctx, int max_
                 s.dtype = t.dtype;
                 s.dims = t.dims;
                 s.dims[0] = rows[i];
-                s.own.assign(t.data + starts[i] * rb, t.data + (starts[i] + rows[i]) * rb);
-                s.data = nullptr;
-                s.nbytes = s.own.size();
+                s.data = t.data + starts[i] * rb;  // a row range of the same mapped bytes: nothing is copied on the host
+                s.nbytes = (size_t)(rows[i] * rb);
                 W[base + nm[i] + suffix] = std::move(s);
             }
         }
@@ -317,8 +323,7 @@ int sp_engine_from_gguf_impl(const char* path, int device, int max_ctx, int max_
     sp::Engine* eng = new sp::Engine(d);
     for (auto& kv : W) {
         HostTensor& h = kv.second;
-        const uint8_t* src = h.own.empty() ? h.data : h.own.data();
-        int st = eng->set_tensor(kv.first.c_str(), h.dtype, h.dims.data(), (int)h.dims.size(), src, h.nbytes);
+        int st = eng->set_tensor_ex(kv.first.c_str(), h.dtype, h.dims.data(), (int)h.dims.size(), h.data, h.nbytes, h.unpermute_heads);
         if (st != SP_OK) { delete eng; return st; }
     }
     int st = eng->finalize();

@@ -282,6 +282,12 @@ class ForwardEngine:
         check(lib().sp_cuda_debug_layer_out(self._h, layer, _p(buf), buf.size, C.byref(n)))
         return buf[: n.value * self.desc.hidden].reshape(n.value, self.desc.hidden).copy()
 
+    def load_stats(self) -> tuple[float, int]:
+        """(seconds spent moving weight bytes to the device, bytes moved)."""
+        sec, nb = C.c_double(), C.c_uint64()
+        check(lib().sp_cuda_engine_load_stats(self._h, C.byref(sec), C.byref(nb)))
+        return float(sec.value), int(nb.value)
+
     def resident_bytes(self) -> tuple[int, int]:
         w, kv = C.c_uint64(), C.c_uint64()
         check(lib().sp_cuda_engine_resident_bytes(self._h, C.byref(w), C.byref(kv)))
