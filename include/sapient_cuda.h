@@ -38,7 +38,7 @@ enum {
 };
 
 /* ggml tensor type codes (crates/sapient-io/src/gguf.rs:88-129) */
-enum { SP_F32 = 0, SP_F16 = 1, SP_Q8_0 = 8, SP_Q4_K = 12, SP_Q6_K = 14, SP_BF16 = 30 };
+enum { SP_F32 = 0, SP_F16 = 1, SP_Q4_0 = 2, SP_Q8_0 = 8, SP_Q4_K = 12, SP_Q5_K = 13, SP_Q6_K = 14, SP_BF16 = 30 };
 
 const char* sp_cuda_last_error(void);
 /* number of visible CUDA devices, or 0 */
