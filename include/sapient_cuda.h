@@ -231,6 +231,53 @@ int32_t sp_cuda_decode_greedy(SpEngine* e, const uint32_t* first_ids, const int3
 int32_t sp_cuda_spec_greedy(SpEngine* target, SpEngine* draft, const uint32_t* prompt, size_t n_prompt, int32_t k, size_t max_new,
                             const uint32_t* eos_ids, int32_t n_eos, uint32_t* tokens_out, size_t* n_out, uint64_t* stats);
 int32_t sp_cuda_engine_synchronize(SpEngine* e);
+
+/* Page sharing between sequence slots. The cache is a pool of 16-token pages with an owner count per page;
+ * sp_cuda_engine_slot_page names the pool page that holds tokens [16 index, 16 index + 16) of a slot, and
+ * sp_cuda_engine_adopt_prefix makes an EMPTY slot a reader of n such pages (its length becomes 16 n): the prefix is not
+ * recomputed and not copied. Shared pages are never written — appending to a slot whose partly filled last page has
+ * another owner (after a truncate into a shared page) first moves the slot to a private copy of that page. The
+ * reference's single cache can only re-use the prefix of its own previous contents
+ * (truncate_cache, crates/sapient-models/src/forward/llama.rs:307-313). */
+int32_t sp_cuda_engine_slot_page(const SpEngine* e, int32_t slot, int32_t index, int32_t* page);
+int32_t sp_cuda_engine_adopt_prefix(SpEngine* e, int32_t slot, const int32_t* pages, int32_t n);
+
+/* ── Continuous batching over the paged KV cache ──
+ * The reference serves one sequence per engine and re-uses a prompt prefix only against the previous turn of the same
+ * conversation (crates/sapient-generate/src/pipeline.rs:818-830); batching is on its roadmap (docs/ROADMAP.md:312).
+ * A batcher owns the sequence slots of one engine (max_batch of them; the engine's caches must be empty when it is
+ * created and the engine must not be driven directly while the batcher lives). Requests are greedy generations
+ * (last-maximum arg-max, sampler.rs:161-168): each request's tokens equal what the engine produces for that prompt
+ * alone. sp_cuda_batcher_step runs ONE scheduler iteration:
+ *   1. admit queued requests, first come first served, while a slot is free and the page pool can hold
+ *      prompt + max_new tokens beside what running requests were promised; pages of an already computed prompt prefix
+ *      (whole 16-token pages, found by content in the prefix index) are shared instead of recomputed, and index pages
+ *      nobody reads are evicted, least recently used first, when the pool is short;
+ *   2. at most prefill_chunk prompt tokens of the oldest prefilling requests;
+ *   3. one decode step carrying one token of every decoding sequence.
+ * A request leaves the batch after an id of its eos list or max_new tokens; its slot is free for the next iteration.
+ * Single thread per batcher. Errors of the engine calls are returned by the step that made them. */
+typedef struct SpBatcher SpBatcher;
+int32_t sp_cuda_batcher_create(SpEngine* e, int32_t prefill_chunk, int32_t prefix_cache, SpBatcher** out);
+/* The same scheduler over a host stand-in instead of an engine (no GPU, no model: the "next token" is a hash of the
+ * sequence as read back through the page tables). It exists so the scheduling logic — admission, page accounting,
+ * sharing, eviction, copy-on-write — can be tested where there is no GPU; it computes nothing of the product. */
+int32_t sp_cuda_batcher_create_selftest(int32_t vocab, int32_t max_slots, int32_t max_ctx, int32_t n_pages, int32_t prefill_chunk,
+                                        int32_t prefix_cache, SpBatcher** out);
+void sp_cuda_batcher_destroy(SpBatcher* b);
+/* Queues a request; *id names it afterwards. SP_ERR_KV_FULL when prompt + max_new exceeds the window or the pool. */
+int32_t sp_cuda_batcher_submit(SpBatcher* b, const uint32_t* prompt, size_t n, size_t max_new, const uint32_t* eos_ids, int32_t n_eos,
+                               uint64_t* id);
+int32_t sp_cuda_batcher_step(SpBatcher* b, int32_t* n_running, int32_t* n_waiting);
+/* Tokens generated so far (at most cap are copied, *n_tokens is the full count); *finished = 1 once the request has left
+ * the batch. Finished requests stay readable until sp_cuda_batcher_forget. */
+int32_t sp_cuda_batcher_poll(const SpBatcher* b, uint64_t id, uint32_t* tokens_out, size_t cap, size_t* n_tokens, int32_t* finished);
+int32_t sp_cuda_batcher_cancel(SpBatcher* b, uint64_t id);
+int32_t sp_cuda_batcher_forget(SpBatcher* b, uint64_t id);
+/* out[0..9): submitted, finished, steps, prompt tokens computed, prompt tokens shared, tokens decoded, index pages evicted,
+ * index pages held, free pool pages. */
+#define SP_BATCHER_STATS 9
+int32_t sp_cuda_batcher_stats(const SpBatcher* b, uint64_t* out, int32_t cap);
 /* Replay decode steps as CUDA graphs (default on). */
 int32_t sp_cuda_engine_set_graphs(SpEngine* e, int32_t on);
 /* Steps of 17 rows and more (prefill chunks, batched decode) on the tcgen05 GEMM: each weight tile is dequantised once

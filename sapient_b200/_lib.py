@@ -99,6 +99,17 @@ SIGNATURES = {
     "sp_cuda_debug_layer_out": (_i32, [_vp, _i32, _vp, _sz, C.POINTER(_i32)]),
     "sp_cuda_launch_count": (C.c_uint64, []),
     "sp_cuda_engine_resident_bytes": (_i32, [_vp, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
+    "sp_cuda_engine_slot_page": (_i32, [_vp, _i32, _i32, C.POINTER(_i32)]),
+    "sp_cuda_engine_adopt_prefix": (_i32, [_vp, _i32, _vp, _i32]),
+    "sp_cuda_batcher_create": (_i32, [_vp, _i32, _i32, C.POINTER(_vp)]),
+    "sp_cuda_batcher_create_selftest": (_i32, [_i32, _i32, _i32, _i32, _i32, _i32, C.POINTER(_vp)]),
+    "sp_cuda_batcher_destroy": (None, [_vp]),
+    "sp_cuda_batcher_submit": (_i32, [_vp, C.POINTER(C.c_uint32), C.c_size_t, C.c_size_t, C.POINTER(C.c_uint32), _i32, C.POINTER(C.c_uint64)]),
+    "sp_cuda_batcher_step": (_i32, [_vp, C.POINTER(_i32), C.POINTER(_i32)]),
+    "sp_cuda_batcher_poll": (_i32, [_vp, C.c_uint64, C.POINTER(C.c_uint32), C.c_size_t, C.POINTER(C.c_size_t), C.POINTER(_i32)]),
+    "sp_cuda_batcher_cancel": (_i32, [_vp, C.c_uint64]),
+    "sp_cuda_batcher_forget": (_i32, [_vp, C.c_uint64]),
+    "sp_cuda_batcher_stats": (_i32, [_vp, C.POINTER(C.c_uint64), _i32]),
     "sp_cuda_engine_load_stats": (_i32, [_vp, C.POINTER(C.c_double), C.POINTER(C.c_uint64)]),
 }
 

@@ -8,6 +8,7 @@
 #include <string>
 #include <vector>
 
+#include "batcher.h"
 #include "engine.h"
 #include "sp_common.cuh"
 
@@ -656,6 +657,122 @@ int32_t sp_cuda_spec_greedy(SpEngine* target, SpEngine* draft, const uint32_t* p
     if (!target || !draft) { set_error("null engine"); return SP_ERR_ARG; }
     if (n_eos < 0 || (n_eos > 0 && !eos_ids)) { set_error("spec_greedy: bad eos list"); return SP_ERR_ARG; }
     return sp::spec_greedy(target->e, draft->e, prompt, n_prompt, k, max_new, eos_ids, n_eos, tokens_out, n_out, stats);
+    API_END
+}
+
+int32_t sp_cuda_engine_slot_page(const SpEngine* e, int32_t slot, int32_t index, int32_t* page) {
+    API_BEGIN
+    if (!e || !page) { set_error("null argument"); return SP_ERR_ARG; }
+    const Engine& en = *e->e;
+    if (!en.finalized) { set_error("engine not finalised"); return SP_ERR_STATE; }
+    if (slot < 0 || slot >= en.d.max_batch || index < 0 || index >= en.pages.held[slot]) { set_error("slot or page index out of range"); return SP_ERR_ARG; }
+    *page = en.pages.page_of(slot, index);
+    return SP_OK;
+    API_END
+}
+
+int32_t sp_cuda_engine_adopt_prefix(SpEngine* e, int32_t slot, const int32_t* pages, int32_t n) {
+    API_BEGIN
+    if (!e) { set_error("null engine"); return SP_ERR_ARG; }
+    if (!e->e->finalized) { set_error("engine not finalised"); return SP_ERR_STATE; }
+    return e->e->adopt_prefix(slot, pages, n);
+    API_END
+}
+
+// ── continuous batching ──
+struct SpBatcher {
+    sp::SeqBackend* be;
+    sp::Batcher* b;
+    int device;  // -1: host stand-in
+};
+
+int32_t sp_cuda_batcher_create(SpEngine* e, int32_t prefill_chunk, int32_t prefix_cache, SpBatcher** out) {
+    API_BEGIN
+    if (!e || !out) { set_error("null argument"); return SP_ERR_ARG; }
+    if (!e->e->finalized) { set_error("engine not finalised"); return SP_ERR_STATE; }
+    if (prefill_chunk < 1) { set_error("batcher: prefill_chunk must be positive"); return SP_ERR_ARG; }
+    for (int s = 0; s < e->e->d.max_batch; ++s)
+        if (e->e->seq_len[s] != 0) { set_error("batcher: the engine's caches must be empty"); return SP_ERR_STATE; }
+    SpBatcher* h = new SpBatcher{sp::make_engine_backend(e->e), nullptr, e->e->d.device};
+    h->b = new sp::Batcher(h->be, prefill_chunk, prefix_cache != 0);
+    *out = h;
+    return SP_OK;
+    API_END
+}
+
+int32_t sp_cuda_batcher_create_selftest(int32_t vocab, int32_t max_slots, int32_t max_ctx, int32_t n_pages, int32_t prefill_chunk,
+                                        int32_t prefix_cache, SpBatcher** out) {
+    API_BEGIN
+    if (!out || vocab < 2 || max_slots < 1 || max_ctx < 2 || n_pages < 1 || prefill_chunk < 1) { set_error("bad argument"); return SP_ERR_ARG; }
+    SpBatcher* h = new SpBatcher{sp::make_mock_backend(vocab, max_slots, max_ctx, n_pages), nullptr, -1};
+    h->b = new sp::Batcher(h->be, prefill_chunk, prefix_cache != 0);
+    *out = h;
+    return SP_OK;
+    API_END
+}
+
+void sp_cuda_batcher_destroy(SpBatcher* b) {
+    if (!b) return;
+    try {
+        if (b->device >= 0) cudaSetDevice(b->device);
+        delete b->b;
+        delete b->be;
+        delete b;
+    } catch (...) {
+    }
+}
+
+int32_t sp_cuda_batcher_submit(SpBatcher* b, const uint32_t* prompt, size_t n, size_t max_new, const uint32_t* eos_ids, int32_t n_eos,
+                               uint64_t* id) {
+    API_BEGIN
+    if (!b) { set_error("null batcher"); return SP_ERR_ARG; }
+    return b->b->submit(prompt, n, max_new, eos_ids, n_eos, id);
+    API_END
+}
+
+int32_t sp_cuda_batcher_step(SpBatcher* b, int32_t* n_running, int32_t* n_waiting) {
+    API_BEGIN
+    if (!b) { set_error("null batcher"); return SP_ERR_ARG; }
+    int r = 0, w = 0;
+    const int st = b->b->step(&r, &w);
+    if (n_running) *n_running = r;
+    if (n_waiting) *n_waiting = w;
+    return st;
+    API_END
+}
+
+int32_t sp_cuda_batcher_poll(const SpBatcher* b, uint64_t id, uint32_t* tokens_out, size_t cap, size_t* n_tokens, int32_t* finished) {
+    API_BEGIN
+    if (!b) { set_error("null batcher"); return SP_ERR_ARG; }
+    int fin = 0;
+    const int st = b->b->poll(id, tokens_out, cap, n_tokens, &fin);
+    if (finished) *finished = fin;
+    return st;
+    API_END
+}
+
+int32_t sp_cuda_batcher_cancel(SpBatcher* b, uint64_t id) {
+    API_BEGIN
+    if (!b) { set_error("null batcher"); return SP_ERR_ARG; }
+    return b->b->cancel(id);
+    API_END
+}
+
+int32_t sp_cuda_batcher_forget(SpBatcher* b, uint64_t id) {
+    API_BEGIN
+    if (!b) { set_error("null batcher"); return SP_ERR_ARG; }
+    return b->b->forget(id);
+    API_END
+}
+
+int32_t sp_cuda_batcher_stats(const SpBatcher* b, uint64_t* out, int32_t cap) {
+    API_BEGIN
+    if (!b || !out || cap < 1) { set_error("null argument"); return SP_ERR_ARG; }
+    const sp::BatcherStats& s = b->b->stats();
+    const uint64_t v[SP_BATCHER_STATS] = {s.submitted, s.finished, s.steps, s.prefill_tokens, s.shared_tokens, s.decode_tokens, s.evicted_pages,
+                                          s.cached_pages, (uint64_t)b->be->pool().available()};
+    for (int i = 0; i < cap && i < SP_BATCHER_STATS; ++i) out[i] = v[i];
+    return SP_OK;
     API_END
 }
 

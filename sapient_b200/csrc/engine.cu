@@ -351,12 +351,9 @@ int Engine::finalize() {
     kv_bytes = (uint64_t)d.n_layers * n_pages * 2 * Hkv * KV_PAGE * hd * sizeof(__half);
     SP_CUDA_TRY(cudaMalloc((void**)&kv_.pool, kv_bytes));
     SP_CUDA_TRY(cudaMalloc((void**)&d_page_table_, (size_t)d.max_batch * pages_per_seq * 4));
-    h_page_table_.assign((size_t)d.max_batch * pages_per_seq, 0);
     SP_CUDA_TRY(cudaMemset(d_page_table_, 0, (size_t)d.max_batch * pages_per_seq * 4));
     kv_.page_table = d_page_table_;
-    free_pages_.clear();
-    for (int p = (int)n_pages - 1; p >= 0; --p) free_pages_.push_back(p);
-    slot_pages_.assign(d.max_batch, 0);
+    pages.init(d.max_batch, pages_per_seq, (int)n_pages);
     // activations
     const size_t T = (size_t)d.max_tokens;
     const size_t qkv_ld = (size_t)(H + 2 * Hkv) * hd;

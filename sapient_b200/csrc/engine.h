@@ -13,6 +13,7 @@
 
 #include "../../include/sapient_cuda.h"
 #include "kernels.h"
+#include "page_pool.h"
 #include "tp.cuh"
 
 namespace sp {
@@ -96,6 +97,10 @@ class Engine {
     int device_check();
     void drop_graphs();                             // forget the captured step graphs (a launch parameter changed)
     int vocab_local() const { return vocab_l_; }
+    // Page bookkeeping of the KV cache (page_pool.h). The batching scheduler reads it to share prompt prefixes between
+    // slots: adopt_prefix makes an EMPTY slot a reader of pages that already hold its first 16 * n tokens.
+    PagePool pages;
+    int adopt_prefix(int slot, const int32_t* page_ids, int n);
 
     SpModelDesc d, g;
     cudaStream_t own_stream = nullptr, stream = nullptr;
@@ -196,9 +201,8 @@ class Engine {
     // paged KV cache
     KvGeom kv_{};
     int32_t* d_page_table_ = nullptr;
-    std::vector<int32_t> h_page_table_;
-    std::vector<int> free_pages_, slot_pages_;
-    bool pages_dirty_ = true;
+    int sync_page_table();        // uploads the host page table when it changed
+    int privatise_tail(int slot); // copy-on-write of a shared, partly filled last page before the slot appends
 
     // activations (sized for max_tokens)
     float *x_ = nullptr, *h_ = nullptr, *qkv_ = nullptr, *attn_ = nullptr, *gu_ = nullptr, *mid_ = nullptr, *sel_ = nullptr,

@@ -194,9 +194,13 @@ int Engine::decode_greedy(const uint32_t* first_ids, const int32_t* slots, int b
     }
     {
         int need = 0;
-        for (int i = 0; i < b; ++i) need += std::max(0, (seq_len[slots[i]] + steps + KV_PAGE - 1) / KV_PAGE - slot_pages_[slots[i]]);
-        if (need > (int)free_pages_.size()) { set_error("KV page pool exhausted"); return SP_ERR_KV_FULL; }
+        for (int i = 0; i < b; ++i) {
+            const int s = slots[i];
+            need += pages.missing(s, seq_len[s] + steps) + ((seq_len[s] % KV_PAGE) && pages.ref[pages.page_of(s, seq_len[s] / KV_PAGE)] > 1 ? 1 : 0);
+        }
+        if (need > pages.available()) { set_error("KV page pool exhausted"); return SP_ERR_KV_FULL; }
     }
+    for (int i = 0; i < b; ++i) SP_TRY(privatise_tail(slots[i]));
     // pages for every step up front, so nothing on the host has to happen between steps
     for (int i = 0; i < b; ++i) {
         SP_TRY(alloc_pages(slots[i], seq_len[slots[i]] + steps));
@@ -215,10 +219,7 @@ int Engine::decode_greedy(const uint32_t* first_ids, const int32_t* slots, int b
     SP_CUDA_TRY(cudaMemcpyAsync(d_ids_, p_ids_, (size_t)b * 4, cudaMemcpyHostToDevice, stream));
     SP_CUDA_TRY(cudaMemcpyAsync(d_tok_slot_, p_slot_, (size_t)b * 4, cudaMemcpyHostToDevice, stream));
     SP_CUDA_TRY(cudaMemcpyAsync(d_tok_pos_, p_pos_, (size_t)b * 4, cudaMemcpyHostToDevice, stream));
-    if (pages_dirty_) {
-        SP_CUDA_TRY(cudaMemcpyAsync(d_page_table_, h_page_table_.data(), h_page_table_.size() * 4, cudaMemcpyHostToDevice, stream));
-        pages_dirty_ = false;
-    }
+    SP_TRY(sync_page_table());
     int done = 0, st = SP_OK, ctx0 = 0;
     for (int i = 0; i < b; ++i) ctx0 = std::max(ctx0, seq_len[slots[i]]);
     for (; done < steps && st == SP_OK; ++done) {

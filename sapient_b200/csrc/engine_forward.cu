@@ -27,15 +27,36 @@ namespace sp {
     } while (0)
 
 int Engine::alloc_pages(int slot, int new_len) {
-    const int need = (new_len + KV_PAGE - 1) / KV_PAGE;
-    while (slot_pages_[slot] < need) {
-        if (free_pages_.empty()) { set_error("KV page pool exhausted"); return SP_ERR_KV_FULL; }
-        const int pg = free_pages_.back();
-        free_pages_.pop_back();
-        h_page_table_[(size_t)slot * kv_.max_pages + slot_pages_[slot]] = pg;
-        slot_pages_[slot]++;
-        pages_dirty_ = true;
+    if (!pages.grow(slot, new_len)) { set_error("KV page pool exhausted"); return SP_ERR_KV_FULL; }
+    return SP_OK;
+}
+
+int Engine::sync_page_table() {
+    if (pages.dirty) {
+        SP_CUDA_TRY(cudaMemcpyAsync(d_page_table_, pages.table.data(), pages.table.size() * 4, cudaMemcpyHostToDevice, stream));
+        pages.dirty = false;
     }
+    return SP_OK;
+}
+
+// One page of one layer is a contiguous run of 2 * n_kv * 16 * head_dim halves; the layers are n_pages such runs apart.
+int Engine::privatise_tail(int slot) {
+    int from = 0, to = 0;
+    const int r = pages.privatise_tail(slot, seq_len[slot], &from, &to);
+    if (r < 0) { set_error("KV page pool exhausted"); return SP_ERR_KV_FULL; }
+    if (r == 0) return SP_OK;
+    const size_t run = (size_t)2 * kv_.n_kv * KV_PAGE * kv_.head_dim * sizeof(__half);
+    const size_t pitch = run * (size_t)kv_.n_pages;
+    const uint8_t* base = reinterpret_cast<const uint8_t*>(kv_.pool);
+    SP_CUDA_TRY(cudaMemcpy2DAsync(const_cast<uint8_t*>(base) + run * (size_t)to, pitch, base + run * (size_t)from, pitch, run, (size_t)d.n_layers,
+                                  cudaMemcpyDeviceToDevice, stream));
+    return SP_OK;
+}
+
+int Engine::adopt_prefix(int slot, const int32_t* page_ids, int n) {
+    if (slot < 0 || slot >= d.max_batch || n < 0 || (n > 0 && !page_ids)) { set_error("adopt_prefix: bad argument"); return SP_ERR_ARG; }
+    if (seq_len[slot] != 0 || !pages.adopt(slot, page_ids, n)) { set_error("adopt_prefix: the slot is not empty or a page is not live"); return SP_ERR_STATE; }
+    seq_len[slot] = n * KV_PAGE;
     return SP_OK;
 }
 
@@ -55,10 +76,7 @@ int Engine::truncate(int slot, size_t n, size_t* kept) {
     const int k = (int)std::min<size_t>(n, (size_t)seq_len[slot]);
     seq_len[slot] = k;
     const int keep_pages = (k + KV_PAGE - 1) / KV_PAGE;
-    while (slot_pages_[slot] > keep_pages) {
-        slot_pages_[slot]--;
-        free_pages_.push_back(h_page_table_[(size_t)slot * kv_.max_pages + slot_pages_[slot]]);
-    }
+    pages.shrink(slot, keep_pages);
     if (kept) *kept = (size_t)k;
     return SP_OK;
 }
@@ -127,10 +145,7 @@ int Engine::run_chunk(const uint32_t* ids, const int32_t* slots, int T, int rows
     SP_CUDA_TRY(cudaMemcpyAsync(d_ids_, p_ids_, (size_t)T * 4, cudaMemcpyHostToDevice, stream));
     SP_CUDA_TRY(cudaMemcpyAsync(d_tok_slot_, p_slot_, (size_t)T * 4, cudaMemcpyHostToDevice, stream));
     SP_CUDA_TRY(cudaMemcpyAsync(d_tok_pos_, p_pos_, (size_t)T * 4, cudaMemcpyHostToDevice, stream));
-    if (pages_dirty_) {
-        SP_CUDA_TRY(cudaMemcpyAsync(d_page_table_, h_page_table_.data(), h_page_table_.size() * 4, cudaMemcpyHostToDevice, stream));
-        pages_dirty_ = false;
-    }
+    SP_TRY(sync_page_table());
     const int hid = d.hidden, V = vocab_l_;
     if (trace_on && !trace_) SP_CUDA_TRY(cudaMalloc((void**)&trace_, (size_t)d.n_layers * d.max_tokens * hid * 4));
     const int rows = T - rows_from;
@@ -183,11 +198,15 @@ int Engine::forward(const uint32_t* ids, const int32_t* slots, int64_t n, bool w
     for (int s = 0; s < d.max_batch; ++s)
         if (seq_len[s] + add[s] > d.max_ctx) { set_error("KV cache full"); return SP_ERR_KV_FULL; }
     {
-        int need = 0;
+        int need = 0;  // fresh pages, plus one per slot whose partly filled last page is shared (copy-on-write)
         for (int s = 0; s < d.max_batch; ++s)
-            need += std::max(0, (seq_len[s] + add[s] + KV_PAGE - 1) / KV_PAGE - slot_pages_[s]);
-        if (need > (int)free_pages_.size()) { set_error("KV page pool exhausted"); return SP_ERR_KV_FULL; }
+            if (add[s])
+                need += pages.missing(s, seq_len[s] + add[s]) +
+                        ((seq_len[s] % KV_PAGE) && pages.ref[pages.page_of(s, seq_len[s] / KV_PAGE)] > 1 ? 1 : 0);
+        if (need > pages.available()) { set_error("KV page pool exhausted"); return SP_ERR_KV_FULL; }
     }
+    for (int s = 0; s < d.max_batch; ++s)
+        if (add[s]) SP_TRY(privatise_tail(s));
     const int C = d.max_tokens;
     for (int64_t c0 = 0; c0 < n; c0 += C) {
         const int T = (int)std::min<int64_t>(C, n - c0);

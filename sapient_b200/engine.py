@@ -196,6 +196,17 @@ class ForwardEngine:
         check(lib().sp_cuda_seq_len(self._h, slot, C.byref(n)))
         return int(n.value)
 
+    def slot_page(self, slot: int, index: int) -> int:
+        """Pool page that holds tokens [16 * index, 16 * index + 16) of `slot`."""
+        pg = C.c_int32()
+        check(lib().sp_cuda_engine_slot_page(self._h, slot, index, C.byref(pg)))
+        return int(pg.value)
+
+    def adopt_prefix(self, slot: int, pages) -> None:
+        """Makes the EMPTY `slot` a reader of pool pages that already hold its first 16 * len(pages) tokens."""
+        pg = np.ascontiguousarray(pages, dtype=np.int32).reshape(-1)
+        check(lib().sp_cuda_engine_adopt_prefix(self._h, slot, _p(pg), pg.size))
+
     def forward_slot(self, slot: int, input_ids, all_positions: bool = False) -> np.ndarray:
         ids = _ids(input_ids)
         if ids.size == 0:
@@ -242,7 +253,8 @@ class ForwardEngine:
         check(lib().sp_cuda_engine_set_large_m_gemm(self._h, int(on)))
 
     def set_ring(self, on: bool) -> None:
-        """Steps of 1-4 rows on the persistent ring GEMV (default) or on the tile-row GEMV with separate producers."""
+        """Steps of 1-5 rows on the persistent ring GEMV (opt-in: measured slower) or, the default, on the tile-row GEMV with
+        separate producers."""
         check(lib().sp_cuda_engine_set_ring(self._h, int(on)))
 
     PROFILE_FAMILIES = ("gemv", "attention", "norm", "rope_kv", "elementwise", "embed", "argmax")

@@ -15,7 +15,7 @@ def _strip_c_comments(s):
 
 
 C2R = {"int32_t": "i32", "int64_t": "i64", "uint32_t": "u32", "uint64_t": "u64", "size_t": "usize", "float": "f32", "double": "f64",
-       "char": "c_char", "void": "c_void", "SpEngine": "SpEngine", "SpWeight": "SpWeight", "SpModelDesc": "SpModelDesc"}
+       "char": "c_char", "void": "c_void", "SpEngine": "SpEngine", "SpWeight": "SpWeight", "SpBatcher": "SpBatcher", "SpModelDesc": "SpModelDesc"}
 
 
 def _header_functions():
