@@ -484,7 +484,7 @@ int32_t sp_cuda_attention(int32_t device, const float* q, const float* k, const 
     SP_CUDA_TRY(dscr.alloc(attention_scratch_floats((int)sq, (int)H, splits, (int)hd) * 4));
     SP_CUDA_TRY(launch_attention(dq.as<float>(), (int)(H * hd), dout.as<float>(), (int)(H * hd), (int)sq, (int)H,
                                  dslot.as<int32_t>(), dpos.as<int32_t>(), g, 0, 1.0f / sqrtf((float)hd), splits,
-                                 dscr.as<float>(), 0));
+                                 dscr.as<float>(), 0, (int)sk));
     SP_CUDA_TRY(cudaMemcpy(qt.data(), dout.p, qt.size() * 4, cudaMemcpyDeviceToHost));
     for (int64_t h = 0; h < H; ++h)
         for (int64_t t = 0; t < sq; ++t)

@@ -147,124 +147,20 @@ attention_split_kernel(const float* __restrict__ q, int ldq, float* __restrict__
     }
 }
 
-// The same for grouped-query attention: a block serves ONE KV head — warp w the w-th query head of its group — over
-// the split's keys, so the K / V rows of a (token, KV head, split) are fetched from HBM once and reach the other query
-// heads of the group through L1 (the kernel above re-reads them once per query head: 4 x the KV bytes on the Llama-3
-// shape, which at 32 sequences x 1024 keys no longer fit the L2). Each warp owns its head: no cross-warp merge.
-constexpr int ATT_GQA_WARPS = 8;
-__global__ void __launch_bounds__(ATT_GQA_WARPS * 32)
-attention_gqa_kernel(const float* __restrict__ q, int ldq, float* __restrict__ out, int ldo, int n_heads, const int32_t* __restrict__ tok_slot,
-                     const int32_t* __restrict__ tok_pos, KvGeom kv, int layer, float scale, int n_splits, float* __restrict__ part) {
-    pdl_wait();
-    pdl_trigger();
-    const int kv_h = blockIdx.x, t = blockIdx.y, sp = blockIdx.z;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
-    const int hd = kv.head_dim, npairs = hd >> 1, group = n_heads / kv.n_kv;
-    const int slot = tok_slot[t], n_keys = tok_pos[t] + 1;
-    const int per = (n_keys + n_splits - 1) / n_splits;
-    const int k_begin = sp * per, k_end = min(n_keys, k_begin + per);
-    const int32_t* pt = kv.page_table + (int64_t)slot * kv.max_pages;
-    for (int gi = warp; gi < group; gi += n_warps) {
-        const int h = kv_h * group + gi;
-        const float* qrow = q + (int64_t)t * ldq + (int64_t)h * hd;
-        float2 qv[ATT_MAX_PAIRS], o[ATT_MAX_PAIRS];
-#pragma unroll
-        for (int i = 0; i < ATT_MAX_PAIRS; ++i) {
-            const int p = lane + 32 * i;
-            qv[i] = (p < npairs) ? make_float2(qrow[2 * p], qrow[2 * p + 1]) : make_float2(0.f, 0.f);
-            o[i] = make_float2(0.f, 0.f);
-        }
-        float m = -INFINITY, l = 0.f;
-        for (int key0 = k_begin; key0 < k_end; key0 += ATT_KEYS) {
-            __half2 kr[ATT_KEYS][ATT_MAX_PAIRS], vr[ATT_KEYS][ATT_MAX_PAIRS];
-            float s[ATT_KEYS];
-#pragma unroll
-            for (int j = 0; j < ATT_KEYS; ++j) {
-                const int key = min(key0 + j, k_end - 1);  // tail keys repeat the last one and get weight 0
-                const int page = pt[key / KV_PAGE];
-                const __half2* kp = reinterpret_cast<const __half2*>(kv.pool + kv_off(kv, layer, page, 0, kv_h) + (int64_t)(key % KV_PAGE) * hd);
-                const __half2* vp = reinterpret_cast<const __half2*>(kv.pool + kv_off(kv, layer, page, 1, kv_h) + (int64_t)(key % KV_PAGE) * hd);
-#pragma unroll
-                for (int i = 0; i < ATT_MAX_PAIRS; ++i) {
-                    const int p = lane + 32 * i;
-                    kr[j][i] = (p < npairs) ? kp[p] : __half2();
-                    vr[j][i] = (p < npairs) ? vp[p] : __half2();
-                }
-            }
-#pragma unroll
-            for (int j = 0; j < ATT_KEYS; ++j) {
-                float part_dot = 0.f;
-#pragma unroll
-                for (int i = 0; i < ATT_MAX_PAIRS; ++i) {
-                    if (lane + 32 * i < npairs) {
-                        const float2 kf = __half22float2(kr[j][i]);
-                        part_dot = fmaf(qv[i].x, kf.x, part_dot);
-                        part_dot = fmaf(qv[i].y, kf.y, part_dot);
-                    }
-                }
-                s[j] = part_dot;
-            }
-#pragma unroll
-            for (int off = 16; off > 0; off >>= 1)
-#pragma unroll
-                for (int j = 0; j < ATT_KEYS; ++j) s[j] += __shfl_xor_sync(0xFFFFFFFFu, s[j], off);
-            float m_new = m;
-#pragma unroll
-            for (int j = 0; j < ATT_KEYS; ++j) {
-                s[j] = (key0 + j < k_end) ? s[j] * scale : -INFINITY;
-                m_new = fmaxf(m_new, s[j]);
-            }
-            const float corr = expf(m - m_new);
-            float pw[ATT_KEYS], psum = 0.f;
-#pragma unroll
-            for (int j = 0; j < ATT_KEYS; ++j) { pw[j] = expf(s[j] - m_new); psum += pw[j]; }
-#pragma unroll
-            for (int i = 0; i < ATT_MAX_PAIRS; ++i) {
-                if (lane + 32 * i < npairs) {
-                    float ox = corr * o[i].x, oy = corr * o[i].y;
-#pragma unroll
-                    for (int j = 0; j < ATT_KEYS; ++j) {
-                        const float2 vf = __half22float2(vr[j][i]);
-                        ox = fmaf(pw[j], vf.x, ox);
-                        oy = fmaf(pw[j], vf.y, oy);
-                    }
-                    o[i].x = ox; o[i].y = oy;
-                }
-            }
-            l = fmaf(corr, l, psum);
-            m = m_new;
-        }
-        if (n_splits == 1) {
-            const float inv = (l == 0.f) ? 0.f : 1.0f / l;
-            float* dst = out + (int64_t)t * ldo + (int64_t)h * hd;
-#pragma unroll
-            for (int i = 0; i < ATT_MAX_PAIRS; ++i) {
-                const int p = lane + 32 * i;
-                if (p < npairs) *reinterpret_cast<float2*>(dst + 2 * p) = make_float2(o[i].x * inv, o[i].y * inv);
-            }
-        } else {
-            float* dst = part + (((int64_t)t * n_heads + h) * n_splits + sp) * (hd + 2);
-            if (lane == 0) { dst[0] = m; dst[1] = l; }  // an empty key range leaves m = -inf, l = 0, o = 0
-#pragma unroll
-            for (int i = 0; i < ATT_MAX_PAIRS; ++i) {
-                const int p = lane + 32 * i;
-                if (p < npairs) { dst[2 + 2 * p] = o[i].x; dst[3 + 2 * p] = o[i].y; }
-            }
-        }
-    }
-}
+bool attention_gqa_mma_supported(int n_heads, int n_kv, int head_dim);
+cudaError_t launch_gqa_mma_phase(const float* q, int ldq, float* out, int ldo, int n_tok, int n_heads, const int32_t* tok_slot,
+                                 const int32_t* tok_pos, KvGeom kv, int layer, float scale, int n_splits, float* scratch, cudaStream_t st);
 
-// Which of the two kernels a launch takes: the grouped one when several query heads share a KV head.
-// ctx_hint: an upper bound of the longest context among the tokens (0: unknown). Short work is latency-bound and runs
-// faster with the four warps of a block sharing one head's keys; from a few thousand (token, key) pairs on the KV bytes
-// matter and the grouped kernel wins.
+// Which kernel a launch takes. ctx_hint: an upper bound of the longest context among the tokens (0: unknown). Short work
+// is latency-bound and runs on the f32 kernel, a block per (head, token, split); from a few thousand (token, key) pairs
+// on, grouped-query shapes take the tensor-core kernel, which reads the K / V rows once per group of query heads (the
+// f32 kernel re-reads them once per query head, and at 32 sequences x 1024 keys spends 5.4 ms per step of the 8B shape
+// on 4.4 GB of KV; the tensor-core kernel 1.5 ms).
 static cudaError_t launch_split_phase(const float* q, int ldq, float* out, int ldo, int n_tok, int n_heads, const int32_t* tok_slot,
                                       const int32_t* tok_pos, KvGeom kv, int layer, float scale, int n_splits, float* scratch, cudaStream_t st,
                                       int ctx_hint) {
-    const int group = kv.n_kv > 0 ? n_heads / kv.n_kv : 1;
-    if (group >= 2 && n_heads % kv.n_kv == 0 && (int64_t)n_tok * ctx_hint >= 4096)
-        return launch_pdl(attention_gqa_kernel, dim3(kv.n_kv, n_tok, n_splits), dim3(32 * (group < ATT_GQA_WARPS ? group : ATT_GQA_WARPS)), 0, st,
-                          q, ldq, out, ldo, n_heads, tok_slot, tok_pos, kv, layer, scale, n_splits, scratch);
+    if ((int64_t)n_tok * ctx_hint >= 4096 && attention_gqa_mma_supported(n_heads, kv.n_kv, kv.head_dim))
+        return launch_gqa_mma_phase(q, ldq, out, ldo, n_tok, n_heads, tok_slot, tok_pos, kv, layer, scale, n_splits, scratch, st);
     return launch_pdl(attention_split_kernel, dim3(n_heads, n_tok, n_splits), dim3(ATT_WARPS * 32), 0, st, q, ldq, out, ldo, n_heads, tok_slot,
                       tok_pos, kv, layer, scale, n_splits, scratch);
 }
@@ -483,6 +379,196 @@ attention_prefill_kernel(const float* __restrict__ q, int ldq, float* __restrict
             if (r1 < n_tok) *reinterpret_cast<float2*>(out + (int64_t)r1 * ldo + c) = make_float2(o[nd][2] * i1, o[nd][3] * i1);
         }
     }
+}
+
+// ───────────────── decode-shaped attention on tensor cores: the query heads of a GQA group as one tile ─────────────────
+// Block (KV head, token, split), 4 warps. A warp walks 16-key pages of the split's range; a page of one KV head is
+// a contiguous [16 keys][head_dim] fp16 run for K and one for V, copied asynchronously (double buffered per warp) into
+// padded shared-memory rows. Both contractions run on mma.sync.m16n8k16 with the GROUP's query heads as the M rows, so
+// K and V are read once for all heads of the group and no shuffle reduction or scalar FMA touches them.
+// Precision stays that of the f32 kernels: the 16 M rows hold, for head g < 8, the fp16 leading part of its (f32) query
+// row in row g and the fp16 remainder in row g + 8 (q = hi + lo to 2^-22); the two accumulator rows are added. The
+// softmax weights are split the same way for the second contraction. K and V are fp16 in the cache, hence exact.
+// Online softmax per page with the reference's recurrence (kernels/attention.rs:98-165); the warps' states are merged
+// through shared memory, and the block writes either the output rows (one split) or the split partials.
+constexpr int GM_WARPS = 4;
+template <int HD16>
+__global__ void __launch_bounds__(GM_WARPS * 32)
+attention_gqa_mma_kernel(const float* __restrict__ q, int ldq, float* __restrict__ out, int ldo, int n_heads, const int32_t* __restrict__ tok_slot,
+                         const int32_t* __restrict__ tok_pos, KvGeom kv, int layer, float scale, int n_splits, float* __restrict__ part) {
+    constexpr int HD = HD16 * 16, LD = HD + 8, TILE = KV_PAGE * LD;
+    extern __shared__ __align__(16) __half gm_smem[];
+    pdl_wait();
+    pdl_trigger();
+    const int kv_h = blockIdx.x, tok = blockIdx.y, sp = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int group = n_heads / kv.n_kv;
+    const int slot = tok_slot[tok], n_keys = tok_pos[tok] + 1;
+    const int n_pg = (n_keys + KV_PAGE - 1) / KV_PAGE;
+    const int per = (n_pg + n_splits - 1) / n_splits;
+    const int p_begin = sp * per, p_end = min(n_pg, p_begin + per);
+    const int32_t* pt = kv.page_table + (int64_t)slot * kv.max_pages;
+    __half* my = gm_smem + (size_t)warp * 4 * TILE;  // [buffer][K | V][16][LD]
+    // query fragments: rows g (leading fp16 part) and g + 8 (remainder) of head kv_h * group + g
+    uint32_t qa[HD16][4];
+    {
+        const bool live = g < group;
+        const float* row = q + (int64_t)tok * ldq + (int64_t)(kv_h * group + (live ? g : 0)) * HD;
+#pragma unroll
+        for (int kd = 0; kd < HD16; ++kd) {
+            float2 x0 = *reinterpret_cast<const float2*>(row + 16 * kd + 2 * t), x2 = *reinterpret_cast<const float2*>(row + 16 * kd + 8 + 2 * t);
+            if (!live) { x0 = make_float2(0.f, 0.f); x2 = x0; }
+            const __half2 h0 = __floats2half2_rn(x0.x, x0.y), h2 = __floats2half2_rn(x2.x, x2.y);
+            const float2 f0 = __half22float2(h0), f2 = __half22float2(h2);
+            qa[kd][0] = *reinterpret_cast<const uint32_t*>(&h0);
+            qa[kd][1] = pack_half2(x0.x - f0.x, x0.y - f0.y);
+            qa[kd][2] = *reinterpret_cast<const uint32_t*>(&h2);
+            qa[kd][3] = pack_half2(x2.x - f2.x, x2.y - f2.y);
+        }
+    }
+    auto fetch = [&](int pg, int buf) {  // keys 16 pg .. 16 pg + 15 of this KV head; keys past the sequence arrive as zeros
+        const int page = pt[pg];
+        const __half* ksrc = kv.pool + kv_off(kv, layer, page, 0, kv_h);
+        const __half* vsrc = kv.pool + kv_off(kv, layer, page, 1, kv_h);
+        __half* Kd = my + (size_t)buf * 2 * TILE;
+        __half* Vd = Kd + TILE;
+#pragma unroll
+        for (int it = 0; it < (KV_PAGE * HD / 8) / 32; ++it) {
+            const int idx = it * 32 + lane, kr = idx / (HD / 8), pc = idx - kr * (HD / 8);
+            const int bytes = (pg * KV_PAGE + kr < n_keys) ? 16 : 0;
+            const uint32_t kd = (uint32_t)__cvta_generic_to_shared(Kd + kr * LD + pc * 8), vd = (uint32_t)__cvta_generic_to_shared(Vd + kr * LD + pc * 8);
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(kd), "l"(ksrc + kr * HD + pc * 8), "r"(bytes) : "memory");
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(vd), "l"(vsrc + kr * HD + pc * 8), "r"(bytes) : "memory");
+        }
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
+    };
+    float o[2 * HD16][4];
+#pragma unroll
+    for (int i = 0; i < 2 * HD16; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+    float m = -INFINITY, l = 0.f;  // head g's running maximum (the same in its four lanes) and this lane's share of the denominator
+    int pg = p_begin + warp;
+    if (pg < p_end) fetch(pg, 0);
+    for (int buf = 0; pg < p_end; pg += GM_WARPS, buf ^= 1) {
+        if (pg + GM_WARPS < p_end) {
+            fetch(pg + GM_WARPS, buf ^ 1);  // that buffer was consumed before the __syncwarp that ended the last iteration
+            asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+        }
+        __syncwarp();  // every lane's copies of this page have landed
+        const __half* Ks = my + (size_t)buf * 2 * TILE;
+        const __half* Vs = Ks + TILE;
+        float s[2][4];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+#pragma unroll
+            for (int kd = 0; kd < HD16; ++kd) {
+                const uint32_t b0 = *reinterpret_cast<const uint32_t*>(Ks + (8 * j + g) * LD + 16 * kd + 2 * t);
+                const uint32_t b1 = *reinterpret_cast<const uint32_t*>(Ks + (8 * j + g) * LD + 16 * kd + 8 + 2 * t);
+                mma_f16(s[j], qa[kd][0], qa[kd][1], qa[kd][2], qa[kd][3], b0, b1);
+            }
+        }
+        // scores of head g for keys 16 pg + 8 j + 2 t (+1): leading + remainder rows, then the scale
+        float sc[2][2], mx = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const int key = pg * KV_PAGE + 8 * j + 2 * t;
+            sc[j][0] = (key < n_keys) ? (s[j][0] + s[j][2]) * scale : -INFINITY;
+            sc[j][1] = (key + 1 < n_keys) ? (s[j][1] + s[j][3]) * scale : -INFINITY;
+            mx = fmaxf(mx, fmaxf(sc[j][0], sc[j][1]));
+        }
+        mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 2));
+        const float mn = fmaxf(m, mx);  // finite: the first key of every page in range is live
+        const float c = expf(m - mn);
+        uint32_t pa[4];
+        float sum = 0.f;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const float e0 = expf(sc[j][0] - mn), e1 = expf(sc[j][1] - mn);  // exp(-inf) = 0 for masked keys
+            sum += e0 + e1;
+            const __half2 hh = __floats2half2_rn(e0, e1);
+            const float2 hf = __half22float2(hh);
+            pa[2 * j] = *reinterpret_cast<const uint32_t*>(&hh);
+            pa[2 * j + 1] = pack_half2(e0 - hf.x, e1 - hf.y);
+        }
+        l = fmaf(c, l, sum);
+        m = mn;
+        if (__any_sync(0xFFFFFFFFu, c != 1.0f)) {
+#pragma unroll
+            for (int nd = 0; nd < 2 * HD16; ++nd) { o[nd][0] *= c; o[nd][1] *= c; o[nd][2] *= c; o[nd][3] *= c; }
+        }
+#pragma unroll
+        for (int nd = 0; nd < 2 * HD16; nd += 2) {
+            uint32_t b0, b1, b2, b3;
+            const __half* src = Vs + (lane & 15) * LD + 8 * (nd + (lane >> 4));
+            const uint32_t addr = (uint32_t)__cvta_generic_to_shared(src);
+            asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3) : "r"(addr));
+            mma_f16(o[nd], pa[0], pa[1], pa[2], pa[3], b0, b1);
+            mma_f16(o[nd + 1], pa[0], pa[1], pa[2], pa[3], b2, b3);
+        }
+        __syncwarp();  // the page's buffer may be refilled from the next iteration on
+    }
+    l += __shfl_xor_sync(0xFFFFFFFFu, l, 1);
+    l += __shfl_xor_sync(0xFFFFFFFFu, l, 2);
+    // merge of the warps' states (the tile buffers are free once every warp is out of its loop)
+    __syncthreads();
+    float* sh_m = reinterpret_cast<float*>(gm_smem);          // [warp][8]
+    float* sh_l = sh_m + GM_WARPS * 8;                        // [warp][8]
+    float* sh_o = sh_l + GM_WARPS * 8;                        // [warp][8][HD]
+    if (t == 0) { sh_m[warp * 8 + g] = m; sh_l[warp * 8 + g] = l; }
+#pragma unroll
+    for (int nd = 0; nd < 2 * HD16; ++nd)
+        *reinterpret_cast<float2*>(sh_o + ((size_t)warp * 8 + g) * HD + 8 * nd + 2 * t) = make_float2(o[nd][0] + o[nd][2], o[nd][1] + o[nd][3]);
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < group * HD; idx += GM_WARPS * 32) {
+        const int hg = idx / HD, e = idx - hg * HD;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < GM_WARPS; ++w) M = fmaxf(M, sh_m[w * 8 + hg]);
+        float L = 0.f, acc = 0.f;
+#pragma unroll
+        for (int w = 0; w < GM_WARPS; ++w) {
+            const float cw = (sh_m[w * 8 + hg] == -INFINITY) ? 0.f : expf(sh_m[w * 8 + hg] - M);
+            L = fmaf(cw, sh_l[w * 8 + hg], L);
+            acc = fmaf(cw, sh_o[((size_t)w * 8 + hg) * HD + e], acc);
+        }
+        const int h = kv_h * group + hg;
+        if (n_splits == 1) {
+            out[(int64_t)tok * ldo + (int64_t)h * HD + e] = acc * ((L == 0.f) ? 0.f : 1.0f / L);
+        } else {
+            float* dst = part + (((int64_t)tok * n_heads + h) * n_splits + sp) * (HD + 2);
+            if (e == 0) { dst[0] = M; dst[1] = L; }
+            dst[2 + e] = acc;  // un-normalised, relative to M
+        }
+    }
+}
+
+bool attention_gqa_mma_supported(int n_heads, int n_kv, int head_dim) {
+    if (n_kv <= 0 || n_heads % n_kv != 0) return false;
+    const int group = n_heads / n_kv;
+    return group >= 2 && group <= 8 && head_dim % 16 == 0 && head_dim >= 16 && head_dim <= 128;
+}
+
+cudaError_t launch_gqa_mma_phase(const float* q, int ldq, float* out, int ldo, int n_tok, int n_heads, const int32_t* tok_slot,
+                                 const int32_t* tok_pos, KvGeom kv, int layer, float scale, int n_splits, float* scratch, cudaStream_t st) {
+    const int hd16 = kv.head_dim / 16;
+    const size_t smem = (size_t)GM_WARPS * 4 * KV_PAGE * (kv.head_dim + 8) * sizeof(__half);
+    const dim3 grid(kv.n_kv, n_tok, n_splits), block(GM_WARPS * 32);
+    cudaError_t le = cudaErrorInvalidValue;
+#define SP_GM(N)                                                                                                        \
+    if (hd16 == N) {                                                                                                    \
+        static PerDeviceOnce big_smem;                                                                                  \
+        if (smem > 48 * 1024) {                                                                                         \
+            le = big_smem.run([] { return cudaFuncSetAttribute(attention_gqa_mma_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024); }); \
+            if (le != cudaSuccess) return le;                                                                           \
+        }                                                                                                               \
+        le = launch_pdl(attention_gqa_mma_kernel<N>, grid, block, smem, st, q, ldq, out, ldo, n_heads, tok_slot, tok_pos, kv, layer, scale, n_splits, scratch); \
+    }
+    SP_GM(1) SP_GM(2) SP_GM(3) SP_GM(4) SP_GM(5) SP_GM(6) SP_GM(7) SP_GM(8)
+#undef SP_GM
+    return le;
 }
 
 bool attention_prefill_supported(int head_dim) { return head_dim % 16 == 0 && head_dim >= 16 && head_dim <= 128; }

@@ -238,10 +238,10 @@ def test_batched_decode_of_twenty_sequences_goes_through_the_large_m_path(oracle
 
 
 @pytest.mark.parametrize("name", ["tiny_llama", "tiny_qwen", "tiny_llama_wide"])
-def test_batched_decode_at_longer_context_takes_the_grouped_attention_kernel(oracle, name):
-    """32 sequences x ~130 cached keys: enough (token, key) pairs for the grouped-query kernel (one block per KV head, a
-    warp per query head of its group, keys split by context). Its rows must equal each sequence decoded alone — a
-    1-row step at the same context takes the other kernel — to rounding, and sit on the oracle."""
+def test_batched_decode_at_longer_context_takes_the_tensor_core_grouped_kernel(oracle, name):
+    """32 sequences x ~130 cached keys: enough (token, key) pairs for the tensor-core grouped-query kernel (a block per
+    KV head whose query heads form the rows of the mma tile, keys split by context). Its rows must equal each sequence
+    decoded alone — a 1-row step at the same context takes the f32 kernel — to rounding, and sit on the oracle."""
     cfg, W = tiny_model(name, max_ctx=192)
     B = 32
     eng = ForwardEngine.from_weights(cfg, W, max_batch=B, max_tokens=64)

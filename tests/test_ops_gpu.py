@@ -159,7 +159,10 @@ def test_rope(oracle):
 
 
 # (H, Hkv, sq, sk, hd) from wgpu/tests/resident.rs:238-277 plus longer contexts spanning several KV pages
-ATT_CASES = [(14, 2, 1, 23, 64), (4, 4, 6, 6, 80), (8, 2, 5, 9, 128), (32, 8, 1, 300, 128), (2, 1, 17, 50, 32)]
+# the last four have enough (token, key) pairs for the tensor-core grouped-query kernel: groups of 4, 7, 6 and 8 heads,
+# split and unsplit (sq > 4), last pages ragged
+ATT_CASES = [(14, 2, 1, 23, 64), (4, 4, 6, 6, 80), (8, 2, 5, 9, 128), (32, 8, 1, 300, 128), (2, 1, 17, 50, 32),
+             (32, 8, 1, 5003, 128), (14, 2, 3, 2001, 64), (12, 2, 6, 1100, 128), (16, 2, 2, 2500, 32)]
 
 
 @pytest.mark.parametrize("H,Hkv,sq,sk,hd", ATT_CASES)
