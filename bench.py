@@ -382,6 +382,26 @@ def main() -> None:
     gemv_n = (4 * cfg["n_layers"] + 1) * P
     eng.truncate_cache(PROMPT)
 
+    # ── comparison arm under tensor parallelism: the same step with its sums through ncclAllReduce ──
+    nccl_arm = None
+    if world > 1 and os.environ.get("SAPIENT_BENCH_NCCL_ARM", "1") != "0":
+        KN = min(K, 64)
+        eng.tp_nccl_init()
+        eng.tp_set_allreduce(True)
+        t2 = eng.decode_greedy(first, [0], Wm)  # captures this arm's step graph
+        barrier()
+        ev0.record(stream)
+        eng.decode_greedy(t2[-1], [0], KN, fetch=False)
+        ev1.record(stream)
+        barrier()
+        tn = torch.tensor([ev0.elapsed_time(ev1)], device=f"cuda:{local}", dtype=torch.float64)
+        dist.all_reduce(tn, op=dist.ReduceOp.MAX)
+        eng.tp_set_allreduce(False)
+        nccl_arm = {"tokens_per_s": KN / (float(tn[0]) / 1000.0), "ms_per_step": float(tn[0]) / KN, "steps": KN,
+                    "what": "the same tensor-parallel decode step with the o_proj / down_proj sums through ncclAllReduce "
+                            "(partial product to scratch, all-reduce in the step graph, one add) instead of the push fused "
+                            "into the GEMV epilogue"}
+
     # ── the other sections of the metric (extra keys of the same line) ──
     eng.close()
     peaks_now, _ = measured_peaks()
@@ -425,6 +445,8 @@ def main() -> None:
                               "frac_of_measured_peak": ((wbytes + kv_bytes) / world / (peaks["hbm_gbs"] * 1e9) * 1e3) / (dev_ms / K)},
             "family_ms_per_step": fam_ms,
         }
+        if nccl_arm:
+            line["tp_allreduce_arm"] = nccl_arm
         if sections.get("batch32"):
             line["batch32"] = sections["batch32"]
         if sections.get("sweep"):

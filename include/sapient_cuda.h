@@ -182,6 +182,16 @@ int32_t sp_cuda_engine_tp_connect_local(SpEngine* e, void* const* blocks, int32_
  * SP_ERR_COMM). Long enough for a peer that is still capturing its first step graph or finishing a prefill; a
  * supervisor that detects failures on the host can lower it. Takes effect with the next launch. */
 int32_t sp_cuda_engine_tp_set_wait_ms(SpEngine* e, int32_t ms);
+/* Comparison arm for the sums of the column-split products (o_proj, down_proj): mode 1 sends them through ncclAllReduce
+ * on the engine's stream (partial product to scratch, all-reduce, one add) instead of the default mode 0, the push from
+ * the GEMV epilogue into every rank's memory. NCCL is not linked: libnccl_path names the shared object to open (the copy
+ * the process already uses; NULL or "" = "libnccl.so.2" by the loader's search). Rank 0 makes a 128-byte id with
+ * sp_cuda_nccl_unique_id, the caller hands it to every rank, every rank calls sp_cuda_engine_tp_nccl_init (a collective),
+ * then sp_cuda_engine_tp_set_allreduce chooses the arm (all ranks the same). The arg-max exchange stays on peer stores. */
+#define SP_NCCL_ID_BYTES 128
+int32_t sp_cuda_nccl_unique_id(const char* libnccl_path, void* out, size_t cap);
+int32_t sp_cuda_engine_tp_nccl_init(SpEngine* e, const char* libnccl_path, const void* unique_id);
+int32_t sp_cuda_engine_tp_set_allreduce(SpEngine* e, int32_t mode);
 /* After SP_ERR_COMM, or to restart a group: exchange counters, arrival marks and the sticky error flag back to their
  * initial state. EVERY rank calls it, with a host-side barrier before (no rank still inside a step) and after (no rank
  * starts a step before all have cleared). The KV caches are untouched: truncate or reset them as the caller sees fit. */

@@ -59,6 +59,9 @@ SIGNATURES = {
     "sp_cuda_engine_tp_connect": (_i32, [_vp, _vp, _i32]),
     "sp_cuda_engine_vocab_local": (_i32, [_vp, _vp, _vp]),
     "sp_cuda_engine_tp_set_wait_ms": (_i32, [_vp, _i32]),
+    "sp_cuda_nccl_unique_id": (_i32, [C.c_char_p, _vp, C.c_size_t]),
+    "sp_cuda_engine_tp_nccl_init": (_i32, [_vp, C.c_char_p, _vp]),
+    "sp_cuda_engine_tp_set_allreduce": (_i32, [_vp, _i32]),
     "sp_cuda_engine_tp_reset": (_i32, [_vp]),
     "sp_cuda_engine_tp_block": (_i32, [_vp, _vp]),
     "sp_cuda_engine_tp_connect_local": (_i32, [_vp, _vp, _i32]),

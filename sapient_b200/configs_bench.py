@@ -78,10 +78,10 @@ def _roof(bytes_per_step: float, ms_per_step: float) -> dict:
             "peak_source": src, "frac_of_8TBs": gbs / 8000.0}
 
 
-def decode_case(name: str, prompt_len: int, steps: int, batch: int, label: str, prefill_timed: bool = False) -> dict:
+def decode_case(name: str, prompt_len: int, steps: int, batch: int, label: str, prefill_timed: bool = False, fast: bool = False) -> dict:
     cfg, W = _build(name, max_ctx=prompt_len + steps + 64, seed=1000)
     # rows per forward step: a whole prompt of up to 512 tokens in one step (fewer, fuller launches of the large-M GEMM)
-    eng, stream = _engine(cfg, W, max_batch=batch, max_tokens=max(256, min(prompt_len, 512)))
+    eng, stream = _engine(cfg, W, max_batch=batch, max_tokens=max(256, min(prompt_len, 512)), fast_large_m=fast)
     rng = np.random.default_rng(0)
     first = np.empty(batch, np.uint32)
     prefill_ms = 0.0
@@ -101,7 +101,8 @@ def decode_case(name: str, prompt_len: int, steps: int, batch: int, label: str, 
     ctx_mid = prompt_len + warm + steps // 2
     step_bytes = _weight_bytes(cfg, W) + batch * ctx_mid * kv_per_pos
     line = {"case": label, "model": name, "batch": batch, "prompt_len": prompt_len, "steps": steps, "ms_per_step": ms / steps,
-            "tokens_per_s": batch * steps / (ms / 1e3), "roofline": _roof(step_bytes, ms / steps), "data": "synthetic"}
+            "tokens_per_s": batch * steps / (ms / 1e3), "roofline": _roof(step_bytes, ms / steps), "data": "synthetic",
+            "large_m_path": "tcgen05 GEMM, fp16 operands (opt-in)" if fast else "integer-digit GEMV passes (default)"}
     if prefill_timed:
         line["prefill_tokens_per_s"] = batch * prompt_len / (prefill_ms / 1e3)
         line["prefill_ms"] = prefill_ms
@@ -216,13 +217,14 @@ def main() -> None:
     ap.add_argument("--model", default="llama8b", choices=sorted(synth.CONFIGS))
     ap.add_argument("--prompt", type=int, default=None)
     ap.add_argument("--steps", type=int, default=None)
+    ap.add_argument("--fast", action="store_true", help="steps of 17 rows and more on the tcgen05 GEMM (fp16 operands)")
     a = ap.parse_args()
     if a.case == "c0":
-        line = decode_case("qwen05b", a.prompt or 128, a.steps or 128, 1, "c0", prefill_timed=True)
+        line = decode_case("qwen05b", a.prompt or 128, a.steps or 128, 1, "c0", prefill_timed=True, fast=a.fast)
     elif a.case == "c2":
-        line = decode_case("phi2", a.prompt or 512, a.steps or 256, 1, "c2", prefill_timed=True)
+        line = decode_case("phi2", a.prompt or 512, a.steps or 256, 1, "c2", prefill_timed=True, fast=a.fast)
     elif a.case == "c3b32":
-        line = decode_case("llama8b", a.prompt or 256, a.steps or 64, 32, "c3b32", prefill_timed=True)
+        line = decode_case("llama8b", a.prompt or 256, a.steps or 64, 32, "c3b32", prefill_timed=True, fast=a.fast)
     elif a.case == "prefill":
         line = prefill_case(a.model, a.prompt or 512)
     elif a.case == "load":

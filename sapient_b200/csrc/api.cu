@@ -30,6 +30,7 @@ struct SpEngine {
 
 int sp_engine_from_gguf_impl(const char* path, int device, int max_ctx, int max_batch, Engine** out);  // gguf.cu
 namespace sp {
+int nccl_unique_id(const char* libpath, void* out, size_t cap);  // nccl_arm.cu
 int spec_greedy(Engine* target, Engine* draft, const uint32_t* prompt, size_t n_prompt, int k, size_t max_new, const uint32_t* eos,
                 int n_eos, uint32_t* tokens_out, size_t* n_out, uint64_t* stats);  // spec.cu
 }
@@ -796,6 +797,26 @@ int32_t sp_cuda_engine_load_stats(const SpEngine* e, double* seconds, uint64_t* 
     if (seconds) *seconds = e->e->load_seconds;
     if (bytes) *bytes = e->e->load_bytes;
     return SP_OK;
+}
+
+int32_t sp_cuda_nccl_unique_id(const char* libnccl_path, void* out, size_t cap) {
+    API_BEGIN
+    return sp::nccl_unique_id(libnccl_path, out, cap);
+    API_END
+}
+
+int32_t sp_cuda_engine_tp_nccl_init(SpEngine* e, const char* libnccl_path, const void* unique_id) {
+    API_BEGIN
+    if (!e) { set_error("null engine"); return SP_ERR_ARG; }
+    return e->e->tp_nccl_init(libnccl_path, unique_id);
+    API_END
+}
+
+int32_t sp_cuda_engine_tp_set_allreduce(SpEngine* e, int32_t mode) {
+    API_BEGIN
+    if (!e) { set_error("null engine"); return SP_ERR_ARG; }
+    return e->e->tp_set_allreduce(mode);
+    API_END
 }
 
 int32_t sp_cuda_engine_tp_set_wait_ms(SpEngine* e, int32_t ms) {

@@ -148,6 +148,9 @@ attention_split_kernel(const float* __restrict__ q, int ldq, float* __restrict__
 }
 
 bool attention_gqa_mma_supported(int n_heads, int n_kv, int head_dim);
+bool attention_takes_mma(int n_tok, int ctx_hint, int n_heads, int n_kv, int head_dim) {
+    return (int64_t)n_tok * ctx_hint >= 4096 && attention_gqa_mma_supported(n_heads, n_kv, head_dim);
+}
 cudaError_t launch_gqa_mma_phase(const float* q, int ldq, float* out, int ldo, int n_tok, int n_heads, const int32_t* tok_slot,
                                  const int32_t* tok_pos, KvGeom kv, int layer, float scale, int n_splits, float* scratch, cudaStream_t st);
 
@@ -159,7 +162,7 @@ cudaError_t launch_gqa_mma_phase(const float* q, int ldq, float* out, int ldo, i
 static cudaError_t launch_split_phase(const float* q, int ldq, float* out, int ldo, int n_tok, int n_heads, const int32_t* tok_slot,
                                       const int32_t* tok_pos, KvGeom kv, int layer, float scale, int n_splits, float* scratch, cudaStream_t st,
                                       int ctx_hint) {
-    if ((int64_t)n_tok * ctx_hint >= 4096 && attention_gqa_mma_supported(n_heads, kv.n_kv, kv.head_dim))
+    if (attention_takes_mma(n_tok, ctx_hint, n_heads, kv.n_kv, kv.head_dim))
         return launch_gqa_mma_phase(q, ldq, out, ldo, n_tok, n_heads, tok_slot, tok_pos, kv, layer, scale, n_splits, scratch, st);
     return launch_pdl(attention_split_kernel, dim3(n_heads, n_tok, n_splits), dim3(ATT_WARPS * 32), 0, st, q, ldq, out, ldo, n_heads, tok_slot,
                       tok_pos, kv, layer, scale, n_splits, scratch);

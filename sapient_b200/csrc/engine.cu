@@ -58,6 +58,7 @@ Engine::~Engine() {
     if (d_tokens_) cudaFree(d_tokens_);
     for (auto& kv : tensors_) { if (kv.second.d) cudaFree(kv.second.d); if (kv.second.tiled) cudaFree(kv.second.tiled); }
     ws_.release();
+    tp_nccl_release();
     tp_release();
     if (att_scratch_) cudaFree(att_scratch_);
     if (argmax_scratch_) cudaFree(argmax_scratch_);

@@ -92,6 +92,9 @@ class Engine {
     int tp_check();                                 // SP_ERR_COMM if a wait on a peer gave up
     int tp_set_wait_ms(int ms);                     // bound of the device-side waits on peers
     int tp_reset();                                 // counters, marks and the sticky flag back to the initial state
+    // Comparison arm (nccl_arm.cu): the sums of the column-split products through ncclAllReduce instead of the fused push.
+    int tp_nccl_init(const char* libpath, const void* unique_id);  // collective over the group
+    int tp_set_allreduce(int mode);                 // 0: fused peer push (default); 1: library all-reduce
     // After a stream synchronise: SP_ERR_CUDA if a bounded mbarrier wait of one of this device's kernels ran out since
     // the last check (the kernel's outputs are then stale), else tp_check().
     int device_check();
@@ -163,6 +166,10 @@ class Engine {
     TpDev* d_tp_ = nullptr;         // device copy of the peer table
     uint8_t* tp_peer_[TP_MAX_RANKS] = {};
     bool tp_connected_ = false;
+    void* nccl_comm_ = nullptr;
+    bool tp_use_nccl_ = false;
+    int nccl_all_reduce(float* buf, size_t count);
+    void tp_nccl_release();
     uint64_t tp_wait_ns_ = TP_WAIT_NS_DEFAULT;
     bool tp_pending_ = false;       // partial rows have been pushed, x_ still lacks their sum
     // decode_greedy returned without waiting (tokens_out == null): copies out of the pinned staging buffers may still be

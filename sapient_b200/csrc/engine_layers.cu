@@ -72,6 +72,9 @@ int Engine::gemv(const float* x, int ldx, int m, int k, const DevTensor* w0, con
             return SP_OK;
         }
     }
+    // comparison arm: the partial product to scratch, a library all-reduce, one add into the residual stream
+    const bool via_nccl = tp_sum && tp_use_nccl_ && tiled;
+    if (via_nccl && (y0 != x_ || res != x_ || ldy0 != d.hidden || w1)) { set_error("internal: tensor-parallel sum outside the residual stream"); return SP_ERR_STATE; }
     if (tiled) {
         // tensor-core path: digits of up to 16 activation rows at a time, all segments share them
         const int pass = imma_rows_per_pass();
@@ -81,12 +84,12 @@ int Engine::gemv(const float* x, int ldx, int m, int k, const DevTensor* w0, con
             ia.k = k; ia.m = std::min(pass, m - m0);
             ia.res = (res && !tp_sum) ? res + (size_t)m0 * ldy0 : nullptr;
             ia.ldres = ldy0;
-            ia.tp = tp_sum ? d_tp_ : nullptr;
+            ia.tp = (tp_sum && !via_nccl) ? d_tp_ : nullptr;
             ia.tp_row0 = m0;
             ia.nseg = 0;
             for (int i = 0; i < 3 && ws[i]; ++i) {
                 ImmaSeg& sgm = ia.seg[i];
-                sgm.wt = ws[i]->tiled; sgm.bias = bs[i]; sgm.y = ys[i] + (size_t)m0 * ldy0; sgm.dtype = ws[i]->dtype;
+                sgm.wt = ws[i]->tiled; sgm.bias = (via_nccl && d.tp_rank != 0) ? nullptr : bs[i]; sgm.y = (via_nccl ? h_ : ys[i]) + (size_t)m0 * ldy0; sgm.dtype = ws[i]->dtype;
                 sgm.n = (int)ws[i]->dims[0]; sgm.ldy = ldy0; sgm.bpt = imma_q8_bpt(k);
                 ia.nseg++;
             }
@@ -95,6 +98,11 @@ int Engine::gemv(const float* x, int ldx, int m, int k, const DevTensor* w0, con
                 SP_LAUNCH(F_ELEM, launch_act_quant(x + (size_t)m0 * ldx, ldx, ia, stream));
             }
             SP_LAUNCH(F_GEMV, launch_gemv_imma(ia, stream));
+        }
+        if (via_nccl) {
+            SP_TRY(nccl_all_reduce(h_, (size_t)m * d.hidden));
+            SP_LAUNCH(F_ELEM, launch_add(x_, h_, x_, (int64_t)m * d.hidden, stream));
+            return SP_OK;
         }
         // the partial rows are on their way to every rank; whoever reads y0 next adds their sum first
         if (tp_sum) {
@@ -171,6 +179,11 @@ int Engine::gemm_xh_sum(int m, int k, const DevTensor* w, const float* b) {
     if (!tp_connected_) { set_error("tensor-parallel engine used before tp_connect"); return SP_ERR_STATE; }
     // the partial product of this rank's columns (the bias once, on rank 0) to scratch, then to every rank's receive area
     SP_TRY(gemm_xh(m, k, w, d.tp_rank == 0 ? b : nullptr, h_, d.hidden));
+    if (tp_use_nccl_) {
+        SP_TRY(nccl_all_reduce(h_, (size_t)m * d.hidden));
+        SP_LAUNCH(F_ELEM, launch_add(x_, h_, x_, (int64_t)m * d.hidden, stream));
+        return SP_OK;
+    }
     SP_LAUNCH(F_GEMV, launch_tp_push(h_, d.hidden, m, d.hidden, d_tp_, stream));
     tp_pending_ = true;
     return SP_OK;
@@ -185,6 +198,14 @@ static inline bool all_tiled(const DevTensor* a, const DevTensor* b = nullptr, c
 // keys the unsplit kernel is a chain of 260 dependent iterations per block (measured 6 ms of attention per step of the
 // 8B shape; the KV bytes need 0.7 ms). The count is a power of two up to 16 and part of the step graph's key.
 int Engine::step_splits(int T) const {
+    if (T <= ATT_SPLIT_TOKENS && attention_takes_mma(T, step_ctx_, d.n_heads, d.n_kv_heads, d.head_dim)) {
+        // tensor-core kernel, a block per (KV head, token, split): enough blocks to fill the SMs three deep, but no range
+        // shorter than 256 keys (4 pages per warp) — its fixed cost per block (query fragments, warp merge) is larger
+        int want = 1, limit = 1;
+        while (want < ATT_SPLITS && d.n_kv_heads * T * want < 444) want <<= 1;
+        while (limit < ATT_SPLITS && limit * 2 * 256 <= step_ctx_) limit <<= 1;
+        return std::min(want, limit);
+    }
     int splits = 1;
     if (T <= imma_rows_per_pass()) splits = d.n_heads * T <= 64 ? ATT_SPLITS : d.n_heads * T <= 128 ? 8 : 4;
     if (T <= ATT_SPLIT_TOKENS) {

@@ -119,6 +119,9 @@ cudaError_t launch_norm_quant(const float* x, int ldx, const float* w, const flo
 cudaError_t launch_act_fn_quant(const float* gu, int ld, int ffn, int act, const ImmaArgs& a, cudaStream_t st);
 cudaError_t launch_attn_merge_quant(const float* part, int n_heads, int n_splits, int hd, float* out, int ldo, const ImmaArgs& a,
                                     cudaStream_t st);
+// Whether a decode-shaped launch with these sizes runs on the tensor-core grouped-query kernel (ctx_hint as for
+// launch_attention): callers choose the split count accordingly — that kernel wants few, long key ranges.
+bool attention_takes_mma(int n_tok, int ctx_hint, int n_heads, int n_kv, int head_dim);
 // The split phase of launch_attention alone (partials to scratch); n_splits > 1.
 cudaError_t launch_attention_split(const float* q, int ldq, int n_tok, int n_heads, const int32_t* tok_slot, const int32_t* tok_pos,
                                    KvGeom kv, int layer, float scale, int n_splits, float* scratch, cudaStream_t st, int ctx_hint = 0);

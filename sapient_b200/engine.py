@@ -122,6 +122,42 @@ class ForwardEngine:
         with a host barrier before and after."""
         check(lib().sp_cuda_engine_tp_reset(self._h))
 
+    @staticmethod
+    def nccl_library_path() -> str:
+        """The NCCL shared object that torch ships (the copy torch.distributed's nccl backend loads), else the soname."""
+        import os
+
+        try:
+            import nvidia.nccl as _n
+
+            for base in list(getattr(_n, "__path__", [])):
+                cand = os.path.join(base, "lib", "libnccl.so.2")
+                if os.path.exists(cand):
+                    return cand
+        except ImportError:
+            pass
+        return "libnccl.so.2"
+
+    def tp_nccl_init(self, group=None) -> None:
+        """Sets up the library all-reduce arm (comparison with the fused peer push): rank 0 makes the NCCL id, the
+        torch.distributed group carries it to the others, every rank joins. Collective over the group."""
+        import torch.distributed as dist
+
+        path = self.nccl_library_path().encode()
+        box = [None]
+        if dist.get_rank(group) == 0:
+            buf = C.create_string_buffer(128)
+            check(lib().sp_cuda_nccl_unique_id(path, buf, 128))
+            box[0] = bytes(buf.raw)
+        src = dist.get_global_rank(group, 0) if group is not None else 0
+        dist.broadcast_object_list(box, src=src, group=group)
+        check(lib().sp_cuda_engine_tp_nccl_init(self._h, path, box[0]))
+
+    def tp_set_allreduce(self, nccl: bool) -> None:
+        """False (default): sums of the column-split products by the push fused into the GEMV epilogue; True: through
+        ncclAllReduce (after tp_nccl_init). Every rank the same."""
+        check(lib().sp_cuda_engine_tp_set_allreduce(self._h, int(bool(nccl))))
+
     def tp_block(self) -> int:
         """Device address of this rank's communication block (for engines of one process)."""
         p = C.c_void_p()

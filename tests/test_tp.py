@@ -172,8 +172,18 @@ def _cuda_rank_main(rank, size, port, name, ids, steps, out_path):
     dist.barrier()
     again = eng.forward_all_logits(ids)
     dist.barrier()
+    # the comparison arm: the same sums through ncclAllReduce (eager 7-row step, then a graph-captured 1-row step)
+    eng.tp_nccl_init()
+    eng.tp_set_allreduce(True)
+    nccl_prefill = eng.forward_all_logits(ids)
+    nccl_step = eng.forward_logits([int(ids[0])], True)
+    eng.tp_set_allreduce(False)
+    dist.barrier()
+    back = eng.forward_all_logits(ids)
+    dist.barrier()
     if rank == 0:
-        np.savez(out_path, prefill=prefill, step=step, toks=np.asarray(toks), big=big, again=again)
+        np.savez(out_path, prefill=prefill, step=step, toks=np.asarray(toks), big=big, again=again, nccl_prefill=nccl_prefill,
+                 nccl_step=nccl_step, back=back)
     eng.close()
     dist.destroy_process_group()
 
@@ -203,6 +213,10 @@ def test_two_gpu_engine_matches_single_gpu(tmp_path):
     assert np.abs(got["step"] - want_step).max() < 2e-2
     assert got["toks"].shape == want_toks.shape
     assert np.array_equal(got["again"], got["prefill"])  # the same exchange sequence after tp_reset
+    # library all-reduce arm: x + (p0 + p1) instead of (x + p0) + p1, otherwise the same arithmetic
+    assert np.abs(got["nccl_prefill"] - got["prefill"]).max() < 1e-3
+    assert np.abs(got["nccl_step"] - got["step"]).max() < 1e-3
+    assert np.array_equal(got["back"], got["prefill"])  # and the fused push again after switching back
     ids40 = np.random.default_rng(40).integers(0, cfg["vocab"], 40).astype(np.uint32)
     one.set_large_m_gemm(True)
     assert np.abs(got["big"] - one.forward_all_logits(ids40)).max() < 2e-2
