@@ -69,19 +69,8 @@ __device__ __forceinline__ void ring_bulk_g2s(void* dst, const void* src, int by
                  "l"(src), "r"(bytes), "r"(ring_smem_u32(bar))
                  : "memory");
 }
-__device__ __forceinline__ bool ring_wait(uint64_t* bar, uint32_t parity, int mode = 0) {
+__device__ __forceinline__ bool ring_wait(uint64_t* bar, uint32_t parity) {
     const uint32_t addr = ring_smem_u32(bar);
-    if (mode) {
-        for (int spin = 0; spin < (1 << 26); ++spin) {
-            uint32_t ok;
-            asm volatile("{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
-                         : "=r"(ok)
-                         : "r"(addr), "r"(parity)
-                         : "memory");
-            if (ok) return true;
-        }
-        return false;
-    }
     for (int spin = 0; spin < RING_SPIN_LIMIT; ++spin) {
         uint32_t ok;
         asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
@@ -316,8 +305,6 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_ring_kernel(const __gri
     const int64_t T = a.total_tiles;
     const int t_begin = (int)(T * blockIdx.x / gridDim.x), t_end = (int)(T * (blockIdx.x + 1) / gridDim.x);
 
-    unsigned long long tk0 = 0;
-    if (a.dbg & 128) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tk0));
     if (threadIdx.x == 0) {
         for (int s = 0; s < a.stages; ++s) { ring_mbar_init(&full[s], 1); ring_mbar_init(&empty[s], CW); }
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -339,23 +326,15 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_ring_kernel(const __gri
                 const int tb = ring_tile_bytes(a.seg[ps].dtype);
                 const uint8_t* src = a.seg[ps].wt + (int64_t)(pt - a.seg_tile0[ps]) * tb;
                 ring_expect_tx(&full[pslot], len * tb);
-                if (a.dbg & 8) {
-                    for (int w = 0; w < len; ++w)
-                        ring_bulk_g2s(ring + (size_t)pslot * a.stage_bytes + (size_t)w * tb, src + (size_t)w * tb, tb, &full[pslot]);
-                } else {
-                    ring_bulk_g2s(ring + (size_t)pslot * a.stage_bytes, src, len * tb, &full[pslot]);
-                }
+                ring_bulk_g2s(ring + (size_t)pslot * a.stage_bytes, src, len * tb, &full[pslot]);
             }
             pt += len;
             pslot = pslot + 1 == a.stages ? 0 : pslot + 1;
         };
         int issued = 0;
         for (int i = 0; i < a.stages && pt < t_end; ++i) { issue(); ++issued; }
-        unsigned long long tk1 = 0, tk2 = 0, tk3 = 0, tk4 = 0;
-        if (a.dbg & 128) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tk1));
         pdl_wait();      // the residual (and the scratch of shared rows) belong to the previous kernel until here
         pdl_trigger();
-        if (a.dbg & 128) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tk2));
 
         // Consumers hand over, per tile, the 16 x m outputs with the digit columns already added (80 floats at most):
         // lane l of this warp owns outputs l, l + 32, l + 64 (output idx = 16 * activation row + weight row of the tile
@@ -398,7 +377,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_ring_kernel(const __gri
                 const float* f = reinterpret_cast<const float*>(slot_base + (size_t)w * tb);
 #pragma unroll
                 for (int r = 0; r < R; ++r) {
-                    v[w][r] = (w < len && lane + 32 * r < n_out && !(a.dbg & 16)) ? f[lane + 32 * r] : 0.f;
+                    v[w][r] = (w < len && lane + 32 * r < n_out) ? f[lane + 32 * r] : 0.f;
                     guard += v[w][r];
                 }
             }
@@ -413,7 +392,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_ring_kernel(const __gri
             for (int w = 0; w < CW; ++w) {
                 if (w < len) {
                     if (cs != cur_seg || nrow != cur_row) {
-                        if (cur_row >= 0 && !(a.dbg & 32)) ring_row_out<R>(ro, cur_seg, cur_row, racc);
+                        if (cur_row >= 0) ring_row_out<R>(ro, cur_seg, cur_row, racc);
 #pragma unroll
                         for (int r = 0; r < R; ++r) racc[r] = 0.f;
                         cur_seg = cs;
@@ -427,13 +406,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_ring_kernel(const __gri
             ct += len;
             if (++cslot == a.stages) { cslot = 0; cpar ^= 1u; }
         }
-        if (a.dbg & 128) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tk3));
         if (ok && cur_row >= 0) ring_row_out<R>(ro, cur_seg, cur_row, racc);
-        if (a.dbg & 128) {
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tk4));
-            if (lane == 0 && (blockIdx.x == 0 || blockIdx.x == 77 || blockIdx.x == 147))
-                printf("cta %d: prime %llu wait %llu loop %llu tail %llu ns, chunks %d stages %d\n", blockIdx.x, tk1 - tk0, tk2 - tk1, tk3 - tk2, tk4 - tk3, retired, a.stages);
-        }
         if (!ok) {
             if (lane == 0) *reinterpret_cast<volatile int*>(a.err) = 1;  // host-mapped flag: a plain store
             // copies still in flight write into this CTA's shared memory: wait for them (bounded) before leaving
@@ -525,8 +498,8 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_ring_kernel(const __gri
         while (ct < t_end) {
             const int len = chunk_len(ct, cs);
             if (warp < len && ok) {
-                ok = ring_wait(&full[slot], par, a.dbg & 2);
-                if (ok && !(a.dbg & 1)) {
+                ok = ring_wait(&full[slot], par);
+                if (ok) {
                     const int dtype = FMT ? FMT : a.seg[cs].dtype, tb = ring_tile_bytes(dtype);
                     const int kt = (ct + warp - a.seg_tile0[cs]) % KT;
                     uint8_t* tile = ring + (size_t)slot * a.stage_bytes + (size_t)warp * tb;
@@ -627,19 +600,15 @@ bool ring_plan(RingArgs& a, const RingScratch& sc, bool share_sm) {
     a.off_xq = off; off += a.kt * ncols * 256;
     off = (off + 127) / 128 * 128;
     a.off_stage = off;
-    static const int forced = [] { const char* e = std::getenv("SAPIENT_RING_STAGES"); return e ? atoi(e) : 0; }();
-    static const int dbg = [] { const char* e = std::getenv("SAPIENT_RING_DEBUG"); return e ? atoi(e) : 0; }();
-    a.dbg = dbg;
     // the wide single-format instance when its ring still has two slots, else the 15-consumer instance
     const int fmt = all_q4 ? T_Q4_K : all_q6 ? T_Q6_K : 0;
-    for (int cw : {fmt && nt == 1 && !(dbg & 64) ? RING_CW_SINGLE : RING_CW_MIXED, RING_CW_MIXED}) {
+    for (int cw : {fmt && nt == 1 ? RING_CW_SINGLE : RING_CW_MIXED, RING_CW_MIXED}) {
         a.cw = cw;
         a.fmt = cw == RING_CW_SINGLE ? fmt : 0;
         a.stage_bytes = (cw * max_tb + 127) / 128 * 128;
         const int stages = (RING_SMEM_MAX - off) / a.stage_bytes;
         if (stages < 2) continue;
         a.stages = std::min(stages, RING_MAX_STAGES);
-        if (forced >= 2) a.stages = std::min(a.stages, forced);
         a.smem_total = off + a.stages * a.stage_bytes;
         a.fix_part = sc.part;
         a.fix_cnt = sc.cnt;

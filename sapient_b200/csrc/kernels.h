@@ -101,7 +101,6 @@ struct RingArgs {
     float* fix_part;
     unsigned* fix_cnt;
     int* err;
-    int dbg;              // experiments: bit 0 = consumers skip the arithmetic
 };
 // One-time per-device set-up of the ring kernel's error flag (host-mapped memory): call before the first launch on a
 // device, outside stream capture (engine finalize and weight upload do).
