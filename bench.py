@@ -217,9 +217,10 @@ def batch32_section(cfg, W, wbytes: int, local: int, rank: int, world: int, stre
 
 
 def sweep_section() -> list:
-    """Operator sweep of the standalone dequant-matmul: achieved GB/s at M = 1 and TFLOP/s at M = 512 for the four
-    benchmark shapes and the three block formats (weights rotated through more than twice the L2, CUDA events on the
-    launching stream)."""
+    """Operator sweep of the standalone dequant-matmul for the four benchmark shapes and the three block formats (weights
+    rotated through more than twice the L2, CUDA events on the launching stream): achieved GB/s at M = 1 and at M = 32
+    (the default path: exact integer products; M = 32 is one pass of the many-row kernel) and TFLOP/s at M = 512 on the
+    opt-in tcgen05 GEMM (fp16 operands)."""
     from sapient_b200 import sweep
 
     rows = []
@@ -227,10 +228,13 @@ def sweep_section() -> list:
         for n, k in sweep.SHAPES:
             big = n * k > (1 << 28)
             r1 = sweep.run_case(dt, n, k, 1, 24 if big else 60, 3, None, 0)
-            r512 = sweep.run_case(dt, n, k, 512, 8 if big else 20, 2, 2 if big else None, 0)
+            r32 = sweep.run_case(dt, n, k, 32, 16 if big else 40, 3, None, 0)
+            r512 = sweep.run_case(dt, n, k, 512, 8 if big else 20, 2, 2 if big else None, 0, large_m=True)
             rows.append({"dtype": dt, "n": n, "k": k, "m1_us": round(r1["us"], 2), "m1_gbs": round(r1["gbs"], 1),
-                         "m1_frac_of_measured_peak": round(r1["frac_of_hbm_peak"], 3), "m512_us": round(r512["us"], 1),
-                         "m512_tflops": round(r512["tflops"], 1)})
+                         "m1_frac_of_measured_peak": round(r1["frac_of_hbm_peak"], 3), "m32_us": round(r32["us"], 2),
+                         "m32_gbs": round(r32["gbs"], 1), "m32_frac_of_measured_peak": round(r32["frac_of_hbm_peak"], 3),
+                         "m512_us": round(r512["us"], 1), "m512_tflops": round(r512["tflops"], 1),
+                         "m512_path": "tcgen05 GEMM, fp16 operands (opt-in)"})
     return rows
 
 

@@ -82,14 +82,17 @@ int32_t sp_cuda_check_kernels(int32_t device);
  * their captured step graphs when it changes (sp_cuda_engine_set_graphs off/on). */
 int32_t sp_cuda_set_activation_digits(int32_t mode);
 /* Which GEMV kernel runs (process-wide; op-level calls — engines have sp_cuda_engine_set_ring):
- *   0 (default) and 2: the tensor-core GEMV with one CTA per 16-row tile row;
+ *   0 (default): the tensor-core GEMV — one CTA per 16-row tile row for up to 10 activation rows, the one-pass many-row
+ *      kernel (a CTA per eight tile rows, digits of a k-tile shared in shared memory) for passes of 11 to 32 rows;
+ *   2: the tile-row kernel only (passes of 10 rows at any row count);
  *   1: the CUDA-core GEMV on the raw blocks (an independent second implementation for cross-checks);
  *   3: the per-warp streaming variant of the tile-row kernel where the shape qualifies;
  *   4: calls of 1-5 rows take the bulk-copy ring GEMV (persistent CTAs, shared-memory ring fed by cp.async.bulk,
  *      activation digits built inside the kernel) where the shape fits. */
 int32_t sp_cuda_set_gemv_path(int32_t path);
-/* 1 (default): op-level matmuls with m >= 17 rows and k % 256 == 0 (Q8_0: k % 128 == 0) run the tcgen05 / TMEM dequant GEMM; 0: always the
- * 16-row GEMV passes (for cross-checks and timing comparisons). Process-wide; engines have their own switch. */
+/* 0 (default): op-level matmuls multiply exact integer products at every row count (passes of up to 32 rows);
+ * 1: calls with m >= 17 rows and k % 256 == 0 (Q8_0: k % 128 == 0) run the tcgen05 / TMEM dequant GEMM, whose operands
+ * are rounded to fp16 (~3e-4 per product). Process-wide; engines have their own switch with the same default. */
 int32_t sp_cuda_set_large_m_gemm(int32_t on);
 /* Device address and byte size of the resident blocks (for benchmarks that rotate buffers). */
 int32_t sp_cuda_weight_info(const SpWeight* w, int32_t* dtype, int64_t* n, int64_t* k, size_t* nbytes);

@@ -15,7 +15,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libsapient_cuda.so")
 SOURCES = ["kernels.cu", "attention.cu", "engine.cu", "engine_forward.cu", "engine_layers.cu", "engine_decode.cu", "gemv_imma.cu", "api.cu", "gguf.cu",
-           "attention_static.cu", "tp.cu", "gemm_tc5.cu", "gemv_ring.cu", "spec.cu", "batcher.cu", "nccl_arm.cu"]
+           "attention_static.cu", "tp.cu", "gemm_tc5.cu", "gemv_ring.cu", "spec.cu", "batcher.cu", "nccl_arm.cu", "gemv_rows.cu"]
 FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "--shared",

@@ -23,6 +23,7 @@ struct SpWeight {
     uint8_t* tiled = nullptr;  // tile-repacked copy for the tensor-core GEMV (quantised types)
     ActWorkspace ws;           // activation digits for up to 16 rows
     RingScratch ring;          // shared-row scratch of the ring GEMV (calls of 1-4 rows)
+    RowsScratch rows;          // K-split partials of the one-pass many-row GEMV
 };
 struct SpEngine {
     Engine* e;
@@ -38,6 +39,7 @@ int spec_greedy(Engine* target, Engine* draft, const uint32_t* prompt, size_t n_
 namespace {
 
 std::atomic<int> g_gemv_path{0};  // 0: tensor-core GEMV on tiled weights; 1: CUDA-core GEMV on raw blocks
+std::atomic<int> g_rows{1};       // calls of 11 rows and more on the one-pass many-row GEMV (path 2 turns it off: passes of 10 rows)
 std::atomic<int> g_ring{0};       // calls of 1-5 rows on the bulk-copy ring GEMV where it fits (path 4)
 
 #define API_BEGIN try {
@@ -210,7 +212,7 @@ int32_t sp_cuda_tp_shard(const char* hf_name, int32_t dtype, const int64_t* dims
     API_END
 }
 
-static std::atomic<int> g_tc5{1};
+static std::atomic<int> g_tc5{0};  // op-level matmuls of 17 rows and more on the tcgen05 GEMM (fp16 operands): opt-in, as for engines
 
 int32_t sp_cuda_set_large_m_gemm(int32_t on) {
     g_tc5.store(on ? 1 : 0);
@@ -226,6 +228,7 @@ int32_t sp_cuda_set_activation_digits(int32_t mode) {
 int32_t sp_cuda_set_gemv_path(int32_t path) {
     if (path < 0 || path > 4) { set_error("gemv path must be 0..4"); return SP_ERR_ARG; }
     g_gemv_path.store(path == 1 ? 1 : 0);
+    g_rows.store(path == 2 ? 0 : 1);
     g_ring.store(path == 4 ? 1 : 0);
     imma_select_kernel(path == 3 ? 3 : 0);
     return SP_OK;
@@ -248,6 +251,7 @@ int32_t sp_cuda_upload_weight(int32_t device, int32_t dtype, int64_t n, int64_t 
         if (ce == cudaSuccess) ce = w->ws.alloc((int)k);
         if (ce == cudaSuccess) ce = ring_device_init();
         if (ce == cudaSuccess) ce = w->ring.alloc((int)((n + 15) / 16));
+        if (ce == cudaSuccess) ce = w->rows.alloc();
     }
     if (ce != cudaSuccess) {
         set_error(std::string("upload_weight: ") + cudaGetErrorString(ce));
@@ -255,6 +259,7 @@ int32_t sp_cuda_upload_weight(int32_t device, int32_t dtype, int64_t n, int64_t 
         if (w->tiled) cudaFree(w->tiled);
         w->ws.release();
         w->ring.release();
+        w->rows.release();
         delete w;
         return ce == cudaErrorMemoryAllocation ? SP_ERR_OOM : SP_ERR_CUDA;
     }
@@ -270,6 +275,7 @@ void sp_cuda_free_weight(SpWeight* w) {
     if (w->tiled) cudaFree(w->tiled);
     w->ws.release();
     w->ring.release();
+    w->rows.release();
     delete w;
 }
 
@@ -316,6 +322,20 @@ int32_t sp_cuda_matmul_nt_dev(const SpWeight* w, const float* x_dev, int64_t m, 
             SP_CUDA_TRY(launch_gemv_ring(ra, (cudaStream_t)stream));
             return SP_OK;
         }
+    }
+    if (w->tiled && g_gemv_path.load() == 0 && g_rows.load() && m > imma_rows_per_pass() && rows_supported(w->dtype, w->k) &&
+        (w->dtype != T_Q8_0 || imma_q8_bpt(w->k) == 8)) {
+        // 11 rows and more: passes of up to 32 rows, each reading the weights once
+        for (int64_t m0 = 0; m0 < m; m0 += IMMA_ROWS_MAX) {
+            ImmaArgs ia{};
+            ia.k = (int)w->k; ia.m = (int)std::min<int64_t>(IMMA_ROWS_MAX, m - m0); ia.nseg = 1;
+            ia.seg[0].wt = w->tiled; ia.seg[0].y = y_dev + m0 * w->n; ia.seg[0].dtype = w->dtype; ia.seg[0].n = (int)w->n;
+            ia.seg[0].ldy = (int)w->n; ia.seg[0].bpt = 8;
+            imma_plan_rows(ia, w->ws);
+            SP_CUDA_TRY(launch_act_quant(x_dev + m0 * w->k, (int)w->k, ia, (cudaStream_t)stream));
+            SP_CUDA_TRY(launch_gemv_rows(ia, w->rows, (cudaStream_t)stream));
+        }
+        return SP_OK;
     }
     if (w->tiled && g_gemv_path.load() == 0) {
         const int pass = imma_rows_per_pass();

@@ -64,6 +64,7 @@ Engine::~Engine() {
     if (att_scratch_) cudaFree(att_scratch_);
     if (argmax_scratch_) cudaFree(argmax_scratch_);
     ring_.release();
+    rows_.release();
     for (void* p : owned_) cudaFree(p);
     void* bufs[] = {kv_.pool, d_page_table_, x_, h_, qkv_, attn_, gu_, mid_, sel_, logits_, trace_, d_ids_, d_argmax_,
                     d_tok_slot_, d_tok_pos_, cos_sin_};
@@ -276,6 +277,7 @@ int Engine::repack_weights() {
         SP_CUDA_TRY(ring_device_init());
         SP_CUDA_TRY(ring_.alloc((int)(widest / 16 + 8)));
     }
+    if (d.max_tokens > imma_rows_per_pass()) SP_CUDA_TRY(rows_.alloc());
     return SP_OK;
 }
 

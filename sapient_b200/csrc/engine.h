@@ -151,6 +151,8 @@ class Engine {
                  const float* b0, float* y0, int ldy, const DevTensor* w1 = nullptr, const float* b1 = nullptr, float* y1 = nullptr,
                  const DevTensor* w2 = nullptr, const float* b2 = nullptr, float* y2 = nullptr, const float* res = nullptr);
     RingScratch ring_;
+    RowsScratch rows_;         // K-split partials of the one-pass many-row GEMV
+    bool use_rows = true;      // steps of 11..32 rows per pass on the one-pass kernel (gemv_rows.cu) instead of passes of 10
     bool big_m(int m, int k, const DevTensor* w0, const DevTensor* w1 = nullptr, const DevTensor* w2 = nullptr) const;
     int gemm_xh(int m, int k, const DevTensor* w0, const float* b0, float* y0, int ldy0, const DevTensor* w1 = nullptr,
                 const float* b1 = nullptr, float* y1 = nullptr, const DevTensor* w2 = nullptr, const float* b2 = nullptr,

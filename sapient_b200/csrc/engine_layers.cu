@@ -72,6 +72,28 @@ int Engine::gemv(const float* x, int ldx, int m, int k, const DevTensor* w0, con
             return SP_OK;
         }
     }
+    // 11 rows and more on one GPU: passes of up to 32 rows, each reading the weights once (gemv_rows.cu)
+    if (tiled && !tp_sum && !pre && use_rows && m > imma_rows_per_pass() && k % 256 == 0 && k <= ws_.k_max) {
+        bool ok = true;
+        for (int i = 0; i < 3 && ws[i]; ++i) ok = ok && rows_supported(ws[i]->dtype, k);
+        if (ok) {
+            for (int m0 = 0; m0 < m; m0 += IMMA_ROWS_MAX) {
+                ImmaArgs ia{};
+                ia.k = k; ia.m = std::min(IMMA_ROWS_MAX, m - m0);
+                ia.res = res ? res + (size_t)m0 * ldy0 : nullptr;
+                ia.ldres = ldy0;
+                for (int i = 0; i < 3 && ws[i]; ++i) {
+                    ImmaSeg& sgm = ia.seg[ia.nseg++];
+                    sgm.wt = ws[i]->tiled; sgm.bias = bs[i]; sgm.y = ys[i] + (size_t)m0 * ldy0; sgm.dtype = ws[i]->dtype;
+                    sgm.n = (int)ws[i]->dims[0]; sgm.ldy = ldy0; sgm.bpt = imma_q8_bpt(k);
+                }
+                imma_plan_rows(ia, ws_);
+                SP_LAUNCH(F_ELEM, launch_act_quant(x + (size_t)m0 * ldx, ldx, ia, stream));
+                SP_LAUNCH(F_GEMV, launch_gemv_rows(ia, rows_, stream));
+            }
+            return SP_OK;
+        }
+    }
     // comparison arm: the partial product to scratch, a library all-reduce, one add into the residual stream
     const bool via_nccl = tp_sum && tp_use_nccl_ && tiled;
     if (via_nccl && (y0 != x_ || res != x_ || ldy0 != d.hidden || w1)) { set_error("internal: tensor-parallel sum outside the residual stream"); return SP_ERR_STATE; }

@@ -439,6 +439,14 @@ void imma_plan(ImmaArgs& a, const ActWorkspace& ws) {
     a.xq = ws.xq; a.colscale = ws.colscale; a.xs32d = ws.xs32d; a.xs16d = ws.xs16d;
 }
 
+void imma_plan_rows(ImmaArgs& a, const ActWorkspace& ws) {
+    a.digits = 3;
+    a.ncp = (a.m * 3 + 31) / 32 * 32;
+    a.eb = (a.k % 256 == 0) ? 256 : 32;
+    a.kp = (a.k + 255) / 256 * 256;
+    a.xq = ws.xq; a.colscale = ws.colscale; a.xs32d = ws.xs32d; a.xs16d = ws.xs16d;
+}
+
 cudaError_t launch_act_quant(const float* x, int ldx, const ImmaArgs& a, cudaStream_t st) {
     if (a.m <= 0) return cudaSuccess;
     act_quant_kernel<<<dim3(a.kp / 256, a.m), 32, 0, st>>>(x, ldx, quant_out(a));

@@ -153,13 +153,29 @@ struct ActWorkspace {
     size_t xh_elems = 0;
     Tc5Scratch tc5;            // allocated with xh
     cudaError_t ensure_xh(size_t elems);  // grows the buffer (allocates: not during stream capture)
-    static constexpr int NCP_MAX = 32;
+    static constexpr int NCP_MAX = 96;  // digit columns: 32 rows x 3 digits (gemv_rows.cu); the tile-row kernel uses up to 32
     cudaError_t alloc(int k_max_);
     void release();
 };
 // Digits for x[m, k] (m <= 16) followed by the tensor-core GEMV over up to three weight segments sharing x.
 // Fills a.digits/ncp/eb/xq/...; a.seg/nseg/k/m/res must be set by the caller.
 cudaError_t launch_quant_gemv(const float* x, int ldx, ImmaArgs& a, const ActWorkspace& ws, bool requantize, cudaStream_t st);
+
+// One-pass tensor-core GEMV for 11..32 activation rows (gemv_rows.cu): a CTA owns eight tile rows and shares the staged
+// digits of each k-tile among its warps. `a` as for launch_gemv_imma with digits planned for a.m <= IMMA_ROWS_MAX rows
+// (imma_plan_rows) and a.eb == 256; every segment Q4_K / Q6_K / Q8_0 with k % 256 == 0; not for tensor-parallel pushes.
+constexpr int IMMA_ROWS_MAX = 32;
+struct RowsScratch {
+    float* part = nullptr;     // partial outputs of K-split launches
+    unsigned* cnt = nullptr;   // arrival counters per 128-row group
+    static constexpr int CNT_MAX = 2048;
+    static size_t part_floats();
+    cudaError_t alloc();
+    void release();
+};
+bool rows_supported(int dtype, int64_t k);
+void imma_plan_rows(ImmaArgs& a, const ActWorkspace& ws);  // three digits, 32-column groups (a.m <= IMMA_ROWS_MAX)
+cudaError_t launch_gemv_rows(const ImmaArgs& a, const RowsScratch& sc, cudaStream_t st);
 
 // Large-M dequant GEMM on tcgen05 / TMEM (gemm_tc5.cu): y[m, n] = x·Wᵀ (+ bias, + res) from the tiled weights and an
 // fp16 copy of the activations; k % 256 == 0, Q4_K / Q6_K / Q8_0.

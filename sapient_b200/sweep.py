@@ -36,7 +36,9 @@ def measured_hbm_gbs() -> tuple[float, str]:
         return 6650.0, "fallback"
 
 
-def run_case(dtype_name: str, n: int, k: int, m: int, iters: int, warmup: int, rotate: int | None, path: int, seed: int = 0):
+def run_case(dtype_name: str, n: int, k: int, m: int, iters: int, warmup: int, rotate: int | None, path: int, seed: int = 0,
+             large_m: bool = False):
+    """large_m: calls of 17 rows and more on the opt-in tcgen05 GEMM (fp16 operands) instead of the exact integer passes."""
     import torch
 
     dtype = DTYPES[dtype_name]
@@ -57,6 +59,7 @@ def run_case(dtype_name: str, n: int, k: int, m: int, iters: int, warmup: int, r
     x = torch.randn(m, k, generator=g, device="cuda", dtype=torch.float32)
     y = torch.empty(m, n, device="cuda", dtype=torch.float32)
     ops.set_gemv_path(path)
+    ops.set_large_m_gemm(large_m)
     warmup = max(warmup, rotate)  # every rotated buffer has made its one-time allocations before the clock starts
     stream = torch.cuda.Stream()
     with torch.cuda.stream(stream):
@@ -70,6 +73,7 @@ def run_case(dtype_name: str, n: int, k: int, m: int, iters: int, warmup: int, r
         e1.record(stream)
         stream.synchronize()
     ops.set_gemv_path(0)
+    ops.set_large_m_gemm(False)
     us = e0.elapsed_time(e1) * 1000.0 / iters
     alg = wbytes + 4 * m * k + 4 * m * n
     peak, src = measured_hbm_gbs()
@@ -78,7 +82,8 @@ def run_case(dtype_name: str, n: int, k: int, m: int, iters: int, warmup: int, r
         w.free()
     return {"op": "matmul_nt", "dtype": dtype_name, "n": n, "k": k, "m": m, "us": us, "gbs": gbs, "frac_of_8TBs": gbs / 8000.0,
             "frac_of_hbm_peak": gbs / peak, "peak_source": src, "tflops": 2.0 * m * n * k / us / 1e6, "weight_bytes": wbytes,
-            "rotate": rotate, "iters": iters, "kernel": "cuda-core" if path else "tensor-core"}
+            "rotate": rotate, "iters": iters,
+            "kernel": "cuda-core" if path else ("tcgen05 (fp16 operands)" if large_m and m >= 17 else "tensor-core, exact integer products")}
 
 
 def main() -> None:
@@ -92,6 +97,7 @@ def main() -> None:
     ap.add_argument("--rotate", type=int, default=None)
     ap.add_argument("--path", type=int, default=0, help="0 tensor-core GEMV (default), 1 CUDA-core GEMV")
     ap.add_argument("--max-m", type=int, default=512)
+    ap.add_argument("--large-m", action="store_true", help="17 rows and more on the opt-in tcgen05 GEMM (fp16 operands)")
     a = ap.parse_args()
     dts = [a.dtype] if a.dtype else list(DTYPES)
     shapes = [(a.n, a.k)] if a.n and a.k else SHAPES
@@ -99,7 +105,7 @@ def main() -> None:
     for dt in dts:
         for n, k in shapes:
             for m in ms:
-                print(json.dumps(run_case(dt, n, k, m, a.iters, a.warmup, a.rotate, a.path)), flush=True)
+                print(json.dumps(run_case(dt, n, k, m, a.iters, a.warmup, a.rotate, a.path, large_m=a.large_m)), flush=True)
 
 
 if __name__ == "__main__":

@@ -1,5 +1,5 @@
 """Large-M dequant GEMM on tcgen05 / TMEM (gemm_tc5.cu) through sp_cuda_matmul_nt, against the CPU oracle and
-against the 16-row tensor-core GEMV passes it replaces.
+against the exact integer-product passes it can replace (it is opt-in: sp_cuda_set_large_m_gemm).
 
 Bar: 1e-3 relative L2 per op. The kernel rounds the (exactly dequantised) weights and the activations to fp16 and
 accumulates in fp32, so it lands near 2e-4."""
@@ -15,6 +15,14 @@ Q8_0, Q4_K, Q6_K = synth.Q8_0, synth.Q4_K, synth.Q6_K
 
 def _large_m(on: bool) -> None:
     _lib.check(_lib.lib().sp_cuda_set_large_m_gemm(int(on)))
+
+
+@pytest.fixture(autouse=True)
+def _opt_in():
+    """The kernel under test is opt-in: on for this module's tests, off again afterwards."""
+    _large_m(True)
+    yield
+    _large_m(False)
 
 
 # (m, k, n): m not a multiple of 16 / over 256 (two CTA columns), n not a multiple of 128 / 16, several K chunks
@@ -35,7 +43,7 @@ def test_large_m_gemm_matches_oracle_and_gemv(oracle, dtype, m, k, n):
         _large_m(False)
         gemv = ops.matmul_nt(x, raw, dtype, n)
     finally:
-        _large_m(True)
+        _large_m(False)
     assert got.shape == (m, n) and np.all(np.isfinite(got))
     assert rel_l2(gemv, want) < 3e-4
     err = rel_l2(got, want)
