@@ -90,6 +90,7 @@ SIGNATURES = {
     "sp_cuda_engine_synchronize": (_i32, [_vp]),
     "sp_cuda_engine_set_graphs": (_i32, [_vp, _i32]),
     "sp_cuda_engine_set_ring": (_i32, [_vp, _i32]),
+    "sp_cuda_engine_set_many_row_gemv": (_i32, [_vp, _i32]),
     "sp_cuda_engine_set_large_m_gemm": (_i32, [_vp, _i32]),
     "sp_cuda_engine_set_profile": (_i32, [_vp, _i32]),
     "sp_cuda_engine_profile_read": (_i32, [_vp, _vp, _vp, _i32, _i32]),

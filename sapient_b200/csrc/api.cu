@@ -863,6 +863,15 @@ int32_t sp_cuda_engine_set_large_m_gemm(SpEngine* e, int32_t on) {
     API_END
 }
 
+int32_t sp_cuda_engine_set_many_row_gemv(SpEngine* e, int32_t on) {
+    API_BEGIN
+    if (!e) { set_error("null engine"); return SP_ERR_ARG; }
+    if ((on != 0) != e->e->use_rows) e->e->drop_graphs();
+    e->e->use_rows = on != 0;
+    return SP_OK;
+    API_END
+}
+
 int32_t sp_cuda_engine_set_ring(SpEngine* e, int32_t on) {
     API_BEGIN
     if (!e) { set_error("null engine"); return SP_ERR_ARG; }

@@ -110,6 +110,11 @@ class Engine {
     bool finalized = false;
     bool trace_on = false;
     bool use_graphs = true;
+    // Steps of 11 rows and more as passes of up to 32 rows on the one-pass kernel (gemv_rows.cu) instead of passes of 10 on
+    // the tile-row kernel. Off by default: inside a step the two cost the same (32-row step of the 8B shape: 15.97 vs
+    // 15.50 ms) — the one-pass kernel reads the weights once but launches per segment and cannot take digits written by
+    // the fused producers; as a stand-alone matmul it is 1.3x faster (op-level default).
+    bool use_rows = false;
     bool use_ring = false;     // steps of 1-5 rows on the bulk-copy ring GEMV (opt-in: measured slower than the tile-row kernels)
     // Steps of TC5_MIN_M rows and more on the tcgen05 GEMM, whose operands are rounded to fp16 (~3e-4 per product: inside
     // the per-op bar, but on a 32-layer model the final logits then leave the 2e-2 bar). Off by default: such steps run as
@@ -152,7 +157,6 @@ class Engine {
                  const DevTensor* w2 = nullptr, const float* b2 = nullptr, float* y2 = nullptr, const float* res = nullptr);
     RingScratch ring_;
     RowsScratch rows_;         // K-split partials of the one-pass many-row GEMV
-    bool use_rows = true;      // steps of 11..32 rows per pass on the one-pass kernel (gemv_rows.cu) instead of passes of 10
     bool big_m(int m, int k, const DevTensor* w0, const DevTensor* w1 = nullptr, const DevTensor* w2 = nullptr) const;
     int gemm_xh(int m, int k, const DevTensor* w0, const float* b0, float* y0, int ldy0, const DevTensor* w1 = nullptr,
                 const float* b1 = nullptr, float* y1 = nullptr, const DevTensor* w2 = nullptr, const float* b2 = nullptr,

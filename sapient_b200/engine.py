@@ -288,6 +288,11 @@ class ForwardEngine:
         leave the 2e-2 bar) or, the default, as integer-digit GEMV passes."""
         check(lib().sp_cuda_engine_set_large_m_gemm(self._h, int(on)))
 
+    def set_many_row_gemv(self, on: bool) -> None:
+        """Steps of 11 rows and more as passes of up to 32 rows on the one-pass GEMV (exact integer products, weights read
+        once per pass) instead of the default passes of 10 rows."""
+        check(lib().sp_cuda_engine_set_many_row_gemv(self._h, int(on)))
+
     def set_ring(self, on: bool) -> None:
         """Steps of 1-5 rows on the persistent ring GEMV (opt-in: measured slower) or, the default, on the tile-row GEMV with
         separate producers."""

@@ -104,6 +104,24 @@ def test_cached_decode_equals_full_forward_and_chunking_is_invisible(oracle, nam
     big.close(); small.close()
 
 
+@pytest.mark.parametrize("name", ["tiny_llama", "tiny_qwen", "tiny_llama_wide"])
+def test_many_row_gemv_passes_give_the_same_logits(oracle, name):
+    """Prompts of 11 rows and more as passes of up to 32 rows on the one-pass GEMV (opt-in for engines): the same integer
+    products as the default passes of 10 rows, only the order of the f32 additions over k differs."""
+    cfg, W = tiny_model(name)
+    ids = prompt(cfg, 45, seed=8)  # 32 + 13 rows
+    eng = ForwardEngine.from_weights(cfg, W, max_tokens=64)
+    eng.set_kv_rounding(False)
+    base = eng.forward_all_logits(ids)
+    eng.set_many_row_gemv(True)
+    rows = eng.forward_all_logits(ids)
+    eng.set_many_row_gemv(False)
+    assert np.max(np.abs(rows - base)) < INVARIANCE_BAR
+    ref = oracle_engine(oracle, cfg, W, kv_mode=1)
+    assert np.max(np.abs(rows - ref.forward_all_logits_cached(ids))) < 2e-3
+    eng.close()
+
+
 def test_use_cache_false_resets_then_appends(oracle):
     cfg, W = tiny_model("tiny_llama")
     eng = ForwardEngine.from_weights(cfg, W)
