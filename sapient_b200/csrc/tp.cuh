@@ -84,23 +84,37 @@ __device__ __forceinline__ uint32_t tp_consume_row(const TpDev& tp, float* x, in
     bool ok = *reinterpret_cast<volatile int*>(tp.timeout) == 0;
     for (int i = threadIdx.x * 4; i < dim; i += blockDim.x * 4) {
         float4 acc = *reinterpret_cast<const float4*>(x + row_off_x + i);
-        for (int s = 0; s < tp.size; ++s) {
-            const volatile ulonglong2* src = reinterpret_cast<const volatile ulonglong2*>(tp_recv(tp, tp.rank, slot, s) + (int64_t)row * dim + i);
-            unsigned long long w0 = 0, w1 = 0, w2 = 0, w3 = 0;
-            uint64_t t0 = 0;  // read on the first miss only: the common case costs no timer access
-            for (;;) {
-                w0 = src[0].x; w1 = src[0].y; w2 = src[1].x; w3 = src[1].y;
-                if ((uint32_t)(w0 >> 32) == epoch && (uint32_t)(w1 >> 32) == epoch && (uint32_t)(w2 >> 32) == epoch &&
-                    (uint32_t)(w3 >> 32) == epoch)
-                    break;
-                if (!ok) break;
-                const uint64_t now = tp_now_ns();
-                if (t0 == 0) t0 = now;
-                else if (now - t0 > tp.wait_ns) { ok = false; break; }
-                __nanosleep(100);
+        // the words of all sources are requested together (one round trip to memory, not one per source); only sources
+        // whose words are still from an earlier exchange are read again
+        unsigned long long w[TP_MAX_RANKS][4];
+        unsigned pending = (1u << tp.size) - 1u;
+        uint64_t t0 = 0;  // read on the first miss only: the common case costs no timer access
+        for (;;) {
+#pragma unroll
+            for (int s = 0; s < TP_MAX_RANKS; ++s) {
+                if (s < tp.size && (pending >> s & 1u)) {
+                    const volatile ulonglong2* src = reinterpret_cast<const volatile ulonglong2*>(tp_recv(tp, tp.rank, slot, s) + (int64_t)row * dim + i);
+                    w[s][0] = src[0].x; w[s][1] = src[0].y; w[s][2] = src[1].x; w[s][3] = src[1].y;
+                }
             }
-            acc.x += __uint_as_float((uint32_t)w0); acc.y += __uint_as_float((uint32_t)w1);
-            acc.z += __uint_as_float((uint32_t)w2); acc.w += __uint_as_float((uint32_t)w3);
+#pragma unroll
+            for (int s = 0; s < TP_MAX_RANKS; ++s) {
+                if (s < tp.size && (pending >> s & 1u) && (uint32_t)(w[s][0] >> 32) == epoch && (uint32_t)(w[s][1] >> 32) == epoch &&
+                    (uint32_t)(w[s][2] >> 32) == epoch && (uint32_t)(w[s][3] >> 32) == epoch)
+                    pending &= ~(1u << s);
+            }
+            if (pending == 0u || !ok) break;
+            const uint64_t now = tp_now_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > tp.wait_ns) { ok = false; break; }
+            __nanosleep(100);
+        }
+#pragma unroll
+        for (int s = 0; s < TP_MAX_RANKS; ++s) {  // rank order: every rank adds the same values in the same order
+            if (s < tp.size) {
+                acc.x += __uint_as_float((uint32_t)w[s][0]); acc.y += __uint_as_float((uint32_t)w[s][1]);
+                acc.z += __uint_as_float((uint32_t)w[s][2]); acc.w += __uint_as_float((uint32_t)w[s][3]);
+            }
         }
         *reinterpret_cast<float4*>(x + row_off_x + i) = acc;
     }
