@@ -86,6 +86,9 @@ fn tensor_payload(t: &Tensor) -> Result<(i32, &[u8])> {
 fn desc_from_info(info: &ModelInfo, place: CudaPlacement, max_ctx: usize) -> Result<SpModelDesc> {
     let arch = match info.arch {
         ArchType::Llama | ArchType::Qwen => 0,
+        // Phi-3 / 3.5 / 4-mini run PhiForward's sequential RMSNorm + SwiGLU block (forward/phi.rs:391-503), which is the
+        // engine's Llama block; the fused `mlp.gate_up_proj` tensor is cut at upload
+        ArchType::Phi if info.model_type == "phi3" => 0,
         ArchType::Phi => 1,
         other => bail!("CudaForwardEngine supports Llama / Qwen2 / Phi-2 decoders (got {other:?})"),
     };

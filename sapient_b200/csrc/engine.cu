@@ -145,6 +145,25 @@ int Engine::set_tensor(const char* name, int dtype, const int64_t* dims, int ndi
 int Engine::set_tensor_ex(const char* name, int dtype, const int64_t* dims, int ndim, const void* bytes, size_t nbytes, int unpermute_heads) {
     if (!name || !dims || !bytes || ndim < 1 || ndim > 2) { set_error("set_tensor: bad argument"); return SP_ERR_ARG; }
     if (finalized) { set_error("set_tensor after finalize"); return SP_ERR_STATE; }
+    {
+        // Phi-3's fused `mlp.gate_up_proj` (rows 0..ffn gate, ffn..2 ffn up: forward/phi.rs:559-604) is kept as two
+        // matrices: two row ranges of the caller's bytes, nothing is copied on the host
+        const std::string nm(name);
+        const size_t at = nm.find("mlp.gate_up_proj.weight");
+        if (at != std::string::npos && at + 23 == nm.size()) {
+            const int bbq = block_bytes(dtype), beq = block_elems(dtype);
+            if (ndim != 2 || bbq == 0 || dims[0] != 2 * (int64_t)g.ffn || dims[1] % beq != 0 ||
+                (uint64_t)nbytes != (uint64_t)dims[0] * (uint64_t)(dims[1] / beq * bbq)) {
+                set_error("set_tensor: fused gate_up_proj must be [2 * ffn, hidden] with matching bytes");
+                return SP_ERR_SHAPE;
+            }
+            const int64_t half[2] = {dims[0] / 2, dims[1]};
+            const std::string base = nm.substr(0, at);
+            int st = set_tensor_ex((base + "mlp.gate_proj.weight").c_str(), dtype, half, 2, bytes, nbytes / 2, 0);
+            if (st != SP_OK) return st;
+            return set_tensor_ex((base + "mlp.up_proj.weight").c_str(), dtype, half, 2, (const uint8_t*)bytes + nbytes / 2, nbytes / 2, 0);
+        }
+    }
     SP_CUDA_TRY(cudaSetDevice(d.device));
     DevTensor t;
     t.dtype = dtype;

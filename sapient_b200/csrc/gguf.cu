@@ -198,7 +198,10 @@ int sp_engine_from_gguf_impl(const char* path, int device, int max_ctx, int max_
     auto has = [&](const std::string& key) { return meta.count(arch + "." + key) != 0; };
     SpModelDesc d{};
     const bool is_phi = arch == "phi" || arch == "phi2";
-    const bool is_llama_family = arch == "llama" || arch == "mistral" || arch == "qwen2" || arch == "qwen3" || arch == "idefics3";
+    // Phi-3 / 3.5 / 4-mini: PhiForward's sequential block — RMSNorm, fused q|k|v, fused gate|up SwiGLU
+    // (crates/sapient-models/src/forward/phi.rs:391-503,559-604) — which is the Llama block once the fused tensors are cut
+    const bool is_phi3 = arch == "phi3";
+    const bool is_llama_family = is_phi3 || arch == "llama" || arch == "mistral" || arch == "qwen2" || arch == "qwen3" || arch == "idefics3";
     if (!is_phi && !is_llama_family) { set_error("architecture '" + arch + "' is not supported by the CUDA engine"); return SP_ERR_DTYPE; }
     if (num("expert_count", 0) > 0) { set_error("MoE models are not supported by the CUDA engine"); return SP_ERR_DTYPE; }
     d.arch = is_phi ? 1 : 0;
@@ -219,7 +222,7 @@ int sp_engine_from_gguf_impl(const char* path, int device, int max_ctx, int max_
     // partial rotary factor = rope.dimension_count / head_dim; rotary_dim rule of each forward engine
     // (llama.rs:470-472: round(hd*pf) & !1; phi.rs:388-389: round(pf*hd).clamp(2, hd)).
     double pf = has("rope.dimension_count") ? num("rope.dimension_count", 0) / (double)d.head_dim : 1.0;
-    if (is_phi) {
+    if (is_phi || is_phi3) {
         long rd = std::lround(pf * (double)d.head_dim);
         d.rotary_dim = (int32_t)std::min<long>(std::max<long>(rd, 2), d.head_dim);
     } else {
@@ -285,7 +288,7 @@ int sp_engine_from_gguf_impl(const char* path, int device, int max_ctx, int max_
             h.unpermute_heads = nh;
         }
     }
-    if (is_phi) {
+    if (is_phi || is_phi3) {
         const int64_t q_rows = (int64_t)d.n_heads * d.head_dim, kv_rows = (int64_t)d.n_kv_heads * d.head_dim;
         std::vector<std::string> fused;
         for (auto& kv : W) if (kv.first.find("self_attn.qkv_proj.") != std::string::npos) fused.push_back(kv.first);
@@ -311,7 +314,14 @@ int sp_engine_from_gguf_impl(const char* path, int device, int max_ctx, int max_
                 W[base + nm[i] + suffix] = std::move(s);
             }
         }
+        // Phi-3: `ffn_up` holds the fused gate|up rows (gguf_weights.rs:322-325); the engine cuts it at set_tensor
         std::vector<std::pair<std::string, std::string>> ren;
+        if (is_phi3) {
+            for (auto& kv : W) {
+                size_t at;
+                if ((at = kv.first.find("mlp.up_proj.")) != std::string::npos) ren.push_back({kv.first, kv.first.substr(0, at) + "mlp.gate_up_proj." + kv.first.substr(at + 12)});
+            }
+        } else
         for (auto& kv : W) {
             size_t at;
             if ((at = kv.first.find("mlp.up_proj.")) != std::string::npos) ren.push_back({kv.first, kv.first.substr(0, at) + "mlp.fc1." + kv.first.substr(at + 12)});

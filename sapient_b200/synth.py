@@ -175,6 +175,9 @@ CONFIGS = {
     # biases, head_dim 80
     "tiny_phi2_wide": dict(arch="phi2", n_layers=2, hidden=640, n_heads=8, n_kv_heads=8, head_dim=80, ffn=1280,
                            vocab=144, norm_eps=1e-5, rope_theta=1e4, rotary_dim=32, tied=False),
+    # Phi-3 / Phi-4-mini block: RMSNorm + SwiGLU like Llama, q|k|v and gate|up fused in the GGUF file, grouped-query heads
+    "tiny_phi3": dict(arch="phi3", n_layers=2, hidden=256, n_heads=4, n_kv_heads=2, head_dim=64, ffn=512,
+                      vocab=320, norm_eps=1e-5, rope_theta=1e4, tied=False),
     # Llama block whose rows span several 256-column tiles (hidden 768 = 3 tiles, ffn 2048 = 8 tiles)
     "tiny_llama_wide": dict(arch="llama", n_layers=3, hidden=768, n_heads=6, n_kv_heads=2, head_dim=128, ffn=2048,
                             vocab=1000, norm_eps=1e-5, rope_theta=5e5, tied=False),
@@ -189,6 +192,8 @@ def weight_dtype(cfg: dict, role: str, layer: int, k: int) -> int:
         return Q8_0
     if role in ("embed", "output"):
         return Q6_K
+    if cfg["arch"] == "phi3" and role in ("q", "k"):
+        role = "v"  # q | k | v are ONE tensor in a Phi-3 file: one format for the three
     if role in ("v", "down") and layer % 2 == 0:
         return Q6_K
     return Q4_K
@@ -322,7 +327,7 @@ def permute_qk_rows_for_gguf(raw: np.ndarray, n_head: int, head_dim: int, row_by
 
 def write_gguf(path: str, cfg: dict, W: dict) -> None:
     """Write a GGUF v3 file the reference's loader accepts: ggml dim order [K, N],
-    llama-arch q/k rows permuted, Phi-2 q/k/v fused into attn_qkv."""
+    llama-arch q/k rows permuted, Phi-2 / Phi-3 q/k/v fused into attn_qkv, Phi-3 gate|up fused into ffn_up."""
     import gguf
 
     arch = cfg["arch"]
@@ -344,10 +349,16 @@ def write_gguf(path: str, cfg: dict, W: dict) -> None:
     if cfg["head_dim"] * cfg["n_heads"] != cfg["hidden"]:
         wr.add_uint32(f"{arch}.attention.key_length", cfg["head_dim"])
     Wn = {k: (dt, dims, (t.cpu().numpy() if isinstance(t, torch.Tensor) else t)) for k, (dt, dims, t) in W.items()}
-    if arch == "phi2":  # fuse q|k|v rows (split again by split_phi_gguf_fused)
+    if arch == "phi3":  # fused gate|up rows under the name of up_proj (gguf_weights.rs:322-325)
+        for l in range(cfg["n_layers"]):
+            p = f"model.layers.{l}.mlp."
+            gate, up = Wn.pop(p + "gate_proj.weight"), Wn.pop(p + "up_proj.weight")
+            assert gate[0] == up[0]
+            Wn[p + "up_proj.weight"] = (gate[0], [gate[1][0] + up[1][0], gate[1][1]], np.concatenate([gate[2], up[2]]))
+    if arch in ("phi2", "phi3"):  # fuse q|k|v rows (split again by split_phi_gguf_fused)
         for l in range(cfg["n_layers"]):
             p = f"model.layers.{l}.self_attn."
-            for kind in ("weight", "bias"):
+            for kind in (("weight", "bias") if arch == "phi2" else ("weight",)):
                 parts = [Wn.pop(p + f"{x}_proj.{kind}") for x in "qkv"]
                 dt = parts[0][0]
                 dims = [sum(x[1][0] for x in parts)] + parts[0][1][1:]

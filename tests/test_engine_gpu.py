@@ -18,7 +18,7 @@ LOGIT_BAR = 2e-2
 # carry two int8 digits per activation (2^-15 of the block maximum) instead of three (2^-23), which moves logits
 # by ~1e-4. The reference's own chunked-vs-per-token gate is 5e-3 (wgpu_coherence.rs:556-600).
 INVARIANCE_BAR = 1e-3
-MODELS = ["tiny_llama", "tiny_qwen", "tiny_phi2", "tiny_phi2_wide", "tiny_llama_wide"]
+MODELS = ["tiny_llama", "tiny_qwen", "tiny_phi2", "tiny_phi2_wide", "tiny_llama_wide", "tiny_phi3"]
 
 
 def prompt(cfg, n, seed=0):
@@ -222,6 +222,25 @@ def test_gguf_file_loads_to_the_same_engine(oracle, name, tmp_path):
     ids = prompt(cfg, 7, 4)
     assert np.array_equal(a.forward_logits(ids, True), b.forward_logits(ids, True))
     assert a.desc.rotary_dim == cfg["rotary_dim"] and a.desc.head_dim == cfg["head_dim"]
+    a.close(); b.close()
+
+
+def test_phi3_fused_gate_up_is_cut_at_upload(oracle):
+    """PhiForward keeps Phi-3's `mlp.gate_up_proj` fused (forward/phi.rs:559-604: rows 0..ffn gate, the rest up); an engine
+    handed that tensor must equal one handed the two halves."""
+    cfg, W = tiny_model("tiny_phi3")
+    fused = dict(W)
+    for l in range(cfg["n_layers"]):
+        p = f"model.layers.{l}.mlp."
+        (dt, gd, g), (dt2, ud, u) = fused.pop(p + "gate_proj.weight"), fused.pop(p + "up_proj.weight")
+        assert dt == dt2
+        fused[p + "gate_up_proj.weight"] = (dt, [gd[0] + ud[0], gd[1]], np.concatenate([np.asarray(g).reshape(-1), np.asarray(u).reshape(-1)]))
+    a = ForwardEngine.from_weights(cfg, fused)
+    b = ForwardEngine.from_weights(cfg, W)
+    ids = prompt(cfg, 9, 2)
+    assert np.array_equal(a.forward_logits(ids, True), b.forward_logits(ids, True))
+    ref = oracle_engine(oracle, cfg, W, kv_mode=0)
+    assert np.max(np.abs(b.forward_logits(ids, False) - ref.forward_logits(ids, True))) < 2e-2
     a.close(); b.close()
 
 
