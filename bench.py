@@ -169,7 +169,7 @@ def batch32_section(cfg, W, wbytes: int, local: int, rank: int, world: int, stre
         eng.tp_connect()
     eng.set_stream(stream.cuda_stream)
     rng = np.random.default_rng(32)
-    eng.set_large_m_gemm(True)  # untimed prefill through the tcgen05 path
+    eng.set_large_m_gemm(1)  # untimed prefill on the fastest path
     first = np.empty(B32_BATCH, np.uint32)
     for s in range(B32_BATCH):
         lg = eng.forward_slot(s, rng.integers(0, cfg["vocab"], B32_PROMPT).astype(np.uint32))
@@ -184,7 +184,9 @@ def batch32_section(cfg, W, wbytes: int, local: int, rank: int, world: int, stre
     slots = list(range(B32_BATCH))
     out = {"batch": B32_BATCH, "prompt_len": B32_PROMPT, "steps": B32_STEPS, "model": MODEL, "kv": "fp16 paged/16"}
     kv_per_pos = 2 * cfg["n_layers"] * cfg["n_kv_heads"] * cfg["head_dim"] * 2
-    modes = [("exact", False), ("tcgen05", True)]
+    # exact: the default (tcgen05 GEMM, exact-class operands); tcgen05: its fp16-operand mode; integer_passes: the mma.sync
+    # GEMV passes of 10 rows the default replaced
+    modes = [("exact", 2), ("tcgen05", 1), ("integer_passes", 0)]
     for tag, fast in modes:
         for s in slots:
             eng.truncate_cache(B32_PROMPT, s)
@@ -209,18 +211,18 @@ def batch32_section(cfg, W, wbytes: int, local: int, rank: int, world: int, stre
         out[tag] = {"tokens_per_s": B32_BATCH * B32_STEPS / (ms / 1e3), "ms_per_step": ms / B32_STEPS, "context": ctx_mid,
                     "bytes_per_step_per_gpu": int(step_bytes), "achieved_gbs_per_gpu": gbs, "frac_of_measured_peak": gbs / peaks["hbm_gbs"],
                     "frac_of_8TBs": gbs / 8000.0}
-    out["exact"]["path"] = "integer-digit tensor-core GEMV passes of 10 rows (three digits), the default"
-    if "tcgen05" in out:
-        out["tcgen05"]["path"] = "tcgen05 / TMEM dequant GEMM, fp16 operands (opt-in)"
+    out["exact"]["path"] = "tcgen05 / TMEM dequant GEMM, exact-class operands (fp16 leading part + remainder of weights and activations), the default"
+    out["tcgen05"]["path"] = "tcgen05 / TMEM dequant GEMM, operands rounded to fp16 (opt-in)"
+    out["integer_passes"]["path"] = "integer-digit mma.sync GEMV passes of 10 rows (opt-in)"
     eng.close()
     return out
 
 
 def sweep_section() -> list:
     """Operator sweep of the standalone dequant-matmul for the four benchmark shapes and the three block formats (weights
-    rotated through more than twice the L2, CUDA events on the launching stream): achieved GB/s at M = 1 and at M = 32
-    (the default path: exact integer products; M = 32 is one pass of the many-row kernel) and TFLOP/s at M = 512 on the
-    opt-in tcgen05 GEMM (fp16 operands)."""
+    rotated through more than twice the L2, CUDA events on the launching stream): achieved GB/s at M = 1 (tensor-core GEMV)
+    and at M = 32 (the default for 17 rows and more: tcgen05 GEMM with exact-class operands) and TFLOP/s at M = 512 on the
+    tcgen05 GEMM in both modes (useful flops; the exact-class mode issues three products per useful one)."""
     from sapient_b200 import sweep
 
     rows = []
@@ -230,11 +232,14 @@ def sweep_section() -> list:
             r1 = sweep.run_case(dt, n, k, 1, 24 if big else 60, 3, None, 0)
             r32 = sweep.run_case(dt, n, k, 32, 16 if big else 40, 3, None, 0)
             r512 = sweep.run_case(dt, n, k, 512, 8 if big else 20, 2, 2 if big else None, 0, large_m=True)
+            r512x = sweep.run_case(dt, n, k, 512, 8 if big else 20, 2, 2 if big else None, 0)
             rows.append({"dtype": dt, "n": n, "k": k, "m1_us": round(r1["us"], 2), "m1_gbs": round(r1["gbs"], 1),
                          "m1_frac_of_measured_peak": round(r1["frac_of_hbm_peak"], 3), "m32_us": round(r32["us"], 2),
                          "m32_gbs": round(r32["gbs"], 1), "m32_frac_of_measured_peak": round(r32["frac_of_hbm_peak"], 3),
-                         "m512_us": round(r512["us"], 1), "m512_tflops": round(r512["tflops"], 1),
-                         "m512_path": "tcgen05 GEMM, fp16 operands (opt-in)"})
+                         "m512_us": round(r512x["us"], 1), "m512_tflops": round(r512x["tflops"], 1),
+                         "m512_fp16_operands_us": round(r512["us"], 1), "m512_fp16_operands_tflops": round(r512["tflops"], 1),
+                         "paths": "m1: integer-digit GEMV; m32, m512: tcgen05 GEMM, exact-class operands (default); "
+                                  "m512_fp16_operands: the same GEMM with operands rounded to fp16 (opt-in)"})
     return rows
 
 
@@ -321,9 +326,9 @@ def main() -> None:
 
     # ── value: device-resident greedy loop ──
     if args.quick:
-        eng.set_large_m_gemm(True)  # profiler runs: the (untimed) prompt in 7 launches per layer instead of ~140
+        eng.set_large_m_gemm(1)  # profiler runs: the (untimed) prompt on the path with the fewest launches
     logits = eng.forward_logits(prompt, use_cache=False)
-    eng.set_large_m_gemm(False)
+    eng.set_large_m_gemm(2)
     first = np.array([int(np.flatnonzero(logits == logits.max())[-1])], np.uint32)
     toks = eng.decode_greedy(first, [0], Wm)  # warm-up (captures the step graph)
     sampler = ClockSampler(local)

@@ -90,9 +90,13 @@ int32_t sp_cuda_set_activation_digits(int32_t mode);
  *   4: calls of 1-5 rows take the bulk-copy ring GEMV (persistent CTAs, shared-memory ring fed by cp.async.bulk,
  *      activation digits built inside the kernel) where the shape fits. */
 int32_t sp_cuda_set_gemv_path(int32_t path);
-/* 0 (default): op-level matmuls multiply exact integer products at every row count (passes of up to 32 rows);
- * 1: calls with m >= 17 rows and k % 256 == 0 (Q8_0: k % 128 == 0) run the tcgen05 / TMEM dequant GEMM, whose operands
- * are rounded to fp16 (~3e-4 per product). Process-wide; engines have their own switch with the same default. */
+/* Op-level matmuls with m >= 17 rows and k % 256 == 0 (Q8_0: k % 128 == 0):
+ * 2 (default): the tcgen05 / TMEM dequant GEMM with exact-class operands — weights and activations each as an fp16
+ *    leading part plus the fp16 of what that rounding dropped (rows scaled by a power of two first), three tensor-core
+ *    products per chunk of K: ~1e-6 per product, the level of the integer-digit GEMV;
+ * 1: the same GEMM with operands rounded once to fp16 (~3e-4 per product, 2x faster);
+ * 0: exact integer products on the mma.sync kernels at every row count (passes of up to 32 rows).
+ * Process-wide; engines have their own switch with the same values and default. */
 int32_t sp_cuda_set_large_m_gemm(int32_t on);
 /* Device address and byte size of the resident blocks (for benchmarks that rotate buffers). */
 int32_t sp_cuda_weight_info(const SpWeight* w, int32_t* dtype, int64_t* n, int64_t* k, size_t* nbytes);
@@ -293,12 +297,16 @@ int32_t sp_cuda_batcher_forget(SpBatcher* b, uint64_t id);
 int32_t sp_cuda_batcher_stats(const SpBatcher* b, uint64_t* out, int32_t cap);
 /* Replay decode steps as CUDA graphs (default on). */
 int32_t sp_cuda_engine_set_graphs(SpEngine* e, int32_t on);
-/* Steps of 17 rows and more (prefill chunks, batched decode) on the tcgen05 GEMM: each weight tile is dequantised once
- * and multiplied with all rows on the 5th-generation tensor cores, operands rounded to fp16 (~3e-4 relative per product,
- * inside the 1e-3 per-op bar). Default OFF: on the full-size models those roundings move the final logits by up to 4e-2
- * (8B shape, 128-token prompt), outside the 2e-2 bar, so such steps run as integer-digit GEMV passes unless the caller
- * asks for speed: a 512-token prefill of the 8B shape takes 10 ms with the GEMM on, 7 times that with it off. Drops the
- * captured step graphs. */
+/* Steps of 17 rows and more (prefill chunks, batched decode) run on the tcgen05 GEMM: each weight tile is dequantised
+ * once and multiplied with all rows on the 5th-generation tensor cores.
+ * on = 2 (default): exact-class operands (leading fp16 part + remainder for weights and activations, three products per
+ *    chunk of K, ~1e-6 per product); activations are converted from their f32 rows, attention stays on the f32-class
+ *    kernels. Full-size models keep the 2e-2 final-logit bar (8B shape, 128-token prompt: 6.7e-3).
+ * on = 1: operands rounded once to fp16 (~3e-4 per product, inside the 1e-3 per-op bar, but the 8B shape's final logits
+ *    then move by up to 4e-2), fused fp16 producers and the fp16 prefill attention: a 512-token prefill of the 8B shape
+ *    takes 15 ms instead of 28 ms.
+ * on = 0: integer-digit GEMV passes of 10 rows at any row count (201 ms for that prefill).
+ * Drops the captured step graphs. */
 int32_t sp_cuda_engine_set_large_m_gemm(SpEngine* e, int32_t on);
 /* Steps of 1-5 rows on the bulk-copy ring GEMV with the preceding norm / activation fused into it (default off: it
  * measures slower than the default kernels). Drops the captured step graphs. */

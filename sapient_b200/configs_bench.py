@@ -102,7 +102,7 @@ def decode_case(name: str, prompt_len: int, steps: int, batch: int, label: str, 
     step_bytes = _weight_bytes(cfg, W) + batch * ctx_mid * kv_per_pos
     line = {"case": label, "model": name, "batch": batch, "prompt_len": prompt_len, "steps": steps, "ms_per_step": ms / steps,
             "tokens_per_s": batch * steps / (ms / 1e3), "roofline": _roof(step_bytes, ms / steps), "data": "synthetic",
-            "large_m_path": "tcgen05 GEMM, fp16 operands (opt-in)" if fast else "integer-digit GEMV passes (default)"}
+            "large_m_path": "tcgen05 GEMM, operands rounded to fp16 (opt-in)" if fast else "tcgen05 GEMM, exact-class operands (default)"}
     if prefill_timed:
         line["prefill_tokens_per_s"] = batch * prompt_len / (prefill_ms / 1e3)
         line["prefill_ms"] = prefill_ms
@@ -217,7 +217,7 @@ def main() -> None:
     ap.add_argument("--model", default="llama8b", choices=sorted(synth.CONFIGS))
     ap.add_argument("--prompt", type=int, default=None)
     ap.add_argument("--steps", type=int, default=None)
-    ap.add_argument("--fast", action="store_true", help="steps of 17 rows and more on the tcgen05 GEMM (fp16 operands)")
+    ap.add_argument("--fast", action="store_true", help="steps of 17 rows and more on the tcgen05 GEMM with operands rounded to fp16 (default: exact-class operands)")
     a = ap.parse_args()
     if a.case == "c0":
         line = decode_case("qwen05b", a.prompt or 128, a.steps or 128, 1, "c0", prefill_timed=True, fast=a.fast)

@@ -212,10 +212,11 @@ int32_t sp_cuda_tp_shard(const char* hf_name, int32_t dtype, const int64_t* dims
     API_END
 }
 
-static std::atomic<int> g_tc5{0};  // op-level matmuls of 17 rows and more on the tcgen05 GEMM (fp16 operands): opt-in, as for engines
+static std::atomic<int> g_tc5{2};  // op-level matmuls of 17 rows and more: 2 tcgen05 GEMM with exact-class operands (default), 1 fp16 operands, 0 integer passes
 
 int32_t sp_cuda_set_large_m_gemm(int32_t on) {
-    g_tc5.store(on ? 1 : 0);
+    if (on < 0 || on > 2) { set_error("large-M mode must be 0, 1 or 2"); return SP_ERR_ARG; }
+    g_tc5.store(on);
     return SP_OK;
 }
 
@@ -307,10 +308,13 @@ int32_t sp_cuda_matmul_nt_dev(const SpWeight* w, const float* x_dev, int64_t m, 
     SP_CUDA_TRY(cudaSetDevice(w->device));
     if (w->tiled && g_gemv_path.load() == 0 && g_tc5.load() && m >= TC5_MIN_M && tc5_supported(w->dtype, w->k)) {
         SpWeight* wm = const_cast<SpWeight*>(w);
-        SP_CUDA_TRY(wm->ws.ensure_xh((size_t)m * w->k));
-        SP_CUDA_TRY(launch_x_to_f16(x_dev, (int)w->k, (int)m, (int)w->k, wm->ws.xh, (cudaStream_t)stream));
+        const bool exact = g_tc5.load() == 2;
+        SP_CUDA_TRY(wm->ws.ensure_xh((size_t)m * w->k * (exact ? 2 : 1)));
+        if (exact && m > ActWorkspace::XSCALE_ROWS) { set_error("matmul: more than 4096 rows in the exact tensor-core mode"); return SP_ERR_SHAPE; }
+        if (exact) SP_CUDA_TRY(launch_x_to_f16_hilo(x_dev, (int)w->k, (int)m, (int)w->k, wm->ws.xh, wm->ws.xscale, (cudaStream_t)stream));
+        else SP_CUDA_TRY(launch_x_to_f16(x_dev, (int)w->k, (int)m, (int)w->k, wm->ws.xh, (cudaStream_t)stream));
         SP_CUDA_TRY(launch_gemm_tc5(w->tiled, w->dtype, (int)w->n, (int)w->k, wm->ws.xh, (int)m, y_dev, (int)w->n, nullptr, nullptr, 0,
-                                    (cudaStream_t)stream, &wm->ws.tc5));
+                                    (cudaStream_t)stream, &wm->ws.tc5, exact ? wm->ws.xscale : nullptr));
         return SP_OK;
     }
     if (w->tiled && g_gemv_path.load() == 0 && g_ring.load() && m >= 1 && m <= RING_MAX_M) {
@@ -857,7 +861,9 @@ int32_t sp_cuda_engine_set_large_m_gemm(SpEngine* e, int32_t on) {
     API_BEGIN
     if (!e) { set_error("null engine"); return SP_ERR_ARG; }
     SP_CUDA_TRY(cudaSetDevice(e->e->d.device));
+    if (on < 0 || on > 2) { set_error("large-M mode must be 0, 1 or 2"); return SP_ERR_ARG; }
     e->e->use_tc5 = on != 0;
+    e->e->tc5_exact = on == 2;
     e->e->drop_graphs();
     return SP_OK;
     API_END

@@ -289,7 +289,7 @@ int Engine::repack_weights() {
         }
     }
     SP_CUDA_TRY(ws_.alloc(kmax));
-    if (d.max_tokens >= TC5_MIN_M) SP_CUDA_TRY(ws_.ensure_xh((size_t)d.max_tokens * kmax));
+    if (d.max_tokens >= TC5_MIN_M) SP_CUDA_TRY(ws_.ensure_xh((size_t)2 * d.max_tokens * kmax));  // x 2: leading parts + remainders of the exact mode
     {
         // tile rows of the widest launch: q|k|v, gate|up (two segments), lm_head
         const int64_t widest = std::max<int64_t>({(int64_t)d.vocab, 2 * (int64_t)d.ffn, (int64_t)(d.n_heads + 2 * d.n_kv_heads) * d.head_dim, (int64_t)d.hidden});

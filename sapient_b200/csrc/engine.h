@@ -116,10 +116,15 @@ class Engine {
     // the fused producers; as a stand-alone matmul it is 1.3x faster (op-level default).
     bool use_rows = false;
     bool use_ring = false;     // steps of 1-5 rows on the bulk-copy ring GEMV (opt-in: measured slower than the tile-row kernels)
-    // Steps of TC5_MIN_M rows and more on the tcgen05 GEMM, whose operands are rounded to fp16 (~3e-4 per product: inside
-    // the per-op bar, but on a 32-layer model the final logits then leave the 2e-2 bar). Off by default: such steps run as
-    // integer-digit GEMV passes; sp_cuda_engine_set_large_m_gemm turns the fast path on.
-    bool use_tc5 = false;
+    // Steps of TC5_MIN_M rows and more (prompts, batches) run on the tcgen05 GEMM. tc5_exact (the default): its exact-class
+    // mode — weights and activations each as a leading fp16 part plus remainder, three products per chunk of K, ~1e-6 per
+    // product; activations are converted from their f32 rows, attention stays on the f32-class kernels. Full-size models
+    // keep the 2e-2 final-logit bar in this mode (8B shape, 128-token prompt: 6.7e-3).
+    // tc5_exact == false: operands rounded once to fp16 (~3e-4 per product; 2x faster; the 8B shape's logits then move by up
+    // to 4e-2), with the fused fp16 producers and the fp16 prefill attention. use_tc5 == false: integer-digit GEMV passes of
+    // 10 rows at any row count (7x slower on a 512-token prompt). sp_cuda_engine_set_large_m_gemm chooses.
+    bool use_tc5 = true;
+    bool tc5_exact = true;
     bool graph_step_ = false;  // a step is being captured: its kernels may take positions only from device memory
     // 1 (default): new K / V rows get the reference's Q8_0 cache rounding before they are stored as fp16 (head_dim % 32
     // == 0, where the reference keeps a Q8_0 cache); 0: plain fp16 rounding. Change only while the caches are empty.

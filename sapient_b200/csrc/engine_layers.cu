@@ -59,16 +59,18 @@ int Engine::gemv(const float* x, int ldx, int m, int k, const DevTensor* w0, con
     float* ys[3] = {y0, y1, y2};
     bool tiled = true;
     for (int i = 0; i < 3 && ws[i]; ++i) tiled = tiled && ws[i]->tiled != nullptr;
-    if (tiled && !tp_sum && !pre && m >= TC5_MIN_M && use_tc5 && ws_.xh && (size_t)m * k <= ws_.xh_elems) {
+    if (tiled && !tp_sum && !pre && m >= TC5_MIN_M && use_tc5 && ws_.xh && (size_t)m * k * (tc5_exact ? 2 : 1) <= ws_.xh_elems &&
+        (!tc5_exact || m <= ActWorkspace::XSCALE_ROWS)) {
         bool ok = true;
         for (int i = 0; i < 3 && ws[i]; ++i) ok = ok && tc5_supported(ws[i]->dtype, k);
         if (ok) {
             // many rows: dequantise each weight tile once and multiply on the 5th-generation tensor cores
-            SP_LAUNCH(F_ELEM, launch_x_to_f16(x, ldx, m, k, ws_.xh, stream));
+            if (tc5_exact) SP_LAUNCH(F_ELEM, launch_x_to_f16_hilo(x, ldx, m, k, ws_.xh, ws_.xscale, stream));
+            else SP_LAUNCH(F_ELEM, launch_x_to_f16(x, ldx, m, k, ws_.xh, stream));
             Tc5Seg segs[3];
             int ns = 0;
             for (int i = 0; i < 3 && ws[i]; ++i) segs[ns++] = Tc5Seg{ws[i]->tiled, ys[i], bs[i], ws[i]->dtype, (int)ws[i]->dims[0]};
-            SP_LAUNCH(F_GEMV, launch_gemm_tc5_multi(segs, ns, k, ws_.xh, m, ldy0, res, ldy0, stream, &ws_.tc5));
+            SP_LAUNCH(F_GEMV, launch_gemm_tc5_multi(segs, ns, k, ws_.xh, m, ldy0, res, ldy0, stream, &ws_.tc5, tc5_exact ? ws_.xscale : nullptr));
             return SP_OK;
         }
     }
@@ -177,7 +179,7 @@ int Engine::try_ring(bool* done, int m, int k, int src, const float* x, int ldx,
 }
 
 bool Engine::big_m(int m, int k, const DevTensor* w0, const DevTensor* w1, const DevTensor* w2) const {
-    if (m < TC5_MIN_M || !use_tc5 || !ws_.xh || (size_t)m * k > ws_.xh_elems) return false;
+    if (m < TC5_MIN_M || !use_tc5 || tc5_exact || !ws_.xh || (size_t)m * k > ws_.xh_elems) return false;
     const DevTensor* ws[3] = {w0, w1, w2};
     for (int i = 0; i < 3 && ws[i]; ++i)
         if (!ws[i]->tiled || !tc5_supported(ws[i]->dtype, k)) return false;
@@ -264,7 +266,7 @@ int Engine::attention_and_oproj(const LayerW& w, int l, int T) {
     }
     // a prefill chunk (one sequence, consecutive positions): the tiled tensor-core kernel
     // (takes the sequence and its first position as launch arguments: not inside a captured step, which is replayed)
-    bool one_seq = splits == 1 && !graph_step_ && use_tc5 && attention_prefill_supported(hd);
+    bool one_seq = splits == 1 && !graph_step_ && use_tc5 && !tc5_exact && attention_prefill_supported(hd);
     for (int i = 1; one_seq && i < T; ++i) one_seq = p_slot_[i] == p_slot_[0] && p_pos_[i] == p_pos_[0] + i;
     if (one_seq && big_m(T, H * hd, w.o)) {
         SP_LAUNCH(F_ATTN, launch_attention_prefill(qkv_, qkv_ld, nullptr, H * hd, T, H, p_slot_[0], p_pos_[0], kv_, l, scale, stream, ws_.xh));

@@ -223,13 +223,21 @@ __device__ __forceinline__ void tc5_put(Tc5Out& o, int cg, int hi8, uint32_t c01
     o[cg][2 * hi8] = c01;
     o[cg][2 * hi8 + 1] = c23;
 }
-__device__ __forceinline__ void tc5_put4f(Tc5Out& o, int cg, int hi8, float f0, float f1, float f2, float f3) {
-    tc5_put(o, cg, hi8, bits_h2(__floats2half2_rn(f0, f1)), bits_h2(__floats2half2_rn(f2, f3)));
+// EXACT: ol receives what the rounding to fp16 dropped (f - half(f), itself rounded to fp16): hi + lo holds the f32
+// weight to ~2^-22 of its magnitude (2^-24 absolute once the remainder is subnormal, i.e. for |w| < 0.06: then still
+// ~2^-19 of a 0.02-sized weight).
+template <bool EXACT>
+__device__ __forceinline__ void tc5_put4f(Tc5Out& o, Tc5Out& ol, int cg, int hi8, float f0, float f1, float f2, float f3) {
+    const __half2 h01 = __floats2half2_rn(f0, f1), h23 = __floats2half2_rn(f2, f3);
+    tc5_put(o, cg, hi8, bits_h2(h01), bits_h2(h23));
+    if (EXACT)
+        tc5_put(ol, cg, hi8, bits_h2(__floats2half2_rn(f0 - __low2float(h01), f1 - __high2float(h01))),
+                bits_h2(__floats2half2_rn(f2 - __low2float(h23), f3 - __high2float(h23))));
 }
 
 // Converts the raw words of chunk group cq to the thread's 32 fp16 weights.
-template <int DT>
-__device__ __forceinline__ void tc5_convert(const Tc5Raw& r, int cq, Tc5Out& o) {
+template <int DT, bool EXACT>
+__device__ __forceinline__ void tc5_convert(const Tc5Raw& r, int cq, Tc5Out& o, Tc5Out& ol) {
     if (DT == T_Q4_K) {
 #pragma unroll
         for (int hi8 = 0; hi8 < 2; ++hi8) {
@@ -265,8 +273,8 @@ __device__ __forceinline__ void tc5_convert(const Tc5Raw& r, int cq, Tc5Out& o) 
                 for (int hh = 0; hh < 2; ++hh) {
                     const uint32_t mask = hh ? 0x00F000F0u : 0x000F000Fu;
                     const __half2 p02 = h2_bits((w & mask) | 0x64006400u), p13 = h2_bits((w8 & mask) | 0x64006400u);
-                    tc5_put4f(o, 2 * hh + h16, hi8, fmaf(__low2float(p02), sl[hh], cl[hh]), fmaf(__low2float(p13), sl[hh], cl[hh]),
-                              fmaf(__high2float(p02), sl[hh], cl[hh]), fmaf(__high2float(p13), sl[hh], cl[hh]));
+                    tc5_put4f<EXACT>(o, ol, 2 * hh + h16, hi8, fmaf(__low2float(p02), sl[hh], cl[hh]), fmaf(__low2float(p13), sl[hh], cl[hh]),
+                                     fmaf(__high2float(p02), sl[hh], cl[hh]), fmaf(__high2float(p13), sl[hh], cl[hh]));
                 }
             }
         }
@@ -279,9 +287,15 @@ __device__ __forceinline__ void tc5_convert(const Tc5Raw& r, int cq, Tc5Out& o) 
 #pragma unroll
                 for (int h16 = 0; h16 < 2; ++h16) {
                     const uint32_t v = u4_word(r.q[blk], 2 * hi8 + h16) ^ 0x80808080u;  // int8 -> offset-128 unsigned
-                    const uint32_t e02 = bits_h2(__hmul2(bytes02(v, 0x00FF00FFu, 1152.f), d));       // columns +0, +2
-                    const uint32_t e13 = bits_h2(__hmul2(bytes02(v >> 8, 0x00FF00FFu, 1152.f), d));  // columns +1, +3
-                    tc5_put(o, 2 * blk + h16, hi8, __byte_perm(e02, e13, 0x5410), __byte_perm(e02, e13, 0x7632));
+                    if (EXACT) {  // int8 x f16 scale is exact in f32 (8 + 11 bits): leading part and remainder
+                        const float2 q02 = __half22float2(bytes02(v, 0x00FF00FFu, 1152.f)), q13 = __half22float2(bytes02(v >> 8, 0x00FF00FFu, 1152.f));
+                        const float df = __low2float(d);
+                        tc5_put4f<true>(o, ol, 2 * blk + h16, hi8, q02.x * df, q13.x * df, q02.y * df, q13.y * df);
+                    } else {
+                        const uint32_t e02 = bits_h2(__hmul2(bytes02(v, 0x00FF00FFu, 1152.f), d));       // columns +0, +2
+                        const uint32_t e13 = bits_h2(__hmul2(bytes02(v >> 8, 0x00FF00FFu, 1152.f), d));  // columns +1, +3
+                        tc5_put(o, 2 * blk + h16, hi8, __byte_perm(e02, e13, 0x5410), __byte_perm(e02, e13, 0x7632));
+                    }
                 }
             }
         }
@@ -305,8 +319,8 @@ __device__ __forceinline__ void tc5_convert(const Tc5Raw& r, int cq, Tc5Out& o) 
                     // dsc * (q - 32) = 256 dsc * (0.5 + q / 256) - 160 dsc: both constants exact, one rounding in the fma
                     const float s256 = 256.0f * dsc, c = -160.0f * dsc;
                     const uint32_t q = ((odd ? (ql >> 4) : ql) & 0x0F0F0F0Fu) | (((qh >> (2 * quarter)) & 0x03030303u) << 4);
-                    tc5_put4f(o, 2 * ab + p, hi8, fmaf(half_plus(q, 0), s256, c), fmaf(half_plus(q, 1), s256, c),
-                              fmaf(half_plus(q, 2), s256, c), fmaf(half_plus(q, 3), s256, c));
+                    tc5_put4f<EXACT>(o, ol, 2 * ab + p, hi8, fmaf(half_plus(q, 0), s256, c), fmaf(half_plus(q, 1), s256, c),
+                                     fmaf(half_plus(q, 2), s256, c), fmaf(half_plus(q, 3), s256, c));
                 }
             }
         }
@@ -316,7 +330,7 @@ __device__ __forceinline__ void tc5_convert(const Tc5Raw& r, int cq, Tc5Out& o) 
 // One producer warp's pass over the CTA's chunks, for one weight format and one of the two 64-column groups of a
 // chunk. c_begin and n_chunks are even, so the warp alternates between groups SUB and SUB + 2 of a superblock tile and
 // moves to the next tile every second chunk: all offsets inside a tile are compile-time constants.
-template <int DT, int SUB>
+template <int DT, int SUB, bool EXACT>
 __device__ __forceinline__ bool tc5_produce(const uint8_t* tile_row, bool row_live, int c_begin, int n_chunks, int lane, uint32_t a_base,
                                             uint64_t* full_a, uint64_t* empty_a) {
     constexpr bool HALF = DT == T_Q8_0_HALF;  // one tile per chunk: group SUB of every tile, any c_begin and n_chunks
@@ -324,23 +338,28 @@ __device__ __forceinline__ bool tc5_produce(const uint8_t* tile_row, bool row_li
     bool ok = true;
     const uint8_t* tile = tile_row + (int64_t)(HALF ? c_begin : c_begin >> 1) * TILE_BYTES;
     int s = -1, u = 0;  // stage of the current chunk and the number of times the ring has wrapped
+    // EXACT: a chunk is handed over three times — leading parts (for x's leading parts), remainders (for x's leading parts),
+    // leading parts again (for x's remainders) — into three consecutive stages; the weights are rebuilt once.
     auto build = [&](const Tc5Raw& raw, int cq) {  // next chunk: rebuild the weights in registers, wait for its stage, store
-        if (++s == TC5_A_STAGES) { s = 0; ++u; }
-        Tc5Out o;
+        Tc5Out o, ol;
         if (row_live) {
-            tc5_convert<DT>(raw, cq, o);
+            tc5_convert<DT, EXACT>(raw, cq, o, ol);
         } else {
 #pragma unroll
-            for (int i = 0; i < 16; ++i) o[i >> 2][i & 3] = 0u;  // rows past the matrix
+            for (int i = 0; i < 16; ++i) { o[i >> 2][i & 3] = 0u; ol[i >> 2][i & 3] = 0u; }  // rows past the matrix
         }
-        if (u > 0) ok = ok && tc5_wait(&empty_a[s], (uint32_t)((u - 1) & 1));  // the MMAs of the chunk 4 back have read this stage
-        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
 #pragma unroll
-        for (int cg = 0; cg < 4; ++cg) tc5_tmem_st(a_base + (uint32_t)(64 * s + 8 * cg), o[cg]);
-        asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
-        asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-        __syncwarp();
-        if (lane == 0) tc5_arrive(&full_a[s]);
+        for (int j = 0; j < (EXACT ? 3 : 1); ++j) {
+            if (++s == TC5_A_STAGES) { s = 0; ++u; }
+            if (u > 0) ok = ok && tc5_wait(&empty_a[s], (uint32_t)((u - 1) & 1));  // the MMAs that last read this stage are done
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+#pragma unroll
+            for (int cg = 0; cg < 4; ++cg) tc5_tmem_st(a_base + (uint32_t)(64 * s + 8 * cg), (EXACT && j == 1) ? ol[cg] : o[cg]);
+            asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+            __syncwarp();
+            if (lane == 0) tc5_arrive(&full_a[s]);
+        }
     };
     // two register sets: the loads of the next chunk are in flight while a chunk is rebuilt
     Tc5Raw raw_a, raw_b;
@@ -383,6 +402,11 @@ struct Tc5Args {
     unsigned* split_cnt;
     int stage_bytes;    // 256 * (widest activation tile of the launch, rounded to 16): two boxes of 64 columns
     int stages;         // depth of the activation ring that fits shared memory (3..8)
+    // 1: exact-class operands. xh holds [2 m][k]: rows 0..m-1 the fp16 leading parts of the activations, rows m..2m-1
+    // their remainders; the weights are split the same way by the producers. Every chunk of K is multiplied three times
+    // into the same accumulators — W_hi X_hi, W_lo X_hi, W_hi X_lo (the remainder x remainder term is below f32 rounding).
+    int exact;
+    const float* xscale;  // exact: [m] power-of-two factors the rows of xh were divided by
 };
 
 __global__ void __launch_bounds__(TC5_THREADS, 1) gemm_tc5_kernel(const Tc5Args a, const __grid_constant__ CUtensorMap tmap_x) {
@@ -416,6 +440,7 @@ __global__ void __launch_bounds__(TC5_THREADS, 1) gemm_tc5_kernel(const Tc5Args 
     const int even = (a.k & 255) ? ~0 : ~1;  // (widths that are odd multiples of 128 exist only with one tile per chunk)
     const int c_begin = (int)((int64_t)part * all_chunks / parts) & even, c_end = (int)((int64_t)(part + 1) * all_chunks / parts) & even;
     const int n_chunks = c_end - c_begin;
+    const int reps = a.exact ? 3 : 1, n_handed = n_chunks * reps;  // stage hand-overs: three per chunk with exact operands
 
     if (warp == TC5_MMA_WARP) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tc5_smem_u32(&tmem_slot)), "r"(TC5_TMEM_COLS)
@@ -452,9 +477,11 @@ __global__ void __launch_bounds__(TC5_THREADS, 1) gemm_tc5_kernel(const Tc5Args 
         const uint8_t* tile_row = sg.wt + (int64_t)rt * row_tile_bytes;
         // lanes 16 tile_w .. + 15, columns of stage 0 of the weight ring
         const uint32_t a_base = tmem + ((uint32_t)(16 * tile_w) << 16) + (uint32_t)(TC5_NB_MAX + 32 * sub);
-#define SP_PRODUCE(T)                                                                                            \
-    ok = sub ? tc5_produce<T, 1>(tile_row, row_live, c_begin, n_chunks, lane, a_base, full_a, empty_a)          \
-             : tc5_produce<T, 0>(tile_row, row_live, c_begin, n_chunks, lane, a_base, full_a, empty_a)
+#define SP_PRODUCE(T)                                                                                                      \
+    ok = a.exact ? (sub ? tc5_produce<T, 1, true>(tile_row, row_live, c_begin, n_chunks, lane, a_base, full_a, empty_a)    \
+                        : tc5_produce<T, 0, true>(tile_row, row_live, c_begin, n_chunks, lane, a_base, full_a, empty_a))   \
+                 : (sub ? tc5_produce<T, 1, false>(tile_row, row_live, c_begin, n_chunks, lane, a_base, full_a, empty_a)   \
+                        : tc5_produce<T, 0, false>(tile_row, row_live, c_begin, n_chunks, lane, a_base, full_a, empty_a))
         if (DT == T_Q4_K) SP_PRODUCE(T_Q4_K);
         else if (DT == T_Q6_K) SP_PRODUCE(T_Q6_K);
         else if (DT == T_Q8_0) SP_PRODUCE(T_Q8_0);
@@ -470,7 +497,7 @@ __global__ void __launch_bounds__(TC5_THREADS, 1) gemm_tc5_kernel(const Tc5Args 
             const uint32_t bd_hi = (uint32_t)(bd0 >> 32), bd_lo0 = (uint32_t)bd0;
             const uint32_t stage16 = (uint32_t)a.stage_bytes >> 4, half16 = stage16 >> 1;
             uint32_t accumulate = 0u;
-            for (int c = 0, sa = 0, ua = 0, sb = 0, ub = 0; c < n_chunks; ++c, ++sa, ++sb) {
+            for (int c = 0, sa = 0, ua = 0, sb = 0, ub = 0; c < n_handed; ++c, ++sa, ++sb) {
                 if (sa == TC5_A_STAGES) { sa = 0; ++ua; }
                 if (sb == a.stages) { sb = 0; ++ub; }
                 ok = ok && tc5_wait(&full_b[sb], (uint32_t)(ub & 1));  // after one expired wait nothing else is waited for
@@ -494,18 +521,20 @@ __global__ void __launch_bounds__(TC5_THREADS, 1) gemm_tc5_kernel(const Tc5Args 
         }
     } else if (lane == 0) {
         // ── TMA: per chunk the activation tile as two boxes of (64 columns x nb_max rows), counted in bytes on `full_b` ──
-        for (int c = 0, sb = 0, ub = 0; c < n_chunks; ++c, ++sb) {
+        for (int h = 0, sb = 0, ub = 0; h < n_handed; ++h, ++sb) {
+            const int c = h / reps, j = h - c * reps;
+            const int row = m0 + (j == 2 ? a.m : 0);  // the third hand-over of a chunk multiplies the activations' remainders
             if (sb == a.stages) { sb = 0; ++ub; }
             if (ub > 0) ok = ok && tc5_wait(&empty_b[sb], (uint32_t)((ub - 1) & 1));
             const uint32_t bar = tc5_smem_u32(&full_b[sb]);
             const uint32_t dst = tc5_smem_u32(smem + (size_t)sb * a.stage_bytes);
             asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(a.stage_bytes) : "memory");
 #pragma unroll
-            for (int h = 0; h < 2; ++h)
+            for (int hh = 0; hh < 2; ++hh)
                 asm volatile(
                     "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::"r"(
-                        dst + h * (a.stage_bytes / 2)),
-                    "l"(&tmap_x), "r"((c_begin + c) * TC5_BK + 64 * h), "r"(m0), "r"(bar)
+                        dst + hh * (a.stage_bytes / 2)),
+                    "l"(&tmap_x), "r"((c_begin + c) * TC5_BK + 64 * hh), "r"(row), "r"(bar)
                     : "memory");
         }
     }
@@ -535,13 +564,17 @@ __global__ void __launch_bounds__(TC5_THREADS, 1) gemm_tc5_kernel(const Tc5Args 
                 asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
                 if (parts > 1) {
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) pbuf[(gi * 16 + j) * TC5_BM + 32 * q4 + lane] = __uint_as_float(r[j]) + bias;
+                    for (int j = 0; j < 16; ++j) {
+                        const int m = m0 + gi * 16 + j;
+                        const float sc = (a.xscale && m < a.m) ? a.xscale[m] : 1.f;
+                        pbuf[(gi * 16 + j) * TC5_BM + 32 * q4 + lane] = fmaf(__uint_as_float(r[j]), sc, bias);
+                    }
                 } else if (n < sg.n) {
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
                         const int m = m0 + gi * 16 + j;
                         if (m < a.m) {
-                            float v = __uint_as_float(r[j]) + bias;
+                            float v = a.xscale ? fmaf(__uint_as_float(r[j]), a.xscale[m], bias) : __uint_as_float(r[j]) + bias;
                             if (add_res) v += a.res[(int64_t)m * a.ldres + n];
                             yb[(int64_t)m * a.ldy + n] = v;
                         }
@@ -593,6 +626,50 @@ __global__ void x_to_f16_kernel(const float* __restrict__ x, int ldx, int k, __h
         make_uint4(pack_h2(p0.x, p0.y), pack_h2(p0.z, p0.w), pack_h2(p1.x, p1.y), pack_h2(p1.z, p1.w));
 }
 
+// Row m of x[m, k] (f32), scaled by the power of two that brings it into (-1, 1): out[m] = fp16 leading parts,
+// out[m_rows + m] = fp16 of what the first rounding dropped, rowscale[m] = the inverse of the scale. One block per row.
+__global__ void __launch_bounds__(256) x_to_f16_hilo_kernel(const float* __restrict__ x, int ldx, int k, int m_rows, __half* __restrict__ out,
+                                                            float* __restrict__ rowscale) {
+    __shared__ float sh[8];
+    pdl_wait();
+    pdl_trigger();
+    const int m = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const float* row = x + (int64_t)m * ldx;
+    float amax = 0.f;
+    for (int c = threadIdx.x * 8; c < k; c += 256 * 8) {
+        const float4 p0 = *reinterpret_cast<const float4*>(row + c), p1 = *reinterpret_cast<const float4*>(row + c + 4);
+        amax = fmaxf(amax, fmaxf(fmaxf(fmaxf(fabsf(p0.x), fabsf(p0.y)), fmaxf(fabsf(p0.z), fabsf(p0.w))),
+                                 fmaxf(fmaxf(fabsf(p1.x), fabsf(p1.y)), fmaxf(fabsf(p1.z), fabsf(p1.w)))));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+    if (lane == 0) sh[warp] = amax;
+    __syncthreads();
+    amax = sh[0];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) amax = fmaxf(amax, sh[w]);
+    float up = 1.f, down = 1.f;
+    if (amax > 0.f && amax < INFINITY) {
+        const int e = max(-100, min(100, ilogbf(amax) + 1));  // amax < 2^e
+        up = scalbnf(1.0f, -e);
+        down = scalbnf(1.0f, e);
+    }
+    if (threadIdx.x == 0) rowscale[m] = down;
+    for (int c = threadIdx.x * 8; c < k; c += 256 * 8) {
+        const float4 p0 = *reinterpret_cast<const float4*>(row + c), p1 = *reinterpret_cast<const float4*>(row + c + 4);
+        const float v[8] = {p0.x * up, p0.y * up, p0.z * up, p0.w * up, p1.x * up, p1.y * up, p1.z * up, p1.w * up};
+        uint32_t hi[4], lo[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const __half2 h = __floats2half2_rn(v[2 * j], v[2 * j + 1]);
+            hi[j] = bits_h2(h);
+            lo[j] = bits_h2(__floats2half2_rn(v[2 * j] - __low2float(h), v[2 * j + 1] - __high2float(h)));
+        }
+        *reinterpret_cast<uint4*>(out + (int64_t)m * k + c) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+        *reinterpret_cast<uint4*>(out + ((int64_t)m + m_rows) * k + c) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+    }
+}
+
 // Reads and clears the flag a bounded mbarrier wait of gemm_tc5_kernel raises when it runs out (the kernel then skips
 // its epilogue, so y is stale). Synchronous copy from the device the calling thread has current: call it only where
 // the stream has been synchronised already. 1 = a wait expired since the last call, 0 = none, -1 = CUDA error.
@@ -617,6 +694,14 @@ cudaError_t launch_x_to_f16(const float* x, int ldx, int m, int k, __half* out, 
     if (m <= 0) return cudaSuccess;
     const int64_t total8 = (int64_t)m * k / 8;
     cudaError_t le = launch_pdl(x_to_f16_kernel, dim3((unsigned)((total8 + 255) / 256)), dim3(256), 0, st, x, ldx, k, out, total8);
+    if (le != cudaSuccess) return le;
+    return count_launch_and_check();
+}
+
+cudaError_t launch_x_to_f16_hilo(const float* x, int ldx, int m, int k, __half* out, float* rowscale, cudaStream_t st) {
+    if (m <= 0) return cudaSuccess;
+    if (k % 8 != 0 || !rowscale) return cudaErrorInvalidValue;
+    cudaError_t le = launch_pdl(x_to_f16_hilo_kernel, dim3((unsigned)m), dim3(256), 0, st, x, ldx, k, m, out, rowscale);
     if (le != cudaSuccess) return le;
     return count_launch_and_check();
 }
@@ -646,8 +731,9 @@ void Tc5Scratch::release() {
 }
 
 cudaError_t launch_gemm_tc5_multi(const Tc5Seg* segs, int nseg, int k, const __half* xh, int m, int ldy, const float* res, int ldres,
-                                  cudaStream_t st, const Tc5Scratch* scratch) {
+                                  cudaStream_t st, const Tc5Scratch* scratch, const float* xscale) {
     if (m <= 0 || nseg <= 0) return cudaSuccess;
+    const bool exact = xscale != nullptr;
     if (nseg > 3 || k % 128 != 0) return cudaErrorInvalidValue;
     Tc5Args a{};
     int tiles = 0;
@@ -671,7 +757,7 @@ cudaError_t launch_gemm_tc5_multi(const Tc5Seg* segs, int nseg, int k, const __h
         if (tail > 0) {
             int first = (items - tail) / m_tiles * m_tiles;  // whole weight tiles only
             tail = items - first;
-            const int ts = std::min({8, sm_count / tail, chunks / 4});
+            const int ts = std::min({8, sm_count / tail, chunks / 4});  // (chunks of K: a split part keeps at least four)
             if (ts >= 2 && tail <= TC5_SPLIT_MAX_ITEMS && (size_t)tail * ts <= scratch->parts_cap) { full_items = first; tail_split = ts; }
         }
     }
@@ -685,7 +771,7 @@ cudaError_t launch_gemm_tc5_multi(const Tc5Seg* segs, int nseg, int k, const __h
     if (!encode) return cudaErrorNotSupported;
     CUtensorMap tmap;
     {
-        const cuuint64_t gdim[2] = {(cuuint64_t)k, (cuuint64_t)m};
+        const cuuint64_t gdim[2] = {(cuuint64_t)k, (cuuint64_t)(exact ? 2 * m : m)};
         const cuuint64_t gstride[1] = {(cuuint64_t)k * sizeof(__half)};
         const cuuint32_t box[2] = {64u, (cuuint32_t)nb_max};
         const cuuint32_t estr[2] = {1u, 1u};
@@ -696,6 +782,8 @@ cudaError_t launch_gemm_tc5_multi(const Tc5Seg* segs, int nseg, int k, const __h
     a.nseg = nseg; a.k = k; a.xh = xh; a.m = m; a.ldy = ldy; a.res = res; a.ldres = ldres;
     a.m_tiles = m_tiles; a.full_items = full_items; a.tail_split = tail_split;
     a.stage_bytes = stage_bytes; a.stages = stages;
+    a.exact = exact ? 1 : 0;
+    a.xscale = xscale;
     constexpr int SMEM_CAP = TC5_SMEM_LIMIT + 1024;
     cudaError_t le;
     le = attr_once.run([] { return cudaFuncSetAttribute(gemm_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_CAP); });
@@ -709,9 +797,9 @@ cudaError_t launch_gemm_tc5_multi(const Tc5Seg* segs, int nseg, int k, const __h
 }
 
 cudaError_t launch_gemm_tc5(const uint8_t* wt, int dtype, int n, int k, const __half* xh, int m, float* y, int ldy, const float* bias,
-                            const float* res, int ldres, cudaStream_t st, const Tc5Scratch* scratch) {
+                            const float* res, int ldres, cudaStream_t st, const Tc5Scratch* scratch, const float* xscale) {
     Tc5Seg sg{wt, y, bias, dtype, n};
-    return launch_gemm_tc5_multi(&sg, 1, k, xh, m, ldy, res, ldres, st, scratch);
+    return launch_gemm_tc5_multi(&sg, 1, k, xh, m, ldy, res, ldres, st, scratch, xscale);
 }
 
 }  // namespace sp

@@ -504,16 +504,18 @@ cudaError_t ActWorkspace::ensure_xh(size_t elems) {
     if (elems <= xh_elems) return cudaSuccess;
     if (xh) cudaFree(xh);
     xh = nullptr;
+    xscale = nullptr;
     xh_elems = 0;
-    cudaError_t e = cudaMalloc((void**)&xh, elems * sizeof(__half));
-    if (e == cudaSuccess) xh_elems = elems;
+    const size_t bytes = (elems * sizeof(__half) + 255) / 256 * 256;
+    cudaError_t e = cudaMalloc((void**)&xh, bytes + XSCALE_ROWS * sizeof(float));
+    if (e == cudaSuccess) { xh_elems = elems; xscale = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(xh) + bytes); }
     if (e == cudaSuccess && !tc5.buf) e = tc5.alloc();
     return e;
 }
 
 void ActWorkspace::release() {
     if (xh) cudaFree(xh);
-    xh = nullptr; xh_elems = 0;
+    xh = nullptr; xh_elems = 0; xscale = nullptr;
     tc5.release();
     if (xq) cudaFree(xq);
     if (colscale) cudaFree(colscale);

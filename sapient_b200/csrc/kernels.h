@@ -151,6 +151,8 @@ struct ActWorkspace {
     int k_max = 0;
     __half* xh = nullptr;      // fp16 copy of the activations for the large-M tensor-core GEMM (gemm_tc5.cu)
     size_t xh_elems = 0;
+    float* xscale = nullptr;   // per-row power-of-two scales of the exact mode's activations (same allocation as xh)
+    static constexpr int XSCALE_ROWS = 4096;
     Tc5Scratch tc5;            // allocated with xh
     cudaError_t ensure_xh(size_t elems);  // grows the buffer (allocates: not during stream capture)
     static constexpr int NCP_MAX = 96;  // digit columns: 32 rows x 3 digits (gemv_rows.cu); the tile-row kernel uses up to 32
@@ -182,8 +184,12 @@ cudaError_t launch_gemv_rows(const ImmaArgs& a, const RowsScratch& sc, cudaStrea
 constexpr int TC5_MIN_M = 17;  // up to 16 rows one GEMV pass is faster; from 17 rows on (two passes) the tcgen05 GEMM wins (measured at 32 rows: 5.6 vs 7.1 ms per decode step of the 8B shape)
 bool tc5_supported(int dtype, int64_t k);
 cudaError_t launch_x_to_f16(const float* x, int ldx, int m, int k, __half* out, cudaStream_t st);
+// For the GEMM's exact mode: every row is scaled by a power of two to (-1, 1) first (rowscale[m] receives the inverse), so
+// that the remainders stay inside the fp16 range whatever the row's magnitude; out[2 m][k]: rows 0..m-1 the fp16 leading
+// parts, rows m..2m-1 the fp16 of what that rounding dropped.
+cudaError_t launch_x_to_f16_hilo(const float* x, int ldx, int m, int k, __half* out, float* rowscale, cudaStream_t st);
 cudaError_t launch_gemm_tc5(const uint8_t* wt, int dtype, int n, int k, const __half* xh, int m, float* y, int ldy, const float* bias,
-                            const float* res, int ldres, cudaStream_t st, const Tc5Scratch* scratch = nullptr);
+                            const float* res, int ldres, cudaStream_t st, const Tc5Scratch* scratch = nullptr, const float* xscale = nullptr);
 struct Tc5Seg {
     const uint8_t* wt;  // tiled weights
     float* y;           // output base: element (m, r) at y[m * ldy + r]
@@ -192,7 +198,8 @@ struct Tc5Seg {
 };
 // Up to three matrices sharing the activations in ONE launch (q|k|v, gate|up); res is added to segment 0.
 cudaError_t launch_gemm_tc5_multi(const Tc5Seg* segs, int nseg, int k, const __half* xh, int m, int ldy, const float* res, int ldres,
-                                  cudaStream_t st, const Tc5Scratch* scratch = nullptr);
+                                  cudaStream_t st, const Tc5Scratch* scratch = nullptr, const float* xscale = nullptr);
+// xscale != null selects the exact mode: xh holds [2 m][k] as launch_x_to_f16_hilo writes it, xscale its row scales.
 
 cudaError_t launch_dequant(int dtype, const uint8_t* w, int64_t n, int64_t k, float* out, cudaStream_t st);
 cudaError_t launch_gemv(const GemvArgs& a, cudaStream_t st);

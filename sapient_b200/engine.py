@@ -45,7 +45,8 @@ class ForwardEngine:
         """cfg: arch ('llama'|'qwen2'|'phi2'), n_layers, hidden, n_heads, n_kv_heads, head_dim, ffn, vocab,
         max_ctx, rotary_dim (optional), norm_eps, rope_theta. weights: name -> (ggml dtype, dims, uint8 bytes)
         with HF names and [out, in] dims, as the reference's GGUF name map yields. fast_large_m: steps of 17 rows and
-        more on the tcgen05 GEMM with fp16 operands (see set_large_m_gemm)."""
+        more on the tcgen05 GEMM with operands rounded to fp16 instead of the default exact-class mode (see
+        set_large_m_gemm)."""
         d = SpModelDesc()
         d.arch = 1 if cfg["arch"] in ("phi2", "phi") else 0
         d.n_layers, d.hidden, d.n_heads, d.n_kv_heads = cfg["n_layers"], cfg["hidden"], cfg["n_heads"], cfg["n_kv_heads"]
@@ -283,9 +284,10 @@ class ForwardEngine:
     def set_graphs(self, on: bool) -> None:
         check(lib().sp_cuda_engine_set_graphs(self._h, int(on)))
 
-    def set_large_m_gemm(self, on: bool) -> None:
-        """Steps of 17 rows and more on the tcgen05 GEMM with fp16 operands (fast; final logits of full-size models may
-        leave the 2e-2 bar) or, the default, as integer-digit GEMV passes."""
+    def set_large_m_gemm(self, on) -> None:
+        """Steps of 17 rows and more: 2 (default) the tcgen05 GEMM with exact-class operands (leading fp16 part + remainder
+        of weights and activations); True / 1 the same GEMM with operands rounded to fp16 (2x faster; final logits of
+        full-size models may leave the 2e-2 bar); False / 0 integer-digit GEMV passes of 10 rows."""
         check(lib().sp_cuda_engine_set_large_m_gemm(self._h, int(on)))
 
     def set_many_row_gemv(self, on: bool) -> None:

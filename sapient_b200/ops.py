@@ -168,8 +168,13 @@ def set_gemv_path(path: int) -> None:
     check(lib().sp_cuda_set_gemv_path(path))
 
 
-def set_large_m_gemm(on: bool) -> None:
-    """Op-level matmuls with m >= 17 and k % 256 == 0 use the tcgen05 / TMEM dequant GEMM (default on)."""
+LARGE_M_DEFAULT = 2
+
+
+def set_large_m_gemm(on) -> None:
+    """Op-level matmuls with m >= 17 and k % 256 == 0: 2 (default) the tcgen05 / TMEM dequant GEMM with exact-class (leading
+    part + remainder) operands; 1 / True the same GEMM with operands rounded to fp16; 0 / False exact integer-digit passes
+    on the mma.sync kernels."""
     check(lib().sp_cuda_set_large_m_gemm(int(on)))
 
 

@@ -38,7 +38,8 @@ def measured_hbm_gbs() -> tuple[float, str]:
 
 def run_case(dtype_name: str, n: int, k: int, m: int, iters: int, warmup: int, rotate: int | None, path: int, seed: int = 0,
              large_m: bool = False):
-    """large_m: calls of 17 rows and more on the opt-in tcgen05 GEMM (fp16 operands) instead of the exact integer passes."""
+    """large_m: calls of 17 rows and more on the tcgen05 GEMM with operands rounded to fp16 instead of its default exact-class
+    mode."""
     import torch
 
     dtype = DTYPES[dtype_name]
@@ -59,7 +60,7 @@ def run_case(dtype_name: str, n: int, k: int, m: int, iters: int, warmup: int, r
     x = torch.randn(m, k, generator=g, device="cuda", dtype=torch.float32)
     y = torch.empty(m, n, device="cuda", dtype=torch.float32)
     ops.set_gemv_path(path)
-    ops.set_large_m_gemm(large_m)
+    ops.set_large_m_gemm(1 if large_m else ops.LARGE_M_DEFAULT)
     warmup = max(warmup, rotate)  # every rotated buffer has made its one-time allocations before the clock starts
     stream = torch.cuda.Stream()
     with torch.cuda.stream(stream):
@@ -73,7 +74,7 @@ def run_case(dtype_name: str, n: int, k: int, m: int, iters: int, warmup: int, r
         e1.record(stream)
         stream.synchronize()
     ops.set_gemv_path(0)
-    ops.set_large_m_gemm(False)
+    ops.set_large_m_gemm(ops.LARGE_M_DEFAULT)
     us = e0.elapsed_time(e1) * 1000.0 / iters
     alg = wbytes + 4 * m * k + 4 * m * n
     peak, src = measured_hbm_gbs()
@@ -83,7 +84,8 @@ def run_case(dtype_name: str, n: int, k: int, m: int, iters: int, warmup: int, r
     return {"op": "matmul_nt", "dtype": dtype_name, "n": n, "k": k, "m": m, "us": us, "gbs": gbs, "frac_of_8TBs": gbs / 8000.0,
             "frac_of_hbm_peak": gbs / peak, "peak_source": src, "tflops": 2.0 * m * n * k / us / 1e6, "weight_bytes": wbytes,
             "rotate": rotate, "iters": iters,
-            "kernel": "cuda-core" if path else ("tcgen05 (fp16 operands)" if large_m and m >= 17 else "tensor-core, exact integer products")}
+            "kernel": "cuda-core" if path else ("tcgen05, fp16 operands" if large_m and m >= 17 else
+                                                "tcgen05, exact-class operands" if m >= 17 else "tensor-core GEMV, exact integer products")}
 
 
 def main() -> None:
@@ -97,7 +99,7 @@ def main() -> None:
     ap.add_argument("--rotate", type=int, default=None)
     ap.add_argument("--path", type=int, default=0, help="0 tensor-core GEMV (default), 1 CUDA-core GEMV")
     ap.add_argument("--max-m", type=int, default=512)
-    ap.add_argument("--large-m", action="store_true", help="17 rows and more on the opt-in tcgen05 GEMM (fp16 operands)")
+    ap.add_argument("--large-m", action="store_true", help="17 rows and more on the tcgen05 GEMM with operands rounded to fp16 (default: exact-class operands)")
     a = ap.parse_args()
     dts = [a.dtype] if a.dtype else list(DTYPES)
     shapes = [(a.n, a.k)] if a.n and a.k else SHAPES

@@ -61,8 +61,10 @@ def _oracle_run(oracle, cfg, Wn, ids, steps, kv_mode, tokens=None):
     return np.stack(out), np.array(fed, np.uint32)
 
 
-def _cuda_run(cfg, Wn, ids, tokens, reference_cache, fast_large_m=False):
+def _cuda_run(cfg, Wn, ids, tokens, reference_cache, fast_large_m=False, large_m_mode=None):
     eng = ForwardEngine.from_weights(cfg, Wn, max_tokens=256, fast_large_m=fast_large_m)
+    if large_m_mode is not None:
+        eng.set_large_m_gemm(large_m_mode)
     eng.set_kv_rounding(reference_cache)
     out = [eng.forward_logits(ids, True)]
     for tok in tokens:
@@ -128,6 +130,28 @@ def test_full_size_model_logits_and_greedy_agreement(oracle, name, prompt_len, s
              "oracle_reordered_exact_top1": self_exact, "median_top2_gap": gap})
     assert worst <= max(LOGIT_BAR, SELF_FACTOR * self_worst), (worst, self_worst)
     assert exact >= min(need, self_exact), (exact, self_exact, steps)
+
+
+@pytest.mark.parametrize("name,prompt_len,steps", [c for c in CASES if c[0] in ("qwen05b", "llama8b", "phi2")])
+def test_exact_tensor_core_prompt_meets_the_same_bars(oracle, name, prompt_len, steps):
+    """The prompt (128 rows) on the tcgen05 GEMM with exact-class operands (mode 2: leading fp16 part + remainder of weights
+    and activations), decode steps unchanged: the bars of the default path, unloosened — 2e-2 on the final logits and
+    exact greedy agreement on >= 99 % of the steps, with the continuous cache rounding on both sides."""
+    import torch
+
+    cfg, W = synth.build_model(synth.CONFIGS[name], seed=3000, device="cuda", max_ctx=512)
+    Wn = synth.weights_to_numpy(W)
+    del W
+    torch.cuda.empty_cache()
+    ids = np.random.default_rng(0).integers(0, cfg["vocab"], prompt_len).astype(np.uint32)
+    steps = min(steps, 48)
+    want, toks = _oracle_run(oracle, cfg, Wn, ids, steps, kv_mode=1)
+    got = _cuda_run(cfg, Wn, ids, toks, reference_cache=False, large_m_mode=2)
+    worst, rms, exact, gap = _compare(oracle, got, want)
+    _report({"model": name, "prompt": prompt_len, "steps": steps, "cache": "fp16 both sides", "path": "tcgen05 prompt, exact-class operands",
+             "worst_dlogit": worst, "rms_dlogit": rms, "exact_top1": exact, "logit_std": float(want.std())})
+    assert worst < LOGIT_BAR, worst
+    assert exact >= int(np.ceil(AGREE * steps)), (exact, steps)
 
 
 @pytest.mark.parametrize("name,prompt_len,steps", [c for c in CASES if c[0] in ("qwen05b", "llama8b")])

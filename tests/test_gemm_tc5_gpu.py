@@ -1,5 +1,6 @@
 """Large-M dequant GEMM on tcgen05 / TMEM (gemm_tc5.cu) through sp_cuda_matmul_nt, against the CPU oracle and
-against the exact integer-product passes it can replace (it is opt-in: sp_cuda_set_large_m_gemm).
+against the exact integer-product passes (mode 0 of sp_cuda_set_large_m_gemm); mode 1 = operands rounded to fp16,
+mode 2 (the default) = exact-class operands.
 
 Bar: 1e-3 relative L2 per op. The kernel rounds the (exactly dequantised) weights and the activations to fp16 and
 accumulates in fp32, so it lands near 2e-4."""
@@ -13,16 +14,17 @@ pytestmark = pytest.mark.gpu
 Q8_0, Q4_K, Q6_K = synth.Q8_0, synth.Q4_K, synth.Q6_K
 
 
-def _large_m(on: bool) -> None:
+def _large_m(on) -> None:
     _lib.check(_lib.lib().sp_cuda_set_large_m_gemm(int(on)))
 
 
 @pytest.fixture(autouse=True)
 def _opt_in():
-    """The kernel under test is opt-in: on for this module's tests, off again afterwards."""
-    _large_m(True)
+    """Most tests here are about the fp16-operand mode (1); the process default (2, exact-class operands) is put back
+    afterwards."""
+    _large_m(1)
     yield
-    _large_m(False)
+    _large_m(2)
 
 
 # (m, k, n): m not a multiple of 16 / over 256 (two CTA columns), n not a multiple of 128 / 16, several K chunks
@@ -43,7 +45,7 @@ def test_large_m_gemm_matches_oracle_and_gemv(oracle, dtype, m, k, n):
         _large_m(False)
         gemv = ops.matmul_nt(x, raw, dtype, n)
     finally:
-        _large_m(False)
+        _large_m(1)
     assert got.shape == (m, n) and np.all(np.isfinite(got))
     assert rel_l2(gemv, want) < 3e-4
     err = rel_l2(got, want)
@@ -52,6 +54,34 @@ def test_large_m_gemm_matches_oracle_and_gemv(oracle, dtype, m, k, n):
     # every output element, not only the norm: a misplaced tile or a wrong swizzle shows up as O(1) errors
     scale = np.abs(want).max()
     assert np.abs(got - want).max() < 5e-3 * scale
+
+
+@pytest.mark.parametrize("dtype", [Q4_K, Q6_K, Q8_0])
+@pytest.mark.parametrize("m,k,n", CASES + [(32, 4096, 1024), (64, 2048, 640), (200, 4096, 300), (128, 14336, 256)])
+def test_exact_operand_mode_is_at_the_level_of_the_integer_path(oracle, dtype, m, k, n):
+    """Mode 2: weights and activations each as an fp16 leading part plus remainder, three products per chunk of K. The
+    result must sit where the exact integer-digit GEMV sits (2e-5 of the oracle, whose own f32 sums differ by that much
+    between summation orders), two hundred times below the fp16-operand mode."""
+    be, _ = synth.BLOCK[dtype]
+    rng = np.random.default_rng(m + k + n + 1)
+    raw = synth.random_bit_blocks(dtype, n * k // be, seed=m + n + dtype + 1)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    x[0, 3] = 250.0   # an outlier, a small row, a row far below the fp16 range and a zero row: rows are scaled by a power
+    x[1] *= 1e-3      # of two before they are split, so none of this reaches the fp16 limits
+    x[2] *= 1e-30
+    x[3] = 0.0
+    want = oracle.matmul_nt(x, raw, dtype, n)
+    try:
+        _large_m(2)
+        got = ops.matmul_nt(x, raw, dtype, n)
+        again = ops.matmul_nt(x, raw, dtype, n)
+    finally:
+        _large_m(True)
+    assert got.shape == (m, n) and np.all(np.isfinite(got))
+    assert np.array_equal(got, again)
+    assert np.all(got[3] == 0.0)
+    worst = max(rel_l2(got[i], want[i]) for i in range(m) if i != 3)
+    assert worst < 2e-5, worst
 
 
 @pytest.mark.parametrize("m,k,n", [(64, 128, 64), (40, 384, 130), (300, 896, 200), (33, 1152, 272)])

@@ -76,9 +76,25 @@ def test_matmul_nt_random_bits(oracle, gemv_path, dtype, m, k, n):
     err = rel_l2(got, want)
     assert err < REL_L2_BAR, err
     # cuda-core: f32 accumulation in a different order. tensor-core: exact integer products, activations held to 2^-23
-    # (three digits) of each 256-column block's maximum at every row count (the fp16 tcgen05 GEMM is opt-in and has its
-    # own tests).
+    # (three digits) of each 256-column block's maximum up to 16 rows; from 17 rows on the tcgen05 GEMM with exact-class
+    # operands (leading fp16 part + remainder).
     assert err < 2e-5, err
+
+
+@pytest.mark.parametrize("dtype", [Q4_K, Q6_K, Q8_0])
+@pytest.mark.parametrize("m,k,n", [c for c in MATMUL_CASES if c[0] >= 11])
+def test_matmul_nt_many_rows_on_the_integer_kernels(oracle, dtype, m, k, n):
+    """Mode 0: 11 rows and more on the one-pass mma.sync kernel (passes of up to 32 rows) instead of the tcgen05 GEMM."""
+    be, _ = synth.BLOCK[dtype]
+    rng = np.random.default_rng(m * 1000 + k + n)
+    raw = synth.random_bit_blocks(dtype, n * k // be, seed=k + n + dtype)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    try:
+        ops.set_large_m_gemm(0)
+        got = ops.matmul_nt(x, raw, dtype, n)
+    finally:
+        ops.set_large_m_gemm(ops.LARGE_M_DEFAULT)
+    assert rel_l2(got, oracle.matmul_nt(x, raw, dtype, n)) < 2e-5
 
 
 @pytest.mark.parametrize("dtype,m,k,n", [(Q4_K, 32, 4096, 1024), (Q6_K, 20, 2048, 640), (Q8_0, 64, 4096, 300)])
@@ -92,11 +108,13 @@ def test_many_row_pass_is_reproducible_and_equals_the_small_passes(oracle, dtype
     x = rng.standard_normal((m, k)).astype(np.float32)
     w = ops.Weight(dtype, n, k, raw)
     try:
+        ops.set_large_m_gemm(0)  # the mma.sync kernels (17 rows and more go to the tcgen05 GEMM by default)
         runs = [w.matmul_nt(x) for _ in range(5)]
         ops.set_gemv_path(2)
         small = w.matmul_nt(x)
     finally:
         ops.set_gemv_path(0)
+        ops.set_large_m_gemm(ops.LARGE_M_DEFAULT)
         w.free()
     for r in runs[1:]:
         assert np.array_equal(r.view(np.uint32), runs[0].view(np.uint32))

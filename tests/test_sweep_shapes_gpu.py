@@ -56,12 +56,12 @@ def test_matmul_nt_at_sweep_shapes(oracle, dtype_name, n, k):
             want = oracle.matmul_nt(x, sub.reshape(-1), dtype, pick.size)
             worst = max(rel_l2(got[i], want[i]) for i in range(m))
             assert worst < 1e-3, (dtype_name, n, k, m, worst)
-            if m >= 17:  # the opt-in tcgen05 GEMM (fp16 operands) on the same inputs
-                ops.set_large_m_gemm(True)
+            if m >= 17:  # the tcgen05 GEMM with operands rounded to fp16 (mode 1) on the same inputs
+                ops.set_large_m_gemm(1)
                 try:
                     got = w.matmul_nt(x)[:, pick]
                 finally:
-                    ops.set_large_m_gemm(False)
+                    ops.set_large_m_gemm(ops.LARGE_M_DEFAULT)
                 worst = max(rel_l2(got[i], want[i]) for i in range(m))
                 assert worst < 1e-3, (dtype_name, n, k, m, "tcgen05", worst)
     finally:
