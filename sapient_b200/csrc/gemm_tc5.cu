@@ -29,6 +29,7 @@
 
 #include <algorithm>
 #include <atomic>
+#include <type_traits>
 
 #include "kernels.h"
 #include "pdl.cuh"
@@ -338,9 +339,11 @@ __device__ __forceinline__ bool tc5_produce(const uint8_t* tile_row, bool row_li
     bool ok = true;
     const uint8_t* tile = tile_row + (int64_t)(HALF ? c_begin : c_begin >> 1) * TILE_BYTES;
     int s = -1, u = 0;  // stage of the current chunk and the number of times the ring has wrapped
-    // EXACT: a chunk is handed over three times — leading parts (for x's leading parts), remainders (for x's leading parts),
-    // leading parts again (for x's remainders) — into three consecutive stages; the weights are rebuilt once.
+    // EXACT: a stage is 128 columns wide — the leading parts in its first 64 columns, the remainders in the other 64 — and
+    // the ring has two stages instead of four; one hand-over per chunk either way.
+    constexpr int STAGES = EXACT ? TC5_A_STAGES / 2 : TC5_A_STAGES, STAGE_COLS = EXACT ? 128 : 64;
     auto build = [&](const Tc5Raw& raw, int cq) {  // next chunk: rebuild the weights in registers, wait for its stage, store
+        if (++s == STAGES) { s = 0; ++u; }
         Tc5Out o, ol;
         if (row_live) {
             tc5_convert<DT, EXACT>(raw, cq, o, ol);
@@ -348,18 +351,18 @@ __device__ __forceinline__ bool tc5_produce(const uint8_t* tile_row, bool row_li
 #pragma unroll
             for (int i = 0; i < 16; ++i) { o[i >> 2][i & 3] = 0u; ol[i >> 2][i & 3] = 0u; }  // rows past the matrix
         }
+        if (u > 0) ok = ok && tc5_wait(&empty_a[s], (uint32_t)((u - 1) & 1));  // the MMAs that last read this stage are done
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
 #pragma unroll
-        for (int j = 0; j < (EXACT ? 3 : 1); ++j) {
-            if (++s == TC5_A_STAGES) { s = 0; ++u; }
-            if (u > 0) ok = ok && tc5_wait(&empty_a[s], (uint32_t)((u - 1) & 1));  // the MMAs that last read this stage are done
-            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        for (int cg = 0; cg < 4; ++cg) tc5_tmem_st(a_base + (uint32_t)(STAGE_COLS * s + 8 * cg), o[cg]);
+        if (EXACT) {
 #pragma unroll
-            for (int cg = 0; cg < 4; ++cg) tc5_tmem_st(a_base + (uint32_t)(64 * s + 8 * cg), (EXACT && j == 1) ? ol[cg] : o[cg]);
-            asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
-            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-            __syncwarp();
-            if (lane == 0) tc5_arrive(&full_a[s]);
+            for (int cg = 0; cg < 4; ++cg) tc5_tmem_st(a_base + (uint32_t)(STAGE_COLS * s + 64 + 8 * cg), ol[cg]);
         }
+        asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+        asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+        __syncwarp();
+        if (lane == 0) tc5_arrive(&full_a[s]);
     };
     // two register sets: the loads of the next chunk are in flight while a chunk is rebuilt
     Tc5Raw raw_a, raw_b;
@@ -403,7 +406,8 @@ struct Tc5Args {
     int stage_bytes;    // 256 * (widest activation tile of the launch, rounded to 16): two boxes of 64 columns
     int stages;         // depth of the activation ring that fits shared memory (3..8)
     // 1: exact-class operands. xh holds [2 m][k]: rows 0..m-1 the fp16 leading parts of the activations, rows m..2m-1
-    // their remainders; the weights are split the same way by the producers. Every chunk of K is multiplied three times
+    // their remainders; the weights are split the same way by the producers (a weight stage of tensor memory holds both
+    // parts, an activation stage of shared memory both tiles: twice stage_bytes). Every chunk of K is multiplied three times
     // into the same accumulators — W_hi X_hi, W_lo X_hi, W_hi X_lo (the remainder x remainder term is below f32 rounding).
     int exact;
     const float* xscale;  // exact: [m] power-of-two factors the rows of xh were divided by
@@ -440,7 +444,7 @@ __global__ void __launch_bounds__(TC5_THREADS, 1) gemm_tc5_kernel(const Tc5Args 
     const int even = (a.k & 255) ? ~0 : ~1;  // (widths that are odd multiples of 128 exist only with one tile per chunk)
     const int c_begin = (int)((int64_t)part * all_chunks / parts) & even, c_end = (int)((int64_t)(part + 1) * all_chunks / parts) & even;
     const int n_chunks = c_end - c_begin;
-    const int reps = a.exact ? 3 : 1, n_handed = n_chunks * reps;  // stage hand-overs: three per chunk with exact operands
+    const int b_stage_bytes = a.exact ? 2 * a.stage_bytes : a.stage_bytes;
 
     if (warp == TC5_MMA_WARP) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tc5_smem_u32(&tmem_slot)), "r"(TC5_TMEM_COLS)
@@ -496,46 +500,61 @@ __global__ void __launch_bounds__(TC5_THREADS, 1) gemm_tc5_kernel(const Tc5Args 
             const uint64_t bd0 = tc5_desc(tc5_smem_u32(smem));
             const uint32_t bd_hi = (uint32_t)(bd0 >> 32), bd_lo0 = (uint32_t)bd0;
             const uint32_t stage16 = (uint32_t)a.stage_bytes >> 4, half16 = stage16 >> 1;
-            uint32_t accumulate = 0u;
-            for (int c = 0, sa = 0, ua = 0, sb = 0, ub = 0; c < n_handed; ++c, ++sa, ++sb) {
-                if (sa == TC5_A_STAGES) { sa = 0; ++ua; }
-                if (sb == a.stages) { sb = 0; ++ub; }
-                ok = ok && tc5_wait(&full_b[sb], (uint32_t)(ub & 1));  // after one expired wait nothing else is waited for
-                ok = ok && tc5_wait(&full_a[sa], (uint32_t)(ua & 1));
-                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                const uint32_t bd_lo = bd_lo0 + (uint32_t)sb * stage16;  // the address field: no carry out of the low word
-                const uint32_t At = tmem + (uint32_t)(TC5_NB_MAX + 64 * sa);
+            // two compile-time variants of the loop: the issuing thread is the serial part, a run-time test per MMA costs
+            auto issue_all = [&](auto exact_tag) {
+                constexpr bool EX = decltype(exact_tag)::value;
+                constexpr int A_STAGES = EX ? TC5_A_STAGES / 2 : TC5_A_STAGES;
+                constexpr uint32_t A_COLS = EX ? 128u : 64u;
+                const uint32_t b16 = EX ? 2u * stage16 : stage16;
+                uint32_t accumulate = 0u;
+                for (int c = 0, sa = 0, ua = 0, sb = 0, ub = 0; c < n_chunks; ++c, ++sa, ++sb) {
+                    if (sa == A_STAGES) { sa = 0; ++ua; }
+                    if (sb == a.stages) { sb = 0; ++ub; }
+                    ok = ok && tc5_wait(&full_b[sb], (uint32_t)(ub & 1));  // after one expired wait nothing else is waited for
+                    ok = ok && tc5_wait(&full_a[sa], (uint32_t)(ua & 1));
+                    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                    const uint32_t bd_lo = bd_lo0 + (uint32_t)sb * b16;  // the address field: no carry out of the low word
+                    const uint32_t At = tmem + (uint32_t)TC5_NB_MAX + A_COLS * (uint32_t)sa;
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {  // 16 columns each: 8 columns of tensor memory, 32 bytes inside the swizzle row (+2 x 16 B)
-                    const uint32_t lo = bd_lo + (uint32_t)(i >> 2) * half16 + 2u * (i & 3);
-                    uint64_t bd;
-                    asm("mov.b64 %0, {%1, %2};\n" : "=l"(bd) : "r"(lo), "r"(bd_hi));
-                    if (i == 0) tc5_mma_ts(tmem, At, bd, idesc, accumulate);
-                    else tc5_mma_ts_acc(tmem, At + 8u * i, bd, idesc);
+                    for (int i = 0; i < 8; ++i) {  // 16 columns each: 8 columns of tensor memory, 32 bytes inside the swizzle row (+2 x 16 B)
+                        const uint32_t lo = bd_lo + (uint32_t)(i >> 2) * half16 + 2u * (i & 3);
+                        uint64_t bd;
+                        asm("mov.b64 %0, {%1, %2};\n" : "=l"(bd) : "r"(lo), "r"(bd_hi));
+                        if (i == 0) tc5_mma_ts(tmem, At, bd, idesc, accumulate);
+                        else tc5_mma_ts_acc(tmem, At + 8u * i, bd, idesc);
+                        if (EX) {
+                            uint64_t bdl;  // the remainders' tile follows the leading parts' tile in the stage
+                            asm("mov.b64 %0, {%1, %2};\n" : "=l"(bdl) : "r"(lo + stage16), "r"(bd_hi));
+                            tc5_mma_ts_acc(tmem, At + 64u + 8u * i, bd, idesc);   // W_lo X_hi
+                            tc5_mma_ts_acc(tmem, At + 8u * i, bdl, idesc);        // W_hi X_lo
+                        }
+                    }
+                    accumulate = 1u;
+                    tc5_commit(&empty_a[sa]);
+                    tc5_commit(&empty_b[sb]);
                 }
-                accumulate = 1u;
-                tc5_commit(&empty_a[sa]);
-                tc5_commit(&empty_b[sb]);
-            }
+            };
+            if (a.exact) issue_all(std::true_type{});
+            else issue_all(std::false_type{});
             tc5_commit(&done_bar);  // arrives when every MMA above has completed
         }
     } else if (lane == 0) {
         // ── TMA: per chunk the activation tile as two boxes of (64 columns x nb_max rows), counted in bytes on `full_b` ──
-        for (int h = 0, sb = 0, ub = 0; h < n_handed; ++h, ++sb) {
-            const int c = h / reps, j = h - c * reps;
-            const int row = m0 + (j == 2 ? a.m : 0);  // the third hand-over of a chunk multiplies the activations' remainders
+        for (int c = 0, sb = 0, ub = 0; c < n_chunks; ++c, ++sb) {
             if (sb == a.stages) { sb = 0; ++ub; }
             if (ub > 0) ok = ok && tc5_wait(&empty_b[sb], (uint32_t)((ub - 1) & 1));
             const uint32_t bar = tc5_smem_u32(&full_b[sb]);
-            const uint32_t dst = tc5_smem_u32(smem + (size_t)sb * a.stage_bytes);
-            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(a.stage_bytes) : "memory");
+            const uint32_t dst = tc5_smem_u32(smem + (size_t)sb * b_stage_bytes);
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(b_stage_bytes) : "memory");
+            for (int part_x = 0; part_x < (a.exact ? 2 : 1); ++part_x) {  // exact: the leading parts' tile, then the remainders'
 #pragma unroll
-            for (int hh = 0; hh < 2; ++hh)
-                asm volatile(
-                    "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::"r"(
-                        dst + hh * (a.stage_bytes / 2)),
-                    "l"(&tmap_x), "r"((c_begin + c) * TC5_BK + 64 * hh), "r"(row), "r"(bar)
-                    : "memory");
+                for (int hh = 0; hh < 2; ++hh)
+                    asm volatile(
+                        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::"r"(
+                            dst + part_x * a.stage_bytes + hh * (a.stage_bytes / 2)),
+                        "l"(&tmap_x), "r"((c_begin + c) * TC5_BK + 64 * hh), "r"(m0 + part_x * a.m), "r"(bar)
+                        : "memory");
+            }
         }
     }
     if (pw >= 0) {
@@ -746,8 +765,8 @@ cudaError_t launch_gemm_tc5_multi(const Tc5Seg* segs, int nseg, int k, const __h
     const int sm_count = device_sm_count();
     const int nb_max = std::min(TC5_NB_MAX, (m + 15) & ~15);
     const int stage_bytes = nb_max * 256;
-    const int stages = std::min(TC5_MAX_STAGES, TC5_SMEM_LIMIT / stage_bytes);
-    const int smem_bytes = std::max(stages * stage_bytes + 1024, TC5_SMEM_MIN);  // + slack to align the stages to 1024 B
+    const int stages = std::min(TC5_MAX_STAGES, TC5_SMEM_LIMIT / (stage_bytes * (xscale ? 2 : 1)));  // exact: a stage holds two tiles
+    const int smem_bytes = std::max(stages * stage_bytes * (xscale ? 2 : 1) + 1024, TC5_SMEM_MIN);  // + slack to align the stages to 1024 B
     const int m_tiles = (m + TC5_NB_MAX - 1) / TC5_NB_MAX;
     const int chunks = k / TC5_BK, items = tiles * m_tiles;
     int full_items = items, tail_split = 1;
