@@ -59,8 +59,8 @@ int Engine::gemv(const float* x, int ldx, int m, int k, const DevTensor* w0, con
     float* ys[3] = {y0, y1, y2};
     bool tiled = true;
     for (int i = 0; i < 3 && ws[i]; ++i) tiled = tiled && ws[i]->tiled != nullptr;
-    if (tiled && !tp_sum && !pre && m >= TC5_MIN_M && use_tc5 && ws_.xh && (size_t)m * k * (tc5_exact ? 2 : 1) <= ws_.xh_elems &&
-        (!tc5_exact || m <= ActWorkspace::XSCALE_ROWS)) {
+    if (tiled && !pre && m >= TC5_MIN_M && use_tc5 && ws_.xh && (size_t)m * k * (tc5_exact ? 2 : 1) <= ws_.xh_elems &&
+        (!tc5_exact || m <= ActWorkspace::XSCALE_ROWS) && (!tp_sum || (y0 == x_ && res == x_ && ldy0 == d.hidden && !w1 && x != h_))) {
         bool ok = true;
         for (int i = 0; i < 3 && ws[i]; ++i) ok = ok && tc5_supported(ws[i]->dtype, k);
         if (ok) {
@@ -69,6 +69,20 @@ int Engine::gemv(const float* x, int ldx, int m, int k, const DevTensor* w0, con
             else SP_LAUNCH(F_ELEM, launch_x_to_f16(x, ldx, m, k, ws_.xh, stream));
             Tc5Seg segs[3];
             int ns = 0;
+            if (tp_sum) {
+                // column-split matrix: this rank's partial product to scratch (the bias once, on rank 0), then to every
+                // rank's receive area (or through the library all-reduce of the comparison arm)
+                segs[ns++] = Tc5Seg{w0->tiled, h_, d.tp_rank == 0 ? b0 : nullptr, w0->dtype, (int)w0->dims[0]};
+                SP_LAUNCH(F_GEMV, launch_gemm_tc5_multi(segs, ns, k, ws_.xh, m, d.hidden, nullptr, 0, stream, &ws_.tc5, tc5_exact ? ws_.xscale : nullptr));
+                if (tp_use_nccl_) {
+                    SP_TRY(nccl_all_reduce(h_, (size_t)m * d.hidden));
+                    SP_LAUNCH(F_ELEM, launch_add(x_, h_, x_, (int64_t)m * d.hidden, stream));
+                    return SP_OK;
+                }
+                SP_LAUNCH(F_GEMV, launch_tp_push(h_, d.hidden, m, d.hidden, d_tp_, stream));
+                tp_pending_ = true;
+                return SP_OK;
+            }
             for (int i = 0; i < 3 && ws[i]; ++i) segs[ns++] = Tc5Seg{ws[i]->tiled, ys[i], bs[i], ws[i]->dtype, (int)ws[i]->dims[0]};
             SP_LAUNCH(F_GEMV, launch_gemm_tc5_multi(segs, ns, k, ws_.xh, m, ldy0, res, ldy0, stream, &ws_.tc5, tc5_exact ? ws_.xscale : nullptr));
             return SP_OK;

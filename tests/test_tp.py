@@ -161,11 +161,13 @@ def _cuda_rank_main(rank, size, port, name, ids, steps, out_path):
     step = eng.forward_logits([int(ids[0])], True)     # 1-row decode step through the graph
     eng.truncate_cache(len(ids))
     toks = eng.decode_greedy([int(ids[0])], [0], steps)
-    # a 40-row step on the opt-in tcgen05 GEMM: column-split products go to scratch and are pushed by a separate kernel
-    eng.set_large_m_gemm(True)
+    # 40-row steps on the tcgen05 GEMM: column-split products go to scratch and are pushed by a separate kernel — in the
+    # fp16-rounded mode (1, with the fused fp16 producers) and in the default exact-class mode (2)
     ids40 = np.random.default_rng(40).integers(0, cfg["vocab"], 40).astype(np.uint32)
+    eng.set_large_m_gemm(1)
     big = eng.forward_all_logits(ids40)
-    eng.set_large_m_gemm(False)
+    eng.set_large_m_gemm(2)
+    big_exact = eng.forward_all_logits(ids40)
     # clearing the exchange state on every rank (host barrier before and after), then the first call again
     dist.barrier()
     eng.tp_reset()
@@ -182,7 +184,7 @@ def _cuda_rank_main(rank, size, port, name, ids, steps, out_path):
     back = eng.forward_all_logits(ids)
     dist.barrier()
     if rank == 0:
-        np.savez(out_path, prefill=prefill, step=step, toks=np.asarray(toks), big=big, again=again, nccl_prefill=nccl_prefill,
+        np.savez(out_path, prefill=prefill, step=step, toks=np.asarray(toks), big=big, big_exact=big_exact, again=again, nccl_prefill=nccl_prefill,
                  nccl_step=nccl_step, back=back)
     eng.close()
     dist.destroy_process_group()
@@ -218,8 +220,10 @@ def test_two_gpu_engine_matches_single_gpu(tmp_path):
     assert np.abs(got["nccl_step"] - got["step"]).max() < 1e-3
     assert np.array_equal(got["back"], got["prefill"])  # and the fused push again after switching back
     ids40 = np.random.default_rng(40).integers(0, cfg["vocab"], 40).astype(np.uint32)
-    one.set_large_m_gemm(True)
+    one.set_large_m_gemm(1)
     assert np.abs(got["big"] - one.forward_all_logits(ids40)).max() < 2e-2
+    one.set_large_m_gemm(2)
+    assert np.abs(got["big_exact"] - one.forward_all_logits(ids40)).max() < 2e-3  # exact-class operands on both sides
     # greedy tokens: equal unless the single-GPU logits had a near-tie at that step
     if not np.array_equal(got["toks"], want_toks):
         first = int(np.flatnonzero(got["toks"].reshape(-1) != want_toks.reshape(-1))[0])
