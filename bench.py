@@ -158,8 +158,9 @@ B32_BATCH, B32_PROMPT, B32_WARM, B32_STEPS = 32, 1024, 4, 24
 def batch32_section(cfg, W, wbytes: int, local: int, rank: int, world: int, stream, barrier, peaks) -> dict:
     """The other half of the metric: 32 sequences with 1024-token prompts decoded together over the paged fp16 KV cache
     (the tensor-parallel configuration of the benchmark at its own sizes; one GPU holds it whole, N GPUs split it).
-    Two timings of the same step at context ~1024: the default exact path (integer-digit GEMV passes of 10 rows) and
-    the opt-in tcgen05 GEMM (fp16 operands). Prompts are prefilled untimed through the tcgen05 path either way."""
+    Three timings of the same step at context ~1024: the default (tcgen05 GEMM with exact-class operands), the same GEMM
+    with operands rounded to fp16 (opt-in) and integer-digit GEMV passes of 10 rows (opt-in). Prompts are prefilled
+    untimed on the fastest path in every case."""
     import torch
 
     from sapient_b200.engine import ForwardEngine

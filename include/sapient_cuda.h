@@ -311,9 +311,10 @@ int32_t sp_cuda_engine_set_large_m_gemm(SpEngine* e, int32_t on);
 /* Steps of 1-5 rows on the bulk-copy ring GEMV with the preceding norm / activation fused into it (default off: it
  * measures slower than the default kernels). Drops the captured step graphs. */
 int32_t sp_cuda_engine_set_ring(SpEngine* e, int32_t on);
-/* 1: steps of 11 rows and more (prompts, batches) run as passes of up to 32 rows on the one-pass many-row GEMV — exact
- * integer products like the default passes of 10 rows, weights read once per 32 rows; 0 (default): passes of 10 rows on
- * the tile-row kernel. Same arithmetic, another order of the f32 additions over k. */
+/* For the steps that do not go to the tcgen05 GEMM (11-16 rows; every step of 11 rows and more when
+ * sp_cuda_engine_set_large_m_gemm is 0): 1 = passes of up to 32 rows on the one-pass many-row GEMV, weights read once per
+ * 32 rows; 0 (default) = passes of 10 rows on the tile-row kernel. The same exact integer products, another order of the
+ * f32 additions over k. */
 int32_t sp_cuda_engine_set_many_row_gemv(SpEngine* e, int32_t on);
 /* Per-kernel-family device timing (CUDA events around every launch; disables graphs while on). Families, in order:
  * gemv, attention, norm, rope_kv, elementwise, embed, argmax. Returns the family count; ms/launches accumulate

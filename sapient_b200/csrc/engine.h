@@ -110,10 +110,11 @@ class Engine {
     bool finalized = false;
     bool trace_on = false;
     bool use_graphs = true;
-    // Steps of 11 rows and more as passes of up to 32 rows on the one-pass kernel (gemv_rows.cu) instead of passes of 10 on
-    // the tile-row kernel. Off by default: inside a step the two cost the same (32-row step of the 8B shape: 15.97 vs
-    // 15.50 ms) — the one-pass kernel reads the weights once but launches per segment and cannot take digits written by
-    // the fused producers; as a stand-alone matmul it is 1.3x faster (op-level default).
+    // Steps of 11 rows and more that do not take the tcgen05 GEMM (11-16 rows, or use_tc5 off) as passes of up to 32 rows on
+    // the one-pass kernel (gemv_rows.cu) instead of passes of 10 on the tile-row kernel. Off by default: inside a step the
+    // two cost the same (32-row step of the 8B shape: 15.97 vs 15.50 ms) — the one-pass kernel reads the weights once but
+    // launches per segment and cannot take digits written by the fused producers; as a stand-alone matmul it is 1.3x
+    // faster (the op-level choice for 11-16 rows).
     bool use_rows = false;
     bool use_ring = false;     // steps of 1-5 rows on the bulk-copy ring GEMV (opt-in: measured slower than the tile-row kernels)
     // Steps of TC5_MIN_M rows and more (prompts, batches) run on the tcgen05 GEMM. tc5_exact (the default): its exact-class

@@ -22,6 +22,12 @@
 // fp16 rather than bf16 operands: same instruction kind and rate, and the 11-bit significand keeps the result within
 // ~2e-4 relative L2 of the f32 reference (bf16 would sit at ~2e-3, above the 1e-3 parity bar). Each weight is computed
 // in f32 from exact operands and rounded to fp16 once (Q8_0: the exact product of int8 and f16 scale, in half2).
+// Exact-class mode (Tc5Args::exact, the default of the callers): an fp16 operand carries 11 bits, so weights and
+// activations are each handed over as TWO fp16 numbers — the value rounded to fp16 and the fp16 of what that rounding
+// dropped (activation rows are first scaled by a power of two into (-1, 1), the epilogue multiplies it back) — and every
+// 16-column step issues three MMAs into the same accumulators: W_hi X_hi + W_lo X_hi + W_hi X_lo (the remainder x
+// remainder term is below f32 rounding). A tensor-memory stage then holds both weight parts (128 columns, ring of two),
+// a shared-memory stage both activation tiles. The result sits at ~1e-6 per product, the level of the integer GEMV.
 // Every wait on an mbarrier is bounded; on expiry the kernel raises g_tc5_timeout, still frees its tensor memory
 // and returns.
 #include <cuda.h>

@@ -292,7 +292,8 @@ class ForwardEngine:
 
     def set_many_row_gemv(self, on: bool) -> None:
         """Steps of 11 rows and more as passes of up to 32 rows on the one-pass GEMV (exact integer products, weights read
-        once per pass) instead of the default passes of 10 rows."""
+        once per pass) instead of passes of 10 rows — for the steps that do not go to the tcgen05 GEMM (11-16 rows, or
+        set_large_m_gemm(0))."""
         check(lib().sp_cuda_engine_set_many_row_gemv(self._h, int(on)))
 
     def set_ring(self, on: bool) -> None:

@@ -107,11 +107,13 @@ def test_cached_decode_equals_full_forward_and_chunking_is_invisible(oracle, nam
 @pytest.mark.parametrize("name", ["tiny_llama", "tiny_qwen", "tiny_llama_wide"])
 def test_many_row_gemv_passes_give_the_same_logits(oracle, name):
     """Prompts of 11 rows and more as passes of up to 32 rows on the one-pass GEMV (opt-in for engines): the same integer
-    products as the default passes of 10 rows, only the order of the f32 additions over k differs."""
+    products as passes of 10 rows on the tile-row kernel, only the order of the f32 additions over k differs. (Both are
+    what steps of 17 rows and more fall back to with the tcgen05 GEMM switched off; here it is off.)"""
     cfg, W = tiny_model(name)
     ids = prompt(cfg, 45, seed=8)  # 32 + 13 rows
     eng = ForwardEngine.from_weights(cfg, W, max_tokens=64)
     eng.set_kv_rounding(False)
+    eng.set_large_m_gemm(0)
     base = eng.forward_all_logits(ids)
     eng.set_many_row_gemv(True)
     rows = eng.forward_all_logits(ids)
@@ -244,11 +246,11 @@ def test_phi3_fused_gate_up_is_cut_at_upload(oracle):
     a.close(); b.close()
 
 
-@pytest.mark.parametrize("fast", [False, True], ids=["integer-digit-passes", "tcgen05-gemm"])
+@pytest.mark.parametrize("fast", [False, True], ids=["exact-class-operands", "fp16-rounded-operands"])
 def test_batched_decode_of_twenty_sequences_goes_through_the_large_m_path(oracle, fast):
-    """A 20-row decode step: by default two integer-digit GEMV passes of 10 rows (three digits: rows agree with each
-    sequence decoded alone to rounding), with the fast path on one tcgen05 GEMM launch per matrix (fp16 operands: rows
-    agree to the fp16 rounding of the operands). Attention runs unsplit either way."""
+    """A 20-row decode step is one tcgen05 GEMM launch per matrix: by default with exact-class operands (rows agree with
+    each sequence decoded alone to f32 rounding), with fast_large_m with operands rounded to fp16 (rows agree to that
+    rounding). Attention runs unsplit either way."""
     cfg, W = tiny_model("tiny_llama")
     B = 20
     eng = ForwardEngine.from_weights(cfg, W, max_batch=B, max_tokens=32, fast_large_m=fast)

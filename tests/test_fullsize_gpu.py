@@ -23,10 +23,11 @@ Per model, two comparisons, both with the bars of the task written out and no pe
     factor covers the scatter of a maximum over ~10^7 logits of two chaotic trajectories — and it agrees with the
     oracle's greedy pick at least as often as the reordered oracle does, or on 99 % of the steps.
 
-The engines run in their default configuration: every step on exact integer products with three-digit activations
-(prompts as passes of 10 rows). The opt-in fast path for steps of 17 rows and more (tcgen05 GEMM, fp16 operands,
-~3e-4 per product) is measured by a second test on the same inputs: its prompt leaves the 2e-2 bar on the largest
-model (that is why it is opt-in); what is asserted for it is that the deviation stays of the order of the fp16
+The engines run in their default configuration: decode steps on exact integer products with three-digit activations,
+prompts (steps of 17 rows and more) on the tcgen05 GEMM with exact-class operands (fp16 leading part + remainder of weights
+and activations, ~1e-6 per product). The same GEMM with operands rounded once to fp16 (~3e-4 per product, twice as fast)
+is measured by a further test on the same inputs: its prompt leaves the 2e-2 bar on the largest model (that is why it is
+not the default); what is asserted for it is that the deviation stays of the order of the fp16
 roundings it introduces — an O(1) fault (a misplaced tile) would be hundreds of times larger — and that greedy decoding
 still follows the oracle.
 
@@ -156,7 +157,7 @@ def test_exact_tensor_core_prompt_meets_the_same_bars(oracle, name, prompt_len, 
 
 @pytest.mark.parametrize("name,prompt_len,steps", [c for c in CASES if c[0] in ("qwen05b", "llama8b")])
 def test_fast_large_m_path_is_reported_and_sane(oracle, name, prompt_len, steps):
-    """The opt-in tcgen05 path for the prompt (fp16 operands), decode steps unchanged: numbers for the record, and two
+    """The tcgen05 GEMM with operands rounded to fp16 for the prompt (opt-in), decode steps unchanged: numbers for the record, and two
     sanity bounds — the logit deviation stays below 5 % of the logits' own spread (the fp16 roundings account for ~3 %
     on the 8B shape; a wrong tile would give ~100 %), and at least 95 % of the greedy picks equal the oracle's."""
     import torch
