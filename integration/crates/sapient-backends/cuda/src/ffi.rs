@@ -11,6 +11,10 @@ pub struct SpEngine {
 pub struct SpWeight {
     _opaque: [u8; 0],
 }
+#[repr(C)]
+pub struct SpBatcher {
+    _opaque: [u8; 0],
+}
 
 pub const SP_OK: i32 = 0;
 pub const SP_ERR_SHAPE: i32 = 1;
@@ -139,6 +143,33 @@ extern "C" {
         n_out: *mut usize,
         stats: *mut u64,
     ) -> i32;
+
+    pub fn sp_cuda_engine_slot_page(e: *const SpEngine, slot: i32, index: i32, page: *mut i32) -> i32;
+    pub fn sp_cuda_engine_adopt_prefix(e: *mut SpEngine, slot: i32, pages: *const i32, n: i32) -> i32;
+
+    pub fn sp_cuda_batcher_create(e: *mut SpEngine, prefill_chunk: i32, prefix_cache: i32, out: *mut *mut SpBatcher) -> i32;
+    pub fn sp_cuda_batcher_destroy(b: *mut SpBatcher);
+    pub fn sp_cuda_batcher_submit(
+        b: *mut SpBatcher,
+        prompt: *const u32,
+        n: usize,
+        max_new: usize,
+        eos_ids: *const u32,
+        n_eos: i32,
+        id: *mut u64,
+    ) -> i32;
+    pub fn sp_cuda_batcher_step(b: *mut SpBatcher, n_running: *mut i32, n_waiting: *mut i32) -> i32;
+    pub fn sp_cuda_batcher_poll(
+        b: *const SpBatcher,
+        id: u64,
+        tokens_out: *mut u32,
+        cap: usize,
+        n_tokens: *mut usize,
+        finished: *mut i32,
+    ) -> i32;
+    pub fn sp_cuda_batcher_cancel(b: *mut SpBatcher, id: u64) -> i32;
+    pub fn sp_cuda_batcher_forget(b: *mut SpBatcher, id: u64) -> i32;
+    pub fn sp_cuda_batcher_stats(b: *const SpBatcher, out: *mut u64, cap: i32) -> i32;
 
     pub fn sp_cuda_reset_cache(e: *mut SpEngine, slot: i32) -> i32;
     pub fn sp_cuda_truncate_cache(e: *mut SpEngine, slot: i32, n: usize, kept: *mut usize) -> i32;

@@ -289,6 +289,65 @@ pub fn spec_greedy(
     Ok((out, stats))
 }
 
+/// Continuous batching over one engine's sequence slots (greedy generations; prompt prefixes shared on reference-counted
+/// KV pages). The reference serves one sequence per engine (crates/sapient-generate/src/pipeline.rs:540-659) and lists
+/// batching as future work (docs/ROADMAP.md:312); a server's request loop calls `step` while anything is queued or running.
+pub struct CudaBatcher {
+    raw: *mut ffi::SpBatcher,
+    /// The batcher drives this engine; it stays alive (and must not be used directly) as long as the batcher does.
+    _engine: Box<CudaForwardEngine>,
+}
+
+unsafe impl Send for CudaBatcher {}
+
+impl CudaBatcher {
+    pub fn new(mut engine: Box<CudaForwardEngine>, prefill_chunk: usize, prefix_cache: bool) -> Result<Self> {
+        let mut raw = std::ptr::null_mut();
+        check(unsafe { ffi::sp_cuda_batcher_create(engine.raw(), prefill_chunk as i32, prefix_cache as i32, &mut raw) })?;
+        Ok(Self { raw, _engine: engine })
+    }
+
+    /// Queues a generation; the id names it in `poll` / `cancel` / `forget`.
+    pub fn submit(&mut self, prompt: &[u32], max_new: usize, eos: &[u32]) -> Result<u64> {
+        let mut id = 0u64;
+        check(unsafe {
+            ffi::sp_cuda_batcher_submit(self.raw, prompt.as_ptr(), prompt.len(), max_new, eos.as_ptr(), eos.len() as i32, &mut id)
+        })?;
+        Ok(id)
+    }
+
+    /// One scheduler iteration (admit, a bounded prefill chunk, one decode step); returns (running, waiting).
+    pub fn step(&mut self) -> Result<(usize, usize)> {
+        let (mut r, mut w) = (0i32, 0i32);
+        check(unsafe { ffi::sp_cuda_batcher_step(self.raw, &mut r, &mut w) })?;
+        Ok((r as usize, w as usize))
+    }
+
+    /// Tokens generated so far and whether the request has left the batch.
+    pub fn poll(&self, id: u64) -> Result<(Vec<u32>, bool)> {
+        let (mut n, mut fin) = (0usize, 0i32);
+        check(unsafe { ffi::sp_cuda_batcher_poll(self.raw, id, std::ptr::null_mut(), 0, &mut n, &mut fin) })?;
+        let mut out = vec![0u32; n];
+        check(unsafe { ffi::sp_cuda_batcher_poll(self.raw, id, out.as_mut_ptr(), out.len(), &mut n, &mut fin) })?;
+        out.truncate(n);
+        Ok((out, fin != 0))
+    }
+
+    pub fn cancel(&mut self, id: u64) -> Result<()> {
+        check(unsafe { ffi::sp_cuda_batcher_cancel(self.raw, id) })
+    }
+
+    pub fn forget(&mut self, id: u64) -> Result<()> {
+        check(unsafe { ffi::sp_cuda_batcher_forget(self.raw, id) })
+    }
+}
+
+impl Drop for CudaBatcher {
+    fn drop(&mut self) {
+        unsafe { ffi::sp_cuda_batcher_destroy(self.raw) } // before the engine it drives
+    }
+}
+
 /// The context window the CPU engines allocate (kv_cache_ctx, crates/sapient-models/src/forward/common.rs:25-37):
 /// min(model maximum, SAPIENT_CTX or 8192). Restated here because that function is private to sapient-models; when this
 /// crate is wired in, call the original instead.

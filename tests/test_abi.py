@@ -127,3 +127,26 @@ def test_product_never_imports_the_oracle():
             if f.endswith((".py", ".cu", ".cuh", ".h", ".cpp")):
                 src = open(os.path.join(dirpath, f)).read()
                 assert "oracle" not in src.lower(), f"{f} mentions the oracle"
+
+
+@pytest.mark.parametrize("name", ["tiny_llama", "tiny_qwen", "tiny_phi2", "tiny_phi3"])
+def test_gguf_of_every_family_parses_up_to_the_first_device_call(name, tmp_path):
+    """Header, metadata, name map, fused-tensor splits (Phi-2 q|k|v, Phi-3 q|k|v and gate|up) and every bounds check run
+    on the host before any device work: without a GPU the load must get as far as the first CUDA call (SP_ERR_CUDA) and
+    not stop at an IO / shape / dtype error. With a GPU it simply succeeds."""
+    import torch
+
+    from sapient_b200 import synth
+    from sapient_b200.engine import ForwardEngine
+
+    cfg, W = synth.build_model(synth.CONFIGS[name], seed=5, device="cpu", max_ctx=64)
+    if cfg["arch"] == "phi2":
+        W.pop("model.norm.bias")
+    path = str(tmp_path / f"{name}.gguf")
+    synth.write_gguf(path, cfg, W)
+    if torch.cuda.is_available():
+        ForwardEngine.from_gguf(path).close()
+        return
+    with pytest.raises(_lib.SapientCudaError) as e:
+        ForwardEngine.from_gguf(path)
+    assert e.value.status == _lib.SP_ERR_CUDA, (e.value.status, str(e.value))
