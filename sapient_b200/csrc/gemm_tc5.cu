@@ -27,7 +27,8 @@
 // dropped (activation rows are first scaled by a power of two into (-1, 1), the epilogue multiplies it back) — and every
 // 16-column step issues three MMAs into the same accumulators: W_hi X_hi + W_lo X_hi + W_hi X_lo (the remainder x
 // remainder term is below f32 rounding). A tensor-memory stage then holds both weight parts (128 columns, ring of two),
-// a shared-memory stage both activation tiles. The result sits at ~1e-6 per product, the level of the integer GEMV.
+// a shared-memory stage both activation tiles of the chunk (or, for tiles of more than 128 rows, 64 columns of both with
+// two hand-overs per chunk on that side). The result sits at ~1e-6 per product, the level of the integer GEMV.
 // Every wait on an mbarrier is bounded; on expiry the kernel raises g_tc5_timeout, still frees its tensor memory
 // and returns.
 #include <cuda.h>
@@ -413,7 +414,8 @@ struct Tc5Args {
     int stages;         // depth of the activation ring that fits shared memory (3..8)
     // 1: exact-class operands. xh holds [2 m][k]: rows 0..m-1 the fp16 leading parts of the activations, rows m..2m-1
     // their remainders; the weights are split the same way by the producers (a weight stage of tensor memory holds both
-    // parts, an activation stage of shared memory both tiles: twice stage_bytes). Every chunk of K is multiplied three times
+    // parts; an activation stage of shared memory holds both tiles of the chunk (1) or, for tiles of more than 128 rows,
+    // 64 columns of both row planes (2)). Every chunk of K is multiplied three times
     // into the same accumulators — W_hi X_hi, W_lo X_hi, W_hi X_lo (the remainder x remainder term is below f32 rounding).
     int exact;
     const float* xscale;  // exact: [m] power-of-two factors the rows of xh were divided by
@@ -450,7 +452,6 @@ __global__ void __launch_bounds__(TC5_THREADS, 1) gemm_tc5_kernel(const Tc5Args 
     const int even = (a.k & 255) ? ~0 : ~1;  // (widths that are odd multiples of 128 exist only with one tile per chunk)
     const int c_begin = (int)((int64_t)part * all_chunks / parts) & even, c_end = (int)((int64_t)(part + 1) * all_chunks / parts) & even;
     const int n_chunks = c_end - c_begin;
-    const int b_stage_bytes = a.exact ? 2 * a.stage_bytes : a.stage_bytes;
 
     if (warp == TC5_MMA_WARP) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tc5_smem_u32(&tmem_slot)), "r"(TC5_TMEM_COLS)
@@ -507,59 +508,98 @@ __global__ void __launch_bounds__(TC5_THREADS, 1) gemm_tc5_kernel(const Tc5Args 
             const uint32_t bd_hi = (uint32_t)(bd0 >> 32), bd_lo0 = (uint32_t)bd0;
             const uint32_t stage16 = (uint32_t)a.stage_bytes >> 4, half16 = stage16 >> 1;
             // two compile-time variants of the loop: the issuing thread is the serial part, a run-time test per MMA costs
-            auto issue_all = [&](auto exact_tag) {
-                constexpr bool EX = decltype(exact_tag)::value;
+            // MODE 0: operands rounded to fp16. MODE 1: exact-class, an activation stage holds both tiles of a chunk (twice
+            // stage_bytes; tiles of up to 128 rows). MODE 2: exact-class, an activation stage holds 64 columns of both row
+            // planes (stage_bytes; two hand-overs per chunk), so that 256-row tiles still have a ring of three stages.
+            auto issue_all = [&](auto mode_tag) {
+                constexpr int MODE = decltype(mode_tag)::value;
+                constexpr bool EX = MODE != 0;
                 constexpr int A_STAGES = EX ? TC5_A_STAGES / 2 : TC5_A_STAGES;
                 constexpr uint32_t A_COLS = EX ? 128u : 64u;
-                const uint32_t b16 = EX ? 2u * stage16 : stage16;
+                const uint32_t b16 = MODE == 1 ? 2u * stage16 : stage16;
                 uint32_t accumulate = 0u;
-                for (int c = 0, sa = 0, ua = 0, sb = 0, ub = 0; c < n_chunks; ++c, ++sa, ++sb) {
+                for (int c = 0, sa = 0, ua = 0, sb = 0, ub = 0; c < n_chunks; ++c, ++sa) {
                     if (sa == A_STAGES) { sa = 0; ++ua; }
-                    if (sb == a.stages) { sb = 0; ++ub; }
-                    ok = ok && tc5_wait(&full_b[sb], (uint32_t)(ub & 1));  // after one expired wait nothing else is waited for
+                    if (MODE != 2) {
+                        if (sb == a.stages) { sb = 0; ++ub; }
+                        ok = ok && tc5_wait(&full_b[sb], (uint32_t)(ub & 1));  // after one expired wait nothing else is waited for
+                    }
                     ok = ok && tc5_wait(&full_a[sa], (uint32_t)(ua & 1));
                     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                    const uint32_t bd_lo = bd_lo0 + (uint32_t)sb * b16;  // the address field: no carry out of the low word
                     const uint32_t At = tmem + (uint32_t)TC5_NB_MAX + A_COLS * (uint32_t)sa;
+                    if (MODE != 2) {
+                        const uint32_t bd_lo = bd_lo0 + (uint32_t)sb * b16;  // the address field: no carry out of the low word
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) {  // 16 columns each: 8 columns of tensor memory, 32 bytes inside the swizzle row (+2 x 16 B)
-                        const uint32_t lo = bd_lo + (uint32_t)(i >> 2) * half16 + 2u * (i & 3);
-                        uint64_t bd;
-                        asm("mov.b64 %0, {%1, %2};\n" : "=l"(bd) : "r"(lo), "r"(bd_hi));
-                        if (i == 0) tc5_mma_ts(tmem, At, bd, idesc, accumulate);
-                        else tc5_mma_ts_acc(tmem, At + 8u * i, bd, idesc);
-                        if (EX) {
-                            uint64_t bdl;  // the remainders' tile follows the leading parts' tile in the stage
-                            asm("mov.b64 %0, {%1, %2};\n" : "=l"(bdl) : "r"(lo + stage16), "r"(bd_hi));
-                            tc5_mma_ts_acc(tmem, At + 64u + 8u * i, bd, idesc);   // W_lo X_hi
-                            tc5_mma_ts_acc(tmem, At + 8u * i, bdl, idesc);        // W_hi X_lo
+                        for (int i = 0; i < 8; ++i) {  // 16 columns each: 8 columns of tensor memory, 32 bytes inside the swizzle row (+2 x 16 B)
+                            const uint32_t lo = bd_lo + (uint32_t)(i >> 2) * half16 + 2u * (i & 3);
+                            uint64_t bd;
+                            asm("mov.b64 %0, {%1, %2};\n" : "=l"(bd) : "r"(lo), "r"(bd_hi));
+                            if (i == 0) tc5_mma_ts(tmem, At, bd, idesc, accumulate);
+                            else tc5_mma_ts_acc(tmem, At + 8u * i, bd, idesc);            // W (or W_hi) X (X_hi)
+                            if (MODE == 1) {
+                                uint64_t bdl;  // the remainders' tile follows the leading parts' tile in the stage
+                                asm("mov.b64 %0, {%1, %2};\n" : "=l"(bdl) : "r"(lo + stage16), "r"(bd_hi));
+                                tc5_mma_ts_acc(tmem, At + 64u + 8u * i, bd, idesc);       // W_lo X_hi
+                                tc5_mma_ts_acc(tmem, At + 8u * i, bdl, idesc);            // W_hi X_lo
+                            }
+                        }
+                        tc5_commit(&empty_b[sb]);
+                        ++sb;
+                    } else {
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            if (sb == a.stages) { sb = 0; ++ub; }
+                            ok = ok && tc5_wait(&full_b[sb], (uint32_t)(ub & 1));
+                            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                            const uint32_t bd_lo = bd_lo0 + (uint32_t)sb * stage16;
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                const uint32_t i = 4u * h + j;
+                                uint64_t bd, bdl;  // the leading parts' box, then the remainders' box
+                                asm("mov.b64 %0, {%1, %2};\n" : "=l"(bd) : "r"(bd_lo + 2u * j), "r"(bd_hi));
+                                asm("mov.b64 %0, {%1, %2};\n" : "=l"(bdl) : "r"(bd_lo + half16 + 2u * j), "r"(bd_hi));
+                                if (i == 0) tc5_mma_ts(tmem, At, bd, idesc, accumulate);
+                                else tc5_mma_ts_acc(tmem, At + 8u * i, bd, idesc);          // W_hi X_hi
+                                tc5_mma_ts_acc(tmem, At + 64u + 8u * i, bd, idesc);           // W_lo X_hi
+                                tc5_mma_ts_acc(tmem, At + 8u * i, bdl, idesc);                // W_hi X_lo
+                            }
+                            tc5_commit(&empty_b[sb]);
+                            ++sb;
                         }
                     }
                     accumulate = 1u;
                     tc5_commit(&empty_a[sa]);
-                    tc5_commit(&empty_b[sb]);
                 }
             };
-            if (a.exact) issue_all(std::true_type{});
-            else issue_all(std::false_type{});
+            if (a.exact == 2) issue_all(std::integral_constant<int, 2>{});
+            else if (a.exact == 1) issue_all(std::integral_constant<int, 1>{});
+            else issue_all(std::integral_constant<int, 0>{});
             tc5_commit(&done_bar);  // arrives when every MMA above has completed
         }
     } else if (lane == 0) {
         // ── TMA: per chunk the activation tile as two boxes of (64 columns x nb_max rows), counted in bytes on `full_b` ──
-        for (int c = 0, sb = 0, ub = 0; c < n_chunks; ++c, ++sb) {
+        // exact == 1: a stage is the chunk's two tiles (leading parts, then remainders: rows m0 + m ..), twice stage_bytes.
+        // exact == 2: a stage is 64 columns of the chunk — the leading parts' box and the remainders' box — two hand-overs
+        // per chunk, so that 256-row tiles still have a ring of three stages.
+        const int per_chunk = a.exact == 2 ? 2 : 1;
+        const int b_bytes = a.exact == 1 ? 2 * a.stage_bytes : a.stage_bytes;
+        for (int h = 0, sb = 0, ub = 0; h < n_chunks * per_chunk; ++h, ++sb) {
+            const int c = a.exact == 2 ? (h >> 1) : h, half = a.exact == 2 ? (h & 1) : 0;
             if (sb == a.stages) { sb = 0; ++ub; }
             if (ub > 0) ok = ok && tc5_wait(&empty_b[sb], (uint32_t)((ub - 1) & 1));
             const uint32_t bar = tc5_smem_u32(&full_b[sb]);
-            const uint32_t dst = tc5_smem_u32(smem + (size_t)sb * b_stage_bytes);
-            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(b_stage_bytes) : "memory");
-            for (int part_x = 0; part_x < (a.exact ? 2 : 1); ++part_x) {  // exact: the leading parts' tile, then the remainders'
-#pragma unroll
-                for (int hh = 0; hh < 2; ++hh)
-                    asm volatile(
-                        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::"r"(
-                            dst + part_x * a.stage_bytes + hh * (a.stage_bytes / 2)),
-                        "l"(&tmap_x), "r"((c_begin + c) * TC5_BK + 64 * hh), "r"(m0 + part_x * a.m), "r"(bar)
-                        : "memory");
+            const uint32_t dst = tc5_smem_u32(smem + (size_t)sb * b_bytes);
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(b_bytes) : "memory");
+            for (int bx = 0; bx < (a.exact == 1 ? 4 : 2); ++bx) {
+                // plain: the chunk's two 64-column boxes; exact 1: the same for both row planes; exact 2: one 64-column box
+                // of each row plane
+                const int plane = a.exact == 1 ? (bx >> 1) : a.exact == 2 ? bx : 0;
+                const int colbox = a.exact == 2 ? half : (bx & 1);
+                asm volatile(
+                    "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::"r"(
+                        dst + bx * (a.stage_bytes / 2)),
+                    "l"(&tmap_x), "r"((c_begin + c) * TC5_BK + 64 * colbox), "r"(m0 + plane * a.m), "r"(bar)
+                    : "memory");
             }
         }
     }
@@ -771,8 +811,11 @@ cudaError_t launch_gemm_tc5_multi(const Tc5Seg* segs, int nseg, int k, const __h
     const int sm_count = device_sm_count();
     const int nb_max = std::min(TC5_NB_MAX, (m + 15) & ~15);
     const int stage_bytes = nb_max * 256;
-    const int stages = std::min(TC5_MAX_STAGES, TC5_SMEM_LIMIT / (stage_bytes * (xscale ? 2 : 1)));  // exact: a stage holds two tiles
-    const int smem_bytes = std::max(stages * stage_bytes * (xscale ? 2 : 1) + 1024, TC5_SMEM_MIN);  // + slack to align the stages to 1024 B
+    // exact-class operands: whole-chunk activation stages (two tiles) while at least three fit, else half-chunk stages
+    const int exact_mode = !xscale ? 0 : (TC5_SMEM_LIMIT / (2 * stage_bytes) >= 3 ? 1 : 2);
+    const int b_stage_bytes = exact_mode == 1 ? 2 * stage_bytes : stage_bytes;
+    const int stages = std::min(TC5_MAX_STAGES, TC5_SMEM_LIMIT / b_stage_bytes);
+    const int smem_bytes = std::max(stages * b_stage_bytes + 1024, TC5_SMEM_MIN);  // + slack to align the stages to 1024 B
     const int m_tiles = (m + TC5_NB_MAX - 1) / TC5_NB_MAX;
     const int chunks = k / TC5_BK, items = tiles * m_tiles;
     int full_items = items, tail_split = 1;
@@ -807,7 +850,7 @@ cudaError_t launch_gemm_tc5_multi(const Tc5Seg* segs, int nseg, int k, const __h
     a.nseg = nseg; a.k = k; a.xh = xh; a.m = m; a.ldy = ldy; a.res = res; a.ldres = ldres;
     a.m_tiles = m_tiles; a.full_items = full_items; a.tail_split = tail_split;
     a.stage_bytes = stage_bytes; a.stages = stages;
-    a.exact = exact ? 1 : 0;
+    a.exact = exact_mode;
     a.xscale = xscale;
     constexpr int SMEM_CAP = TC5_SMEM_LIMIT + 1024;
     cudaError_t le;
