@@ -150,3 +150,14 @@ def test_gguf_of_every_family_parses_up_to_the_first_device_call(name, tmp_path)
     with pytest.raises(_lib.SapientCudaError) as e:
         ForwardEngine.from_gguf(path)
     assert e.value.status == _lib.SP_ERR_CUDA, (e.value.status, str(e.value))
+
+
+def test_nccl_arm_reports_a_missing_library_instead_of_crashing():
+    """The library all-reduce arm opens NCCL at run time from a caller-named path: a wrong path is a status code and a
+    message, and an undersized id buffer is refused before anything is opened."""
+    L = _lib.lib()
+    buf = C.create_string_buffer(128)
+    assert L.sp_cuda_nccl_unique_id(b"/nonexistent/libnccl.so.2", buf, 128) == _lib.SP_ERR_STATE
+    assert b"NCCL" in L.sp_cuda_last_error()
+    assert L.sp_cuda_nccl_unique_id(b"/nonexistent/libnccl.so.2", buf, 64) == _lib.SP_ERR_ARG
+    assert L.sp_cuda_engine_tp_set_allreduce(None, 1) == _lib.SP_ERR_ARG
