@@ -1,6 +1,7 @@
-"""Generates tests/golden/golden_v1.npz from the CPU oracle.
+"""Generates tests/golden/golden_v1.npz (and, with --v2, golden_v2.npz: the block formats and the model family added
+later, kept in a file of their own so that the first fixture never has to be regenerated) from the CPU oracle.
 
-    python tests/golden/make_golden.py
+    python tests/golden/make_golden.py [--v2]
 
 The reference is Rust and cannot be built in this environment, so these vectors come
 from the oracle after it has been pinned against the reference's own known-answer
@@ -49,7 +50,30 @@ def model_case(name):
     return out
 
 
+OUT2 = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden_v2.npz")
+
+
+def main_v2():
+    """Q4_0 and Q5_K blocks (dequant + matmul) and the Phi-3-shaped tiny model."""
+    data = {}
+    rng = np.random.default_rng(43)
+    for dtype, tag in ((synth.Q4_0, "q4_0"), (synth.Q5_K, "q5_k")):
+        n, k, m = 6, 512, 3
+        raw = synth.random_bit_blocks(dtype, n * k // synth.BLOCK[dtype][0], seed=dtype)
+        x = rng.standard_normal((m, k)).astype(np.float32)
+        data[f"{tag}_blocks"] = raw
+        data[f"{tag}_x"] = x
+        data[f"{tag}_dequant"] = oracle.dequant(dtype, raw, n * k).reshape(n, k)
+        data[f"{tag}_y"] = oracle.matmul_nt(x, raw, dtype, n)
+    for key, val in model_case("tiny_phi3").items():
+        data[f"tiny_phi3_{key}"] = val
+    np.savez_compressed(OUT2, **data)
+    print(OUT2, os.path.getsize(OUT2), "bytes")
+
+
 def main():
+    if "--v2" in sys.argv:
+        return main_v2()
     data = {}
     rng = np.random.default_rng(42)
     for dtype, tag in ((synth.Q4_K, "q4_k"), (synth.Q6_K, "q6_k"), (synth.Q8_0, "q8_0")):

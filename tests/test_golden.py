@@ -1,5 +1,5 @@
-"""Committed golden vectors (tests/golden/golden_v1.npz, made by tests/golden/make_golden.py):
-the oracle must still reproduce them on CPU; the CUDA path must match them on a GPU."""
+"""Committed golden vectors (tests/golden/golden_v1.npz and golden_v2.npz — the formats and the model family added later —
+made by tests/golden/make_golden.py): the oracle must still reproduce them on CPU; the CUDA path must match them on a GPU."""
 import os
 import sys
 
@@ -12,8 +12,10 @@ from sapient_b200 import synth
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.join(HERE, "golden"))
 G = np.load(os.path.join(HERE, "golden", "golden_v1.npz"))
-TYPES = [(synth.Q4_K, "q4_k"), (synth.Q6_K, "q6_k"), (synth.Q8_0, "q8_0")]
-MODELS = ["tiny_llama", "tiny_qwen", "tiny_phi2"]
+G2 = np.load(os.path.join(HERE, "golden", "golden_v2.npz"))
+G = {**{k: G[k] for k in G.files}, **{k: G2[k] for k in G2.files}}
+TYPES = [(synth.Q4_K, "q4_k"), (synth.Q6_K, "q6_k"), (synth.Q8_0, "q8_0"), (synth.Q4_0, "q4_0"), (synth.Q5_K, "q5_k")]
+MODELS = ["tiny_llama", "tiny_qwen", "tiny_phi2", "tiny_phi3"]
 
 
 @pytest.mark.parametrize("dtype,tag", TYPES)
