@@ -273,7 +273,8 @@ int32_t sp_cuda_engine_adopt_prefix(SpEngine* e, int32_t slot, const int32_t* pa
  *   2. at most prefill_chunk prompt tokens of the oldest prefilling requests;
  *   3. one decode step carrying one token of every decoding sequence.
  * A request leaves the batch after an id of its eos list or max_new tokens; its slot is free for the next iteration.
- * Single thread per batcher. Errors of the engine calls are returned by the step that made them. */
+ * Single thread per batcher. Errors of the engine calls are returned by the step that made them. Destroy the batcher
+ * before the engine it drives (its destructor returns the slots' pages to the engine's pool). */
 typedef struct SpBatcher SpBatcher;
 int32_t sp_cuda_batcher_create(SpEngine* e, int32_t prefill_chunk, int32_t prefix_cache, SpBatcher** out);
 /* The same scheduler over a host stand-in instead of an engine (no GPU, no model: the "next token" is a hash of the

@@ -30,7 +30,8 @@ class BatcherStats:
 
 class ContinuousBatcher:
     def __init__(self, engine, prefill_chunk: int = 256, prefix_cache: bool = True):
-        """engine: a finalised ForwardEngine with empty caches; its max_batch is the number of concurrent sequences."""
+        """engine: a finalised ForwardEngine with empty caches; its max_batch is the number of concurrent sequences. Close
+        the batcher before the engine."""
         self._h = C.c_void_p()
         self._engine = engine  # keeps the engine alive
         check(lib().sp_cuda_batcher_create(engine._h, int(prefill_chunk), int(bool(prefix_cache)), C.byref(self._h)))
