@@ -161,3 +161,46 @@ def test_nccl_arm_reports_a_missing_library_instead_of_crashing():
     assert b"NCCL" in L.sp_cuda_last_error()
     assert L.sp_cuda_nccl_unique_id(b"/nonexistent/libnccl.so.2", buf, 64) == _lib.SP_ERR_ARG
     assert L.sp_cuda_engine_tp_set_allreduce(None, 1) == _lib.SP_ERR_ARG
+
+
+def test_gguf_loader_survives_corrupted_headers(tmp_path):
+    """GGUF files are downloaded content: whatever bytes the header, metadata and tensor table hold, the loader must answer
+    with a status code (an IO / shape / dtype / state error, or SP_ERR_CUDA once it reaches device work on a machine
+    without a GPU) and never read outside the mapping. 400 seeded corruptions of a valid file: single bytes, 64-bit
+    fields set to extreme values, truncations."""
+    import torch
+
+    from sapient_b200 import synth
+    from sapient_b200.engine import ForwardEngine
+
+    cfg, W = synth.build_model(synth.CONFIGS["tiny_llama"], seed=6, device="cpu", max_ctx=64)
+    good = str(tmp_path / "good.gguf")
+    synth.write_gguf(good, cfg, W)
+    data = bytearray(open(good, "rb").read())
+    # the header region: everything before the first tensor's bytes (found by parsing nothing: corrupt the first 6 KB)
+    region = min(len(data), 6144)
+    rng = np.random.default_rng(1234)
+    bad = str(tmp_path / "bad.gguf")
+    extreme = [0, 1, 0xFFFFFFFF, 0x7FFFFFFFFFFFFFFF, 0xFFFFFFFFFFFFFFFF, 0x8000000000000000, 1 << 40]
+    ok_status = {_lib.SP_ERR_IO, _lib.SP_ERR_SHAPE, _lib.SP_ERR_DTYPE, _lib.SP_ERR_STATE, _lib.SP_ERR_ARG, _lib.SP_ERR_CUDA,
+                 _lib.SP_ERR_OOM, _lib.SP_ERR_KV_FULL}
+    for trial in range(400):
+        buf = bytearray(data)
+        kind = trial % 3
+        if kind == 0:
+            for _ in range(int(rng.integers(1, 4))):
+                buf[int(rng.integers(4, region))] = int(rng.integers(0, 256))
+        elif kind == 1:
+            at = int(rng.integers(4, region - 8))
+            buf[at:at + 8] = int(extreme[int(rng.integers(0, len(extreme)))]).to_bytes(8, "little")
+        else:
+            buf = buf[: int(rng.integers(5, len(buf)))]
+        with open(bad, "wb") as f:
+            f.write(buf)
+        try:
+            eng = ForwardEngine.from_gguf(bad)
+        except _lib.SapientCudaError as e:
+            assert e.status in ok_status, (trial, e.status, str(e))
+        else:
+            assert torch.cuda.is_available()  # a harmless corruption (an unused byte): only a GPU box gets this far
+            eng.close()
