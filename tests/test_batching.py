@@ -259,3 +259,52 @@ def test_copy_on_write_of_a_shared_partial_page():
     ref = eng.forward_slot(2, p + [3], all_positions=False)
     np.testing.assert_allclose(nxt, ref, atol=2e-3)
     eng.close()
+
+
+@pytest.mark.parametrize("seed", [0, 1, 2, 3])
+def test_random_arrivals_cancellations_and_tight_pools_keep_every_invariant(seed):
+    """Seeded stress of the scheduling logic on the host stand-in: requests with shared and unshared prefixes arrive at
+    random iterations, some are cancelled while queued, prefilling or decoding, the pool is a fraction of what all of them
+    would need at once. After every iteration the pool balances (free + index pages + pages of running slots = total);
+    at the end every request that was not cancelled equals its solo generation and every page is free or indexed."""
+    rng = np.random.default_rng(seed)
+    n_pages, slots, ctx = int(rng.integers(10, 30)), int(rng.integers(1, 6)), 160
+    b = ContinuousBatcher.selftest(VOCAB, max_slots=slots, max_ctx=ctx, n_pages=n_pages, prefill_chunk=int(rng.integers(4, 50)),
+                                   prefix_cache=True)
+    shared = [rng.integers(0, VOCAB, int(n)).tolist() for n in (33, 48, 17)]
+    want, cancelled, pending = {}, set(), []
+    for _ in range(60):
+        base = shared[int(rng.integers(0, 3))] if rng.random() < 0.6 else []
+        p = base + rng.integers(0, VOCAB, int(rng.integers(1, 40))).tolist()
+        mn = int(rng.integers(1, 30))
+        if (len(p) + mn + 15) // 16 > n_pages or len(p) + mn > ctx:
+            continue
+        pending.append((int(rng.integers(0, 120)), p, mn))
+    pending.sort(key=lambda t: t[0])
+    it, live = 0, []
+    while pending or live:
+        while pending and pending[0][0] <= it:
+            _, p, mn = pending.pop(0)
+            rid = b.submit(p, mn)
+            want[rid] = _alone(p, mn)
+            live.append(rid)
+        if live and rng.random() < 0.08:
+            victim = live[int(rng.integers(0, len(live)))]
+            b.cancel(victim)
+            cancelled.add(victim)
+        b.step()
+        s = b.stats()
+        assert 0 <= s.free_pages <= n_pages and s.cached_pages <= n_pages
+        live = [r for r in live if not b.poll(r)[1]]
+        it += 1
+        assert it < 20000, "scheduler stopped making progress"
+    for rid, w in want.items():
+        got, fin = b.poll(rid)
+        assert fin
+        if rid in cancelled:
+            assert got.tolist() == w[: len(got)]  # whatever it had produced before the cancel is still right
+        else:
+            assert got.tolist() == w, rid
+    s = b.stats()
+    assert s.free_pages + s.cached_pages == n_pages
+    b.close()
