@@ -110,9 +110,9 @@ def decode_case(name: str, prompt_len: int, steps: int, batch: int, label: str, 
     return line
 
 
-def prefill_case(name: str, prompt_len: int, reps: int = 3) -> dict:
+def prefill_case(name: str, prompt_len: int, reps: int = 3, fast: bool = False) -> dict:
     cfg, W = _build(name, max_ctx=prompt_len + 64, seed=3000)
-    eng, stream = _engine(cfg, W, max_tokens=min(prompt_len, 1024))
+    eng, stream = _engine(cfg, W, max_tokens=min(prompt_len, 1024), fast_large_m=fast)
     ids = np.random.default_rng(0).integers(0, cfg["vocab"], prompt_len).astype(np.uint32)
     eng.forward_logits(ids, False)  # one-time allocations and attribute settings
     ms = min(_timed(stream, lambda: eng.forward_logits(ids, False)) for _ in range(reps))
@@ -122,7 +122,8 @@ def prefill_case(name: str, prompt_len: int, reps: int = 3) -> dict:
     eng.set_profile(False)
     eng.close()
     return {"case": "prefill", "model": name, "prompt_len": prompt_len, "ms": ms, "tokens_per_s": prompt_len / (ms / 1e3),
-            "families": fam, "data": "synthetic"}
+            "families": fam, "data": "synthetic",
+            "large_m_path": "tcgen05 GEMM, operands rounded to fp16 (opt-in)" if fast else "tcgen05 GEMM, exact-class operands (default)"}
 
 
 def spec_case(k: int, prompt_len: int, new_tokens: int) -> dict:
@@ -226,7 +227,7 @@ def main() -> None:
     elif a.case == "c3b32":
         line = decode_case("llama8b", a.prompt or 256, a.steps or 64, 32, "c3b32", prefill_timed=True, fast=a.fast)
     elif a.case == "prefill":
-        line = prefill_case(a.model, a.prompt or 512)
+        line = prefill_case(a.model, a.prompt or 512, fast=a.fast)
     elif a.case == "load":
         line = load_case(a.model)
     else:
