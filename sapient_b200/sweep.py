@@ -37,9 +37,9 @@ def measured_hbm_gbs() -> tuple[float, str]:
 
 
 def run_case(dtype_name: str, n: int, k: int, m: int, iters: int, warmup: int, rotate: int | None, path: int, seed: int = 0,
-             large_m: bool = False):
+             large_m: bool = False, large_m_mode: int | None = None):
     """large_m: calls of 17 rows and more on the tcgen05 GEMM with operands rounded to fp16 instead of its default exact-class
-    mode."""
+    mode. large_m_mode: the mode number itself (0 integer passes on the mma.sync kernels, 1 fp16-rounded, 2 exact-class)."""
     import torch
 
     dtype = DTYPES[dtype_name]
@@ -60,7 +60,8 @@ def run_case(dtype_name: str, n: int, k: int, m: int, iters: int, warmup: int, r
     x = torch.randn(m, k, generator=g, device="cuda", dtype=torch.float32)
     y = torch.empty(m, n, device="cuda", dtype=torch.float32)
     ops.set_gemv_path(path)
-    ops.set_large_m_gemm(1 if large_m else ops.LARGE_M_DEFAULT)
+    mode = large_m_mode if large_m_mode is not None else (1 if large_m else ops.LARGE_M_DEFAULT)
+    ops.set_large_m_gemm(mode)
     warmup = max(warmup, rotate)  # every rotated buffer has made its one-time allocations before the clock starts
     stream = torch.cuda.Stream()
     with torch.cuda.stream(stream):
@@ -84,8 +85,9 @@ def run_case(dtype_name: str, n: int, k: int, m: int, iters: int, warmup: int, r
     return {"op": "matmul_nt", "dtype": dtype_name, "n": n, "k": k, "m": m, "us": us, "gbs": gbs, "frac_of_8TBs": gbs / 8000.0,
             "frac_of_hbm_peak": gbs / peak, "peak_source": src, "tflops": 2.0 * m * n * k / us / 1e6, "weight_bytes": wbytes,
             "rotate": rotate, "iters": iters,
-            "kernel": "cuda-core" if path else ("tcgen05, fp16 operands" if large_m and m >= 17 else
-                                                "tcgen05, exact-class operands" if m >= 17 else "tensor-core GEMV, exact integer products")}
+            "kernel": "cuda-core" if path else ("tcgen05, fp16 operands" if mode == 1 and m >= 17 else
+                                                "tcgen05, exact-class operands" if mode == 2 and m >= 17 else
+                                                "tensor-core GEMV (mma.sync), exact integer products")}
 
 
 def main() -> None:
@@ -100,6 +102,8 @@ def main() -> None:
     ap.add_argument("--path", type=int, default=0, help="0 tensor-core GEMV (default), 1 CUDA-core GEMV")
     ap.add_argument("--max-m", type=int, default=512)
     ap.add_argument("--large-m", action="store_true", help="17 rows and more on the tcgen05 GEMM with operands rounded to fp16 (default: exact-class operands)")
+    ap.add_argument("--large-m-mode", type=int, choices=[0, 1, 2], default=None,
+                    help="17 rows and more: 0 integer passes on the mma.sync kernels, 1 tcgen05 fp16-rounded, 2 tcgen05 exact-class (default)")
     a = ap.parse_args()
     dts = [a.dtype] if a.dtype else list(DTYPES)
     shapes = [(a.n, a.k)] if a.n and a.k else SHAPES
@@ -107,7 +111,7 @@ def main() -> None:
     for dt in dts:
         for n, k in shapes:
             for m in ms:
-                print(json.dumps(run_case(dt, n, k, m, a.iters, a.warmup, a.rotate, a.path, large_m=a.large_m)), flush=True)
+                print(json.dumps(run_case(dt, n, k, m, a.iters, a.warmup, a.rotate, a.path, large_m=a.large_m, large_m_mode=a.large_m_mode)), flush=True)
 
 
 if __name__ == "__main__":
